@@ -1,0 +1,148 @@
+/*
+ * px_b200 -- C ABI of the sm_100a Pairformer pair-representation kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (a `cudaStream_t` passed as `void*`; NULL = the legacy default stream), launches
+ * asynchronously on that stream and returns PX_OK or a negative status.  Nothing here
+ * allocates device memory: intermediate tensors are carved from a caller-provided
+ * workspace whose size the `*_workspace_bytes` functions report.  No exception crosses
+ * this boundary.  Entry points are re-entrant across streams as long as calls do not
+ * share output or workspace memory.
+ *
+ * Conventions
+ *   - N            number of tokens; the pair tensor z is [N][N][128], row-major, channel last.
+ *   - z_dtype      storage type of the residual stream: PX_F32 or PX_BF16.  All matrix
+ *                  products take bf16 operands and accumulate in fp32.
+ *   - weights      bf16, row-major [out_features][in_features] exactly as the reference's
+ *                  nn.Linear.weight (cast to bf16 by the caller); LayerNorm scale/offset fp32.
+ *   - mask         fp32 [N][N] (1 = keep, 0 = masked) or NULL for all ones.
+ *   - ld           px_ld(N): N rounded up to a multiple of 8; row stride (in elements) of the
+ *                  intermediate tensors so that every row starts on a 16-byte boundary.
+ *
+ * The reference interfaces each entry point stands in for are cited as file:line of
+ * bytedance/Protenix v2.0.0.
+ */
+#ifndef PX_B200_H_
+#define PX_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PX_OK 0
+#define PX_ERR_BAD_ARG (-1)     /* null pointer, non-positive size, misaligned pointer */
+#define PX_ERR_UNSUPPORTED (-2) /* shape / dtype outside the compiled specialisations   */
+#define PX_ERR_LAUNCH (-3)      /* the CUDA runtime refused the launch                  */
+#define PX_ERR_WORKSPACE (-4)   /* workspace too small                                  */
+
+#define PX_F32 0
+#define PX_BF16 1
+#define PX_F16 2
+
+typedef uint16_t px_bf16; /* storage of one bfloat16 */
+
+#if defined(__GNUC__)
+#define PX_API __attribute__((visibility("default")))
+#else
+#define PX_API
+#endif
+
+/* Library version (major*10000 + minor*100 + patch). */
+PX_API int32_t px_version(void);
+/* Static, human-readable text for a status code. */
+PX_API const char* px_status_string(int32_t status);
+/* Leading dimension used for intermediates: N rounded up to a multiple of 8. */
+PX_API int64_t px_ld(int64_t n);
+
+/* ---- LayerNorm op ---------------------------------------------------------------------
+ * y = (x - mean) * rsqrt(var + eps) * gamma + beta over the last axis of x[rows][cols];
+ * gamma and/or beta may be NULL (the four affine variants).  x, y, gamma, beta share `dtype`
+ * (PX_F32, PX_BF16, PX_F16); mean and invvar are fp32 [rows] (may be NULL when not wanted).
+ * Replaces the pybind functions forward_{none,with_bias,with_weight,with_both}_affine of
+ * protenix/model/layer_norm/kernel/layer_norm_cuda.cpp:142-160 (wrapper :73-90, kernel
+ * layer_norm_cuda_kernel.cu:145-388).  Unlike the reference it launches on `stream`. */
+PX_API int32_t px_layer_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* invvar,
+                          int64_t rows, int64_t cols, float eps, int32_t dtype, void* stream);
+
+/* ---- Triangle multiplication (outgoing / incoming) ---------------------------------------
+ * Stage 1: zn = LN(z); a = mask * sigmoid(W_ag zn) * (W_ap zn); b likewise.  a and b are
+ * written channel-major, contraction index contiguous: a[c][i][k] (row stride ld), zero in
+ * the pad columns k >= N.  For `incoming` the two token indices are exchanged on the way out
+ * (a[c][i][k] holds the reference's a[k][i][c]) so that stage 2 is the same product for both.
+ * Replaces protenix/model/triangular/triangular.py:535-543. */
+PX_API int32_t px_trimul_in_proj(const void* z, int32_t z_dtype, const float* mask, const float* ln_w, const float* ln_b,
+                          const px_bf16* w_ap, const px_bf16* w_ag, const px_bf16* w_bp, const px_bf16* w_bg,
+                          px_bf16* a, px_bf16* b, int64_t n, int64_t ld, int32_t incoming, float eps, void* stream);
+/* Stage 2: x[c][i][j] = sum_k a[c][i][k] * b[c][j][k] for the 128 channels (bf16 in, fp32
+ * accumulate, bf16 out, row stride ld).  Replaces _combine_projections,
+ * protenix/model/triangular/triangular.py:123-150. */
+PX_API int32_t px_trimul_contract(const px_bf16* a, const px_bf16* b, px_bf16* x, int64_t n, int64_t ld, void* stream);
+/* Stage 3: z_out = [z_in +] W_z LN_out(x) * sigmoid(W_g LN_in(z_in)).  z_out may alias z_in.
+ * Replaces protenix/model/triangular/triangular.py:559-565. */
+PX_API int32_t px_trimul_out(const px_bf16* x, const void* z_in, void* z_out, int32_t z_dtype, const float* ln_in_w,
+                      const float* ln_in_b, const float* ln_out_w, const float* ln_out_b, const px_bf16* w_z,
+                      const px_bf16* w_g, int64_t n, int64_t ld, int32_t add_residual, float eps, void* stream);
+/* Bytes of workspace px_triangle_multiplication needs for N tokens (a, b and x). */
+PX_API int64_t px_trimul_workspace_bytes(int64_t n);
+/* The three stages in sequence.  Stands in for TriangleMultiplicativeUpdate.forward,
+ * protenix/model/triangular/triangular.py:470-570 (and for the cuEquivariance call
+ * :28-90 the reference can dispatch to). */
+PX_API int32_t px_triangle_multiplication(const void* z_in, void* z_out, int32_t z_dtype, const float* mask,
+                                   const float* ln_in_w, const float* ln_in_b, const float* ln_out_w,
+                                   const float* ln_out_b, const px_bf16* w_ap, const px_bf16* w_ag,
+                                   const px_bf16* w_bp, const px_bf16* w_bg, const px_bf16* w_z, const px_bf16* w_g,
+                                   void* workspace, int64_t workspace_bytes, int64_t n, int32_t incoming,
+                                   int32_t add_residual, float eps, void* stream);
+
+/* ---- Triangle attention (starting / ending node), 4 heads x 32 -------------------------
+ * Stage 1: xn = LN(z); q,k,v = W xn written per attended row u as [u][h][t][32] bf16 with q
+ * pre-scaled by log2(e)/sqrt(32); bias[h][u][t] = log2(e) * (W_b xn)[u][t][h] (fp32, row
+ * stride ld); mask_bias[u][t] = log2(e) * inf * (mask - 1) (fp32, row stride ld).  For the
+ * ending node the pair element read for (u,t) is z[t][u] and mask[t][u], which is what the
+ * reference obtains by transposing z (protenix/model/modules/pairformer.py:160-168).
+ * Replaces protenix/model/triangular/triangular.py:683-692 and layers.py:361-382. */
+PX_API int32_t px_triatt_in_proj(const void* z, int32_t z_dtype, const float* mask, const float* ln_w, const float* ln_b,
+                          const px_bf16* w_q, const px_bf16* w_k, const px_bf16* w_v, const px_bf16* w_bias,
+                          px_bf16* q, px_bf16* k, px_bf16* v, float* bias, float* mask_bias, int64_t n, int64_t ld,
+                          int32_t ending, float eps, float inf, void* stream);
+/* Stage 2: o[u][t][h*32+d] = softmax_k(q.k + bias[h][t][k] + mask_bias[u][k]) v, online
+ * softmax in base 2, logits never leave the SM.  Replaces the back-ends selected in
+ * protenix/model/triangular/layers.py:441-469 (_attention :276-296, the Triton kernel
+ * protenix/model/tri_attention/forward.py:22-188, DS4Sci and cuEquivariance calls). */
+PX_API int32_t px_triatt_flash(const px_bf16* q, const px_bf16* k, const px_bf16* v, const float* bias,
+                        const float* mask_bias, px_bf16* o, int64_t n, int64_t ld, void* stream);
+/* Stage 3: z_out(u,t) = [z_in(u,t) +] W_o (o[u][t] * sigmoid(W_g LN(z_in(u,t)))), where (u,t)
+ * addresses z[u][t] (starting) or z[t][u] (ending).  z_out may alias z_in.
+ * Replaces Attention._wrap_up, protenix/model/triangular/layers.py:384-398. */
+PX_API int32_t px_triatt_out(const px_bf16* o, const void* z_in, void* z_out, int32_t z_dtype, const float* ln_w,
+                      const float* ln_b, const px_bf16* w_g, const px_bf16* w_o, int64_t n, int32_t ending,
+                      int32_t add_residual, float eps, void* stream);
+PX_API int64_t px_triatt_workspace_bytes(int64_t n);
+/* The three stages in sequence.  Stands in for TriangleAttention.forward,
+ * protenix/model/triangular/triangular.py:657-715. */
+PX_API int32_t px_triangle_attention(const void* z_in, void* z_out, int32_t z_dtype, const float* mask, const float* ln_w,
+                              const float* ln_b, const px_bf16* w_bias, const px_bf16* w_q, const px_bf16* w_k,
+                              const px_bf16* w_v, const px_bf16* w_g, const px_bf16* w_o, void* workspace,
+                              int64_t workspace_bytes, int64_t n, int32_t ending, int32_t add_residual, float eps,
+                              float inf, void* stream);
+
+/* ---- Transition (SwiGLU), c = 128, expansion 4 -------------------------------------------
+ * x_out = [x_in +] W_o( silu(W_a LN(x_in)) * (W_b LN(x_in)) ) over rows of 128 channels; the
+ * [rows][512] intermediates stay on chip.  x_out may alias x_in.
+ * Replaces Transition.forward, protenix/model/modules/primitives.py:190-230. */
+PX_API int32_t px_transition(const void* x_in, void* x_out, int32_t dtype, const float* ln_w, const float* ln_b,
+                      const px_bf16* w_a, const px_bf16* w_b, const px_bf16* w_o, int64_t rows, int32_t add_residual,
+                      float eps, void* stream);
+
+/* ---- Pair bias for the single-representation attention ----------------------------------
+ * out[h][row] = (W LN(z[row]))[h] for h < n_heads (<= 16), fp32; ln_b may be NULL.
+ * Replaces protenix/model/modules/transformer.py:185-188. */
+PX_API int32_t px_pair_bias_proj(const void* z, int32_t z_dtype, const float* ln_w, const float* ln_b, const px_bf16* w,
+                          float* out, int64_t rows, int32_t n_heads, float eps, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PX_B200_H_ */

@@ -1,0 +1,195 @@
+"""CPU oracle for the Pairformer pair-representation forward path.
+
+TEST INFRASTRUCTURE ONLY.  This file is the checker, never the product: it may be imported
+by ``tests/``, by ``__graft_entry__.smoke()`` and by the CPU-baseline leg of ``bench.py``;
+nothing under ``protenix_b200/`` imports it.
+
+It is an independent restatement, in plain torch tensor algebra, of what the reference
+(bytedance/Protenix v2.0.0, torch back-end, eval mode) computes.  Every function names the
+reference lines it follows.  Parity of this restatement with the reference itself is pinned
+by ``tests/golden/`` (vectors produced by importing the reference, see
+``tests/golden/make_golden.py``) and checked by ``tests/test_oracle_golden.py``.
+
+All functions take plain tensors plus a flat ``dict`` of parameters whose keys are the
+reference's ``state_dict`` keys relative to the module (e.g. ``"tri_mul_out.linear_g.weight"``).
+Arithmetic runs in the dtype of the inputs (fp32 by default, fp64 for tighter checks).
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+Params = Dict[str, torch.Tensor]
+
+
+def _sub(p: Params, prefix: str) -> Params:
+    """Parameters below ``prefix.`` with the prefix stripped."""
+    n = len(prefix) + 1
+    return {k[n:]: v for k, v in p.items() if k.startswith(prefix + ".")}
+
+
+def layer_norm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+               eps: float = 1e-5) -> torch.Tensor:
+    """y = (x - mean) * rsqrt(var_biased + eps) * weight + bias over the last axis.
+
+    Follows protenix/model/triangular/layers.py:200-243 (OpenFoldLayerNorm) and the CUDA op
+    protenix/model/layer_norm/kernel/layer_norm_cuda_kernel.cu:145-229 (biased variance,
+    optional scale / offset).
+    """
+    mu = x.mean(dim=-1, keepdim=True)
+    xc = x - mu
+    var = (xc * xc).mean(dim=-1, keepdim=True)
+    y = xc * torch.rsqrt(var + eps)
+    if weight is not None:
+        y = y * weight
+    if bias is not None:
+        y = y + bias
+    return y
+
+
+def layer_norm_stats(x: torch.Tensor, eps: float = 1e-5) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(mean, invvar) per row as the reference op returns them for its backward
+    (protenix/model/layer_norm/kernel/layer_norm_cuda.cpp:73-90)."""
+    mu = x.mean(dim=-1)
+    var = ((x - mu[..., None]) ** 2).mean(dim=-1)
+    return mu, torch.rsqrt(var + eps)
+
+
+def transition(x: torch.Tensor, p: Params) -> torch.Tensor:
+    """SwiGLU transition: W_o( silu(W_a LN(x)) * (W_b LN(x)) ), no residual.
+
+    Follows protenix/model/modules/primitives.py:190-230.
+    """
+    y = layer_norm(x, p["layernorm1.weight"], p["layernorm1.bias"])
+    a = y @ p["linear_no_bias_a.weight"].T
+    b = y @ p["linear_no_bias_b.weight"].T
+    return (F.silu(a) * b) @ p["linear_no_bias.weight"].T
+
+
+def triangle_multiplication(z: torch.Tensor, mask: Optional[torch.Tensor], p: Params,
+                            outgoing: bool) -> torch.Tensor:
+    """Triangle multiplicative update (returns the update, without the residual).
+
+    Follows protenix/model/triangular/triangular.py:519-566 (functional branch) and
+    :123-150 (_combine_projections): outgoing x[i,j,c] = sum_k a[i,k,c] b[j,k,c],
+    incoming x[i,j,c] = sum_k a[k,i,c] b[k,j,c]; the mask multiplies a and b after gating.
+    """
+    if mask is None:
+        mask = z.new_ones(z.shape[:-1])
+    m = mask[..., None]
+    zn = layer_norm(z, p["layer_norm_in.weight"], p["layer_norm_in.bias"])
+    a = m * torch.sigmoid(zn @ p["linear_a_g.weight"].T) * (zn @ p["linear_a_p.weight"].T)
+    b = m * torch.sigmoid(zn @ p["linear_b_g.weight"].T) * (zn @ p["linear_b_p.weight"].T)
+    if outgoing:
+        x = torch.einsum("ikc,jkc->ijc", a, b)
+    else:
+        x = torch.einsum("kic,kjc->ijc", a, b)
+    x = layer_norm(x, p["layer_norm_out.weight"], p["layer_norm_out.bias"])
+    x = x @ p["linear_z.weight"].T
+    g = torch.sigmoid(zn @ p["linear_g.weight"].T)
+    return x * g
+
+
+def triangle_attention(x: torch.Tensor, mask: Optional[torch.Tensor], p: Params,
+                       starting: bool = True, inf: float = 1e9,
+                       row_chunk: Optional[int] = None) -> torch.Tensor:
+    """Triangle attention around the starting node (``starting=False``: ending node, i.e.
+    the same thing on the transposed pair tensor).  Returns the update, no residual.
+
+    Follows protenix/model/triangular/triangular.py:657-715 and the torch attention of
+    protenix/model/triangular/layers.py:276-296, :361-398:
+    L[i,h,q,k] = (q[i,q,h]/sqrt(d)) . k[i,k,h] + inf*(mask[i,k]-1) + (W_b LN(x))[q,k,h],
+    softmax over k, o = P v, out = W_o(o * sigmoid(W_g LN(x))).
+    ``row_chunk`` only bounds memory (rows i are independent).
+    """
+    if mask is None:
+        mask = x.new_ones(x.shape[:-1])
+    if not starting:
+        x = x.transpose(0, 1)
+        mask = mask.transpose(0, 1)
+    n = x.shape[0]
+    h = p["linear.weight"].shape[0]
+    xn = layer_norm(x, p["layer_norm.weight"], p["layer_norm.bias"])
+    tri_bias = (xn @ p["linear.weight"].T).permute(2, 0, 1)          # [H, Q, K]
+    d = p["mha.linear_q.weight"].shape[0] // h
+    out = torch.empty_like(xn)
+    step = n if row_chunk is None else row_chunk
+    for r0 in range(0, n, step):
+        xr = xn[r0:r0 + step]
+        q = (xr @ p["mha.linear_q.weight"].T).view(-1, n, h, d) / math.sqrt(d)
+        k = (xr @ p["mha.linear_k.weight"].T).view(-1, n, h, d)
+        v = (xr @ p["mha.linear_v.weight"].T).view(-1, n, h, d)
+        logits = torch.einsum("iqhd,ikhd->ihqk", q, k)
+        logits = logits + (inf * (mask[r0:r0 + step] - 1))[:, None, None, :] + tri_bias[None]
+        w = torch.softmax(logits, dim=-1)
+        o = torch.einsum("ihqk,ikhd->iqhd", w, v)
+        g = torch.sigmoid(xr @ p["mha.linear_g.weight"].T).view(-1, n, h, d)
+        out[r0:r0 + step] = (o * g).reshape(-1, n, h * d) @ p["mha.linear_o.weight"].T
+    if not starting:
+        out = out.transpose(0, 1)
+    return out
+
+
+def attention_pair_bias(s: torch.Tensor, z: torch.Tensor, p: Params, n_heads: int) -> torch.Tensor:
+    """Single-representation attention with pair bias, has_s=False variant (no residual).
+
+    Follows protenix/model/modules/transformer.py:159-254 (standard_multihead_attention)
+    and protenix/model/modules/primitives.py:233-291, :782-879: q has a bias term, logits are
+    q.k/sqrt(d) + W_z LN(z), gate sigmoid(W_g a) applied before the output projection.
+    """
+    a = layer_norm(s, p["layernorm_a.weight"], p["layernorm_a.bias"])
+    bias = layer_norm(z, p["layernorm_z.weight"], p.get("layernorm_z.bias")) @ p["linear_nobias_z.weight"].T
+    bias = bias.permute(2, 0, 1)                                      # [H, N, N]
+    n, c = a.shape
+    d = c // n_heads
+    q = (a @ p["attention.linear_q.weight"].T + p["attention.linear_q.bias"]).view(n, n_heads, d)
+    k = (a @ p["attention.linear_k.weight"].T).view(n, n_heads, d)
+    v = (a @ p["attention.linear_v.weight"].T).view(n, n_heads, d)
+    logits = torch.einsum("qhd,khd->hqk", q / math.sqrt(d), k) + bias
+    w = torch.softmax(logits, dim=-1)
+    o = torch.einsum("hqk,khd->qhd", w, v).reshape(n, c)
+    g = torch.sigmoid(a @ p["attention.linear_g.weight"].T)
+    return (o * g) @ p["attention.linear_o.weight"].T
+
+
+def pairformer_block(s: Optional[torch.Tensor], z: torch.Tensor, pair_mask: Optional[torch.Tensor],
+                     p: Params, n_heads: int = 16, row_chunk: Optional[int] = None
+                     ) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
+    """One Pairformer block in eval mode (dropout is the identity).
+
+    Follows protenix/model/modules/pairformer.py:103-224.  The reference transposes z,
+    runs a starting-node module on it and transposes back (:160-168); here the ending-node
+    form of ``triangle_attention`` does the same arithmetic.
+    """
+    z = z + triangle_multiplication(z, pair_mask, _sub(p, "tri_mul_out"), outgoing=True)
+    z = z + triangle_multiplication(z, pair_mask, _sub(p, "tri_mul_in"), outgoing=False)
+    z = z + triangle_attention(z, pair_mask, _sub(p, "tri_att_start"), starting=True, row_chunk=row_chunk)
+    z = z + triangle_attention(z, pair_mask, _sub(p, "tri_att_end"), starting=False, row_chunk=row_chunk)
+    z = z + transition(z, _sub(p, "pair_transition"))
+    if s is not None and any(k.startswith("attention_pair_bias.") for k in p):
+        s = s + attention_pair_bias(s, z, _sub(p, "attention_pair_bias"), n_heads)
+        s = s + transition(s, _sub(p, "single_transition"))
+    return s, z
+
+
+def pairformer_stack(s: Optional[torch.Tensor], z: torch.Tensor, pair_mask: Optional[torch.Tensor],
+                     p: Params, n_blocks: int, n_heads: int = 16, row_chunk: Optional[int] = None
+                     ) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
+    """``n_blocks`` blocks in sequence; parameter keys are ``blocks.{i}.<block key>``.
+
+    Follows protenix/model/modules/pairformer.py:291-340 (no-grad path of checkpoint_blocks,
+    protenix/model/utils.py:865-866: a plain loop).
+    """
+    for i in range(n_blocks):
+        s, z = pairformer_block(s, z, pair_mask, _sub(p, f"blocks.{i}"), n_heads, row_chunk)
+    return s, z
+
+
+def rel_frobenius(a: torch.Tensor, b: torch.Tensor) -> float:
+    """||a - b||_F / ||b||_F in fp64."""
+    a = a.detach().double().cpu()
+    b = b.detach().double().cpu()
+    return float((a - b).norm() / b.norm().clamp_min(1e-30))

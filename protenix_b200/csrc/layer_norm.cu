@@ -1,0 +1,191 @@
+// Stand-alone LayerNorm forward over the last axis (general width, fp32 / bf16 / fp16).
+//
+// HBM-bound: 2 * cols * sizeof(T) algorithmic bytes per row.  One warp owns a row; the row is
+// held in registers between the statistics and the write-back (cols <= 32*VEC*kMaxIt), so x is
+// read from HBM exactly once.  VEC is the widest vector (up to 16 bytes) that divides cols.
+#include <cuda_fp16.h>
+
+#include "px_common.cuh"
+
+namespace px {
+
+template <typename T>
+struct Cvt;
+template <>
+struct Cvt<float> {
+  static __device__ __forceinline__ float to_f(float v) { return v; }
+  static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+template <>
+struct Cvt<bf16> {
+  static __device__ __forceinline__ float to_f(bf16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ bf16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+template <>
+struct Cvt<__half> {
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+};
+
+template <typename T, int VEC>
+struct alignas(sizeof(T) * VEC) Vec {
+  T v[VEC];
+};
+
+constexpr int kMaxIt = 8;
+
+// Register-resident path: cols <= 32 * VEC * kMaxIt.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) ln_fwd_cached(const T* __restrict__ x, const T* __restrict__ gamma,
+                                                     const T* __restrict__ beta, T* __restrict__ y,
+                                                     float* __restrict__ mean_out, float* __restrict__ invvar_out,
+                                                     int64_t rows, int cols, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int nvec = cols / VEC;
+  const float inv_c = 1.0f / (float)cols;
+  for (int64_t row = warp0; row < rows; row += nwarps) {
+    const Vec<T, VEC>* xr = reinterpret_cast<const Vec<T, VEC>*>(x + row * cols);
+    float v[kMaxIt][VEC];
+    float s = 0.f;
+#pragma unroll
+    for (int it = 0; it < kMaxIt; ++it) {
+      int i = lane + 32 * it;
+      if (i < nvec) {
+        Vec<T, VEC> t = xr[i];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          v[it][e] = Cvt<T>::to_f(t.v[e]);
+          s += v[it][e];
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) v[it][e] = 0.f;
+      }
+    }
+    const float mean = warp_sum(s) * inv_c;
+    float q = 0.f;
+#pragma unroll
+    for (int it = 0; it < kMaxIt; ++it) {
+      if (lane + 32 * it < nvec) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          float d = v[it][e] - mean;
+          q += d * d;
+        }
+      }
+    }
+    const float var = fmaxf(warp_sum(q) * inv_c, 0.f);
+    const float rstd = rsqrtf(var + eps);
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (invvar_out) invvar_out[row] = rstd;
+    }
+    Vec<T, VEC>* yr = reinterpret_cast<Vec<T, VEC>*>(y + row * cols);
+#pragma unroll
+    for (int it = 0; it < kMaxIt; ++it) {
+      int i = lane + 32 * it;
+      if (i < nvec) {
+        Vec<T, VEC> g, b, o;
+        if (gamma) g = reinterpret_cast<const Vec<T, VEC>*>(gamma)[i];
+        if (beta) b = reinterpret_cast<const Vec<T, VEC>*>(beta)[i];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          float r = (v[it][e] - mean) * rstd;
+          if (gamma) r *= Cvt<T>::to_f(g.v[e]);
+          if (beta) r += Cvt<T>::to_f(b.v[e]);
+          o.v[e] = Cvt<T>::from_f(r);
+        }
+        yr[i] = o;
+      }
+    }
+  }
+}
+
+// Wide rows: three passes over the row (the second and third hit L1/L2).
+template <typename T>
+__global__ void __launch_bounds__(256) ln_fwd_wide(const T* __restrict__ x, const T* __restrict__ gamma,
+                                                   const T* __restrict__ beta, T* __restrict__ y,
+                                                   float* __restrict__ mean_out, float* __restrict__ invvar_out,
+                                                   int64_t rows, int cols, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const float inv_c = 1.0f / (float)cols;
+  for (int64_t row = warp0; row < rows; row += nwarps) {
+    const T* xr = x + row * cols;
+    float s = 0.f;
+    for (int i = lane; i < cols; i += 32) s += Cvt<T>::to_f(xr[i]);
+    const float mean = warp_sum(s) * inv_c;
+    float q = 0.f;
+    for (int i = lane; i < cols; i += 32) {
+      float d = Cvt<T>::to_f(xr[i]) - mean;
+      q += d * d;
+    }
+    const float rstd = rsqrtf(fmaxf(warp_sum(q) * inv_c, 0.f) + eps);
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (invvar_out) invvar_out[row] = rstd;
+    }
+    T* yr = y + row * cols;
+    for (int i = lane; i < cols; i += 32) {
+      float r = (Cvt<T>::to_f(xr[i]) - mean) * rstd;
+      if (gamma) r *= Cvt<T>::to_f(gamma[i]);
+      if (beta) r += Cvt<T>::to_f(beta[i]);
+      yr[i] = Cvt<T>::from_f(r);
+    }
+  }
+}
+
+template <typename T, int VEC>
+static cudaError_t launch_cached(const void* x, const void* g, const void* b, void* y, float* mean, float* invvar,
+                                 int64_t rows, int cols, float eps, cudaStream_t st) {
+  const int warps_per_cta = 8;
+  int64_t ctas = (rows + warps_per_cta - 1) / warps_per_cta;
+  const int64_t cap = 148 * 8 * 4;  // a few waves of resident CTAs; warps stride over the rows
+  if (ctas > cap) ctas = cap;
+  ln_fwd_cached<T, VEC><<<(unsigned)ctas, 256, 0, st>>>((const T*)x, (const T*)g, (const T*)b, (T*)y, mean, invvar,
+                                                         rows, cols, eps);
+  return cudaGetLastError();
+}
+
+template <typename T>
+static cudaError_t dispatch(const void* x, const void* g, const void* b, void* y, float* mean, float* invvar,
+                            int64_t rows, int cols, float eps, cudaStream_t st) {
+  constexpr int kMaxVec = 16 / (int)sizeof(T);
+  auto aligned = [&](int vec) {
+    uintptr_t m = (uintptr_t)(sizeof(T) * vec) - 1;
+    return cols % vec == 0 && cols <= 32 * vec * kMaxIt && !((uintptr_t)x & m) && !((uintptr_t)y & m) &&
+           !((uintptr_t)g & m) && !((uintptr_t)b & m);
+  };
+  if (kMaxVec >= 8 && aligned(8) && cols >= 32 * 8)
+    return launch_cached<T, (kMaxVec >= 8 ? 8 : 1)>(x, g, b, y, mean, invvar, rows, cols, eps, st);
+  if (aligned(4)) return launch_cached<T, 4>(x, g, b, y, mean, invvar, rows, cols, eps, st);
+  if (aligned(2)) return launch_cached<T, 2>(x, g, b, y, mean, invvar, rows, cols, eps, st);
+  if (aligned(1)) return launch_cached<T, 1>(x, g, b, y, mean, invvar, rows, cols, eps, st);
+  const int warps_per_cta = 8;
+  int64_t ctas = (rows + warps_per_cta - 1) / warps_per_cta;
+  if (ctas > 148 * 32) ctas = 148 * 32;
+  ln_fwd_wide<T><<<(unsigned)ctas, 256, 0, st>>>((const T*)x, (const T*)g, (const T*)b, (T*)y, mean, invvar, rows,
+                                                 cols, eps);
+  return cudaGetLastError();
+}
+
+}  // namespace px
+
+extern "C" int32_t px_layer_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean,
+                                     float* invvar, int64_t rows, int64_t cols, float eps, int32_t dtype,
+                                     void* stream) {
+  if (!x || !y || rows < 0 || cols <= 0 || cols > (1 << 30)) return PX_ERR_BAD_ARG;
+  if (rows == 0) return PX_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e;
+  switch (dtype) {
+    case PX_F32: e = px::dispatch<float>(x, gamma, beta, y, mean, invvar, rows, (int)cols, eps, st); break;
+    case PX_BF16: e = px::dispatch<px::bf16>(x, gamma, beta, y, mean, invvar, rows, (int)cols, eps, st); break;
+    case PX_F16: e = px::dispatch<__half>(x, gamma, beta, y, mean, invvar, rows, (int)cols, eps, st); break;
+    default: return PX_ERR_UNSUPPORTED;
+  }
+  return e == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
+}

@@ -1,0 +1,421 @@
+// Triangle multiplication: input projection, channel-batched contraction, output stage.
+#include "px_common.cuh"
+
+namespace px {
+
+// =========================================================================================
+// Stage 1: LN(z) -> gated projections a, b, stored channel-major with the contraction index
+// contiguous.  One CTA = one (u, 128 consecutive t) tile of pair elements, 8 warps x 16 rows.
+// The element for (u,t) is z[u][t] (outgoing) or z[t][u] (incoming).
+// HBM-bound: reads 128*sizeof(Tz) + 4 bytes, writes 512 bytes per pair element.
+// =========================================================================================
+struct TriMulInSmem {
+  bf16 A[128 * kLdA];       // LayerNorm'd operand rows
+  bf16 W[2][64 * kLdA];     // weight chunk double buffer: rows 0..31 projection, 32..63 gate
+  bf16 S[2][32 * kLdA];     // transposed output staging [channel][t]
+};
+
+template <typename Tz>
+__global__ void __launch_bounds__(256, 2)
+trimul_in_proj_kernel(const Tz* __restrict__ z, const float* __restrict__ mask, const float* __restrict__ ln_w,
+                      const float* __restrict__ ln_b, const bf16* __restrict__ w_ap, const bf16* __restrict__ w_ag,
+                      const bf16* __restrict__ w_bp, const bf16* __restrict__ w_bg, bf16* __restrict__ a_out,
+                      bf16* __restrict__ b_out, int n, int ld, int swap, float eps) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  TriMulInSmem& sm = *reinterpret_cast<TriMulInSmem*>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int u = blockIdx.y, t0 = blockIdx.x * 128;
+
+  auto load_chunk = [&](int q, int buf) {
+    const bf16* wp = (q < 4) ? w_ap : w_bp;
+    const bf16* wg = (q < 4) ? w_ag : w_bg;
+    load_w_rows(sm.W[buf], 0, wp, 32 * (q & 3), 32, tid);
+    load_w_rows(sm.W[buf], 32, wg, 32 * (q & 3), 32, tid);
+    cp_async_commit();
+  };
+  load_chunk(0, 0);
+
+  auto pair_index = [&](int t) -> size_t { return swap ? ((size_t)t * n + u) : ((size_t)u * n + t); };
+  ln_tile_rows<Tz>(sm.A, warp, lane, ln_w, ln_b, eps, [&](int r) -> const Tz* {
+    int t = t0 + r;
+    return t < n ? z + pair_index(t) * kC : nullptr;
+  });
+  __syncwarp();
+  uint32_t afr[8][4];
+  load_a_frags(afr, sm.A, warp, lane);
+
+  const int g = lane >> 2, tq = lane & 3;
+  const int r0 = 16 * warp + g;
+  float m0 = 0.f, m1 = 0.f;
+  if (t0 + r0 < n) m0 = mask ? mask[pair_index(t0 + r0)] : 1.f;
+  if (t0 + r0 + 8 < n) m1 = mask ? mask[pair_index(t0 + r0 + 8)] : 1.f;
+
+  for (int q = 0; q < 8; ++q) {
+    if (q + 1 < 8) {
+      load_chunk(q + 1, (q + 1) & 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    warp_gemm_k128<0, 8, 8>(acc, afr, sm.W[q & 1], lane);
+    bf16* S = sm.S[q & 1];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int ch = 8 * j + 2 * tq;
+      S[ch * kLdA + r0] = __float2bfloat16_rn(m0 * acc[j][0] * sigmoidf_fast(acc[j + 4][0]));
+      S[(ch + 1) * kLdA + r0] = __float2bfloat16_rn(m0 * acc[j][1] * sigmoidf_fast(acc[j + 4][1]));
+      S[ch * kLdA + r0 + 8] = __float2bfloat16_rn(m1 * acc[j][2] * sigmoidf_fast(acc[j + 4][2]));
+      S[(ch + 1) * kLdA + r0 + 8] = __float2bfloat16_rn(m1 * acc[j][3] * sigmoidf_fast(acc[j + 4][3]));
+    }
+    __syncthreads();
+    // 32 channels x 128 t: thread -> channel tid/8, 16 consecutive t
+    {
+      bf16* dst = (q < 4) ? a_out : b_out;
+      const int ch = tid >> 3, seg = tid & 7;
+      const size_t row = ((size_t)(32 * (q & 3) + ch) * n + u) * ld;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int t = t0 + seg * 16 + h * 8;
+        if (t < ld) {
+          uint4 v = *reinterpret_cast<const uint4*>(S + ch * kLdA + seg * 16 + h * 8);
+          *reinterpret_cast<uint4*>(dst + row + t) = v;
+        }
+      }
+    }
+  }
+}
+
+// =========================================================================================
+// Stage 2: x[c][i][j] = sum_k a[c][i][k] b[c][j][k], 128 independent NT products.
+// CTA tile 128x128x64, 8 warps as 2(M) x 4(N), warp tile 64x32, 3-stage cp.async pipeline,
+// 128-byte swizzled rows.  Tensor-bound: 256 N^3 FLOP, 3 * 256 N^2 bytes.
+// =========================================================================================
+constexpr int kCtBK = 64;
+constexpr int kCtStages = 3;
+constexpr int kCtStageBytes = 2 * 128 * kCtBK * 2;
+
+__global__ void __launch_bounds__(256, 2)
+trimul_contract_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, bf16* __restrict__ x, int n, int ld) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wm = warp >> 2, wn = warp & 3;
+  const int j0 = blockIdx.x * 128, i0 = blockIdx.y * 128, c = blockIdx.z;
+  const bf16* A = a + (size_t)c * n * ld;
+  const bf16* B = b + (size_t)c * n * ld;
+  const int nk = (ld + kCtBK - 1) / kCtBK;
+  const uint32_t sbase = smem_u32(smem_raw);
+
+  auto load_stage = [&](int kt, int stage) {
+    const int k0 = kt * kCtBK;
+    const uint32_t sA = sbase + stage * kCtStageBytes, sB = sA + 128 * kCtBK * 2;
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int idx = tid + 256 * it, r = idx >> 3, ch = idx & 7;
+      const bool kin = (k0 + ch * 8) < ld;
+      const uint32_t off = r * 128 + ((ch ^ (r & 7)) << 4);
+      const bool pa = kin && (i0 + r) < n, pb = kin && (j0 + r) < n;
+      cp_async16(sA + off, pa ? (A + (size_t)(i0 + r) * ld + k0 + ch * 8) : A, pa);
+      cp_async16(sB + off, pb ? (B + (size_t)(j0 + r) * ld + k0 + ch * 8) : B, pb);
+    }
+  };
+
+  float acc[4][4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+
+#pragma unroll
+  for (int s = 0; s < kCtStages - 1; ++s) {
+    if (s < nk) load_stage(s, s);
+    cp_async_commit();
+  }
+  for (int kt = 0; kt < nk; ++kt) {
+    cp_async_wait<kCtStages - 2>();
+    __syncthreads();
+    {
+      const int nxt = kt + kCtStages - 1;
+      if (nxt < nk) load_stage(nxt, nxt % kCtStages);
+      cp_async_commit();
+    }
+    const uint32_t sA = sbase + (kt % kCtStages) * kCtStageBytes, sB = sA + 128 * kCtBK * 2;
+#pragma unroll
+    for (int ks = 0; ks < kCtBK / 16; ++ks) {
+      uint32_t af[4][4], bfr[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        const int r = wm * 64 + mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int ch = ks * 2 + (lane >> 4);
+        ldmatrix_x4(af[mt], sA + r * 128 + ((ch ^ (r & 7)) << 4));
+      }
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {
+        const int r = wn * 32 + np * 16 + (lane & 7) + (lane >> 4) * 8;
+        const int ch = ks * 2 + ((lane >> 3) & 1);
+        ldmatrix_x4(bfr[np], sB + r * 128 + ((ch ^ (r & 7)) << 4));
+      }
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int np = 0; np < 2; ++np) {
+          mma_bf16(acc[mt][2 * np], af[mt], bfr[np][0], bfr[np][1]);
+          mma_bf16(acc[mt][2 * np + 1], af[mt], bfr[np][2], bfr[np][3]);
+        }
+    }
+  }
+  cp_async_wait<0>();
+  bf16* X = x + (size_t)c * n * ld;
+  const int g = lane >> 2, tq = lane & 3;
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt) {
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int j = j0 + wn * 32 + nt * 8 + 2 * tq;
+      const int i = i0 + wm * 64 + mt * 16 + g;
+      if (j < n) {
+        if (i < n) *reinterpret_cast<uint32_t*>(X + (size_t)i * ld + j) = pack_bf16x2(acc[mt][nt][0], acc[mt][nt][1]);
+        if (i + 8 < n)
+          *reinterpret_cast<uint32_t*>(X + (size_t)(i + 8) * ld + j) = pack_bf16x2(acc[mt][nt][2], acc[mt][nt][3]);
+      }
+    }
+  }
+}
+
+// =========================================================================================
+// Stage 3: z_out = [z +] W_z LN_out(x) * sigmoid(W_g LN_in(z)).  One CTA = (i, 128 consecutive j).
+// x arrives channel-major (256-byte runs per channel) and is transposed through shared memory.
+// HBM-bound: reads 256 (x) + sizeof(Tz)*128 (z), writes sizeof(Tz)*128 per pair element.
+// =========================================================================================
+struct TriMulOutSmem {
+  bf16 A1[128 * kLdA];      // LN_out(x) rows [j][c]
+  bf16 XS[128 * kLdA];      // raw x tile [c][j]; later reused for LN_in(z) rows [j][c]
+  bf16 W[2][64 * kLdA];     // rows 0..31 of W_z chunk, rows 32..63 of W_g chunk
+  float red[2][128];
+  float stat[2][128];       // mean, rstd per j
+};
+
+template <typename Tz>
+__global__ void __launch_bounds__(256, 2)
+trimul_out_kernel(const bf16* __restrict__ x, const Tz* __restrict__ z_in, Tz* __restrict__ z_out,
+                  const float* __restrict__ ln_in_w, const float* __restrict__ ln_in_b,
+                  const float* __restrict__ ln_out_w, const float* __restrict__ ln_out_b,
+                  const bf16* __restrict__ w_z, const bf16* __restrict__ w_g, int n, int ld, int add_residual,
+                  float eps) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  TriMulOutSmem& sm = *reinterpret_cast<TriMulOutSmem*>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int i = blockIdx.y, j0 = blockIdx.x * 128;
+
+  // x tile: 128 channels x 128 j (16-byte pieces, zero beyond ld)
+  for (int idx = tid; idx < 128 * 16; idx += 256) {
+    const int c = idx >> 4, seg = idx & 15;
+    const int j = j0 + seg * 8;
+    const bool p = j < ld;
+    cp_async16(smem_u32(sm.XS + c * kLdA + seg * 8), p ? (x + ((size_t)c * n + i) * ld + j) : x, p);
+  }
+  cp_async_commit();
+  auto load_chunk = [&](int q, int buf) {
+    load_w_rows(sm.W[buf], 0, w_z, 32 * q, 32, tid);
+    load_w_rows(sm.W[buf], 32, w_g, 32 * q, 32, tid);
+    cp_async_commit();
+  };
+  load_chunk(0, 0);
+  cp_async_wait<1>();
+  __syncthreads();
+
+  // statistics over c for each j: two threads per j, each half of the channels
+  {
+    const int j = tid & 127, half = tid >> 7;
+    float s = 0.f;
+#pragma unroll 8
+    for (int c = 0; c < 64; ++c) s += __bfloat162float(sm.XS[(64 * half + c) * kLdA + j]);
+    sm.red[half][j] = s;
+    __syncthreads();
+    const float mean = (sm.red[0][j] + sm.red[1][j]) * (1.0f / kC);
+    float qv = 0.f;
+#pragma unroll 8
+    for (int c = 0; c < 64; ++c) {
+      float d = __bfloat162float(sm.XS[(64 * half + c) * kLdA + j]) - mean;
+      qv += d * d;
+    }
+    __syncthreads();
+    sm.red[half][j] = qv;
+    __syncthreads();
+    if (half == 0) {
+      sm.stat[0][j] = mean;
+      sm.stat[1][j] = rsqrtf((sm.red[0][j] + sm.red[1][j]) * (1.0f / kC) + eps);
+    }
+    __syncthreads();
+  }
+  // transpose + normalise into A1: warp handles its own 16 rows j; lane = jj + 8*cc
+  {
+    const int jj = lane & 7, cc = lane >> 3;
+#pragma unroll 4
+    for (int it = 0; it < 32; ++it) {
+      const int j = 16 * warp + (it & 1) * 8 + jj;
+      const int c = ((it >> 1) * 4 + cc) * 2;
+      const float mean = sm.stat[0][j], rstd = sm.stat[1][j];
+      float v0 = (__bfloat162float(sm.XS[c * kLdA + j]) - mean) * rstd * ln_out_w[c] + ln_out_b[c];
+      float v1 = (__bfloat162float(sm.XS[(c + 1) * kLdA + j]) - mean) * rstd * ln_out_w[c + 1] + ln_out_b[c + 1];
+      if (j0 + j >= n) v0 = v1 = 0.f;
+      *reinterpret_cast<uint32_t*>(sm.A1 + j * kLdA + c) = pack_bf16x2(v0, v1);
+    }
+  }
+  __syncthreads();  // every warp is done with the raw x tile
+  ln_tile_rows<Tz>(sm.XS, warp, lane, ln_in_w, ln_in_b, eps, [&](int r) -> const Tz* {
+    int j = j0 + r;
+    return j < n ? z_in + ((size_t)i * n + j) * kC : nullptr;
+  });
+  __syncwarp();
+  uint32_t a1[8][4], a2[8][4];
+  load_a_frags(a1, sm.A1, warp, lane);
+  load_a_frags(a2, sm.XS, warp, lane);
+
+  const int g = lane >> 2, tq = lane & 3;
+  const int jr = j0 + 16 * warp + g;
+  for (int q = 0; q < 4; ++q) {
+    if (q + 1 < 4) {
+      load_chunk(q + 1, (q + 1) & 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    warp_gemm_k128<0, 4, 8>(acc, a1, sm.W[q & 1], lane);
+    warp_gemm_k128<4, 4, 8>(acc, a2, sm.W[q & 1], lane);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int col = 32 * q + 8 * j + 2 * tq;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int jrow = jr + 8 * h;
+        if (jrow < n) {
+          const size_t off = ((size_t)i * n + jrow) * kC + col;
+          float v0 = acc[j][2 * h] * sigmoidf_fast(acc[j + 4][2 * h]);
+          float v1 = acc[j][2 * h + 1] * sigmoidf_fast(acc[j + 4][2 * h + 1]);
+          if (add_residual) {
+            float2 r = load2(z_in + off);
+            v0 += r.x;
+            v1 += r.y;
+          }
+          store2(z_out + off, v0, v1);
+        }
+      }
+    }
+    __syncthreads();  // all warps done with W[q&1] before it is refilled two chunks later
+  }
+}
+
+static size_t trimul_elems(int64_t n) { return (size_t)kC * n * px_ld(n); }
+
+}  // namespace px
+
+using namespace px;
+
+extern "C" int64_t px_ld(int64_t n) { return (n + 7) / 8 * 8; }
+
+static bool bad_n(int64_t n, int64_t ld) { return n <= 0 || n > 32768 || ld != px_ld(n); }
+
+extern "C" int32_t px_trimul_in_proj(const void* z, int32_t z_dtype, const float* mask, const float* ln_w,
+                                     const float* ln_b, const px_bf16* w_ap, const px_bf16* w_ag,
+                                     const px_bf16* w_bp, const px_bf16* w_bg, px_bf16* a, px_bf16* b, int64_t n,
+                                     int64_t ld, int32_t incoming, float eps, void* stream) {
+  if (!z || !ln_w || !ln_b || !w_ap || !w_ag || !w_bp || !w_bg || !a || !b || bad_n(n, ld)) return PX_ERR_BAD_ARG;
+  dim3 grid((unsigned)((ld + 127) / 128), (unsigned)n);
+  const size_t smem = sizeof(TriMulInSmem);
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e;
+  if (z_dtype == PX_F32) {
+    e = cudaFuncSetAttribute(trimul_in_proj_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return PX_ERR_LAUNCH;
+    trimul_in_proj_kernel<float><<<grid, 256, smem, st>>>((const float*)z, mask, ln_w, ln_b, (const bf16*)w_ap,
+                                                          (const bf16*)w_ag, (const bf16*)w_bp, (const bf16*)w_bg,
+                                                          (bf16*)a, (bf16*)b, (int)n, (int)ld, incoming, eps);
+  } else if (z_dtype == PX_BF16) {
+    e = cudaFuncSetAttribute(trimul_in_proj_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return PX_ERR_LAUNCH;
+    trimul_in_proj_kernel<bf16><<<grid, 256, smem, st>>>((const bf16*)z, mask, ln_w, ln_b, (const bf16*)w_ap,
+                                                         (const bf16*)w_ag, (const bf16*)w_bp, (const bf16*)w_bg,
+                                                         (bf16*)a, (bf16*)b, (int)n, (int)ld, incoming, eps);
+  } else {
+    return PX_ERR_UNSUPPORTED;
+  }
+  return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
+}
+
+extern "C" int32_t px_trimul_contract(const px_bf16* a, const px_bf16* b, px_bf16* x, int64_t n, int64_t ld,
+                                      void* stream) {
+  if (!a || !b || !x || bad_n(n, ld)) return PX_ERR_BAD_ARG;
+  const unsigned tiles = (unsigned)((n + 127) / 128);
+  dim3 grid(tiles, tiles, kC);
+  const size_t smem = (size_t)kCtStages * kCtStageBytes;
+  if (cudaFuncSetAttribute(trimul_contract_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess)
+    return PX_ERR_LAUNCH;
+  trimul_contract_kernel<<<grid, 256, smem, (cudaStream_t)stream>>>((const bf16*)a, (const bf16*)b, (bf16*)x, (int)n,
+                                                                    (int)ld);
+  return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
+}
+
+extern "C" int32_t px_trimul_out(const px_bf16* x, const void* z_in, void* z_out, int32_t z_dtype,
+                                 const float* ln_in_w, const float* ln_in_b, const float* ln_out_w,
+                                 const float* ln_out_b, const px_bf16* w_z, const px_bf16* w_g, int64_t n, int64_t ld,
+                                 int32_t add_residual, float eps, void* stream) {
+  if (!x || !z_in || !z_out || !ln_in_w || !ln_in_b || !ln_out_w || !ln_out_b || !w_z || !w_g || bad_n(n, ld))
+    return PX_ERR_BAD_ARG;
+  dim3 grid((unsigned)((n + 127) / 128), (unsigned)n);
+  const size_t smem = sizeof(TriMulOutSmem);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (z_dtype == PX_F32) {
+    if (cudaFuncSetAttribute(trimul_out_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return PX_ERR_LAUNCH;
+    trimul_out_kernel<float><<<grid, 256, smem, st>>>((const bf16*)x, (const float*)z_in, (float*)z_out, ln_in_w,
+                                                      ln_in_b, ln_out_w, ln_out_b, (const bf16*)w_z,
+                                                      (const bf16*)w_g, (int)n, (int)ld, add_residual, eps);
+  } else if (z_dtype == PX_BF16) {
+    if (cudaFuncSetAttribute(trimul_out_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return PX_ERR_LAUNCH;
+    trimul_out_kernel<bf16><<<grid, 256, smem, st>>>((const bf16*)x, (const bf16*)z_in, (bf16*)z_out, ln_in_w,
+                                                     ln_in_b, ln_out_w, ln_out_b, (const bf16*)w_z, (const bf16*)w_g,
+                                                     (int)n, (int)ld, add_residual, eps);
+  } else {
+    return PX_ERR_UNSUPPORTED;
+  }
+  return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
+}
+
+extern "C" int64_t px_trimul_workspace_bytes(int64_t n) {
+  if (n <= 0) return 0;
+  return (int64_t)(3 * trimul_elems(n) * sizeof(bf16));
+}
+
+extern "C" int32_t px_triangle_multiplication(const void* z_in, void* z_out, int32_t z_dtype, const float* mask,
+                                              const float* ln_in_w, const float* ln_in_b, const float* ln_out_w,
+                                              const float* ln_out_b, const px_bf16* w_ap, const px_bf16* w_ag,
+                                              const px_bf16* w_bp, const px_bf16* w_bg, const px_bf16* w_z,
+                                              const px_bf16* w_g, void* workspace, int64_t workspace_bytes, int64_t n,
+                                              int32_t incoming, int32_t add_residual, float eps, void* stream) {
+  if (!workspace || n <= 0) return PX_ERR_BAD_ARG;
+  if (workspace_bytes < px_trimul_workspace_bytes(n)) return PX_ERR_WORKSPACE;
+  if ((uintptr_t)workspace & 15) return PX_ERR_BAD_ARG;
+  const int64_t ld = px_ld(n);
+  px_bf16* a = (px_bf16*)workspace;
+  px_bf16* b = a + trimul_elems(n);
+  px_bf16* x = b + trimul_elems(n);
+  int32_t s = px_trimul_in_proj(z_in, z_dtype, mask, ln_in_w, ln_in_b, w_ap, w_ag, w_bp, w_bg, a, b, n, ld, incoming,
+                                eps, stream);
+  if (s != PX_OK) return s;
+  s = px_trimul_contract(a, b, x, n, ld, stream);
+  if (s != PX_OK) return s;
+  return px_trimul_out(x, z_in, z_out, z_dtype, ln_in_w, ln_in_b, ln_out_w, ln_out_b, w_z, w_g, n, ld, add_residual,
+                       eps, stream);
+}

@@ -1,0 +1,199 @@
+"""Tensor-level wrappers over the C ABI (``include/px_b200.h``).
+
+Each function validates its tensors on the host (device, dtype, contiguity, shape), passes raw
+pointers plus the current CUDA stream to the library and raises ``RuntimeError`` on a non-zero
+status.  torch is used for memory and streams only.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import PX_BF16, PX_F16, PX_F32
+
+_DTYPE = {torch.float32: PX_F32, torch.bfloat16: PX_BF16, torch.float16: PX_F16}
+C_Z = 128
+N_HEAD_PAIR = 4
+D_HEAD_PAIR = 32
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _need_cuda(t: torch.Tensor, name: str) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: this package has no CPU path")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+
+
+def _pair_dtype(z: torch.Tensor) -> int:
+    if z.dtype not in (torch.float32, torch.bfloat16):
+        raise RuntimeError(f"pair tensor must be float32 or bfloat16, got {z.dtype}")
+    return _DTYPE[z.dtype]
+
+
+def _check_pair(z: torch.Tensor, name: str = "z") -> int:
+    _need_cuda(z, name)
+    if z.dim() != 3 or z.shape[0] != z.shape[1] or z.shape[2] != C_Z:
+        raise RuntimeError(f"{name} must have shape [N, N, {C_Z}], got {tuple(z.shape)}")
+    return z.shape[0]
+
+
+def _check_w(w: torch.Tensor, shape: Tuple[int, ...], name: str) -> None:
+    _need_cuda(w, name)
+    if w.dtype != torch.bfloat16 or tuple(w.shape) != shape:
+        raise RuntimeError(f"{name} must be bfloat16 {shape}, got {w.dtype} {tuple(w.shape)}")
+
+
+def _check_v(v: torch.Tensor, n: int, name: str) -> None:
+    _need_cuda(v, name)
+    if v.dtype != torch.float32 or tuple(v.shape) != (n,):
+        raise RuntimeError(f"{name} must be float32 ({n},), got {v.dtype} {tuple(v.shape)}")
+
+
+def _check_mask(mask: Optional[torch.Tensor], n: int) -> Optional[torch.Tensor]:
+    if mask is None:
+        return None
+    _need_cuda(mask, "mask")
+    if mask.dtype != torch.float32 or tuple(mask.shape) != (n, n):
+        raise RuntimeError(f"mask must be float32 ({n},{n}), got {mask.dtype} {tuple(mask.shape)}")
+    return mask
+
+
+# ---------------------------------------------------------------------------------------------
+_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """A per-(device, stream) scratch buffer, grown on demand and reused between calls."""
+    dev = torch.device(device)
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(dev).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        _workspaces.pop(key, None)
+        buf = None
+        buf = torch.empty(int(nbytes), dtype=torch.uint8, device=dev)
+        _workspaces[key] = buf
+    return buf
+
+
+def release_workspaces() -> None:
+    _workspaces.clear()
+
+
+def ld(n: int) -> int:
+    return int(_lib.load().px_ld(n))
+
+
+# ---------------------------------------------------------------------------------------------
+def layer_norm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor], eps: float = 1e-5,
+               return_stats: bool = False):
+    """LayerNorm over the last axis.  Returns y, or (y, mean, invvar) with fp32 statistics."""
+    _need_cuda(x, "input")
+    if x.dtype not in _DTYPE:
+        raise RuntimeError(f"layer_norm supports float32/bfloat16/float16, got {x.dtype}")
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    for t, nm in ((weight, "weight"), (bias, "bias")):
+        if t is not None:
+            _need_cuda(t, nm)
+            if t.dtype != x.dtype or t.numel() != cols:
+                raise RuntimeError(f"{nm} must be {x.dtype} with {cols} elements")
+    y = torch.empty_like(x)
+    mean = invvar = None
+    if return_stats:
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+        invvar = torch.empty(rows, dtype=torch.float32, device=x.device)
+    lib = _lib.load()
+    st = lib.px_layer_norm_fwd(_ptr(x), _ptr(weight), _ptr(bias), _ptr(y), _ptr(mean), _ptr(invvar), rows, cols,
+                               float(eps), _DTYPE[x.dtype], _stream(x))
+    _lib.check(st, "px_layer_norm_fwd")
+    return (y, mean, invvar) if return_stats else y
+
+
+def triangle_multiplication(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optional[torch.Tensor],
+                            ln_in_w, ln_in_b, ln_out_w, ln_out_b, w_ap, w_ag, w_bp, w_bg, w_z, w_g,
+                            incoming: bool, add_residual: bool, eps: float = 1e-5) -> torch.Tensor:
+    n = _check_pair(z_in, "z_in")
+    if _check_pair(z_out, "z_out") != n or z_out.dtype != z_in.dtype:
+        raise RuntimeError("z_out must match z_in in shape and dtype")
+    mask = _check_mask(mask, n)
+    for v, nm in ((ln_in_w, "ln_in_w"), (ln_in_b, "ln_in_b"), (ln_out_w, "ln_out_w"), (ln_out_b, "ln_out_b")):
+        _check_v(v, C_Z, nm)
+    for w, nm in ((w_ap, "w_ap"), (w_ag, "w_ag"), (w_bp, "w_bp"), (w_bg, "w_bg"), (w_z, "w_z"), (w_g, "w_g")):
+        _check_w(w, (C_Z, C_Z), nm)
+    lib = _lib.load()
+    nbytes = lib.px_trimul_workspace_bytes(n)
+    ws = workspace(z_in.device, nbytes)
+    st = lib.px_triangle_multiplication(_ptr(z_in), _ptr(z_out), _pair_dtype(z_in), _ptr(mask), _ptr(ln_in_w),
+                                        _ptr(ln_in_b), _ptr(ln_out_w), _ptr(ln_out_b), _ptr(w_ap), _ptr(w_ag),
+                                        _ptr(w_bp), _ptr(w_bg), _ptr(w_z), _ptr(w_g), _ptr(ws), ws.numel(), n,
+                                        int(incoming), int(add_residual), float(eps), _stream(z_in))
+    _lib.check(st, "px_triangle_multiplication")
+    return z_out
+
+
+def triangle_attention(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optional[torch.Tensor], ln_w, ln_b, w_bias,
+                       w_q, w_k, w_v, w_g, w_o, ending: bool, add_residual: bool, eps: float = 1e-5,
+                       inf: float = 1e9) -> torch.Tensor:
+    n = _check_pair(z_in, "z_in")
+    if _check_pair(z_out, "z_out") != n or z_out.dtype != z_in.dtype:
+        raise RuntimeError("z_out must match z_in in shape and dtype")
+    mask = _check_mask(mask, n)
+    _check_v(ln_w, C_Z, "ln_w")
+    _check_v(ln_b, C_Z, "ln_b")
+    _check_w(w_bias, (N_HEAD_PAIR, C_Z), "w_bias")
+    for w, nm in ((w_q, "w_q"), (w_k, "w_k"), (w_v, "w_v"), (w_g, "w_g"), (w_o, "w_o")):
+        _check_w(w, (C_Z, C_Z), nm)
+    lib = _lib.load()
+    nbytes = lib.px_triatt_workspace_bytes(n)
+    ws = workspace(z_in.device, nbytes)
+    st = lib.px_triangle_attention(_ptr(z_in), _ptr(z_out), _pair_dtype(z_in), _ptr(mask), _ptr(ln_w), _ptr(ln_b),
+                                   _ptr(w_bias), _ptr(w_q), _ptr(w_k), _ptr(w_v), _ptr(w_g), _ptr(w_o), _ptr(ws),
+                                   ws.numel(), n, int(ending), int(add_residual), float(eps), float(inf),
+                                   _stream(z_in))
+    _lib.check(st, "px_triangle_attention")
+    return z_out
+
+
+def transition(x_in: torch.Tensor, x_out: torch.Tensor, ln_w, ln_b, w_a, w_b, w_o, add_residual: bool,
+               eps: float = 1e-5) -> torch.Tensor:
+    _need_cuda(x_in, "x_in")
+    _need_cuda(x_out, "x_out")
+    if x_in.shape[-1] != C_Z or x_out.shape != x_in.shape or x_out.dtype != x_in.dtype:
+        raise RuntimeError(f"transition kernel handles [..., {C_Z}] rows with matching output")
+    _check_v(ln_w, C_Z, "ln_w")
+    _check_v(ln_b, C_Z, "ln_b")
+    _check_w(w_a, (4 * C_Z, C_Z), "w_a")
+    _check_w(w_b, (4 * C_Z, C_Z), "w_b")
+    _check_w(w_o, (C_Z, 4 * C_Z), "w_o")
+    rows = x_in.numel() // C_Z
+    st = _lib.load().px_transition(_ptr(x_in), _ptr(x_out), _pair_dtype(x_in), _ptr(ln_w), _ptr(ln_b), _ptr(w_a),
+                                   _ptr(w_b), _ptr(w_o), rows, int(add_residual), float(eps), _stream(x_in))
+    _lib.check(st, "px_transition")
+    return x_out
+
+
+def pair_bias_proj(z: torch.Tensor, ln_w, ln_b: Optional[torch.Tensor], w: torch.Tensor, eps: float = 1e-5
+                   ) -> torch.Tensor:
+    """bias[h, i, j] = (W LN(z[i, j]))[h] in fp32, for the single-representation attention."""
+    n = _check_pair(z)
+    _check_v(ln_w, C_Z, "ln_w")
+    if ln_b is not None:
+        _check_v(ln_b, C_Z, "ln_b")
+    heads = w.shape[0]
+    _check_w(w, (heads, C_Z), "w")
+    out = torch.empty(heads, n, n, dtype=torch.float32, device=z.device)
+    st = _lib.load().px_pair_bias_proj(_ptr(z), _pair_dtype(z), _ptr(ln_w), _ptr(ln_b), _ptr(w), _ptr(out), n * n,
+                                       heads, float(eps), _stream(z))
+    _lib.check(st, "px_pair_bias_proj")
+    return out

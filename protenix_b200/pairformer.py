@@ -1,0 +1,90 @@
+"""``PairformerBlock`` / ``PairformerStack`` drop-ins over the sm_100a kernels.
+
+Constructor arguments, forward signature, return values and ``state_dict`` keys are those of
+protenix/model/modules/pairformer.py:42-340.  A block is eight kernel families on the pair
+tensor (triangle multiplication out/in: projection, contraction, output stage; triangle
+attention start/end: projection, flash attention, output stage; transition) plus the small
+single-representation branch.  z is updated in place on a private copy (or on the caller's
+tensor with ``inplace_safe=True``); the two transposed copies of z the reference makes around
+the ending-node attention do not exist here -- the ending-node kernels index z transposed.
+
+Inference only: dropout is the identity (eval mode), gradients are not produced.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from .primitives import Transition
+from .transformer import AttentionPairBias
+from .triangular import (TriangleAttention, TriangleMultiplicationIncoming, TriangleMultiplicationOutgoing,
+                         _pair_input)
+
+
+class PairformerBlock(nn.Module):
+    def __init__(self, n_heads: int = 16, c_z: int = 128, c_s: int = 384, c_hidden_mul: int = 128,
+                 c_hidden_pair_att: int = 32, no_heads_pair: int = 4, num_intermediate_factor: int = 4,
+                 dropout: float = 0.25, hidden_scale_up: bool = False) -> None:
+        super().__init__()
+        self.n_heads = n_heads
+        if hidden_scale_up:
+            no_heads_pair = c_z // c_hidden_pair_att
+            c_hidden_mul = c_z
+        self.tri_mul_out = TriangleMultiplicationOutgoing(c_z=c_z, c_hidden=c_hidden_mul)
+        self.tri_mul_in = TriangleMultiplicationIncoming(c_z=c_z, c_hidden=c_hidden_mul)
+        self.tri_att_start = TriangleAttention(c_in=c_z, c_hidden=c_hidden_pair_att, no_heads=no_heads_pair)
+        self.tri_att_end = TriangleAttention(c_in=c_z, c_hidden=c_hidden_pair_att, no_heads=no_heads_pair)
+        self.p_drop = dropout
+        self.pair_transition = Transition(c_in=c_z, n=num_intermediate_factor)
+        self.c_s = c_s
+        if self.c_s > 0:
+            self.attention_pair_bias = AttentionPairBias(has_s=False, create_offset_ln_z=True, n_heads=n_heads,
+                                                         c_a=c_s, c_z=c_z)
+            self.single_transition = Transition(c_in=c_s, n=4)
+
+    @torch.no_grad()
+    def forward(self, s: Optional[torch.Tensor], z: torch.Tensor, pair_mask: Optional[torch.Tensor],
+                triangle_multiplicative: str = "torch", triangle_attention: str = "torch",
+                inplace_safe: bool = False, chunk_size: Optional[int] = None
+                ) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
+        if self.training and self.p_drop > 0:
+            raise RuntimeError("PairformerBlock: training-mode dropout is not implemented; call .eval()")
+        zc, mask, batch = _pair_input(z, pair_mask)
+        if not inplace_safe and zc.data_ptr() == z.data_ptr():
+            zc = zc.clone()
+        self.tri_mul_out.apply_(zc, mask)
+        self.tri_mul_in.apply_(zc, mask)
+        self.tri_att_start.apply_(zc, mask, ending=False)
+        self.tri_att_end.apply_(zc, mask, ending=True)
+        self.pair_transition.forward_residual_(zc)
+        if self.c_s > 0:
+            s = s + self.attention_pair_bias(a=s, s=None, z=zc)
+            s = s + self.single_transition(s)
+        return s, (zc[None] if batch else zc)
+
+
+class PairformerStack(nn.Module):
+    def __init__(self, n_blocks: int = 48, n_heads: int = 16, c_z: int = 128, c_s: int = 384,
+                 num_intermediate_factor: int = 4, dropout: float = 0.25, blocks_per_ckpt: Optional[int] = None,
+                 hidden_scale_up: bool = False) -> None:
+        super().__init__()
+        self.n_blocks = n_blocks
+        self.n_heads = n_heads
+        self.blocks_per_ckpt = blocks_per_ckpt
+        self.blocks = nn.ModuleList(
+            PairformerBlock(n_heads=n_heads, c_z=c_z, c_s=c_s, num_intermediate_factor=num_intermediate_factor,
+                            dropout=dropout, hidden_scale_up=hidden_scale_up) for _ in range(n_blocks))
+
+    @torch.no_grad()
+    def forward(self, s: torch.Tensor, z: torch.Tensor, pair_mask: Optional[torch.Tensor],
+                triangle_multiplicative: str = "torch", triangle_attention: str = "torch",
+                inplace_safe: bool = False, chunk_size: Optional[int] = None
+                ) -> Tuple[torch.Tensor, torch.Tensor]:
+        zc, mask, batch = _pair_input(z, pair_mask)
+        if not inplace_safe and zc.data_ptr() == z.data_ptr():
+            zc = zc.clone()
+        for block in self.blocks:
+            s, zc = block(s, zc, mask, inplace_safe=True)
+        return s, (zc[None] if batch else zc)

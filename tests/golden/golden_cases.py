@@ -1,0 +1,57 @@
+"""Seeded inputs shared by the golden-vector generator and the tests that consume them."""
+from __future__ import annotations
+
+import torch
+
+
+def padding_mask(n: int, n_pad: int) -> torch.Tensor:
+    """pair_mask = t t^T with the last ``n_pad`` tokens masked."""
+    t = torch.ones(n)
+    if n_pad:
+        t[n - n_pad:] = 0
+    return t[:, None] * t[None, :]
+
+
+def random_mask(n: int, seed: int, p_drop: float = 0.2) -> torch.Tensor:
+    """A general (non-separable) 0/1 pair mask; column 0 is kept so no row is fully masked."""
+    g = torch.Generator().manual_seed(seed)
+    m = (torch.rand(n, n, generator=g) > p_drop).float()
+    m[:, 0] = 1
+    m[0, :] = 1
+    return m
+
+
+CASES = {
+    # whole block with the single-representation branch, padding mask
+    "block_n24": dict(kind="block", n=24, c_s=384, seed=11, wseed=1, pad=3),
+    # pair-only block (as embedded in the MSA module), no mask
+    "block_pair_n20": dict(kind="block", n=20, c_s=0, seed=12, wseed=2, pad=0, no_mask=True),
+    "stack2_n16": dict(kind="stack", n=16, c_s=384, n_blocks=2, seed=13, wseed=3, pad=2),
+    "tri_mul_out_n20": dict(kind="tri_mul_out", n=20, seed=21, wseed=4, rand_mask=True),
+    "tri_mul_in_n20": dict(kind="tri_mul_in", n=20, seed=22, wseed=5, rand_mask=True),
+    "tri_att_start_n20": dict(kind="tri_att_start", n=20, seed=23, wseed=6, rand_mask=True),
+    "tri_att_end_n20": dict(kind="tri_att_end", n=20, seed=24, wseed=7, rand_mask=True),
+    "transition_pair": dict(kind="transition", rows=300, c=128, n=4, seed=31, wseed=8),
+    "transition_single": dict(kind="transition", rows=50, c=384, n=4, seed=32, wseed=9),
+    "ln_128_both": dict(kind="layer_norm", rows=200, c=128, scale=True, offset=True, seed=41, wseed=10),
+    "ln_384_both": dict(kind="layer_norm", rows=64, c=384, scale=True, offset=True, seed=42, wseed=11),
+    "ln_833_scale": dict(kind="layer_norm", rows=33, c=833, scale=True, offset=False, seed=43, wseed=12),
+    "ln_64_none": dict(kind="layer_norm", rows=77, c=64, scale=False, offset=False, seed=44, wseed=13),
+}
+
+
+def make_inputs(case: dict) -> dict:
+    g = torch.Generator().manual_seed(case["seed"])
+    kind = case["kind"]
+    if kind in ("transition", "layer_norm"):
+        return {"x": torch.randn(case["rows"], case["c"], generator=g)}
+    n = case["n"]
+    z = torch.randn(n, n, 128, generator=g)
+    s = torch.randn(n, case["c_s"], generator=g) if case.get("c_s", 0) > 0 else None
+    if case.get("no_mask"):
+        mask = None
+    elif case.get("rand_mask"):
+        mask = random_mask(n, case["seed"] + 1000)
+    else:
+        mask = padding_mask(n, case.get("pad", 0))
+    return {"z": z, "s": s, "mask": mask}

@@ -1,0 +1,126 @@
+"""Generate the golden vectors in this folder by running the reference itself on the CPU.
+
+Usage (only where a checkout of bytedance/Protenix v2.0.0 is available):
+
+    python tests/golden/make_golden.py --reference /path/to/Protenix
+
+The reference's torch back-end is imported with two in-memory stand-ins for packages that
+its hot path never really uses (``optree`` -> torch pytree, ``rdkit.Chem.GetPeriodicTable``)
+and with ``LAYERNORM_TYPE=torch``.  Modules are built with the reference's constructors,
+their parameters re-drawn by ``protenix_b200.init_utils.randomize_parameters_`` (a function of
+seed, parameter name and shape only), and run in fp32 and eval mode.  Inputs are re-created
+from the recorded seeds by ``golden_cases.py`` beside this script; only outputs are stored.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+
+def import_reference(path: str):
+    os.environ["LAYERNORM_TYPE"] = "torch"
+    sys.path.insert(0, path)
+    import torch.utils._pytree as pt
+
+    opt = types.ModuleType("optree")
+    opt.tree_map = lambda f, tree: pt.tree_map(f, tree)
+    opt.tree_flatten = lambda tree: pt.tree_flatten(tree)
+    sys.modules["optree"] = opt
+    rd = types.ModuleType("rdkit")
+    ch = types.ModuleType("rdkit.Chem")
+
+    class _Table:
+        def GetElementSymbol(self, i):
+            return f"E{i}"
+
+    ch.GetPeriodicTable = lambda: _Table()
+    rd.Chem = ch
+    sys.modules["rdkit"] = rd
+    sys.modules["rdkit.Chem"] = ch
+    from protenix.model.modules import pairformer as ref_pf
+    from protenix.model.modules import primitives as ref_prim
+    from protenix.model.triangular import layers as ref_layers
+    from protenix.model.triangular import triangular as ref_tri
+
+    return ref_pf, ref_prim, ref_layers, ref_tri
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    ref_pf, ref_prim, ref_layers, ref_tri = import_reference(args.reference)
+
+    from protenix_b200.init_utils import randomize_parameters_
+    sys.path.insert(0, HERE)
+    from golden_cases import CASES, make_inputs
+
+    torch.set_grad_enabled(False)
+    out = {}
+    for name, case in CASES.items():
+        kind = case["kind"]
+        inp = make_inputs(case)
+        torch.manual_seed(0)
+        np.random.seed(0)
+        if kind == "block":
+            mod = ref_pf.PairformerBlock(c_s=case["c_s"]).eval()
+            randomize_parameters_(mod, case["wseed"])
+            for inplace in (False, True):
+                s, z = mod(inp["s"].clone() if inp["s"] is not None else None, inp["z"].clone(),
+                           inp["mask"], inplace_safe=inplace)
+                if not inplace:
+                    out[name + ".z"] = z.numpy()
+                    if s is not None:
+                        out[name + ".s"] = s.numpy()
+                else:  # the reference's in-place branch must agree with its functional one
+                    assert np.abs(z.numpy() - out[name + ".z"]).max() <= 1e-4 * np.abs(out[name + ".z"]).max()
+        elif kind == "stack":
+            mod = ref_pf.PairformerStack(n_blocks=case["n_blocks"], c_s=case["c_s"]).eval()
+            randomize_parameters_(mod, case["wseed"])
+            s, z = mod(inp["s"], inp["z"], inp["mask"])
+            out[name + ".z"] = z.numpy()
+            out[name + ".s"] = s.numpy()
+        elif kind in ("tri_mul_out", "tri_mul_in"):
+            cls = ref_tri.TriangleMultiplicationOutgoing if kind == "tri_mul_out" else ref_tri.TriangleMultiplicationIncoming
+            mod = cls(c_z=128, c_hidden=128).eval()
+            randomize_parameters_(mod, case["wseed"])
+            out[name + ".y"] = mod(inp["z"], mask=inp["mask"]).numpy()
+        elif kind in ("tri_att_start", "tri_att_end"):
+            mod = ref_tri.TriangleAttention(c_in=128, c_hidden=32, no_heads=4, starting=(kind == "tri_att_start")).eval()
+            randomize_parameters_(mod, case["wseed"])
+            out[name + ".y"] = mod(inp["z"], mask=inp["mask"]).numpy()
+        elif kind == "transition":
+            mod = ref_prim.Transition(c_in=case["c"], n=case["n"]).eval()
+            randomize_parameters_(mod, case["wseed"])
+            out[name + ".y"] = mod(inp["x"]).numpy()
+        elif kind == "layer_norm":
+            mod = ref_layers.LayerNorm(case["c"], create_scale=case["scale"], create_offset=case["offset"]).eval()
+            randomize_parameters_(mod, case["wseed"])
+            out[name + ".y"] = mod(inp["x"]).numpy()
+        else:
+            raise ValueError(kind)
+        print(name, {k: v.shape for k, v in out.items() if k.startswith(name + ".")})
+    # state_dict layout of one reference block: the drop-in must load it with strict=True
+    import json
+
+    torch.manual_seed(0)
+    np.random.seed(0)
+    blk = ref_pf.PairformerBlock().eval()
+    keys = {k: list(v.shape) for k, v in blk.state_dict().items()}
+    with open(os.path.join(HERE, "block_state_dict_keys.json"), "w") as f:
+        json.dump(keys, f, indent=0, sort_keys=True)
+    path = os.path.join(HERE, "pairformer_golden.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
+if __name__ == "__main__":
+    main()
