@@ -1,0 +1,321 @@
+#!/usr/bin/env python
+"""Benchmark of the Pairformer pair-representation forward path on B200.
+
+One "step" = one forward of a PairformerStack (default: 48 blocks, N_token = 1536, c_z = 128,
+c_s = 384, bf16 residual stream, random-init weights, z,s ~ N(0,1), trailing padding mask).
+metric: token-pairs/s = N^2 * blocks / seconds-per-stack  (= N^2 / seconds per block).
+
+    python bench.py --gpus 1 --steps 3 --warmup 3
+    python bench.py --impl reference ...      # the CPU arm: oracle port on the host cores
+
+Prints ONE JSON line (rank 0).  See DESIGN.md for how every field is obtained.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "pairformer_token_pairs_per_s"
+UNIT = "token-pairs/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--n-token", type=int, default=1536)
+    ap.add_argument("--blocks", type=int, default=48)
+    ap.add_argument("--pad", type=int, default=37, help="trailing masked tokens (config: 0-64 per seed)")
+    ap.add_argument("--z-dtype", default="bf16", choices=["bf16", "fp32"])
+    ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU row-slab sample (0 = auto)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def block_flops(n: int) -> float:
+    return 1536.0 * n ** 3 + 1121792.0 * n ** 2
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": d["hbm_gbs"], "tflops": d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1400.0, "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, index: int) -> None:
+        super().__init__(daemon=True)
+        self.index, self.stop_flag, self.samples, self.reasons, self.max_mhz = index, False, [], set(), None
+
+    def run(self) -> None:
+        try:
+            import pynvml as nv
+
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {
+                getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+                getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+                getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+                getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            }
+            get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            while not self.stop_flag:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                r = get(h)
+                for bit, nm in names.items():
+                    if r & bit:
+                        self.reasons.add(nm)
+                time.sleep(0.1)
+        except Exception as e:  # NVML missing: report that no clocks were read
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+
+    def result(self) -> dict:
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def cpu_baseline(n: int, pad: int, rows: int, threads: int, target_s: float = 10.0) -> dict:
+    """Oracle (CPU port of the reference's torch path, fp32) on a row slab of one block's pair path.
+
+    The slab does rows/N of every row-wise op and of every O(N^3) product of a block, so one block
+    costs slab_time * N / rows.  The full-size operands of the other token axis are stand-ins of the
+    right shape (z itself and a random [4, N, N] bias): their values do not change the cost.
+    """
+    import torch
+
+    import protenix_b200 as px
+    from oracle import pairformer_oracle as O
+    from protenix_b200.init_utils import randomize_parameters_
+
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    z = torch.randn(n, n, 128, generator=g)
+    t = torch.ones(n)
+    if pad:
+        t[n - pad:] = 0
+    mask = t[:, None] * t[None, :]
+    blk = randomize_parameters_(px.PairformerBlock(c_s=0), 1).eval()
+    p = {k: v.detach() for k, v in blk.state_dict().items()}
+    bias = torch.randn(4, n, n, generator=g)
+    shared = {"tri_mul_out.a": z, "tri_mul_out.b": z, "tri_mul_in.a": z, "tri_mul_in.b": z,
+              "tri_att_start.bias": bias, "tri_att_end.bias": bias}
+
+    def sample(r: int) -> float:
+        t0 = time.perf_counter()
+        O.pair_path_row_slab(z, mask, p, 0, r, shared)
+        return time.perf_counter() - t0
+
+    with torch.no_grad():
+        if rows <= 0:
+            probe = min(2, n)
+            sample(probe)                      # warm the thread pool and the allocator
+            t_probe = sample(probe)
+            rows = int(max(probe, min(n, 128, probe * target_s / max(t_probe, 1e-3))))
+        dt = sample(rows)
+    sec_per_block = dt * n / rows
+    return {"value": n * n / sec_per_block, "unit": UNIT, "cores": threads, "kind": "port",
+            "sec_per_block_est": sec_per_block,
+            "sample": f"oracle fp32 pair path of one block at N={n}: row slab of {rows}/{n} rows timed "
+                      f"({dt:.2f} s), scaled by {n}/{rows}"}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    times = []
+    cb = None
+    for i in range(args.warmup + args.steps):
+        cb = cpu_baseline(args.n_token, args.pad, args.cpu_rows, threads)
+        if i >= args.warmup:
+            times.append(cb["sec_per_block_est"])
+    sec_block = sum(times) / len(times)
+    value = args.n_token ** 2 / sec_block
+    cb["value"] = value
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec_block * args.blocks * 1e3,
+        "ms_per_block": sec_block * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp32", "data": "synthetic",
+        "config": workload_config(args, 1), "cpu_baseline": cb,
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "CPU arm: oracle port of the reference torch path on the host cores; each step is a row-slab "
+                "sample of one block, extrapolated to a block",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, world: int) -> dict:
+    return {"workload": f"pairformer_stack_{args.blocks}blocks_N{args.n_token}_cz128_cs384",
+            "n_token": args.n_token, "blocks": args.blocks, "pad_tokens": args.pad, "z_storage": args.z_dtype,
+            "l2": "inputs larger than L2 (z alone is %d MB)" % (args.n_token ** 2 * 128 * (2 if args.z_dtype == "bf16" else 4) >> 20),
+            "parallelism": "single GPU" if world == 1 else f"replicas x{world}"}
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import protenix_b200 as px
+    from protenix_b200 import ops
+    from protenix_b200.init_utils import randomize_parameters_
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    n, nb = args.n_token, args.blocks
+    zdt = torch.bfloat16 if args.z_dtype == "bf16" else torch.float32
+    stack = px.PairformerStack(n_blocks=nb).eval()
+    randomize_parameters_(stack, 1 + rank)
+    stack = stack.to(dev)
+    g = torch.Generator().manual_seed(rank)
+    z_host = torch.randn(n, n, 128, generator=g).to(zdt).pin_memory()
+    s_host = torch.randn(n, 384, generator=g).pin_memory()
+    t = torch.ones(n)
+    if args.pad:
+        t[n - args.pad:] = 0
+    mask = (t[:, None] * t[None, :]).to(dev)
+    z0, s0 = z_host.to(dev), s_host.to(dev)
+    z_work = torch.empty_like(z0)
+    z_out_host = torch.empty_like(z_host).pin_memory()
+    s_out_host = torch.empty_like(s_host).pin_memory()
+
+    def step_device():
+        z_work.copy_(z0)
+        return stack(s0, z_work, mask, inplace_safe=True)
+
+    def step_e2e():
+        zd = z_host.to(dev, non_blocking=True)
+        sd = s_host.to(dev, non_blocking=True)
+        s1, z1 = stack(sd, zd, mask, inplace_safe=True)
+        z_out_host.copy_(z1, non_blocking=True)
+        s_out_host.copy_(s1, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        tt = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item())
+
+    # ---- device-resident timing --------------------------------------------------------------
+    for _ in range(args.warmup):
+        step_device()
+    barrier()
+    ops.reset_launch_count()
+    timer = ops.StageTimer()
+    ops.set_stage_timer(timer)
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step_device()
+    e1.record()
+    barrier()
+    sampler.stop_flag = True
+    ops.set_stage_timer(None)
+    launches = ops.reset_launch_count()
+    ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    sampler.join(timeout=2)
+    stages = timer.summary()
+
+    # ---- end to end through the module API with host buffers ---------------------------------
+    for _ in range(2):
+        step_e2e()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step_e2e()
+    e1.record()
+    barrier()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    pk = peaks()
+    pairs = float(n) * n * nb * world            # replicas: every rank runs its own stack
+    value = pairs / (ms_step * 1e-3)
+    # dominant kernel: the one with the largest share of stage time
+    name = max(stages, key=lambda k: stages[k][1])
+    cnt, tot = stages[name]
+    avg_ms = tot / cnt
+    algo = {  # algorithmic FLOPs / bytes per launch
+        "px_triatt_flash": ("tensor", 512.0 * n ** 3),
+        "px_trimul_contract": ("tensor", 256.0 * n ** 3),
+        "px_transition": ("tensor", 393216.0 * n * n),
+        "px_trimul_in_proj": ("hbm", (128 * z0.element_size() + 4 + 512) * n * n),
+        "px_trimul_out": ("hbm", (256 + 2 * 128 * z0.element_size()) * n * n),
+        "px_triatt_in_proj": ("hbm", (128 * z0.element_size() + 4 + 768 + 20) * n * n),
+        "px_triatt_out": ("hbm", (256 + 2 * 128 * z0.element_size()) * n * n),
+    }.get(name, ("hbm", 0.0))
+    if algo[0] == "tensor":
+        achieved, peak, runit = algo[1] / (avg_ms * 1e-3) / 1e12, pk["tflops"], "TFLOP/s"
+    else:
+        achieved, peak, runit = algo[1] / (avg_ms * 1e-3) / 1e9, pk["hbm_gbs"], "GB/s"
+    step_total = sum(v[1] for v in stages.values()) / args.steps
+    roof = {"kernel": name, "bound": algo[0], "achieved": achieved, "peak": peak, "unit": runit,
+            "frac": achieved / peak, "peak_source": pk["source"], "traffic": None, "avg_launch_ms": avg_ms,
+            "launches": cnt,
+            "stage_ms_per_step": {k: round(v[1] / args.steps, 3) for k, v in sorted(stages.items())},
+            "stage_share": {k: round(v[1] / args.steps / step_total, 4) for k, v in sorted(stages.items())}}
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "ms_per_block": ms_step / nb, "higher_is_better": True,
+        "scaling": "weak" if world > 1 else "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "config": workload_config(args, world),
+        "tflops_per_gpu": block_flops(n) * nb / (ms_step * 1e-3) / 1e12,
+        "frac_of_bf16_peak": block_flops(n) * nb / (ms_step * 1e-3) / 1e12 / pk["tflops"],
+        "clocks": sampler.result(),
+        "e2e": {"value": pairs / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": z_host.numel() * z_host.element_size() + s_host.numel() * 4,
+                "d2h_bytes_per_step": z_out_host.numel() * z_out_host.element_size() + s_out_host.numel() * 4},
+        "gpu_launches": launches,
+        "roofline": roof,
+    }
+    if not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(n, args.pad, args.cpu_rows, os.cpu_count() or 1)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

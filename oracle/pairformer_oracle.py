@@ -69,6 +69,24 @@ def transition(x: torch.Tensor, p: Params) -> torch.Tensor:
     return (F.silu(a) * b) @ p["linear_no_bias.weight"].T
 
 
+def _contract(a: torch.Tensor, b: torch.Tensor, outgoing: bool) -> torch.Tensor:
+    """Channel-batched product as the reference forms it (protenix/model/triangular/triangular.py:123-150):
+    channels first, one matmul per channel, channels last again.  a: [I, K, C] (outgoing) or [K, I, C]."""
+    if outgoing:
+        x = torch.matmul(a.permute(2, 0, 1), b.permute(2, 1, 0))
+    else:
+        x = torch.matmul(a.permute(2, 1, 0), b.permute(2, 0, 1))
+    return x.permute(1, 2, 0)
+
+
+def _attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """softmax(q k^T + bias) v for q,k,v [I, N, H, D] and bias broadcastable to [I, H, Q, K]; returns
+    [I, Q, H, D] (protenix/model/triangular/layers.py:276-296)."""
+    q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)      # [I, H, N, D]
+    w = torch.softmax(torch.matmul(q, k.transpose(-1, -2)) + bias, dim=-1)
+    return torch.matmul(w, v).transpose(1, 2)
+
+
 def triangle_multiplication(z: torch.Tensor, mask: Optional[torch.Tensor], p: Params,
                             outgoing: bool) -> torch.Tensor:
     """Triangle multiplicative update (returns the update, without the residual).
@@ -83,10 +101,7 @@ def triangle_multiplication(z: torch.Tensor, mask: Optional[torch.Tensor], p: Pa
     zn = layer_norm(z, p["layer_norm_in.weight"], p["layer_norm_in.bias"])
     a = m * torch.sigmoid(zn @ p["linear_a_g.weight"].T) * (zn @ p["linear_a_p.weight"].T)
     b = m * torch.sigmoid(zn @ p["linear_b_g.weight"].T) * (zn @ p["linear_b_p.weight"].T)
-    if outgoing:
-        x = torch.einsum("ikc,jkc->ijc", a, b)
-    else:
-        x = torch.einsum("kic,kjc->ijc", a, b)
+    x = _contract(a, b, outgoing)
     x = layer_norm(x, p["layer_norm_out.weight"], p["layer_norm_out.bias"])
     x = x @ p["linear_z.weight"].T
     g = torch.sigmoid(zn @ p["linear_g.weight"].T)
@@ -122,10 +137,7 @@ def triangle_attention(x: torch.Tensor, mask: Optional[torch.Tensor], p: Params,
         q = (xr @ p["mha.linear_q.weight"].T).view(-1, n, h, d) / math.sqrt(d)
         k = (xr @ p["mha.linear_k.weight"].T).view(-1, n, h, d)
         v = (xr @ p["mha.linear_v.weight"].T).view(-1, n, h, d)
-        logits = torch.einsum("iqhd,ikhd->ihqk", q, k)
-        logits = logits + (inf * (mask[r0:r0 + step] - 1))[:, None, None, :] + tri_bias[None]
-        w = torch.softmax(logits, dim=-1)
-        o = torch.einsum("ihqk,ikhd->iqhd", w, v)
+        o = _attend(q, k, v, (inf * (mask[r0:r0 + step] - 1))[:, None, None, :] + tri_bias[None])
         g = torch.sigmoid(xr @ p["mha.linear_g.weight"].T).view(-1, n, h, d)
         out[r0:r0 + step] = (o * g).reshape(-1, n, h * d) @ p["mha.linear_o.weight"].T
     if not starting:
@@ -193,3 +205,71 @@ def rel_frobenius(a: torch.Tensor, b: torch.Tensor) -> float:
     a = a.detach().double().cpu()
     b = b.detach().double().cpu()
     return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+
+def pair_path_row_slab(z: torch.Tensor, pair_mask: Optional[torch.Tensor], p: Params, r0: int, r1: int,
+                       shared: Optional[dict] = None) -> Tuple[Dict[str, torch.Tensor], dict]:
+    """Timing sample of one block's pair path: the five pair updates for output rows [r0, r1) only.
+
+    Every update is computed from the same input z (the sequential dependence between the five
+    sub-modules is dropped: values do not change the cost).  All row-wise work -- LayerNorms, every
+    projection including both a and b of the two multiplications and the pair-bias projection,
+    gates, output projections, the transition -- is done for the slab's (r1 - r0) * N pair elements,
+    and the O(N^3) products are done for the slab's output rows, so the arithmetic volume is
+    exactly (r1 - r0) / N of one block's pair path.  The operands of the other token axis that a
+    slab needs in full (b over all rows for the outgoing product, a and b for the incoming one,
+    the [H, N, N] pair bias) come from ``shared``: computed here by the same formulas when it is
+    None (so that the slabs equal the full updates; the tests use this), or supplied by a caller
+    that only wants the timing and passes stand-in tensors of the right shapes.  Returns the five
+    update slabs by sub-module name; the ending-node slab is indexed by column (rows [r0, r1) of
+    the transposed update).  Used only by the CPU-baseline leg of the benchmark.
+    """
+    n = z.shape[0]
+    mask = pair_mask if pair_mask is not None else z.new_ones(n, n)
+
+    def gated(zn, q, which, m):
+        return m[..., None] * torch.sigmoid(zn @ q[f"linear_{which}_g.weight"].T) * (zn @ q[f"linear_{which}_p.weight"].T)
+
+    if shared is None:
+        shared = {}
+        for name in ("tri_mul_out", "tri_mul_in"):
+            q = _sub(p, name)
+            zn = layer_norm(z, q["layer_norm_in.weight"], q["layer_norm_in.bias"])
+            shared[name + ".a"] = gated(zn, q, "a", mask)
+            shared[name + ".b"] = gated(zn, q, "b", mask)
+        for name, tr in (("tri_att_start", False), ("tri_att_end", True)):
+            q = _sub(p, name)
+            x = z.transpose(0, 1) if tr else z
+            xn = layer_norm(x, q["layer_norm.weight"], q["layer_norm.bias"])
+            shared[name + ".bias"] = (xn @ q["linear.weight"].T).permute(2, 0, 1).contiguous()
+    rows = slice(r0, r1)
+    out: Dict[str, torch.Tensor] = {}
+    for name in ("tri_mul_out", "tri_mul_in"):
+        q = _sub(p, name)
+        zn = layer_norm(z[rows], q["layer_norm_in.weight"], q["layer_norm_in.bias"])
+        a_slab = gated(zn, q, "a", mask[rows])
+        b_slab = gated(zn, q, "b", mask[rows])      # this slab's share of the other operand's projection
+        if name == "tri_mul_out":
+            x = _contract(a_slab, shared[name + ".b"], True)
+        else:
+            x = _contract(shared[name + ".a"][:, rows], shared[name + ".b"], False)
+        del b_slab
+        x = layer_norm(x, q["layer_norm_out.weight"], q["layer_norm_out.bias"]) @ q["linear_z.weight"].T
+        out[name] = x * torch.sigmoid(zn @ q["linear_g.weight"].T)
+    for name, tr in (("tri_att_start", False), ("tri_att_end", True)):
+        q = _sub(p, name)
+        x = (z.transpose(0, 1) if tr else z)[rows]
+        m = (mask.transpose(0, 1) if tr else mask)[rows]
+        h = q["linear.weight"].shape[0]
+        d = q["mha.linear_q.weight"].shape[0] // h
+        xn = layer_norm(x, q["layer_norm.weight"], q["layer_norm.bias"])
+        bias_slab = xn @ q["linear.weight"].T        # this slab's share of the pair-bias projection
+        del bias_slab
+        qq = (xn @ q["mha.linear_q.weight"].T).view(-1, n, h, d) / math.sqrt(d)
+        kk = (xn @ q["mha.linear_k.weight"].T).view(-1, n, h, d)
+        vv = (xn @ q["mha.linear_v.weight"].T).view(-1, n, h, d)
+        o = _attend(qq, kk, vv, (1e9 * (m - 1))[:, None, None, :] + shared[name + ".bias"][None])
+        g = torch.sigmoid(xn @ q["mha.linear_g.weight"].T).view(-1, n, h, d)
+        out[name] = (o * g).reshape(-1, n, h * d) @ q["mha.linear_o.weight"].T
+    out["pair_transition"] = transition(z[rows], _sub(p, "pair_transition"))
+    return out, shared

@@ -69,6 +69,52 @@ def _check_mask(mask: Optional[torch.Tensor], n: int) -> Optional[torch.Tensor]:
 
 
 # ---------------------------------------------------------------------------------------------
+class StageTimer:
+    """Optional per-kernel CUDA-event timing on the launching stream (used by bench.py)."""
+
+    def __init__(self) -> None:
+        self.events = []          # (name, start, stop)
+
+    def summary(self) -> Dict[str, Tuple[int, float]]:
+        """name -> (launches, total milliseconds); call after a device synchronize."""
+        out: Dict[str, Tuple[int, float]] = {}
+        for name, a, b in self.events:
+            c, t = out.get(name, (0, 0.0))
+            out[name] = (c + 1, t + a.elapsed_time(b))
+        return out
+
+
+_timer: Optional[StageTimer] = None
+launch_count = 0     # kernels of this library launched since import (or since reset_launch_count)
+
+
+def set_stage_timer(t: Optional[StageTimer]) -> None:
+    global _timer
+    _timer = t
+
+
+def reset_launch_count() -> int:
+    global launch_count
+    n, launch_count = launch_count, 0
+    return n
+
+
+def _launch(name: str, fn, *args) -> None:
+    """Call one C-ABI launcher (exactly one kernel), optionally bracketed by CUDA events."""
+    global launch_count
+    if _timer is not None:
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        a.record()
+        st = fn(*args)
+        b.record()
+        _timer.events.append((name, a, b))
+    else:
+        st = fn(*args)
+    launch_count += 1
+    _lib.check(st, name)
+
+
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
 
 
@@ -113,10 +159,8 @@ def layer_norm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[t
     if return_stats:
         mean = torch.empty(rows, dtype=torch.float32, device=x.device)
         invvar = torch.empty(rows, dtype=torch.float32, device=x.device)
-    lib = _lib.load()
-    st = lib.px_layer_norm_fwd(_ptr(x), _ptr(weight), _ptr(bias), _ptr(y), _ptr(mean), _ptr(invvar), rows, cols,
-                               float(eps), _DTYPE[x.dtype], _stream(x))
-    _lib.check(st, "px_layer_norm_fwd")
+    _launch("px_layer_norm_fwd", _lib.load().px_layer_norm_fwd, _ptr(x), _ptr(weight), _ptr(bias), _ptr(y),
+            _ptr(mean), _ptr(invvar), rows, cols, float(eps), _DTYPE[x.dtype], _stream(x))
     return (y, mean, invvar) if return_stats else y
 
 
@@ -132,13 +176,16 @@ def triangle_multiplication(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optio
     for w, nm in ((w_ap, "w_ap"), (w_ag, "w_ag"), (w_bp, "w_bp"), (w_bg, "w_bg"), (w_z, "w_z"), (w_g, "w_g")):
         _check_w(w, (C_Z, C_Z), nm)
     lib = _lib.load()
-    nbytes = lib.px_trimul_workspace_bytes(n)
-    ws = workspace(z_in.device, nbytes)
-    st = lib.px_triangle_multiplication(_ptr(z_in), _ptr(z_out), _pair_dtype(z_in), _ptr(mask), _ptr(ln_in_w),
-                                        _ptr(ln_in_b), _ptr(ln_out_w), _ptr(ln_out_b), _ptr(w_ap), _ptr(w_ag),
-                                        _ptr(w_bp), _ptr(w_bg), _ptr(w_z), _ptr(w_g), _ptr(ws), ws.numel(), n,
-                                        int(incoming), int(add_residual), float(eps), _stream(z_in))
-    _lib.check(st, "px_triangle_multiplication")
+    ws = workspace(z_in.device, lib.px_trimul_workspace_bytes(n))
+    ldn = lib.px_ld(n)
+    per = C_Z * n * ldn * 2                      # bytes of one channel-major [128][N][ld] bf16 tensor
+    a, b, x = ws.data_ptr(), ws.data_ptr() + per, ws.data_ptr() + 2 * per
+    dt, st, eps = _pair_dtype(z_in), _stream(z_in), float(eps)
+    _launch("px_trimul_in_proj", lib.px_trimul_in_proj, _ptr(z_in), dt, _ptr(mask), _ptr(ln_in_w), _ptr(ln_in_b),
+            _ptr(w_ap), _ptr(w_ag), _ptr(w_bp), _ptr(w_bg), a, b, n, ldn, int(incoming), eps, st)
+    _launch("px_trimul_contract", lib.px_trimul_contract, a, b, x, n, ldn, st)
+    _launch("px_trimul_out", lib.px_trimul_out, x, _ptr(z_in), _ptr(z_out), dt, _ptr(ln_in_w), _ptr(ln_in_b),
+            _ptr(ln_out_w), _ptr(ln_out_b), _ptr(w_z), _ptr(w_g), n, ldn, int(add_residual), eps, st)
     return z_out
 
 
@@ -155,13 +202,21 @@ def triangle_attention(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optional[t
     for w, nm in ((w_q, "w_q"), (w_k, "w_k"), (w_v, "w_v"), (w_g, "w_g"), (w_o, "w_o")):
         _check_w(w, (C_Z, C_Z), nm)
     lib = _lib.load()
-    nbytes = lib.px_triatt_workspace_bytes(n)
-    ws = workspace(z_in.device, nbytes)
-    st = lib.px_triangle_attention(_ptr(z_in), _ptr(z_out), _pair_dtype(z_in), _ptr(mask), _ptr(ln_w), _ptr(ln_b),
-                                   _ptr(w_bias), _ptr(w_q), _ptr(w_k), _ptr(w_v), _ptr(w_g), _ptr(w_o), _ptr(ws),
-                                   ws.numel(), n, int(ending), int(add_residual), float(eps), float(inf),
-                                   _stream(z_in))
-    _lib.check(st, "px_triangle_attention")
+    ws = workspace(z_in.device, lib.px_triatt_workspace_bytes(n))
+    ldn = lib.px_ld(n)
+    al = lambda nb: (nb + 255) // 256 * 256
+    qkv = al(n * N_HEAD_PAIR * n * D_HEAD_PAIR * 2)
+    q = ws.data_ptr()
+    k, v, o = q + qkv, q + 2 * qkv, q + 3 * qkv
+    bias = o + al(n * n * C_Z * 2)
+    mbias = bias + al(N_HEAD_PAIR * n * ldn * 4)
+    dt, st, eps = _pair_dtype(z_in), _stream(z_in), float(eps)
+    _launch("px_triatt_in_proj", lib.px_triatt_in_proj, _ptr(z_in), dt, _ptr(mask), _ptr(ln_w), _ptr(ln_b),
+            _ptr(w_q), _ptr(w_k), _ptr(w_v), _ptr(w_bias), q, k, v, bias, mbias, n, ldn, int(ending), eps,
+            float(inf), st)
+    _launch("px_triatt_flash", lib.px_triatt_flash, q, k, v, bias, mbias, o, n, ldn, st)
+    _launch("px_triatt_out", lib.px_triatt_out, o, _ptr(z_in), _ptr(z_out), dt, _ptr(ln_w), _ptr(ln_b), _ptr(w_g),
+            _ptr(w_o), n, int(ending), int(add_residual), eps, st)
     return z_out
 
 
@@ -177,9 +232,8 @@ def transition(x_in: torch.Tensor, x_out: torch.Tensor, ln_w, ln_b, w_a, w_b, w_
     _check_w(w_b, (4 * C_Z, C_Z), "w_b")
     _check_w(w_o, (C_Z, 4 * C_Z), "w_o")
     rows = x_in.numel() // C_Z
-    st = _lib.load().px_transition(_ptr(x_in), _ptr(x_out), _pair_dtype(x_in), _ptr(ln_w), _ptr(ln_b), _ptr(w_a),
-                                   _ptr(w_b), _ptr(w_o), rows, int(add_residual), float(eps), _stream(x_in))
-    _lib.check(st, "px_transition")
+    _launch("px_transition", _lib.load().px_transition, _ptr(x_in), _ptr(x_out), _pair_dtype(x_in), _ptr(ln_w),
+            _ptr(ln_b), _ptr(w_a), _ptr(w_b), _ptr(w_o), rows, int(add_residual), float(eps), _stream(x_in))
     return x_out
 
 
@@ -193,7 +247,6 @@ def pair_bias_proj(z: torch.Tensor, ln_w, ln_b: Optional[torch.Tensor], w: torch
     heads = w.shape[0]
     _check_w(w, (heads, C_Z), "w")
     out = torch.empty(heads, n, n, dtype=torch.float32, device=z.device)
-    st = _lib.load().px_pair_bias_proj(_ptr(z), _pair_dtype(z), _ptr(ln_w), _ptr(ln_b), _ptr(w), _ptr(out), n * n,
-                                       heads, float(eps), _stream(z))
-    _lib.check(st, "px_pair_bias_proj")
+    _launch("px_pair_bias_proj", _lib.load().px_pair_bias_proj, _ptr(z), _pair_dtype(z), _ptr(ln_w), _ptr(ln_b),
+            _ptr(w), _ptr(out), n * n, heads, float(eps), _stream(z))
     return out

@@ -1,0 +1,256 @@
+"""Parity of the CUDA path (through the module API -> ctypes -> C ABI) with the CPU oracle and
+with the vectors produced by the reference itself.
+
+Tolerances (relative Frobenius error against fp32 ground truth):
+  * bf16-operand kernels, per op and per block: <= 1e-2 (the reference's own bf16 noise floor
+    for one block is 0.6-0.95e-2);  after a multi-block stack: <= 3e-2
+  * LayerNorm op in fp32: <= 1e-5; in bf16/fp16: bounded by output rounding
+  * mask / padding handling: bit-exact
+"""
+import math
+
+import pytest
+import torch
+
+import protenix_b200 as px
+from golden_cases import CASES, make_inputs, padding_mask, random_mask
+from helpers import build_module, golden, params_of, relf
+from oracle import pairformer_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+TOL_OP = 1e-2
+TOL_BLOCK = 1e-2
+TOL_STACK = 3e-2
+
+
+def cuda(t):
+    return None if t is None else t.to(DEV)
+
+
+# ------------------------------------------------------------------------------- LayerNorm
+@pytest.mark.parametrize("name", [k for k in sorted(CASES) if CASES[k]["kind"] == "layer_norm"])
+def test_layer_norm_golden_fp32(name):
+    case = CASES[name]
+    m = build_module("layer_norm", case).to(DEV)
+    y = m(cuda(make_inputs(case)["x"]))
+    assert relf(y, golden()[name + ".y"]) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("cols", [128, 384, 64, 16, 833, 768, 256, 2050, 9000])
+def test_layer_norm_widths_dtypes_and_stats(dtype, cols):
+    from protenix_b200 import ops
+
+    g = torch.Generator().manual_seed(cols)
+    x = (torch.randn(37, cols, generator=g) * 2 + 0.5).to(dtype)
+    w = (1 + 0.1 * torch.randn(cols, generator=g)).to(dtype)
+    b = (0.1 * torch.randn(cols, generator=g)).to(dtype)
+    for ww, bb in ((w, b), (w, None), (None, b), (None, None)):
+        y, mean, invvar = ops.layer_norm(cuda(x), cuda(ww), cuda(bb), 1e-5, return_stats=True)
+        ref = O.layer_norm(x.double(), None if ww is None else ww.double(), None if bb is None else bb.double())
+        tol = 1e-5 if dtype == torch.float32 else (6e-3 if dtype == torch.bfloat16 else 8e-4)
+        assert y.dtype == dtype and relf(y, ref) < tol
+        mu, iv = O.layer_norm_stats(x.double())
+        assert relf(mean, mu) < 1e-5 and relf(invvar, iv) < 1e-5
+
+
+def test_layer_norm_leading_dims_and_empty():
+    m = px.LayerNorm(128).to(DEV)
+    x = torch.randn(3, 5, 7, 128, device=DEV)
+    assert m(x).shape == x.shape
+    assert m(torch.empty(0, 128, device=DEV)).shape == (0, 128)
+    with pytest.raises(RuntimeError):
+        m(torch.randn(4, 64, device=DEV))
+
+
+# --------------------------------------------------------------------- per-op golden vectors
+@pytest.mark.parametrize("zdtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["tri_mul_out_n20", "tri_mul_in_n20", "tri_att_start_n20", "tri_att_end_n20",
+                                  "transition_pair"])
+def test_ops_against_reference_vectors(name, zdtype):
+    case = CASES[name]
+    m = build_module(case["kind"], case).to(DEV)
+    inp = make_inputs(case)
+    if case["kind"] == "transition":
+        y = m(cuda(inp["x"]).to(zdtype))
+    else:
+        y = m(cuda(inp["z"]).to(zdtype), mask=cuda(inp["mask"]))
+    assert y.dtype == zdtype
+    assert relf(y, golden()[name + ".y"]) < TOL_OP
+
+
+def test_transition_single_width_matches_reference_vector():
+    case = CASES["transition_single"]
+    m = build_module("transition", case).to(DEV)
+    assert relf(m(cuda(make_inputs(case)["x"])), golden()["transition_single.y"]) < 1e-4
+
+
+# ------------------------------------------------------------------ per-op, ragged sizes, masks
+def _mask(kind, n, seed):
+    if kind == "none":
+        return None
+    if kind == "pad":
+        return padding_mask(n, max(1, n // 10))
+    return random_mask(n, seed)
+
+
+@pytest.mark.parametrize("n,mask_kind,zdtype", [
+    (1, "none", torch.float32), (7, "rand", torch.bfloat16), (17, "pad", torch.float32),
+    (64, "none", torch.bfloat16), (100, "rand", torch.bfloat16), (128, "pad", torch.bfloat16),
+    (136, "rand", torch.float32), (200, "pad", torch.bfloat16), (257, "rand", torch.bfloat16)])
+@pytest.mark.parametrize("kind", ["tri_mul_out", "tri_mul_in", "tri_att_start", "tri_att_end"])
+def test_triangle_ops_vs_oracle(kind, n, mask_kind, zdtype):
+    g = torch.Generator().manual_seed(100 + n)
+    z = torch.randn(n, n, 128, generator=g)
+    mask = _mask(mask_kind, n, n)
+    m = build_module(kind, dict(wseed=n + 1)).to(DEV)
+    zq = z.to(zdtype)
+    y = m(cuda(zq), mask=cuda(mask))
+    p = params_of(m)
+    if kind.startswith("tri_mul"):
+        ref = O.triangle_multiplication(zq.float(), mask, p, outgoing=(kind == "tri_mul_out"))
+    else:
+        ref = O.triangle_attention(zq.float(), mask, p, starting=(kind == "tri_att_start"), row_chunk=64)
+    assert torch.isfinite(y.float()).all()
+    assert relf(y, ref) < TOL_OP, (kind, n, mask_kind)
+
+
+@pytest.mark.parametrize("rows", [1, 100, 128, 129, 1000])
+def test_transition_ragged_rows(rows):
+    m = build_module("transition", dict(c=128, n=4, wseed=77)).to(DEV)
+    x = torch.randn(rows, 128, generator=torch.Generator().manual_seed(rows))
+    for dt in (torch.float32, torch.bfloat16):
+        xq = x.to(dt)
+        assert relf(m(cuda(xq)), O.transition(xq.float(), params_of(m))) < TOL_OP
+
+
+# ----------------------------------------------------------------------- mask semantics (exact)
+@pytest.mark.parametrize("kind", ["tri_mul_out", "tri_mul_in", "tri_att_start", "tri_att_end"])
+def test_padded_positions_do_not_change_a_bit_of_the_valid_region(kind):
+    n, pad = 150, 20
+    g = torch.Generator().manual_seed(9)
+    z = torch.randn(n, n, 128, generator=g)
+    z2 = z.clone()
+    z2[n - pad:] += torch.randn(pad, n, 128, generator=g)
+    z2[:, n - pad:] += torch.randn(n, pad, 128, generator=g)
+    mask = cuda(padding_mask(n, pad))
+    m = build_module(kind, dict(wseed=12)).to(DEV)
+    v = n - pad
+    for dt in (torch.float32, torch.bfloat16):
+        a = m(cuda(z).to(dt), mask=mask)
+        b = m(cuda(z2).to(dt), mask=mask)
+        assert torch.equal(a[:v, :v], b[:v, :v])
+
+
+def test_fully_masked_rows_give_the_uniform_average_like_the_reference():
+    n = 40
+    g = torch.Generator().manual_seed(3)
+    z = torch.randn(n, n, 128, generator=g)
+    mask = torch.ones(n, n)
+    mask[5, :] = 0          # starting node: every key of row 5 is masked
+    m = build_module("tri_att_start", dict(wseed=8)).to(DEV)
+    y = m(cuda(z), mask=cuda(mask))
+    ref = O.triangle_attention(z, mask, params_of(m), starting=True)
+    assert torch.isfinite(y).all() and relf(y[5], ref[5]) < TOL_OP and relf(y, ref) < TOL_OP
+
+
+def test_mask_none_equals_all_ones():
+    n = 48
+    z = cuda(torch.randn(n, n, 128, generator=torch.Generator().manual_seed(4)))
+    for kind in ("tri_mul_in", "tri_att_end"):
+        m = build_module(kind, dict(wseed=5)).to(DEV)
+        assert torch.equal(m(z, mask=None), m(z, mask=torch.ones(n, n, device=DEV)))
+
+
+# ------------------------------------------------------------------------------ block and stack
+@pytest.mark.parametrize("zdtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["block_n24", "block_pair_n20"])
+def test_block_against_reference_vectors(name, zdtype):
+    case = CASES[name]
+    m = build_module("block", case).to(DEV)
+    inp = make_inputs(case)
+    s, z = m(cuda(inp["s"]), cuda(inp["z"]).to(zdtype), cuda(inp["mask"]))
+    g = golden()
+    assert relf(z, g[name + ".z"]) < TOL_BLOCK
+    if s is not None:
+        assert relf(s, g[name + ".s"]) < TOL_BLOCK
+
+
+def test_stack_against_reference_vectors():
+    case = CASES["stack2_n16"]
+    m = build_module("stack", case).to(DEV)
+    inp = make_inputs(case)
+    s, z = m(cuda(inp["s"]), cuda(inp["z"]), cuda(inp["mask"]))
+    g = golden()
+    assert relf(z, g["stack2_n16.z"]) < TOL_STACK and relf(s, g["stack2_n16.s"]) < TOL_STACK
+
+
+@pytest.mark.parametrize("zdtype", [torch.float32, torch.bfloat16])
+def test_block_config1_n128(zdtype):
+    """Single block, N=128, c_z=128, c_s=384, all-ones mask, z,s ~ N(0,1) (re-drawn weights)."""
+    n = 128
+    torch.manual_seed(0)
+    z, s = torch.randn(n, n, 128), torch.randn(n, 384)
+    m = build_module("block", dict(c_s=384, wseed=1)).to(DEV)
+    s1, z1 = m(cuda(s), cuda(z).to(zdtype), torch.ones(n, n, device=DEV))
+    s0, z0 = O.pairformer_block(s, z, torch.ones(n, n), params_of(m))
+    assert relf(z1, z0) < TOL_BLOCK and relf(s1, s0) < TOL_BLOCK
+    # update-only error: the residual does not hide it
+    assert relf(z1.float().cpu() - z.to(zdtype).float(), z0 - z) < 2e-2
+
+
+def test_stack_error_growth_stays_in_budget():
+    n, nb = 64, 6
+    g = torch.Generator().manual_seed(21)
+    z, s = torch.randn(n, n, 128, generator=g), torch.randn(n, 384, generator=g)
+    mask = padding_mask(n, 5)
+    m = build_module("stack", dict(n_blocks=nb, c_s=384, wseed=31)).to(DEV)
+    s0, z0 = O.pairformer_stack(s, z, mask, params_of(m), n_blocks=nb)
+    for dt in (torch.float32, torch.bfloat16):
+        s1, z1 = m(cuda(s), cuda(z).to(dt), cuda(mask))
+        assert relf(z1, z0) < TOL_STACK and relf(s1, s0) < TOL_STACK
+
+
+def test_block_api_contract():
+    n = 33
+    g = torch.Generator().manual_seed(2)
+    z = cuda(torch.randn(n, n, 128, generator=g))
+    s = cuda(torch.randn(n, 384, generator=g))
+    mask = cuda(padding_mask(n, 3))
+    m = build_module("block", dict(c_s=384, wseed=6)).to(DEV)
+    z_keep = z.clone()
+    s1, z1 = m(s, z, mask, triangle_multiplicative="cuequivariance", triangle_attention="triattention", chunk_size=64)
+    assert torch.equal(z, z_keep) and z1.data_ptr() != z.data_ptr()          # functional by default
+    zi = z.clone()
+    s2, z2 = m(s, zi, mask, inplace_safe=True)
+    assert z2.data_ptr() == zi.data_ptr() and torch.equal(z2, z1) and torch.equal(s2, s1)   # in-place == functional
+    s3, z3 = m(s, z, mask)
+    assert torch.equal(z3, z1) and torch.equal(s3, s1)                         # run-to-run determinism
+    s4, z4 = m(s, z[None], mask[None])                                         # batch of one, as the reference's test
+    assert z4.shape == (1, n, n, 128) and torch.equal(z4[0], z1)
+    sp, zp = build_module("block", dict(c_s=0, wseed=6)).to(DEV)(None, z, mask)
+    assert sp is None and zp.shape == z.shape
+    with pytest.raises(RuntimeError):
+        m(s, z[:, :, :64].contiguous(), mask)
+
+
+def test_tri_mul_add_with_inplace_returns_sum():
+    n = 40
+    z = cuda(torch.randn(n, n, 128, generator=torch.Generator().manual_seed(8)))
+    m = build_module("tri_mul_out", dict(wseed=2)).to(DEV)
+    upd = m(z)
+    zi = z.clone()
+    out = m(zi, inplace_safe=True, _add_with_inplace=True)
+    assert out.data_ptr() == zi.data_ptr() and relf(out, z + upd) < 1e-6
+
+
+def test_state_dict_round_trip_changes_results():
+    n = 24
+    z = cuda(torch.randn(n, n, 128, generator=torch.Generator().manual_seed(1)))
+    a = build_module("block", dict(c_s=0, wseed=1)).to(DEV)
+    b = build_module("block", dict(c_s=0, wseed=2)).to(DEV)
+    za = a(None, z, None)[1]
+    assert not torch.equal(za, b(None, z, None)[1])
+    b.load_state_dict(a.state_dict(), strict=True)
+    assert torch.equal(za, b(None, z, None)[1])

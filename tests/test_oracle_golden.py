@@ -81,3 +81,25 @@ def test_mask_independence_is_bit_exact_in_oracle():
         a = O.triangle_attention(z, mask, p, starting=(kind == "tri_att_start"))
         b = O.triangle_attention(z2, mask, p, starting=(kind == "tri_att_start"))
         assert torch.equal(a[:v, :v], b[:v, :v])
+
+
+def test_row_slab_timing_sample_equals_the_full_updates():
+    """The CPU-baseline sample computes exactly a row slab of each of the five pair updates."""
+    from golden_cases import random_mask
+
+    n, r0, r1 = 40, 8, 20
+    p = params_of(build_module("block", dict(c_s=0, wseed=3)))
+    z = torch.randn(n, n, 128, generator=torch.Generator().manual_seed(1))
+    mask = random_mask(n, 1)
+    slab, shared = O.pair_path_row_slab(z, mask, p, r0, r1)
+    slab2, _ = O.pair_path_row_slab(z, mask, p, r0, r1, shared)
+    full = {
+        "tri_mul_out": O.triangle_multiplication(z, mask, O._sub(p, "tri_mul_out"), True)[r0:r1],
+        "tri_mul_in": O.triangle_multiplication(z, mask, O._sub(p, "tri_mul_in"), False)[r0:r1],
+        "tri_att_start": O.triangle_attention(z, mask, O._sub(p, "tri_att_start"), True)[r0:r1],
+        "tri_att_end": O.triangle_attention(z, mask, O._sub(p, "tri_att_end"), False).transpose(0, 1)[r0:r1],
+        "pair_transition": O.transition(z, O._sub(p, "pair_transition"))[r0:r1],
+    }
+    for k, v in full.items():
+        assert relf(slab[k], v) < 1e-5, k
+        assert torch.equal(slab[k], slab2[k])
