@@ -177,8 +177,8 @@ static cudaError_t dispatch(const void* x, const void* g, const void* b, void* y
 extern "C" int32_t px_layer_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean,
                                      float* invvar, int64_t rows, int64_t cols, float eps, int32_t dtype,
                                      void* stream) {
+  if (rows == 0 && cols > 0) return PX_OK;  // empty input: nothing to launch, pointers may be null
   if (!x || !y || rows < 0 || cols <= 0 || cols > (1 << 30)) return PX_ERR_BAD_ARG;
-  if (rows == 0) return PX_OK;
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
   switch (dtype) {
