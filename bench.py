@@ -39,6 +39,8 @@ def parse_args():
     ap.add_argument("--z-dtype", default="bf16", choices=["bf16", "fp32"])
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU row-slab sample (0 = auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--micro", action="store_true",
+                    help="per-kernel micro-benchmark of one block (tri-att start/end, tri-mul out/in, transition)")
     return ap.parse_args()
 
 
@@ -171,10 +173,76 @@ def workload_config(args, world: int) -> dict:
             "parallelism": "single GPU" if world == 1 else f"replicas x{world}"}
 
 
+def kernel_algo(n: int, zbytes: int) -> dict:
+    """Algorithmic FLOPs (tensor-bound kernels) or bytes (HBM-bound kernels) of one launch."""
+    n2 = float(n) * n
+    return {
+        "px_triatt_flash": ("tensor", 512.0 * n ** 3),
+        "px_trimul_contract": ("tensor", 256.0 * n ** 3),
+        "px_transition": ("tensor", 393216.0 * n2),
+        "px_trimul_in_proj": ("hbm", (128 * zbytes + 4 + 512) * n2),
+        "px_trimul_out": ("hbm", (256 + 2 * 128 * zbytes) * n2),
+        "px_triatt_in_proj": ("hbm", (128 * zbytes + 4 + 768 + 20) * n2),
+        "px_triatt_out": ("hbm", (256 + 2 * 128 * zbytes) * n2),
+        "px_pair_bias_proj": ("hbm", (128 * zbytes + 64) * n2),
+    }
+
+
+def run_micro(args) -> None:
+    """One block's kernels timed one by one (N=768 by default via --n-token): last 10 % of tokens masked."""
+    import torch
+
+    import protenix_b200 as px
+    from protenix_b200 import ops
+    from protenix_b200.init_utils import randomize_parameters_
+
+    torch.cuda.set_device(0)
+    n = args.n_token
+    zdt = torch.bfloat16 if args.z_dtype == "bf16" else torch.float32
+    blk = randomize_parameters_(px.PairformerBlock(c_s=0), 1).eval().cuda()
+    z = torch.randn(n, n, 128, generator=torch.Generator().manual_seed(0)).to(zdt).cuda()
+    t = torch.ones(n)
+    t[n - n // 10:] = 0
+    mask = (t[:, None] * t[None, :]).cuda()
+    work = torch.empty_like(z)
+    variants = [("tri_mul_out", lambda: blk.tri_mul_out.apply_(work, mask)),
+                ("tri_mul_in", lambda: blk.tri_mul_in.apply_(work, mask)),
+                ("tri_att_start", lambda: blk.tri_att_start.apply_(work, mask, ending=False)),
+                ("tri_att_end", lambda: blk.tri_att_end.apply_(work, mask, ending=True)),
+                ("pair_transition", lambda: blk.pair_transition.forward_residual_(work))]
+    pk = peaks()
+    algo = kernel_algo(n, z.element_size())
+    out = {}
+    for name, fn in variants:
+        for _ in range(args.warmup):
+            work.copy_(z)
+            fn()
+        torch.cuda.synchronize()
+        timer = ops.StageTimer()
+        ops.set_stage_timer(timer)
+        for _ in range(args.steps):
+            work.copy_(z)
+            fn()
+        torch.cuda.synchronize()
+        ops.set_stage_timer(None)
+        for k, (cnt, tot) in timer.summary().items():
+            ms = tot / cnt
+            bound, work_units = algo[k]
+            ach = work_units / (ms * 1e-3) / (1e12 if bound == "tensor" else 1e9)
+            peak = pk["tflops"] if bound == "tensor" else pk["hbm_gbs"]
+            out[f"{name}/{k}"] = {"ms": round(ms, 4), "bound": bound, "achieved": round(ach, 1),
+                                  "unit": "TFLOP/s" if bound == "tensor" else "GB/s", "frac": round(ach / peak, 4)}
+    print(json.dumps({"micro": True, "n_token": n, "z_storage": args.z_dtype, "peak_source": pk["source"],
+                      "steps": args.steps, "warmup": args.warmup, "kernels": out}), flush=True)
+
+
 def main() -> None:
     args = parse_args()
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.micro:
+        run_micro(args)
         return
 
     import torch
@@ -277,15 +345,7 @@ def main() -> None:
     name = max(stages, key=lambda k: stages[k][1])
     cnt, tot = stages[name]
     avg_ms = tot / cnt
-    algo = {  # algorithmic FLOPs / bytes per launch
-        "px_triatt_flash": ("tensor", 512.0 * n ** 3),
-        "px_trimul_contract": ("tensor", 256.0 * n ** 3),
-        "px_transition": ("tensor", 393216.0 * n * n),
-        "px_trimul_in_proj": ("hbm", (128 * z0.element_size() + 4 + 512) * n * n),
-        "px_trimul_out": ("hbm", (256 + 2 * 128 * z0.element_size()) * n * n),
-        "px_triatt_in_proj": ("hbm", (128 * z0.element_size() + 4 + 768 + 20) * n * n),
-        "px_triatt_out": ("hbm", (256 + 2 * 128 * z0.element_size()) * n * n),
-    }.get(name, ("hbm", 0.0))
+    algo = kernel_algo(n, z0.element_size()).get(name, ("hbm", 0.0))
     if algo[0] == "tensor":
         achieved, peak, runit = algo[1] / (avg_ms * 1e-3) / 1e12, pk["tflops"], "TFLOP/s"
     else:

@@ -55,6 +55,8 @@ PX_API int32_t px_version(void);
 PX_API const char* px_status_string(int32_t status);
 /* Leading dimension used for intermediates: N rounded up to a multiple of 8. */
 PX_API int64_t px_ld(int64_t n);
+/* Row stride of the attention bias tensors: N rounded up to a multiple of 64 (one key tile). */
+PX_API int64_t px_ld_mask(int64_t n);
 
 /* ---- LayerNorm op ---------------------------------------------------------------------
  * y = (x - mean) * rsqrt(var + eps) * gamma + beta over the last axis of x[rows][cols];
@@ -99,20 +101,21 @@ PX_API int32_t px_triangle_multiplication(const void* z_in, void* z_out, int32_t
 /* ---- Triangle attention (starting / ending node), 4 heads x 32 -------------------------
  * Stage 1: xn = LN(z); q,k,v = W xn written per attended row u as [u][h][t][32] bf16 with q
  * pre-scaled by log2(e)/sqrt(32); bias[h][u][t] = log2(e) * (W_b xn)[u][t][h] (fp32, row
- * stride ld); mask_bias[u][t] = log2(e) * inf * (mask - 1) (fp32, row stride ld).  For the
+ * stride ldm = px_ld_mask(N), zero in the pad columns); mask_bias[u][t] = log2(e) * inf *
+ * (mask - 1) (fp32, row stride ldm, -infinity in the pad columns).  For the
  * ending node the pair element read for (u,t) is z[t][u] and mask[t][u], which is what the
  * reference obtains by transposing z (protenix/model/modules/pairformer.py:160-168).
  * Replaces protenix/model/triangular/triangular.py:683-692 and layers.py:361-382. */
 PX_API int32_t px_triatt_in_proj(const void* z, int32_t z_dtype, const float* mask, const float* ln_w, const float* ln_b,
                           const px_bf16* w_q, const px_bf16* w_k, const px_bf16* w_v, const px_bf16* w_bias,
-                          px_bf16* q, px_bf16* k, px_bf16* v, float* bias, float* mask_bias, int64_t n, int64_t ld,
+                          px_bf16* q, px_bf16* k, px_bf16* v, float* bias, float* mask_bias, int64_t n, int64_t ldm,
                           int32_t ending, float eps, float inf, void* stream);
 /* Stage 2: o[u][t][h*32+d] = softmax_k(q.k + bias[h][t][k] + mask_bias[u][k]) v, online
  * softmax in base 2, logits never leave the SM.  Replaces the back-ends selected in
  * protenix/model/triangular/layers.py:441-469 (_attention :276-296, the Triton kernel
  * protenix/model/tri_attention/forward.py:22-188, DS4Sci and cuEquivariance calls). */
 PX_API int32_t px_triatt_flash(const px_bf16* q, const px_bf16* k, const px_bf16* v, const float* bias,
-                        const float* mask_bias, px_bf16* o, int64_t n, int64_t ld, void* stream);
+                        const float* mask_bias, px_bf16* o, int64_t n, int64_t ldm, void* stream);
 /* Stage 3: z_out(u,t) = [z_in(u,t) +] W_o (o[u][t] * sigmoid(W_g LN(z_in(u,t)))), where (u,t)
  * addresses z[u][t] (starting) or z[t][u] (ending).  z_out may alias z_in.
  * Replaces Attention._wrap_up, protenix/model/triangular/layers.py:384-398. */

@@ -65,6 +65,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
 }
+// 2^x for a packed pair: the arguments are rounded to bf16, the results are bf16 (one MUFU op for two).
+__device__ __forceinline__ uint32_t exp2_bf16x2(float lo, float hi) {
+  uint32_t x = pack_bf16x2(lo, hi), y;
+  asm("ex2.approx.ftz.bf16x2 %0, %1;\n" : "=r"(y) : "r"(x));
+  return y;
+}
 __device__ __forceinline__ float sigmoidf_fast(float x) {
   return __fdividef(1.0f, 1.0f + fast_exp2(-kLog2e * x));
 }

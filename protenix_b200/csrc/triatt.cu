@@ -24,7 +24,7 @@ triatt_in_proj_kernel(const Tz* __restrict__ z, const float* __restrict__ mask, 
                       const float* __restrict__ ln_b, const bf16* __restrict__ w_q, const bf16* __restrict__ w_k,
                       const bf16* __restrict__ w_v, const bf16* __restrict__ w_bias, bf16* __restrict__ q_out,
                       bf16* __restrict__ k_out, bf16* __restrict__ v_out, float* __restrict__ bias_out,
-                      float* __restrict__ mb_out, int n, int ld, int swap, float eps, float inf) {
+                      float* __restrict__ mb_out, int n, int ldm, int swap, float eps, float inf) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   TriAttInSmem& sm = *reinterpret_cast<TriAttInSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -51,12 +51,12 @@ triatt_in_proj_kernel(const Tz* __restrict__ z, const float* __restrict__ mask, 
   uint32_t afr[8][4];
   load_a_frags(afr, sm.A, warp, lane);
 
-  if (tid < 128) {
+  if (tid < 128) {  // mask bias, -inf in the pad columns [n, ldm)
     const int t = t0 + tid;
-    if (t < ld) {
-      float mv = 0.f;
-      if (t < n && mask) mv = (mask[pair_index(t)] - 1.0f) * inf * kLog2e;
-      mb_out[(size_t)u * ld + t] = mv;
+    if (t < ldm) {
+      float mv = -CUDART_INF_F;
+      if (t < n) mv = mask ? (mask[pair_index(t)] - 1.0f) * inf * kLog2e : 0.f;
+      mb_out[(size_t)u * ldm + t] = mv;
     }
   }
 
@@ -94,8 +94,9 @@ triatt_in_proj_kernel(const Tz* __restrict__ z, const float* __restrict__ mask, 
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int head = 2 * tq + e;
-          if (tr < n) bias_out[((size_t)head * n + u) * ld + tr] = acc[0][e] * kLog2e;
-          if (tr + 8 < n) bias_out[((size_t)head * n + u) * ld + tr + 8] = acc[0][2 + e] * kLog2e;
+          // zero in the pad columns [n, ldm)
+          if (tr < ldm) bias_out[((size_t)head * n + u) * ldm + tr] = tr < n ? acc[0][e] * kLog2e : 0.f;
+          if (tr + 8 < ldm) bias_out[((size_t)head * n + u) * ldm + tr + 8] = tr + 8 < n ? acc[0][2 + e] * kLog2e : 0.f;
         }
       }
     }
@@ -105,8 +106,11 @@ triatt_in_proj_kernel(const Tz* __restrict__ z, const float* __restrict__ mask, 
 
 // =========================================================================================
 // Stage 2: flash attention.  One CTA = (64 queries, head h, R attended rows u); 4 warps x 16
-// queries.  For every 64-key tile the pair-bias fragment [q][k] is fetched once and reused by
-// the R rows; logits start as bias + mask_bias in the accumulator of the q.k product.
+// queries.  For every 64-key tile the pair-bias fragment [q][k] is fetched once (prefetched one
+// tile ahead into registers) and reused by the R rows; logits start as bias + mask_bias in the
+// accumulator of the q.k product.  K, V and mask_bias tiles arrive through a double-buffered
+// cp.async pipeline.  bias and mask_bias rows are padded to a multiple of 64 keys (bias 0,
+// mask_bias -inf in the pad) so the inner loop carries no column predicates.
 // =========================================================================================
 constexpr int kFaLd = kD + 8;  // shared row stride of q/k/v tiles (80 bytes: conflict-free ldmatrix)
 
@@ -115,13 +119,14 @@ struct FlashSmem {
   bf16 Q[R][64 * kFaLd];
   bf16 K[2][R][64 * kFaLd];
   bf16 V[2][R][64 * kFaLd];
+  float MB[2][R][64];
 };
 
 template <int R>
-__global__ void __launch_bounds__(128, 3)
+__global__ void __launch_bounds__(128, 2)
 triatt_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                     const float* __restrict__ bias, const float* __restrict__ mb, bf16* __restrict__ o, int n,
-                    int ld) {
+                    int ldm) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   FlashSmem<R>& sm = *reinterpret_cast<FlashSmem<R>*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -144,6 +149,11 @@ triatt_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
         cp_async16(smem_u32(sm.V[stage][r] + row * kFaLd + ch * 8), v + off, p);
       }
     }
+    if (tid < R * 16) {
+      const int r = tid >> 4, ch = tid & 15;
+      const bool urow = (u0 + r) < n;
+      cp_async16(smem_u32(&sm.MB[stage][r][ch * 4]), mb + (urow ? (size_t)(u0 + r) * ldm + kt * 64 + ch * 4 : 0), urow);
+    }
   };
 #pragma unroll
   for (int r = 0; r < R; ++r) {
@@ -160,15 +170,26 @@ triatt_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
   cp_async_commit();
 
   uint32_t qf[R][2][4];
-  float oacc[R][4][4], mrow[R][2], lrow[R][2];
+  // oacc[r][0..3]: output columns; oacc[r][4]: row sums of P, produced by the same MMA against a
+  // constant "ones" column, so they are rescaled together with the output.
+  float oacc[R][5][4], mrow[R][2];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     mrow[r][0] = mrow[r][1] = -CUDART_INF_F;
-    lrow[r][0] = lrow[r][1] = 0.f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) oacc[r][j][0] = oacc[r][j][1] = oacc[r][j][2] = oacc[r][j][3] = 0.f;
+    for (int j = 0; j < 5; ++j) oacc[r][j][0] = oacc[r][j][1] = oacc[r][j][2] = oacc[r][j][3] = 0.f;
   }
+  const uint32_t ones_b = (g == 0) ? 0x3F803F80u : 0u;  // B fragment of a [16 x 8] tile whose column 0 is 1
   const int qr = q0 + 16 * warp + g;  // this thread's query rows: qr and qr + 8
+  // rows of the pair bias this thread reads (clamped: out-of-range queries are never stored)
+  const float* brow0 = bias + ((size_t)h * n + min(qr, n - 1)) * ldm + 2 * tq;
+  const float* brow1 = bias + ((size_t)h * n + min(qr + 8, n - 1)) * ldm + 2 * tq;
+  float2 bnext[8][2];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    bnext[j][0] = *reinterpret_cast<const float2*>(brow0 + 8 * j);
+    bnext[j][1] = *reinterpret_cast<const float2*>(brow1 + 8 * j);
+  }
 
   for (int kt = 0; kt < nkt; ++kt) {
     cp_async_wait<0>();
@@ -181,41 +202,32 @@ triatt_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
 #pragma unroll
         for (int ks = 0; ks < 2; ++ks) load_a_frag(qf[r][ks], sm.Q[r], kFaLd, warp, lane, ks);
     }
-    const int k0 = kt * 64;
-    // pair-bias fragment, shared by the R rows
-    float bfr[8][4];
+    // pair-bias fragment of this tile (shared by the R rows); fetch the next tile's behind the math
+    float2 bcur[8][2];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const int kc = k0 + 8 * j + 2 * tq;
-      float2 b0 = make_float2(0.f, 0.f), b1 = make_float2(0.f, 0.f);
-      if (kc < n) {
-        if (qr < n) b0 = *reinterpret_cast<const float2*>(bias + ((size_t)h * n + qr) * ld + kc);
-        if (qr + 8 < n) b1 = *reinterpret_cast<const float2*>(bias + ((size_t)h * n + qr + 8) * ld + kc);
-        if (kc + 1 >= n) b0.y = b1.y = 0.f;
+      bcur[j][0] = bnext[j][0];
+      bcur[j][1] = bnext[j][1];
+    }
+    if (kt + 1 < nkt) {
+      const int ko = (kt + 1) * 64;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        bnext[j][0] = *reinterpret_cast<const float2*>(brow0 + ko + 8 * j);
+        bnext[j][1] = *reinterpret_cast<const float2*>(brow1 + ko + 8 * j);
       }
-      bfr[j][0] = b0.x;
-      bfr[j][1] = b0.y;
-      bfr[j][2] = b1.x;
-      bfr[j][3] = b1.y;
     }
     const int stage = kt & 1;
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      if (u0 + r >= n) continue;
+    for (int r = 0; r < R; ++r) {  // rows past the end run on zero tiles and are not stored
       float s[8][4];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const int kc = k0 + 8 * j + 2 * tq;
-        float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F;
-        if (kc < n) {
-          float2 mv = *reinterpret_cast<const float2*>(mb + (size_t)(u0 + r) * ld + kc);
-          m0 = mv.x;
-          if (kc + 1 < n) m1 = mv.y;
-        }
-        s[j][0] = bfr[j][0] + m0;
-        s[j][1] = bfr[j][1] + m1;
-        s[j][2] = bfr[j][2] + m0;
-        s[j][3] = bfr[j][3] + m1;
+        const float2 mv = *reinterpret_cast<const float2*>(&sm.MB[stage][r][8 * j + 2 * tq]);
+        s[j][0] = bcur[j][0].x + mv.x;
+        s[j][1] = bcur[j][0].y + mv.y;
+        s[j][2] = bcur[j][1].x + mv.x;
+        s[j][3] = bcur[j][1].y + mv.y;
       }
       // S += Q K^T
       {
@@ -247,21 +259,14 @@ triatt_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
       const float al0 = fast_exp2(mrow[r][0] - mn0), al1 = fast_exp2(mrow[r][1] - mn1);
       mrow[r][0] = mn0;
       mrow[r][1] = mn1;
-      float sum0 = 0.f, sum1 = 0.f;
       uint32_t pf[4][4];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float p0 = fast_exp2(s[j][0] - mn0), p1 = fast_exp2(s[j][1] - mn0);
-        const float p2 = fast_exp2(s[j][2] - mn1), p3 = fast_exp2(s[j][3] - mn1);
-        sum0 += p0 + p1;
-        sum1 += p2 + p3;
-        pf[j >> 1][(j & 1) * 2] = pack_bf16x2(p0, p1);
-        pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16x2(p2, p3);
+        pf[j >> 1][(j & 1) * 2] = exp2_bf16x2(s[j][0] - mn0, s[j][1] - mn0);
+        pf[j >> 1][(j & 1) * 2 + 1] = exp2_bf16x2(s[j][2] - mn1, s[j][3] - mn1);
       }
-      lrow[r][0] = lrow[r][0] * al0 + sum0;
-      lrow[r][1] = lrow[r][1] * al1 + sum1;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < 5; ++j) {
         oacc[r][j][0] *= al0;
         oacc[r][j][1] *= al0;
         oacc[r][j][2] *= al1;
@@ -281,6 +286,8 @@ triatt_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
             mma_bf16(oacc[r][2 * dp], pf[kk], b[0], b[1]);
             mma_bf16(oacc[r][2 * dp + 1], pf[kk], b[2], b[3]);
           }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) mma_bf16(oacc[r][4], pf[kk], ones_b, ones_b);
       }
     }
   }
@@ -288,11 +295,9 @@ triatt_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     if (u0 + r >= n) continue;
-    float l0 = lrow[r][0], l1 = lrow[r][1];
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    // row sums sit in column 0 of the extra tile: lane 4*g of each quad holds them
+    const float l0 = __shfl_sync(0xffffffffu, oacc[r][4][0], lane & ~3);
+    const float l1 = __shfl_sync(0xffffffffu, oacc[r][4][2], lane & ~3);
     const float i0 = 1.0f / l0, i1 = 1.0f / l1;
     bf16* orow = o + ((size_t)(u0 + r) * n) * kC + h * kD;
 #pragma unroll
@@ -409,17 +414,17 @@ static size_t align256(size_t b) { return (b + 255) / 256 * 256; }
 
 using namespace px;
 
-static bool att_bad_n(int64_t n, int64_t ld) { return n <= 0 || n > 32768 || ld != px_ld(n); }
+static bool att_bad_n(int64_t n, int64_t ldm) { return n <= 0 || n > 32768 || ldm != px_ld_mask(n); }
 
 extern "C" int32_t px_triatt_in_proj(const void* z, int32_t z_dtype, const float* mask, const float* ln_w,
                                      const float* ln_b, const px_bf16* w_q, const px_bf16* w_k, const px_bf16* w_v,
                                      const px_bf16* w_bias, px_bf16* q, px_bf16* k, px_bf16* v, float* bias,
-                                     float* mask_bias, int64_t n, int64_t ld, int32_t ending, float eps, float inf,
+                                     float* mask_bias, int64_t n, int64_t ldm, int32_t ending, float eps, float inf,
                                      void* stream) {
   if (!z || !ln_w || !ln_b || !w_q || !w_k || !w_v || !w_bias || !q || !k || !v || !bias || !mask_bias ||
-      att_bad_n(n, ld))
+      att_bad_n(n, ldm))
     return PX_ERR_BAD_ARG;
-  dim3 grid((unsigned)((ld + 127) / 128), (unsigned)n);
+  dim3 grid((unsigned)((n + 127) / 128), (unsigned)n);   // 128-wide tiles cover the pad columns up to ldm too
   const size_t smem = sizeof(TriAttInSmem);
   cudaStream_t st = (cudaStream_t)stream;
   if (z_dtype == PX_F32) {
@@ -428,14 +433,14 @@ extern "C" int32_t px_triatt_in_proj(const void* z, int32_t z_dtype, const float
       return PX_ERR_LAUNCH;
     triatt_in_proj_kernel<float><<<grid, 256, smem, st>>>(
         (const float*)z, mask, ln_w, ln_b, (const bf16*)w_q, (const bf16*)w_k, (const bf16*)w_v,
-        (const bf16*)w_bias, (bf16*)q, (bf16*)k, (bf16*)v, bias, mask_bias, (int)n, (int)ld, ending, eps, inf);
+        (const bf16*)w_bias, (bf16*)q, (bf16*)k, (bf16*)v, bias, mask_bias, (int)n, (int)ldm, ending, eps, inf);
   } else if (z_dtype == PX_BF16) {
     if (cudaFuncSetAttribute(triatt_in_proj_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return PX_ERR_LAUNCH;
     triatt_in_proj_kernel<bf16><<<grid, 256, smem, st>>>(
         (const bf16*)z, mask, ln_w, ln_b, (const bf16*)w_q, (const bf16*)w_k, (const bf16*)w_v, (const bf16*)w_bias,
-        (bf16*)q, (bf16*)k, (bf16*)v, bias, mask_bias, (int)n, (int)ld, ending, eps, inf);
+        (bf16*)q, (bf16*)k, (bf16*)v, bias, mask_bias, (int)n, (int)ldm, ending, eps, inf);
   } else {
     return PX_ERR_UNSUPPORTED;
   }
@@ -445,15 +450,15 @@ extern "C" int32_t px_triatt_in_proj(const void* z, int32_t z_dtype, const float
 constexpr int kFlashR = 2;
 
 extern "C" int32_t px_triatt_flash(const px_bf16* q, const px_bf16* k, const px_bf16* v, const float* bias,
-                                   const float* mask_bias, px_bf16* o, int64_t n, int64_t ld, void* stream) {
-  if (!q || !k || !v || !bias || !mask_bias || !o || att_bad_n(n, ld)) return PX_ERR_BAD_ARG;
+                                   const float* mask_bias, px_bf16* o, int64_t n, int64_t ldm, void* stream) {
+  if (!q || !k || !v || !bias || !mask_bias || !o || att_bad_n(n, ldm)) return PX_ERR_BAD_ARG;
   dim3 grid((unsigned)((n + 63) / 64), kH, (unsigned)((n + kFlashR - 1) / kFlashR));
   const size_t smem = sizeof(FlashSmem<kFlashR>);
   if (cudaFuncSetAttribute(triatt_flash_kernel<kFlashR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
     return PX_ERR_LAUNCH;
   triatt_flash_kernel<kFlashR><<<grid, 128, smem, (cudaStream_t)stream>>>(
-      (const bf16*)q, (const bf16*)k, (const bf16*)v, bias, mask_bias, (bf16*)o, (int)n, (int)ld);
+      (const bf16*)q, (const bf16*)k, (const bf16*)v, bias, mask_bias, (bf16*)o, (int)n, (int)ldm);
   return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
 }
 
@@ -484,10 +489,12 @@ extern "C" int32_t px_triatt_out(const px_bf16* o, const void* z_in, void* z_out
   return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
 }
 
-// workspace layout: q | k | v | o (bf16) | bias (fp32 [4][n][ld]) | mask_bias (fp32 [n][ld])
+extern "C" int64_t px_ld_mask(int64_t n) { return (n + 63) / 64 * 64; }
+
+// workspace layout: q | k | v | o (bf16) | bias (fp32 [4][n][ldm]) | mask_bias (fp32 [n][ldm])
 extern "C" int64_t px_triatt_workspace_bytes(int64_t n) {
   if (n <= 0) return 0;
-  const int64_t ld = px_ld(n);
+  const int64_t ld = px_ld_mask(n);
   return (int64_t)(3 * align256(att_qkv_elems(n) * 2) + align256((size_t)n * n * kC * 2) +
                    align256((size_t)kH * n * ld * 4) + align256((size_t)n * ld * 4));
 }
@@ -500,7 +507,7 @@ extern "C" int32_t px_triangle_attention(const void* z_in, void* z_out, int32_t 
                                          float eps, float inf, void* stream) {
   if (!workspace || n <= 0 || ((uintptr_t)workspace & 255)) return PX_ERR_BAD_ARG;
   if (workspace_bytes < px_triatt_workspace_bytes(n)) return PX_ERR_WORKSPACE;
-  const int64_t ld = px_ld(n);
+  const int64_t ld = px_ld_mask(n);
   unsigned char* p = (unsigned char*)workspace;
   px_bf16* q = (px_bf16*)p;
   p += align256(att_qkv_elems(n) * 2);

@@ -203,7 +203,7 @@ def triangle_attention(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optional[t
         _check_w(w, (C_Z, C_Z), nm)
     lib = _lib.load()
     ws = workspace(z_in.device, lib.px_triatt_workspace_bytes(n))
-    ldn = lib.px_ld(n)
+    ldn = lib.px_ld_mask(n)
     al = lambda nb: (nb + 255) // 256 * 256
     qkv = al(n * N_HEAD_PAIR * n * D_HEAD_PAIR * 2)
     q = ws.data_ptr()
