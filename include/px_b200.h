@@ -36,6 +36,9 @@ extern "C" {
 #define PX_ERR_UNSUPPORTED (-2) /* shape / dtype outside the compiled specialisations   */
 #define PX_ERR_LAUNCH (-3)      /* the CUDA runtime refused the launch                  */
 #define PX_ERR_WORKSPACE (-4)   /* workspace too small                                  */
+#define PX_ERR_TOO_LARGE (-5)   /* N beyond the capacity of the built-in scratch array  */
+
+#define PX_STATIC_MAX_N 128     /* largest N px_triangle_multiplication_static accepts  */
 
 #define PX_F32 0
 #define PX_BF16 1
@@ -97,6 +100,28 @@ PX_API int32_t px_triangle_multiplication(const void* z_in, void* z_out, int32_t
                                    const px_bf16* w_bp, const px_bf16* w_bg, const px_bf16* w_z, const px_bf16* w_g,
                                    void* workspace, int64_t workspace_bytes, int64_t n, int32_t incoming,
                                    int32_t add_residual, float eps, void* stream);
+
+/* Triangle multiplication without any workspace argument, for callers that must not or cannot
+ * allocate device memory: a plug-in running inside a host application that has handed all device
+ * memory to its own pool (cudaMalloc then fails), or a latency-critical thread that must avoid
+ * cudaMalloc/cudaFree because they synchronise the device.  The scratch for a, b and x is a
+ * 12 MiB array inside the library image (held by every GPU that loads the library until the
+ * process exits), so N is limited to PX_STATIC_MAX_N = 128; a larger N returns PX_ERR_TOO_LARGE.
+ * The call itself allocates nothing.  Its first call on a device looks up the array's device
+ * address (cudaGetSymbolAddress, with that device current); make that first call before any stream
+ * capture.  All calls on one device share the one array: calls that overlap on the GPU (different
+ * streams, or different host threads without ordering) race on it and must be serialised by the
+ * caller.  Nothing needs clearing between calls: each call writes every scratch element it reads.
+ * Results are those of px_triangle_multiplication on the same inputs.
+ * This entry point has no counterpart in the reference. */
+PX_API int32_t px_triangle_multiplication_static(const void* z_in, void* z_out, int32_t z_dtype, const float* mask,
+                                          const float* ln_in_w, const float* ln_in_b, const float* ln_out_w,
+                                          const float* ln_out_b, const px_bf16* w_ap, const px_bf16* w_ag,
+                                          const px_bf16* w_bp, const px_bf16* w_bg, const px_bf16* w_z,
+                                          const px_bf16* w_g, int64_t n, int32_t incoming, int32_t add_residual,
+                                          float eps, void* stream);
+/* PX_STATIC_MAX_N as seen by the loaded library. */
+PX_API int64_t px_static_max_n(void);
 
 /* ---- Triangle attention (starting / ending node), 4 heads x 32 -------------------------
  * Stage 1: xn = LN(z); q,k,v = W xn written per attended row u as [u][h][t][32] bf16 with q

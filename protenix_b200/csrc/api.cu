@@ -10,6 +10,7 @@ extern "C" const char* px_status_string(int32_t status) {
     case PX_ERR_UNSUPPORTED: return "shape or dtype outside the compiled specialisations (c_z=128, 4 heads x 32, expansion 4)";
     case PX_ERR_LAUNCH: return "the CUDA runtime refused the kernel launch";
     case PX_ERR_WORKSPACE: return "workspace too small";
+    case PX_ERR_TOO_LARGE: return "N exceeds the capacity of the built-in scratch array (N <= 128)";
     default: return "unknown status";
   }
 }
