@@ -81,9 +81,14 @@ PX_API int32_t px_trimul_in_proj(const void* z, int32_t z_dtype, const float* ma
                           const px_bf16* w_ap, const px_bf16* w_ag, const px_bf16* w_bp, const px_bf16* w_bg,
                           px_bf16* a, px_bf16* b, int64_t n, int64_t ld, int32_t incoming, float eps, void* stream);
 /* Stage 2: x[c][i][j] = sum_k a[c][i][k] * b[c][j][k] for the 128 channels (bf16 in, fp32
- * accumulate, bf16 out, row stride ld).  Replaces _combine_projections,
- * protenix/model/triangular/triangular.py:123-150. */
+ * accumulate, bf16 out, row stride ld) on the tcgen05 tensor cores: persistent kernel, TMA-fed
+ * 128x256x64 tiles, fp32 accumulators in tensor memory, double-buffered epilogue.  a, b, x must be
+ * 16-byte aligned.  Replaces _combine_projections, protenix/model/triangular/triangular.py:123-150. */
 PX_API int32_t px_trimul_contract(const px_bf16* a, const px_bf16* b, px_bf16* x, int64_t n, int64_t ld, void* stream);
+/* Synchronises the device, then returns and clears the flags set by device-side bounded waits
+ * that ran out (0 = none).  A non-zero value means a kernel gave up waiting and its output is
+ * not valid.  No counterpart in the reference. */
+PX_API int32_t px_device_error_flags(uint32_t* flags);
 /* Stage 3: z_out = [z_in +] W_z LN_out(x) * sigmoid(W_g LN_in(z_in)).  z_out may alias z_in.
  * Replaces protenix/model/triangular/triangular.py:559-565. */
 PX_API int32_t px_trimul_out(const px_bf16* x, const void* z_in, void* z_out, int32_t z_dtype, const float* ln_in_w,

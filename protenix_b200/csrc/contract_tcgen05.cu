@@ -1,0 +1,307 @@
+// Triangle-multiplication contraction on the 5th-generation tensor cores:
+//   x[c][i][j] = sum_k a[c][i][k] * b[c][j][k]      (128 channels, bf16 in, fp32 accumulate, bf16 out)
+//
+// Persistent kernel, one CTA per SM, 192 threads:
+//   warp 0      TMA producer: A tile [128 i][64 k] and B tile [256 j][64 k] per k-block, 128-byte swizzle,
+//               4-stage ring guarded by full/empty mbarriers
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=256, K=16) four times per k-block;
+//               tcgen05.commit releases the shared-memory stage and, after the last k-block, publishes
+//               the accumulator
+//   warps 2..5  epilogue: tcgen05.ld of the fp32 accumulator (each warp its own 32 TMEM lanes = 32 rows),
+//               convert to bf16, 16-byte stores
+// The accumulator is double-buffered in TMEM (2 x 256 columns) so the epilogue of tile t overlaps the
+// main loop of tile t+1.  Ragged edges need no predicates on the load side: the TMA zero-fills rows
+// >= N and k >= ld.  Tiles are ordered channel-major so that a channel's operands (2 * N * ld * 2
+// bytes) stay in L2 while its tiles are computed.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out records a flag in g_tc_error, the
+// role stops issuing work, and the kernel still frees its TMEM and returns.
+#include <cuda.h>
+
+#include "px_common.cuh"
+
+namespace px {
+
+constexpr int kTcBM = 128, kTcBN = 256, kTcBK = 64, kTcStages = 4;
+constexpr int kTcABytes = kTcBM * kTcBK * 2, kTcBBytes = kTcBN * kTcBK * 2;
+constexpr int kTcStageBytes = kTcABytes + kTcBBytes;
+constexpr uint32_t kTcCols = 512;  // two 256-column fp32 accumulators
+constexpr long long kWaitCycles = 1ll << 31;  // about one second at 2 GHz
+
+__device__ unsigned int g_tc_error = 0;
+
+struct TcBarriers {
+  uint64_t full[kTcStages], empty[kTcStages], acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+};
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait for the phase with the given parity; false = gave up (error flag set).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int code) {
+  const uint32_t addr = smem_u32(bar);
+  const long long t0 = clock64();
+  for (;;) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.b32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (clock64() - t0 > kWaitCycles) {
+      atomicOr(&g_tc_error, code);
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
+// K-major operand tile, rows of 64 bf16 (128 bytes), 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// kind::f16, A and B bf16 K-major, D fp32, M=128, N=256
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTcBN >> 3) << 17) | ((uint32_t)(kTcBM >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(192, 1)
+trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                          bf16* __restrict__ x, int n, int ld, int tiles_i, int tiles_j, int total_tiles) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // operand ring first (1024-byte aligned for the 128-byte swizzle), barriers after it
+  unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  TcBarriers& bars = *reinterpret_cast<TcBarriers*>(ring + kTcStages * kTcStageBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nk = (ld + kTcBK - 1) / kTcBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kTcStages; ++s) {
+      mbar_init(&bars.full[s], 1);
+      mbar_init(&bars.empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars.acc_full[b], 1);
+      mbar_init(&bars.acc_empty[b], 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&bars.tmem_base)),
+                 "r"(kTcCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem_base = bars.tmem_base;
+
+  auto tile_coords = [&](int tile, int& c, int& i0, int& j0) {
+    const int per_c = tiles_i * tiles_j;
+    c = tile / per_c;
+    const int r = tile - c * per_c;
+    i0 = (r / tiles_j) * kTcBM;
+    j0 = (r % tiles_j) * kTcBN;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        int c, i0, j0;
+        tile_coords(tile, c, i0, j0);
+        for (int kt = 0; kt < nk && ok; ++kt, ++it) {
+          const int s = it % kTcStages;
+          const uint32_t ph = (it / kTcStages) & 1;
+          ok = mbar_wait(&bars.empty[s], ph ^ 1, 1u);
+          if (!ok) break;
+          mbar_expect_tx(&bars.full[s], kTcStageBytes);
+          const uint32_t sa = smem_u32(ring + s * kTcStageBytes);
+          tma_load_3d(sa, &map_a, &bars.full[s], kt * kTcBK, i0, c);
+          tma_load_3d(sa + kTcABytes, &map_b, &bars.full[s], kt * kTcBK, j0, c);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+        const uint32_t ab = tcount & 1, aph = (tcount >> 1) & 1;
+        ok = mbar_wait(&bars.acc_empty[ab], aph ^ 1, 2u);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint32_t d_tmem = tmem_base + ab * kTcBN;
+        for (int kt = 0; kt < nk; ++kt, ++it) {
+          const int s = it % kTcStages;
+          const uint32_t ph = (it / kTcStages) & 1;
+          ok = mbar_wait(&bars.full[s], ph, 4u);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const uint32_t sa = smem_u32(ring + s * kTcStageBytes);
+          const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sa + kTcABytes);
+#pragma unroll
+          for (int k = 0; k < kTcBK / 16; ++k)  // 16 bf16 = 32 bytes = 2 units of the start-address field
+            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, (kt | k) ? 1u : 0u);
+          umma_commit(&bars.empty[s]);
+        }
+        if (!ok) break;
+        umma_commit(&bars.acc_full[ab]);
+      }
+    }
+  } else {
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+      int c, i0, j0;
+      tile_coords(tile, c, i0, j0);
+      const uint32_t ab = tcount & 1, aph = (tcount >> 1) & 1;
+      ok = mbar_wait(&bars.acc_full[ab], aph, 8u);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const int i = i0 + 32 * q + lane;
+      bf16* xrow = x + ((size_t)c * n + (i < n ? i : 0)) * ld;
+#pragma unroll 1
+      for (int cc = 0; cc < kTcBN / 32; ++cc) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + ab * kTcBN + cc * 32, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        if (i < n) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int j = j0 + cc * 32 + v * 8;
+            if (j < ld) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+              o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+              o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+              o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+              *reinterpret_cast<uint4*>(xrow + j) = o;
+            }
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars.acc_empty[ab]);
+    }
+  }
+
+  // teardown: everybody meets, then the allocating warp frees the tensor memory
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (g_tc_error != 0) {  // a wait ran out somewhere: give copies that may still be in flight time to land
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) {
+    }
+    __syncthreads();
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTcCols) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// [128 c][n rows][ld k] bf16 tensor, box = [1][box_rows][64], 128-byte swizzle, zero fill outside.
+static bool make_operand_map(CUtensorMap* map, const void* base, int64_t n, int64_t ld, uint32_t box_rows) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)ld, (cuuint64_t)n, (cuuint64_t)kC};
+  const cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)n * ld * 2};
+  const cuuint32_t box[3] = {(cuuint32_t)kTcBK, box_rows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace px
+
+using namespace px;
+
+extern "C" int32_t px_trimul_contract(const px_bf16* a, const px_bf16* b, px_bf16* x, int64_t n, int64_t ld,
+                                      void* stream) {
+  if (!a || !b || !x || n <= 0 || n > 32768 || ld != px_ld(n)) return PX_ERR_BAD_ARG;
+  if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)x) & 15) return PX_ERR_BAD_ARG;
+  CUtensorMap ma, mb;
+  if (!make_operand_map(&ma, a, n, ld, kTcBM) || !make_operand_map(&mb, b, n, ld, kTcBN)) return PX_ERR_LAUNCH;
+  const int tiles_i = (int)((n + kTcBM - 1) / kTcBM), tiles_j = (int)((n + kTcBN - 1) / kTcBN);
+  const int total = tiles_i * tiles_j * kC;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = total < sms ? total : sms;
+  const size_t smem = (size_t)kTcStages * kTcStageBytes + sizeof(TcBarriers) + 1024;
+  if (cudaFuncSetAttribute(trimul_contract_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess)
+    return PX_ERR_LAUNCH;
+  trimul_contract_tc_kernel<<<grid, 192, smem, (cudaStream_t)stream>>>(ma, mb, (bf16*)x, (int)n, (int)ld, tiles_i,
+                                                                       tiles_j, total);
+  return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
+}
+
+// Synchronises the device and returns (and clears) the flags recorded by bounded waits that ran out.
+extern "C" int32_t px_device_error_flags(uint32_t* flags) {
+  if (!flags) return PX_ERR_BAD_ARG;
+  unsigned int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(v)) != cudaSuccess) return PX_ERR_LAUNCH;
+  if (v && cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(zero)) != cudaSuccess) return PX_ERR_LAUNCH;
+  *flags = v;
+  return PX_OK;
+}

@@ -89,101 +89,7 @@ trimul_in_proj_kernel(const Tz* __restrict__ z, const float* __restrict__ mask, 
   }
 }
 
-// =========================================================================================
-// Stage 2: x[c][i][j] = sum_k a[c][i][k] b[c][j][k], 128 independent NT products.
-// CTA tile 128x128x64, 8 warps as 2(M) x 4(N), warp tile 64x32, 3-stage cp.async pipeline,
-// 128-byte swizzled rows.  Tensor-bound: 256 N^3 FLOP, 3 * 256 N^2 bytes.
-// =========================================================================================
-constexpr int kCtBK = 64;
-constexpr int kCtStages = 3;
-constexpr int kCtStageBytes = 2 * 128 * kCtBK * 2;
-
-__global__ void __launch_bounds__(256, 2)
-trimul_contract_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, bf16* __restrict__ x, int n, int ld) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int wm = warp >> 2, wn = warp & 3;
-  const int j0 = blockIdx.x * 128, i0 = blockIdx.y * 128, c = blockIdx.z;
-  const bf16* A = a + (size_t)c * n * ld;
-  const bf16* B = b + (size_t)c * n * ld;
-  const int nk = (ld + kCtBK - 1) / kCtBK;
-  const uint32_t sbase = smem_u32(smem_raw);
-
-  auto load_stage = [&](int kt, int stage) {
-    const int k0 = kt * kCtBK;
-    const uint32_t sA = sbase + stage * kCtStageBytes, sB = sA + 128 * kCtBK * 2;
-#pragma unroll
-    for (int it = 0; it < 4; ++it) {
-      const int idx = tid + 256 * it, r = idx >> 3, ch = idx & 7;
-      const bool kin = (k0 + ch * 8) < ld;
-      const uint32_t off = r * 128 + ((ch ^ (r & 7)) << 4);
-      const bool pa = kin && (i0 + r) < n, pb = kin && (j0 + r) < n;
-      cp_async16(sA + off, pa ? (A + (size_t)(i0 + r) * ld + k0 + ch * 8) : A, pa);
-      cp_async16(sB + off, pb ? (B + (size_t)(j0 + r) * ld + k0 + ch * 8) : B, pb);
-    }
-  };
-
-  float acc[4][4][4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
-
-#pragma unroll
-  for (int s = 0; s < kCtStages - 1; ++s) {
-    if (s < nk) load_stage(s, s);
-    cp_async_commit();
-  }
-  for (int kt = 0; kt < nk; ++kt) {
-    cp_async_wait<kCtStages - 2>();
-    __syncthreads();
-    {
-      const int nxt = kt + kCtStages - 1;
-      if (nxt < nk) load_stage(nxt, nxt % kCtStages);
-      cp_async_commit();
-    }
-    const uint32_t sA = sbase + (kt % kCtStages) * kCtStageBytes, sB = sA + 128 * kCtBK * 2;
-#pragma unroll
-    for (int ks = 0; ks < kCtBK / 16; ++ks) {
-      uint32_t af[4][4], bfr[2][4];
-#pragma unroll
-      for (int mt = 0; mt < 4; ++mt) {
-        const int r = wm * 64 + mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-        const int ch = ks * 2 + (lane >> 4);
-        ldmatrix_x4(af[mt], sA + r * 128 + ((ch ^ (r & 7)) << 4));
-      }
-#pragma unroll
-      for (int np = 0; np < 2; ++np) {
-        const int r = wn * 32 + np * 16 + (lane & 7) + (lane >> 4) * 8;
-        const int ch = ks * 2 + ((lane >> 3) & 1);
-        ldmatrix_x4(bfr[np], sB + r * 128 + ((ch ^ (r & 7)) << 4));
-      }
-#pragma unroll
-      for (int mt = 0; mt < 4; ++mt)
-#pragma unroll
-        for (int np = 0; np < 2; ++np) {
-          mma_bf16(acc[mt][2 * np], af[mt], bfr[np][0], bfr[np][1]);
-          mma_bf16(acc[mt][2 * np + 1], af[mt], bfr[np][2], bfr[np][3]);
-        }
-    }
-  }
-  cp_async_wait<0>();
-  bf16* X = x + (size_t)c * n * ld;
-  const int g = lane >> 2, tq = lane & 3;
-#pragma unroll
-  for (int mt = 0; mt < 4; ++mt) {
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
-      const int j = j0 + wn * 32 + nt * 8 + 2 * tq;
-      const int i = i0 + wm * 64 + mt * 16 + g;
-      if (j < n) {
-        if (i < n) *reinterpret_cast<uint32_t*>(X + (size_t)i * ld + j) = pack_bf16x2(acc[mt][nt][0], acc[mt][nt][1]);
-        if (i + 8 < n)
-          *reinterpret_cast<uint32_t*>(X + (size_t)(i + 8) * ld + j) = pack_bf16x2(acc[mt][nt][2], acc[mt][nt][3]);
-      }
-    }
-  }
-}
+// Stage 2 (the channel-batched contraction) lives in contract_tcgen05.cu.
 
 // =========================================================================================
 // Stage 3: z_out = [z +] W_z LN_out(x) * sigmoid(W_g LN_in(z)).  One CTA = (i, 128 consecutive j).
@@ -347,20 +253,6 @@ extern "C" int32_t px_trimul_in_proj(const void* z, int32_t z_dtype, const float
   } else {
     return PX_ERR_UNSUPPORTED;
   }
-  return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
-}
-
-extern "C" int32_t px_trimul_contract(const px_bf16* a, const px_bf16* b, px_bf16* x, int64_t n, int64_t ld,
-                                      void* stream) {
-  if (!a || !b || !x || bad_n(n, ld)) return PX_ERR_BAD_ARG;
-  const unsigned tiles = (unsigned)((n + 127) / 128);
-  dim3 grid(tiles, tiles, kC);
-  const size_t smem = (size_t)kCtStages * kCtStageBytes;
-  if (cudaFuncSetAttribute(trimul_contract_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-      cudaSuccess)
-    return PX_ERR_LAUNCH;
-  trimul_contract_kernel<<<grid, 256, smem, (cudaStream_t)stream>>>((const bf16*)a, (const bf16*)b, (bf16*)x, (int)n,
-                                                                    (int)ld);
   return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
 }
 
