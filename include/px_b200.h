@@ -18,6 +18,11 @@
  *   - mask         fp32 [N][N] (1 = keep, 0 = masked) or NULL for all ones.
  *   - ld           px_ld(N): N rounded up to a multiple of 8; row stride (in elements) of the
  *                  intermediate tensors so that every row starts on a 16-byte boundary.
+ *   - n_u, n_t     the stage entry points work on a rectangular slab of pair elements (u, t),
+ *                  u < n_u, t < n_t: the whole pair tensor (n_u = n_t = N) or, when z is sharded
+ *                  by rows over several GPUs, the local rows (n_u = N / ranks, n_t = N).  The slab
+ *                  is stored [n_u][n_t][128]; with `incoming` / `ending` set it is stored
+ *                  [n_t][n_u][128] and read transposed.
  *
  * The reference interfaces each entry point stands in for are cited as file:line of
  * bytedance/Protenix v2.0.0.
@@ -79,12 +84,14 @@ PX_API int32_t px_layer_norm_fwd(const void* x, const void* gamma, const void* b
  * Replaces protenix/model/triangular/triangular.py:535-543. */
 PX_API int32_t px_trimul_in_proj(const void* z, int32_t z_dtype, const float* mask, const float* ln_w, const float* ln_b,
                           const px_bf16* w_ap, const px_bf16* w_ag, const px_bf16* w_bp, const px_bf16* w_bg,
-                          px_bf16* a, px_bf16* b, int64_t n, int64_t ld, int32_t incoming, float eps, void* stream);
+                          px_bf16* a, px_bf16* b, int64_t n_u, int64_t n_t, int64_t ld, int32_t incoming, float eps,
+                          void* stream);
 /* Stage 2: x[c][i][j] = sum_k a[c][i][k] * b[c][j][k] for the 128 channels (bf16 in, fp32
  * accumulate, bf16 out, row stride ld) on the tcgen05 tensor cores: persistent kernel, TMA-fed
  * 128x256x64 tiles, fp32 accumulators in tensor memory, double-buffered epilogue.  a, b, x must be
  * 16-byte aligned.  Replaces _combine_projections, protenix/model/triangular/triangular.py:123-150. */
-PX_API int32_t px_trimul_contract(const px_bf16* a, const px_bf16* b, px_bf16* x, int64_t n, int64_t ld, void* stream);
+PX_API int32_t px_trimul_contract(const px_bf16* a, const px_bf16* b, px_bf16* x, int64_t channels, int64_t n, int64_t ld,
+                           void* stream);
 /* Synchronises the device, then returns and clears the flags set by device-side bounded waits
  * that ran out (0 = none).  A non-zero value means a kernel gave up waiting and its output is
  * not valid.  No counterpart in the reference. */
@@ -93,7 +100,8 @@ PX_API int32_t px_device_error_flags(uint32_t* flags);
  * Replaces protenix/model/triangular/triangular.py:559-565. */
 PX_API int32_t px_trimul_out(const px_bf16* x, const void* z_in, void* z_out, int32_t z_dtype, const float* ln_in_w,
                       const float* ln_in_b, const float* ln_out_w, const float* ln_out_b, const px_bf16* w_z,
-                      const px_bf16* w_g, int64_t n, int64_t ld, int32_t add_residual, float eps, void* stream);
+                      const px_bf16* w_g, int64_t n_i, int64_t n_j, int64_t ld, int32_t add_residual, float eps,
+                      void* stream);
 /* Bytes of workspace px_triangle_multiplication needs for N tokens (a, b and x). */
 PX_API int64_t px_trimul_workspace_bytes(int64_t n);
 /* The three stages in sequence.  Stands in for TriangleMultiplicativeUpdate.forward,
@@ -138,19 +146,19 @@ PX_API int64_t px_static_max_n(void);
  * Replaces protenix/model/triangular/triangular.py:683-692 and layers.py:361-382. */
 PX_API int32_t px_triatt_in_proj(const void* z, int32_t z_dtype, const float* mask, const float* ln_w, const float* ln_b,
                           const px_bf16* w_q, const px_bf16* w_k, const px_bf16* w_v, const px_bf16* w_bias,
-                          px_bf16* q, px_bf16* k, px_bf16* v, float* bias, float* mask_bias, int64_t n, int64_t ldm,
-                          int32_t ending, float eps, float inf, void* stream);
+                          px_bf16* q, px_bf16* k, px_bf16* v, float* bias, float* mask_bias, int64_t n_u, int64_t n_t,
+                          int64_t ldm, int32_t ending, float eps, float inf, void* stream);
 /* Stage 2: o[u][t][h*32+d] = softmax_k(q.k + bias[h][t][k] + mask_bias[u][k]) v, online
  * softmax in base 2, logits never leave the SM.  Replaces the back-ends selected in
  * protenix/model/triangular/layers.py:441-469 (_attention :276-296, the Triton kernel
  * protenix/model/tri_attention/forward.py:22-188, DS4Sci and cuEquivariance calls). */
 PX_API int32_t px_triatt_flash(const px_bf16* q, const px_bf16* k, const px_bf16* v, const float* bias,
-                        const float* mask_bias, px_bf16* o, int64_t n, int64_t ldm, void* stream);
+                        const float* mask_bias, px_bf16* o, int64_t n_u, int64_t n, int64_t ldm, void* stream);
 /* Stage 3: z_out(u,t) = [z_in(u,t) +] W_o (o[u][t] * sigmoid(W_g LN(z_in(u,t)))), where (u,t)
  * addresses z[u][t] (starting) or z[t][u] (ending).  z_out may alias z_in.
  * Replaces Attention._wrap_up, protenix/model/triangular/layers.py:384-398. */
 PX_API int32_t px_triatt_out(const px_bf16* o, const void* z_in, void* z_out, int32_t z_dtype, const float* ln_w,
-                      const float* ln_b, const px_bf16* w_g, const px_bf16* w_o, int64_t n, int32_t ending,
+                      const float* ln_b, const px_bf16* w_g, const px_bf16* w_o, int64_t n_u, int64_t n_t, int32_t ending,
                       int32_t add_residual, float eps, void* stream);
 PX_API int64_t px_triatt_workspace_bytes(int64_t n);
 /* The three stages in sequence.  Stands in for TriangleAttention.forward,

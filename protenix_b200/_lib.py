@@ -23,17 +23,17 @@ SIGNATURES = {
     "px_ld": (I64, [I64]),
     "px_ld_mask": (I64, [I64]),
     "px_layer_norm_fwd": (I32, [P, P, P, P, P, P, I64, I64, F, I32, P]),
-    "px_trimul_in_proj": (I32, [P, I32, P, P, P, P, P, P, P, P, P, I64, I64, I32, F, P]),
-    "px_trimul_contract": (I32, [P, P, P, I64, I64, P]),
+    "px_trimul_in_proj": (I32, [P, I32, P, P, P, P, P, P, P, P, P, I64, I64, I64, I32, F, P]),
+    "px_trimul_contract": (I32, [P, P, P, I64, I64, I64, P]),
     "px_device_error_flags": (I32, [P]),
-    "px_trimul_out": (I32, [P, P, P, I32, P, P, P, P, P, P, I64, I64, I32, F, P]),
+    "px_trimul_out": (I32, [P, P, P, I32, P, P, P, P, P, P, I64, I64, I64, I32, F, P]),
     "px_trimul_workspace_bytes": (I64, [I64]),
     "px_triangle_multiplication": (I32, [P, P, I32, P, P, P, P, P, P, P, P, P, P, P, P, I64, I64, I32, I32, F, P]),
     "px_triangle_multiplication_static": (I32, [P, P, I32, P, P, P, P, P, P, P, P, P, P, P, I64, I32, I32, F, P]),
     "px_static_max_n": (I64, []),
-    "px_triatt_in_proj": (I32, [P, I32, P, P, P, P, P, P, P, P, P, P, P, P, I64, I64, I32, F, F, P]),
-    "px_triatt_flash": (I32, [P, P, P, P, P, P, I64, I64, P]),
-    "px_triatt_out": (I32, [P, P, P, I32, P, P, P, P, I64, I32, I32, F, P]),
+    "px_triatt_in_proj": (I32, [P, I32, P, P, P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I32, F, F, P]),
+    "px_triatt_flash": (I32, [P, P, P, P, P, P, I64, I64, I64, P]),
+    "px_triatt_out": (I32, [P, P, P, I32, P, P, P, P, I64, I64, I32, I32, F, P]),
     "px_triatt_workspace_bytes": (I64, [I64]),
     "px_triangle_attention": (I32, [P, P, I32, P, P, P, P, P, P, P, P, P, P, I64, I64, I32, I32, F, F, P]),
     "px_transition": (I32, [P, P, I32, P, P, P, P, P, I64, I32, F, P]),

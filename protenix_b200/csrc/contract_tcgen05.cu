@@ -259,11 +259,12 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// [128 c][n rows][ld k] bf16 tensor, box = [1][box_rows][64], 128-byte swizzle, zero fill outside.
-static bool make_operand_map(CUtensorMap* map, const void* base, int64_t n, int64_t ld, uint32_t box_rows) {
+// [channels][n rows][ld k] bf16 tensor, box = [1][box_rows][64], 128-byte swizzle, zero fill outside.
+static bool make_operand_map(CUtensorMap* map, const void* base, int64_t channels, int64_t n, int64_t ld,
+                             uint32_t box_rows) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) return false;
-  const cuuint64_t dims[3] = {(cuuint64_t)ld, (cuuint64_t)n, (cuuint64_t)kC};
+  const cuuint64_t dims[3] = {(cuuint64_t)ld, (cuuint64_t)n, (cuuint64_t)channels};
   const cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)n * ld * 2};
   const cuuint32_t box[3] = {(cuuint32_t)kTcBK, box_rows, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
@@ -276,14 +277,16 @@ static bool make_operand_map(CUtensorMap* map, const void* base, int64_t n, int6
 
 using namespace px;
 
-extern "C" int32_t px_trimul_contract(const px_bf16* a, const px_bf16* b, px_bf16* x, int64_t n, int64_t ld,
-                                      void* stream) {
-  if (!a || !b || !x || n <= 0 || n > 32768 || ld != px_ld(n)) return PX_ERR_BAD_ARG;
+extern "C" int32_t px_trimul_contract(const px_bf16* a, const px_bf16* b, px_bf16* x, int64_t channels, int64_t n,
+                                      int64_t ld, void* stream) {
+  if (!a || !b || !x || channels <= 0 || channels > 65535 || n <= 0 || n > 32768 || ld != px_ld(n))
+    return PX_ERR_BAD_ARG;
   if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)x) & 15) return PX_ERR_BAD_ARG;
   CUtensorMap ma, mb;
-  if (!make_operand_map(&ma, a, n, ld, kTcBM) || !make_operand_map(&mb, b, n, ld, kTcBN)) return PX_ERR_LAUNCH;
+  if (!make_operand_map(&ma, a, channels, n, ld, kTcBM) || !make_operand_map(&mb, b, channels, n, ld, kTcBN))
+    return PX_ERR_LAUNCH;
   const int tiles_i = (int)((n + kTcBM - 1) / kTcBM), tiles_j = (int)((n + kTcBN - 1) / kTcBN);
-  const int total = tiles_i * tiles_j * kC;
+  const int total = tiles_i * tiles_j * (int)channels;
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = total < sms ? total : sms;

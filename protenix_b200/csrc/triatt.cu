@@ -24,7 +24,7 @@ triatt_in_proj_kernel(const Tz* __restrict__ z, const float* __restrict__ mask, 
                       const float* __restrict__ ln_b, const bf16* __restrict__ w_q, const bf16* __restrict__ w_k,
                       const bf16* __restrict__ w_v, const bf16* __restrict__ w_bias, bf16* __restrict__ q_out,
                       bf16* __restrict__ k_out, bf16* __restrict__ v_out, float* __restrict__ bias_out,
-                      float* __restrict__ mb_out, int n, int ldm, int swap, float eps, float inf) {
+                      float* __restrict__ mb_out, int n_u, int n, int ldm, int swap, float eps, float inf) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   TriAttInSmem& sm = *reinterpret_cast<TriAttInSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -42,7 +42,8 @@ triatt_in_proj_kernel(const Tz* __restrict__ z, const float* __restrict__ mask, 
   };
   load_chunk(0, 0);
 
-  auto pair_index = [&](int t) -> size_t { return swap ? ((size_t)t * n + u) : ((size_t)u * n + t); };
+  // z (and the mask) is [n_u][n] pair elements, or [n][n_u] when the two indices are exchanged
+  auto pair_index = [&](int t) -> size_t { return swap ? ((size_t)t * n_u + u) : ((size_t)u * n + t); };
   ln_tile_rows<Tz>(sm.A, warp, lane, ln_w, ln_b, eps, [&](int r) -> const Tz* {
     int t = t0 + r;
     return t < n ? z + pair_index(t) * kC : nullptr;
@@ -95,8 +96,8 @@ triatt_in_proj_kernel(const Tz* __restrict__ z, const float* __restrict__ mask, 
         for (int e = 0; e < 2; ++e) {
           const int head = 2 * tq + e;
           // zero in the pad columns [n, ldm)
-          if (tr < ldm) bias_out[((size_t)head * n + u) * ldm + tr] = tr < n ? acc[0][e] * kLog2e : 0.f;
-          if (tr + 8 < ldm) bias_out[((size_t)head * n + u) * ldm + tr + 8] = tr + 8 < n ? acc[0][2 + e] * kLog2e : 0.f;
+          if (tr < ldm) bias_out[((size_t)head * n_u + u) * ldm + tr] = tr < n ? acc[0][e] * kLog2e : 0.f;
+          if (tr + 8 < ldm) bias_out[((size_t)head * n_u + u) * ldm + tr + 8] = tr + 8 < n ? acc[0][2 + e] * kLog2e : 0.f;
         }
       }
     }
@@ -125,8 +126,8 @@ struct FlashSmem {
 template <int R>
 __global__ void __launch_bounds__(128, 2)
 triatt_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
-                    const float* __restrict__ bias, const float* __restrict__ mb, bf16* __restrict__ o, int n,
-                    int ldm) {
+                    const float* __restrict__ bias, const float* __restrict__ mb, bf16* __restrict__ o, int n_u,
+                    int n, int ldm) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   FlashSmem<R>& sm = *reinterpret_cast<FlashSmem<R>*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -138,7 +139,7 @@ triatt_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
   auto load_kv = [&](int kt, int stage) {
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      const bool urow = (u0 + r) < n;
+      const bool urow = (u0 + r) < n_u;
       const size_t base = urow ? rows_base(r) : 0;
 #pragma unroll
       for (int it = 0; it < 2; ++it) {
@@ -151,13 +152,13 @@ triatt_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
     }
     if (tid < R * 16) {
       const int r = tid >> 4, ch = tid & 15;
-      const bool urow = (u0 + r) < n;
+      const bool urow = (u0 + r) < n_u;
       cp_async16(smem_u32(&sm.MB[stage][r][ch * 4]), mb + (urow ? (size_t)(u0 + r) * ldm + kt * 64 + ch * 4 : 0), urow);
     }
   };
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    const bool urow = (u0 + r) < n;
+    const bool urow = (u0 + r) < n_u;
     const size_t base = urow ? rows_base(r) : 0;
 #pragma unroll
     for (int it = 0; it < 2; ++it) {
@@ -294,7 +295,7 @@ triatt_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
   cp_async_wait<0>();
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    if (u0 + r >= n) continue;
+    if (u0 + r >= n_u) continue;
     // row sums sit in column 0 of the extra tile: lane 4*g of each quad holds them
     const float l0 = __shfl_sync(0xffffffffu, oacc[r][4][0], lane & ~3);
     const float l1 = __shfl_sync(0xffffffffu, oacc[r][4][2], lane & ~3);
@@ -326,7 +327,7 @@ template <typename Tz>
 __global__ void __launch_bounds__(256, 2)
 triatt_out_kernel(const bf16* __restrict__ o, const Tz* __restrict__ z_in, Tz* __restrict__ z_out,
                   const float* __restrict__ ln_w, const float* __restrict__ ln_b, const bf16* __restrict__ w_g,
-                  const bf16* __restrict__ w_o, int n, int swap, int add_residual, float eps) {
+                  const bf16* __restrict__ w_o, int n_u, int n, int swap, int add_residual, float eps) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   TriAttOutSmem& sm = *reinterpret_cast<TriAttOutSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -345,7 +346,7 @@ triatt_out_kernel(const bf16* __restrict__ o, const Tz* __restrict__ z_in, Tz* _
   };
   load_chunk(0, 0);
 
-  auto pair_index = [&](int t) -> size_t { return swap ? ((size_t)t * n + u) : ((size_t)u * n + t); };
+  auto pair_index = [&](int t) -> size_t { return swap ? ((size_t)t * n_u + u) : ((size_t)u * n + t); };
   ln_tile_rows<Tz>(sm.A, warp, lane, ln_w, ln_b, eps, [&](int r) -> const Tz* {
     int t = t0 + r;
     return t < n ? z_in + pair_index(t) * kC : nullptr;
@@ -414,17 +415,19 @@ static size_t align256(size_t b) { return (b + 255) / 256 * 256; }
 
 using namespace px;
 
-static bool att_bad_n(int64_t n, int64_t ldm) { return n <= 0 || n > 32768 || ldm != px_ld_mask(n); }
+static bool att_bad_dims(int64_t n_u, int64_t n, int64_t ldm) {
+  return n_u <= 0 || n <= 0 || n_u > 32768 || n > 32768 || ldm != px_ld_mask(n);
+}
 
 extern "C" int32_t px_triatt_in_proj(const void* z, int32_t z_dtype, const float* mask, const float* ln_w,
                                      const float* ln_b, const px_bf16* w_q, const px_bf16* w_k, const px_bf16* w_v,
                                      const px_bf16* w_bias, px_bf16* q, px_bf16* k, px_bf16* v, float* bias,
-                                     float* mask_bias, int64_t n, int64_t ldm, int32_t ending, float eps, float inf,
-                                     void* stream) {
+                                     float* mask_bias, int64_t n_u, int64_t n_t, int64_t ldm, int32_t ending,
+                                     float eps, float inf, void* stream) {
   if (!z || !ln_w || !ln_b || !w_q || !w_k || !w_v || !w_bias || !q || !k || !v || !bias || !mask_bias ||
-      att_bad_n(n, ldm))
+      att_bad_dims(n_u, n_t, ldm))
     return PX_ERR_BAD_ARG;
-  dim3 grid((unsigned)((n + 127) / 128), (unsigned)n);   // 128-wide tiles cover the pad columns up to ldm too
+  dim3 grid((unsigned)((n_t + 127) / 128), (unsigned)n_u);  // 128-wide tiles cover the pad columns up to ldm too
   const size_t smem = sizeof(TriAttInSmem);
   cudaStream_t st = (cudaStream_t)stream;
   if (z_dtype == PX_F32) {
@@ -433,14 +436,15 @@ extern "C" int32_t px_triatt_in_proj(const void* z, int32_t z_dtype, const float
       return PX_ERR_LAUNCH;
     triatt_in_proj_kernel<float><<<grid, 256, smem, st>>>(
         (const float*)z, mask, ln_w, ln_b, (const bf16*)w_q, (const bf16*)w_k, (const bf16*)w_v,
-        (const bf16*)w_bias, (bf16*)q, (bf16*)k, (bf16*)v, bias, mask_bias, (int)n, (int)ldm, ending, eps, inf);
+        (const bf16*)w_bias, (bf16*)q, (bf16*)k, (bf16*)v, bias, mask_bias, (int)n_u, (int)n_t, (int)ldm, ending, eps,
+        inf);
   } else if (z_dtype == PX_BF16) {
     if (cudaFuncSetAttribute(triatt_in_proj_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return PX_ERR_LAUNCH;
     triatt_in_proj_kernel<bf16><<<grid, 256, smem, st>>>(
         (const bf16*)z, mask, ln_w, ln_b, (const bf16*)w_q, (const bf16*)w_k, (const bf16*)w_v, (const bf16*)w_bias,
-        (bf16*)q, (bf16*)k, (bf16*)v, bias, mask_bias, (int)n, (int)ldm, ending, eps, inf);
+        (bf16*)q, (bf16*)k, (bf16*)v, bias, mask_bias, (int)n_u, (int)n_t, (int)ldm, ending, eps, inf);
   } else {
     return PX_ERR_UNSUPPORTED;
   }
@@ -450,23 +454,25 @@ extern "C" int32_t px_triatt_in_proj(const void* z, int32_t z_dtype, const float
 constexpr int kFlashR = 2;
 
 extern "C" int32_t px_triatt_flash(const px_bf16* q, const px_bf16* k, const px_bf16* v, const float* bias,
-                                   const float* mask_bias, px_bf16* o, int64_t n, int64_t ldm, void* stream) {
-  if (!q || !k || !v || !bias || !mask_bias || !o || att_bad_n(n, ldm)) return PX_ERR_BAD_ARG;
-  dim3 grid((unsigned)((n + 63) / 64), kH, (unsigned)((n + kFlashR - 1) / kFlashR));
+                                   const float* mask_bias, px_bf16* o, int64_t n_u, int64_t n, int64_t ldm,
+                                   void* stream) {
+  if (!q || !k || !v || !bias || !mask_bias || !o || att_bad_dims(n_u, n, ldm)) return PX_ERR_BAD_ARG;
+  dim3 grid((unsigned)((n + 63) / 64), kH, (unsigned)((n_u + kFlashR - 1) / kFlashR));
   const size_t smem = sizeof(FlashSmem<kFlashR>);
   if (cudaFuncSetAttribute(triatt_flash_kernel<kFlashR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
     return PX_ERR_LAUNCH;
   triatt_flash_kernel<kFlashR><<<grid, 128, smem, (cudaStream_t)stream>>>(
-      (const bf16*)q, (const bf16*)k, (const bf16*)v, bias, mask_bias, (bf16*)o, (int)n, (int)ldm);
+      (const bf16*)q, (const bf16*)k, (const bf16*)v, bias, mask_bias, (bf16*)o, (int)n_u, (int)n, (int)ldm);
   return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
 }
 
 extern "C" int32_t px_triatt_out(const px_bf16* o, const void* z_in, void* z_out, int32_t z_dtype, const float* ln_w,
-                                 const float* ln_b, const px_bf16* w_g, const px_bf16* w_o, int64_t n, int32_t ending,
-                                 int32_t add_residual, float eps, void* stream) {
-  if (!o || !z_in || !z_out || !ln_w || !ln_b || !w_g || !w_o || n <= 0 || n > 32768) return PX_ERR_BAD_ARG;
-  dim3 grid((unsigned)((n + 127) / 128), (unsigned)n);
+                                 const float* ln_b, const px_bf16* w_g, const px_bf16* w_o, int64_t n_u, int64_t n_t,
+                                 int32_t ending, int32_t add_residual, float eps, void* stream) {
+  if (!o || !z_in || !z_out || !ln_w || !ln_b || !w_g || !w_o || n_u <= 0 || n_t <= 0 || n_u > 32768 || n_t > 32768)
+    return PX_ERR_BAD_ARG;
+  dim3 grid((unsigned)((n_t + 127) / 128), (unsigned)n_u);
   const size_t smem = sizeof(TriAttOutSmem);
   cudaStream_t st = (cudaStream_t)stream;
   if (z_dtype == PX_F32) {
@@ -474,15 +480,15 @@ extern "C" int32_t px_triatt_out(const px_bf16* o, const void* z_in, void* z_out
         cudaSuccess)
       return PX_ERR_LAUNCH;
     triatt_out_kernel<float><<<grid, 256, smem, st>>>((const bf16*)o, (const float*)z_in, (float*)z_out, ln_w, ln_b,
-                                                      (const bf16*)w_g, (const bf16*)w_o, (int)n, ending,
+                                                      (const bf16*)w_g, (const bf16*)w_o, (int)n_u, (int)n_t, ending,
                                                       add_residual, eps);
   } else if (z_dtype == PX_BF16) {
     if (cudaFuncSetAttribute(triatt_out_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return PX_ERR_LAUNCH;
     triatt_out_kernel<bf16><<<grid, 256, smem, st>>>((const bf16*)o, (const bf16*)z_in, (bf16*)z_out, ln_w, ln_b,
-                                                     (const bf16*)w_g, (const bf16*)w_o, (int)n, ending, add_residual,
-                                                     eps);
+                                                     (const bf16*)w_g, (const bf16*)w_o, (int)n_u, (int)n_t, ending,
+                                                     add_residual, eps);
   } else {
     return PX_ERR_UNSUPPORTED;
   }
@@ -520,10 +526,10 @@ extern "C" int32_t px_triangle_attention(const void* z_in, void* z_out, int32_t 
   float* bias = (float*)p;
   p += align256((size_t)kH * n * ld * 4);
   float* mbias = (float*)p;
-  int32_t s = px_triatt_in_proj(z_in, z_dtype, mask, ln_w, ln_b, w_q, w_k, w_v, w_bias, q, k, v, bias, mbias, n, ld,
-                                ending, eps, inf, stream);
+  int32_t s = px_triatt_in_proj(z_in, z_dtype, mask, ln_w, ln_b, w_q, w_k, w_v, w_bias, q, k, v, bias, mbias, n, n,
+                                ld, ending, eps, inf, stream);
   if (s != PX_OK) return s;
-  s = px_triatt_flash(q, k, v, bias, mbias, o, n, ld, stream);
+  s = px_triatt_flash(q, k, v, bias, mbias, o, n, n, ld, stream);
   if (s != PX_OK) return s;
-  return px_triatt_out(o, z_in, z_out, z_dtype, ln_w, ln_b, w_g, w_o, n, ending, add_residual, eps, stream);
+  return px_triatt_out(o, z_in, z_out, z_dtype, ln_w, ln_b, w_g, w_o, n, n, ending, add_residual, eps, stream);
 }

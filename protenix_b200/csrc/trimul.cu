@@ -20,7 +20,7 @@ __global__ void __launch_bounds__(256, 2)
 trimul_in_proj_kernel(const Tz* __restrict__ z, const float* __restrict__ mask, const float* __restrict__ ln_w,
                       const float* __restrict__ ln_b, const bf16* __restrict__ w_ap, const bf16* __restrict__ w_ag,
                       const bf16* __restrict__ w_bp, const bf16* __restrict__ w_bg, bf16* __restrict__ a_out,
-                      bf16* __restrict__ b_out, int n, int ld, int swap, float eps) {
+                      bf16* __restrict__ b_out, int n_u, int n_t, int ld, int swap, float eps) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   TriMulInSmem& sm = *reinterpret_cast<TriMulInSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -35,10 +35,11 @@ trimul_in_proj_kernel(const Tz* __restrict__ z, const float* __restrict__ mask, 
   };
   load_chunk(0, 0);
 
-  auto pair_index = [&](int t) -> size_t { return swap ? ((size_t)t * n + u) : ((size_t)u * n + t); };
+  // z (and the mask) is [n_u][n_t] pair elements, or [n_t][n_u] when the two indices are exchanged
+  auto pair_index = [&](int t) -> size_t { return swap ? ((size_t)t * n_u + u) : ((size_t)u * n_t + t); };
   ln_tile_rows<Tz>(sm.A, warp, lane, ln_w, ln_b, eps, [&](int r) -> const Tz* {
     int t = t0 + r;
-    return t < n ? z + pair_index(t) * kC : nullptr;
+    return t < n_t ? z + pair_index(t) * kC : nullptr;
   });
   __syncwarp();
   uint32_t afr[8][4];
@@ -47,8 +48,8 @@ trimul_in_proj_kernel(const Tz* __restrict__ z, const float* __restrict__ mask, 
   const int g = lane >> 2, tq = lane & 3;
   const int r0 = 16 * warp + g;
   float m0 = 0.f, m1 = 0.f;
-  if (t0 + r0 < n) m0 = mask ? mask[pair_index(t0 + r0)] : 1.f;
-  if (t0 + r0 + 8 < n) m1 = mask ? mask[pair_index(t0 + r0 + 8)] : 1.f;
+  if (t0 + r0 < n_t) m0 = mask ? mask[pair_index(t0 + r0)] : 1.f;
+  if (t0 + r0 + 8 < n_t) m1 = mask ? mask[pair_index(t0 + r0 + 8)] : 1.f;
 
   for (int q = 0; q < 8; ++q) {
     if (q + 1 < 8) {
@@ -76,7 +77,7 @@ trimul_in_proj_kernel(const Tz* __restrict__ z, const float* __restrict__ mask, 
     {
       bf16* dst = (q < 4) ? a_out : b_out;
       const int ch = tid >> 3, seg = tid & 7;
-      const size_t row = ((size_t)(32 * (q & 3) + ch) * n + u) * ld;
+      const size_t row = ((size_t)(32 * (q & 3) + ch) * n_u + u) * ld;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int t = t0 + seg * 16 + h * 8;
@@ -109,7 +110,7 @@ __global__ void __launch_bounds__(256, 2)
 trimul_out_kernel(const bf16* __restrict__ x, const Tz* __restrict__ z_in, Tz* __restrict__ z_out,
                   const float* __restrict__ ln_in_w, const float* __restrict__ ln_in_b,
                   const float* __restrict__ ln_out_w, const float* __restrict__ ln_out_b,
-                  const bf16* __restrict__ w_z, const bf16* __restrict__ w_g, int n, int ld, int add_residual,
+                  const bf16* __restrict__ w_z, const bf16* __restrict__ w_g, int n_i, int n, int ld, int add_residual,
                   float eps) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   TriMulOutSmem& sm = *reinterpret_cast<TriMulOutSmem*>(smem_raw);
@@ -121,7 +122,7 @@ trimul_out_kernel(const bf16* __restrict__ x, const Tz* __restrict__ z_in, Tz* _
     const int c = idx >> 4, seg = idx & 15;
     const int j = j0 + seg * 8;
     const bool p = j < ld;
-    cp_async16(smem_u32(sm.XS + c * kLdA + seg * 8), p ? (x + ((size_t)c * n + i) * ld + j) : x, p);
+    cp_async16(smem_u32(sm.XS + c * kLdA + seg * 8), p ? (x + ((size_t)c * n_i + i) * ld + j) : x, p);
   }
   cp_async_commit();
   auto load_chunk = [&](int q, int buf) {
@@ -227,14 +228,17 @@ using namespace px;
 
 extern "C" int64_t px_ld(int64_t n) { return (n + 7) / 8 * 8; }
 
-static bool bad_n(int64_t n, int64_t ld) { return n <= 0 || n > 32768 || ld != px_ld(n); }
+static bool bad_dims(int64_t n_u, int64_t n_t, int64_t ld) {
+  return n_u <= 0 || n_t <= 0 || n_u > 32768 || n_t > 32768 || ld != px_ld(n_t);
+}
 
 extern "C" int32_t px_trimul_in_proj(const void* z, int32_t z_dtype, const float* mask, const float* ln_w,
                                      const float* ln_b, const px_bf16* w_ap, const px_bf16* w_ag,
-                                     const px_bf16* w_bp, const px_bf16* w_bg, px_bf16* a, px_bf16* b, int64_t n,
-                                     int64_t ld, int32_t incoming, float eps, void* stream) {
-  if (!z || !ln_w || !ln_b || !w_ap || !w_ag || !w_bp || !w_bg || !a || !b || bad_n(n, ld)) return PX_ERR_BAD_ARG;
-  dim3 grid((unsigned)((ld + 127) / 128), (unsigned)n);
+                                     const px_bf16* w_bp, const px_bf16* w_bg, px_bf16* a, px_bf16* b, int64_t n_u,
+                                     int64_t n_t, int64_t ld, int32_t incoming, float eps, void* stream) {
+  if (!z || !ln_w || !ln_b || !w_ap || !w_ag || !w_bp || !w_bg || !a || !b || bad_dims(n_u, n_t, ld))
+    return PX_ERR_BAD_ARG;
+  dim3 grid((unsigned)((ld + 127) / 128), (unsigned)n_u);
   const size_t smem = sizeof(TriMulInSmem);
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
@@ -243,13 +247,15 @@ extern "C" int32_t px_trimul_in_proj(const void* z, int32_t z_dtype, const float
     if (e != cudaSuccess) return PX_ERR_LAUNCH;
     trimul_in_proj_kernel<float><<<grid, 256, smem, st>>>((const float*)z, mask, ln_w, ln_b, (const bf16*)w_ap,
                                                           (const bf16*)w_ag, (const bf16*)w_bp, (const bf16*)w_bg,
-                                                          (bf16*)a, (bf16*)b, (int)n, (int)ld, incoming, eps);
+                                                          (bf16*)a, (bf16*)b, (int)n_u, (int)n_t, (int)ld, incoming,
+                                                          eps);
   } else if (z_dtype == PX_BF16) {
     e = cudaFuncSetAttribute(trimul_in_proj_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return PX_ERR_LAUNCH;
     trimul_in_proj_kernel<bf16><<<grid, 256, smem, st>>>((const bf16*)z, mask, ln_w, ln_b, (const bf16*)w_ap,
                                                          (const bf16*)w_ag, (const bf16*)w_bp, (const bf16*)w_bg,
-                                                         (bf16*)a, (bf16*)b, (int)n, (int)ld, incoming, eps);
+                                                         (bf16*)a, (bf16*)b, (int)n_u, (int)n_t, (int)ld, incoming,
+                                                         eps);
   } else {
     return PX_ERR_UNSUPPORTED;
   }
@@ -258,11 +264,12 @@ extern "C" int32_t px_trimul_in_proj(const void* z, int32_t z_dtype, const float
 
 extern "C" int32_t px_trimul_out(const px_bf16* x, const void* z_in, void* z_out, int32_t z_dtype,
                                  const float* ln_in_w, const float* ln_in_b, const float* ln_out_w,
-                                 const float* ln_out_b, const px_bf16* w_z, const px_bf16* w_g, int64_t n, int64_t ld,
-                                 int32_t add_residual, float eps, void* stream) {
-  if (!x || !z_in || !z_out || !ln_in_w || !ln_in_b || !ln_out_w || !ln_out_b || !w_z || !w_g || bad_n(n, ld))
+                                 const float* ln_out_b, const px_bf16* w_z, const px_bf16* w_g, int64_t n_i,
+                                 int64_t n_j, int64_t ld, int32_t add_residual, float eps, void* stream) {
+  if (!x || !z_in || !z_out || !ln_in_w || !ln_in_b || !ln_out_w || !ln_out_b || !w_z || !w_g ||
+      bad_dims(n_i, n_j, ld))
     return PX_ERR_BAD_ARG;
-  dim3 grid((unsigned)((n + 127) / 128), (unsigned)n);
+  dim3 grid((unsigned)((n_j + 127) / 128), (unsigned)n_i);
   const size_t smem = sizeof(TriMulOutSmem);
   cudaStream_t st = (cudaStream_t)stream;
   if (z_dtype == PX_F32) {
@@ -271,20 +278,20 @@ extern "C" int32_t px_trimul_out(const px_bf16* x, const void* z_in, void* z_out
       return PX_ERR_LAUNCH;
     trimul_out_kernel<float><<<grid, 256, smem, st>>>((const bf16*)x, (const float*)z_in, (float*)z_out, ln_in_w,
                                                       ln_in_b, ln_out_w, ln_out_b, (const bf16*)w_z,
-                                                      (const bf16*)w_g, (int)n, (int)ld, add_residual, eps);
+                                                      (const bf16*)w_g, (int)n_i, (int)n_j, (int)ld, add_residual,
+                                                      eps);
   } else if (z_dtype == PX_BF16) {
     if (cudaFuncSetAttribute(trimul_out_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return PX_ERR_LAUNCH;
     trimul_out_kernel<bf16><<<grid, 256, smem, st>>>((const bf16*)x, (const bf16*)z_in, (bf16*)z_out, ln_in_w,
                                                      ln_in_b, ln_out_w, ln_out_b, (const bf16*)w_z, (const bf16*)w_g,
-                                                     (int)n, (int)ld, add_residual, eps);
+                                                     (int)n_i, (int)n_j, (int)ld, add_residual, eps);
   } else {
     return PX_ERR_UNSUPPORTED;
   }
   return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
 }
-
 extern "C" int64_t px_trimul_workspace_bytes(int64_t n) {
   if (n <= 0) return 0;
   return (int64_t)(3 * trimul_elems(n) * sizeof(bf16));
@@ -303,13 +310,13 @@ extern "C" int32_t px_triangle_multiplication(const void* z_in, void* z_out, int
   px_bf16* a = (px_bf16*)workspace;
   px_bf16* b = a + trimul_elems(n);
   px_bf16* x = b + trimul_elems(n);
-  int32_t s = px_trimul_in_proj(z_in, z_dtype, mask, ln_in_w, ln_in_b, w_ap, w_ag, w_bp, w_bg, a, b, n, ld, incoming,
-                                eps, stream);
+  int32_t s = px_trimul_in_proj(z_in, z_dtype, mask, ln_in_w, ln_in_b, w_ap, w_ag, w_bp, w_bg, a, b, n, n, ld,
+                                incoming, eps, stream);
   if (s != PX_OK) return s;
-  s = px_trimul_contract(a, b, x, n, ld, stream);
+  s = px_trimul_contract(a, b, x, kC, n, ld, stream);
   if (s != PX_OK) return s;
-  return px_trimul_out(x, z_in, z_out, z_dtype, ln_in_w, ln_in_b, ln_out_w, ln_out_b, w_z, w_g, n, ld, add_residual,
-                       eps, stream);
+  return px_trimul_out(x, z_in, z_out, z_dtype, ln_in_w, ln_in_b, ln_out_w, ln_out_b, w_z, w_g, n, n, ld,
+                       add_residual, eps, stream);
 }
 
 // =========================================================================================

@@ -182,10 +182,10 @@ def triangle_multiplication(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optio
     a, b, x = ws.data_ptr(), ws.data_ptr() + per, ws.data_ptr() + 2 * per
     dt, st, eps = _pair_dtype(z_in), _stream(z_in), float(eps)
     _launch("px_trimul_in_proj", lib.px_trimul_in_proj, _ptr(z_in), dt, _ptr(mask), _ptr(ln_in_w), _ptr(ln_in_b),
-            _ptr(w_ap), _ptr(w_ag), _ptr(w_bp), _ptr(w_bg), a, b, n, ldn, int(incoming), eps, st)
-    _launch("px_trimul_contract", lib.px_trimul_contract, a, b, x, n, ldn, st)
+            _ptr(w_ap), _ptr(w_ag), _ptr(w_bp), _ptr(w_bg), a, b, n, n, ldn, int(incoming), eps, st)
+    _launch("px_trimul_contract", lib.px_trimul_contract, a, b, x, C_Z, n, ldn, st)
     _launch("px_trimul_out", lib.px_trimul_out, x, _ptr(z_in), _ptr(z_out), dt, _ptr(ln_in_w), _ptr(ln_in_b),
-            _ptr(ln_out_w), _ptr(ln_out_b), _ptr(w_z), _ptr(w_g), n, ldn, int(add_residual), eps, st)
+            _ptr(ln_out_w), _ptr(ln_out_b), _ptr(w_z), _ptr(w_g), n, n, ldn, int(add_residual), eps, st)
     return z_out
 
 
@@ -212,11 +212,11 @@ def triangle_attention(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optional[t
     mbias = bias + al(N_HEAD_PAIR * n * ldn * 4)
     dt, st, eps = _pair_dtype(z_in), _stream(z_in), float(eps)
     _launch("px_triatt_in_proj", lib.px_triatt_in_proj, _ptr(z_in), dt, _ptr(mask), _ptr(ln_w), _ptr(ln_b),
-            _ptr(w_q), _ptr(w_k), _ptr(w_v), _ptr(w_bias), q, k, v, bias, mbias, n, ldn, int(ending), eps,
+            _ptr(w_q), _ptr(w_k), _ptr(w_v), _ptr(w_bias), q, k, v, bias, mbias, n, n, ldn, int(ending), eps,
             float(inf), st)
-    _launch("px_triatt_flash", lib.px_triatt_flash, q, k, v, bias, mbias, o, n, ldn, st)
+    _launch("px_triatt_flash", lib.px_triatt_flash, q, k, v, bias, mbias, o, n, n, ldn, st)
     _launch("px_triatt_out", lib.px_triatt_out, o, _ptr(z_in), _ptr(z_out), dt, _ptr(ln_w), _ptr(ln_b), _ptr(w_g),
-            _ptr(w_o), n, int(ending), int(add_residual), eps, st)
+            _ptr(w_o), n, n, int(ending), int(add_residual), eps, st)
     return z_out
 
 
@@ -250,3 +250,106 @@ def pair_bias_proj(z: torch.Tensor, ln_w, ln_b: Optional[torch.Tensor], w: torch
     _launch("px_pair_bias_proj", _lib.load().px_pair_bias_proj, _ptr(z), _pair_dtype(z), _ptr(ln_w), _ptr(ln_b),
             _ptr(w), _ptr(out), n * n, heads, float(eps), _stream(z))
     return out
+
+
+# ---------------------------------------------------------------------------------------------
+# Stage-level calls on rectangular slabs (row-sharded pair tensor).  Outputs are allocated here.
+def _slab(z: torch.Tensor, name: str = "z") -> Tuple[int, int]:
+    _need_cuda(z, name)
+    if z.dim() != 3 or z.shape[2] != C_Z:
+        raise RuntimeError(f"{name} must have shape [rows, cols, {C_Z}], got {tuple(z.shape)}")
+    return z.shape[0], z.shape[1]
+
+
+def trimul_in_proj(z: torch.Tensor, mask: Optional[torch.Tensor], ln_w, ln_b, w_ap, w_ag, w_bp, w_bg,
+                   incoming: bool, eps: float = 1e-5) -> Tuple[torch.Tensor, torch.Tensor]:
+    """a, b as [128][n_u][ld(n_t)] bf16.  z is [n_u][n_t][128]; with ``incoming`` it is [n_t][n_u][128]."""
+    r, c = _slab(z)
+    n_u, n_t = (c, r) if incoming else (r, c)
+    lib = _lib.load()
+    ldt = lib.px_ld(n_t)
+    a = torch.empty(C_Z, n_u, ldt, dtype=torch.bfloat16, device=z.device)
+    b = torch.empty_like(a)
+    _launch("px_trimul_in_proj", lib.px_trimul_in_proj, _ptr(z), _pair_dtype(z), _ptr(mask), _ptr(ln_w), _ptr(ln_b),
+            _ptr(w_ap), _ptr(w_ag), _ptr(w_bp), _ptr(w_bg), _ptr(a), _ptr(b), n_u, n_t, ldt, int(incoming), float(eps),
+            _stream(z))
+    return a, b
+
+
+def trimul_contract(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """x[c][i][j] = sum_k a[c][i][k] b[c][j][k] for [C][n][ld] bf16 operands (pad columns zero)."""
+    _need_cuda(a, "a")
+    _need_cuda(b, "b")
+    ch, n, ldn = a.shape
+    if a.dtype != torch.bfloat16 or b.shape != a.shape or b.dtype != a.dtype or ldn != ld(n):
+        raise RuntimeError("contraction operands must be bfloat16 [C][n][ld(n)] of equal shape")
+    x = torch.empty_like(a)
+    _launch("px_trimul_contract", _lib.load().px_trimul_contract, _ptr(a), _ptr(b), _ptr(x), ch, n, ldn, _stream(a))
+    return x
+
+
+def trimul_out(x: torch.Tensor, z: torch.Tensor, ln_in_w, ln_in_b, ln_out_w, ln_out_b, w_z, w_g,
+               eps: float = 1e-5) -> torch.Tensor:
+    """z[n_i][n_j] += W_z LN(x) * sigmoid(W_g LN(z)) in place; x is [128][n_i][ld(n_j)]."""
+    n_i, n_j = _slab(z)
+    _launch("px_trimul_out", _lib.load().px_trimul_out, _ptr(x), _ptr(z), _ptr(z), _pair_dtype(z), _ptr(ln_in_w),
+            _ptr(ln_in_b), _ptr(ln_out_w), _ptr(ln_out_b), _ptr(w_z), _ptr(w_g), n_i, n_j, x.shape[2], 1, float(eps),
+            _stream(z))
+    return z
+
+
+def triatt_in_proj(z: torch.Tensor, mask: Optional[torch.Tensor], ln_w, ln_b, w_bias, w_q, w_k, w_v,
+                   eps: float = 1e-5, inf: float = 1e9):
+    """q, k, v [n_u][4][n_t][32] bf16, bias [4][n_u][ldm] fp32, mask_bias [n_u][ldm] fp32 for a row slab."""
+    n_u, n_t = _slab(z)
+    lib = _lib.load()
+    ldm = lib.px_ld_mask(n_t)
+    q = torch.empty(n_u, N_HEAD_PAIR, n_t, D_HEAD_PAIR, dtype=torch.bfloat16, device=z.device)
+    k, v = torch.empty_like(q), torch.empty_like(q)
+    bias = torch.empty(N_HEAD_PAIR, n_u, ldm, dtype=torch.float32, device=z.device)
+    mb = torch.empty(n_u, ldm, dtype=torch.float32, device=z.device)
+    _launch("px_triatt_in_proj", lib.px_triatt_in_proj, _ptr(z), _pair_dtype(z), _ptr(mask), _ptr(ln_w), _ptr(ln_b),
+            _ptr(w_q), _ptr(w_k), _ptr(w_v), _ptr(w_bias), _ptr(q), _ptr(k), _ptr(v), _ptr(bias), _ptr(mb), n_u, n_t,
+            ldm, 0, float(eps), float(inf), _stream(z))
+    return q, k, v, bias, mb
+
+
+def triatt_flash(q, k, v, bias_full: torch.Tensor, mb) -> torch.Tensor:
+    """o [n_u][n][128] bf16 from q,k,v [n_u][4][n][32], the full pair bias [4][n][ldm] and mask_bias [n_u][ldm]."""
+    n_u, _, n, _ = q.shape
+    for t, nm in ((q, "q"), (k, "k"), (v, "v"), (bias_full, "bias"), (mb, "mask_bias")):
+        _need_cuda(t, nm)
+    ldm = bias_full.shape[2]
+    if tuple(bias_full.shape) != (N_HEAD_PAIR, n, ldm) or tuple(mb.shape) != (n_u, ldm):
+        raise RuntimeError("pair bias must be [4][n][ldm] and mask_bias [n_u][ldm]")
+    o = torch.empty(n_u, n, C_Z, dtype=torch.bfloat16, device=q.device)
+    _launch("px_triatt_flash", _lib.load().px_triatt_flash, _ptr(q), _ptr(k), _ptr(v), _ptr(bias_full), _ptr(mb),
+            _ptr(o), n_u, n, ldm, _stream(q))
+    return o
+
+
+def triatt_out(o: torch.Tensor, z: torch.Tensor, ln_w, ln_b, w_g, w_o, eps: float = 1e-5) -> torch.Tensor:
+    """z[n_u][n_t] += W_o(o * sigmoid(W_g LN(z))) in place."""
+    n_u, n_t = _slab(z)
+    _launch("px_triatt_out", _lib.load().px_triatt_out, _ptr(o), _ptr(z), _ptr(z), _pair_dtype(z), _ptr(ln_w),
+            _ptr(ln_b), _ptr(w_g), _ptr(w_o), n_u, n_t, 0, 1, float(eps), _stream(z))
+    return z
+
+
+def pair_bias_rows(z: torch.Tensor, ln_w, ln_b: Optional[torch.Tensor], w: torch.Tensor, eps: float = 1e-5
+                   ) -> torch.Tensor:
+    """bias[h, u, t] for a row slab z [n_u][n_t][128]."""
+    n_u, n_t = _slab(z)
+    heads = w.shape[0]
+    out = torch.empty(heads, n_u, n_t, dtype=torch.float32, device=z.device)
+    _launch("px_pair_bias_proj", _lib.load().px_pair_bias_proj, _ptr(z), _pair_dtype(z), _ptr(ln_w), _ptr(ln_b),
+            _ptr(w), _ptr(out), n_u * n_t, heads, float(eps), _stream(z))
+    return out
+
+
+def transition_rows(x: torch.Tensor, ln_w, ln_b, w_a, w_b, w_o, eps: float = 1e-5) -> torch.Tensor:
+    """x += Transition(x) in place for any [..., 128] slab."""
+    _need_cuda(x, "x")
+    _launch("px_transition", _lib.load().px_transition, _ptr(x), _ptr(x), _pair_dtype(x), _ptr(ln_w), _ptr(ln_b),
+            _ptr(w_a), _ptr(w_b), _ptr(w_o), x.numel() // C_Z, 1, float(eps), _stream(x))
+    return x

@@ -1,0 +1,224 @@
+"""Row-sharded Pairformer over the GPUs of one NVSwitch box (one process per GPU).
+
+Rank r of P holds rows [r*N/P, (r+1)*N/P) of the pair tensor: ``z_loc`` is [N/P, N, 128].  The
+single representation s and the pair mask are replicated.  Per block:
+
+* LayerNorms, projections, gates, the transition and the residual adds are row-local.
+* Triangle multiplication: the contraction is independent per channel, so after the local input
+  projection a and b go from row shards to channel shards with one ``all_to_all`` each
+  (each rank then contracts 128/P channels over the full N x N), and x returns with a third.
+  For the incoming direction the local rows are the contraction index: the local projection
+  yields a[c][i][k in local rows] and the same ``all_to_all`` assembles the k axis.
+* Starting-node attention: only the pair bias [4, N, N] couples the rows: one ``all_gather``.
+* Ending-node attention: z is exchanged to column shards with an ``all_to_all`` (a distributed
+  transpose), the starting-node path runs on the transposed slab, and a second ``all_to_all``
+  brings the update back.
+* Single branch: every rank computes the attention output of its own query rows (it holds
+  their pair bias); one small ``all_gather`` assembles the [N, c_s] result.
+
+Received data always lands in this GPU's memory (NCCL receive buffers) before a kernel reads it;
+no kernel touches peer memory.  The choreography is written against a small stage interface so
+that it can be exercised on CPU ranks (gloo) with a plain-torch stage implementation.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from . import ops
+from .weights import bf16_of
+
+
+# ----------------------------------------------------------------------------------------------
+class CudaStages:
+    """Stage interface backed by the C-ABI kernels."""
+
+    @staticmethod
+    def _f(p):
+        return p.detach().float()
+
+    def trimul_in_proj(self, mod, z, mask, incoming):
+        f = self._f
+        return ops.trimul_in_proj(z, mask, f(mod.layer_norm_in.weight), f(mod.layer_norm_in.bias),
+                                  bf16_of(mod.linear_a_p.weight), bf16_of(mod.linear_a_g.weight),
+                                  bf16_of(mod.linear_b_p.weight), bf16_of(mod.linear_b_g.weight), incoming,
+                                  mod.layer_norm_in.eps)
+
+    def trimul_contract(self, a, b):
+        return ops.trimul_contract(a, b)
+
+    def trimul_out(self, mod, x, z):
+        f = self._f
+        return ops.trimul_out(x, z, f(mod.layer_norm_in.weight), f(mod.layer_norm_in.bias),
+                              f(mod.layer_norm_out.weight), f(mod.layer_norm_out.bias), bf16_of(mod.linear_z.weight),
+                              bf16_of(mod.linear_g.weight), mod.layer_norm_in.eps)
+
+    def triatt_in_proj(self, mod, z, mask):
+        f, m = self._f, mod.mha
+        return ops.triatt_in_proj(z, mask, f(mod.layer_norm.weight), f(mod.layer_norm.bias), bf16_of(mod.linear.weight),
+                                  bf16_of(m.linear_q.weight), bf16_of(m.linear_k.weight), bf16_of(m.linear_v.weight),
+                                  mod.layer_norm.eps, mod.inf)
+
+    def triatt_flash(self, q, k, v, bias_full, mb):
+        return ops.triatt_flash(q, k, v, bias_full, mb)
+
+    def triatt_out(self, mod, o, z):
+        f, m = self._f, mod.mha
+        return ops.triatt_out(o, z, f(mod.layer_norm.weight), f(mod.layer_norm.bias), bf16_of(m.linear_g.weight),
+                              bf16_of(m.linear_o.weight), mod.layer_norm.eps)
+
+    def transition(self, mod, z):
+        f = self._f
+        return ops.transition_rows(z, f(mod.layernorm1.weight), f(mod.layernorm1.bias),
+                                   bf16_of(mod.linear_no_bias_a.weight), bf16_of(mod.linear_no_bias_b.weight),
+                                   bf16_of(mod.linear_no_bias.weight), mod.layernorm1.eps)
+
+    def pair_bias(self, mod, z):
+        b = mod.layernorm_z.bias
+        return ops.pair_bias_rows(z, self._f(mod.layernorm_z.weight), None if b is None else self._f(b),
+                                  bf16_of(mod.linear_nobias_z.weight), mod.layernorm_z.eps)
+
+    def single_layer_norm(self, ln, x):
+        return ln(x)
+
+
+# ----------------------------------------------------------------------------------------------
+class ShardedPairformer:
+    """Runs the blocks of a ``PairformerStack`` (or one ``PairformerBlock``) on a row-sharded z."""
+
+    def __init__(self, module, group: Optional[dist.ProcessGroup] = None, stages=None) -> None:
+        self.blocks = list(module.blocks) if hasattr(module, "blocks") else [module]
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.stages = stages if stages is not None else CudaStages()
+
+    # ---- helpers ------------------------------------------------------------------------------
+    def shard_rows(self, z: torch.Tensor) -> torch.Tensor:
+        n = z.shape[0]
+        if n % self.world:
+            raise RuntimeError(f"N={n} is not divisible by the number of ranks ({self.world}); pad with masked tokens")
+        nl = n // self.world
+        return z[self.rank * nl:(self.rank + 1) * nl].clone()       # private copy: the shard is updated in place
+
+    def _all_gather(self, t: torch.Tensor) -> torch.Tensor:
+        """[world, *t.shape]: slice p is rank p's tensor."""
+        t = t.contiguous()
+        out = torch.empty(self.world * t.numel(), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t.view(-1), group=self.group)
+        return out.view((self.world,) + tuple(t.shape))
+
+    def gather_rows(self, z_loc: torch.Tensor) -> torch.Tensor:
+        return self._all_gather(z_loc).reshape((-1,) + tuple(z_loc.shape[1:]))
+
+    def _all_to_all(self, send: torch.Tensor) -> torch.Tensor:
+        """send[p] goes to rank p; returns recv with recv[p] = what rank p sent to this rank."""
+        send = send.contiguous()
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=self.group)
+        return recv
+
+    def _rows_to_channels(self, t: torch.Tensor, k_sharded: bool) -> torch.Tensor:
+        """[128][rows_loc][ld] (rows sharded) -> [128/P][N][ld(N)] (channels sharded).
+
+        With ``k_sharded`` the local tensor is [128][N][ld(N/P)]: the contraction index is the
+        sharded one and the exchange concatenates it instead of the rows."""
+        p = self.world
+        c, r, ldl = t.shape
+        cp = c // p
+        recv = self._all_to_all(t.view(p, cp, r, ldl))                      # [src][cp][r][ldl]
+        if not k_sharded:
+            return recv.permute(1, 0, 2, 3).reshape(cp, p * r, ldl)          # rows of source p come p-th
+        n = r
+        nl = n // p
+        full = recv[..., :nl].permute(1, 2, 0, 3).reshape(cp, n, n)          # k blocks of source p come p-th
+        ldn = (n + 7) // 8 * 8
+        return F.pad(full, (0, ldn - n)) if ldn != n else full.contiguous()
+
+    def _channels_to_rows(self, x: torch.Tensor) -> torch.Tensor:
+        """[128/P][N][ld] (channels sharded) -> [128][N/P][ld] (rows sharded)."""
+        p = self.world
+        cp, n, ldn = x.shape
+        nl = n // p
+        send = x.view(cp, p, nl, ldn).permute(1, 0, 2, 3)                    # [dst][cp][nl][ld]
+        recv = self._all_to_all(send)                                        # [src = channel block][cp][nl][ld]
+        return recv.reshape(p * cp, nl, ldn)
+
+    def _transpose_shard(self, z_loc: torch.Tensor) -> torch.Tensor:
+        """Row shard [N/P i][N j][c] of z  ->  row shard [N/P j][N i][c] of z^T (and back: an involution)."""
+        p = self.world
+        nl, n, c = z_loc.shape
+        send = z_loc.view(nl, p, nl, c).permute(1, 0, 2, 3)                  # [dst j-block][i][j][c]
+        recv = self._all_to_all(send)                                        # [src i-block][i][j][c]
+        return recv.permute(2, 0, 1, 3).reshape(nl, n, c).contiguous()
+
+    # ---- sub-modules ----------------------------------------------------------------------------
+    def _tri_mul(self, mod, z_loc, mask_loc, incoming: bool) -> None:
+        st = self.stages
+        a, b = st.trimul_in_proj(mod, z_loc, mask_loc, incoming)
+        a = self._rows_to_channels(a, k_sharded=incoming)
+        b = self._rows_to_channels(b, k_sharded=incoming)
+        x = st.trimul_contract(a, b)
+        del a, b
+        st.trimul_out(mod, self._channels_to_rows(x), z_loc)
+
+    def _tri_att_rows(self, mod, z_loc, mask_loc) -> None:
+        st = self.stages
+        q, k, v, bias_loc, mb = st.triatt_in_proj(mod, z_loc, mask_loc)
+        h, nl, ldm = bias_loc.shape
+        bias_full = self._all_gather(bias_loc).permute(1, 0, 2, 3).reshape(h, self.world * nl, ldm)
+        st.triatt_out(mod, st.triatt_flash(q, k, v, bias_full, mb), z_loc)
+
+    def _single_branch(self, blk, s, z_loc):
+        """s + AttentionPairBias(s, z) + Transition(.), query rows sharded like z."""
+        apb, att = blk.attention_pair_bias, blk.attention_pair_bias.attention
+        nl = z_loc.shape[0]
+        rows = slice(self.rank * nl, (self.rank + 1) * nl)
+        bias = self.stages.pair_bias(apb, z_loc)                                       # [H, nl, N]
+        dt = s.dtype
+        x = self.stages.single_layer_norm(apb.layernorm_a, s.float().contiguous())
+        n, h, d = x.shape[0], apb.n_heads, att.c_hidden
+        q = F.linear(x[rows], att.linear_q.weight, att.linear_q.bias).view(nl, h, d).transpose(0, 1)
+        k = F.linear(x, att.linear_k.weight).view(n, h, d).transpose(0, 1)
+        v = F.linear(x, att.linear_v.weight).view(n, h, d).transpose(0, 1)
+        o = F.scaled_dot_product_attention(q / math.sqrt(d), k, v, attn_mask=bias.to(q.dtype), scale=1.0)
+        o = o.transpose(0, 1).reshape(nl, h * d).contiguous()
+        o_full = self._all_gather(o).reshape(self.world * nl, h * d)
+        o_full = o_full * torch.sigmoid(F.linear(x, att.linear_g.weight))
+        s = s + F.linear(o_full, att.linear_o.weight).to(dt)
+        tr = blk.single_transition
+        y = self.stages.single_layer_norm(tr.layernorm1, s.float().contiguous())
+        upd = F.linear(F.silu(F.linear(y, tr.linear_no_bias_a.weight)) * F.linear(y, tr.linear_no_bias_b.weight),
+                       tr.linear_no_bias.weight)
+        return s + upd.to(dt)
+
+    # ---- public ---------------------------------------------------------------------------------
+    @torch.no_grad()
+    def forward(self, s: Optional[torch.Tensor], z_loc: torch.Tensor, pair_mask: Optional[torch.Tensor]
+                ) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
+        """z_loc [N/P, N, 128] is updated in place; s [N, c_s] (replicated) is returned updated."""
+        nl, n, _ = z_loc.shape
+        if nl * self.world != n:
+            raise RuntimeError(f"z_loc has {nl} rows; expected N/P = {n}/{self.world}")
+        rows = slice(self.rank * nl, (self.rank + 1) * nl)
+        mask_loc = mask_t_loc = None
+        if pair_mask is not None:
+            pair_mask = pair_mask.to(torch.float32)
+            mask_loc = pair_mask[rows].contiguous()
+            mask_t_loc = pair_mask.t()[rows].contiguous()
+        for blk in self.blocks:
+            self._tri_mul(blk.tri_mul_out, z_loc, mask_loc, incoming=False)
+            self._tri_mul(blk.tri_mul_in, z_loc, mask_loc, incoming=True)
+            self._tri_att_rows(blk.tri_att_start, z_loc, mask_loc)
+            zt = self._transpose_shard(z_loc)
+            self._tri_att_rows(blk.tri_att_end, zt, mask_t_loc)
+            z_loc.copy_(self._transpose_shard(zt))
+            del zt
+            self.stages.transition(blk.pair_transition, z_loc)
+            if blk.c_s > 0 and s is not None:
+                s = self._single_branch(blk, s, z_loc)
+        return s, z_loc

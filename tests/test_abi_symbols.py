@@ -60,12 +60,12 @@ def test_host_side_queries(lib):
 def test_argument_errors_are_status_codes_not_crashes(lib):
     """Bad arguments are rejected on the host before any launch (no GPU needed)."""
     assert lib.px_layer_norm_fwd(None, None, None, None, None, None, 4, 128, 1e-5, 0, None) == -1
-    assert lib.px_trimul_contract(None, None, None, 16, 16, None) == -1
+    assert lib.px_trimul_contract(None, None, None, 128, 16, 16, None) == -1
     assert lib.px_transition(None, None, 0, None, None, None, None, None, 10, 1, 1e-5, None) == -1
     buf = ctypes.create_string_buffer(64)
     p = ctypes.addressof(buf)
     # wrong leading dimension
-    assert lib.px_trimul_contract(p, p, p, 20, 20, None) == -1
+    assert lib.px_trimul_contract(p, p, p, 128, 20, 20, None) == -1
     # unsupported dtype
     assert lib.px_layer_norm_fwd(p, None, None, p, None, None, 1, 8, 1e-5, 7, None) == -2
     # too many heads for the pair-bias projection

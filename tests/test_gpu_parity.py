@@ -274,7 +274,7 @@ def test_contraction_stage_through_c_abi(n):
     b[:, :, :n] = torch.randn(128, n, n, generator=g).to(torch.bfloat16)
     a, b = a.cuda(), b.cuda()
     x = torch.full((128, n, ldn), float("nan"), dtype=torch.bfloat16, device=DEV)
-    rc = lib.px_trimul_contract(a.data_ptr(), b.data_ptr(), x.data_ptr(), n, ldn,
+    rc = lib.px_trimul_contract(a.data_ptr(), b.data_ptr(), x.data_ptr(), 128, n, ldn,
                                 torch.cuda.current_stream().cuda_stream)
     assert rc == 0
     flags = ctypes.c_uint32(99)

@@ -1,0 +1,133 @@
+"""GPU checks of the row-sharded path on one device: the rectangular (row-slab) forms of the stage
+kernels against their square forms, and the whole sharded choreography with a one-rank NCCL group
+against the plain module."""
+import os
+import socket
+
+import pytest
+import torch
+
+import protenix_b200 as px
+from golden_cases import random_mask
+from helpers import build_module, params_of, relf
+from oracle import pairformer_oracle as O
+from protenix_b200 import ops
+from protenix_b200.sharded import CudaStages
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("n,parts", [(48, 2), (96, 4), (120, 3)])
+def test_row_slab_stages_equal_square_stages(n, parts):
+    g = torch.Generator().manual_seed(n)
+    z = torch.randn(n, n, 128, generator=g).to(torch.bfloat16).to(DEV)
+    mask = random_mask(n, 2).to(DEV)
+    blk = build_module("block", dict(c_s=0, wseed=3)).to(DEV)
+    st = CudaStages()
+    nl = n // parts
+    a_f, b_f = st.trimul_in_proj(blk.tri_mul_out, z, mask, False)
+    ai_f, bi_f = st.trimul_in_proj(blk.tri_mul_in, z, mask, True)
+    q_f, k_f, v_f, bias_f, mb_f = st.triatt_in_proj(blk.tri_att_start, z, mask)
+    o_f = st.triatt_flash(q_f, k_f, v_f, bias_f, mb_f)
+    x_f = st.trimul_contract(a_f, b_f)
+    z_mul = st.trimul_out(blk.tri_mul_out, x_f, z.clone())
+    z_att = st.triatt_out(blk.tri_att_start, o_f, z.clone())
+    for r in range(parts):
+        rows = slice(r * nl, (r + 1) * nl)
+        zs, ms = z[rows].contiguous(), mask[rows].contiguous()
+        a, b = st.trimul_in_proj(blk.tri_mul_out, zs, ms, False)
+        assert torch.equal(a, a_f[:, rows]) and torch.equal(b, b_f[:, rows])
+        ai, bi = st.trimul_in_proj(blk.tri_mul_in, zs, ms, True)          # local rows are the k index
+        assert torch.equal(ai[:, :, :nl], ai_f[:, :, rows]) and torch.equal(bi[:, :, :nl], bi_f[:, :, rows])
+        assert float(ai[:, :, nl:].abs().sum()) == 0.0
+        q, k, v, bias, mb = st.triatt_in_proj(blk.tri_att_start, zs, ms)
+        assert torch.equal(q, q_f[rows]) and torch.equal(k, k_f[rows]) and torch.equal(v, v_f[rows])
+        assert torch.equal(bias, bias_f[:, rows]) and torch.equal(mb, mb_f[rows])
+        assert torch.equal(st.triatt_flash(q, k, v, bias_f, mb), o_f[rows])
+        assert torch.equal(st.trimul_out(blk.tri_mul_out, x_f[:, rows].contiguous(), zs.clone()), z_mul[rows])
+        assert torch.equal(st.triatt_out(blk.tri_att_start, o_f[rows].contiguous(), zs.clone()), z_att[rows])
+    # the contraction on a subset of channels
+    assert torch.equal(st.trimul_contract(a_f[32:48].contiguous(), b_f[32:48].contiguous()), x_f[32:48])
+
+
+def test_sharded_path_with_one_rank_equals_module():
+    import torch.distributed as dist
+
+    from protenix_b200.sharded import ShardedPairformer
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+    try:
+        n = 72
+        g = torch.Generator().manual_seed(4)
+        z = torch.randn(n, n, 128, generator=g).to(DEV)
+        s = torch.randn(n, 384, generator=g).to(DEV)
+        mask = random_mask(n, 9).to(DEV)
+        stack = build_module("stack", dict(n_blocks=2, c_s=384, wseed=5)).to(DEV)
+        s_ref, z_ref = stack(s, z, mask)
+        sp = ShardedPairformer(stack)
+        s_out, z_out = sp.forward(s, sp.shard_rows(z), mask)
+        assert relf(z_out, z_ref) < 1e-6 and relf(s_out, s_ref) < 1e-5
+        s0, z0 = O.pairformer_stack(s.cpu(), z.cpu(), mask.cpu(), params_of(stack), n_blocks=2)
+        assert relf(z_out, z0) < 2e-2 and relf(s_out, s0) < 2e-2
+    finally:
+        dist.destroy_process_group()
+
+
+def _nccl_worker(rank, world, port, n, q):
+    import sys
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    for p in (os.path.dirname(here), here, os.path.join(here, "golden")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import torch.distributed as dist
+
+    from protenix_b200.sharded import ShardedPairformer
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        g = torch.Generator().manual_seed(4)
+        z = torch.randn(n, n, 128, generator=g).to(torch.bfloat16).to(dev)
+        s = torch.randn(n, 384, generator=g).to(dev)
+        mask = random_mask(n, 9).to(dev)
+        stack = build_module("stack", dict(n_blocks=2, c_s=384, wseed=5)).to(dev)
+        sp = ShardedPairformer(stack)
+        s_out, z_loc = sp.forward(s, sp.shard_rows(z), mask)
+        z_out = sp.gather_rows(z_loc)
+        if rank == 0:
+            s_ref, z_ref = stack(s, z, mask)            # the single-GPU path on the same device
+            q.put((relf(z_out, z_ref), relf(s_out, s_ref), bool(torch.equal(z_out, z_ref))))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,n", [(2, 136), (4, 192), (8, 256)])
+def test_sharded_over_nccl_equals_single_gpu(world, n):
+    """Gathered output of the row-sharded stack on `world` GPUs against the one-GPU stack."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_nccl_worker, args=(r, world, port, n, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    ez, es, same = q.get(timeout=10)
+    # same kernels, same per-element arithmetic: only the reduction-free re-layouts differ
+    assert ez < 1e-3 and es < 1e-3, (ez, es, same)
