@@ -16,6 +16,7 @@ constexpr int kD = 32;  // head width
 struct TriAttInSmem {
   bf16 A[128 * kLdA];
   bf16 W[2][64 * kLdA];
+  bf16 S[64 * kLdA];  // transposed staging of a v chunk: [channel][t]
 };
 
 template <typename Tz>
@@ -24,7 +25,7 @@ triatt_in_proj_kernel(const Tz* __restrict__ z, const float* __restrict__ mask, 
                       const float* __restrict__ ln_b, const bf16* __restrict__ w_q, const bf16* __restrict__ w_k,
                       const bf16* __restrict__ w_v, const bf16* __restrict__ w_bias, bf16* __restrict__ q_out,
                       bf16* __restrict__ k_out, bf16* __restrict__ v_out, float* __restrict__ bias_out,
-                      float* __restrict__ mb_out, int n_u, int n, int ldm, int swap, float eps, float inf) {
+                      float* __restrict__ mb_out, int n_u, int n, int ldm, int ldt, int swap, float eps, float inf) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   TriAttInSmem& sm = *reinterpret_cast<TriAttInSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -75,9 +76,34 @@ triatt_in_proj_kernel(const Tz* __restrict__ z, const float* __restrict__ mask, 
     float acc[8][4];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-    if (c < 6) {
+    if (c >= 4 && c < 6) {
+      // v is stored transposed, [u][h][d][t] with t contiguous (row stride ldt, zero pad columns), so
+      // that the value tile is a K-major operand of the P.V product
       warp_gemm_k128<0, 8, 8>(acc, afr, sm.W[c & 1], lane);
-      bf16* dst = (c < 2) ? q_out : (c < 4 ? k_out : v_out);
+      const int r0 = 16 * warp + g;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int ch = 8 * j + 2 * tq;
+        sm.S[ch * kLdA + r0] = __float2bfloat16_rn(acc[j][0]);
+        sm.S[(ch + 1) * kLdA + r0] = __float2bfloat16_rn(acc[j][1]);
+        sm.S[ch * kLdA + r0 + 8] = __float2bfloat16_rn(acc[j][2]);
+        sm.S[(ch + 1) * kLdA + r0 + 8] = __float2bfloat16_rn(acc[j][3]);
+      }
+      __syncthreads();
+      {
+        const int ch = tid >> 2, seg = tid & 3;  // 64 channels x 4 segments of 32 t
+        const size_t row = (((size_t)u * kH + 2 * (c & 1) + (ch >> 5)) * kD + (ch & 31)) * ldt;
+#pragma unroll
+        for (int h8 = 0; h8 < 4; ++h8) {
+          const int t = t0 + seg * 32 + h8 * 8;
+          if (t < ldt)
+            *reinterpret_cast<uint4*>(v_out + row + t) =
+                *reinterpret_cast<const uint4*>(sm.S + ch * kLdA + seg * 32 + h8 * 8);
+        }
+      }
+    } else if (c < 4) {
+      warp_gemm_k128<0, 8, 8>(acc, afr, sm.W[c & 1], lane);
+      bf16* dst = (c < 2) ? q_out : k_out;
       const float sc = (c < 2) ? qscale : 1.0f;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -115,11 +141,13 @@ triatt_in_proj_kernel(const Tz* __restrict__ z, const float* __restrict__ mask, 
 // =========================================================================================
 constexpr int kFaLd = kD + 8;  // shared row stride of q/k/v tiles (80 bytes: conflict-free ldmatrix)
 
+constexpr int kFaLdV = 64 + 8;  // row stride of a transposed value tile [32 d][64 keys]
+
 template <int R>
 struct FlashSmem {
   bf16 Q[R][64 * kFaLd];
   bf16 K[2][R][64 * kFaLd];
-  bf16 V[2][R][64 * kFaLd];
+  bf16 V[2][R][kD * kFaLdV];
   float MB[2][R][64];
 };
 
@@ -127,7 +155,7 @@ template <int R>
 __global__ void __launch_bounds__(128, 2)
 triatt_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                     const float* __restrict__ bias, const float* __restrict__ mb, bf16* __restrict__ o, int n_u,
-                    int n, int ldm) {
+                    int n, int ldm, int ldt) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   FlashSmem<R>& sm = *reinterpret_cast<FlashSmem<R>*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -147,7 +175,11 @@ triatt_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
         const bool p = urow && (kt * 64 + row) < n;
         const size_t off = p ? (base + kt * 64 + row) * kD + ch * 8 : 0;
         cp_async16(smem_u32(sm.K[stage][r] + row * kFaLd + ch * 8), k + off, p);
-        cp_async16(smem_u32(sm.V[stage][r] + row * kFaLd + ch * 8), v + off, p);
+        // value tile, transposed: 32 rows (d) x 64 keys, 8 pieces of 16 bytes per row
+        const int d = idx >> 3, kc = idx & 7;
+        const bool pv = urow && (kt * 64 + kc * 8) < ldt;
+        const size_t offv = pv ? (((size_t)(u0 + r) * kH + h) * kD + d) * ldt + kt * 64 + kc * 8 : 0;
+        cp_async16(smem_u32(sm.V[stage][r] + d * kFaLdV + kc * 8), v + offv, pv);
       }
     }
     if (tid < R * 16) {
@@ -276,14 +308,14 @@ triatt_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
       // O += P V
       {
         const bf16* Vs = sm.V[stage][r];
-        const int krow = (lane & 7) + ((lane >> 3) & 1) * 8;
-        const int dof = (lane >> 4) * 8;
+        const int drow = (lane & 7) + (lane >> 4) * 8;
+        const int kof2 = ((lane >> 3) & 1) * 8;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
 #pragma unroll
           for (int dp = 0; dp < 2; ++dp) {
             uint32_t b[4];
-            ldmatrix_x4_trans(b, smem_u32(Vs + (kk * 16 + krow) * kFaLd + dp * 16 + dof));
+            ldmatrix_x4(b, smem_u32(Vs + (dp * 16 + drow) * kFaLdV + kk * 16 + kof2));
             mma_bf16(oacc[r][2 * dp], pf[kk], b[0], b[1]);
             mma_bf16(oacc[r][2 * dp + 1], pf[kk], b[2], b[3]);
           }
@@ -408,7 +440,7 @@ triatt_out_kernel(const bf16* __restrict__ o, const Tz* __restrict__ z_in, Tz* _
   }
 }
 
-static size_t att_qkv_elems(int64_t n) { return (size_t)n * kH * n * kD; }
+static size_t att_qkv_elems(int64_t n) { return (size_t)n * kH * px_ld(n) * kD; }
 static size_t align256(size_t b) { return (b + 255) / 256 * 256; }
 
 }  // namespace px
@@ -436,15 +468,16 @@ extern "C" int32_t px_triatt_in_proj(const void* z, int32_t z_dtype, const float
       return PX_ERR_LAUNCH;
     triatt_in_proj_kernel<float><<<grid, 256, smem, st>>>(
         (const float*)z, mask, ln_w, ln_b, (const bf16*)w_q, (const bf16*)w_k, (const bf16*)w_v,
-        (const bf16*)w_bias, (bf16*)q, (bf16*)k, (bf16*)v, bias, mask_bias, (int)n_u, (int)n_t, (int)ldm, ending, eps,
-        inf);
+        (const bf16*)w_bias, (bf16*)q, (bf16*)k, (bf16*)v, bias, mask_bias, (int)n_u, (int)n_t, (int)ldm, (int)px_ld(n_t), ending,
+        eps, inf);
   } else if (z_dtype == PX_BF16) {
     if (cudaFuncSetAttribute(triatt_in_proj_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return PX_ERR_LAUNCH;
     triatt_in_proj_kernel<bf16><<<grid, 256, smem, st>>>(
         (const bf16*)z, mask, ln_w, ln_b, (const bf16*)w_q, (const bf16*)w_k, (const bf16*)w_v, (const bf16*)w_bias,
-        (bf16*)q, (bf16*)k, (bf16*)v, bias, mask_bias, (int)n_u, (int)n_t, (int)ldm, ending, eps, inf);
+        (bf16*)q, (bf16*)k, (bf16*)v, bias, mask_bias, (int)n_u, (int)n_t, (int)ldm, (int)px_ld(n_t), ending, eps,
+        inf);
   } else {
     return PX_ERR_UNSUPPORTED;
   }
@@ -463,7 +496,8 @@ extern "C" int32_t px_triatt_flash(const px_bf16* q, const px_bf16* k, const px_
       cudaSuccess)
     return PX_ERR_LAUNCH;
   triatt_flash_kernel<kFlashR><<<grid, 128, smem, (cudaStream_t)stream>>>(
-      (const bf16*)q, (const bf16*)k, (const bf16*)v, bias, mask_bias, (bf16*)o, (int)n_u, (int)n, (int)ldm);
+      (const bf16*)q, (const bf16*)k, (const bf16*)v, bias, mask_bias, (bf16*)o, (int)n_u, (int)n, (int)ldm,
+      (int)px_ld(n));
   return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
 }
 

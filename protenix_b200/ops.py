@@ -205,7 +205,7 @@ def triangle_attention(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optional[t
     ws = workspace(z_in.device, lib.px_triatt_workspace_bytes(n))
     ldn = lib.px_ld_mask(n)
     al = lambda nb: (nb + 255) // 256 * 256
-    qkv = al(n * N_HEAD_PAIR * n * D_HEAD_PAIR * 2)
+    qkv = al(n * N_HEAD_PAIR * lib.px_ld(n) * D_HEAD_PAIR * 2)   # v is [n][4][32][ld(n)], q and k fit as well
     q = ws.data_ptr()
     k, v, o = q + qkv, q + 2 * qkv, q + 3 * qkv
     bias = o + al(n * n * C_Z * 2)
@@ -300,12 +300,14 @@ def trimul_out(x: torch.Tensor, z: torch.Tensor, ln_in_w, ln_in_b, ln_out_w, ln_
 
 def triatt_in_proj(z: torch.Tensor, mask: Optional[torch.Tensor], ln_w, ln_b, w_bias, w_q, w_k, w_v,
                    eps: float = 1e-5, inf: float = 1e9):
-    """q, k, v [n_u][4][n_t][32] bf16, bias [4][n_u][ldm] fp32, mask_bias [n_u][ldm] fp32 for a row slab."""
+    """q, k [n_u][4][n_t][32] and v (transposed) [n_u][4][32][ld(n_t)] bf16, bias [4][n_u][ldm] fp32,
+    mask_bias [n_u][ldm] fp32 for a row slab."""
     n_u, n_t = _slab(z)
     lib = _lib.load()
     ldm = lib.px_ld_mask(n_t)
     q = torch.empty(n_u, N_HEAD_PAIR, n_t, D_HEAD_PAIR, dtype=torch.bfloat16, device=z.device)
-    k, v = torch.empty_like(q), torch.empty_like(q)
+    k = torch.empty_like(q)
+    v = torch.empty(n_u, N_HEAD_PAIR, D_HEAD_PAIR, lib.px_ld(n_t), dtype=torch.bfloat16, device=z.device)
     bias = torch.empty(N_HEAD_PAIR, n_u, ldm, dtype=torch.float32, device=z.device)
     mb = torch.empty(n_u, ldm, dtype=torch.float32, device=z.device)
     _launch("px_triatt_in_proj", lib.px_triatt_in_proj, _ptr(z), _pair_dtype(z), _ptr(mask), _ptr(ln_w), _ptr(ln_b),

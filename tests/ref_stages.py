@@ -52,7 +52,8 @@ class TorchStages:
         h, d = mod.no_heads, mod.c_hidden
         sh = lambda t: t.view(n_u, n_t, h, d).permute(0, 2, 1, 3).contiguous()
         q = sh(xn @ mod.mha.linear_q.weight.T) * (LOG2E / math.sqrt(d))
-        k, v = sh(xn @ mod.mha.linear_k.weight.T), sh(xn @ mod.mha.linear_v.weight.T)
+        k = sh(xn @ mod.mha.linear_k.weight.T)
+        v = _pad_last(sh(xn @ mod.mha.linear_v.weight.T).transpose(2, 3), _ld(n_t))   # [u][h][d][ld(t)]
         ldm = _ld(n_t, 64)
         bias = _pad_last(((xn @ mod.linear.weight.T) * LOG2E).permute(2, 0, 1), ldm)
         m = mask if mask is not None else z.new_ones(n_u, n_t)
@@ -63,7 +64,7 @@ class TorchStages:
         n_u, h, n, d = q.shape
         logits = torch.einsum("uhqd,uhkd->uhqk", q, k) + bias_full[None, :, :, :n] + mb[:, None, None, :n]
         w = torch.softmax(logits * math.log(2.0), dim=-1)
-        return torch.einsum("uhqk,uhkd->uqhd", w, v).reshape(n_u, n, h * d)
+        return torch.einsum("uhqk,uhdk->uqhd", w, v[..., :n]).reshape(n_u, n, h * d)
 
     def triatt_out(self, mod, o, z):
         xn = _ln(z, mod.layer_norm)
