@@ -63,7 +63,7 @@ PX_API int32_t px_version(void);
 PX_API const char* px_status_string(int32_t status);
 /* Leading dimension used for intermediates: N rounded up to a multiple of 8. */
 PX_API int64_t px_ld(int64_t n);
-/* Row stride of the attention bias tensors: N rounded up to a multiple of 64 (one key tile). */
+/* Row stride of the attention bias tensors: N rounded up to a multiple of 128 (one key tile). */
 PX_API int64_t px_ld_mask(int64_t n);
 
 /* ---- LayerNorm op ---------------------------------------------------------------------
@@ -137,7 +137,7 @@ PX_API int32_t px_triangle_multiplication_static(const void* z_in, void* z_out, 
 PX_API int64_t px_static_max_n(void);
 
 /* ---- Triangle attention (starting / ending node), 4 heads x 32 -------------------------
- * Stage 1: xn = LN(z); q,k,v = W xn written per attended row u as [u][h][t][32] bf16 with q
+ * Stage 1: xn = LN(z); q,k,v = W xn written per attended row u as [u][h][t][32] bf16 (v transposed: [u][h][32][ld(n_t)]) with q
  * pre-scaled by log2(e)/sqrt(32); bias[h][u][t] = log2(e) * (W_b xn)[u][t][h] (fp32, row
  * stride ldm = px_ld_mask(N), zero in the pad columns); mask_bias[u][t] = log2(e) * inf *
  * (mask - 1) (fp32, row stride ldm, -infinity in the pad columns).  For the
@@ -148,12 +148,17 @@ PX_API int32_t px_triatt_in_proj(const void* z, int32_t z_dtype, const float* ma
                           const px_bf16* w_q, const px_bf16* w_k, const px_bf16* w_v, const px_bf16* w_bias,
                           px_bf16* q, px_bf16* k, px_bf16* v, float* bias, float* mask_bias, int64_t n_u, int64_t n_t,
                           int64_t ldm, int32_t ending, float eps, float inf, void* stream);
-/* Stage 2: o[u][t][h*32+d] = softmax_k(q.k + bias[h][t][k] + mask_bias[u][k]) v, online
- * softmax in base 2, logits never leave the SM.  Replaces the back-ends selected in
- * protenix/model/triangular/layers.py:441-469 (_attention :276-296, the Triton kernel
- * protenix/model/tri_attention/forward.py:22-188, DS4Sci and cuEquivariance calls). */
+/* Stage 2: o[u][t][h*32+d] = softmax_k(q.k + bias[h][t][k] + mask_bias[u][k]) v on the tcgen05
+ * tensor cores: TMA-fed, logits and probabilities live in tensor memory only, online softmax in
+ * base 2.  v is the transposed layout [u][h][32][ld(n)] written by stage 1; `scratch` needs
+ * px_triatt_flash_scratch_bytes(n_u, n) bytes (per-tile mask flags).  All pointers 16-byte aligned.
+ * Replaces the back-ends selected in protenix/model/triangular/layers.py:441-469 (_attention
+ * :276-296, the Triton kernel protenix/model/tri_attention/forward.py:22-188, DS4Sci and
+ * cuEquivariance calls). */
 PX_API int32_t px_triatt_flash(const px_bf16* q, const px_bf16* k, const px_bf16* v, const float* bias,
-                        const float* mask_bias, px_bf16* o, int64_t n_u, int64_t n, int64_t ldm, void* stream);
+                        const float* mask_bias, px_bf16* o, void* scratch, int64_t n_u, int64_t n, int64_t ldm,
+                        void* stream);
+PX_API int64_t px_triatt_flash_scratch_bytes(int64_t n_u, int64_t n);
 /* Stage 3: z_out(u,t) = [z_in(u,t) +] W_o (o[u][t] * sigmoid(W_g LN(z_in(u,t)))), where (u,t)
  * addresses z[u][t] (starting) or z[t][u] (ending).  z_out may alias z_in.
  * Replaces Attention._wrap_up, protenix/model/triangular/layers.py:384-398. */

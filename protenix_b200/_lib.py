@@ -32,7 +32,8 @@ SIGNATURES = {
     "px_triangle_multiplication_static": (I32, [P, P, I32, P, P, P, P, P, P, P, P, P, P, P, I64, I32, I32, F, P]),
     "px_static_max_n": (I64, []),
     "px_triatt_in_proj": (I32, [P, I32, P, P, P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I32, F, F, P]),
-    "px_triatt_flash": (I32, [P, P, P, P, P, P, I64, I64, I64, P]),
+    "px_triatt_flash": (I32, [P, P, P, P, P, P, P, I64, I64, I64, P]),
+    "px_triatt_flash_scratch_bytes": (I64, [I64, I64]),
     "px_triatt_out": (I32, [P, P, P, I32, P, P, P, P, I64, I64, I32, I32, F, P]),
     "px_triatt_workspace_bytes": (I64, [I64]),
     "px_triangle_attention": (I32, [P, P, I32, P, P, P, P, P, P, P, P, P, P, I64, I64, I32, I32, F, F, P]),

@@ -1,6 +1,20 @@
 // Version and status text of the C ABI.
 #include "px_common.cuh"
 
+namespace px {
+unsigned int contract_error_flags();
+unsigned int flash_error_flags();
+}  // namespace px
+
+// Synchronises the device and returns (and clears) the flags recorded by bounded waits that ran out.
+// Bits 0-7: contraction kernel, bits 8-15: flash-attention kernel.
+extern "C" int32_t px_device_error_flags(uint32_t* flags) {
+  if (!flags) return PX_ERR_BAD_ARG;
+  if (cudaDeviceSynchronize() != cudaSuccess) return PX_ERR_LAUNCH;
+  *flags = px::contract_error_flags() | (px::flash_error_flags() << 8);
+  return PX_OK;
+}
+
 extern "C" int32_t px_version(void) { return 100; }
 
 extern "C" const char* px_status_string(int32_t status) {

@@ -16,9 +16,7 @@
 //
 // Every wait on an mbarrier is bounded; a wait that runs out records a flag in g_tc_error, the
 // role stops issuing work, and the kernel still frees its TMEM and returns.
-#include <cuda.h>
-
-#include "px_common.cuh"
+#include "px_tcgen05.cuh"
 
 namespace px {
 
@@ -26,81 +24,11 @@ constexpr int kTcBM = 128, kTcBN = 256, kTcBK = 64, kTcStages = 4;
 constexpr int kTcABytes = kTcBM * kTcBK * 2, kTcBBytes = kTcBN * kTcBK * 2;
 constexpr int kTcStageBytes = kTcABytes + kTcBBytes;
 constexpr uint32_t kTcCols = 512;  // two 256-column fp32 accumulators
-constexpr long long kWaitCycles = 1ll << 31;  // about one second at 2 GHz
-
-__device__ unsigned int g_tc_error = 0;
 
 struct TcBarriers {
   uint64_t full[kTcStages], empty[kTcStages], acc_full[2], acc_empty[2];
   uint32_t tmem_base;
 };
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-// Bounded wait for the phase with the given parity; false = gave up (error flag set).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int code) {
-  const uint32_t addr = smem_u32(bar);
-  const long long t0 = clock64();
-  for (;;) {
-    uint32_t done;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.b32 %0, 1, 0, p;\n}\n"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return true;
-    if (clock64() - t0 > kWaitCycles) {
-      atomicOr(&g_tc_error, code);
-      return false;
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
-      : "memory");
-}
-
-// K-major operand tile, rows of 64 bf16 (128 bytes), 128-byte swizzle, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-// kind::f16, A and B bf16 K-major, D fp32, M=128, N=256
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTcBN >> 3) << 17) | ((uint32_t)(kTcBM >> 4) << 24);
-
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
 
 __global__ void __launch_bounds__(192, 1)
 trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -181,7 +109,7 @@ trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
           const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sa + kTcABytes);
 #pragma unroll
           for (int k = 0; k < kTcBK / 16; ++k)  // 16 bf16 = 32 bytes = 2 units of the start-address field
-            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, (kt | k) ? 1u : 0u);
+            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, umma_idesc_bf16(kTcBM, kTcBN), (kt | k) ? 1u : 0u);
           umma_commit(&bars.empty[s]);
         }
         if (!ok) break;
@@ -243,34 +171,16 @@ trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
-
 // [channels][n rows][ld k] bf16 tensor, box = [1][box_rows][64], 128-byte swizzle, zero fill outside.
 static bool make_operand_map(CUtensorMap* map, const void* base, int64_t channels, int64_t n, int64_t ld,
                              uint32_t box_rows) {
-  EncodeTiledFn enc = encode_fn();
-  if (!enc) return false;
-  const cuuint64_t dims[3] = {(cuuint64_t)ld, (cuuint64_t)n, (cuuint64_t)channels};
-  const cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)n * ld * 2};
-  const cuuint32_t box[3] = {(cuuint32_t)kTcBK, box_rows, 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return make_map_3d(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, (uint64_t)ld, (uint64_t)n, (uint64_t)channels,
+                     (uint64_t)ld * 2, (uint64_t)n * ld * 2, kTcBK, box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+unsigned int contract_error_flags() {
+  unsigned int v = 0;
+  return read_clear_tc_error(&v) == 0 ? v : 0x80000000u;
 }
 
 }  // namespace px
@@ -299,12 +209,3 @@ extern "C" int32_t px_trimul_contract(const px_bf16* a, const px_bf16* b, px_bf1
   return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
 }
 
-// Synchronises the device and returns (and clears) the flags recorded by bounded waits that ran out.
-extern "C" int32_t px_device_error_flags(uint32_t* flags) {
-  if (!flags) return PX_ERR_BAD_ARG;
-  unsigned int v = 0, zero = 0;
-  if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(v)) != cudaSuccess) return PX_ERR_LAUNCH;
-  if (v && cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(zero)) != cudaSuccess) return PX_ERR_LAUNCH;
-  *flags = v;
-  return PX_OK;
-}

@@ -210,11 +210,12 @@ def triangle_attention(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optional[t
     k, v, o = q + qkv, q + 2 * qkv, q + 3 * qkv
     bias = o + al(n * n * C_Z * 2)
     mbias = bias + al(N_HEAD_PAIR * n * ldn * 4)
+    flags = mbias + al(n * ldn * 4)
     dt, st, eps = _pair_dtype(z_in), _stream(z_in), float(eps)
     _launch("px_triatt_in_proj", lib.px_triatt_in_proj, _ptr(z_in), dt, _ptr(mask), _ptr(ln_w), _ptr(ln_b),
             _ptr(w_q), _ptr(w_k), _ptr(w_v), _ptr(w_bias), q, k, v, bias, mbias, n, n, ldn, int(ending), eps,
             float(inf), st)
-    _launch("px_triatt_flash", lib.px_triatt_flash, q, k, v, bias, mbias, o, n, n, ldn, st)
+    _launch("px_triatt_flash", lib.px_triatt_flash, q, k, v, bias, mbias, o, flags, n, n, ldn, st)
     _launch("px_triatt_out", lib.px_triatt_out, o, _ptr(z_in), _ptr(z_out), dt, _ptr(ln_w), _ptr(ln_b), _ptr(w_g),
             _ptr(w_o), n, n, int(ending), int(add_residual), eps, st)
     return z_out
@@ -325,8 +326,10 @@ def triatt_flash(q, k, v, bias_full: torch.Tensor, mb) -> torch.Tensor:
     if tuple(bias_full.shape) != (N_HEAD_PAIR, n, ldm) or tuple(mb.shape) != (n_u, ldm):
         raise RuntimeError("pair bias must be [4][n][ldm] and mask_bias [n_u][ldm]")
     o = torch.empty(n_u, n, C_Z, dtype=torch.bfloat16, device=q.device)
-    _launch("px_triatt_flash", _lib.load().px_triatt_flash, _ptr(q), _ptr(k), _ptr(v), _ptr(bias_full), _ptr(mb),
-            _ptr(o), n_u, n, ldm, _stream(q))
+    lib = _lib.load()
+    scratch = torch.empty(int(lib.px_triatt_flash_scratch_bytes(n_u, n)), dtype=torch.uint8, device=q.device)
+    _launch("px_triatt_flash", lib.px_triatt_flash, _ptr(q), _ptr(k), _ptr(v), _ptr(bias_full), _ptr(mb), _ptr(o),
+            _ptr(scratch), n_u, n, ldm, _stream(q))
     return o
 
 

@@ -54,7 +54,7 @@ class TorchStages:
         q = sh(xn @ mod.mha.linear_q.weight.T) * (LOG2E / math.sqrt(d))
         k = sh(xn @ mod.mha.linear_k.weight.T)
         v = _pad_last(sh(xn @ mod.mha.linear_v.weight.T).transpose(2, 3), _ld(n_t))   # [u][h][d][ld(t)]
-        ldm = _ld(n_t, 64)
+        ldm = _ld(n_t, 128)
         bias = _pad_last(((xn @ mod.linear.weight.T) * LOG2E).permute(2, 0, 1), ldm)
         m = mask if mask is not None else z.new_ones(n_u, n_t)
         mb = _pad_last((m - 1) * mod.inf * LOG2E, ldm, float("-inf"))
