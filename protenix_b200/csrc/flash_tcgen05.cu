@@ -2,23 +2,24 @@
 //
 //   o[u][q][h*32+d] = softmax_k( q[u,h,q,:] . k[u,h,k,:] + bias[h][q][k] + mask_bias[u][k] ) v[u,h,k,d]
 //
-// One CTA = (head h, 128 queries, 4 attended rows u), 10 warps:
-//   warps 0..3  softmax group 0: rows u0+0 and u0+2   (each thread owns one query row)
-//   warps 4..7  softmax group 1: rows u0+1 and u0+3
-//   warp 8      TMA producer: the four Q tiles once, then per work item a K tile [128 keys][32] (64-byte
-//               swizzle) and a transposed V tile [32 d][128 keys] (128-byte swizzle, two boxes) into a
-//               3-stage ring; per key tile the pair-bias tile [128 q][128 k] fp32 (four 128-byte-swizzled
-//               boxes) into a 2-deep ring.  The bias tile is shared by the four rows.
-//   warp 9      MMA issuer (one thread): S = Q K^T (M=128, N=128, K=32) into one of two TMEM buffers; after
-//               the group has turned S into P (bf16, written back over S in TMEM), O_u += P V with P as the
-//               TMEM-resident A operand (M=128, N=48, K=128).  Row 32 of the value operand is all ones, so
-//               column 32 of O_u accumulates the softmax denominators.
-// Work items are ordered (key tile, row); consecutive items alternate between the two groups, so the
-// tensor core computes the next S while a group is busy with exponentials.
+// One CTA = (head h, 128 queries, 4 attended rows u), 20 warps:
+//   warps 0..15   four softmax groups of four warps; group g owns row u0+g, each thread one query row
+//   warps 16..19  one control thread per group (tcgen05 and TMA instructions cost ~100 cycles of issue
+//                 each, so one issuing thread for all four groups would be the bottleneck).  It loads the
+//                 group's Q tile once and, per 64-key tile, a K tile [64 keys][32] (64-byte swizzle) and a
+//                 transposed V tile [32 d][64 keys] (128-byte swizzle) into the group's 3-stage ring;
+//                 issues S = Q K^T (M=128, N=64, K=32) into the group's TMEM buffer; and, once the group
+//                 has turned S into P (bf16, written back over S in TMEM), issues O_u += P V with P as the
+//                 TMEM-resident A operand (M=128, N=48, K=64).  Row 32 of the value operand is all ones, so
+//                 column 32 of O_u accumulates the softmax denominators.  The control thread of group 0 also
+//                 loads the pair-bias tile [128 q][64 k] fp32 (two 128-byte-swizzled boxes, 2-deep ring)
+//                 that all four rows share.
+// While one group is busy with exponentials the tensor core serves the other three.
 //
 // Softmax is online in base 2 with a lazy reference maximum: the reference only moves (and O_u is rescaled
 // through TMEM) when the tile maximum exceeds it by more than 8, so probabilities stay below 2^8.
-// Exponentials use the packed bf16 ex2 (P feeds a bf16 MMA anyway).  Every mbarrier wait is bounded.
+// Exponentials use the packed bf16 ex2 (P feeds a bf16 MMA anyway); adds run as packed f32x2 and the row
+// maximum as 3-input max.  Every mbarrier wait is bounded.
 #include <math_constants.h>
 
 #include "px_tcgen05.cuh"
@@ -26,70 +27,94 @@
 namespace px {
 
 constexpr int kFH = 4, kFD = 32;
-constexpr int kFRows = 4;                 // attended rows per CTA
-constexpr int kFStages = 3;               // K/V ring
+constexpr int kFRows = 4;                 // attended rows per CTA = softmax groups
+constexpr int kFKT = 64;                  // keys per work item
+constexpr int kFStages = 3;               // K/V ring of each group
 constexpr int kFQBytes = 128 * 64;        // [128][32] bf16
-constexpr int kFKBytes = 128 * 64;
-constexpr int kFVBox = 32 * 128;          // one TMA box of the value tile: 32 rows x 64 keys
-constexpr int kFVSub = 48 * 128;          // shared footprint of one half (48 operand rows: 32 d, ones, 15 zero)
-constexpr int kFStageBytes = kFKBytes + 2 * kFVSub;
-constexpr int kFBiasBytes = 128 * 128 * 4;
+constexpr int kFKBytes = kFKT * 64;       // [64][32] bf16
+constexpr int kFVBox = 32 * 128;          // the TMA box of the value tile: 32 rows x 64 keys
+constexpr int kFVBytes = 48 * 128;        // shared footprint (48 operand rows: 32 d, ones, 15 zero)
+constexpr int kFStageBytes = kFKBytes + kFVBytes;
+constexpr int kFBiasBytes = 128 * kFKT * 4;
 constexpr int kFON = 48;                  // columns of an O accumulator (32 d + denominator + pad)
 constexpr uint32_t kFCols = 512;
 constexpr float kRescaleGap = 8.0f;
+constexpr int kFThreads = 32 * (4 * kFRows + kFRows);
 
 struct FlashBars {
-  uint64_t q_full, kv_full[kFStages], kv_empty[kFStages], bias_full[2], bias_empty[2], s_full[2], p_ready[2], o_done;
+  uint64_t q_full[kFRows], kv_full[kFRows][kFStages], kv_empty[kFRows][kFStages], bias_full[2], bias_empty[2],
+      s_full[kFRows], p_ready[kFRows], o_done[kFRows];
   uint32_t tmem_base;
 };
 
 struct FlashLayout {
   static constexpr int q = 0;
   static constexpr int kv = q + kFRows * kFQBytes;
-  static constexpr int bias = kv + kFStages * kFStageBytes;
+  static constexpr int bias = kv + kFRows * kFStages * kFStageBytes;
   static constexpr int bars = bias + 2 * kFBiasBytes;
   static constexpr int total = bars + (int)sizeof(FlashBars);
 };
 
-__global__ void __launch_bounds__(320, 1)
+#ifdef PX_FLASH_TRACE
+// Timeline probe (debug builds only): CTA (0,0,0) records clock64 stamps of its pipeline phases.
+__device__ long long g_flash_trace[4096];
+#define PX_TRACE(slot, idx) \
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (idx) < 64) g_flash_trace[(slot) * 64 + (idx)] = clock64();
+#else
+#define PX_TRACE(slot, idx)
+#endif
+
+__device__ __forceinline__ void add2(float& a0, float& a1, float b0, float b1) {
+  uint64_t x, y;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(x) : "f"(a0), "f"(a1));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(y) : "f"(b0), "f"(b1));
+  asm("add.rn.f32x2 %0, %0, %1;" : "+l"(x) : "l"(y));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(x));
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+__global__ void __launch_bounds__(kFThreads, 1)
 triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_b,
-                       const float* __restrict__ mb, const unsigned char* __restrict__ tile_masked,
+                       const float* __restrict__ mb, const unsigned long long* __restrict__ tile_masked,
                        bf16* __restrict__ o, int n_u, int n, int ldm, int nkt) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   FlashBars& bars = *reinterpret_cast<FlashBars*>(sm + FlashLayout::bars);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q0 = blockIdx.x * 128, h = blockIdx.y, u0 = blockIdx.z * kFRows;
-  const int n_items = nkt * kFRows;
 
   if (threadIdx.x == 0) {
-    mbar_init(&bars.q_full, 1);
-    for (int s = 0; s < kFStages; ++s) {
-      mbar_init(&bars.kv_full[s], 1);
-      mbar_init(&bars.kv_empty[s], 1);
-    }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars.bias_full[b], 1);
-      mbar_init(&bars.bias_empty[b], 8);
-      mbar_init(&bars.s_full[b], 1);
-      mbar_init(&bars.p_ready[b], 4);
+      mbar_init(&bars.bias_empty[b], 4 * kFRows);
     }
-    mbar_init(&bars.o_done, 1);
+    for (int g = 0; g < kFRows; ++g) {
+      mbar_init(&bars.q_full[g], 1);
+      for (int s = 0; s < kFStages; ++s) {
+        mbar_init(&bars.kv_full[g][s], 1);
+        mbar_init(&bars.kv_empty[g][s], 1);
+      }
+      mbar_init(&bars.s_full[g], 1);
+      mbar_init(&bars.p_ready[g], 4);
+      mbar_init(&bars.o_done[g], 1);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  // operand rows 32..47 of every value half-tile: row 32 = ones (denominator column), the rest zero.  The
-  // TMA boxes only ever write rows 0..31.  Rows 32..39 are one 8-row swizzle group; row 32 is its row 0,
-  // whose 16-byte pieces are not permuted.
-  for (int i = threadIdx.x; i < kFStages * 2 * (16 * 128 / 16); i += blockDim.x) {
-    const int half = i / 128, piece = i % 128;                    // 128 pieces of 16 bytes per 16 rows
-    const int stage = half >> 1, sub = half & 1;
+  // operand rows 32..47 of every value tile: row 32 = ones (denominator column), the rest zero.  The TMA
+  // box only ever writes rows 0..31.  Rows 32..39 are one 8-row swizzle group; row 32 is its row 0, whose
+  // 16-byte pieces are not permuted.
+  for (int i = threadIdx.x; i < kFRows * kFStages * 128; i += blockDim.x) {
+    const int stage = i / 128, piece = i % 128;                   // 128 pieces of 16 bytes per 16 rows
     uint4 v = (piece < 8) ? make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u) : make_uint4(0, 0, 0, 0);
-    *reinterpret_cast<uint4*>(sm + FlashLayout::kv + stage * kFStageBytes + kFKBytes + sub * kFVSub + 32 * 128 +
-                              piece * 16) = v;
+    *reinterpret_cast<uint4*>(sm + FlashLayout::kv + stage * kFStageBytes + kFKBytes + 32 * 128 + piece * 16) = v;
   }
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy writes above -> MMA reads
-  if (warp == 8) {
+  if (warp == 4 * kFRows) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&bars.tmem_base)),
                  "r"(kFCols)
                  : "memory");
@@ -99,183 +124,201 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars.tmem_base;
-  // TMEM columns: S/P buffer g at 128*g, O accumulator of row r at 256 + 48*r
+  // TMEM columns: S/P buffer of group g at 64*g, O accumulator of row r at 256 + 48*r
 
-  if (warp == 8) {
-    // ------------------------------------------------------------------ TMA producer
+  if (warp >= 4 * kFRows) {
+    // ------------------------------------------------------------------ control thread of group g
+    // the control warpgroup hands most of its registers to the softmax warpgroups
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 24;\n");
+    const int g = warp - 4 * kFRows;
     if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, kFKT), idesc_o = umma_idesc_bf16(128, kFON);
+      constexpr int kAhead = kFStages - 1;          // key tiles in flight ahead of the one being consumed
+      const int uh = (u0 + g) * kFH + h;            // rows past n_u: coordinate beyond the tensor -> zero fill
+      const uint32_t q_addr = smem_u32(sm + FlashLayout::q + g * kFQBytes);
+      const uint32_t ring = smem_u32(sm + FlashLayout::kv + g * kFStages * kFStageBytes);
+      const uint32_t d_s = tmem_base + kFKT * g, d_o = tmem_base + 256 + kFON * g;
       bool ok = true;
-      mbar_expect_tx(&bars.q_full, kFRows * kFQBytes);
-      for (int r = 0; r < kFRows; ++r)  // rows past n_u: coordinate beyond the tensor -> zero fill
-        tma_load_3d(smem_u32(sm + FlashLayout::q + r * kFQBytes), &map_q, &bars.q_full, 0, q0, (u0 + r) * kFH + h);
-      for (int i = 0; i < n_items && ok; ++i) {
-        const int kt = i / kFRows, r = i % kFRows;
-        if (r == 0) {
-          const int b = kt & 1;
-          ok = mbar_wait(&bars.bias_empty[b], ((kt >> 1) & 1) ^ 1, 1u);
-          if (!ok) break;
-          mbar_expect_tx(&bars.bias_full[b], kFBiasBytes);
-          for (int c = 0; c < 4; ++c)
-            tma_load_3d(smem_u32(sm + FlashLayout::bias + b * kFBiasBytes + c * (128 * 128)), &map_b,
-                        &bars.bias_full[b], kt * 128 + c * 32, q0, h);
-        }
-        const int s = i % kFStages;
-        ok = mbar_wait(&bars.kv_empty[s], ((i / kFStages) & 1) ^ 1, 2u);
-        if (!ok) break;
-        mbar_expect_tx(&bars.kv_full[s], kFKBytes + 2 * kFVBox);
-        const uint32_t base = smem_u32(sm + FlashLayout::kv + s * kFStageBytes);
-        const int uh = (u0 + r) * kFH + h;
-        tma_load_3d(base, &map_k, &bars.kv_full[s], 0, kt * 128, uh);
-        tma_load_3d(base + kFKBytes, &map_v, &bars.kv_full[s], kt * 128, 0, uh);
-        tma_load_3d(base + kFKBytes + kFVSub, &map_v, &bars.kv_full[s], kt * 128 + 64, 0, uh);
-      }
-    }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128), idesc_o = umma_idesc_bf16(128, kFON);
-      bool ok = mbar_wait(&bars.q_full, 0, 4u);
-      auto issue_s = [&](int i) -> bool {  // S(i) = Q_r K^T into buffer (i & 1)
-        const int s = i % kFStages, r = i % kFRows;
-        if (!mbar_wait(&bars.kv_full[s], (i / kFStages) & 1, 8u)) return false;
-        tc_fence_after();
-        const uint64_t dq = umma_desc_sw64(smem_u32(sm + FlashLayout::q + r * kFQBytes));
-        const uint64_t dk = umma_desc_sw64(smem_u32(sm + FlashLayout::kv + s * kFStageBytes));
-        umma_bf16(tmem_base + 128 * (i & 1), dq, dk, idesc_s, 0u);
-        umma_bf16(tmem_base + 128 * (i & 1), dq + 2, dk + 2, idesc_s, 1u);
-        umma_commit(&bars.s_full[i & 1]);
+      auto load_kv = [&](int kt) {                  // K and V tiles of key tile kt into stage kt % kFStages
+        const int s = kt % kFStages;
+        if (!mbar_wait(&bars.kv_empty[g][s], ((kt / kFStages) & 1) ^ 1, 2u)) return false;
+        mbar_expect_tx(&bars.kv_full[g][s], kFKBytes + kFVBox);
+        tma_load_3d(ring + s * kFStageBytes, &map_k, &bars.kv_full[g][s], 0, kt * kFKT, uh);
+        tma_load_3d(ring + s * kFStageBytes + kFKBytes, &map_v, &bars.kv_full[g][s], kt * kFKT, 0, uh);
         return true;
       };
-      if (ok && n_items > 0) ok = issue_s(0);
-      if (ok && n_items > 1) ok = issue_s(1);
-      for (int i = 0; i < n_items && ok; ++i) {
-        const int g = i & 1, s = i % kFStages, kt = i / kFRows, r = i % kFRows;
-        ok = mbar_wait(&bars.p_ready[g], (i >> 1) & 1, 16u);
+      auto load_bias = [&](int kt) {                // group 0 only: the bias tile all four rows share
+        const int b = kt & 1;
+        if (!mbar_wait(&bars.bias_empty[b], ((kt >> 1) & 1) ^ 1, 1u)) return false;
+        mbar_expect_tx(&bars.bias_full[b], kFBiasBytes);
+        for (int c = 0; c < kFKT / 32; ++c)
+          tma_load_3d(smem_u32(sm + FlashLayout::bias + b * kFBiasBytes + c * (128 * 128)), &map_b, &bars.bias_full[b],
+                      kt * kFKT + c * 32, q0, h);
+        return true;
+      };
+      mbar_expect_tx(&bars.q_full[g], kFQBytes);
+      tma_load_3d(q_addr, &map_q, &bars.q_full[g], 0, q0, uh);
+      if (g == 0) {
+        ok = load_bias(0);
+        if (ok && nkt > 1) ok = load_bias(1);
+      }
+      for (int kt = 0; kt < kAhead && kt < nkt && ok; ++kt) ok = load_kv(kt);
+      ok = ok && mbar_wait(&bars.q_full[g], 0, 4u);
+      const uint64_t dq = umma_desc_sw64(q_addr);
+      for (int kt = 0; kt < nkt && ok; ++kt) {
+        const int s = kt % kFStages;
+        PX_TRACE(8 + g, kt);
+        ok = mbar_wait(&bars.kv_full[g][s], (kt / kFStages) & 1, 8u);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t vbase = smem_u32(sm + FlashLayout::kv + s * kFStageBytes + kFKBytes);
-        const uint32_t d_o = tmem_base + 256 + kFON * r, a_p = tmem_base + 128 * g;
+        const uint64_t dk = umma_desc_sw64(ring + s * kFStageBytes);
+        umma_bf16(d_s, dq, dk, idesc_s, 0u);
+        umma_bf16(d_s, dq + 2, dk + 2, idesc_s, 1u);
+        umma_commit(&bars.s_full[g]);
+        PX_TRACE(12 + g, kt);
+        // while the group works on this tile: refill the ring (and the shared bias ring)
+        if (kt + kAhead < nkt) ok = load_kv(kt + kAhead);
+        if (ok && g == 0 && kt >= 1 && kt + 1 < nkt) ok = load_bias(kt + 1);
+        if (!ok) break;
+        ok = mbar_wait(&bars.p_ready[g], kt & 1, 16u);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t dv = umma_desc_sw128(ring + s * kFStageBytes + kFKBytes);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {  // 16 keys per step: 8 TMEM columns of P, 32 bytes of the value rows
-          const uint64_t dv = umma_desc_sw128(vbase + (ks >> 2) * kFVSub) + 2 * (ks & 3);
-          umma_bf16_ts(d_o, a_p + 8 * ks, dv, idesc_o, (kt | ks) ? 1u : 0u);
-        }
-        umma_commit(&bars.kv_empty[s]);
-        if (i + 2 < n_items) ok = issue_s(i + 2);
+        for (int ks = 0; ks < kFKT / 16; ++ks)  // 16 keys per step: 8 TMEM columns of P, 32 bytes of the value rows
+          umma_bf16_ts(d_o, d_s + 8 * ks, dv + 2 * ks, idesc_o, (kt | ks) ? 1u : 0u);
+        umma_commit(&bars.kv_empty[g][s]);
       }
-      if (ok) umma_commit(&bars.o_done);
+      if (ok) umma_commit(&bars.o_done[g]);
     }
   } else {
     // ------------------------------------------------------------------ softmax groups
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 112;\n");
     const int g = warp >> 2, qw = warp & 3;
     const int row = 32 * qw + lane;                 // query row inside the tile = TMEM lane
     const uint32_t lane_addr = (uint32_t)(32 * qw) << 16;
-    const uint32_t t_s = tmem_base + lane_addr + 128 * g;
-    float m_ref[2] = {-CUDART_INF_F, -CUDART_INF_F};
+    const uint32_t t_s = tmem_base + lane_addr + kFKT * g;
+    const uint32_t t_o = tmem_base + lane_addr + 256 + kFON * g;
+    const int u = u0 + g;
+    const bool urow = u < n_u;
+    const float* mrow_base = mb + (size_t)(urow ? u : 0) * ldm;
+    // one bit per 64-key tile: does the tile carry any non-zero mask bias for this row?
+    const unsigned long long* flag_row = tile_masked + (size_t)(urow ? u : 0) * ((nkt + 63) / 64);
+    unsigned long long flag_word = 0;
+    float m_ref = -CUDART_INF_F;
     bool ok = true;
     for (int kt = 0; kt < nkt && ok; ++kt) {
+      if ((kt & 63) == 0) flag_word = urow ? __ldg(flag_row + (kt >> 6)) : ~0ull;
+      ok = mbar_wait(&bars.bias_full[kt & 1], (kt >> 1) & 1, 32u);
+      if (qw == 0) { PX_TRACE(16 * g + 0 + (g ? 0 : 0), kt); }
+      ok = ok && mbar_wait(&bars.s_full[g], kt & 1, 64u);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (qw == 0) { PX_TRACE(16 * g + 1, kt); }
+      tc_fence_after();
+      uint32_t t[kFKT];
+      {
+        uint32_t(&t0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&t[0]);
+        uint32_t(&t1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&t[32]);
+        tmem_ld32(t_s, t0);
+        tmem_ld32(t_s + 32, t1);
+        tmem_wait_ld();
+      }
+      if (qw == 0) { PX_TRACE(16 * g + 2, kt); }
+      float s[kFKT];
       const float* bias_tile = reinterpret_cast<const float*>(sm + FlashLayout::bias + (kt & 1) * kFBiasBytes);
-      for (int rr = 0; rr < 2 && ok; ++rr) {
-        const int r = 2 * rr + g;                   // row of this item inside the CTA's group of four
-        const int j = 2 * kt + rr;                  // this group's item counter
-        if (rr == 0) ok = mbar_wait(&bars.bias_full[kt & 1], (kt >> 1) & 1, 32u);
-        ok = ok && mbar_wait(&bars.s_full[g], j & 1, 64u);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-        float s[128];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t t[32];
-          tmem_ld32(t_s + 32 * c, t);
-          tmem_wait_ld();
-          // bias: box c holds columns 32c..32c+31 of all 128 rows, 128-byte rows, 16-byte pieces swizzled
-          const float* brow = bias_tile + c * (128 * 32) + row * 32;
+      for (int c = 0; c < kFKT / 32; ++c) {
+        // box c holds columns 32c..32c+31 of all 128 rows: 128-byte rows, 16-byte pieces swizzled by row
+        const float* brow = bias_tile + c * (128 * 32) + row * 32;
 #pragma unroll
-          for (int p = 0; p < 8; ++p) {
-            const float4 b4 = *reinterpret_cast<const float4*>(brow + ((p ^ (row & 7)) << 2));
-            s[32 * c + 4 * p + 0] = __uint_as_float(t[4 * p + 0]) + b4.x;
-            s[32 * c + 4 * p + 1] = __uint_as_float(t[4 * p + 1]) + b4.y;
-            s[32 * c + 4 * p + 2] = __uint_as_float(t[4 * p + 2]) + b4.z;
-            s[32 * c + 4 * p + 3] = __uint_as_float(t[4 * p + 3]) + b4.w;
-          }
-        }
-        const int u = u0 + r;
-        const bool urow = u < n_u;
-        if (!urow || tile_masked[(size_t)(urow ? u : 0) * nkt + kt]) {   // warp-uniform
-          const float* mrow = mb + (size_t)(urow ? u : 0) * ldm + kt * 128;
-#pragma unroll
-          for (int c4 = 0; c4 < 32; ++c4) {
-            const float4 m4 = __ldg(reinterpret_cast<const float4*>(mrow) + c4);
-            s[4 * c4 + 0] += m4.x;
-            s[4 * c4 + 1] += m4.y;
-            s[4 * c4 + 2] += m4.z;
-            s[4 * c4 + 3] += m4.w;
-          }
-        }
-        float mt = s[0];
-#pragma unroll
-        for (int c = 1; c < 128; ++c) mt = fmaxf(mt, s[c]);
-        if (kt == 0) {
-          m_ref[rr] = mt;                           // first tile: the P.V product overwrites O
-        } else if (__any_sync(0xffffffffu, mt > m_ref[rr] + kRescaleGap)) {
-          const float m_new = (mt > m_ref[rr] + kRescaleGap) ? mt : m_ref[rr];
-          const float alpha = fast_exp2(m_ref[rr] - m_new);
-          m_ref[rr] = m_new;
-          const uint32_t t_o = tmem_base + lane_addr + 256 + kFON * r;
-          uint32_t a[32], b[16];
-          tmem_ld32(t_o, a);
-          tmem_ld16(t_o + 32, b);
-          tmem_wait_ld();
-#pragma unroll
-          for (int c = 0; c < 32; ++c) a[c] = __float_as_uint(__uint_as_float(a[c]) * alpha);
-#pragma unroll
-          for (int c = 0; c < 16; ++c) b[c] = __float_as_uint(__uint_as_float(b[c]) * alpha);
-          tmem_st32(t_o, a);
-          tmem_st16(t_o + 32, b);
-        }
-        const float mr = m_ref[rr];
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t w[32];
-#pragma unroll
-          for (int e = 0; e < 32; ++e) w[e] = exp2_bf16x2(s[64 * c + 2 * e] - mr, s[64 * c + 2 * e + 1] - mr);
-          tmem_st32(t_s + 32 * c, w);               // P overwrites the first 64 columns of S
-        }
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(&bars.p_ready[g]);
-          if (rr == 1) mbar_arrive(&bars.bias_empty[kt & 1]);
+        for (int p = 0; p < 8; ++p) {
+          const float4 b4 = *reinterpret_cast<const float4*>(brow + ((p ^ (row & 7)) << 2));
+          float x0 = __uint_as_float(t[32 * c + 4 * p + 0]), x1 = __uint_as_float(t[32 * c + 4 * p + 1]);
+          float x2 = __uint_as_float(t[32 * c + 4 * p + 2]), x3 = __uint_as_float(t[32 * c + 4 * p + 3]);
+          add2(x0, x1, b4.x, b4.y);
+          add2(x2, x3, b4.z, b4.w);
+          s[32 * c + 4 * p + 0] = x0;
+          s[32 * c + 4 * p + 1] = x1;
+          s[32 * c + 4 * p + 2] = x2;
+          s[32 * c + 4 * p + 3] = x3;
         }
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars.bias_empty[kt & 1]);       // this warp is done with the bias tile
+      if ((flag_word >> (kt & 63)) & 1ull) {                      // warp-uniform
+        const float4* mrow = reinterpret_cast<const float4*>(mrow_base + kt * kFKT);
+#pragma unroll
+        for (int c4 = 0; c4 < kFKT / 4; ++c4) {
+          const float4 m4 = __ldg(mrow + c4);
+          add2(s[4 * c4 + 0], s[4 * c4 + 1], m4.x, m4.y);
+          add2(s[4 * c4 + 2], s[4 * c4 + 3], m4.z, m4.w);
+        }
+      }
+      if (qw == 0) { PX_TRACE(16 * g + 3, kt); }
+      float mt = max3(s[0], s[1], s[2]);
+#pragma unroll
+      for (int c = 3; c + 1 < kFKT; c += 2) mt = max3(mt, s[c], s[c + 1]);
+      mt = fmaxf(mt, s[kFKT - 1]);
+      if (kt == 0) {
+        m_ref = mt;                                 // first tile: the P.V product overwrites O
+      } else if (__any_sync(0xffffffffu, mt > m_ref + kRescaleGap)) {
+        const float m_new = (mt > m_ref + kRescaleGap) ? mt : m_ref;
+        const float alpha = fast_exp2(m_ref - m_new);
+        m_ref = m_new;
+        uint32_t a[32], b[16];
+        tmem_ld32(t_o, a);
+        tmem_ld16(t_o + 32, b);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) a[c] = __float_as_uint(__uint_as_float(a[c]) * alpha);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) b[c] = __float_as_uint(__uint_as_float(b[c]) * alpha);
+        tmem_st32(t_o, a);
+        tmem_st16(t_o + 32, b);
+      }
+      {
+        const float nm = -m_ref;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {            // P overwrites the first 32 columns of S
+          uint32_t w[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            float x0 = s[32 * hf + 2 * e], x1 = s[32 * hf + 2 * e + 1];
+            add2(x0, x1, nm, nm);
+            w[e] = exp2_bf16x2(x0, x1);
+          }
+          tmem_st16(t_s + 16 * hf, w);
+        }
+      }
+      if (qw == 0) { PX_TRACE(16 * g + 4, kt); }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars.p_ready[g]);
+      if (qw == 0) { PX_TRACE(16 * g + 5, kt); }
     }
-    // ---- epilogue: o = O / denominator for this group's two rows
-    ok = ok && mbar_wait(&bars.o_done, 0, 128u);
+    // ---- epilogue: o = O / denominator for this group's row
+    ok = ok && mbar_wait(&bars.o_done[g], 0, 128u);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();
       const int qi = q0 + row;
-      for (int rr = 0; rr < 2; ++rr) {
-        const int r = 2 * rr + g, u = u0 + r;
-        uint32_t a[32], b[16];
-        const uint32_t t_o = tmem_base + lane_addr + 256 + kFON * r;
-        tmem_ld32(t_o, a);
-        tmem_ld16(t_o + 32, b);
-        tmem_wait_ld();
-        if (u < n_u && qi < n) {
-          const float inv = 1.0f / __uint_as_float(b[0]);
-          bf16* dst = o + ((size_t)u * n + qi) * kC + h * kFD;
+      uint32_t a[32], b[16];
+      tmem_ld32(t_o, a);
+      tmem_ld16(t_o + 32, b);
+      tmem_wait_ld();
+      if (urow && qi < n) {
+        const float inv = 1.0f / __uint_as_float(b[0]);
+        bf16* dst = o + ((size_t)u * n + qi) * kC + h * kFD;
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 pk;
-            pk.x = pack_bf16x2(__uint_as_float(a[8 * v + 0]) * inv, __uint_as_float(a[8 * v + 1]) * inv);
-            pk.y = pack_bf16x2(__uint_as_float(a[8 * v + 2]) * inv, __uint_as_float(a[8 * v + 3]) * inv);
-            pk.z = pack_bf16x2(__uint_as_float(a[8 * v + 4]) * inv, __uint_as_float(a[8 * v + 5]) * inv);
-            pk.w = pack_bf16x2(__uint_as_float(a[8 * v + 6]) * inv, __uint_as_float(a[8 * v + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + 8 * v) = pk;
-          }
+        for (int v = 0; v < 4; ++v) {
+          uint4 pk;
+          pk.x = pack_bf16x2(__uint_as_float(a[8 * v + 0]) * inv, __uint_as_float(a[8 * v + 1]) * inv);
+          pk.y = pack_bf16x2(__uint_as_float(a[8 * v + 2]) * inv, __uint_as_float(a[8 * v + 3]) * inv);
+          pk.z = pack_bf16x2(__uint_as_float(a[8 * v + 4]) * inv, __uint_as_float(a[8 * v + 5]) * inv);
+          pk.w = pack_bf16x2(__uint_as_float(a[8 * v + 6]) * inv, __uint_as_float(a[8 * v + 7]) * inv);
+          *reinterpret_cast<uint4*>(dst + 8 * v) = pk;
         }
       }
     }
@@ -289,20 +332,38 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     __syncthreads();
   }
-  if (warp == 8) {
+  if (warp == 4 * kFRows) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kFCols) : "memory");
   }
 }
 
-// tile_masked[u][kt] = 1 when any key of the 128-key tile kt carries a non-zero mask bias for row u
-__global__ void flash_tile_flags_kernel(const float* __restrict__ mb, unsigned char* __restrict__ flags, int n_u, int ldm,
+// Bit (kt & 63) of flags[u][kt >> 6] is set when any key of the 64-key tile kt carries a non-zero mask bias
+// for row u.  One CTA per (u, word); each warp handles tiles warp, warp + 4, ...
+__global__ void flash_tile_flags_kernel(const float* __restrict__ mb, unsigned long long* __restrict__ flags, int ldm,
                                         int nkt) {
-  const int u = blockIdx.x, kt = blockIdx.y;
-  const float v = mb[(size_t)u * ldm + kt * 128 + threadIdx.x];
-  const int any = __syncthreads_or(v != 0.0f);
-  if (threadIdx.x == 0) flags[(size_t)u * nkt + kt] = (unsigned char)(any ? 1 : 0);
+  __shared__ unsigned long long word;
+  const int u = blockIdx.x, w = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) word = 0ull;
+  __syncthreads();
+  for (int t = warp; t < 64; t += 4) {
+    const int kt = 64 * w + t;
+    if (kt >= nkt) break;
+    const float* p = mb + (size_t)u * ldm + kt * kFKT;
+    const bool any = __any_sync(0xffffffffu, p[lane] != 0.0f || p[lane + 32] != 0.0f);
+    if (any && lane == 0) atomicOr(&word, 1ull << t);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) flags[(size_t)u * gridDim.y + w] = word;
 }
+
+#ifdef PX_FLASH_TRACE
+}  // namespace px
+extern "C" __attribute__((visibility("default"))) int px_debug_flash_trace(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, px::g_flash_trace, sizeof(long long) * 4096);
+}
+namespace px {
+#endif
 
 unsigned int flash_error_flags() {
   unsigned int v = 0;
@@ -317,7 +378,7 @@ extern "C" int64_t px_ld_mask(int64_t n) { return (n + 127) / 128 * 128; }
 
 extern "C" int64_t px_triatt_flash_scratch_bytes(int64_t n_u, int64_t n) {
   if (n_u <= 0 || n <= 0) return 0;
-  return (n_u * ((n + 127) / 128) + 255) / 256 * 256;
+  return (n_u * ((((n + kFKT - 1) / kFKT) + 63) / 64) * 8 + 255) / 256 * 256;
 }
 
 extern "C" int32_t px_triatt_flash(const px_bf16* q, const px_bf16* k, const px_bf16* v, const float* bias,
@@ -329,14 +390,14 @@ extern "C" int32_t px_triatt_flash(const px_bf16* q, const px_bf16* k, const px_
   if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)bias | (uintptr_t)mask_bias | (uintptr_t)o) & 15)
     return PX_ERR_BAD_ARG;
   const int64_t ldt = px_ld(n);
-  const int nkt = (int)((n + 127) / 128);
+  const int nkt = (int)((n + kFKT - 1) / kFKT);
   CUtensorMap mq, mk, mv, mbias;
   const uint64_t uh = (uint64_t)n_u * kFH;
   // q, k: [n_u*4][n][32] bf16, box [1][128][32], 64-byte swizzle
   if (!make_map_3d(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, q, kFD, (uint64_t)n, uh, kFD * 2, (uint64_t)n * kFD * 2, kFD,
                    128, CU_TENSOR_MAP_SWIZZLE_64B) ||
       !make_map_3d(&mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, k, kFD, (uint64_t)n, uh, kFD * 2, (uint64_t)n * kFD * 2, kFD,
-                   128, CU_TENSOR_MAP_SWIZZLE_64B) ||
+                   kFKT, CU_TENSOR_MAP_SWIZZLE_64B) ||
       // v (transposed): [n_u*4][32][n keys, row stride ldt] bf16, box [1][32][64], 128-byte swizzle
       !make_map_3d(&mv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, v, (uint64_t)n, kFD, uh, (uint64_t)ldt * 2,
                    (uint64_t)kFD * ldt * 2, 64, kFD, CU_TENSOR_MAP_SWIZZLE_128B) ||
@@ -345,14 +406,15 @@ extern "C" int32_t px_triatt_flash(const px_bf16* q, const px_bf16* k, const px_
                    (uint64_t)n * ldm * 4, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B))
     return PX_ERR_LAUNCH;
   cudaStream_t st = (cudaStream_t)stream;
-  flash_tile_flags_kernel<<<dim3((unsigned)n_u, (unsigned)nkt), 128, 0, st>>>(mask_bias, (unsigned char*)scratch,
-                                                                                (int)n_u, (int)ldm, nkt);
+  if ((uintptr_t)scratch & 7) return PX_ERR_BAD_ARG;
+  flash_tile_flags_kernel<<<dim3((unsigned)n_u, (unsigned)((nkt + 63) / 64)), 128, 0, st>>>(
+      mask_bias, (unsigned long long*)scratch, (int)ldm, nkt);
   const size_t smem = FlashLayout::total + 1024;
   if (cudaFuncSetAttribute(triatt_flash_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
     return PX_ERR_LAUNCH;
   dim3 grid((unsigned)((n + 127) / 128), kFH, (unsigned)((n_u + kFRows - 1) / kFRows));
-  triatt_flash_tc_kernel<<<grid, 320, smem, st>>>(mq, mk, mv, mbias, mask_bias, (const unsigned char*)scratch, (bf16*)o,
+  triatt_flash_tc_kernel<<<grid, kFThreads, smem, st>>>(mq, mk, mv, mbias, mask_bias, (const unsigned long long*)scratch, (bf16*)o,
                                                   (int)n_u, (int)n, (int)ldm, nkt);
   return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
 }

@@ -26,10 +26,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
   const long long t0 = clock64();
   for (;;) {
     uint32_t done;
+    // the hardware suspends the thread until the phase completes or the hint (in ns) runs out, so a waiting
+    // warp does not spend issue slots on polling
     asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.b32 %0, 1, 0, p;\n}\n"
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.b32 %0, 1, 0, p;\n}\n"
         : "=r"(done)
-        : "r"(addr), "r"(parity)
+        : "r"(addr), "r"(parity), "r"(1000000u)
         : "memory");
     if (done) return true;
     if (clock64() - t0 > kWaitCycles) {
