@@ -2,24 +2,24 @@
 //
 //   o[u][q][h*32+d] = softmax_k( q[u,h,q,:] . k[u,h,k,:] + bias[h][q][k] + mask_bias[u][k] ) v[u,h,k,d]
 //
-// One CTA = (head h, 128 queries, 4 attended rows u), 20 warps:
-//   warps 0..15   four softmax groups of four warps; group g owns row u0+g, each thread one query row
-//   warps 16..19  one control thread per group (tcgen05 and TMA instructions cost ~100 cycles of issue
-//                 each, so one issuing thread for all four groups would be the bottleneck).  It loads the
+// One CTA = (head h, 128 queries, 3 attended rows u), 16 warps:
+//   warps 0..11   three softmax groups of four warps; group g owns row u0+g, each thread one query row
+//   warps 12..14  one control thread per group (tcgen05 and TMA instructions cost ~100 cycles of issue
+//                 each, so one issuing thread for all groups would be the bottleneck).  It loads the
 //                 group's Q tile once and, per 64-key tile, a K tile [64 keys][32] (64-byte swizzle) and a
 //                 transposed V tile [32 d][64 keys] (128-byte swizzle) into the group's 3-stage ring;
-//                 issues S = Q K^T (M=128, N=64, K=32) into the group's TMEM buffer; and, once the group
-//                 has turned S into P (bf16, written back over S in TMEM), issues O_u += P V with P as the
+//                 issues S = Q K^T (M=128, N=64, K=32) into the group's S buffer in tensor memory; and,
+//                 once the group has written P (bf16) into its P buffer, issues O_u += P V with P as the
 //                 TMEM-resident A operand (M=128, N=48, K=64).  Row 32 of the value operand is all ones, so
-//                 column 32 of O_u accumulates the softmax denominators.  The control thread of group 0 also
-//                 loads the pair-bias tile [128 q][64 k] fp32 (two 128-byte-swizzled boxes, 2-deep ring)
-//                 that all four rows share.
-// While one group is busy with exponentials the tensor core serves the other three.
+//                 column 32 of O_u accumulates the softmax denominators.  S of the next key tile is issued
+//                 as soon as the group has pulled the current S into registers, so it is ready when the
+//                 group comes back.  The control thread of group 0 also loads the pair-bias tile
+//                 [128 q][64 k] fp32 (two 128-byte-swizzled boxes, 2-deep ring) shared by the three rows.
+//   warp 15       idle (completes the control warpgroup, which hands its registers to the softmax groups)
 //
 // Softmax is online in base 2 with a lazy reference maximum: the reference only moves (and O_u is rescaled
 // through TMEM) when the tile maximum exceeds it by more than 8, so probabilities stay below 2^8.
-// Exponentials use the packed bf16 ex2 (P feeds a bf16 MMA anyway); adds run as packed f32x2 and the row
-// maximum as 3-input max.  Every mbarrier wait is bounded.
+// Exponentials are fp32 ex2; P is their truncation to bf16.  Every mbarrier wait is bounded.
 #include <math_constants.h>
 
 #include "px_tcgen05.cuh"
@@ -27,7 +27,7 @@
 namespace px {
 
 constexpr int kFH = 4, kFD = 32;
-constexpr int kFRows = 4;                 // attended rows per CTA = softmax groups
+constexpr int kFRows = 3;                 // attended rows per CTA = softmax groups
 constexpr int kFKT = 64;                  // keys per work item
 constexpr int kFStages = 3;               // K/V ring of each group
 constexpr int kFQBytes = 128 * 64;        // [128][32] bf16
@@ -38,12 +38,14 @@ constexpr int kFStageBytes = kFKBytes + kFVBytes;
 constexpr int kFBiasBytes = 128 * kFKT * 4;
 constexpr int kFON = 48;                  // columns of an O accumulator (32 d + denominator + pad)
 constexpr uint32_t kFCols = 512;
+constexpr int kFColS = 0, kFColP = kFRows * kFKT, kFColO = kFColP + kFRows * (kFKT / 2);  // TMEM column map
 constexpr float kRescaleGap = 8.0f;
-constexpr int kFThreads = 32 * (4 * kFRows + kFRows);
+constexpr int kFThreads = 32 * 16;
+static_assert(kFColO + kFRows * kFON <= 512, "tensor memory budget");
 
 struct FlashBars {
-  uint64_t q_full[kFRows], kv_full[kFRows][kFStages], kv_empty[kFRows][kFStages], bias_full[2], bias_empty[2],
-      s_full[kFRows], p_ready[kFRows], o_done[kFRows];
+  uint64_t q_full[kFRows], kv_full[kFRows][kFStages], bias_full[2], bias_empty[2], s_full[kFRows], s_free[kFRows],
+      p_ready[kFRows], pv_done[kFRows];
   uint32_t tmem_base;
 };
 
@@ -54,6 +56,7 @@ struct FlashLayout {
   static constexpr int bars = bias + 2 * kFBiasBytes;
   static constexpr int total = bars + (int)sizeof(FlashBars);
 };
+static_assert(FlashLayout::kv % 1024 == 0 && FlashLayout::bias % 1024 == 0 && kFStageBytes % 1024 == 0, "swizzle alignment");
 
 #ifdef PX_FLASH_TRACE
 // Timeline probe (debug builds only): CTA (0,0,0) records clock64 stamps of its pipeline phases.
@@ -64,13 +67,6 @@ __device__ long long g_flash_trace[4096];
 #define PX_TRACE(slot, idx)
 #endif
 
-__device__ __forceinline__ void add2(float& a0, float& a1, float b0, float b1) {
-  uint64_t x, y;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(x) : "f"(a0), "f"(a1));
-  asm("mov.b64 %0, {%1, %2};" : "=l"(y) : "f"(b0), "f"(b1));
-  asm("add.rn.f32x2 %0, %0, %1;" : "+l"(x) : "l"(y));
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(x));
-}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -95,13 +91,11 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     for (int g = 0; g < kFRows; ++g) {
       mbar_init(&bars.q_full[g], 1);
-      for (int s = 0; s < kFStages; ++s) {
-        mbar_init(&bars.kv_full[g][s], 1);
-        mbar_init(&bars.kv_empty[g][s], 1);
-      }
+      for (int s = 0; s < kFStages; ++s) mbar_init(&bars.kv_full[g][s], 1);
       mbar_init(&bars.s_full[g], 1);
+      mbar_init(&bars.s_free[g], 4);
       mbar_init(&bars.p_ready[g], 4);
-      mbar_init(&bars.o_done[g], 1);
+      mbar_init(&bars.pv_done[g], 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -114,7 +108,7 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     *reinterpret_cast<uint4*>(sm + FlashLayout::kv + stage * kFStageBytes + kFKBytes + 32 * 128 + piece * 16) = v;
   }
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy writes above -> MMA reads
-  if (warp == 4 * kFRows) {
+  if (warp == 12) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&bars.tmem_base)),
                  "r"(kFCols)
                  : "memory");
@@ -124,30 +118,26 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars.tmem_base;
-  // TMEM columns: S/P buffer of group g at 64*g, O accumulator of row r at 256 + 48*r
 
-  if (warp >= 4 * kFRows) {
+  if (warp >= 12) {
     // ------------------------------------------------------------------ control thread of group g
-    // the control warpgroup hands most of its registers to the softmax warpgroups
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 24;\n");
-    const int g = warp - 4 * kFRows;
-    if (lane == 0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 24;\n");   // registers go to the softmax warpgroups
+    const int g = warp - 12;
+    if (g < kFRows && lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, kFKT), idesc_o = umma_idesc_bf16(128, kFON);
-      constexpr int kAhead = kFStages - 1;          // key tiles in flight ahead of the one being consumed
       const int uh = (u0 + g) * kFH + h;            // rows past n_u: coordinate beyond the tensor -> zero fill
       const uint32_t q_addr = smem_u32(sm + FlashLayout::q + g * kFQBytes);
       const uint32_t ring = smem_u32(sm + FlashLayout::kv + g * kFStages * kFStageBytes);
-      const uint32_t d_s = tmem_base + kFKT * g, d_o = tmem_base + 256 + kFON * g;
+      const uint32_t d_s = tmem_base + kFColS + kFKT * g, d_p = tmem_base + kFColP + (kFKT / 2) * g;
+      const uint32_t d_o = tmem_base + kFColO + kFON * g;
       bool ok = true;
       auto load_kv = [&](int kt) {                  // K and V tiles of key tile kt into stage kt % kFStages
         const int s = kt % kFStages;
-        if (!mbar_wait(&bars.kv_empty[g][s], ((kt / kFStages) & 1) ^ 1, 2u)) return false;
         mbar_expect_tx(&bars.kv_full[g][s], kFKBytes + kFVBox);
         tma_load_3d(ring + s * kFStageBytes, &map_k, &bars.kv_full[g][s], 0, kt * kFKT, uh);
         tma_load_3d(ring + s * kFStageBytes + kFKBytes, &map_v, &bars.kv_full[g][s], kt * kFKT, 0, uh);
-        return true;
       };
-      auto load_bias = [&](int kt) {                // group 0 only: the bias tile all four rows share
+      auto load_bias = [&](int kt) {                // group 0 only: the bias tile all rows share
         const int b = kt & 1;
         if (!mbar_wait(&bars.bias_empty[b], ((kt >> 1) & 1) ^ 1, 1u)) return false;
         mbar_expect_tx(&bars.bias_full[b], kFBiasBytes);
@@ -156,49 +146,58 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                       kt * kFKT + c * 32, q0, h);
         return true;
       };
+      auto issue_s = [&](int kt) {                  // S(kt) = Q K(kt)^T
+        const int s = kt % kFStages;
+        if (!mbar_wait(&bars.kv_full[g][s], (kt / kFStages) & 1, 8u)) return false;
+        tc_fence_after();
+        const uint64_t dq = umma_desc_sw64(q_addr), dk = umma_desc_sw64(ring + s * kFStageBytes);
+        umma_bf16(d_s, dq, dk, idesc_s, 0u);
+        umma_bf16(d_s, dq + 2, dk + 2, idesc_s, 1u);
+        umma_commit(&bars.s_full[g]);
+        return true;
+      };
       mbar_expect_tx(&bars.q_full[g], kFQBytes);
       tma_load_3d(q_addr, &map_q, &bars.q_full[g], 0, q0, uh);
       if (g == 0) {
         ok = load_bias(0);
         if (ok && nkt > 1) ok = load_bias(1);
       }
-      for (int kt = 0; kt < kAhead && kt < nkt && ok; ++kt) ok = load_kv(kt);
+      for (int kt = 0; kt < 2 && kt < nkt; ++kt) load_kv(kt);      // first use of these stages: nothing to wait for
       ok = ok && mbar_wait(&bars.q_full[g], 0, 4u);
-      const uint64_t dq = umma_desc_sw64(q_addr);
+      ok = ok && issue_s(0);
       for (int kt = 0; kt < nkt && ok; ++kt) {
-        const int s = kt % kFStages;
         PX_TRACE(8 + g, kt);
-        ok = mbar_wait(&bars.kv_full[g][s], (kt / kFStages) & 1, 8u);
-        if (!ok) break;
-        tc_fence_after();
-        const uint64_t dk = umma_desc_sw64(ring + s * kFStageBytes);
-        umma_bf16(d_s, dq, dk, idesc_s, 0u);
-        umma_bf16(d_s, dq + 2, dk + 2, idesc_s, 1u);
-        umma_commit(&bars.s_full[g]);
+        if (kt + 1 < nkt) {                         // next S as soon as the group holds the current one in registers
+          ok = mbar_wait(&bars.s_free[g], kt & 1, 2u) && issue_s(kt + 1);
+          if (!ok) break;
+        }
         PX_TRACE(12 + g, kt);
-        // while the group works on this tile: refill the ring (and the shared bias ring)
-        if (kt + kAhead < nkt) ok = load_kv(kt + kAhead);
-        if (ok && g == 0 && kt >= 1 && kt + 1 < nkt) ok = load_bias(kt + 1);
+        if (kt + 2 < nkt) {                         // refill: stage of tile kt+2 was last read by P.V of tile kt-1
+          if (kt >= 1) ok = mbar_wait(&bars.pv_done[g], (kt - 1) & 1, 32u);
+          if (!ok) break;
+          load_kv(kt + 2);
+        }
+        if (g == 0 && kt >= 1 && kt + 1 < nkt) ok = load_bias(kt + 1);
         if (!ok) break;
         ok = mbar_wait(&bars.p_ready[g], kt & 1, 16u);
         if (!ok) break;
         tc_fence_after();
-        const uint64_t dv = umma_desc_sw128(ring + s * kFStageBytes + kFKBytes);
+        const uint64_t dv = umma_desc_sw128(ring + (kt % kFStages) * kFStageBytes + kFKBytes);
 #pragma unroll
         for (int ks = 0; ks < kFKT / 16; ++ks)  // 16 keys per step: 8 TMEM columns of P, 32 bytes of the value rows
-          umma_bf16_ts(d_o, d_s + 8 * ks, dv + 2 * ks, idesc_o, (kt | ks) ? 1u : 0u);
-        umma_commit(&bars.kv_empty[g][s]);
+          umma_bf16_ts(d_o, d_p + 8 * ks, dv + 2 * ks, idesc_o, (kt | ks) ? 1u : 0u);
+        umma_commit(&bars.pv_done[g]);
       }
-      if (ok) umma_commit(&bars.o_done[g]);
     }
   } else {
     // ------------------------------------------------------------------ softmax groups
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 112;\n");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 160;\n");
     const int g = warp >> 2, qw = warp & 3;
     const int row = 32 * qw + lane;                 // query row inside the tile = TMEM lane
     const uint32_t lane_addr = (uint32_t)(32 * qw) << 16;
-    const uint32_t t_s = tmem_base + lane_addr + kFKT * g;
-    const uint32_t t_o = tmem_base + lane_addr + 256 + kFON * g;
+    const uint32_t t_s = tmem_base + lane_addr + kFColS + kFKT * g;
+    const uint32_t t_p = tmem_base + lane_addr + kFColP + (kFKT / 2) * g;
+    const uint32_t t_o = tmem_base + lane_addr + kFColO + kFON * g;
     const int u = u0 + g;
     const bool urow = u < n_u;
     const float* mrow_base = mb + (size_t)(urow ? u : 0) * ldm;
@@ -209,23 +208,25 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     bool ok = true;
     for (int kt = 0; kt < nkt && ok; ++kt) {
       if ((kt & 63) == 0) flag_word = urow ? __ldg(flag_row + (kt >> 6)) : ~0ull;
-      ok = mbar_wait(&bars.bias_full[kt & 1], (kt >> 1) & 1, 32u);
-      if (qw == 0) { PX_TRACE(16 * g + 0 + (g ? 0 : 0), kt); }
-      ok = ok && mbar_wait(&bars.s_full[g], kt & 1, 64u);
+      ok = mbar_wait(&bars.bias_full[kt & 1], (kt >> 1) & 1, 64u);
+      if (qw == 0) { PX_TRACE(16 * g + 0, kt); }
+      ok = ok && mbar_wait(&bars.s_full[g], kt & 1, 128u);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       if (qw == 0) { PX_TRACE(16 * g + 1, kt); }
       tc_fence_after();
-      uint32_t t[kFKT];
+      float s[kFKT];
       {
-        uint32_t(&t0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&t[0]);
-        uint32_t(&t1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&t[32]);
+        uint32_t(&t0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[0]);
+        uint32_t(&t1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[32]);
         tmem_ld32(t_s, t0);
         tmem_ld32(t_s + 32, t1);
         tmem_wait_ld();
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars.s_free[g]);  // S is in registers: the next S may be computed
       if (qw == 0) { PX_TRACE(16 * g + 2, kt); }
-      float s[kFKT];
       const float* bias_tile = reinterpret_cast<const float*>(sm + FlashLayout::bias + (kt & 1) * kFBiasBytes);
 #pragma unroll
       for (int c = 0; c < kFKT / 32; ++c) {
@@ -234,14 +235,10 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
         for (int p = 0; p < 8; ++p) {
           const float4 b4 = *reinterpret_cast<const float4*>(brow + ((p ^ (row & 7)) << 2));
-          float x0 = __uint_as_float(t[32 * c + 4 * p + 0]), x1 = __uint_as_float(t[32 * c + 4 * p + 1]);
-          float x2 = __uint_as_float(t[32 * c + 4 * p + 2]), x3 = __uint_as_float(t[32 * c + 4 * p + 3]);
-          add2(x0, x1, b4.x, b4.y);
-          add2(x2, x3, b4.z, b4.w);
-          s[32 * c + 4 * p + 0] = x0;
-          s[32 * c + 4 * p + 1] = x1;
-          s[32 * c + 4 * p + 2] = x2;
-          s[32 * c + 4 * p + 3] = x3;
+          s[32 * c + 4 * p + 0] += b4.x;
+          s[32 * c + 4 * p + 1] += b4.y;
+          s[32 * c + 4 * p + 2] += b4.z;
+          s[32 * c + 4 * p + 3] += b4.w;
         }
       }
       __syncwarp();
@@ -251,8 +248,10 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
         for (int c4 = 0; c4 < kFKT / 4; ++c4) {
           const float4 m4 = __ldg(mrow + c4);
-          add2(s[4 * c4 + 0], s[4 * c4 + 1], m4.x, m4.y);
-          add2(s[4 * c4 + 2], s[4 * c4 + 3], m4.z, m4.w);
+          s[4 * c4 + 0] += m4.x;
+          s[4 * c4 + 1] += m4.y;
+          s[4 * c4 + 2] += m4.z;
+          s[4 * c4 + 3] += m4.w;
         }
       }
       if (qw == 0) { PX_TRACE(16 * g + 3, kt); }
@@ -260,35 +259,42 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
       for (int c = 3; c + 1 < kFKT; c += 2) mt = max3(mt, s[c], s[c + 1]);
       mt = fmaxf(mt, s[kFKT - 1]);
+      // P.V of the previous tile must be through before O is rescaled or its P buffer overwritten
+      if (kt >= 1) {
+        ok = mbar_wait(&bars.pv_done[g], (kt - 1) & 1, 256u);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+      }
       if (kt == 0) {
         m_ref = mt;                                 // first tile: the P.V product overwrites O
       } else if (__any_sync(0xffffffffu, mt > m_ref + kRescaleGap)) {
         const float m_new = (mt > m_ref + kRescaleGap) ? mt : m_ref;
         const float alpha = fast_exp2(m_ref - m_new);
         m_ref = m_new;
-        uint32_t a[32], b[16];
-        tmem_ld32(t_o, a);
-        tmem_ld16(t_o + 32, b);
-        tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) a[c] = __float_as_uint(__uint_as_float(a[c]) * alpha);
+        for (int c = 0; c < kFON / 16; ++c) {
+          uint32_t a[16];
+          tmem_ld16(t_o + 16 * c, a);
+          tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 16; ++c) b[c] = __float_as_uint(__uint_as_float(b[c]) * alpha);
-        tmem_st32(t_o, a);
-        tmem_st16(t_o + 32, b);
+          for (int e = 0; e < 16; ++e) a[e] = __float_as_uint(__uint_as_float(a[e]) * alpha);
+          tmem_st16(t_o + 16 * c, a);
+        }
       }
       {
         const float nm = -m_ref;
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {            // P overwrites the first 32 columns of S
+        for (int hf = 0; hf < 2; ++hf) {
           uint32_t w[16];
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
-            float x0 = s[32 * hf + 2 * e], x1 = s[32 * hf + 2 * e + 1];
-            add2(x0, x1, nm, nm);
-            w[e] = exp2_bf16x2(x0, x1);
+            // fp32 exponentials; P keeps the upper halves (truncation to bf16: the same truncated values feed the
+            // denominator column, so the bias cancels in the normalisation)
+            const float p0 = fast_exp2(s[32 * hf + 2 * e] + nm), p1 = fast_exp2(s[32 * hf + 2 * e + 1] + nm);
+            w[e] = __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
           }
-          tmem_st16(t_s + 16 * hf, w);
+          tmem_st16(t_p + 16 * hf, w);
         }
       }
       if (qw == 0) { PX_TRACE(16 * g + 4, kt); }
@@ -299,7 +305,7 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (qw == 0) { PX_TRACE(16 * g + 5, kt); }
     }
     // ---- epilogue: o = O / denominator for this group's row
-    ok = ok && mbar_wait(&bars.o_done[g], 0, 128u);
+    ok = ok && mbar_wait(&bars.pv_done[g], (nkt - 1) & 1, 512u);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();
@@ -332,7 +338,7 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     __syncthreads();
   }
-  if (warp == 4 * kFRows) {
+  if (warp == 12) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kFCols) : "memory");
   }

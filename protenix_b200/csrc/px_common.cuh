@@ -71,6 +71,13 @@ __device__ __forceinline__ uint32_t exp2_bf16x2(float lo, float hi) {
   asm("ex2.approx.ftz.bf16x2 %0, %1;\n" : "=r"(y) : "r"(x));
   return y;
 }
+// Same, but the pair is rounded and packed with integer ALU operations (add half an ulp, keep the upper
+// halves) instead of cvt.rn.bf16x2.f32, which occupies the same quarter-rate unit as ex2.
+__device__ __forceinline__ uint32_t exp2_bf16x2_alu(float lo, float hi) {
+  uint32_t x = __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632), y;
+  asm("ex2.approx.ftz.bf16x2 %0, %1;\n" : "=r"(y) : "r"(x));
+  return y;
+}
 __device__ __forceinline__ float sigmoidf_fast(float x) {
   return __fdividef(1.0f, 1.0f + fast_exp2(-kLog2e * x));
 }
