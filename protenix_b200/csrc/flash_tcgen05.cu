@@ -2,20 +2,22 @@
 //
 //   o[u][q][h*32+d] = softmax_k( q[u,h,q,:] . k[u,h,k,:] + bias[h][q][k] + mask_bias[u][k] ) v[u,h,k,d]
 //
-// One CTA = (head h, 128 queries, 3 attended rows u), 16 warps:
-//   warps 0..11   three softmax groups of four warps; group g owns row u0+g, each thread one query row
-//   warps 12..14  one control thread per group (tcgen05 and TMA instructions cost ~100 cycles of issue
+// One CTA = (head h, 128 queries, 6 attended rows u), 12 warps:
+//   warps 0..7    two softmax groups of four warps; group g owns rows u0+3g .. u0+3g+2, each thread one query
+//                 row.  Per 64-key tile a thread reads its 64 pair-bias values from shared memory once and
+//                 reuses them for the group's three rows (the bias does not depend on u).
+//   warps 8..9    one control thread per group (tcgen05 and TMA instructions cost ~100 cycles of issue
 //                 each, so one issuing thread for all groups would be the bottleneck).  It loads the
 //                 group's Q tile once and, per 64-key tile, a K tile [64 keys][32] (64-byte swizzle) and a
-//                 transposed V tile [32 d][64 keys] (128-byte swizzle) into the group's 3-stage ring;
+//                 transposed V tile [32 d][64 keys] (128-byte swizzle) into the group's 4-stage ring;
 //                 issues S = Q K^T (M=128, N=64, K=32) into the group's S buffer in tensor memory; and,
 //                 once the group has written P (bf16) into its P buffer, issues O_u += P V with P as the
 //                 TMEM-resident A operand (M=128, N=48, K=64).  Row 32 of the value operand is all ones, so
 //                 column 32 of O_u accumulates the softmax denominators.  S of the next key tile is issued
 //                 as soon as the group has pulled the current S into registers, so it is ready when the
 //                 group comes back.  The control thread of group 0 also loads the pair-bias tile
-//                 [128 q][64 k] fp32 (two 128-byte-swizzled boxes, 2-deep ring) shared by the three rows.
-//   warp 15       idle (completes the control warpgroup, which hands its registers to the softmax groups)
+//                 [128 q][64 k] fp32 (two 128-byte-swizzled boxes, 2-deep ring) shared by all six rows.
+//   warps 10..11  idle (they complete the control warpgroup, which hands its registers to the softmax groups)
 //
 // Softmax is online in base 2 with a lazy reference maximum: the reference only moves (and O_u is rescaled
 // through TMEM) when the tile maximum exceeds it by more than 8, so probabilities stay below 2^8.
@@ -27,9 +29,11 @@
 namespace px {
 
 constexpr int kFH = 4, kFD = 32;
-constexpr int kFRows = 3;                 // attended rows per CTA = softmax groups
+constexpr int kFGroups = 2;               // softmax groups per CTA
+constexpr int kFRpg = 3;                  // attended rows per group
+constexpr int kFRows = kFGroups * kFRpg;  // attended rows per CTA
 constexpr int kFKT = 64;                  // keys per work item
-constexpr int kFStages = 3;               // K/V ring of each group
+constexpr int kFStages = 4;               // K/V ring of each group (work items = (key tile, row))
 constexpr int kFQBytes = 128 * 64;        // [128][32] bf16
 constexpr int kFKBytes = kFKT * 64;       // [64][32] bf16
 constexpr int kFVBox = 32 * 128;          // the TMA box of the value tile: 32 rows x 64 keys
@@ -38,21 +42,21 @@ constexpr int kFStageBytes = kFKBytes + kFVBytes;
 constexpr int kFBiasBytes = 128 * kFKT * 4;
 constexpr int kFON = 48;                  // columns of an O accumulator (32 d + denominator + pad)
 constexpr uint32_t kFCols = 512;
-constexpr int kFColS = 0, kFColP = kFRows * kFKT, kFColO = kFColP + kFRows * (kFKT / 2);  // TMEM column map
+constexpr int kFColS = 0, kFColP = kFGroups * kFKT, kFColO = kFColP + kFGroups * (kFKT / 2);  // TMEM column map
 constexpr float kRescaleGap = 8.0f;
-constexpr int kFThreads = 32 * 16;
+constexpr int kFThreads = 32 * (4 * kFGroups + 4);
 static_assert(kFColO + kFRows * kFON <= 512, "tensor memory budget");
 
 struct FlashBars {
-  uint64_t q_full[kFRows], kv_full[kFRows][kFStages], bias_full[2], bias_empty[2], s_full[kFRows], s_free[kFRows],
-      p_ready[kFRows], pv_done[kFRows];
+  uint64_t q_full[kFGroups], kv_full[kFGroups][kFStages], bias_full[2], bias_empty[2], s_full[kFGroups],
+      s_free[kFGroups], p_ready[kFGroups], pv_done[kFGroups];
   uint32_t tmem_base;
 };
 
 struct FlashLayout {
   static constexpr int q = 0;
   static constexpr int kv = q + kFRows * kFQBytes;
-  static constexpr int bias = kv + kFRows * kFStages * kFStageBytes;
+  static constexpr int bias = kv + kFGroups * kFStages * kFStageBytes;
   static constexpr int bars = bias + 2 * kFBiasBytes;
   static constexpr int total = bars + (int)sizeof(FlashBars);
 };
@@ -87,9 +91,9 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (threadIdx.x == 0) {
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars.bias_full[b], 1);
-      mbar_init(&bars.bias_empty[b], 4 * kFRows);
+      mbar_init(&bars.bias_empty[b], 4 * kFGroups);
     }
-    for (int g = 0; g < kFRows; ++g) {
+    for (int g = 0; g < kFGroups; ++g) {
       mbar_init(&bars.q_full[g], 1);
       for (int s = 0; s < kFStages; ++s) mbar_init(&bars.kv_full[g][s], 1);
       mbar_init(&bars.s_full[g], 1);
@@ -102,13 +106,13 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   // operand rows 32..47 of every value tile: row 32 = ones (denominator column), the rest zero.  The TMA
   // box only ever writes rows 0..31.  Rows 32..39 are one 8-row swizzle group; row 32 is its row 0, whose
   // 16-byte pieces are not permuted.
-  for (int i = threadIdx.x; i < kFRows * kFStages * 128; i += blockDim.x) {
+  for (int i = threadIdx.x; i < kFGroups * kFStages * 128; i += blockDim.x) {
     const int stage = i / 128, piece = i % 128;                   // 128 pieces of 16 bytes per 16 rows
     uint4 v = (piece < 8) ? make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u) : make_uint4(0, 0, 0, 0);
     *reinterpret_cast<uint4*>(sm + FlashLayout::kv + stage * kFStageBytes + kFKBytes + 32 * 128 + piece * 16) = v;
   }
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy writes above -> MMA reads
-  if (warp == 12) {
+  if (warp == 4 * kFGroups) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&bars.tmem_base)),
                  "r"(kFCols)
                  : "memory");
@@ -119,20 +123,21 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = bars.tmem_base;
 
-  if (warp >= 12) {
+  if (warp >= 4 * kFGroups) {
     // ------------------------------------------------------------------ control thread of group g
     asm volatile("setmaxnreg.dec.sync.aligned.u32 24;\n");   // registers go to the softmax warpgroups
-    const int g = warp - 12;
-    if (g < kFRows && lane == 0) {
+    const int g = warp - 4 * kFGroups;
+    if (g < kFGroups && lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, kFKT), idesc_o = umma_idesc_bf16(128, kFON);
-      const int uh = (u0 + g) * kFH + h;            // rows past n_u: coordinate beyond the tensor -> zero fill
-      const uint32_t q_addr = smem_u32(sm + FlashLayout::q + g * kFQBytes);
+      const int n_items = nkt * kFRpg;              // work item i = (key tile i / 3, row i % 3 of the group)
+      const uint32_t q_addr = smem_u32(sm + FlashLayout::q + g * kFRpg * kFQBytes);
       const uint32_t ring = smem_u32(sm + FlashLayout::kv + g * kFStages * kFStageBytes);
       const uint32_t d_s = tmem_base + kFColS + kFKT * g, d_p = tmem_base + kFColP + (kFKT / 2) * g;
-      const uint32_t d_o = tmem_base + kFColO + kFON * g;
+      const uint32_t d_o = tmem_base + kFColO + kFON * kFRpg * g;
+      const int uh0 = (u0 + g * kFRpg) * kFH + h;   // rows past n_u: coordinate beyond the tensor -> zero fill
       bool ok = true;
-      auto load_kv = [&](int kt) {                  // K and V tiles of key tile kt into stage kt % kFStages
-        const int s = kt % kFStages;
+      auto load_kv = [&](int i) {                   // K and V tiles of item i into stage i % kFStages
+        const int s = i % kFStages, kt = i / kFRpg, uh = uh0 + (i % kFRpg) * kFH;
         mbar_expect_tx(&bars.kv_full[g][s], kFKBytes + kFVBox);
         tma_load_3d(ring + s * kFStageBytes, &map_k, &bars.kv_full[g][s], 0, kt * kFKT, uh);
         tma_load_3d(ring + s * kFStageBytes + kFKBytes, &map_v, &bars.kv_full[g][s], kt * kFKT, 0, uh);
@@ -146,185 +151,231 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                       kt * kFKT + c * 32, q0, h);
         return true;
       };
-      auto issue_s = [&](int kt) {                  // S(kt) = Q K(kt)^T
-        const int s = kt % kFStages;
-        if (!mbar_wait(&bars.kv_full[g][s], (kt / kFStages) & 1, 8u)) return false;
+      auto issue_s = [&](int i) {                   // S(i) = Q_r K^T
+        const int s = i % kFStages;
+        if (!mbar_wait(&bars.kv_full[g][s], (i / kFStages) & 1, 8u)) return false;
         tc_fence_after();
-        const uint64_t dq = umma_desc_sw64(q_addr), dk = umma_desc_sw64(ring + s * kFStageBytes);
+        const uint64_t dq = umma_desc_sw64(q_addr + (i % kFRpg) * kFQBytes), dk = umma_desc_sw64(ring + s * kFStageBytes);
         umma_bf16(d_s, dq, dk, idesc_s, 0u);
         umma_bf16(d_s, dq + 2, dk + 2, idesc_s, 1u);
         umma_commit(&bars.s_full[g]);
         return true;
       };
-      mbar_expect_tx(&bars.q_full[g], kFQBytes);
-      tma_load_3d(q_addr, &map_q, &bars.q_full[g], 0, q0, uh);
+      mbar_expect_tx(&bars.q_full[g], kFRpg * kFQBytes);
+      for (int r = 0; r < kFRpg; ++r) tma_load_3d(q_addr + r * kFQBytes, &map_q, &bars.q_full[g], 0, q0, uh0 + r * kFH);
       if (g == 0) {
         ok = load_bias(0);
         if (ok && nkt > 1) ok = load_bias(1);
       }
-      for (int kt = 0; kt < 2 && kt < nkt; ++kt) load_kv(kt);      // first use of these stages: nothing to wait for
+      for (int i = 0; i < kFStages - 1 && i < n_items; ++i) load_kv(i);   // first use of these stages
       ok = ok && mbar_wait(&bars.q_full[g], 0, 4u);
       ok = ok && issue_s(0);
-      for (int kt = 0; kt < nkt && ok; ++kt) {
-        PX_TRACE(8 + g, kt);
-        if (kt + 1 < nkt) {                         // next S as soon as the group holds the current one in registers
-          ok = mbar_wait(&bars.s_free[g], kt & 1, 2u) && issue_s(kt + 1);
+      for (int i = 0; i < n_items && ok; ++i) {
+        const int kt = i / kFRpg, r = i % kFRpg;
+        PX_TRACE(8 + g, i);
+        if (i + 1 < n_items) {                      // next S as soon as the group holds the current one in registers
+          ok = mbar_wait(&bars.s_free[g], i & 1, 2u) && issue_s(i + 1);
           if (!ok) break;
         }
-        PX_TRACE(12 + g, kt);
-        if (kt + 2 < nkt) {                         // refill: stage of tile kt+2 was last read by P.V of tile kt-1
-          if (kt >= 1) ok = mbar_wait(&bars.pv_done[g], (kt - 1) & 1, 32u);
+        PX_TRACE(12 + g, i);
+        if (i + kFStages - 1 < n_items) {           // refill: that stage was last read by P.V of item i-1
+          if (i >= 1) ok = mbar_wait(&bars.pv_done[g], (i - 1) & 1, 32u);
           if (!ok) break;
-          load_kv(kt + 2);
+          load_kv(i + kFStages - 1);
         }
-        if (g == 0 && kt >= 1 && kt + 1 < nkt) ok = load_bias(kt + 1);
+        if (g == 0 && r == 0 && kt >= 1 && kt + 1 < nkt) ok = load_bias(kt + 1);
         if (!ok) break;
-        ok = mbar_wait(&bars.p_ready[g], kt & 1, 16u);
+        ok = mbar_wait(&bars.p_ready[g], i & 1, 16u);
         if (!ok) break;
         tc_fence_after();
-        const uint64_t dv = umma_desc_sw128(ring + (kt % kFStages) * kFStageBytes + kFKBytes);
+        const uint64_t dv = umma_desc_sw128(ring + (i % kFStages) * kFStageBytes + kFKBytes);
 #pragma unroll
         for (int ks = 0; ks < kFKT / 16; ++ks)  // 16 keys per step: 8 TMEM columns of P, 32 bytes of the value rows
-          umma_bf16_ts(d_o, d_p + 8 * ks, dv + 2 * ks, idesc_o, (kt | ks) ? 1u : 0u);
+          umma_bf16_ts(d_o + kFON * r, d_p + 8 * ks, dv + 2 * ks, idesc_o, (kt | ks) ? 1u : 0u);
         umma_commit(&bars.pv_done[g]);
       }
     }
   } else {
     // ------------------------------------------------------------------ softmax groups
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 160;\n");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;\n");
     const int g = warp >> 2, qw = warp & 3;
     const int row = 32 * qw + lane;                 // query row inside the tile = TMEM lane
     const uint32_t lane_addr = (uint32_t)(32 * qw) << 16;
     const uint32_t t_s = tmem_base + lane_addr + kFColS + kFKT * g;
     const uint32_t t_p = tmem_base + lane_addr + kFColP + (kFKT / 2) * g;
-    const uint32_t t_o = tmem_base + lane_addr + kFColO + kFON * g;
-    const int u = u0 + g;
-    const bool urow = u < n_u;
-    const float* mrow_base = mb + (size_t)(urow ? u : 0) * ldm;
-    // one bit per 64-key tile: does the tile carry any non-zero mask bias for this row?
-    const unsigned long long* flag_row = tile_masked + (size_t)(urow ? u : 0) * ((nkt + 63) / 64);
-    unsigned long long flag_word = 0;
-    float m_ref = -CUDART_INF_F;
+    const uint32_t t_o = tmem_base + lane_addr + kFColO + kFON * kFRpg * g;
+    const int ug = u0 + kFRpg * g;                  // first row of this group
+    const int words = (nkt + 63) / 64;              // mask-flag words per row: one bit per 64-key tile
+    unsigned long long flag_word[kFRpg];
+    float m_ref[kFRpg];
+#pragma unroll
+    for (int r = 0; r < kFRpg; ++r) {
+      flag_word[r] = 0;
+      m_ref[r] = -CUDART_INF_F;
+    }
     bool ok = true;
+#ifndef PX_FLASH_STAGGER
+#define PX_FLASH_STAGGER 900
+#endif
+    if (g == 1) {
+      // Start the second group half a work item late: the two groups then alternate between their
+      // exponential phase (which saturates the special-function unit) and everything else, instead of
+      // colliding on that unit and idling together.
+      const long long t0 = clock64();
+      while (clock64() - t0 < PX_FLASH_STAGGER) {
+      }
+    }
     for (int kt = 0; kt < nkt && ok; ++kt) {
-      if ((kt & 63) == 0) flag_word = urow ? __ldg(flag_row + (kt >> 6)) : ~0ull;
+      if ((kt & 63) == 0) {
+#pragma unroll
+        for (int r = 0; r < kFRpg; ++r)
+          flag_word[r] = (ug + r < n_u) ? __ldg(tile_masked + (size_t)(ug + r) * words + (kt >> 6)) : ~0ull;
+      }
       ok = mbar_wait(&bars.bias_full[kt & 1], (kt >> 1) & 1, 64u);
-      if (qw == 0) { PX_TRACE(16 * g + 0, kt); }
-      ok = ok && mbar_wait(&bars.s_full[g], kt & 1, 128u);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      if (qw == 0) { PX_TRACE(16 * g + 1, kt); }
-      tc_fence_after();
-      float s[kFKT];
+      // this thread's 64 bias values of the tile: read once, used for the group's three rows
+      float bv[kFKT];
       {
-        uint32_t(&t0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[0]);
-        uint32_t(&t1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[32]);
-        tmem_ld32(t_s, t0);
-        tmem_ld32(t_s + 32, t1);
-        tmem_wait_ld();
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars.s_free[g]);  // S is in registers: the next S may be computed
-      if (qw == 0) { PX_TRACE(16 * g + 2, kt); }
-      const float* bias_tile = reinterpret_cast<const float*>(sm + FlashLayout::bias + (kt & 1) * kFBiasBytes);
+        const float* bias_tile = reinterpret_cast<const float*>(sm + FlashLayout::bias + (kt & 1) * kFBiasBytes);
 #pragma unroll
-      for (int c = 0; c < kFKT / 32; ++c) {
-        // box c holds columns 32c..32c+31 of all 128 rows: 128-byte rows, 16-byte pieces swizzled by row
-        const float* brow = bias_tile + c * (128 * 32) + row * 32;
+        for (int c = 0; c < kFKT / 32; ++c) {
+          // box c holds columns 32c..32c+31 of all 128 rows: 128-byte rows, 16-byte pieces swizzled by row
+          const float* brow = bias_tile + c * (128 * 32) + row * 32;
 #pragma unroll
-        for (int p = 0; p < 8; ++p) {
-          const float4 b4 = *reinterpret_cast<const float4*>(brow + ((p ^ (row & 7)) << 2));
-          s[32 * c + 4 * p + 0] += b4.x;
-          s[32 * c + 4 * p + 1] += b4.y;
-          s[32 * c + 4 * p + 2] += b4.z;
-          s[32 * c + 4 * p + 3] += b4.w;
+          for (int p = 0; p < 8; ++p) {
+            const float4 b4 = *reinterpret_cast<const float4*>(brow + ((p ^ (row & 7)) << 2));
+            bv[32 * c + 4 * p + 0] = b4.x;
+            bv[32 * c + 4 * p + 1] = b4.y;
+            bv[32 * c + 4 * p + 2] = b4.z;
+            bv[32 * c + 4 * p + 3] = b4.w;
+          }
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars.bias_empty[kt & 1]);     // this warp is done with the bias tile
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars.bias_empty[kt & 1]);       // this warp is done with the bias tile
-      if ((flag_word >> (kt & 63)) & 1ull) {                      // warp-uniform
-        const float4* mrow = reinterpret_cast<const float4*>(mrow_base + kt * kFKT);
 #pragma unroll
-        for (int c4 = 0; c4 < kFKT / 4; ++c4) {
-          const float4 m4 = __ldg(mrow + c4);
-          s[4 * c4 + 0] += m4.x;
-          s[4 * c4 + 1] += m4.y;
-          s[4 * c4 + 2] += m4.z;
-          s[4 * c4 + 3] += m4.w;
-        }
-      }
-      if (qw == 0) { PX_TRACE(16 * g + 3, kt); }
-      float mt = max3(s[0], s[1], s[2]);
-#pragma unroll
-      for (int c = 3; c + 1 < kFKT; c += 2) mt = max3(mt, s[c], s[c + 1]);
-      mt = fmaxf(mt, s[kFKT - 1]);
-      // P.V of the previous tile must be through before O is rescaled or its P buffer overwritten
-      if (kt >= 1) {
-        ok = mbar_wait(&bars.pv_done[g], (kt - 1) & 1, 256u);
+      for (int r = 0; r < kFRpg; ++r) {
+        const int i = kt * kFRpg + r;               // this group's work item
+        if (qw == 0) { PX_TRACE(16 * g + 0, i); }
+        ok = mbar_wait(&bars.s_full[g], i & 1, 128u);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        if (qw == 0) { PX_TRACE(16 * g + 1, i); }
         tc_fence_after();
-      }
-      if (kt == 0) {
-        m_ref = mt;                                 // first tile: the P.V product overwrites O
-      } else if (__any_sync(0xffffffffu, mt > m_ref + kRescaleGap)) {
-        const float m_new = (mt > m_ref + kRescaleGap) ? mt : m_ref;
-        const float alpha = fast_exp2(m_ref - m_new);
-        m_ref = m_new;
-#pragma unroll
-        for (int c = 0; c < kFON / 16; ++c) {
-          uint32_t a[16];
-          tmem_ld16(t_o + 16 * c, a);
+        float s[kFKT];
+        {
+          uint32_t(&t0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[0]);
+          uint32_t(&t1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[32]);
+          tmem_ld32(t_s, t0);
+          tmem_ld32(t_s + 32, t1);
           tmem_wait_ld();
-#pragma unroll
-          for (int e = 0; e < 16; ++e) a[e] = __float_as_uint(__uint_as_float(a[e]) * alpha);
-          tmem_st16(t_o + 16 * c, a);
         }
-      }
-      {
-        const float nm = -m_ref;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars.s_free[g]);  // S is in registers: the next S may be computed
+        if (qw == 0) { PX_TRACE(16 * g + 2, i); }
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          uint32_t w[16];
+        for (int c = 0; c < kFKT; ++c) s[c] += bv[c];
+        if ((flag_word[r] >> (kt & 63)) & 1ull) {     // warp-uniform
+          const int u = (ug + r < n_u) ? ug + r : 0;
+          const float4* mrow = reinterpret_cast<const float4*>(mb + (size_t)u * ldm + kt * kFKT);
 #pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            // fp32 exponentials; P keeps the upper halves (truncation to bf16: the same truncated values feed the
-            // denominator column, so the bias cancels in the normalisation)
-            const float p0 = fast_exp2(s[32 * hf + 2 * e] + nm), p1 = fast_exp2(s[32 * hf + 2 * e + 1] + nm);
+          for (int c4 = 0; c4 < kFKT / 4; ++c4) {
+            const float4 m4 = __ldg(mrow + c4);
+            s[4 * c4 + 0] += m4.x;
+            s[4 * c4 + 1] += m4.y;
+            s[4 * c4 + 2] += m4.z;
+            s[4 * c4 + 3] += m4.w;
+          }
+        }
+        if (qw == 0) { PX_TRACE(16 * g + 3, i); }
+        // tile maximum: four independent chains, so the reduction costs about 8 dependent steps
+        float mq[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          mq[c] = max3(s[16 * c], s[16 * c + 1], s[16 * c + 2]);
+#pragma unroll
+          for (int e = 3; e + 1 < 16; e += 2) mq[c] = max3(mq[c], s[16 * c + e], s[16 * c + e + 1]);
+          mq[c] = fmaxf(mq[c], s[16 * c + 15]);
+        }
+        const float mt = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
+        // Does the reference maximum have to move?  Rare after the first tiles (warp-uniform decision).
+        const bool first = (kt == 0);
+        const bool move = !first && __any_sync(0xffffffffu, mt > m_ref[r] + kRescaleGap);
+        float alpha = 1.0f;
+        if (first) {
+          m_ref[r] = mt;                              // first tile: the P.V product overwrites O
+        } else if (move) {
+          const float m_new = (mt > m_ref[r] + kRescaleGap) ? mt : m_ref[r];
+          alpha = fast_exp2(m_ref[r] - m_new);
+          m_ref[r] = m_new;
+        }
+        uint32_t w[kFKT / 2];
+        {
+          const float nm = -m_ref[r];
+#pragma unroll
+          for (int e = 0; e < kFKT / 2; ++e) {
+            // fp32 exponentials; P keeps the upper halves (truncation to bf16: the same truncated values feed
+            // the denominator column, so the bias cancels in the normalisation)
+            const float p0 = fast_exp2(s[2 * e] + nm), p1 = fast_exp2(s[2 * e + 1] + nm);
             w[e] = __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
           }
-          tmem_st16(t_p + 16 * hf, w);
         }
+        // P.V of the previous item must be through before O is rescaled or the P buffer overwritten
+        if (i >= 1) {
+          ok = mbar_wait(&bars.pv_done[g], (i - 1) & 1, 256u);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        if (move) {
+#pragma unroll
+          for (int c = 0; c < kFON / 16; ++c) {
+            uint32_t a[16];
+            tmem_ld16(t_o + kFON * r + 16 * c, a);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) a[e] = __float_as_uint(__uint_as_float(a[e]) * alpha);
+            tmem_st16(t_o + kFON * r + 16 * c, a);
+          }
+        }
+        {
+          uint32_t(&w0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&w[0]);
+          tmem_st32(t_p, w0);
+        }
+        if (qw == 0) { PX_TRACE(16 * g + 4, i); }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars.p_ready[g]);
+        if (qw == 0) { PX_TRACE(16 * g + 5, i); }
       }
-      if (qw == 0) { PX_TRACE(16 * g + 4, kt); }
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars.p_ready[g]);
-      if (qw == 0) { PX_TRACE(16 * g + 5, kt); }
     }
-    // ---- epilogue: o = O / denominator for this group's row
-    ok = ok && mbar_wait(&bars.pv_done[g], (nkt - 1) & 1, 512u);
+    // ---- epilogue: o = O / denominator for this group's rows
+    ok = ok && mbar_wait(&bars.pv_done[g], (nkt * kFRpg - 1) & 1, 512u);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();
       const int qi = q0 + row;
-      uint32_t a[32], b[16];
-      tmem_ld32(t_o, a);
-      tmem_ld16(t_o + 32, b);
-      tmem_wait_ld();
-      if (urow && qi < n) {
-        const float inv = 1.0f / __uint_as_float(b[0]);
-        bf16* dst = o + ((size_t)u * n + qi) * kC + h * kFD;
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          uint4 pk;
-          pk.x = pack_bf16x2(__uint_as_float(a[8 * v + 0]) * inv, __uint_as_float(a[8 * v + 1]) * inv);
-          pk.y = pack_bf16x2(__uint_as_float(a[8 * v + 2]) * inv, __uint_as_float(a[8 * v + 3]) * inv);
-          pk.z = pack_bf16x2(__uint_as_float(a[8 * v + 4]) * inv, __uint_as_float(a[8 * v + 5]) * inv);
-          pk.w = pack_bf16x2(__uint_as_float(a[8 * v + 6]) * inv, __uint_as_float(a[8 * v + 7]) * inv);
-          *reinterpret_cast<uint4*>(dst + 8 * v) = pk;
+      for (int r = 0; r < kFRpg; ++r) {
+        uint32_t a[32], b[16];
+        tmem_ld32(t_o + kFON * r, a);
+        tmem_ld16(t_o + kFON * r + 32, b);
+        tmem_wait_ld();
+        if (ug + r < n_u && qi < n) {
+          const float inv = 1.0f / __uint_as_float(b[0]);
+          bf16* dst = o + ((size_t)(ug + r) * n + qi) * kC + h * kFD;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 pk;
+            pk.x = pack_bf16x2(__uint_as_float(a[8 * v + 0]) * inv, __uint_as_float(a[8 * v + 1]) * inv);
+            pk.y = pack_bf16x2(__uint_as_float(a[8 * v + 2]) * inv, __uint_as_float(a[8 * v + 3]) * inv);
+            pk.z = pack_bf16x2(__uint_as_float(a[8 * v + 4]) * inv, __uint_as_float(a[8 * v + 5]) * inv);
+            pk.w = pack_bf16x2(__uint_as_float(a[8 * v + 6]) * inv, __uint_as_float(a[8 * v + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + 8 * v) = pk;
+          }
         }
       }
     }
@@ -338,7 +389,7 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     __syncthreads();
   }
-  if (warp == 12) {
+  if (warp == 4 * kFGroups) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kFCols) : "memory");
   }
