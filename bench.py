@@ -188,6 +188,19 @@ def kernel_algo(n: int, zbytes: int) -> dict:
     }
 
 
+# DRAM bytes per pair element (dram__bytes_read.sum + dram__bytes_write.sum of one launch / N^2) from the ncu
+# captures at N = 768 summarised under profiles/ (<kernel>_N768.md).  For these kernels traffic grows with
+# N^2 (operands of the N^3 kernels are re-read from L2, not DRAM), so a launch at another N is scaled by N^2.
+NCU_TRAFFIC_PER_PAIR = {
+    "px_triatt_flash": 598.5e6 / 768 ** 2,
+    "px_trimul_contract": 419.3e6 / 768 ** 2,
+    "px_trimul_in_proj": 397.8e6 / 768 ** 2,
+    "px_trimul_out": 405.6e6 / 768 ** 2,
+    "px_triatt_in_proj": 563.2e6 / 768 ** 2,
+    "px_triatt_out": 404.3e6 / 768 ** 2,
+}
+
+
 def run_micro(args) -> None:
     """One block's kernels timed one by one (N=768 by default via --n-token): last 10 % of tokens masked."""
     import torch
@@ -369,7 +382,9 @@ def main() -> None:
         achieved, peak, runit = algo[1] / (avg_ms * 1e-3) / 1e9, pk["hbm_gbs"], "GB/s"
     step_total = sum(v[1] for v in stages.values()) / args.steps
     roof = {"kernel": name, "bound": algo[0], "achieved": achieved, "peak": peak, "unit": runit,
-            "frac": achieved / peak, "peak_source": pk["source"], "traffic": None, "avg_launch_ms": avg_ms,
+            "frac": achieved / peak, "peak_source": pk["source"],
+            "traffic": (NCU_TRAFFIC_PER_PAIR[name] * n * n / world) if name in NCU_TRAFFIC_PER_PAIR else None,
+            "traffic_note": "bytes per launch; ncu capture at N=768 (profiles/) scaled by N^2", "avg_launch_ms": avg_ms,
             "launches": cnt,
             "stage_ms_per_step": {k: round(v[1] / args.steps, 3) for k, v in sorted(stages.items())},
             "stage_share": {k: round(v[1] / args.steps / step_total, 4) for k, v in sorted(stages.items())}}
