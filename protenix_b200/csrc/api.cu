@@ -4,14 +4,15 @@
 namespace px {
 unsigned int contract_error_flags();
 unsigned int flash_error_flags();
+unsigned int transition_error_flags();
 }  // namespace px
 
 // Synchronises the device and returns (and clears) the flags recorded by bounded waits that ran out.
-// Bits 0-7: contraction kernel, bits 8-15: flash-attention kernel.
+// Bits 0-7: contraction kernel, bits 8-15: flash-attention kernel, bits 16-23: transition kernel.
 extern "C" int32_t px_device_error_flags(uint32_t* flags) {
   if (!flags) return PX_ERR_BAD_ARG;
   if (cudaDeviceSynchronize() != cudaSuccess) return PX_ERR_LAUNCH;
-  *flags = px::contract_error_flags() | (px::flash_error_flags() << 8);
+  *flags = px::contract_error_flags() | (px::flash_error_flags() << 8) | (px::transition_error_flags() << 16);
   return PX_OK;
 }
 
