@@ -5,14 +5,17 @@ namespace px {
 unsigned int contract_error_flags();
 unsigned int flash_error_flags();
 unsigned int transition_error_flags();
+unsigned int trimul_in_error_flags();
 }  // namespace px
 
 // Synchronises the device and returns (and clears) the flags recorded by bounded waits that ran out.
-// Bits 0-7: contraction kernel, bits 8-15: flash-attention kernel, bits 16-23: transition kernel.
+// Bits 0-7: contraction kernel, bits 8-15: flash-attention kernel, bits 16-23: transition kernel,
+// bits 24-31: projection and output stages.
 extern "C" int32_t px_device_error_flags(uint32_t* flags) {
   if (!flags) return PX_ERR_BAD_ARG;
   if (cudaDeviceSynchronize() != cudaSuccess) return PX_ERR_LAUNCH;
-  *flags = px::contract_error_flags() | (px::flash_error_flags() << 8) | (px::transition_error_flags() << 16);
+  *flags = px::contract_error_flags() | (px::flash_error_flags() << 8) | (px::transition_error_flags() << 16) |
+           (px::trimul_in_error_flags() << 24);
   return PX_OK;
 }
 

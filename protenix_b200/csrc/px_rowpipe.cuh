@@ -1,0 +1,209 @@
+// Pieces shared by the persistent, TMA-fed row kernels (LayerNorm'd 128-channel rows times resident weights).
+//
+// LayerNorm is not applied to the operand.  With W' = W diag(gamma), s = W' 1, t = W beta and std = 1/rstd,
+//     W LN(x) = rstd * ( W' x - mean * s + std * t ),
+// so the tensor core multiplies the rows exactly as they are stored (bf16 rows go from global memory to the swizzled
+// operand by TMA without passing through registers).  The two correction terms ride along as one extra K step of 16:
+// the row side holds (-mean, std) and the weight side (s, t), each split into a bf16 head and tail so that the
+// products carry about 17 bits.  What is left for the epilogue is one multiplication by the row's rstd.
+// Rows stored as fp32 are standardised ((x - mean) * rstd) while they are converted, and then carry mean 0, std 1.
+#pragma once
+#include "px_tcgen05.cuh"
+
+namespace px {
+
+constexpr int kPanelBytes = 128 * 128;        // [128 rows][64 k] bf16, 128-byte swizzle
+constexpr int kOperandBytes = 2 * kPanelBytes;  // [128 rows][128 k] as two k panels
+
+// Optional timeline of CTA 0 (debug builds only): slot = event kind, idx = tile counter.
+#ifdef PX_ROW_TRACE
+__device__ long long g_row_trace[32 * 32];
+#define ROW_TRACE(slot, idx) \
+  if (blockIdx.x == 0 && lane == 0 && (idx) < 32) g_row_trace[(slot) * 32 + (idx)] = clock64();
+#else
+#define ROW_TRACE(slot, idx)
+#endif
+
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Two fp32 -> one bf16x2 word, round half up, on the integer pipe (the conversion instruction shares the
+// special-function pipe with tanh, which these kernels keep busy).
+__device__ __forceinline__ uint32_t pack_bf16x2_int(float lo, float hi) {
+  return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
+}
+
+// Byte offset of the 16-byte piece holding channels 8*piece16..8*piece16+7 of row r inside a [128][128] operand.
+__device__ __forceinline__ int operand_piece_offset(int r, int piece16, int panel_bytes = kPanelBytes) {
+  return (piece16 >> 3) * panel_bytes + r * 128 + (((piece16 & 7) ^ (r & 7)) << 4);
+}
+
+// bf16 head and tail of an fp32 value: head + tail carries about 17 significant bits.
+__device__ __forceinline__ void split_bf16(float v, uint32_t& head, uint32_t& tail) {
+  const bf16 h = __float2bfloat16_rn(v);
+  const bf16 t = __float2bfloat16_rn(v - __bfloat162float(h));
+  head = (uint32_t)__bfloat16_as_ushort(h);
+  tail = (uint32_t)__bfloat16_as_ushort(t);
+}
+
+// Row r of a correction panel ([rows][16 k] bf16, 32-byte swizzle): k = 0..3 pair up x with the other side's first
+// value, k = 4..7 pair up y with its second value; `weight_side` picks the interleaving so that the four head/tail
+// products of each pair meet:  row side (xh, xh, xl, xl, yh, yh, yl, yl), weight side (xh, xl, xh, xl, yh, yl, yh, yl).
+__device__ __forceinline__ void write_correction_row(unsigned char* panel, int r, float x, float y, bool weight_side) {
+  uint32_t xh, xl, yh, yl;
+  split_bf16(x, xh, xl);
+  split_bf16(y, yh, yl);
+  uint4 v;
+  if (weight_side) {
+    v.x = xh | (xl << 16), v.y = v.x, v.z = yh | (yl << 16), v.w = v.z;
+  } else {
+    v.x = xh | (xh << 16), v.y = xl | (xl << 16), v.z = yh | (yh << 16), v.w = yl | (yl << 16);
+  }
+  const int sw = (r >> 2) & 1;
+  *reinterpret_cast<uint4*>(panel + r * 32 + (sw << 4)) = v;
+  *reinterpret_cast<uint4*>(panel + r * 32 + ((sw ^ 1) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+}
+
+// Rounds to bf16 (half up) on the integer pipe and stores two bytes.
+__device__ __forceinline__ void store_bf16_int(bf16* p, float v) {
+  *reinterpret_cast<unsigned short*>(p) = (unsigned short)((__float_as_uint(v) + 0x8000u) >> 16);
+}
+
+// Folds gamma (and `scale`) into rows [row_begin, row_begin + count) of a [*][128] bf16 weight and writes them as rows
+// dst_row0.. of a K-major swizzled operand with `panel_bytes` per 64-wide k panel; the matching rows of the
+// correction panel `extra` receive (s, t): s = sum_c W'[row][c] over the rounded values,
+// t = scale * sum_c W[row][c] * beta[c].  Warp-per-row; called by `nwarps` warps with consecutive `warp` numbers.
+__device__ __forceinline__ void fold_weight_rows(unsigned char* dst, unsigned char* extra, int dst_row0, int panel_bytes,
+                                                 const bf16* __restrict__ W, int row_begin, int count,
+                                                 const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                 float scale, int warp, int nwarps, int lane) {
+  const float4 g4 = *reinterpret_cast<const float4*>(gamma + 4 * lane);
+  const float4 b4 = *reinterpret_cast<const float4*>(beta + 4 * lane);
+#pragma unroll 2
+  for (int i = warp; i < count; i += nwarps) {
+    const float4 w = load4(W + (size_t)(row_begin + i) * kC + 4 * lane);
+    const uint32_t lo = pack_bf16x2(w.x * g4.x * scale, w.y * g4.y * scale);
+    const uint32_t hi = pack_bf16x2(w.z * g4.z * scale, w.w * g4.w * scale);
+    const float2 f0 = unpack_bf16x2(lo), f1 = unpack_bf16x2(hi);
+    const float s = warp_sum(f0.x + f0.y + f1.x + f1.y);
+    const float t = warp_sum(w.x * b4.x + w.y * b4.y + w.z * b4.z + w.w * b4.w) * scale;
+    const int r = i + dst_row0;
+    *reinterpret_cast<uint2*>(dst + operand_piece_offset(r, lane >> 1, panel_bytes) + (lane & 1) * 8) = make_uint2(lo, hi);
+    if (lane == 0) write_correction_row(extra, r, s, t, true);
+  }
+}
+
+// The register of a 32-entry array that belongs to this lane (arr[lane] without local memory).
+__device__ __forceinline__ float select_own(const uint32_t (&arr)[32], int lane) {
+  uint32_t v = 0;
+#pragma unroll
+  for (int e = 0; e < 32; ++e) v = (lane == e) ? arr[e] : v;
+  return __uint_as_float(v);
+}
+
+// TMA store of a 3-D box from shared memory (bulk async group of the calling thread).
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];\n"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
+// Waits until at most N of this thread's store groups still read their shared-memory source.
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tma_store_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;\n" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+  asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Mean and 1/std of one bf16 row already in the swizzled operand at `op` (row r), computed by two threads, each
+// over 64 channels (`half` = 0/1; the two threads are neighbouring lanes).  One pass: sums of (x - x0) and
+// (x - x0)^2 with the row's first element as pivot, which keeps the variance accurate when |mean| >> std.
+__device__ __forceinline__ void row_stats_from_operand(const unsigned char* op, int r, int half, float eps, float& mean,
+                                                       float& rstd) {
+  const float x0 = __uint_as_float(*reinterpret_cast<const uint32_t*>(op + operand_piece_offset(r, 0)) << 16);
+  float s0 = 0.f, s1 = 0.f, q0 = 0.f, q1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    // pieces 4*half..4*half+3 of both k panels: the 8 lanes of a quarter warp touch 8 distinct bank groups
+    const int p = ((i >> 2) << 3) + 4 * half + (i & 3);
+    const uint4 v = *reinterpret_cast<const uint4*>(op + operand_piece_offset(r, p));
+    const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+    float e;
+    e = a.x - x0, s0 += e, q0 = fmaf(e, e, q0);
+    e = a.y - x0, s1 += e, q1 = fmaf(e, e, q1);
+    e = b.x - x0, s0 += e, q0 = fmaf(e, e, q0);
+    e = b.y - x0, s1 += e, q1 = fmaf(e, e, q1);
+    e = c.x - x0, s0 += e, q0 = fmaf(e, e, q0);
+    e = c.y - x0, s1 += e, q1 = fmaf(e, e, q1);
+    e = d.x - x0, s0 += e, q0 = fmaf(e, e, q0);
+    e = d.y - x0, s1 += e, q1 = fmaf(e, e, q1);
+  }
+  float s = s0 + s1, q = q0 + q1;
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  q += __shfl_xor_sync(0xffffffffu, q, 1);
+  const float m = s * (1.0f / kC);
+  mean = x0 + m;
+  rstd = rsqrtf(fmaxf(q * (1.0f / kC) - m * m, 0.f) + eps);
+}
+
+// One fp32 row from global memory (nullptr = a row of zeros) -> standardised bf16 row r of the operand at `op`;
+// one thread per row.  The row is read twice (the second pass hits L1/L2).
+__device__ __forceinline__ void standardise_row_to_operand(unsigned char* op, int r, const float* __restrict__ src,
+                                                           float eps) {
+  float mean = 0.f, rstd = 0.f;
+  if (src) {
+    float s = 0.f;
+#pragma unroll 8
+    for (int p = 0; p < 32; ++p) {
+      const float4 v = load4(src + 4 * p);
+      s += (v.x + v.y) + (v.z + v.w);
+    }
+    mean = s * (1.0f / kC);
+    float q = 0.f;
+#pragma unroll 8
+    for (int p = 0; p < 32; ++p) {
+      const float4 v = load4(src + 4 * p);
+      q = fmaf(v.x - mean, v.x - mean, q);
+      q = fmaf(v.y - mean, v.y - mean, q);
+      q = fmaf(v.z - mean, v.z - mean, q);
+      q = fmaf(v.w - mean, v.w - mean, q);
+    }
+    rstd = rsqrtf(q * (1.0f / kC) + eps);
+  }
+#pragma unroll 4
+  for (int p = 0; p < 16; ++p) {
+    uint4 o = make_uint4(0u, 0u, 0u, 0u);
+    if (src) {
+      const float4 v0 = load4(src + 8 * p), v1 = load4(src + 8 * p + 4);
+      o.x = pack_bf16x2((v0.x - mean) * rstd, (v0.y - mean) * rstd);
+      o.y = pack_bf16x2((v0.z - mean) * rstd, (v0.w - mean) * rstd);
+      o.z = pack_bf16x2((v1.x - mean) * rstd, (v1.y - mean) * rstd);
+      o.w = pack_bf16x2((v1.z - mean) * rstd, (v1.w - mean) * rstd);
+    }
+    *reinterpret_cast<uint4*>(op + operand_piece_offset(r, p)) = o;
+  }
+}
+
+// Number of SMs of the current device (cached per device ordinal).
+static inline int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!cached[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+}  // namespace px

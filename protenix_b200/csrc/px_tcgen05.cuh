@@ -58,6 +58,11 @@ __device__ __forceinline__ uint64_t umma_desc_sw64(uint32_t saddr) {
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(512 >> 4) << 32) |
          ((uint64_t)1 << 46) | ((uint64_t)4 << 61);
 }
+// K-major operand tile, rows of 16 bf16 (32 bytes), 32-byte swizzle, 8-row groups 256 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw32(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(256 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)6 << 61);
+}
 // Instruction descriptor of kind::f16 with bf16 A and B (both K-major) and fp32 D, M x N tile.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
@@ -151,12 +156,12 @@ static inline EncodeTiledFn tensor_map_encoder() {
 // 3-D tiled map: dims/strides innermost first (strides in bytes for dims 1 and 2), zero fill outside.
 static inline bool make_map_3d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t d0, uint64_t d1,
                                uint64_t d2, uint64_t s1, uint64_t s2, uint32_t b0, uint32_t b1,
-                               CUtensorMapSwizzle swz) {
+                               CUtensorMapSwizzle swz, uint32_t b2 = 1) {
   EncodeTiledFn enc = tensor_map_encoder();
   if (!enc) return false;
   const cuuint64_t dims[3] = {d0, d1, d2};
   const cuuint64_t strides[2] = {s1, s2};
-  const cuuint32_t box[3] = {b0, b1, 1};
+  const cuuint32_t box[3] = {b0, b1, b2};
   const cuuint32_t estr[3] = {1, 1, 1};
   return enc(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;

@@ -3,93 +3,7 @@
 
 namespace px {
 
-// =========================================================================================
-// Stage 1: LN(z) -> gated projections a, b, stored channel-major with the contraction index
-// contiguous.  One CTA = one (u, 128 consecutive t) tile of pair elements, 8 warps x 16 rows.
-// The element for (u,t) is z[u][t] (outgoing) or z[t][u] (incoming).
-// HBM-bound: reads 128*sizeof(Tz) + 4 bytes, writes 512 bytes per pair element.
-// =========================================================================================
-struct TriMulInSmem {
-  bf16 A[128 * kLdA];       // LayerNorm'd operand rows
-  bf16 W[2][64 * kLdA];     // weight chunk double buffer: rows 0..31 projection, 32..63 gate
-  bf16 S[2][32 * kLdA];     // transposed output staging [channel][t]
-};
-
-template <typename Tz>
-__global__ void __launch_bounds__(256, 2)
-trimul_in_proj_kernel(const Tz* __restrict__ z, const float* __restrict__ mask, const float* __restrict__ ln_w,
-                      const float* __restrict__ ln_b, const bf16* __restrict__ w_ap, const bf16* __restrict__ w_ag,
-                      const bf16* __restrict__ w_bp, const bf16* __restrict__ w_bg, bf16* __restrict__ a_out,
-                      bf16* __restrict__ b_out, int n_u, int n_t, int ld, int swap, float eps) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  TriMulInSmem& sm = *reinterpret_cast<TriMulInSmem*>(smem_raw);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int u = blockIdx.y, t0 = blockIdx.x * 128;
-
-  auto load_chunk = [&](int q, int buf) {
-    const bf16* wp = (q < 4) ? w_ap : w_bp;
-    const bf16* wg = (q < 4) ? w_ag : w_bg;
-    load_w_rows(sm.W[buf], 0, wp, 32 * (q & 3), 32, tid);
-    load_w_rows(sm.W[buf], 32, wg, 32 * (q & 3), 32, tid);
-    cp_async_commit();
-  };
-  load_chunk(0, 0);
-
-  // z (and the mask) is [n_u][n_t] pair elements, or [n_t][n_u] when the two indices are exchanged
-  auto pair_index = [&](int t) -> size_t { return swap ? ((size_t)t * n_u + u) : ((size_t)u * n_t + t); };
-  ln_tile_rows<Tz>(sm.A, warp, lane, ln_w, ln_b, eps, [&](int r) -> const Tz* {
-    int t = t0 + r;
-    return t < n_t ? z + pair_index(t) * kC : nullptr;
-  });
-  __syncwarp();
-  uint32_t afr[8][4];
-  load_a_frags(afr, sm.A, warp, lane);
-
-  const int g = lane >> 2, tq = lane & 3;
-  const int r0 = 16 * warp + g;
-  float m0 = 0.f, m1 = 0.f;
-  if (t0 + r0 < n_t) m0 = mask ? mask[pair_index(t0 + r0)] : 1.f;
-  if (t0 + r0 + 8 < n_t) m1 = mask ? mask[pair_index(t0 + r0 + 8)] : 1.f;
-
-  for (int q = 0; q < 8; ++q) {
-    if (q + 1 < 8) {
-      load_chunk(q + 1, (q + 1) & 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
-    float acc[8][4];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-    warp_gemm_k128<0, 8, 8>(acc, afr, sm.W[q & 1], lane);
-    bf16* S = sm.S[q & 1];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int ch = 8 * j + 2 * tq;
-      S[ch * kLdA + r0] = __float2bfloat16_rn(m0 * acc[j][0] * sigmoidf_fast(acc[j + 4][0]));
-      S[(ch + 1) * kLdA + r0] = __float2bfloat16_rn(m0 * acc[j][1] * sigmoidf_fast(acc[j + 4][1]));
-      S[ch * kLdA + r0 + 8] = __float2bfloat16_rn(m1 * acc[j][2] * sigmoidf_fast(acc[j + 4][2]));
-      S[(ch + 1) * kLdA + r0 + 8] = __float2bfloat16_rn(m1 * acc[j][3] * sigmoidf_fast(acc[j + 4][3]));
-    }
-    __syncthreads();
-    // 32 channels x 128 t: thread -> channel tid/8, 16 consecutive t
-    {
-      bf16* dst = (q < 4) ? a_out : b_out;
-      const int ch = tid >> 3, seg = tid & 7;
-      const size_t row = ((size_t)(32 * (q & 3) + ch) * n_u + u) * ld;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int t = t0 + seg * 16 + h * 8;
-        if (t < ld) {
-          uint4 v = *reinterpret_cast<const uint4*>(S + ch * kLdA + seg * 16 + h * 8);
-          *reinterpret_cast<uint4*>(dst + row + t) = v;
-        }
-      }
-    }
-  }
-}
-
+// Stage 1 (the gated input projections) lives in trimul_in_tc.cu.
 // Stage 2 (the channel-batched contraction) lives in contract_tcgen05.cu.
 
 // =========================================================================================
@@ -230,36 +144,6 @@ extern "C" int64_t px_ld(int64_t n) { return (n + 7) / 8 * 8; }
 
 static bool bad_dims(int64_t n_u, int64_t n_t, int64_t ld) {
   return n_u <= 0 || n_t <= 0 || n_u > 32768 || n_t > 32768 || ld != px_ld(n_t);
-}
-
-extern "C" int32_t px_trimul_in_proj(const void* z, int32_t z_dtype, const float* mask, const float* ln_w,
-                                     const float* ln_b, const px_bf16* w_ap, const px_bf16* w_ag,
-                                     const px_bf16* w_bp, const px_bf16* w_bg, px_bf16* a, px_bf16* b, int64_t n_u,
-                                     int64_t n_t, int64_t ld, int32_t incoming, float eps, void* stream) {
-  if (!z || !ln_w || !ln_b || !w_ap || !w_ag || !w_bp || !w_bg || !a || !b || bad_dims(n_u, n_t, ld))
-    return PX_ERR_BAD_ARG;
-  dim3 grid((unsigned)((ld + 127) / 128), (unsigned)n_u);
-  const size_t smem = sizeof(TriMulInSmem);
-  cudaStream_t st = (cudaStream_t)stream;
-  cudaError_t e;
-  if (z_dtype == PX_F32) {
-    e = cudaFuncSetAttribute(trimul_in_proj_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return PX_ERR_LAUNCH;
-    trimul_in_proj_kernel<float><<<grid, 256, smem, st>>>((const float*)z, mask, ln_w, ln_b, (const bf16*)w_ap,
-                                                          (const bf16*)w_ag, (const bf16*)w_bp, (const bf16*)w_bg,
-                                                          (bf16*)a, (bf16*)b, (int)n_u, (int)n_t, (int)ld, incoming,
-                                                          eps);
-  } else if (z_dtype == PX_BF16) {
-    e = cudaFuncSetAttribute(trimul_in_proj_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return PX_ERR_LAUNCH;
-    trimul_in_proj_kernel<bf16><<<grid, 256, smem, st>>>((const bf16*)z, mask, ln_w, ln_b, (const bf16*)w_ap,
-                                                         (const bf16*)w_ag, (const bf16*)w_bp, (const bf16*)w_bg,
-                                                         (bf16*)a, (bf16*)b, (int)n_u, (int)n_t, (int)ld, incoming,
-                                                         eps);
-  } else {
-    return PX_ERR_UNSUPPORTED;
-  }
-  return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
 }
 
 extern "C" int32_t px_trimul_out(const px_bf16* x, const void* z_in, void* z_out, int32_t z_dtype,
