@@ -120,6 +120,17 @@ template <int N>
 __device__ __forceinline__ void tma_store_wait() {
   asm volatile("cp.async.bulk.wait_group %0;\n" ::"n"(N) : "memory");
 }
+// Barrier over `threads` threads that also returns whether `ok` held on all of them, so that a group can leave a
+// loop together after one of its waits ran out.
+__device__ __forceinline__ bool named_barrier_all(int id, int threads, bool ok) {
+  uint32_t r;
+  asm volatile(
+      "{\n .reg .pred p, q;\n setp.ne.b32 q, %1, 0;\n bar.red.and.pred p, %2, %3, q;\n selp.b32 %0, 1, 0, p;\n}\n"
+      : "=r"(r)
+      : "r"((uint32_t)ok), "r"(id), "r"(threads)
+      : "memory");
+  return r != 0;
+}
 __device__ __forceinline__ void named_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory");
 }
@@ -158,7 +169,7 @@ __device__ __forceinline__ void row_stats_from_operand(const unsigned char* op, 
 // One fp32 row from global memory (nullptr = a row of zeros) -> standardised bf16 row r of the operand at `op`;
 // one thread per row.  The row is read twice (the second pass hits L1/L2).
 __device__ __forceinline__ void standardise_row_to_operand(unsigned char* op, int r, const float* __restrict__ src,
-                                                           float eps) {
+                                                           float eps, int panel_bytes = kPanelBytes) {
   float mean = 0.f, rstd = 0.f;
   if (src) {
     float s = 0.f;
@@ -189,7 +200,7 @@ __device__ __forceinline__ void standardise_row_to_operand(unsigned char* op, in
       o.z = pack_bf16x2((v1.x - mean) * rstd, (v1.y - mean) * rstd);
       o.w = pack_bf16x2((v1.z - mean) * rstd, (v1.w - mean) * rstd);
     }
-    *reinterpret_cast<uint4*>(op + operand_piece_offset(r, p)) = o;
+    *reinterpret_cast<uint4*>(op + operand_piece_offset(r, p, panel_bytes)) = o;
   }
 }
 

@@ -2,21 +2,26 @@
 //   a[c][u][t] = mask * (W_ap LN(z))_c * sigmoid((W_ag LN(z))_c),  b likewise, for the pair element (u, t),
 //   stored channel-major with the contraction index t contiguous.
 //
-// Persistent kernel, one CTA per SM, 128 pair elements (one u, 128 consecutive t) per tile.  The four weight
-// matrices stay in shared memory for the whole kernel with gamma and the 1/2 of the sigmoid folded in; LayerNorm's
-// mean and beta terms enter the product as one extra K step, so the epilogue multiplies by the row's rstd and nothing
-// else.
+// Persistent kernel, one CTA per SM.  A tile is 128 pair elements (one u, 128 consecutive t); the CTAs work in
+// pairs on the same sequence of tiles, each CTA producing 64 of the 128 channels of a and of b (the second read of
+// a tile comes from L2).  Halving the weights a CTA keeps resident leaves shared memory for output staging and
+// tensor memory for the row statistics:
+//   * The weights stay in shared memory for the whole kernel with gamma and the 1/2 of the sigmoid folded in;
+//     LayerNorm's mean and beta terms enter the product as one extra K step (see px_rowpipe.cuh).
+//   * The row statistics come from the tensor core as well: Z Z^T has the sums of squares on its diagonal, and 16
+//     rows of ones kept behind every tile in shared memory add the plain sums as columns 128..143 of that product.
+//     Variance = E[x^2] - mean^2 in fp32: accurate while |mean| is not orders of magnitude above the deviation.
+//   * The gated outputs are staged as [channel][t] in shared memory (two-byte stores, conflict-free) and leave
+//     through TMA stores, 256-byte runs per channel.
 //
-//   warps 0..7    epilogue: a thread owns one pair element (accumulator lane) and 64 of the 128 channels.  For a
-//                 fixed channel the 32 lanes of a warp hold 32 consecutive t: the channel-major output is written
-//                 as coalesced 64-byte runs, two bytes per lane.
-//   warps 8..15   two threads per row of the tile: LayerNorm statistics (bf16 rows: read from the operand that TMA
-//                 wrote; fp32 rows: read from global memory and written standardised), the correction row and the
-//                 mask value.
-//   warp 16       TMA producer of the bf16 row tiles, two-stage ring.
-//   warp 17       MMA issuer: per tile and per output (a, b) 9 MMAs M=128 (t) N=256 (projection | gate) K=16 into
-//                 one of two 256-column accumulator buffers, so the epilogue of one output overlaps the products of
-//                 the next.
+//   warps 0..7    epilogue of output a: a thread owns one pair element (accumulator lane) and 32 of the CTA's 64
+//                 channels; warps 8..15 do the same for output b, concurrently.
+//   warps 16..19  one thread per row: reads the two statistics out of tensor memory, writes the correction row,
+//                 the row's scale pair and (fp32 rows only) first converts the row into the operand.
+//   warp 20       TMA producer of the bf16 row tiles, two-stage ring.
+//   warps 21..23  MMA issuers (a tcgen05.mma costs its issuing thread 100 cycles and more, so the work is split):
+//                 warp 21 output a, warp 22 output b, each 8 MMAs M=128 (t) N=128 (projection | gate) K=16 plus the
+//                 correction step; warp 23 the statistics product (8 MMAs, N=144).
 // Algorithmic HBM traffic per pair element: 128*sizeof(Tz) + 4 read, 512 written.  Every mbarrier wait is bounded.
 #include <cstring>
 
@@ -25,68 +30,80 @@
 namespace px {
 
 constexpr int kTiStages = 2;
-constexpr int kTiSlots = kTiStages + 1;   // row-scale slots: the epilogue reads them after the operand is freed
-constexpr int kTiWPanel = 256 * 128;      // [256 rows: projection | gate][64 k] bf16
-constexpr int kTiWExtra = 256 * 32;       // [256 rows][16 k] correction panel
+constexpr int kTiSlots = kTiStages + 1;        // row-scale slots: the epilogue reads them after the operand is freed
+constexpr int kTiTilePanel = 144 * 128;        // [128 rows + 16 rows of ones][64 k] bf16
+constexpr int kTiTileBytes = 2 * kTiTilePanel;
+constexpr int kTiWExtra = 128 * 32;            // [128 rows][16 k] correction panel
 constexpr int kTiAExtra = 128 * 32;
-constexpr int kTiEpiWarps = 8;            // 4 lane quarters x 2 channel halves
-constexpr int kTiStatWarps = 8;           // two threads per row of the tile
-constexpr int kTiWarps = kTiEpiWarps + kTiStatWarps + 2;  // + TMA producer, MMA issuer
+constexpr int kTiStageOut = 64 * 256;          // [64 channels][128 t] bf16
+constexpr int kTiWarps = 24;
 constexpr int kTiThreads = 32 * kTiWarps;
+constexpr uint32_t kTiColGram = 256;           // tensor memory: out a | out b | statistics (144 columns)
 
 struct TiBars {
-  uint64_t raw_full[kTiStages], a_ready[kTiStages], a_empty[kTiStages], acc_full[2], acc_free[2];
+  uint64_t raw_full[kTiStages], a_ready[kTiStages], a_empty[kTiStages], acc_full[2], acc_free[2], gram_full, gram_free;
   uint32_t tmem_base;
 };
 struct TiLayout {
-  static constexpr int w = 0;                                   // per output: two k panels
-  static constexpr int wx = w + 4 * kTiWPanel;                  // per output: correction panel
+  static constexpr int w = 0;                                   // per output: [projection 64 | gate 64][128 k]
+  static constexpr int wx = w + 2 * kOperandBytes;              // per output: correction panel
   static constexpr int a = wx + 2 * kTiWExtra;                  // row-tile ring
-  static constexpr int ax = a + kTiStages * kOperandBytes;      // row-tile correction panels
-  static constexpr int scale = ax + kTiStages * kTiAExtra;      // float2 (rstd, rstd*mask/2) per row and slot
+  static constexpr int ax = a + kTiStages * kTiTileBytes;       // row-tile correction panels
+  static constexpr int out = ax + kTiStages * kTiAExtra;        // output staging, one buffer per output
+  static constexpr int scale = out + 2 * kTiStageOut;           // float2 (rstd, rstd*mask/2) per row and slot
   static constexpr int bars = scale + kTiSlots * 128 * 8;
   static constexpr int total = bars + (int)sizeof(TiBars);
 };
 
 template <typename Tz>
 __global__ void __launch_bounds__(kTiThreads, 1)
-trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const Tz* __restrict__ z, const float* __restrict__ mask,
+trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_a,
+                    const __grid_constant__ CUtensorMap map_b, const Tz* __restrict__ z, const float* __restrict__ mask,
                     const float* __restrict__ ln_w, const float* __restrict__ ln_b, const bf16* __restrict__ w_ap,
                     const bf16* __restrict__ w_ag, const bf16* __restrict__ w_bp, const bf16* __restrict__ w_bg,
-                    bf16* __restrict__ a_out, bf16* __restrict__ b_out, int n_u, int n_t, int ld, int swap, float eps,
-                    int tiles_t, int n_tiles) {
+                    int n_u, int n_t, int swap, float eps, int tiles_t, int n_tiles) {
   constexpr bool kTma = sizeof(Tz) == 2;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   TiBars& bars = *reinterpret_cast<TiBars*>(sm + TiLayout::bars);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chan0 = 64 * (blockIdx.x & 1);               // this CTA's channels of a and b
+  const int first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kTiStages; ++s) {
-      mbar_init(&bars.raw_full[s], 1);
-      mbar_init(&bars.a_ready[s], kTiStatWarps);
-      mbar_init(&bars.a_empty[s], 1);
+      mbar_init(&bars.raw_full[s], kTma ? 1 : 4);
+      mbar_init(&bars.a_ready[s], 4);
+      mbar_init(&bars.a_empty[s], 3);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars.acc_full[b], 1);
-      mbar_init(&bars.acc_free[b], kTiEpiWarps);
+      mbar_init(&bars.acc_free[b], 8);
     }
+    mbar_init(&bars.gram_full, 1);
+    mbar_init(&bars.gram_free, 4);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == kTiEpiWarps + kTiStatWarps) {
+  if (warp == 20) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&bars.tmem_base)),
                  "r"(512u)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
-  // weights -> resident operands; the gate rows carry the 1/2 of sigmoid(x) = 1/2 + 1/2 tanh(x/2)
   {
+    // weights -> resident operands; the gate rows carry the 1/2 of sigmoid(x) = 1/2 + 1/2 tanh(x/2)
     unsigned char* w0 = sm + TiLayout::w;
     unsigned char* x0 = sm + TiLayout::wx;
-    fold_weight_rows(w0, x0, 0, kTiWPanel, w_ap, 0, 128, ln_w, ln_b, 1.0f, warp, kTiWarps, lane);
-    fold_weight_rows(w0, x0, 128, kTiWPanel, w_ag, 0, 128, ln_w, ln_b, 0.5f, warp, kTiWarps, lane);
-    fold_weight_rows(w0 + 2 * kTiWPanel, x0 + kTiWExtra, 0, kTiWPanel, w_bp, 0, 128, ln_w, ln_b, 1.0f, warp, kTiWarps, lane);
-    fold_weight_rows(w0 + 2 * kTiWPanel, x0 + kTiWExtra, 128, kTiWPanel, w_bg, 0, 128, ln_w, ln_b, 0.5f, warp, kTiWarps, lane);
+    fold_weight_rows(w0, x0, 0, kPanelBytes, w_ap, chan0, 64, ln_w, ln_b, 1.0f, warp, kTiWarps, lane);
+    fold_weight_rows(w0, x0, 64, kPanelBytes, w_ag, chan0, 64, ln_w, ln_b, 0.5f, warp, kTiWarps, lane);
+    fold_weight_rows(w0 + kOperandBytes, x0 + kTiWExtra, 0, kPanelBytes, w_bp, chan0, 64, ln_w, ln_b, 1.0f, warp, kTiWarps, lane);
+    fold_weight_rows(w0 + kOperandBytes, x0 + kTiWExtra, 64, kPanelBytes, w_bg, chan0, 64, ln_w, ln_b, 0.5f, warp, kTiWarps, lane);
+    // the 16 rows of ones behind every tile panel (never overwritten: a tile load covers 128 rows)
+    for (int i = threadIdx.x; i < kTiStages * 2 * 16 * 8; i += kTiThreads) {
+      const int panel = i >> 7, piece = i & 127;
+      *reinterpret_cast<uint4*>(sm + TiLayout::a + panel * kTiTilePanel + 128 * 128 + piece * 16) =
+          make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
+    }
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
   tc_fence_before();
@@ -95,152 +112,165 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const Tz* __restr
   const uint32_t tmem_base = bars.tmem_base;
   if (warp == 0) { ROW_TRACE(12, 0); }
 
-  if (warp >= kTiEpiWarps + kTiStatWarps) {
-    if (warp == kTiEpiWarps + kTiStatWarps && lane == 0 && kTma) {
+  if (warp >= 20) {
+    if (warp == 20 && lane == 0 && kTma) {
       // ---------------------------------------------------------------- row-tile producer (bf16 rows)
       int k = 0;
-      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++k) {
+      for (int tile = first_tile; tile < n_tiles; tile += tile_step, ++k) {
         const int s = k % kTiStages, n = k / kTiStages;
         if (!mbar_wait(&bars.a_empty[s], (n & 1) ^ 1, 1u)) break;
         ROW_TRACE(0, k);
         const int u = tile / tiles_t, t0 = (tile % tiles_t) * 128;
         mbar_expect_tx(&bars.raw_full[s], kOperandBytes);
-        const uint32_t dst = smem_u32(sm + TiLayout::a + s * kOperandBytes);
+        const uint32_t dst = smem_u32(sm + TiLayout::a + s * kTiTileBytes);
         for (int p = 0; p < 2; ++p)
-          tma_load_3d(dst + p * kPanelBytes, &map_z, &bars.raw_full[s], 64 * p, swap ? u : t0, swap ? t0 : u);
+          tma_load_3d(dst + p * kTiTilePanel, &map_z, &bars.raw_full[s], 64 * p, swap ? u : t0, swap ? t0 : u);
       }
-    } else if (warp == kTiEpiWarps + kTiStatWarps + 1 && lane == 0) {
-      // ---------------------------------------------------------------- MMA issuer
-      constexpr uint32_t idesc = umma_idesc_bf16(128, 256);
-      const uint32_t w_addr = smem_u32(sm + TiLayout::w), wx_addr = smem_u32(sm + TiLayout::wx);
+    } else if ((warp == 21 || warp == 22) && lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer of output ph
+      const int ph = warp - 21;
+      constexpr uint32_t idesc = umma_idesc_bf16(128, 128);
+      const uint32_t wm = smem_u32(sm + TiLayout::w) + ph * kOperandBytes;
+      const uint64_t wx_desc = umma_desc_sw32(smem_u32(sm + TiLayout::wx) + ph * kTiWExtra);
       int k = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++k) {
+      for (int tile = first_tile; tile < n_tiles && ok; tile += tile_step, ++k) {
         const int s = k % kTiStages, n = k / kTiStages;
-        // The products over the stored rows need only the tile; the correction step waits for the statistics,
-        // which are computed meanwhile.
-        if (kTma) {
-          ok = mbar_wait(&bars.raw_full[s], n & 1, 2u);
-        } else {
-          ok = mbar_wait(&bars.a_ready[s], n & 1, 4u);
-        }
+        ok = mbar_wait(&bars.raw_full[s], n & 1, 2u);
         if (!ok) break;
-        ROW_TRACE(1, k);
-        const uint32_t a_addr = smem_u32(sm + TiLayout::a + s * kOperandBytes);
-        const uint64_t ax_desc = umma_desc_sw32(smem_u32(sm + TiLayout::ax + s * kTiAExtra));
-        for (int ph = 0; ph < 2 && ok; ++ph) {
-          ok = mbar_wait(&bars.acc_free[ph], (k & 1) ^ 1, 8u);
-          if (!ok) break;
-          ROW_TRACE(2 + 2 * ph, k);
-          tc_fence_after();
-          const uint32_t wm = w_addr + 2 * ph * kTiWPanel;
+        const uint32_t a_addr = smem_u32(sm + TiLayout::a + s * kTiTileBytes);
+        ok = mbar_wait(&bars.acc_free[ph], (k & 1) ^ 1, 8u);
+        if (!ok) break;
+        ROW_TRACE(2 + 2 * ph, k);
+        tc_fence_after();
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks)
-            umma_bf16(tmem_base + 256 * ph, umma_desc_sw128(a_addr + (ks >> 2) * kPanelBytes) + 2 * (ks & 3),
-                      umma_desc_sw128(wm + (ks >> 2) * kTiWPanel) + 2 * (ks & 3), idesc, ks ? 1u : 0u);
-          if (kTma && ph == 0) {
-            ok = mbar_wait(&bars.a_ready[s], n & 1, 4u);
-            if (!ok) break;
-            tc_fence_after();
-          }
-          umma_bf16(tmem_base + 256 * ph, ax_desc, umma_desc_sw32(wx_addr + ph * kTiWExtra), idesc, 1u);
-          umma_commit(&bars.acc_full[ph]);
-          ROW_TRACE(3 + 2 * ph, k);
+        for (int ks = 0; ks < 8; ++ks)
+          umma_bf16(tmem_base + 128 * ph, umma_desc_sw128(a_addr + (ks >> 2) * kTiTilePanel) + 2 * (ks & 3),
+                    umma_desc_sw128(wm + (ks >> 2) * kPanelBytes) + 2 * (ks & 3), idesc, ks ? 1u : 0u);
+        ok = mbar_wait(&bars.a_ready[s], n & 1, 4u);       // the correction step needs the statistics
+        if (!ok) break;
+        tc_fence_after();
+        umma_bf16(tmem_base + 128 * ph, umma_desc_sw32(smem_u32(sm + TiLayout::ax + s * kTiAExtra)), wx_desc, idesc, 1u);
+        umma_commit(&bars.acc_full[ph]);
+        umma_commit(&bars.a_empty[s]);                     // this thread's share of the reads of the stage
+        ROW_TRACE(3 + 2 * ph, k);
+      }
+    } else if (warp == 23 && lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer of the statistics product
+      constexpr uint32_t idesc_gram = umma_idesc_bf16(128, 144);
+      int k = 0;
+      for (int tile = first_tile; tile < n_tiles; tile += tile_step, ++k) {
+        const int s = k % kTiStages, n = k / kTiStages;
+        if (!mbar_wait(&bars.raw_full[s], n & 1, 2u) || !mbar_wait(&bars.gram_free, (k & 1) ^ 1, 2u)) break;
+        ROW_TRACE(1, k);
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(sm + TiLayout::a + s * kTiTileBytes);
+        // Z Z^T (diagonal = sums of squares) | Z 1 (sums)
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t d = umma_desc_sw128(a_addr + (ks >> 2) * kTiTilePanel) + 2 * (ks & 3);
+          umma_bf16(tmem_base + kTiColGram, d, d, idesc_gram, ks ? 1u : 0u);
         }
-        if (ok) umma_commit(&bars.a_empty[s]);
+        umma_commit(&bars.gram_full);
+        umma_commit(&bars.a_empty[s]);
       }
     }
-  } else if (warp >= kTiEpiWarps) {
-    // ------------------------------------------------------------------ row statistics, two threads per row
-    const int r = (threadIdx.x - 32 * kTiEpiWarps) >> 1, half = threadIdx.x & 1;
+  } else if (warp >= 16) {
+    // ------------------------------------------------------------------ row statistics, one thread per row
+    const int qw = warp - 16, r = 32 * qw + lane;
+    const uint32_t t_gram = tmem_base + ((uint32_t)(32 * qw) << 16) + kTiColGram;
     int k = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++k) {
+    for (int tile = first_tile; tile < n_tiles; tile += tile_step, ++k) {
       const int s = k % kTiStages, n = k / kTiStages;
       const int u = tile / tiles_t, t = (tile % tiles_t) * 128 + r;
-      unsigned char* op = sm + TiLayout::a + s * kOperandBytes;
       const size_t pair = swap ? ((size_t)t * n_u + u) : ((size_t)u * n_t + t);
       float mk = 0.f;
-      if (t < n_t && half == 0) mk = mask ? __ldg(mask + pair) : 1.f;
-      float mean = 0.f, rstd = 1.f;
-      if (kTma) {
-        ok = mbar_wait(&bars.raw_full[s], n & 1, 16u);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        if (warp == kTiEpiWarps) { ROW_TRACE(6, k); }
-        row_stats_from_operand(op, r, half, eps, mean, rstd);
-      } else {
+      if (t < n_t) mk = mask ? __ldg(mask + pair) : 1.f;
+      if (!kTma) {
+        // fp32 rows: standardised while they are converted into the operand
         ok = mbar_wait(&bars.a_empty[s], (n & 1) ^ 1, 16u);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (half == 0)
-          standardise_row_to_operand(op, r, t < n_t ? reinterpret_cast<const float*>(z) + pair * kC : nullptr, eps);
+        standardise_row_to_operand(sm + TiLayout::a + s * kTiTileBytes, r,
+                                   t < n_t ? reinterpret_cast<const float*>(z) + pair * kC : nullptr, eps, kTiTilePanel);
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars.raw_full[s]);
       }
-      if (half == 0) {
-        // rstd * (W'x - mean * s + std * t): the row side of the correction step holds (-mean, std)
-        write_correction_row(sm + TiLayout::ax + s * kTiAExtra, r, -mean, 1.0f / rstd, false);
-        reinterpret_cast<float2*>(sm + TiLayout::scale)[(k % kTiSlots) * 128 + r] = make_float2(rstd, 0.5f * rstd * mk);
-      }
+      ok = mbar_wait(&bars.gram_full, k & 1, 16u);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (warp == 16) { ROW_TRACE(6, k); }
+      tc_fence_after();
+      uint32_t diag[32], sums[16];
+      tmem_ld32(t_gram + 32 * qw, diag);
+      tmem_ld16(t_gram + 128, sums);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars.gram_free);
+      const float mean = __uint_as_float(sums[0]) * (1.0f / kC);
+      const float var = fmaxf(select_own(diag, lane) * (1.0f / kC) - mean * mean, 0.f);
+      const float rstd = rsqrtf(var + eps);
+      // rstd * (W'x - mean * s + std * t): the row side of the correction step holds (-mean, std)
+      write_correction_row(sm + TiLayout::ax + s * kTiAExtra, r, -mean, sqrtf(var + eps), false);
+      reinterpret_cast<float2*>(sm + TiLayout::scale)[(k % kTiSlots) * 128 + r] = make_float2(rstd, 0.5f * rstd * mk);
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars.a_ready[s]);
-      if (warp == kTiEpiWarps) { ROW_TRACE(7, k); }
+      if (warp == 16) { ROW_TRACE(7, k); }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue
-    const int part = warp >> 2, qw = warp & 3;
+    // ------------------------------------------------------------------ epilogue of output ph
+    const int ph = warp >> 3, half = (warp >> 2) & 1, qw = warp & 3;
     const int row = 32 * qw + lane;                      // this thread's pair element = accumulator lane
-    const uint32_t t_acc = tmem_base + ((uint32_t)(32 * qw) << 16);
-    const int ch_stride = n_u * ld;                      // elements between channels (both factors <= 32768)
+    const uint32_t t_acc = tmem_base + ((uint32_t)(32 * qw) << 16) + 128 * ph + 32 * half;
+    const bool leader = (threadIdx.x & 255) == 0;
+    const CUtensorMap* map_out = ph ? &map_b : &map_a;
+    unsigned char* stage = sm + TiLayout::out + ph * kTiStageOut + (32 * half) * 256 + row * 2;
     int k = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++k) {
-      const int u = tile / tiles_t, t = (tile % tiles_t) * 128 + row;
-      const bool live = t < ld;
+    for (int tile = first_tile; tile < n_tiles && ok; tile += tile_step, ++k) {
+      const int u = tile / tiles_t, t0 = (tile % tiles_t) * 128;
+      ok = mbar_wait(&bars.acc_full[ph], k & 1, 32u);
+      // the store that last read the staging buffer (one tile ago) must be through with it
+      if (leader) tma_store_wait_read<0>();
+      ok = named_barrier_all(1 + ph, 256, ok);             // all eight warps go on, or none
+      if (!ok) break;
+      if ((warp & 7) == 0) { ROW_TRACE(8 + 2 * ph, k); }
+      tc_fence_after();
+      const float2 sc = reinterpret_cast<const float2*>(sm + TiLayout::scale)[(k % kTiSlots) * 128 + row];
+      // mask * p * sigmoid(g) = h + h * tanh(g / 2) with h = mask * p / 2 (the halves are folded in)
+      auto emit = [&](const uint32_t(&p)[16], const uint32_t(&g)[16], int hh) {
 #pragma unroll
-      for (int ph = 0; ph < 2; ++ph) {
-        ok = mbar_wait(&bars.acc_full[ph], k & 1, 32u);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        if (warp == 0) { ROW_TRACE(8 + 2 * ph, k); }
-        tc_fence_after();
-        const float2 sc = reinterpret_cast<const float2*>(sm + TiLayout::scale)[(k % kTiSlots) * 128 + row];
-        bf16* dst = (ph ? b_out : a_out) + ((size_t)(64 * part) * n_u + u) * ld + t;
-        const uint32_t t_p = t_acc + 256 * ph + 64 * part, t_g = t_p + 128;
-        // 16 channels: mask * p * sigmoid(g) = h + h * tanh(g / 2) with h = mask * p / 2 (the halves are folded in)
-        auto emit = [&](const uint32_t(&p)[16], const uint32_t(&g)[16]) {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const float h = sc.y * __uint_as_float(p[e]);
-            const float v = fmaf(h, tanh_fast(sc.x * __uint_as_float(g[e])), h);
-            if (live) store_bf16_int(dst, v);
-            dst += ch_stride;
-          }
-        };
-        // two register sets: the next 16 columns are on their way while the current ones are worked on
-        uint32_t p0[16], g0[16], p1[16], g1[16];
-        tmem_ld16(t_p, p0);
-        tmem_ld16(t_g, g0);
-#pragma unroll 1
-        for (int jj = 0; jj < 4; jj += 2) {
-          tmem_wait_ld();
-          tmem_ld16(t_p + 16 * (jj + 1), p1);
-          tmem_ld16(t_g + 16 * (jj + 1), g1);
-          emit(p0, g0);
-          tmem_wait_ld();
-          if (jj == 0) {
-            tmem_ld16(t_p + 32, p0);
-            tmem_ld16(t_g + 32, g0);
-          } else {                                       // this warp has read its part of the buffer
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars.acc_free[ph]);
-          }
-          emit(p1, g1);
+        for (int e = 0; e < 16; ++e) {
+          const float h = sc.y * __uint_as_float(p[e]);
+          const float v = fmaf(h, tanh_fast(sc.x * __uint_as_float(g[e])), h);
+          *reinterpret_cast<unsigned short*>(stage + (16 * hh + e) * 256) =
+              (unsigned short)((__float_as_uint(v) + 0x8000u) >> 16);
         }
-        if (warp == 0) { ROW_TRACE(9 + 2 * ph, k); }
+      };
+      uint32_t p0[16], g0[16], p1[16], g1[16];
+      tmem_ld16(t_acc, p0);
+      tmem_ld16(t_acc + 64, g0);
+      tmem_ld16(t_acc + 16, p1);
+      tmem_ld16(t_acc + 64 + 16, g1);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars.acc_free[ph]);      // this warp has read its part of the accumulator
+      emit(p0, g0, 0);
+      emit(p1, g1, 1);
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      named_barrier(1 + ph, 256);
+      if (leader) {
+        tma_store_3d(map_out, smem_u32(sm + TiLayout::out + ph * kTiStageOut), t0, u, chan0);
+        tma_store_commit();
       }
+      if ((warp & 7) == 0) { ROW_TRACE(9 + 2 * ph, k); }
     }
+    if (leader) tma_store_wait<0>();
   }
 
   tc_fence_before();
@@ -251,7 +281,7 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const Tz* __restr
     }
     __syncthreads();
   }
-  if (warp == kTiEpiWarps + kTiStatWarps) {
+  if (warp == 20) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
   }
@@ -275,7 +305,7 @@ static int32_t launch_trimul_in(const void* z, const float* mask, const float* l
                                 const px_bf16* w_ap, const px_bf16* w_ag, const px_bf16* w_bp, const px_bf16* w_bg,
                                 px_bf16* a, px_bf16* b, int64_t n_u, int64_t n_t, int64_t ld, int32_t incoming, float eps,
                                 cudaStream_t st) {
-  CUtensorMap mz;
+  CUtensorMap mz, ma, mb;
   if (sizeof(Tz) == 2) {
     // pair element (u, t) is row u*n_t + t of z, or row t*n_u + u when the two indices are exchanged
     const bool ok = incoming ? make_map_3d(&mz, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, z, 128, (uint64_t)n_u, (uint64_t)n_t,
@@ -286,15 +316,22 @@ static int32_t launch_trimul_in(const void* z, const float* mask, const float* l
   } else {
     memset(&mz, 0, sizeof(mz));
   }
+  // outputs [128 channels][n_u][ld]: a store writes [64 channels][one u][128 t]
+  if (!make_map_3d(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a, (uint64_t)ld, (uint64_t)n_u, 128, (uint64_t)ld * 2,
+                   (uint64_t)n_u * ld * 2, 128, 1, CU_TENSOR_MAP_SWIZZLE_NONE, 64) ||
+      !make_map_3d(&mb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, b, (uint64_t)ld, (uint64_t)n_u, 128, (uint64_t)ld * 2,
+                   (uint64_t)n_u * ld * 2, 128, 1, CU_TENSOR_MAP_SWIZZLE_NONE, 64))
+    return PX_ERR_LAUNCH;
   const size_t smem = TiLayout::total + 1024;
   if (cudaFuncSetAttribute(trimul_in_tc_kernel<Tz>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return PX_ERR_LAUNCH;
   const int64_t tiles_t = (ld + 127) / 128, n_tiles = tiles_t * n_u;
   if (n_tiles > 0x7fffffff) return PX_ERR_UNSUPPORTED;
-  const int grid = (int)(n_tiles < sm_count() ? n_tiles : sm_count());
-  trimul_in_tc_kernel<Tz><<<grid, kTiThreads, smem, st>>>(mz, (const Tz*)z, mask, ln_w, ln_b, (const bf16*)w_ap, (const bf16*)w_ag,
-                                                   (const bf16*)w_bp, (const bf16*)w_bg, (bf16*)a, (bf16*)b, (int)n_u,
-                                                   (int)n_t, (int)ld, incoming, eps, (int)tiles_t, (int)n_tiles);
+  const int pairs = (int)(n_tiles < sm_count() / 2 ? n_tiles : sm_count() / 2);
+  trimul_in_tc_kernel<Tz><<<2 * pairs, kTiThreads, smem, st>>>(mz, ma, mb, (const Tz*)z, mask, ln_w, ln_b, (const bf16*)w_ap,
+                                                               (const bf16*)w_ag, (const bf16*)w_bp, (const bf16*)w_bg,
+                                                               (int)n_u, (int)n_t, incoming, eps, (int)tiles_t,
+                                                               (int)n_tiles);
   return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
 }
 
