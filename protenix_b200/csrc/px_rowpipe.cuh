@@ -204,6 +204,162 @@ __device__ __forceinline__ void standardise_row_to_operand(unsigned char* op, in
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Row tiles: the part of the pipeline that is the same for every kernel that consumes LayerNorm'd pair rows.
+// A tile is 128 pair elements (one u, 128 consecutive t); element (u, t) is row u*n_t + t of z, or row t*n_u + u when
+// the two indices are exchanged (`swap`).  A stage of the ring holds the tile as two k panels of 144 rows (the
+// last 16 rows are ones, see below) and the tile's correction panel.
+//   * producer thread: TMA loads of bf16 rows (fp32 rows are converted by the statistics threads instead);
+//   * statistics issuer thread: Z Z^T | Z 1 (M=128, N=144) into tensor memory: the diagonal holds each row's sum
+//     of squares and columns 128..143 its plain sum;
+//   * statistics threads (one per row): variance = E[x^2] - mean^2 in fp32 (accurate while |mean| is not orders of
+//     magnitude above the deviation), correction row (-mean, std), and whatever the kernel wants per row.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kTileStages = 2;
+constexpr int kTileSlots = kTileStages + 1;    // per-row scale slots: read by the epilogue after the stage is freed
+constexpr int kTilePanel = 144 * 128;          // [128 rows + 16 rows of ones][64 k] bf16
+constexpr int kTileBytes = 2 * kTilePanel;
+constexpr int kTileExtra = 128 * 32;           // [128 rows][16 k] correction panel
+constexpr int kTileRing = kTileStages * (kTileBytes + kTileExtra);
+constexpr uint32_t kGramCols = 144;
+
+struct TileBars {
+  // raw_full: tile in shared memory; a_ready: statistics, correction rows and scales written;
+  // a_empty: every MMA that reads the stage is complete (one commit per issuing thread)
+  uint64_t raw_full[kTileStages], a_ready[kTileStages], a_empty[kTileStages], gram_full, gram_free;
+};
+struct TileCtx {
+  unsigned char* tiles;     // kTileStages x kTileBytes
+  unsigned char* extras;    // kTileStages x kTileExtra
+  TileBars* bars;
+  int first_tile, tile_step, n_tiles, tiles_t, n_u, n_t, swap;
+};
+
+__device__ __forceinline__ void tile_bars_init(TileBars& b, bool tma, int issuers) {
+  for (int s = 0; s < kTileStages; ++s) {
+    mbar_init(&b.raw_full[s], tma ? 1 : 4);
+    mbar_init(&b.a_ready[s], 4);
+    mbar_init(&b.a_empty[s], issuers);
+  }
+  mbar_init(&b.gram_full, 1);
+  mbar_init(&b.gram_free, 4);
+}
+
+// The 16 rows of ones behind every tile panel (never overwritten: a tile load covers 128 rows).
+__device__ __forceinline__ void tile_write_ones(unsigned char* tiles, int tid, int nthreads) {
+  for (int i = tid; i < kTileStages * 2 * 16 * 8; i += nthreads) {
+    const int panel = i >> 7, piece = i & 127;
+    *reinterpret_cast<uint4*>(tiles + panel * kTilePanel + 128 * 128 + piece * 16) =
+        make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
+  }
+}
+
+// One thread: TMA loads of the bf16 tiles.
+__device__ __forceinline__ void tile_producer_loop(const TileCtx& c, const CUtensorMap* map_z) {
+  int k = 0;
+  for (int tile = c.first_tile; tile < c.n_tiles; tile += c.tile_step, ++k) {
+    const int s = k % kTileStages, n = k / kTileStages;
+    if (!mbar_wait(&c.bars->a_empty[s], (n & 1) ^ 1, 1u)) break;
+    const int u = tile / c.tiles_t, t0 = (tile % c.tiles_t) * 128;
+    mbar_expect_tx(&c.bars->raw_full[s], kOperandBytes);
+    const uint32_t dst = smem_u32(c.tiles + s * kTileBytes);
+    for (int p = 0; p < 2; ++p)
+      tma_load_3d(dst + p * kTilePanel, map_z, &c.bars->raw_full[s], 64 * p, c.swap ? u : t0, c.swap ? t0 : u);
+  }
+}
+
+// One thread: the statistics product of every tile into tensor-memory columns [gram_col, gram_col + 144).
+__device__ __forceinline__ void tile_gram_loop(const TileCtx& c, uint32_t tmem_gram) {
+  constexpr uint32_t idesc_gram = umma_idesc_bf16(128, kGramCols);
+  int k = 0;
+  for (int tile = c.first_tile; tile < c.n_tiles; tile += c.tile_step, ++k) {
+    const int s = k % kTileStages, n = k / kTileStages;
+    if (!mbar_wait(&c.bars->raw_full[s], n & 1, 2u) || !mbar_wait(&c.bars->gram_free, (k & 1) ^ 1, 2u)) break;
+    tc_fence_after();
+    const uint32_t a_addr = smem_u32(c.tiles + s * kTileBytes);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const uint64_t d = umma_desc_sw128(a_addr + (ks >> 2) * kTilePanel) + 2 * (ks & 3);
+      umma_bf16(tmem_gram, d, d, idesc_gram, ks ? 1u : 0u);
+    }
+    umma_commit(&c.bars->gram_full);
+    umma_commit(&c.bars->a_empty[s]);
+  }
+}
+
+// Four warps, one thread per row (`qw` = warp's lane quarter, 0..3).  per_row(k, u, t, r, rstd) is called once per
+// tile and row with the row's 1/std, before a_ready is signalled.
+template <typename Tz, typename PerRow>
+__device__ __forceinline__ void tile_stats_loop(const TileCtx& c, const Tz* __restrict__ z, float eps, uint32_t tmem_gram,
+                                                int qw, int lane, PerRow per_row) {
+  constexpr bool kTma = sizeof(Tz) == 2;
+  const int r = 32 * qw + lane;
+  const uint32_t t_gram = tmem_gram + ((uint32_t)(32 * qw) << 16);
+  int k = 0;
+  bool ok = true;
+  for (int tile = c.first_tile; tile < c.n_tiles; tile += c.tile_step, ++k) {
+    const int s = k % kTileStages, n = k / kTileStages;
+    const int u = tile / c.tiles_t, t = (tile % c.tiles_t) * 128 + r;
+    if (!kTma) {
+      // fp32 rows: standardised while they are converted into the operand
+      ok = mbar_wait(&c.bars->a_empty[s], (n & 1) ^ 1, 16u);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const size_t pair = c.swap ? ((size_t)t * c.n_u + u) : ((size_t)u * c.n_t + t);
+      standardise_row_to_operand(c.tiles + s * kTileBytes, r,
+                                 t < c.n_t ? reinterpret_cast<const float*>(z) + pair * kC : nullptr, eps, kTilePanel);
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&c.bars->raw_full[s]);
+    }
+    ok = mbar_wait(&c.bars->gram_full, k & 1, 16u);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;
+    tc_fence_after();
+    uint32_t diag[32], sums[16];
+    tmem_ld32(t_gram + 32 * qw, diag);
+    tmem_ld16(t_gram + 128, sums);
+    tmem_wait_ld();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&c.bars->gram_free);
+    const float mean = __uint_as_float(sums[0]) * (1.0f / kC);
+    const float var = fmaxf(select_own(diag, lane) * (1.0f / kC) - mean * mean, 0.f);
+    const float rstd = rsqrtf(var + eps);
+    // rstd * (W'x - mean * s + std * t): the row side of the correction step holds (-mean, std)
+    write_correction_row(c.extras + s * kTileExtra, r, -mean, sqrtf(var + eps), false);
+    per_row(k, u, t, r, rstd);
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&c.bars->a_ready[s]);
+  }
+}
+
+// One thread: for every tile, 8 MMAs M=128 (rows) x N (weight rows of `w_addr`, two k panels of w_panel bytes) into
+// tensor-memory column d_col, then the correction step against the weight-side panel at wx_addr; acc_free/acc_full
+// hand the accumulator back and forth with the epilogue warps (`free_parity_flip`: 1 for a single buffer).
+__device__ __forceinline__ void tile_product_loop(const TileCtx& c, uint32_t d_tmem, uint32_t w_addr, int w_panel,
+                                                  uint32_t wx_addr, uint32_t idesc, uint64_t* acc_full,
+                                                  uint64_t* acc_free) {
+  const uint64_t wx_desc = umma_desc_sw32(wx_addr);
+  int k = 0;
+  for (int tile = c.first_tile; tile < c.n_tiles; tile += c.tile_step, ++k) {
+    const int s = k % kTileStages, n = k / kTileStages;
+    if (!mbar_wait(&c.bars->raw_full[s], n & 1, 4u) || !mbar_wait(acc_free, (k & 1) ^ 1, 8u)) break;
+    tc_fence_after();
+    const uint32_t a_addr = smem_u32(c.tiles + s * kTileBytes);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks)
+      umma_bf16(d_tmem, umma_desc_sw128(a_addr + (ks >> 2) * kTilePanel) + 2 * (ks & 3),
+                umma_desc_sw128(w_addr + (ks >> 2) * w_panel) + 2 * (ks & 3), idesc, ks ? 1u : 0u);
+    if (!mbar_wait(&c.bars->a_ready[s], n & 1, 4u)) break;   // the correction step needs the statistics
+    tc_fence_after();
+    umma_bf16(d_tmem, umma_desc_sw32(smem_u32(c.extras + s * kTileExtra)), wx_desc, idesc, 1u);
+    umma_commit(acc_full);
+    umma_commit(&c.bars->a_empty[s]);                        // this thread's share of the reads of the stage
+  }
+}
+
 // Number of SMs of the current device (cached per device ordinal).
 static inline int sm_count() {
   static int cached[64] = {};

@@ -8,129 +8,7 @@ namespace px {
 constexpr int kH = 4;   // heads
 constexpr int kD = 32;  // head width
 
-// =========================================================================================
-// Stage 1: LN(z) -> q,k,v [u][h][t][32] (q pre-scaled), bias[h][u][t], mask_bias[u][t].
-// One CTA = (u, 128 consecutive t).  Pair element for (u,t): z[u][t] (starting) or z[t][u] (ending).
-// HBM-bound: reads 128*sizeof(Tz)+4, writes 3*256 + 16 + 4/.. bytes per pair element.
-// =========================================================================================
-struct TriAttInSmem {
-  bf16 A[128 * kLdA];
-  bf16 W[2][64 * kLdA];
-  bf16 S[64 * kLdA];  // transposed staging of a v chunk: [channel][t]
-};
-
-template <typename Tz>
-__global__ void __launch_bounds__(256, 2)
-triatt_in_proj_kernel(const Tz* __restrict__ z, const float* __restrict__ mask, const float* __restrict__ ln_w,
-                      const float* __restrict__ ln_b, const bf16* __restrict__ w_q, const bf16* __restrict__ w_k,
-                      const bf16* __restrict__ w_v, const bf16* __restrict__ w_bias, bf16* __restrict__ q_out,
-                      bf16* __restrict__ k_out, bf16* __restrict__ v_out, float* __restrict__ bias_out,
-                      float* __restrict__ mb_out, int n_u, int n, int ldm, int ldt, int swap, float eps, float inf) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  TriAttInSmem& sm = *reinterpret_cast<TriAttInSmem*>(smem_raw);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int u = blockIdx.y, t0 = blockIdx.x * 128;
-
-  auto load_chunk = [&](int c, int buf) {
-    if (c < 6) {
-      const bf16* w = (c < 2) ? w_q : (c < 4 ? w_k : w_v);
-      load_w_rows(sm.W[buf], 0, w, 64 * (c & 1), 64, tid);
-    } else {  // bias projection: 4 real rows, rows 4..15 zero
-      const int r = tid >> 4, ch = tid & 15;
-      cp_async16(smem_u32(sm.W[buf] + r * kLdA + ch * 8), w_bias + (size_t)(r < kH ? r : 0) * kC + ch * 8, r < kH);
-    }
-    cp_async_commit();
-  };
-  load_chunk(0, 0);
-
-  // z (and the mask) is [n_u][n] pair elements, or [n][n_u] when the two indices are exchanged
-  auto pair_index = [&](int t) -> size_t { return swap ? ((size_t)t * n_u + u) : ((size_t)u * n + t); };
-  ln_tile_rows<Tz>(sm.A, warp, lane, ln_w, ln_b, eps, [&](int r) -> const Tz* {
-    int t = t0 + r;
-    return t < n ? z + pair_index(t) * kC : nullptr;
-  });
-  __syncwarp();
-  uint32_t afr[8][4];
-  load_a_frags(afr, sm.A, warp, lane);
-
-  if (tid < 128) {  // mask bias, -inf in the pad columns [n, ldm)
-    const int t = t0 + tid;
-    if (t < ldm) {
-      float mv = -CUDART_INF_F;
-      if (t < n) mv = mask ? (mask[pair_index(t)] - 1.0f) * inf * kLog2e : 0.f;
-      mb_out[(size_t)u * ldm + t] = mv;
-    }
-  }
-
-  const int g = lane >> 2, tq = lane & 3;
-  const int tr = t0 + 16 * warp + g;
-  const float qscale = kLog2e * rsqrtf((float)kD);
-  for (int c = 0; c < 7; ++c) {
-    if (c + 1 < 7) {
-      load_chunk(c + 1, (c + 1) & 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
-    float acc[8][4];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-    if (c >= 4 && c < 6) {
-      // v is stored transposed, [u][h][d][t] with t contiguous (row stride ldt, zero pad columns), so
-      // that the value tile is a K-major operand of the P.V product
-      warp_gemm_k128<0, 8, 8>(acc, afr, sm.W[c & 1], lane);
-      const int r0 = 16 * warp + g;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int ch = 8 * j + 2 * tq;
-        sm.S[ch * kLdA + r0] = __float2bfloat16_rn(acc[j][0]);
-        sm.S[(ch + 1) * kLdA + r0] = __float2bfloat16_rn(acc[j][1]);
-        sm.S[ch * kLdA + r0 + 8] = __float2bfloat16_rn(acc[j][2]);
-        sm.S[(ch + 1) * kLdA + r0 + 8] = __float2bfloat16_rn(acc[j][3]);
-      }
-      __syncthreads();
-      {
-        const int ch = tid >> 2, seg = tid & 3;  // 64 channels x 4 segments of 32 t
-        const size_t row = (((size_t)u * kH + 2 * (c & 1) + (ch >> 5)) * kD + (ch & 31)) * ldt;
-#pragma unroll
-        for (int h8 = 0; h8 < 4; ++h8) {
-          const int t = t0 + seg * 32 + h8 * 8;
-          if (t < ldt)
-            *reinterpret_cast<uint4*>(v_out + row + t) =
-                *reinterpret_cast<const uint4*>(sm.S + ch * kLdA + seg * 32 + h8 * 8);
-        }
-      }
-    } else if (c < 4) {
-      warp_gemm_k128<0, 8, 8>(acc, afr, sm.W[c & 1], lane);
-      bf16* dst = (c < 2) ? q_out : k_out;
-      const float sc = (c < 2) ? qscale : 1.0f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int head = 2 * (c & 1) + (j >> 2);
-        const int d = (j & 3) * 8 + 2 * tq;
-        const size_t base = ((size_t)u * kH + head) * n;
-        if (tr < n)
-          *reinterpret_cast<uint32_t*>(dst + (base + tr) * kD + d) = pack_bf16x2(acc[j][0] * sc, acc[j][1] * sc);
-        if (tr + 8 < n)
-          *reinterpret_cast<uint32_t*>(dst + (base + tr + 8) * kD + d) = pack_bf16x2(acc[j][2] * sc, acc[j][3] * sc);
-      }
-    } else {
-      warp_gemm_k128<0, 2, 8>(acc, afr, sm.W[c & 1], lane);
-      if (tq < 2) {
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int head = 2 * tq + e;
-          // zero in the pad columns [n, ldm)
-          if (tr < ldm) bias_out[((size_t)head * n_u + u) * ldm + tr] = tr < n ? acc[0][e] * kLog2e : 0.f;
-          if (tr + 8 < ldm) bias_out[((size_t)head * n_u + u) * ldm + tr + 8] = tr + 8 < n ? acc[0][2 + e] * kLog2e : 0.f;
-        }
-      }
-    }
-    __syncthreads();
-  }
-}
-
+// Stage 1 (the q, k, v and bias projections) lives in triatt_in_tc.cu.
 // Stage 2 (the attention core) lives in flash_tcgen05.cu.
 
 // =========================================================================================
@@ -234,43 +112,6 @@ static size_t align256(size_t b) { return (b + 255) / 256 * 256; }
 }  // namespace px
 
 using namespace px;
-
-static bool att_bad_dims(int64_t n_u, int64_t n, int64_t ldm) {
-  return n_u <= 0 || n <= 0 || n_u > 32768 || n > 32768 || ldm != px_ld_mask(n);
-}
-
-extern "C" int32_t px_triatt_in_proj(const void* z, int32_t z_dtype, const float* mask, const float* ln_w,
-                                     const float* ln_b, const px_bf16* w_q, const px_bf16* w_k, const px_bf16* w_v,
-                                     const px_bf16* w_bias, px_bf16* q, px_bf16* k, px_bf16* v, float* bias,
-                                     float* mask_bias, int64_t n_u, int64_t n_t, int64_t ldm, int32_t ending,
-                                     float eps, float inf, void* stream) {
-  if (!z || !ln_w || !ln_b || !w_q || !w_k || !w_v || !w_bias || !q || !k || !v || !bias || !mask_bias ||
-      att_bad_dims(n_u, n_t, ldm))
-    return PX_ERR_BAD_ARG;
-  dim3 grid((unsigned)((n_t + 127) / 128), (unsigned)n_u);  // 128-wide tiles cover the pad columns up to ldm too
-  const size_t smem = sizeof(TriAttInSmem);
-  cudaStream_t st = (cudaStream_t)stream;
-  if (z_dtype == PX_F32) {
-    if (cudaFuncSetAttribute(triatt_in_proj_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-        cudaSuccess)
-      return PX_ERR_LAUNCH;
-    triatt_in_proj_kernel<float><<<grid, 256, smem, st>>>(
-        (const float*)z, mask, ln_w, ln_b, (const bf16*)w_q, (const bf16*)w_k, (const bf16*)w_v,
-        (const bf16*)w_bias, (bf16*)q, (bf16*)k, (bf16*)v, bias, mask_bias, (int)n_u, (int)n_t, (int)ldm, (int)px_ld(n_t), ending,
-        eps, inf);
-  } else if (z_dtype == PX_BF16) {
-    if (cudaFuncSetAttribute(triatt_in_proj_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-        cudaSuccess)
-      return PX_ERR_LAUNCH;
-    triatt_in_proj_kernel<bf16><<<grid, 256, smem, st>>>(
-        (const bf16*)z, mask, ln_w, ln_b, (const bf16*)w_q, (const bf16*)w_k, (const bf16*)w_v, (const bf16*)w_bias,
-        (bf16*)q, (bf16*)k, (bf16*)v, bias, mask_bias, (int)n_u, (int)n_t, (int)ldm, (int)px_ld(n_t), ending, eps,
-        inf);
-  } else {
-    return PX_ERR_UNSUPPORTED;
-  }
-  return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
-}
 
 extern "C" int32_t px_triatt_out(const px_bf16* o, const void* z_in, void* z_out, int32_t z_dtype, const float* ln_w,
                                  const float* ln_b, const px_bf16* w_g, const px_bf16* w_o, int64_t n_u, int64_t n_t,

@@ -5,7 +5,7 @@
 // Persistent kernel, one CTA per SM.  A tile is 128 pair elements (one u, 128 consecutive t); the CTAs work in
 // pairs on the same sequence of tiles, each CTA producing 64 of the 128 channels of a and of b (the second read of
 // a tile comes from L2).  Halving the weights a CTA keeps resident leaves shared memory for output staging and
-// tensor memory for the row statistics:
+// tensor memory for the row statistics (px_rowpipe.cuh has the parts shared with the other row kernels):
 //   * The weights stay in shared memory for the whole kernel with gamma and the 1/2 of the sigmoid folded in;
 //     LayerNorm's mean and beta terms enter the product as one extra K step (see px_rowpipe.cuh).
 //   * The row statistics come from the tensor core as well: Z Z^T has the sums of squares on its diagonal, and 16
@@ -29,29 +29,25 @@
 
 namespace px {
 
-constexpr int kTiStages = 2;
-constexpr int kTiSlots = kTiStages + 1;        // row-scale slots: the epilogue reads them after the operand is freed
-constexpr int kTiTilePanel = 144 * 128;        // [128 rows + 16 rows of ones][64 k] bf16
-constexpr int kTiTileBytes = 2 * kTiTilePanel;
-constexpr int kTiWExtra = 128 * 32;            // [128 rows][16 k] correction panel
-constexpr int kTiAExtra = 128 * 32;
+constexpr int kTiWExtra = 128 * 32;            // [128 rows][16 k] weight-side correction panel
 constexpr int kTiStageOut = 64 * 256;          // [64 channels][128 t] bf16
 constexpr int kTiWarps = 24;
 constexpr int kTiThreads = 32 * kTiWarps;
 constexpr uint32_t kTiColGram = 256;           // tensor memory: out a | out b | statistics (144 columns)
 
 struct TiBars {
-  uint64_t raw_full[kTiStages], a_ready[kTiStages], a_empty[kTiStages], acc_full[2], acc_free[2], gram_full, gram_free;
+  TileBars tile;
+  uint64_t acc_full[2], acc_free[2];
   uint32_t tmem_base;
 };
 struct TiLayout {
   static constexpr int w = 0;                                   // per output: [projection 64 | gate 64][128 k]
   static constexpr int wx = w + 2 * kOperandBytes;              // per output: correction panel
   static constexpr int a = wx + 2 * kTiWExtra;                  // row-tile ring
-  static constexpr int ax = a + kTiStages * kTiTileBytes;       // row-tile correction panels
-  static constexpr int out = ax + kTiStages * kTiAExtra;        // output staging, one buffer per output
+  static constexpr int ax = a + kTileStages * kTileBytes;       // row-tile correction panels
+  static constexpr int out = ax + kTileStages * kTileExtra;     // output staging, one buffer per output
   static constexpr int scale = out + 2 * kTiStageOut;           // float2 (rstd, rstd*mask/2) per row and slot
-  static constexpr int bars = scale + kTiSlots * 128 * 8;
+  static constexpr int bars = scale + kTileSlots * 128 * 8;
   static constexpr int total = bars + (int)sizeof(TiBars);
 };
 
@@ -68,20 +64,24 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   TiBars& bars = *reinterpret_cast<TiBars*>(sm + TiLayout::bars);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int chan0 = 64 * (blockIdx.x & 1);               // this CTA's channels of a and b
-  const int first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
+  TileCtx ctx;
+  ctx.tiles = sm + TiLayout::a;
+  ctx.extras = sm + TiLayout::ax;
+  ctx.bars = &bars.tile;
+  ctx.first_tile = blockIdx.x >> 1;
+  ctx.tile_step = gridDim.x >> 1;
+  ctx.n_tiles = n_tiles;
+  ctx.tiles_t = tiles_t;
+  ctx.n_u = n_u;
+  ctx.n_t = n_t;
+  ctx.swap = swap;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kTiStages; ++s) {
-      mbar_init(&bars.raw_full[s], kTma ? 1 : 4);
-      mbar_init(&bars.a_ready[s], 4);
-      mbar_init(&bars.a_empty[s], 3);
-    }
+    tile_bars_init(bars.tile, kTma, 3);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars.acc_full[b], 1);
       mbar_init(&bars.acc_free[b], 8);
     }
-    mbar_init(&bars.gram_full, 1);
-    mbar_init(&bars.gram_free, 4);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 20) {
@@ -98,129 +98,35 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     fold_weight_rows(w0, x0, 64, kPanelBytes, w_ag, chan0, 64, ln_w, ln_b, 0.5f, warp, kTiWarps, lane);
     fold_weight_rows(w0 + kOperandBytes, x0 + kTiWExtra, 0, kPanelBytes, w_bp, chan0, 64, ln_w, ln_b, 1.0f, warp, kTiWarps, lane);
     fold_weight_rows(w0 + kOperandBytes, x0 + kTiWExtra, 64, kPanelBytes, w_bg, chan0, 64, ln_w, ln_b, 0.5f, warp, kTiWarps, lane);
-    // the 16 rows of ones behind every tile panel (never overwritten: a tile load covers 128 rows)
-    for (int i = threadIdx.x; i < kTiStages * 2 * 16 * 8; i += kTiThreads) {
-      const int panel = i >> 7, piece = i & 127;
-      *reinterpret_cast<uint4*>(sm + TiLayout::a + panel * kTiTilePanel + 128 * 128 + piece * 16) =
-          make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
-    }
+    tile_write_ones(ctx.tiles, threadIdx.x, kTiThreads);
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars.tmem_base;
-  if (warp == 0) { ROW_TRACE(12, 0); }
 
   if (warp >= 20) {
-    if (warp == 20 && lane == 0 && kTma) {
-      // ---------------------------------------------------------------- row-tile producer (bf16 rows)
-      int k = 0;
-      for (int tile = first_tile; tile < n_tiles; tile += tile_step, ++k) {
-        const int s = k % kTiStages, n = k / kTiStages;
-        if (!mbar_wait(&bars.a_empty[s], (n & 1) ^ 1, 1u)) break;
-        ROW_TRACE(0, k);
-        const int u = tile / tiles_t, t0 = (tile % tiles_t) * 128;
-        mbar_expect_tx(&bars.raw_full[s], kOperandBytes);
-        const uint32_t dst = smem_u32(sm + TiLayout::a + s * kTiTileBytes);
-        for (int p = 0; p < 2; ++p)
-          tma_load_3d(dst + p * kTiTilePanel, &map_z, &bars.raw_full[s], 64 * p, swap ? u : t0, swap ? t0 : u);
-      }
-    } else if ((warp == 21 || warp == 22) && lane == 0) {
-      // ---------------------------------------------------------------- MMA issuer of output ph
-      const int ph = warp - 21;
-      constexpr uint32_t idesc = umma_idesc_bf16(128, 128);
-      const uint32_t wm = smem_u32(sm + TiLayout::w) + ph * kOperandBytes;
-      const uint64_t wx_desc = umma_desc_sw32(smem_u32(sm + TiLayout::wx) + ph * kTiWExtra);
-      int k = 0;
-      bool ok = true;
-      for (int tile = first_tile; tile < n_tiles && ok; tile += tile_step, ++k) {
-        const int s = k % kTiStages, n = k / kTiStages;
-        ok = mbar_wait(&bars.raw_full[s], n & 1, 2u);
-        if (!ok) break;
-        const uint32_t a_addr = smem_u32(sm + TiLayout::a + s * kTiTileBytes);
-        ok = mbar_wait(&bars.acc_free[ph], (k & 1) ^ 1, 8u);
-        if (!ok) break;
-        ROW_TRACE(2 + 2 * ph, k);
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_bf16(tmem_base + 128 * ph, umma_desc_sw128(a_addr + (ks >> 2) * kTiTilePanel) + 2 * (ks & 3),
-                    umma_desc_sw128(wm + (ks >> 2) * kPanelBytes) + 2 * (ks & 3), idesc, ks ? 1u : 0u);
-        ok = mbar_wait(&bars.a_ready[s], n & 1, 4u);       // the correction step needs the statistics
-        if (!ok) break;
-        tc_fence_after();
-        umma_bf16(tmem_base + 128 * ph, umma_desc_sw32(smem_u32(sm + TiLayout::ax + s * kTiAExtra)), wx_desc, idesc, 1u);
-        umma_commit(&bars.acc_full[ph]);
-        umma_commit(&bars.a_empty[s]);                     // this thread's share of the reads of the stage
-        ROW_TRACE(3 + 2 * ph, k);
-      }
-    } else if (warp == 23 && lane == 0) {
-      // ---------------------------------------------------------------- MMA issuer of the statistics product
-      constexpr uint32_t idesc_gram = umma_idesc_bf16(128, 144);
-      int k = 0;
-      for (int tile = first_tile; tile < n_tiles; tile += tile_step, ++k) {
-        const int s = k % kTiStages, n = k / kTiStages;
-        if (!mbar_wait(&bars.raw_full[s], n & 1, 2u) || !mbar_wait(&bars.gram_free, (k & 1) ^ 1, 2u)) break;
-        ROW_TRACE(1, k);
-        tc_fence_after();
-        const uint32_t a_addr = smem_u32(sm + TiLayout::a + s * kTiTileBytes);
-        // Z Z^T (diagonal = sums of squares) | Z 1 (sums)
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t d = umma_desc_sw128(a_addr + (ks >> 2) * kTiTilePanel) + 2 * (ks & 3);
-          umma_bf16(tmem_base + kTiColGram, d, d, idesc_gram, ks ? 1u : 0u);
-        }
-        umma_commit(&bars.gram_full);
-        umma_commit(&bars.a_empty[s]);
+    if (lane == 0) {
+      if (warp == 20) {
+        if (kTma) tile_producer_loop(ctx, &map_z);
+      } else if (warp == 23) {
+        tile_gram_loop(ctx, tmem_base + kTiColGram);
+      } else {
+        const int ph = warp - 21;                          // MMA issuer of output ph
+        tile_product_loop(ctx, tmem_base + 128 * ph, smem_u32(sm + TiLayout::w) + ph * kOperandBytes, kPanelBytes,
+                          smem_u32(sm + TiLayout::wx) + ph * kTiWExtra, umma_idesc_bf16(128, 128), &bars.acc_full[ph],
+                          &bars.acc_free[ph]);
       }
     }
   } else if (warp >= 16) {
     // ------------------------------------------------------------------ row statistics, one thread per row
-    const int qw = warp - 16, r = 32 * qw + lane;
-    const uint32_t t_gram = tmem_base + ((uint32_t)(32 * qw) << 16) + kTiColGram;
-    int k = 0;
-    bool ok = true;
-    for (int tile = first_tile; tile < n_tiles; tile += tile_step, ++k) {
-      const int s = k % kTiStages, n = k / kTiStages;
-      const int u = tile / tiles_t, t = (tile % tiles_t) * 128 + r;
-      const size_t pair = swap ? ((size_t)t * n_u + u) : ((size_t)u * n_t + t);
+    float2* scale = reinterpret_cast<float2*>(sm + TiLayout::scale);
+    tile_stats_loop<Tz>(ctx, z, eps, tmem_base + kTiColGram, warp - 16, lane, [&](int k, int u, int t, int r, float rstd) {
       float mk = 0.f;
-      if (t < n_t) mk = mask ? __ldg(mask + pair) : 1.f;
-      if (!kTma) {
-        // fp32 rows: standardised while they are converted into the operand
-        ok = mbar_wait(&bars.a_empty[s], (n & 1) ^ 1, 16u);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        standardise_row_to_operand(sm + TiLayout::a + s * kTiTileBytes, r,
-                                   t < n_t ? reinterpret_cast<const float*>(z) + pair * kC : nullptr, eps, kTiTilePanel);
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars.raw_full[s]);
-      }
-      ok = mbar_wait(&bars.gram_full, k & 1, 16u);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      if (warp == 16) { ROW_TRACE(6, k); }
-      tc_fence_after();
-      uint32_t diag[32], sums[16];
-      tmem_ld32(t_gram + 32 * qw, diag);
-      tmem_ld16(t_gram + 128, sums);
-      tmem_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars.gram_free);
-      const float mean = __uint_as_float(sums[0]) * (1.0f / kC);
-      const float var = fmaxf(select_own(diag, lane) * (1.0f / kC) - mean * mean, 0.f);
-      const float rstd = rsqrtf(var + eps);
-      // rstd * (W'x - mean * s + std * t): the row side of the correction step holds (-mean, std)
-      write_correction_row(sm + TiLayout::ax + s * kTiAExtra, r, -mean, sqrtf(var + eps), false);
-      reinterpret_cast<float2*>(sm + TiLayout::scale)[(k % kTiSlots) * 128 + r] = make_float2(rstd, 0.5f * rstd * mk);
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars.a_ready[s]);
-      if (warp == 16) { ROW_TRACE(7, k); }
-    }
+      if (t < n_t) mk = mask ? __ldg(mask + (swap ? ((size_t)t * n_u + u) : ((size_t)u * n_t + t))) : 1.f;
+      scale[(k % kTileSlots) * 128 + r] = make_float2(rstd, 0.5f * rstd * mk);
+    });
   } else {
     // ------------------------------------------------------------------ epilogue of output ph
     const int ph = warp >> 3, half = (warp >> 2) & 1, qw = warp & 3;
@@ -231,16 +137,15 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     unsigned char* stage = sm + TiLayout::out + ph * kTiStageOut + (32 * half) * 256 + row * 2;
     int k = 0;
     bool ok = true;
-    for (int tile = first_tile; tile < n_tiles && ok; tile += tile_step, ++k) {
+    for (int tile = ctx.first_tile; tile < n_tiles && ok; tile += ctx.tile_step, ++k) {
       const int u = tile / tiles_t, t0 = (tile % tiles_t) * 128;
       ok = mbar_wait(&bars.acc_full[ph], k & 1, 32u);
       // the store that last read the staging buffer (one tile ago) must be through with it
       if (leader) tma_store_wait_read<0>();
       ok = named_barrier_all(1 + ph, 256, ok);             // all eight warps go on, or none
       if (!ok) break;
-      if ((warp & 7) == 0) { ROW_TRACE(8 + 2 * ph, k); }
       tc_fence_after();
-      const float2 sc = reinterpret_cast<const float2*>(sm + TiLayout::scale)[(k % kTiSlots) * 128 + row];
+      const float2 sc = reinterpret_cast<const float2*>(sm + TiLayout::scale)[(k % kTileSlots) * 128 + row];
       // mask * p * sigmoid(g) = h + h * tanh(g / 2) with h = mask * p / 2 (the halves are folded in)
       auto emit = [&](const uint32_t(&p)[16], const uint32_t(&g)[16], int hh) {
 #pragma unroll
@@ -268,7 +173,6 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
         tma_store_3d(map_out, smem_u32(sm + TiLayout::out + ph * kTiStageOut), t0, u, chan0);
         tma_store_commit();
       }
-      if ((warp & 7) == 0) { ROW_TRACE(9 + 2 * ph, k); }
     }
     if (leader) tma_store_wait<0>();
   }
@@ -286,14 +190,6 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
   }
 }
-
-#ifdef PX_ROW_TRACE
-}  // namespace px
-extern "C" __attribute__((visibility("default"))) int px_debug_row_trace(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, px::g_row_trace, sizeof(long long) * 1024);
-}
-namespace px {
-#endif
 
 unsigned int trimul_in_error_flags() {
   unsigned int v = 0;
