@@ -49,10 +49,13 @@ __device__ __forceinline__ void split_bf16(float v, uint32_t& head, uint32_t& ta
   tail = (uint32_t)__bfloat16_as_ushort(t);
 }
 
-// Row r of a correction panel ([rows][16 k] bf16, 32-byte swizzle): k = 0..3 pair up x with the other side's first
-// value, k = 4..7 pair up y with its second value; `weight_side` picks the interleaving so that the four head/tail
-// products of each pair meet:  row side (xh, xh, xl, xl, yh, yh, yl, yl), weight side (xh, xl, xh, xl, yh, yl, yh, yl).
-__device__ __forceinline__ void write_correction_row(unsigned char* panel, int r, float x, float y, bool weight_side) {
+// Row r of a correction panel ([rows][16 k] bf16, 32-byte swizzle).  One 8-wide half of the row (`khalf`: k = 0..7 or
+// k = 8..15) pairs up x with the other side's first value in its k = 0..3 and y with its second value in k = 4..7;
+// `weight_side` picks the interleaving so that the four head/tail products of each pair meet:
+// row side (xh, xh, xl, xl, yh, yh, yl, yl), weight side (xh, xl, xh, xl, yh, yl, yh, yl).
+// The other half of the row is zeroed when `zero_other` is set (it must never hold anything but finite values).
+__device__ __forceinline__ void write_correction_row(unsigned char* panel, int r, float x, float y, bool weight_side,
+                                                     int khalf = 0, bool zero_other = true) {
   uint32_t xh, xl, yh, yl;
   split_bf16(x, xh, xl);
   split_bf16(y, yh, yl);
@@ -62,9 +65,9 @@ __device__ __forceinline__ void write_correction_row(unsigned char* panel, int r
   } else {
     v.x = xh | (xh << 16), v.y = xl | (xl << 16), v.z = yh | (yh << 16), v.w = yl | (yl << 16);
   }
-  const int sw = (r >> 2) & 1;
+  const int sw = ((r >> 2) & 1) ^ khalf;
   *reinterpret_cast<uint4*>(panel + r * 32 + (sw << 4)) = v;
-  *reinterpret_cast<uint4*>(panel + r * 32 + ((sw ^ 1) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+  if (zero_other) *reinterpret_cast<uint4*>(panel + r * 32 + ((sw ^ 1) << 4)) = make_uint4(0u, 0u, 0u, 0u);
 }
 
 // Rounds to bf16 (half up) on the integer pipe and stores two bytes.
@@ -79,7 +82,7 @@ __device__ __forceinline__ void store_bf16_int(bf16* p, float v) {
 __device__ __forceinline__ void fold_weight_rows(unsigned char* dst, unsigned char* extra, int dst_row0, int panel_bytes,
                                                  const bf16* __restrict__ W, int row_begin, int count,
                                                  const float* __restrict__ gamma, const float* __restrict__ beta,
-                                                 float scale, int warp, int nwarps, int lane) {
+                                                 float scale, int warp, int nwarps, int lane, int khalf = 0) {
   const float4 g4 = *reinterpret_cast<const float4*>(gamma + 4 * lane);
   const float4 b4 = *reinterpret_cast<const float4*>(beta + 4 * lane);
 #pragma unroll 2
@@ -92,7 +95,7 @@ __device__ __forceinline__ void fold_weight_rows(unsigned char* dst, unsigned ch
     const float t = warp_sum(w.x * b4.x + w.y * b4.y + w.z * b4.z + w.w * b4.w) * scale;
     const int r = i + dst_row0;
     *reinterpret_cast<uint2*>(dst + operand_piece_offset(r, lane >> 1, panel_bytes) + (lane & 1) * 8) = make_uint2(lo, hi);
-    if (lane == 0) write_correction_row(extra, r, s, t, true);
+    if (lane == 0) write_correction_row(extra, r, s, t, true, khalf);
   }
 }
 
