@@ -23,6 +23,16 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // Bounded wait for the phase with the given parity; false = gave up (error flag set).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int code) {
   const uint32_t addr = smem_u32(bar);
+  {
+    // fast path: the phase is often complete already, and a plain test costs one shared-memory round trip
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.b32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
   const long long t0 = clock64();
   for (;;) {
     uint32_t done;
