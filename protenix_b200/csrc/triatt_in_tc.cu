@@ -206,8 +206,7 @@ triatt_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
       if (lane == 0) mbar_arrive(&bars.acc_free[1]);     // this warp has read its part of the accumulator
 #pragma unroll
       for (int e = 0; e < 32; ++e)
-        *reinterpret_cast<unsigned short*>(stage + e * 256) =
-            (unsigned short)((__float_as_uint(sc.y * __uint_as_float(v[e])) + 0x8000u) >> 16);
+        *reinterpret_cast<bf16*>(stage + e * 256) = __float2bfloat16_rn(sc.y * __uint_as_float(v[e]));
       if (half == 0 && t < ldm) {                        // zero in the pad columns [n, ldm)
 #pragma unroll
         for (int e = 0; e < 2; ++e)

@@ -152,8 +152,7 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
         for (int e = 0; e < 16; ++e) {
           const float h = sc.y * __uint_as_float(p[e]);
           const float v = fmaf(h, tanh_fast(sc.x * __uint_as_float(g[e])), h);
-          *reinterpret_cast<unsigned short*>(stage + (16 * hh + e) * 256) =
-              (unsigned short)((__float_as_uint(v) + 0x8000u) >> 16);
+          *reinterpret_cast<bf16*>(stage + (16 * hh + e) * 256) = __float2bfloat16_rn(v);
         }
       };
       uint32_t p0[16], g0[16], p1[16], g1[16];
