@@ -5,9 +5,9 @@
 // Persistent kernel, one CTA per SM, 128 rows per tile, three tiles in flight: while the tensor core works through
 // the eight 64-wide hidden chunks of one tile, the next tile is being normalised and the previous one written out.
 //
-//   warps 0..7    SwiGLU: two groups of four warps, one per H buffer.  A thread owns one row: per hidden chunk it
-//                 pulls a|b (128 fp32 columns) out of tensor memory, forms h = silu(a) * b, and writes h (bf16)
-//                 back over the first 32 columns as the A operand of the second product.
+//   warps 0..7    SwiGLU: a thread owns one row and half of the current hidden chunk: it pulls a|b out of tensor
+//                 memory, forms h = silu(a) * b, and writes h (bf16) back over the first 32 columns of the same
+//                 H buffer as the A operand of the second product.  The two H buffers alternate.
 //   warps 8..11   LayerNorm: lanes across channels (coalesced), eight rows in flight per warp; the normalised rows
 //                 are written as the K-major, 128-byte-swizzled A operand of the first product (two buffers).
 //   warps 12..15  output: accumulator -> shared staging -> + residual -> coalesced stores (two accumulators).
@@ -17,7 +17,7 @@
 //                 as the TMEM-resident A operand).  Two threads because a tcgen05.mma costs its issuing thread
 //                 about 100 cycles.
 // Tensor memory: H_0 | H_1 | OUT_0 | OUT_1, 128 columns each.  Every mbarrier wait is bounded.
-#include "px_tcgen05.cuh"
+#include "px_rowpipe.cuh"
 
 namespace px {
 
@@ -43,11 +43,34 @@ struct TransLayout {
   static constexpr int total = bars + (int)sizeof(TransBars);
 };
 
-__device__ __forceinline__ float tanh_fast_tr(float x) {
-  float y;
-  asm("tanh.approx.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-  return y;
-}
+#ifdef PX_TRANS_TRACE
+__device__ long long g_trans_trace[16 * 64];
+#define TR_TRACE(slot, idx) \
+  if (blockIdx.x == 0 && lane == 0 && (idx) < 64) g_trans_trace[(slot) * 64 + (idx)] = clock64();
+#else
+#define TR_TRACE(slot, idx)
+#endif
+
+// Four consecutive channels as they are stored (8 or 16 bytes), so that loads can be kept in flight cheaply.
+template <typename Tz>
+struct Raw4;
+template <>
+struct Raw4<bf16> {
+  uint2 v;
+  __device__ __forceinline__ void load(const bf16* p) { v = *reinterpret_cast<const uint2*>(p); }
+  __device__ __forceinline__ void zero() { v = make_uint2(0u, 0u); }
+  __device__ __forceinline__ float4 get() const {
+    const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y);
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+};
+template <>
+struct Raw4<float> {
+  float4 v;
+  __device__ __forceinline__ void load(const float* p) { v = *reinterpret_cast<const float4*>(p); }
+  __device__ __forceinline__ void zero() { v = make_float4(0.f, 0.f, 0.f, 0.f); }
+  __device__ __forceinline__ float4 get() const { return v; }
+};
 
 template <typename Tz>
 __global__ void __launch_bounds__(kTrThreads, 1)
@@ -67,7 +90,7 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
       mbar_init(&bars.a_free[b], 1);
       mbar_init(&bars.h_full[b], 1);
       mbar_init(&bars.h_free[b], 1);
-      mbar_init(&bars.p_ready[b], 4);
+      mbar_init(&bars.p_ready[b], 8);
       mbar_init(&bars.out_full[b], 1);
       mbar_init(&bars.out_free[b], 4);
     }
@@ -122,6 +145,7 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
           const int s = j % kTrStages, hb = j & 1;
           ok = mbar_wait(&bars.w_full[s], (j / kTrStages) & 1, 4u) && mbar_wait(&bars.h_free[hb], ((j >> 1) & 1) ^ 1, 4u);
           if (!ok) break;
+          TR_TRACE(0, j);
           tc_fence_after();
           const uint32_t wbase = smem_u32(sm + TransLayout::w + s * kTrStageBytes);
 #pragma unroll
@@ -130,6 +154,7 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
                       umma_desc_sw128(wbase + (ks >> 2) * 16384) + 2 * (ks & 3), idesc, ks ? 1u : 0u);
           umma_commit(&bars.h_full[hb]);
           umma_commit(&bars.w_empty[s]);                // this thread's share of the reads of the stage
+          TR_TRACE(1, j);
         }
         if (ok) umma_commit(&bars.a_free[ab]);          // the tile has been read for the last time
       }
@@ -145,6 +170,7 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
           const int s = j % kTrStages, hb = j & 1;
           ok = mbar_wait(&bars.w_full[s], (j / kTrStages) & 1, 4u) && mbar_wait(&bars.p_ready[hb], (j >> 1) & 1, 8u);
           if (!ok) break;
+          TR_TRACE(2, j);
           tc_fence_after();
           const uint64_t dwo = umma_desc_sw128(smem_u32(sm + TransLayout::w + s * kTrStageBytes) + kTrW1Bytes);
 #pragma unroll
@@ -152,6 +178,7 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
             umma_bf16_ts(tmem_base + 256 + 128 * ob, tmem_base + 128 * hb + 8 * ks, dwo + 2 * ks, idesc, (c | ks) ? 1u : 0u);
           umma_commit(&bars.h_free[hb]);
           umma_commit(&bars.w_empty[s]);
+          TR_TRACE(3, j);
         }
         if (ok) umma_commit(&bars.out_full[ob]);
       }
@@ -170,12 +197,30 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
     for (int tile = first_tile; tile < n_tiles; tile += tile_step, ++k) {
       const int ob = k & 1;
       const long long row0 = (long long)tile * 128;
+      // the residual values of a 32-column block are requested one block ahead (the first before the wait)
+      Raw4<Tz> res[8], res_next[8];
+      auto request = [&](Raw4<Tz>(&dst)[8], int q) {
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const long long grow = row0 + 32 * qw + 4 * it + rsub;
+          if (add_residual && grow < rows) {
+            dst[it].load(x_in + (size_t)grow * kC + 32 * q + 4 * piece);
+          } else {
+            dst[it].zero();
+          }
+        }
+      };
+      request(res_next, 0);
       bool ok = mbar_wait(&bars.out_full[ob], (k >> 1) & 1, 32u);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (qw == 0) { TR_TRACE(10, k); }
       tc_fence_after();
 #pragma unroll 1
       for (int q = 0; q < 4; ++q) {
+#pragma unroll
+        for (int it = 0; it < 8; ++it) res[it] = res_next[it];
+        if (q + 1 < 4) request(res_next, q + 1);
         uint32_t r[32];
         tmem_ld32(lane_addr + 256 + 128 * ob + 32 * q, r);
         tmem_wait_ld();
@@ -196,20 +241,14 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
           const float4 v = *reinterpret_cast<const float4*>(stg + rl * 128 + ((piece ^ (rl & 7)) << 4));
           if (grow < rows) {
             const size_t off = (size_t)grow * kC + 32 * q + 4 * piece;
-            float4 val = v;
-            if (add_residual) {
-              const float4 res = load4(x_in + off);
-              val.x += res.x;
-              val.y += res.y;
-              val.z += res.z;
-              val.w += res.w;
-            }
-            store2(x_out + off, val.x, val.y);
-            store2(x_out + off + 2, val.z, val.w);
+            const float4 rs = res[it].get();
+            store2(x_out + off, v.x + rs.x, v.y + rs.y);
+            store2(x_out + off + 2, v.z + rs.z, v.w + rs.w);
           }
         }
         __syncwarp();
       }
+      if (qw == 0) { TR_TRACE(11, k); }
     }
   } else if (warp >= 8) {
     // ------------------------------------------------------------------ LayerNorm -> swizzled A operand
@@ -225,15 +264,27 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       unsigned char* sa = sm + TransLayout::a + ab * kTrABytes;
-      // eight rows per batch: all loads first, then eight independent reductions
+      if (qw == 0) { TR_TRACE(8, k); }
+      // eight rows per batch; the next batch is requested (as stored) before this one is reduced
+      Raw4<Tz> raw[8];
+      auto request = [&](int rb) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const long long grow = row0 + 32 * qw + rb + j;
+          if (grow < rows) {
+            raw[j].load(x_in + (size_t)grow * kC + 4 * lane);
+          } else {
+            raw[j].zero();
+          }
+        }
+      };
+      request(0);
 #pragma unroll 1
       for (int rb = 0; rb < 32; rb += 8) {
         float4 x[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const long long grow = row0 + 32 * qw + rb + j;
-          x[j] = grow < rows ? load4(x_in + (size_t)grow * kC + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+        for (int j = 0; j < 8; ++j) x[j] = raw[j].get();
+        if (rb + 8 < 32) request(rb + 8);
         float sum[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) sum[j] = x[j].x + x[j].y + x[j].z + x[j].w;
@@ -241,7 +292,6 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
         for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
           for (int j = 0; j < 8; ++j) sum[j] += __shfl_xor_sync(0xffffffffu, sum[j], o);
-        float var[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float mean = sum[j] * (1.0f / kC);
@@ -249,17 +299,17 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
           x[j].y -= mean;
           x[j].z -= mean;
           x[j].w -= mean;
-          var[j] = x[j].x * x[j].x + x[j].y * x[j].y + x[j].z * x[j].z + x[j].w * x[j].w;
+          sum[j] = x[j].x * x[j].x + x[j].y * x[j].y + x[j].z * x[j].z + x[j].w * x[j].w;
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
-          for (int j = 0; j < 8; ++j) var[j] += __shfl_xor_sync(0xffffffffu, var[j], o);
+          for (int j = 0; j < 8; ++j) sum[j] += __shfl_xor_sync(0xffffffffu, sum[j], o);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const int r = 32 * qw + rb + j;                  // row inside the tile
           const long long grow = row0 + r;
-          const float rstd = rsqrtf(var[j] * (1.0f / kC) + eps);
+          const float rstd = rsqrtf(sum[j] * (1.0f / kC) + eps);
           uint2 o = make_uint2(0u, 0u);
           if (grow < rows) {
             o.x = pack_bf16x2(x[j].x * rstd * g4.x + b4.x, x[j].y * rstd * g4.y + b4.y);
@@ -271,39 +321,49 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars.a_full[ab]);
+      if (qw == 0) { TR_TRACE(9, k); }
     }
   } else {
-    // ------------------------------------------------------------------ SwiGLU in registers, group hb = H buffer
-    const int hb = warp >> 2, qw = warp & 3;
-    const uint32_t t_h = tmem_base + ((uint32_t)(32 * qw) << 16) + 128 * hb;
-    int u = 0;                                        // use counter of this H buffer
+    // ------------------------------------------------------------------ SwiGLU in registers
+    // All eight warps work on the current hidden chunk (lane quarter x half of its 64 columns), so that the second
+    // product can start after half the time; the H buffers alternate from chunk to chunk.
+    const int half = warp >> 2, qw = warp & 3;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * qw) << 16);
+    int j = 0;                                        // chunk counter over all tiles of this CTA
     bool ok = true;
     for (int tile = first_tile; tile < n_tiles && ok; tile += tile_step) {
-      for (int c = hb; c < kTrChunks && ok; c += 2, ++u) {
-        ok = mbar_wait(&bars.h_full[hb], u & 1, 64u);
-        ok = __all_sync(0xffffffffu, ok);
+      for (int c = 0; c < kTrChunks && ok; ++c, ++j) {
+        const int hb = j & 1;
+        const uint32_t t_h = lane_addr + 128 * hb;
+        ok = mbar_wait(&bars.h_full[hb], (j >> 1) & 1, 64u);
+        ok = named_barrier_all(2, 256, ok);                // all eight warps go on, or none
         if (!ok) break;
+        if (warp == 0) { TR_TRACE(4 + 2 * hb, j >> 1); }
         tc_fence_after();
-        uint32_t w[32];
+        uint32_t w[16];
 #pragma unroll
-        for (int hh = 0; hh < 4; ++hh) {
+        for (int hh = 0; hh < 2; ++hh) {
           uint32_t a[16], b[16];
-          tmem_ld16(t_h + 16 * hh, a);
-          tmem_ld16(t_h + 64 + 16 * hh, b);
+          tmem_ld16(t_h + 32 * half + 16 * hh, a);
+          tmem_ld16(t_h + 64 + 32 * half + 16 * hh, b);
           tmem_wait_ld();
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             // silu(a) * b = 0.5 * a * b * (1 + tanh(a / 2)): one special-function op per element
             const float a0 = __uint_as_float(a[2 * e]), a1 = __uint_as_float(a[2 * e + 1]);
             const float h0 = 0.5f * a0 * __uint_as_float(b[2 * e]), h1 = 0.5f * a1 * __uint_as_float(b[2 * e + 1]);
-            w[8 * hh + e] = pack_bf16x2(fmaf(h0, tanh_fast_tr(0.5f * a0), h0), fmaf(h1, tanh_fast_tr(0.5f * a1), h1));
+            w[8 * hh + e] = pack_bf16x2(fmaf(h0, tanh_fast(0.5f * a0), h0), fmaf(h1, tanh_fast(0.5f * a1), h1));
           }
         }
-        tmem_st32(t_h, w);                                   // h overwrites the first 32 columns of H
+        // h overwrites the first 32 columns of H; all warps must have read their a before any of them writes:
+        // the a columns 0..31 of the half-0 warps are exactly where h lands
+        named_barrier(2, 256);
+        tmem_st16(t_h + 16 * half, w);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars.p_ready[hb]);
+        if (warp == 0) { TR_TRACE(5 + 2 * hb, j >> 1); }
       }
     }
   }
@@ -322,21 +382,17 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
   }
 }
 
+#ifdef PX_TRANS_TRACE
+}  // namespace px
+extern "C" __attribute__((visibility("default"))) int px_debug_trans_trace(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, px::g_trans_trace, sizeof(long long) * 1024);
+}
+namespace px {
+#endif
+
 unsigned int transition_error_flags() {
   unsigned int v = 0;
   return read_clear_tc_error(&v) == 0 ? v : 0x80u;
-}
-
-static inline int transition_sm_count() {
-  static int cached[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (!cached[dev]) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
-  }
-  return cached[dev];
 }
 
 template <typename Tz>
@@ -357,7 +413,7 @@ static int32_t launch_transition(const void* x_in, void* x_out, const float* ln_
       cudaSuccess)
     return PX_ERR_LAUNCH;
   const int64_t n_tiles = (rows + 127) / 128;
-  const int grid = (int)(n_tiles < transition_sm_count() ? n_tiles : transition_sm_count());
+  const int grid = (int)(n_tiles < sm_count() ? n_tiles : sm_count());
   transition_tc_kernel<Tz><<<grid, kTrThreads, smem, st>>>(ma, mb, mo, (const Tz*)x_in, (Tz*)x_out, ln_w, ln_b,
                                                            (long long)rows, (int)n_tiles, add_residual, eps);
   return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
