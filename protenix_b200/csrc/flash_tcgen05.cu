@@ -2,22 +2,23 @@
 //
 //   o[u][q][h*32+d] = softmax_k( q[u,h,q,:] . k[u,h,k,:] + bias[h][q][k] + mask_bias[u][k] ) v[u,h,k,d]
 //
-// One CTA = (head h, 128 queries, 6 attended rows u), 12 warps:
-//   warps 0..7    two softmax groups of four warps; group g owns rows u0+3g .. u0+3g+2, each thread one query
-//                 row.  Per 64-key tile a thread reads its 64 pair-bias values from shared memory once and
-//                 reuses them for the group's three rows (the bias does not depend on u).
-//   warps 8..9    one control thread per group (tcgen05 and TMA instructions cost ~100 cycles of issue
-//                 each, so one issuing thread for all groups would be the bottleneck).  It loads the
-//                 group's Q tile once and, per 64-key tile, a K tile [64 keys][32] (64-byte swizzle) and a
-//                 transposed V tile [32 d][64 keys] (128-byte swizzle) into the group's 4-stage ring;
-//                 issues S = Q K^T (M=128, N=64, K=32) into the group's S buffer in tensor memory; and,
-//                 once the group has written P (bf16) into its P buffer, issues O_u += P V with P as the
-//                 TMEM-resident A operand (M=128, N=48, K=64).  Row 32 of the value operand is all ones, so
-//                 column 32 of O_u accumulates the softmax denominators.  S of the next key tile is issued
-//                 as soon as the group has pulled the current S into registers, so it is ready when the
-//                 group comes back.  The control thread of group 0 also loads the pair-bias tile
-//                 [128 q][64 k] fp32 (two 128-byte-swizzled boxes, 2-deep ring) shared by all six rows.
-//   warps 10..11  idle (they complete the control warpgroup, which hands its registers to the softmax groups)
+// One CTA = (head h, 128 queries, 6 attended rows u), 16 warps:
+//   warps 0..11   three softmax groups of four warps; group g owns rows u0+2g, u0+2g+1, each thread one query row.
+//                 The kernel is bound by the latency of a group's chain (wait S, load, add, reduce, exponentials,
+//                 store P), not by any one unit, so three groups are kept in flight per SM.  Per work item a thread
+//                 adds its 64 pair-bias values from the shared tile (the bias does not depend on u: all six rows
+//                 use the same tile), and keeps the softmax denominator of its row in a register.
+//   warps 12..14  one control thread per group (tcgen05 and TMA instructions cost ~100 cycles of issue each, so
+//                 one issuing thread for all groups would be the bottleneck).  It loads the group's Q tiles once
+//                 and, per work item, a K tile [64 keys][32] (64-byte swizzle) and a transposed V tile
+//                 [32 d][64 keys] (128-byte swizzle) into the group's 4-stage ring; issues S = Q K^T (M=128, N=64,
+//                 K=32) into the group's S buffer in tensor memory; and, once the group has written P (bf16) into
+//                 its P buffer, issues O_u += P V with P as the TMEM-resident A operand (M=128, N=32, K=64).  S of
+//                 the next item is issued as soon as the group has pulled the current S into registers, so it is
+//                 ready when the group comes back.  The control thread of group 0 also loads the pair-bias tile
+//                 [128 q][64 k] fp32 (two 128-byte-swizzled boxes, 2-deep ring).
+//   warp 15       idle (completes the control warpgroup)
+// Tensor memory: S (3 x 64) | P (3 x 32, two bf16 per column) | O (6 x 32).
 //
 // Softmax is online in base 2 with a lazy reference maximum: the reference only moves (and O_u is rescaled
 // through TMEM) when the tile maximum exceeds it by more than 8, so probabilities stay below 2^8.
@@ -29,18 +30,18 @@
 namespace px {
 
 constexpr int kFH = 4, kFD = 32;
-constexpr int kFGroups = 2;               // softmax groups per CTA
-constexpr int kFRpg = 3;                  // attended rows per group
+constexpr int kFGroups = 3;               // softmax groups per CTA
+constexpr int kFRpg = 2;                  // attended rows per group
 constexpr int kFRows = kFGroups * kFRpg;  // attended rows per CTA
 constexpr int kFKT = 64;                  // keys per work item
 constexpr int kFStages = 4;               // K/V ring of each group (work items = (key tile, row))
 constexpr int kFQBytes = 128 * 64;        // [128][32] bf16
 constexpr int kFKBytes = kFKT * 64;       // [64][32] bf16
 constexpr int kFVBox = 32 * 128;          // the TMA box of the value tile: 32 rows x 64 keys
-constexpr int kFVBytes = 48 * 128;        // shared footprint (48 operand rows: 32 d, ones, 15 zero)
+constexpr int kFVBytes = 32 * 128;        // [32 d][64 keys] bf16
 constexpr int kFStageBytes = kFKBytes + kFVBytes;
 constexpr int kFBiasBytes = 128 * kFKT * 4;
-constexpr int kFON = 48;                  // columns of an O accumulator (32 d + denominator + pad)
+constexpr int kFON = 32;                  // columns of an O accumulator
 constexpr uint32_t kFCols = 512;
 constexpr int kFColS = 0, kFColP = kFGroups * kFKT, kFColO = kFColP + kFGroups * (kFKT / 2);  // TMEM column map
 constexpr float kRescaleGap = 8.0f;
@@ -103,15 +104,6 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  // operand rows 32..47 of every value tile: row 32 = ones (denominator column), the rest zero.  The TMA
-  // box only ever writes rows 0..31.  Rows 32..39 are one 8-row swizzle group; row 32 is its row 0, whose
-  // 16-byte pieces are not permuted.
-  for (int i = threadIdx.x; i < kFGroups * kFStages * 128; i += blockDim.x) {
-    const int stage = i / 128, piece = i % 128;                   // 128 pieces of 16 bytes per 16 rows
-    uint4 v = (piece < 8) ? make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u) : make_uint4(0, 0, 0, 0);
-    *reinterpret_cast<uint4*>(sm + FlashLayout::kv + stage * kFStageBytes + kFKBytes + 32 * 128 + piece * 16) = v;
-  }
-  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy writes above -> MMA reads
   if (warp == 4 * kFGroups) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&bars.tmem_base)),
                  "r"(kFCols)
@@ -197,7 +189,7 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
   } else {
     // ------------------------------------------------------------------ softmax groups
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;\n");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 160;\n");
     const int g = warp >> 2, qw = warp & 3;
     const int row = 32 * qw + lane;                 // query row inside the tile = TMEM lane
     const uint32_t lane_addr = (uint32_t)(32 * qw) << 16;
@@ -207,24 +199,14 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int ug = u0 + kFRpg * g;                  // first row of this group
     const int words = (nkt + 63) / 64;              // mask-flag words per row: one bit per 64-key tile
     unsigned long long flag_word[kFRpg];
-    float m_ref[kFRpg];
+    float m_ref[kFRpg], l_sum[kFRpg];             // reference maximum and denominator of this thread's query per row
 #pragma unroll
     for (int r = 0; r < kFRpg; ++r) {
       flag_word[r] = 0;
       m_ref[r] = -CUDART_INF_F;
+      l_sum[r] = 0.f;
     }
     bool ok = true;
-#ifndef PX_FLASH_STAGGER
-#define PX_FLASH_STAGGER 900
-#endif
-    if (g == 1) {
-      // Start the second group half a work item late: the two groups then alternate between their
-      // exponential phase (which saturates the special-function unit) and everything else, instead of
-      // colliding on that unit and idling together.
-      const long long t0 = clock64();
-      while (clock64() - t0 < PX_FLASH_STAGGER) {
-      }
-    }
     for (int kt = 0; kt < nkt && ok; ++kt) {
       if ((kt & 63) == 0) {
 #pragma unroll
@@ -234,26 +216,7 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       ok = mbar_wait(&bars.bias_full[kt & 1], (kt >> 1) & 1, 64u);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      // this thread's 64 bias values of the tile: read once, used for the group's three rows
-      float bv[kFKT];
-      {
-        const float* bias_tile = reinterpret_cast<const float*>(sm + FlashLayout::bias + (kt & 1) * kFBiasBytes);
-#pragma unroll
-        for (int c = 0; c < kFKT / 32; ++c) {
-          // box c holds columns 32c..32c+31 of all 128 rows: 128-byte rows, 16-byte pieces swizzled by row
-          const float* brow = bias_tile + c * (128 * 32) + row * 32;
-#pragma unroll
-          for (int p = 0; p < 8; ++p) {
-            const float4 b4 = *reinterpret_cast<const float4*>(brow + ((p ^ (row & 7)) << 2));
-            bv[32 * c + 4 * p + 0] = b4.x;
-            bv[32 * c + 4 * p + 1] = b4.y;
-            bv[32 * c + 4 * p + 2] = b4.z;
-            bv[32 * c + 4 * p + 3] = b4.w;
-          }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars.bias_empty[kt & 1]);     // this warp is done with the bias tile
-      }
+      const float* bias_tile = reinterpret_cast<const float*>(sm + FlashLayout::bias + (kt & 1) * kFBiasBytes);
 #pragma unroll
       for (int r = 0; r < kFRpg; ++r) {
         const int i = kt * kFRpg + r;               // this group's work item
@@ -275,8 +238,24 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars.s_free[g]);  // S is in registers: the next S may be computed
         if (qw == 0) { PX_TRACE(16 * g + 2, i); }
+        // + pair bias: box c of the tile holds columns 32c..32c+31 of all 128 rows, 128-byte rows, 16-byte pieces
+        // swizzled by row
 #pragma unroll
-        for (int c = 0; c < kFKT; ++c) s[c] += bv[c];
+        for (int c = 0; c < kFKT / 32; ++c) {
+          const float* brow = bias_tile + c * (128 * 32) + row * 32;
+#pragma unroll
+          for (int p = 0; p < 8; ++p) {
+            const float4 b4 = *reinterpret_cast<const float4*>(brow + ((p ^ (row & 7)) << 2));
+            s[32 * c + 4 * p + 0] += b4.x;
+            s[32 * c + 4 * p + 1] += b4.y;
+            s[32 * c + 4 * p + 2] += b4.z;
+            s[32 * c + 4 * p + 3] += b4.w;
+          }
+        }
+        if (r == kFRpg - 1) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars.bias_empty[kt & 1]);   // this warp is done with the bias tile
+        }
         if ((flag_word[r] >> (kt & 63)) & 1ull) {     // warp-uniform
           const int u = (ug + r < n_u) ? ug + r : 0;
           const float4* mrow = reinterpret_cast<const float4*>(mb + (size_t)u * ldm + kt * kFKT);
@@ -312,16 +291,20 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           m_ref[r] = m_new;
         }
         uint32_t w[kFKT / 2];
+        float l0 = 0.f, l1 = 0.f;
         {
           const float nm = -m_ref[r];
 #pragma unroll
           for (int e = 0; e < kFKT / 2; ++e) {
-            // fp32 exponentials; P keeps the upper halves (truncation to bf16: the same truncated values feed
-            // the denominator column, so the bias cancels in the normalisation)
+            // fp32 exponentials; P keeps the upper halves (truncation to bf16).  The denominator sums the same
+            // truncated values, so the bias of the truncation cancels in the normalisation.
             const float p0 = fast_exp2(s[2 * e] + nm), p1 = fast_exp2(s[2 * e + 1] + nm);
             w[e] = __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
+            l0 += __uint_as_float(w[e] << 16);
+            l1 += __uint_as_float(w[e] & 0xffff0000u);
           }
         }
+        l_sum[r] = l_sum[r] * alpha + (l0 + l1);
         // P.V of the previous item must be through before O is rescaled or the P buffer overwritten
         if (i >= 1) {
           ok = mbar_wait(&bars.pv_done[g], (i - 1) & 1, 256u);
@@ -360,12 +343,11 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const int qi = q0 + row;
 #pragma unroll
       for (int r = 0; r < kFRpg; ++r) {
-        uint32_t a[32], b[16];
+        uint32_t a[32];
         tmem_ld32(t_o + kFON * r, a);
-        tmem_ld16(t_o + kFON * r + 32, b);
         tmem_wait_ld();
         if (ug + r < n_u && qi < n) {
-          const float inv = 1.0f / __uint_as_float(b[0]);
+          const float inv = 1.0f / l_sum[r];
           bf16* dst = o + ((size_t)(ug + r) * n + qi) * kC + h * kFD;
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
