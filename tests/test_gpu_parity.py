@@ -116,6 +116,28 @@ def test_triangle_ops_vs_oracle(kind, n, mask_kind, zdtype):
     assert relf(y, ref) < TOL_OP, (kind, n, mask_kind)
 
 
+@pytest.mark.parametrize("zdtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("kind", ["tri_mul_out", "tri_mul_in", "tri_att_start", "tri_att_end"])
+def test_layer_norm_of_rows_far_from_zero_mean(kind, zdtype):
+    """The projection kernels fold LayerNorm into the weights and take the row statistics from E[x^2] - mean^2:
+    rows whose mean is 30 deviations away from zero (far beyond what a pair representation holds) must still
+    come out within the tolerance."""
+    n = 72
+    g = torch.Generator().manual_seed(5)
+    z = torch.randn(n, n, 128, generator=g) + 30.0 * torch.randn(n, n, 1, generator=g) + 3.0 * torch.randn(1, 1, 128, generator=g)
+    mask = _mask("rand", n, n)
+    m = build_module(kind, dict(wseed=9)).to(DEV)
+    zq = z.to(zdtype)
+    y = m(cuda(zq), mask=cuda(mask))
+    p = params_of(m)
+    if kind.startswith("tri_mul"):
+        ref = O.triangle_multiplication(zq.float(), mask, p, outgoing=(kind == "tri_mul_out"))
+    else:
+        ref = O.triangle_attention(zq.float(), mask, p, starting=(kind == "tri_att_start"), row_chunk=64)
+    assert torch.isfinite(y.float()).all()
+    assert relf(y, ref) < TOL_OP, (kind, zdtype)
+
+
 @pytest.mark.parametrize("rows", [1, 100, 128, 129, 1000])
 def test_transition_ragged_rows(rows):
     m = build_module("transition", dict(c=128, n=4, wseed=77)).to(DEV)
