@@ -188,6 +188,21 @@ PX_API int32_t px_transition(const void* x_in, void* x_out, int32_t dtype, const
 PX_API int32_t px_pair_bias_proj(const void* z, int32_t z_dtype, const float* ln_w, const float* ln_b, const px_bf16* w,
                           float* out, int64_t rows, int32_t n_heads, float eps, void* stream);
 
+/* ---- Exchange between the GPUs of one box (row-sharded path) ------------------------------
+ * No counterpart in the reference (which runs the Pairformer on one GPU).  A peer buffer is a
+ * cudaMalloc allocation whose 64-byte handle other processes on the same machine can open;
+ * px_copy_2d copies `height` rows of `width_bytes` (pointers, pitches and width multiples of 16
+ * bytes) with a hand-written kernel: 16-byte loads and stores, dst may be an opened peer buffer
+ * (plain stores over NVLink; no TMA, no multicast).  Ordering across GPUs is the caller's job
+ * (a stream-ordered collective after the copies, before the receiver's kernels). */
+#define PX_PEER_HANDLE_BYTES 64
+PX_API int32_t px_peer_alloc(int64_t bytes, void** ptr, unsigned char* handle);
+PX_API int32_t px_peer_open(const unsigned char* handle, void** ptr);
+PX_API int32_t px_peer_close(void* ptr);
+PX_API int32_t px_peer_free(void* ptr);
+PX_API int32_t px_copy_2d(void* dst, int64_t dpitch, const void* src, int64_t spitch, int64_t width_bytes,
+                          int64_t height, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,77 @@
+// Buffers that the other GPUs of the box can write into, and the strided copy that fills them.
+//
+// The row-sharded path exchanges slabs between GPUs (row shards <-> channel shards, row shards <-> column shards).
+// Every one of those exchanges is a set of pitched 2-D copies from a local tensor straight into its final place in a
+// peer's receive buffer, so no re-layout pass is needed on either side.  The buffers are plain cudaMalloc
+// allocations exported through CUDA IPC; the copy is a hand-written kernel with 16-byte loads from local memory and
+// 16-byte stores to peer memory over NVLink (no TMA, no multicast).  No counterpart in the reference.
+#include <cstring>
+
+#include "px_common.cuh"
+
+namespace px {
+
+// Rows of `units` 16-byte pieces; one thread per piece, grid-stride over rows x pieces.
+__global__ void __launch_bounds__(256)
+copy_2d_kernel(uint4* __restrict__ dst, long long dpitch16, const uint4* __restrict__ src, long long spitch16,
+               long long units, long long height) {
+  const long long total = units * height;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / units, c = i - r * units;
+    dst[r * dpitch16 + c] = src[r * spitch16 + c];
+  }
+}
+
+}  // namespace px
+
+using namespace px;
+
+static_assert(sizeof(cudaIpcMemHandle_t) == PX_PEER_HANDLE_BYTES, "handle size");
+
+extern "C" int32_t px_peer_alloc(int64_t bytes, void** ptr, unsigned char* handle) {
+  if (bytes <= 0 || !ptr || !handle) return PX_ERR_BAD_ARG;
+  void* p = nullptr;
+  if (cudaMalloc(&p, (size_t)bytes) != cudaSuccess) return PX_ERR_WORKSPACE;
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) {
+    cudaFree(p);
+    return PX_ERR_LAUNCH;
+  }
+  memcpy(handle, &h, sizeof(h));
+  *ptr = p;
+  return PX_OK;
+}
+
+extern "C" int32_t px_peer_open(const unsigned char* handle, void** ptr) {
+  if (!handle || !ptr) return PX_ERR_BAD_ARG;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* p = nullptr;
+  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) return PX_ERR_LAUNCH;
+  *ptr = p;
+  return PX_OK;
+}
+
+extern "C" int32_t px_peer_close(void* ptr) {
+  if (!ptr) return PX_ERR_BAD_ARG;
+  return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
+}
+
+extern "C" int32_t px_peer_free(void* ptr) {
+  if (!ptr) return PX_ERR_BAD_ARG;
+  return cudaFree(ptr) == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
+}
+
+extern "C" int32_t px_copy_2d(void* dst, int64_t dpitch, const void* src, int64_t spitch, int64_t width_bytes,
+                              int64_t height, void* stream) {
+  if (!dst || !src || width_bytes < 0 || height < 0 || dpitch < width_bytes || spitch < width_bytes) return PX_ERR_BAD_ARG;
+  if (((uintptr_t)dst | (uintptr_t)src | (uintptr_t)dpitch | (uintptr_t)spitch | (uintptr_t)width_bytes) & 15)
+    return PX_ERR_BAD_ARG;
+  if (width_bytes == 0 || height == 0) return PX_OK;
+  const long long units = width_bytes / 16, total = units * height;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  copy_2d_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((uint4*)dst, dpitch / 16, (const uint4*)src, spitch / 16,
+                                                                     units, height);
+  return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
+}

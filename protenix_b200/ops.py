@@ -300,10 +300,13 @@ def trimul_out(x: torch.Tensor, z: torch.Tensor, ln_in_w, ln_in_b, ln_out_w, ln_
 
 
 def triatt_in_proj(z: torch.Tensor, mask: Optional[torch.Tensor], ln_w, ln_b, w_bias, w_q, w_k, w_v,
-                   eps: float = 1e-5, inf: float = 1e9):
+                   eps: float = 1e-5, inf: float = 1e9, ending: bool = False):
     """q, k [n_u][4][n_t][32] and v (transposed) [n_u][4][32][ld(n_t)] bf16, bias [4][n_u][ldm] fp32,
-    mask_bias [n_u][ldm] fp32 for a row slab."""
+    mask_bias [n_u][ldm] fp32 for a slab.  z (and the mask) is [n_u][n_t][128]; with ``ending`` it is the
+    column slab [n_t][n_u][128] and the attended rows u are its columns."""
     n_u, n_t = _slab(z)
+    if ending:
+        n_u, n_t = n_t, n_u
     lib = _lib.load()
     ldm = lib.px_ld_mask(n_t)
     q = torch.empty(n_u, N_HEAD_PAIR, n_t, D_HEAD_PAIR, dtype=torch.bfloat16, device=z.device)
@@ -313,7 +316,7 @@ def triatt_in_proj(z: torch.Tensor, mask: Optional[torch.Tensor], ln_w, ln_b, w_
     mb = torch.empty(n_u, ldm, dtype=torch.float32, device=z.device)
     _launch("px_triatt_in_proj", lib.px_triatt_in_proj, _ptr(z), _pair_dtype(z), _ptr(mask), _ptr(ln_w), _ptr(ln_b),
             _ptr(w_q), _ptr(w_k), _ptr(w_v), _ptr(w_bias), _ptr(q), _ptr(k), _ptr(v), _ptr(bias), _ptr(mb), n_u, n_t,
-            ldm, 0, float(eps), float(inf), _stream(z))
+            ldm, int(ending), float(eps), float(inf), _stream(z))
     return q, k, v, bias, mb
 
 
@@ -333,11 +336,15 @@ def triatt_flash(q, k, v, bias_full: torch.Tensor, mb) -> torch.Tensor:
     return o
 
 
-def triatt_out(o: torch.Tensor, z: torch.Tensor, ln_w, ln_b, w_g, w_o, eps: float = 1e-5) -> torch.Tensor:
-    """z[n_u][n_t] += W_o(o * sigmoid(W_g LN(z))) in place."""
+def triatt_out(o: torch.Tensor, z: torch.Tensor, ln_w, ln_b, w_g, w_o, eps: float = 1e-5, ending: bool = False
+               ) -> torch.Tensor:
+    """z(u,t) += W_o(o[u][t] * sigmoid(W_g LN(z(u,t)))) in place; z is [n_u][n_t][128], or the column slab
+    [n_t][n_u][128] with ``ending``."""
     n_u, n_t = _slab(z)
+    if ending:
+        n_u, n_t = n_t, n_u
     _launch("px_triatt_out", _lib.load().px_triatt_out, _ptr(o), _ptr(z), _ptr(z), _pair_dtype(z), _ptr(ln_w),
-            _ptr(ln_b), _ptr(w_g), _ptr(w_o), n_u, n_t, 0, 1, float(eps), _stream(z))
+            _ptr(ln_b), _ptr(w_g), _ptr(w_o), n_u, n_t, int(ending), 1, float(eps), _stream(z))
     return z
 
 
@@ -358,3 +365,65 @@ def transition_rows(x: torch.Tensor, ln_w, ln_b, w_a, w_b, w_o, eps: float = 1e-
     _launch("px_transition", _lib.load().px_transition, _ptr(x), _ptr(x), _pair_dtype(x), _ptr(ln_w), _ptr(ln_b),
             _ptr(w_a), _ptr(w_b), _ptr(w_o), x.numel() // C_Z, 1, float(eps), _stream(x))
     return x
+
+
+# ---------------------------------------------------------------------------------------------
+# Buffers other GPUs of the box can write into (row-sharded path) and the strided copy that fills them.
+class PeerBuffer:
+    """A cudaMalloc allocation of this process together with the handle other processes open it by."""
+
+    def __init__(self, nbytes: int, device: torch.device) -> None:
+        import ctypes
+
+        self.nbytes, self.device = int(nbytes), device
+        ptr, handle = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
+        with torch.cuda.device(device):
+            _lib.check(_lib.load().px_peer_alloc(self.nbytes, ctypes.byref(ptr), handle), "px_peer_alloc")
+        self.ptr, self.handle = int(ptr.value), bytes(handle)
+
+    def tensor(self, shape, dtype: torch.dtype, offset_bytes: int = 0) -> torch.Tensor:
+        """A tensor over (a part of) the buffer; it does not own the memory."""
+        numel = 1
+        for d in shape:
+            numel *= int(d)
+        item = torch.empty(0, dtype=dtype).element_size()
+        if offset_bytes + numel * item > self.nbytes:
+            raise RuntimeError("peer buffer too small for the requested view")
+        typestr = {torch.bfloat16: "<u2", torch.float32: "<f4", torch.uint8: "|u1"}[dtype]
+
+        class _View:
+            pass
+
+        v = _View()
+        v.__cuda_array_interface__ = {"shape": (numel,), "typestr": typestr, "data": (self.ptr + offset_bytes, False),
+                                      "version": 3}
+        t = torch.as_tensor(v, device=self.device)
+        if dtype == torch.bfloat16:
+            t = t.view(torch.bfloat16)
+        return t.view(*shape)
+
+    def free(self) -> None:
+        if self.ptr:
+            _lib.load().px_peer_free(self.ptr)
+            self.ptr = 0
+
+
+def peer_open(handle: bytes, device: torch.device) -> int:
+    """Opens another process's PeerBuffer; returns its address in this process."""
+    import ctypes
+
+    ptr, buf = ctypes.c_void_p(), (ctypes.c_ubyte * 64).from_buffer_copy(handle)
+    with torch.cuda.device(device):
+        _lib.check(_lib.load().px_peer_open(buf, ctypes.byref(ptr)), "px_peer_open")
+    return int(ptr.value)
+
+
+def peer_close(ptr: int) -> None:
+    _lib.load().px_peer_close(ptr)
+
+
+def copy_2d(dst_ptr: int, dpitch: int, src: torch.Tensor, src_offset_bytes: int, spitch: int, width_bytes: int,
+            height: int) -> None:
+    """height rows of width_bytes from src (+offset) to the raw address dst_ptr, on src's current stream."""
+    _launch("px_copy_2d", _lib.load().px_copy_2d, dst_ptr, int(dpitch), src.data_ptr() + int(src_offset_bytes),
+            int(spitch), int(width_bytes), int(height), _stream(src))

@@ -16,14 +16,21 @@ single representation s and the pair mask are replicated.  Per block:
 * Single branch: every rank computes the attention output of its own query rows (it holds
   their pair bias); one small ``all_gather`` assembles the [N, c_s] result.
 
-Received data always lands in this GPU's memory (NCCL receive buffers) before a kernel reads it;
-no kernel touches peer memory.  The choreography is written against a small stage interface so
-that it can be exercised on CPU ranks (gloo) with a plain-torch stage implementation.
+Two transports move the slabs.  On CUDA ranks of one box (default) every exchange is a set of
+pitched 2-D copies from the local tensor straight into its final place in a peer's receive buffer
+(``ops.PeerBuffer``: cudaMalloc + CUDA IPC; ``px_copy_2d``: a hand-written kernel, plain 16-byte
+stores over NVLink), followed by one stream-ordered 4-byte ``all_reduce`` as the fence; no
+re-layout pass runs on either side, and the ending node uses the kernels' own column addressing
+instead of a transposed copy.  Otherwise (CPU ranks, ``PX_PEER_EXCHANGE=0``, shapes the copies do
+not cover) the same exchanges go through ``all_to_all`` plus permutes.  Compute kernels only ever
+read this GPU's memory.  The choreography is written against a small stage interface so that it
+can be exercised on CPU ranks (gloo) with a plain-torch stage implementation.
 """
 from __future__ import annotations
 
 import math
-from typing import Optional, Tuple
+import os
+from typing import Dict, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -57,19 +64,19 @@ class CudaStages:
                               f(mod.layer_norm_out.weight), f(mod.layer_norm_out.bias), bf16_of(mod.linear_z.weight),
                               bf16_of(mod.linear_g.weight), mod.layer_norm_in.eps)
 
-    def triatt_in_proj(self, mod, z, mask):
+    def triatt_in_proj(self, mod, z, mask, ending=False):
         f, m = self._f, mod.mha
         return ops.triatt_in_proj(z, mask, f(mod.layer_norm.weight), f(mod.layer_norm.bias), bf16_of(mod.linear.weight),
                                   bf16_of(m.linear_q.weight), bf16_of(m.linear_k.weight), bf16_of(m.linear_v.weight),
-                                  mod.layer_norm.eps, mod.inf)
+                                  mod.layer_norm.eps, mod.inf, ending)
 
     def triatt_flash(self, q, k, v, bias_full, mb):
         return ops.triatt_flash(q, k, v, bias_full, mb)
 
-    def triatt_out(self, mod, o, z):
+    def triatt_out(self, mod, o, z, ending=False):
         f, m = self._f, mod.mha
         return ops.triatt_out(o, z, f(mod.layer_norm.weight), f(mod.layer_norm.bias), bf16_of(m.linear_g.weight),
-                              bf16_of(m.linear_o.weight), mod.layer_norm.eps)
+                              bf16_of(m.linear_o.weight), mod.layer_norm.eps, ending)
 
     def transition(self, mod, z):
         f = self._f
@@ -87,6 +94,43 @@ class CudaStages:
 
 
 # ----------------------------------------------------------------------------------------------
+class PeerExchange:
+    """Receive buffers of this rank (a, b, x, column slab, returning rows) and the addresses of the
+    same buffers on every other rank.  ``put`` writes a pitched 2-D block into a rank's buffer;
+    ``fence`` orders all ranks' writes before anybody's reads."""
+
+    def __init__(self, group, world: int, rank: int, device: torch.device, n: int, z_itemsize: int) -> None:
+        self.group, self.world, self.rank, self.device = group, world, rank, device
+        nl, cp, ldn = n // world, 128 // world, (n + 7) // 8 * 8
+        sizes = {"a": cp * n * ldn * 2, "b": cp * n * ldn * 2, "x": 128 * nl * ldn * 2,
+                 "zc": n * nl * 128 * z_itemsize, "zr": nl * n * 128 * z_itemsize}
+        self.local: Dict[str, ops.PeerBuffer] = {k: ops.PeerBuffer(v, device) for k, v in sizes.items()}
+        for k in ("a", "b"):       # pad columns [n, ld) are never written by an exchange and must read as zero
+            self.local[k].tensor((sizes[k],), torch.uint8).zero_()
+        torch.cuda.synchronize(device)
+        handles = [None] * world
+        dist.all_gather_object(handles, {k: b.handle for k, b in self.local.items()}, group=group)
+        self.remote: Dict[str, list] = {k: [] for k in sizes}
+        for r in range(world):
+            for k in sizes:
+                self.remote[k].append(self.local[k].ptr if r == rank else ops.peer_open(handles[r][k], device))
+        self.flag = torch.zeros(1, device=device)
+        dist.barrier(group=group)
+
+    def put(self, key: str, dst_rank: int, dst_offset: int, dpitch: int, src: torch.Tensor, src_offset: int, spitch: int,
+            width: int, height: int) -> None:
+        ops.copy_2d(self.remote[key][dst_rank] + dst_offset, dpitch, src, src_offset, spitch, width, height)
+
+    def fence(self) -> None:
+        """Stream-ordered: completes on a rank only after every rank's earlier copies have completed."""
+        dist.all_reduce(self.flag, group=self.group)
+
+    def order(self):
+        """Destination ranks, starting with the next one so that the ranks do not all write to rank 0 first."""
+        return [(self.rank + 1 + i) % self.world for i in range(self.world)]
+
+
+# ----------------------------------------------------------------------------------------------
 class ShardedPairformer:
     """Runs the blocks of a ``PairformerStack`` (or one ``PairformerBlock``) on a row-sharded z."""
 
@@ -96,6 +140,7 @@ class ShardedPairformer:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.stages = stages if stages is not None else CudaStages()
+        self._peer: Dict[tuple, PeerExchange] = {}
 
     # ---- helpers ------------------------------------------------------------------------------
     def shard_rows(self, z: torch.Tensor) -> torch.Tensor:
@@ -156,6 +201,68 @@ class ShardedPairformer:
         recv = self._all_to_all(send)                                        # [src i-block][i][j][c]
         return recv.permute(2, 0, 1, 3).reshape(nl, n, c).contiguous()
 
+    # ---- the same exchanges as direct copies into peer buffers ----------------------------------
+    def _peer_for(self, z_loc: torch.Tensor) -> Optional[PeerExchange]:
+        """The peer transport for this shape, or None when the all_to_all path has to be used."""
+        if not (z_loc.is_cuda and isinstance(self.stages, CudaStages)) or self.world == 1:
+            return None
+        if os.environ.get("PX_PEER_EXCHANGE", "1") == "0":
+            return None
+        nl, n, _ = z_loc.shape
+        if 128 % self.world or nl % 8 or n % 8:          # every copied run must be a multiple of 16 bytes
+            return None
+        key = (n, z_loc.element_size(), z_loc.device.index)
+        if key not in self._peer:
+            self._peer[key] = PeerExchange(self.group, self.world, self.rank, z_loc.device, n, z_loc.element_size())
+        return self._peer[key]
+
+    def _peer_rows_to_channels(self, px: PeerExchange, t: torch.Tensor, key: str, k_sharded: bool) -> None:
+        """The copies of ``_rows_to_channels`` (no fence): t [128][rows][ld] -> buffer ``key`` [128/P][N][ld(N)]."""
+        p, me = self.world, self.rank
+        c, r, ldl = t.shape
+        cp = c // p
+        for d in px.order():
+            if not k_sharded:      # my rows become rows me*r.. of every channel: one run of r*ld per channel
+                px.put(key, d, me * r * ldl * 2, p * r * ldl * 2, t, d * cp * r * ldl * 2, r * ldl * 2, r * ldl * 2, cp)
+            else:                  # my rows are the contraction index: a run of N/P per (channel, i)
+                nl, ldn = r // p, (r + 7) // 8 * 8
+                px.put(key, d, me * nl * 2, ldn * 2, t, d * cp * r * ldl * 2, ldl * 2, nl * 2, cp * r)
+
+    def _tri_mul_peer(self, px: PeerExchange, mod, z_loc, mask_loc, incoming: bool) -> None:
+        st, p, me = self.stages, self.world, self.rank
+        nl, n, _ = z_loc.shape
+        cp, ldn = 128 // p, (n + 7) // 8 * 8
+        a, b = st.trimul_in_proj(mod, z_loc, mask_loc, incoming)
+        self._peer_rows_to_channels(px, a, "a", incoming)
+        self._peer_rows_to_channels(px, b, "b", incoming)
+        px.fence()
+        del a, b
+        x = st.trimul_contract(px.local["a"].tensor((cp, n, ldn), torch.bfloat16),
+                               px.local["b"].tensor((cp, n, ldn), torch.bfloat16))
+        for d in px.order():       # rows d*nl.. of my channels -> channels me*cp.. of rank d's row slab
+            px.put("x", d, me * cp * nl * ldn * 2, nl * ldn * 2, x, d * nl * ldn * 2, n * ldn * 2, nl * ldn * 2, cp)
+        px.fence()
+        del x
+        st.trimul_out(mod, px.local["x"].tensor((128, nl, ldn), torch.bfloat16), z_loc)
+
+    def _tri_att_end_peer(self, px: PeerExchange, mod, z_loc, mask_cols) -> None:
+        """Ending node on the column slab zc [N i][N/P j][c] (the kernels address it as element (u=j, t=i))."""
+        st, p, me = self.stages, self.world, self.rank
+        nl, n, c = z_loc.shape
+        run = nl * c * z_loc.element_size()
+        for d in px.order():       # columns of rank d, my rows i
+            px.put("zc", d, me * nl * run, run, z_loc, d * run, p * run, run, nl)
+        px.fence()
+        zc = px.local["zc"].tensor((n, nl, c), z_loc.dtype)
+        q, k, v, bias_loc, mb = st.triatt_in_proj(mod, zc, mask_cols, True)
+        h, _, ldm = bias_loc.shape
+        bias_full = self._all_gather(bias_loc).permute(1, 0, 2, 3).reshape(h, p * nl, ldm)
+        st.triatt_out(mod, st.triatt_flash(q, k, v, bias_full, mb), zc, True)
+        for e in px.order():       # rows of rank e, my columns
+            px.put("zr", e, me * run, p * run, zc, e * nl * run, run, run, nl)
+        px.fence()
+        z_loc.copy_(px.local["zr"].tensor((nl, n, c), z_loc.dtype))
+
     # ---- sub-modules ----------------------------------------------------------------------------
     def _tri_mul(self, mod, z_loc, mask_loc, incoming: bool) -> None:
         st = self.stages
@@ -205,19 +312,29 @@ class ShardedPairformer:
         if nl * self.world != n:
             raise RuntimeError(f"z_loc has {nl} rows; expected N/P = {n}/{self.world}")
         rows = slice(self.rank * nl, (self.rank + 1) * nl)
-        mask_loc = mask_t_loc = None
+        px = self._peer_for(z_loc)
+        mask_loc = mask_t_loc = mask_cols = None
         if pair_mask is not None:
             pair_mask = pair_mask.to(torch.float32)
             mask_loc = pair_mask[rows].contiguous()
-            mask_t_loc = pair_mask.t()[rows].contiguous()
+            if px is None:
+                mask_t_loc = pair_mask.t()[rows].contiguous()
+            else:
+                mask_cols = pair_mask[:, rows].contiguous()
         for blk in self.blocks:
-            self._tri_mul(blk.tri_mul_out, z_loc, mask_loc, incoming=False)
-            self._tri_mul(blk.tri_mul_in, z_loc, mask_loc, incoming=True)
-            self._tri_att_rows(blk.tri_att_start, z_loc, mask_loc)
-            zt = self._transpose_shard(z_loc)
-            self._tri_att_rows(blk.tri_att_end, zt, mask_t_loc)
-            z_loc.copy_(self._transpose_shard(zt))
-            del zt
+            if px is not None:
+                self._tri_mul_peer(px, blk.tri_mul_out, z_loc, mask_loc, incoming=False)
+                self._tri_mul_peer(px, blk.tri_mul_in, z_loc, mask_loc, incoming=True)
+                self._tri_att_rows(blk.tri_att_start, z_loc, mask_loc)
+                self._tri_att_end_peer(px, blk.tri_att_end, z_loc, mask_cols)
+            else:
+                self._tri_mul(blk.tri_mul_out, z_loc, mask_loc, incoming=False)
+                self._tri_mul(blk.tri_mul_in, z_loc, mask_loc, incoming=True)
+                self._tri_att_rows(blk.tri_att_start, z_loc, mask_loc)
+                zt = self._transpose_shard(z_loc)
+                self._tri_att_rows(blk.tri_att_end, zt, mask_t_loc)
+                z_loc.copy_(self._transpose_shard(zt))
+                del zt
             self.stages.transition(blk.pair_transition, z_loc)
             if blk.c_s > 0 and s is not None:
                 s = self._single_branch(blk, s, z_loc)

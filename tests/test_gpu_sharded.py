@@ -51,6 +51,50 @@ def test_row_slab_stages_equal_square_stages(n, parts):
     assert torch.equal(st.trimul_contract(a_f[32:48].contiguous(), b_f[32:48].contiguous()), x_f[32:48])
 
 
+def test_pitched_copy_and_peer_buffer_on_one_device():
+    """px_copy_2d against torch slicing, into a PeerBuffer viewed as a tensor (the multi-GPU exchanges are such copies)."""
+    g = torch.Generator().manual_seed(1)
+    src = torch.randn(6, 40, 24, generator=g).to(torch.bfloat16).to(DEV)          # [c][rows][ld]
+    buf = ops.PeerBuffer(3 * 80 * 24 * 2, torch.device(DEV, torch.cuda.current_device()))
+    dst = buf.tensor((3, 80, 24), torch.bfloat16)
+    dst.zero_()
+    # channels 3..5 of src become rows 40..79 of every channel of dst: one run of 40*24 elements per channel
+    ops.copy_2d(buf.ptr + 40 * 24 * 2, 80 * 24 * 2, src, 3 * 40 * 24 * 2, 40 * 24 * 2, 40 * 24 * 2, 3)
+    torch.cuda.synchronize()
+    assert torch.equal(dst[:, 40:], src[3:]) and float(dst[:, :40].float().abs().sum()) == 0.0
+    # a narrow run per row (the k-sharded exchange): columns 8..15 of every row
+    ops.copy_2d(buf.ptr + 8 * 2, 24 * 2, src, 0, 24 * 2, 8 * 2, 3 * 40)
+    torch.cuda.synchronize()
+    assert torch.equal(dst.view(-1, 24)[:120, 8:16], src.view(-1, 24)[:120, :8])
+    with pytest.raises(RuntimeError):
+        ops.copy_2d(buf.ptr + 2, 48, src, 0, 48, 16, 1)                              # misaligned destination
+    buf.free()
+
+
+def test_column_slab_attention_equals_transposed_row_slab():
+    """The ending node on a column slab [N i][nl j][c] (kernels' own addressing) against the starting-node kernels on
+    the explicitly transposed slab."""
+    n, parts = 96, 3
+    nl = n // parts
+    g = torch.Generator().manual_seed(7)
+    z = torch.randn(n, n, 128, generator=g).to(torch.bfloat16).to(DEV)
+    mask = random_mask(n, 4).to(DEV)
+    blk = build_module("block", dict(c_s=0, wseed=5)).to(DEV)
+    st = CudaStages()
+    for r in range(parts):
+        cols = slice(r * nl, (r + 1) * nl)
+        zc, mc = z[:, cols].contiguous(), mask[:, cols].contiguous()              # [N i][nl j]
+        zt, mt = z[:, cols].transpose(0, 1).contiguous(), mask[:, cols].t().contiguous()   # [nl j][N i]
+        q, k, v, bias, mb = st.triatt_in_proj(blk.tri_att_end, zc, mc, True)
+        q2, k2, v2, bias2, mb2 = st.triatt_in_proj(blk.tri_att_end, zt, mt)
+        assert torch.equal(q, q2) and torch.equal(k, k2) and torch.equal(v, v2)
+        assert torch.equal(bias, bias2) and torch.equal(mb, mb2)
+        o = torch.randn(nl, n, 128, generator=g).to(torch.bfloat16).to(DEV)
+        out_c = st.triatt_out(blk.tri_att_end, o, zc.clone(), True)
+        out_t = st.triatt_out(blk.tri_att_end, o, zt.clone())
+        assert torch.equal(out_c.transpose(0, 1), out_t)
+
+
 def test_sharded_path_with_one_rank_equals_module():
     import torch.distributed as dist
 
