@@ -202,6 +202,10 @@ PX_API int32_t px_peer_close(void* ptr);
 PX_API int32_t px_peer_free(void* ptr);
 PX_API int32_t px_copy_2d(void* dst, int64_t dpitch, const void* src, int64_t spitch, int64_t width_bytes,
                           int64_t height, void* stream);
+/* The same copy geometry for `count` (<= PX_COPY_BATCH_MAX) source/destination pairs in one launch. */
+#define PX_COPY_BATCH_MAX 16
+PX_API int32_t px_copy_2d_batch(void* const* dst, const void* const* src, int32_t count, int64_t dpitch, int64_t spitch,
+                                int64_t width_bytes, int64_t height, void* stream);
 
 #ifdef __cplusplus
 }

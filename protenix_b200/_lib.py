@@ -44,6 +44,7 @@ SIGNATURES = {
     "px_peer_close": (I32, [P]),
     "px_peer_free": (I32, [P]),
     "px_copy_2d": (I32, [P, I64, P, I64, I64, I64, P]),
+    "px_copy_2d_batch": (I32, [P, P, I32, I64, I64, I64, I64, P]),
 }
 
 _lib = None

@@ -22,6 +22,23 @@ copy_2d_kernel(uint4* __restrict__ dst, long long dpitch16, const uint4* __restr
   }
 }
 
+// The same copy to up to 16 destinations in one launch (blockIdx.y = destination): the exchanges of the row-sharded
+// path send one block of identical shape to every rank.
+struct CopyBatch {
+  uint4* dst[PX_COPY_BATCH_MAX];
+  const uint4* src[PX_COPY_BATCH_MAX];
+};
+__global__ void __launch_bounds__(256)
+copy_2d_batch_kernel(CopyBatch b, long long dpitch16, long long spitch16, long long units, long long height) {
+  uint4* __restrict__ dst = b.dst[blockIdx.y];
+  const uint4* __restrict__ src = b.src[blockIdx.y];
+  const long long total = units * height;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / units, c = i - r * units;
+    dst[r * dpitch16 + c] = src[r * spitch16 + c];
+  }
+}
+
 }  // namespace px
 
 using namespace px;
@@ -73,5 +90,28 @@ extern "C" int32_t px_copy_2d(void* dst, int64_t dpitch, const void* src, int64_
   if (blocks > 148 * 16) blocks = 148 * 16;
   copy_2d_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((uint4*)dst, dpitch / 16, (const uint4*)src, spitch / 16,
                                                                      units, height);
+  return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
+}
+
+extern "C" int32_t px_copy_2d_batch(void* const* dst, const void* const* src, int32_t count, int64_t dpitch, int64_t spitch,
+                                    int64_t width_bytes, int64_t height, void* stream) {
+  if (!dst || !src || count <= 0 || count > PX_COPY_BATCH_MAX || width_bytes < 0 || height < 0 || dpitch < width_bytes ||
+      spitch < width_bytes)
+    return PX_ERR_BAD_ARG;
+  if (((uintptr_t)dpitch | (uintptr_t)spitch | (uintptr_t)width_bytes) & 15) return PX_ERR_BAD_ARG;
+  CopyBatch b;
+  for (int i = 0; i < PX_COPY_BATCH_MAX; ++i) {
+    const int j = i < count ? i : 0;
+    if (!dst[j] || !src[j] || (((uintptr_t)dst[j] | (uintptr_t)src[j]) & 15)) return PX_ERR_BAD_ARG;
+    b.dst[i] = (uint4*)dst[j];
+    b.src[i] = (const uint4*)src[j];
+  }
+  if (width_bytes == 0 || height == 0) return PX_OK;
+  const long long units = width_bytes / 16, total = units * height;
+  long long blocks = (total + 255) / 256;
+  const long long cap = (148 * 16 + count - 1) / count;
+  if (blocks > cap) blocks = cap;
+  copy_2d_batch_kernel<<<dim3((unsigned)blocks, (unsigned)count), 256, 0, (cudaStream_t)stream>>>(b, dpitch / 16, spitch / 16, units,
+                                                                                              height);
   return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
 }

@@ -427,3 +427,14 @@ def copy_2d(dst_ptr: int, dpitch: int, src: torch.Tensor, src_offset_bytes: int,
     """height rows of width_bytes from src (+offset) to the raw address dst_ptr, on src's current stream."""
     _launch("px_copy_2d", _lib.load().px_copy_2d, dst_ptr, int(dpitch), src.data_ptr() + int(src_offset_bytes),
             int(spitch), int(width_bytes), int(height), _stream(src))
+
+
+def copy_2d_batch(dst_ptrs, src: torch.Tensor, src_offsets, dpitch: int, spitch: int, width_bytes: int, height: int) -> None:
+    """One launch: for every i, height rows of width_bytes from src (+src_offsets[i]) to the raw address dst_ptrs[i]."""
+    import ctypes
+
+    n = len(dst_ptrs)
+    d = (ctypes.c_void_p * n)(*[int(p) for p in dst_ptrs])
+    s_ = (ctypes.c_void_p * n)(*[src.data_ptr() + int(o) for o in src_offsets])
+    _launch("px_copy_2d_batch", _lib.load().px_copy_2d_batch, d, s_, n, int(dpitch), int(spitch), int(width_bytes),
+            int(height), _stream(src))

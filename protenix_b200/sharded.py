@@ -117,9 +117,13 @@ class PeerExchange:
         self.flag = torch.zeros(1, device=device)
         dist.barrier(group=group)
 
-    def put(self, key: str, dst_rank: int, dst_offset: int, dpitch: int, src: torch.Tensor, src_offset: int, spitch: int,
-            width: int, height: int) -> None:
-        ops.copy_2d(self.remote[key][dst_rank] + dst_offset, dpitch, src, src_offset, spitch, width, height)
+    def put_all(self, key: str, dst_offset: int, dpitch: int, src: torch.Tensor, src_offset_of, spitch: int, width: int,
+                height: int) -> None:
+        """One block of the same shape to every rank (one launch): rank d receives the block that starts
+        ``src_offset_of(d)`` bytes into src, at ``dst_offset`` of its buffer ``key``."""
+        order = self.order()
+        ops.copy_2d_batch([self.remote[key][d] + dst_offset for d in order], src, [src_offset_of(d) for d in order],
+                          dpitch, spitch, width, height)
 
     def fence(self) -> None:
         """Stream-ordered: completes on a rank only after every rank's earlier copies have completed."""
@@ -221,12 +225,32 @@ class ShardedPairformer:
         p, me = self.world, self.rank
         c, r, ldl = t.shape
         cp = c // p
-        for d in px.order():
-            if not k_sharded:      # my rows become rows me*r.. of every channel: one run of r*ld per channel
-                px.put(key, d, me * r * ldl * 2, p * r * ldl * 2, t, d * cp * r * ldl * 2, r * ldl * 2, r * ldl * 2, cp)
-            else:                  # my rows are the contraction index: a run of N/P per (channel, i)
-                nl, ldn = r // p, (r + 7) // 8 * 8
-                px.put(key, d, me * nl * 2, ldn * 2, t, d * cp * r * ldl * 2, ldl * 2, nl * 2, cp * r)
+        if not k_sharded:          # my rows become rows me*r.. of every channel: one run of r*ld per channel
+            px.put_all(key, me * r * ldl * 2, p * r * ldl * 2, t, lambda d: d * cp * r * ldl * 2, r * ldl * 2, r * ldl * 2, cp)
+        else:                      # my rows are the contraction index: a run of N/P per (channel, i)
+            nl, ldn = r // p, (r + 7) // 8 * 8
+            px.put_all(key, me * nl * 2, ldn * 2, t, lambda d: d * cp * r * ldl * 2, ldl * 2, nl * 2, cp * r)
+
+    def _peer_channels_to_rows(self, px, x: torch.Tensor) -> None:
+        """x [128/P][N][ld] (my channels) -> buffer ``x`` [128][N/P][ld] of every rank: rows d*nl.. go to rank d."""
+        p, me = self.world, self.rank
+        cp, n, ldn = x.shape
+        nl = n // p
+        px.put_all("x", me * cp * nl * ldn * 2, nl * ldn * 2, x, lambda d: d * nl * ldn * 2, n * ldn * 2, nl * ldn * 2, cp)
+
+    def _peer_to_columns(self, px, z_loc: torch.Tensor) -> None:
+        """Row slab [N/P i][N j][c] -> buffer ``zc`` [N i][N/P j][c] of every rank: columns d*nl.. go to rank d."""
+        p, me = self.world, self.rank
+        nl, n, c = z_loc.shape
+        run = nl * c * z_loc.element_size()
+        px.put_all("zc", me * nl * run, run, z_loc, lambda d: d * run, p * run, run, nl)
+
+    def _peer_from_columns(self, px, zc: torch.Tensor) -> None:
+        """Column slab [N i][N/P j][c] -> buffer ``zr`` [N/P i][N j][c] of every rank: rows e*nl.. go to rank e."""
+        p, me = self.world, self.rank
+        n, nl, c = zc.shape
+        run = nl * c * zc.element_size()
+        px.put_all("zr", me * run, p * run, zc, lambda e: e * nl * run, run, run, nl)
 
     def _tri_mul_peer(self, px: PeerExchange, mod, z_loc, mask_loc, incoming: bool) -> None:
         st, p, me = self.stages, self.world, self.rank
@@ -239,8 +263,7 @@ class ShardedPairformer:
         del a, b
         x = st.trimul_contract(px.local["a"].tensor((cp, n, ldn), torch.bfloat16),
                                px.local["b"].tensor((cp, n, ldn), torch.bfloat16))
-        for d in px.order():       # rows d*nl.. of my channels -> channels me*cp.. of rank d's row slab
-            px.put("x", d, me * cp * nl * ldn * 2, nl * ldn * 2, x, d * nl * ldn * 2, n * ldn * 2, nl * ldn * 2, cp)
+        self._peer_channels_to_rows(px, x)
         px.fence()
         del x
         st.trimul_out(mod, px.local["x"].tensor((128, nl, ldn), torch.bfloat16), z_loc)
@@ -249,17 +272,14 @@ class ShardedPairformer:
         """Ending node on the column slab zc [N i][N/P j][c] (the kernels address it as element (u=j, t=i))."""
         st, p, me = self.stages, self.world, self.rank
         nl, n, c = z_loc.shape
-        run = nl * c * z_loc.element_size()
-        for d in px.order():       # columns of rank d, my rows i
-            px.put("zc", d, me * nl * run, run, z_loc, d * run, p * run, run, nl)
+        self._peer_to_columns(px, z_loc)
         px.fence()
         zc = px.local["zc"].tensor((n, nl, c), z_loc.dtype)
         q, k, v, bias_loc, mb = st.triatt_in_proj(mod, zc, mask_cols, True)
         h, _, ldm = bias_loc.shape
         bias_full = self._all_gather(bias_loc).permute(1, 0, 2, 3).reshape(h, p * nl, ldm)
         st.triatt_out(mod, st.triatt_flash(q, k, v, bias_full, mb), zc, True)
-        for e in px.order():       # rows of rank e, my columns
-            px.put("zr", e, me * run, p * run, zc, e * nl * run, run, run, nl)
+        self._peer_from_columns(px, zc)
         px.fence()
         z_loc.copy_(px.local["zr"].tensor((nl, n, c), z_loc.dtype))
 

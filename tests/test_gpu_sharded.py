@@ -68,6 +68,18 @@ def test_pitched_copy_and_peer_buffer_on_one_device():
     assert torch.equal(dst.view(-1, 24)[:120, 8:16], src.view(-1, 24)[:120, :8])
     with pytest.raises(RuntimeError):
         ops.copy_2d(buf.ptr + 2, 48, src, 0, 48, 16, 1)                              # misaligned destination
+    # the batched form: channel pair d of src -> rows 40.. of channels 0..1 of destination d (three destinations)
+    bufs = [ops.PeerBuffer(2 * 80 * 24 * 2, buf.device) for _ in range(3)]
+    views = [b.tensor((2, 80, 24), torch.bfloat16) for b in bufs]
+    for v in views:
+        v.zero_()
+    ops.copy_2d_batch([b.ptr + 40 * 24 * 2 for b in bufs], src, [d * 2 * 40 * 24 * 2 for d in range(3)], 80 * 24 * 2,
+                      40 * 24 * 2, 40 * 24 * 2, 2)
+    torch.cuda.synchronize()
+    for d, v in enumerate(views):
+        assert torch.equal(v[:, 40:], src[2 * d:2 * d + 2]) and float(v[:, :40].float().abs().sum()) == 0.0
+    for b in bufs:
+        b.free()
     buf.free()
 
 
