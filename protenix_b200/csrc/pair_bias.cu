@@ -1,4 +1,4 @@
-// Pair-bias projection of the single-representation branch (the transition lives in transition_tcgen05.cu).
+// Pair-bias projection of the single-representation branch.
 #include "px_common.cuh"
 
 namespace px {

@@ -65,23 +65,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
 }
-// 2^x for a packed pair: the arguments are rounded to bf16, the results are bf16 (one MUFU op for two).
-__device__ __forceinline__ uint32_t exp2_bf16x2(float lo, float hi) {
-  uint32_t x = pack_bf16x2(lo, hi), y;
-  asm("ex2.approx.ftz.bf16x2 %0, %1;\n" : "=r"(y) : "r"(x));
-  return y;
-}
-// Same, but the pair is rounded and packed with integer ALU operations (add half an ulp, keep the upper
-// halves) instead of cvt.rn.bf16x2.f32, which occupies the same quarter-rate unit as ex2.
-__device__ __forceinline__ uint32_t exp2_bf16x2_alu(float lo, float hi) {
-  uint32_t x = __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632), y;
-  asm("ex2.approx.ftz.bf16x2 %0, %1;\n" : "=r"(y) : "r"(x));
-  return y;
-}
-__device__ __forceinline__ float sigmoidf_fast(float x) {
-  return __fdividef(1.0f, 1.0f + fast_exp2(-kLog2e * x));
-}
-
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -107,27 +90,6 @@ __device__ __forceinline__ void store2(bf16* p, float a, float b) {
 }
 
 // eight consecutive channels of a row
-__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
-  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
-__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
-  const uint4 u = *reinterpret_cast<const uint4*>(p);
-  const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
-  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
-}
-__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
-  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
-}
-__device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
-  uint4 u;
-  u.x = pack_bf16x2(v[0], v[1]);
-  u.y = pack_bf16x2(v[2], v[3]);
-  u.z = pack_bf16x2(v[4], v[5]);
-  u.w = pack_bf16x2(v[6], v[7]);
-  *reinterpret_cast<uint4*>(p) = u;
-}
 
 // ---- LayerNorm of a 128-channel tile into a bf16 operand tile ----------------------------
 // Warp `warp` normalises rows [16*warp, 16*warp+16) of a 128-row tile; lane l owns channels
@@ -196,16 +158,6 @@ __device__ __forceinline__ void warp_gemm_k128(float (&acc)[NACC][4], const uint
       mma_bf16(acc[NT0 + 2 * np], a[ks], b[0], b[1]);
       mma_bf16(acc[NT0 + 2 * np + 1], a[ks], b[2], b[3]);
     }
-  }
-}
-
-// Copy `rows` rows of 128 bf16 (256 B) from W (row stride 128) to shared rows [dst_row0, ..) of stride kLdA.
-// All 256 threads of the CTA take part; the caller commits the cp.async group.
-__device__ __forceinline__ void load_w_rows(bf16* sW, int dst_row0, const bf16* __restrict__ W, int src_row0, int rows,
-                                            int tid) {
-  for (int idx = tid; idx < rows * 16; idx += 256) {
-    int r = idx >> 4, ch = idx & 15;
-    cp_async16(smem_u32(sW + (dst_row0 + r) * kLdA + ch * 8), W + (size_t)(src_row0 + r) * kC + ch * 8, true);
   }
 }
 
