@@ -8,7 +8,9 @@ metric: token-pairs/s = N^2 * blocks / seconds-per-stack  (= N^2 / seconds per b
     python bench.py --gpus 1 --steps 3 --warmup 3
     python bench.py --impl reference ...      # the CPU arm: oracle port on the host cores
 
-Prints ONE JSON line (rank 0).  See DESIGN.md for how every field is obtained.
+Prints ONE JSON line (rank 0): value = pairs/s with inputs resident in HBM, e2e = the same through the module API
+with host copies in the timed region, roofline = the kernel with the largest share of event time against the
+measured peaks, cpu_baseline = the oracle on a bounded row slab, clocks = NVML samples taken during the timed region.
 """
 from __future__ import annotations
 

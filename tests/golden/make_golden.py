@@ -55,7 +55,7 @@ def import_reference(path: str):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a bytedance/Protenix checkout")
     args = ap.parse_args()
     ref_pf, ref_prim, ref_layers, ref_tri = import_reference(args.reference)
 
