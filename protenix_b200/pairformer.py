@@ -44,6 +44,20 @@ class PairformerBlock(nn.Module):
                                                          c_a=c_s, c_z=c_z)
             self.single_transition = Transition(c_in=c_s, n=4)
 
+    def pair_path_(self, zc: torch.Tensor, mask: Optional[torch.Tensor]) -> None:
+        """The five pair updates of the block, in place."""
+        self.tri_mul_out.apply_(zc, mask)
+        self.tri_mul_in.apply_(zc, mask)
+        self.tri_att_start.apply_(zc, mask, ending=False)
+        self.tri_att_end.apply_(zc, mask, ending=True)
+        self.pair_transition.forward_residual_(zc)
+
+    def single_path(self, s: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+        """The single-representation update, given the pair bias of the block's final z.  It needs nothing else from
+        z, and the pair path never reads s: a stack can run it beside the pair path of the next block."""
+        s = s + self.attention_pair_bias(a=s, s=None, z=None, bias=bias)
+        return s + self.single_transition(s)
+
     @torch.no_grad()
     def forward(self, s: Optional[torch.Tensor], z: torch.Tensor, pair_mask: Optional[torch.Tensor],
                 triangle_multiplicative: str = "torch", triangle_attention: str = "torch",
@@ -54,14 +68,9 @@ class PairformerBlock(nn.Module):
         zc, mask, batch = _pair_input(z, pair_mask)
         if not inplace_safe and zc.data_ptr() == z.data_ptr():
             zc = zc.clone()
-        self.tri_mul_out.apply_(zc, mask)
-        self.tri_mul_in.apply_(zc, mask)
-        self.tri_att_start.apply_(zc, mask, ending=False)
-        self.tri_att_end.apply_(zc, mask, ending=True)
-        self.pair_transition.forward_residual_(zc)
+        self.pair_path_(zc, mask)
         if self.c_s > 0:
-            s = s + self.attention_pair_bias(a=s, s=None, z=zc)
-            s = s + self.single_transition(s)
+            s = self.single_path(s, self.attention_pair_bias.pair_bias(zc))
         return s, (zc[None] if batch else zc)
 
 
@@ -85,6 +94,32 @@ class PairformerStack(nn.Module):
         zc, mask, batch = _pair_input(z, pair_mask)
         if not inplace_safe and zc.data_ptr() == z.data_ptr():
             zc = zc.clone()
+        # The pair path does not depend on s, and the single path takes only the pair bias from z: the single path of
+        # block b runs on a side stream beside the pair path of block b + 1.
+        main = torch.cuda.current_stream(zc.device)
+        side = _side_stream(zc.device)
+        side.wait_stream(main)
         for block in self.blocks:
-            s, zc = block(s, zc, mask, inplace_safe=True)
+            if block.training and block.p_drop > 0:
+                raise RuntimeError("PairformerBlock: training-mode dropout is not implemented; call .eval()")
+            block.pair_path_(zc, mask)
+            if block.c_s > 0 and s is not None:
+                bias = block.attention_pair_bias.pair_bias(zc)       # reads the block's final z, on the main stream
+                bias.record_stream(side)
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    s = block.single_path(s, bias)
+        main.wait_stream(side)
+        if s is not None:
+            s.record_stream(main)
         return s, (zc[None] if batch else zc)
+
+
+_SIDE_STREAMS = {}
+
+
+def _side_stream(device: torch.device) -> "torch.cuda.Stream":
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+    return _SIDE_STREAMS[key]

@@ -300,12 +300,12 @@ class ShardedPairformer:
         bias_full = self._all_gather(bias_loc).permute(1, 0, 2, 3).reshape(h, self.world * nl, ldm)
         st.triatt_out(mod, st.triatt_flash(q, k, v, bias_full, mb), z_loc)
 
-    def _single_branch(self, blk, s, z_loc):
-        """s + AttentionPairBias(s, z) + Transition(.), query rows sharded like z."""
+    def _single_branch(self, blk, s, bias):
+        """s + AttentionPairBias(s, z) + Transition(.), query rows sharded like z; ``bias`` [H, N/P, N] is the pair
+        bias of this rank's rows of the block's final z (all this branch takes from z)."""
         apb, att = blk.attention_pair_bias, blk.attention_pair_bias.attention
-        nl = z_loc.shape[0]
+        nl = bias.shape[1]
         rows = slice(self.rank * nl, (self.rank + 1) * nl)
-        bias = self.stages.pair_bias(apb, z_loc)                                       # [H, nl, N]
         dt = s.dtype
         x = self.stages.single_layer_norm(apb.layernorm_a, s.float().contiguous())
         n, h, d = x.shape[0], apb.n_heads, att.c_hidden
@@ -333,6 +333,12 @@ class ShardedPairformer:
             raise RuntimeError(f"z_loc has {nl} rows; expected N/P = {n}/{self.world}")
         rows = slice(self.rank * nl, (self.rank + 1) * nl)
         px = self._peer_for(z_loc)
+        main = side = None
+        if z_loc.is_cuda and isinstance(self.stages, CudaStages):
+            from .pairformer import _side_stream
+
+            main, side = torch.cuda.current_stream(z_loc.device), _side_stream(z_loc.device)
+            side.wait_stream(main)
         mask_loc = mask_t_loc = mask_cols = None
         if pair_mask is not None:
             pair_mask = pair_mask.to(torch.float32)
@@ -357,5 +363,16 @@ class ShardedPairformer:
                 del zt
             self.stages.transition(blk.pair_transition, z_loc)
             if blk.c_s > 0 and s is not None:
-                s = self._single_branch(blk, s, z_loc)
+                bias = self.stages.pair_bias(blk.attention_pair_bias, z_loc)        # reads the block's final z
+                if side is None:
+                    s = self._single_branch(blk, s, bias)
+                else:               # the pair path never reads s: the rest runs beside the next block's pair path
+                    bias.record_stream(side)
+                    side.wait_stream(main)
+                    with torch.cuda.stream(side):
+                        s = self._single_branch(blk, s, bias)
+        if side is not None:
+            main.wait_stream(side)
+            if s is not None:
+                s.record_stream(main)
         return s, z_loc

@@ -52,15 +52,22 @@ class AttentionPairBias(nn.Module):
         self.layernorm_z = LayerNorm(c_z, create_offset=create_offset_ln_z)
         self.linear_nobias_z = LinearNoBias(in_features=c_z, out_features=n_heads)
 
-    def forward(self, a: torch.Tensor, s: Optional[torch.Tensor], z: torch.Tensor, **_unused) -> torch.Tensor:
+    def pair_bias(self, z: torch.Tensor) -> torch.Tensor:
+        """[H, N, N] fp32 = Linear(LayerNorm(z)): the only thing this module takes from the pair representation."""
         if z.dim() == 4:
             z = z[0]
+        ln_b = self.layernorm_z.bias
+        return ops.pair_bias_proj(z.contiguous(), self.layernorm_z.weight.detach().float(),
+                                  ln_b.detach().float() if ln_b is not None else None,
+                                  bf16_of(self.linear_nobias_z.weight), eps=self.layernorm_z.eps)
+
+    def forward(self, a: torch.Tensor, s: Optional[torch.Tensor], z: Optional[torch.Tensor],
+                bias: Optional[torch.Tensor] = None, **_unused) -> torch.Tensor:
+        """``bias`` = a pair bias computed earlier with ``pair_bias(z)`` (z may then be None)."""
         dt = a.dtype
         att = self.attention
-        ln_b = self.layernorm_z.bias
-        bias = ops.pair_bias_proj(z.contiguous(), self.layernorm_z.weight.detach().float(),
-                                  ln_b.detach().float() if ln_b is not None else None,
-                                  bf16_of(self.linear_nobias_z.weight), eps=self.layernorm_z.eps)  # [H, N, N] fp32
+        if bias is None:
+            bias = self.pair_bias(z)
         x = self.layernorm_a(a.float().contiguous())
         lead = x.shape[:-2]
         n, h, d = x.shape[-2], self.n_heads, att.c_hidden
