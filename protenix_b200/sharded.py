@@ -9,7 +9,7 @@ single representation s and the pair mask are replicated.  Per block:
   (each rank then contracts 128/P channels over the full N x N), and x returns with a third.
   For the incoming direction the local rows are the contraction index: the local projection
   yields a[c][i][k in local rows] and the same ``all_to_all`` assembles the k axis.
-* Starting-node attention: only the pair bias [4, N, N] couples the rows: one ``all_gather``.
+* Starting-node attention: only the pair bias [4, N, N] couples the rows: it is gathered.
 * Ending-node attention: z is exchanged to column shards with an ``all_to_all`` (a distributed
   transpose), the starting-node path runs on the transposed slab, and a second ``all_to_all``
   brings the update back.
@@ -102,8 +102,9 @@ class PeerExchange:
     def __init__(self, group, world: int, rank: int, device: torch.device, n: int, z_itemsize: int) -> None:
         self.group, self.world, self.rank, self.device = group, world, rank, device
         nl, cp, ldn = n // world, 128 // world, (n + 7) // 8 * 8
+        ldm = (n + 127) // 128 * 128
         sizes = {"a": cp * n * ldn * 2, "b": cp * n * ldn * 2, "x": 128 * nl * ldn * 2,
-                 "zc": n * nl * 128 * z_itemsize, "zr": nl * n * 128 * z_itemsize}
+                 "zc": n * nl * 128 * z_itemsize, "zr": nl * n * 128 * z_itemsize, "bias": 4 * n * ldm * 4}
         self.local: Dict[str, ops.PeerBuffer] = {k: ops.PeerBuffer(v, device) for k, v in sizes.items()}
         for k in ("a", "b"):       # pad columns [n, ld) are never written by an exchange and must read as zero
             self.local[k].tensor((sizes[k],), torch.uint8).zero_()
@@ -252,6 +253,22 @@ class ShardedPairformer:
         run = nl * c * zc.element_size()
         px.put_all("zr", me * run, p * run, zc, lambda e: e * nl * run, run, run, nl)
 
+    def _peer_gather_bias(self, px, bias_loc: torch.Tensor) -> None:
+        """Pair bias [4][N/P u][ldm] of my rows -> rows me*nl.. of buffer ``bias`` [4][N][ldm] of every rank."""
+        p, me = self.world, self.rank
+        h, nl, ldm = bias_loc.shape
+        run = nl * ldm * 4
+        px.put_all("bias", me * run, p * run, bias_loc, lambda d: 0, run, run, h)
+
+    def _tri_att_start_peer(self, px: PeerExchange, mod, z_loc, mask_loc) -> None:
+        st = self.stages
+        q, k, v, bias_loc, mb = st.triatt_in_proj(mod, z_loc, mask_loc)
+        h, nl, ldm = bias_loc.shape
+        self._peer_gather_bias(px, bias_loc)
+        px.fence()
+        bias_full = px.local["bias"].tensor((h, self.world * nl, ldm), torch.float32)
+        st.triatt_out(mod, st.triatt_flash(q, k, v, bias_full, mb), z_loc)
+
     def _tri_mul_peer(self, px: PeerExchange, mod, z_loc, mask_loc, incoming: bool) -> None:
         st, p, me = self.stages, self.world, self.rank
         nl, n, _ = z_loc.shape
@@ -277,7 +294,9 @@ class ShardedPairformer:
         zc = px.local["zc"].tensor((n, nl, c), z_loc.dtype)
         q, k, v, bias_loc, mb = st.triatt_in_proj(mod, zc, mask_cols, True)
         h, _, ldm = bias_loc.shape
-        bias_full = self._all_gather(bias_loc).permute(1, 0, 2, 3).reshape(h, p * nl, ldm)
+        self._peer_gather_bias(px, bias_loc)
+        px.fence()
+        bias_full = px.local["bias"].tensor((h, p * nl, ldm), torch.float32)
         st.triatt_out(mod, st.triatt_flash(q, k, v, bias_full, mb), zc, True)
         self._peer_from_columns(px, zc)
         px.fence()
@@ -351,7 +370,7 @@ class ShardedPairformer:
             if px is not None:
                 self._tri_mul_peer(px, blk.tri_mul_out, z_loc, mask_loc, incoming=False)
                 self._tri_mul_peer(px, blk.tri_mul_in, z_loc, mask_loc, incoming=True)
-                self._tri_att_rows(blk.tri_att_start, z_loc, mask_loc)
+                self._tri_att_start_peer(px, blk.tri_att_start, z_loc, mask_loc)
                 self._tri_att_end_peer(px, blk.tri_att_end, z_loc, mask_cols)
             else:
                 self._tri_mul(blk.tri_mul_out, z_loc, mask_loc, incoming=False)

@@ -42,8 +42,9 @@ def _ld(n):
 def test_peer_copies_assemble_the_same_tensors_as_all_to_all(world, n):
     g = torch.Generator().manual_seed(world * 100 + n)
     nl, cp, ldn = n // world, 128 // world, _ld(n)
+    ldm = (n + 127) // 128 * 128
     sizes = {"a": cp * n * ldn * 2, "b": cp * n * ldn * 2, "x": 128 * nl * ldn * 2, "zc": n * nl * 128 * 2,
-             "zr": nl * n * 128 * 2}
+             "zr": nl * n * 128 * 2, "bias": 4 * n * ldm * 4}
     fx = FakeExchange(world, sizes)
     bf = torch.bfloat16
     # (1) rows -> channels, rows sharded: full_a [128][N][ld]
@@ -83,3 +84,10 @@ def test_peer_copies_assemble_the_same_tensors_as_all_to_all(world, n):
         _rank(world, r)._peer_from_columns(fx, fx.bufs["zc"][r].view(bf).view(n, nl, 128))
     for d in range(world):
         assert torch.equal(fx.bufs["zr"][d].view(bf).view(nl, n, 128), z[d * nl:(d + 1) * nl])
+    # (5) pair bias: [4][nl][ldm] of every rank -> [4][N][ldm] everywhere
+    bias = torch.randn(4, n, ldm, generator=g)
+    for r in range(world):
+        fx.rank = r
+        _rank(world, r)._peer_gather_bias(fx, bias[:, r * nl:(r + 1) * nl].contiguous())
+    for d in range(world):
+        assert torch.equal(fx.bufs["bias"][d].view(torch.float32).view(4, n, ldm), bias)
