@@ -42,7 +42,8 @@ def parse_args():
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU row-slab sample (0 = auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--micro", action="store_true",
-                    help="per-kernel micro-benchmark of one block (tri-att start/end, tri-mul out/in, transition)")
+                    help="per-kernel micro-benchmark of one block (tri-att start/end, tri-mul out/in, transition) and of "
+                         "the recycling update")
     return ap.parse_args()
 
 
@@ -187,6 +188,7 @@ def kernel_algo(n: int, zbytes: int) -> dict:
         "px_triatt_in_proj": ("hbm", (128 * zbytes + 4 + 768 + 20) * n2),
         "px_triatt_out": ("hbm", (256 + 2 * 128 * zbytes) * n2),
         "px_pair_bias_proj": ("hbm", (128 * zbytes + 64) * n2),
+        "px_recycle_update": ("hbm", 3 * 128 * zbytes * n2),
     }
 
 
@@ -221,11 +223,14 @@ def run_micro(args) -> None:
     t[n - n // 10:] = 0
     mask = (t[:, None] * t[None, :]).cuda()
     work = torch.empty_like(z)
+    trunk = randomize_parameters_(px.RecyclingTrunk(n_blocks=0), 2).eval().cuda()
+    z_init = torch.randn(n, n, 128, generator=torch.Generator().manual_seed(1)).to(zdt).cuda()
     variants = [("tri_mul_out", lambda: blk.tri_mul_out.apply_(work, mask)),
                 ("tri_mul_in", lambda: blk.tri_mul_in.apply_(work, mask)),
                 ("tri_att_start", lambda: blk.tri_att_start.apply_(work, mask, ending=False)),
                 ("tri_att_end", lambda: blk.tri_att_end.apply_(work, mask, ending=True)),
-                ("pair_transition", lambda: blk.pair_transition.forward_residual_(work))]
+                ("pair_transition", lambda: blk.pair_transition.forward_residual_(work)),
+                ("recycle_update", lambda: trunk.update_pair(work, z_init, out=work))]
     pk = peaks()
     algo = kernel_algo(n, z.element_size())
     out = {}

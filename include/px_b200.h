@@ -188,6 +188,14 @@ PX_API int32_t px_transition(const void* x_in, void* x_out, int32_t dtype, const
 PX_API int32_t px_pair_bias_proj(const void* z, int32_t z_dtype, const float* ln_w, const float* ln_b, const px_bf16* w,
                           float* out, int64_t rows, int32_t n_heads, float eps, void* stream);
 
+/* ---- Recycling update of the pair representation ------------------------------------------
+ * out[row] = z_init[row] + W LN(z[row]) for `rows` rows of 128 channels (W [128][128] bf16,
+ * z, z_init and out of one dtype, PX_BF16 or PX_F32); ln_b may be NULL; out may be z or z_init.
+ * Replaces protenix/model/protenix.py:246
+ * (z = z_init + linear_no_bias_z_cycle(layernorm_z_cycle(z))). */
+PX_API int32_t px_recycle_update(const void* z, const void* z_init, void* out, int32_t z_dtype, const float* ln_w,
+                          const float* ln_b, const px_bf16* w, int64_t rows, float eps, void* stream);
+
 /* ---- Exchange between the GPUs of one box (row-sharded path) ------------------------------
  * No counterpart in the reference (which runs the Pairformer on one GPU).  A peer buffer is a
  * cudaMalloc allocation whose 64-byte handle other processes on the same machine can open;

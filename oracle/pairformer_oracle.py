@@ -200,6 +200,28 @@ def pairformer_stack(s: Optional[torch.Tensor], z: torch.Tensor, pair_mask: Opti
     return s, z
 
 
+def recycle_update(x: torch.Tensor, x_init: torch.Tensor, p: Params, ln: str, lin: str) -> torch.Tensor:
+    """x_init + W LN(x): one recycling update (protenix/model/protenix.py:246 for z, :287 for s)."""
+    return x_init + layer_norm(x, p[ln + ".weight"], p.get(ln + ".bias")) @ p[lin + ".weight"].t()
+
+
+def recycling_trunk(s_init: torch.Tensor, z_init: torch.Tensor, pair_mask: Optional[torch.Tensor], p: Params,
+                    n_blocks: int, n_cycle: int, n_heads: int = 16) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The recycling loop around the Pairformer stack, without template embedder and MSA module.
+
+    Follows protenix/model/protenix.py:230-296: z and s start at zero (:230-231); every cycle
+    z = z_init + linear_no_bias_z_cycle(layernorm_z_cycle(z)) (:246),
+    s = s_init + linear_no_bias_s(layernorm_s(s)) (:287), then the stack (:288-296).
+    """
+    z = torch.zeros_like(z_init)
+    s = torch.zeros_like(s_init)
+    for _ in range(n_cycle):
+        z = recycle_update(z, z_init, p, "layernorm_z_cycle", "linear_no_bias_z_cycle")
+        s = recycle_update(s, s_init, p, "layernorm_s", "linear_no_bias_s")
+        s, z = pairformer_stack(s, z, pair_mask, _sub(p, "pairformer_stack"), n_blocks, n_heads)
+    return s, z
+
+
 def rel_frobenius(a: torch.Tensor, b: torch.Tensor) -> float:
     """||a - b||_F / ||b||_F in fp64."""
     a = a.detach().double().cpu()

@@ -4,6 +4,7 @@ bytedance/Protenix.  One code path: hand-written CUDA kernels reached through a 
 from .layer_norm import FusedLayerNorm, LayerNorm
 from .pairformer import PairformerBlock, PairformerStack
 from .primitives import Linear, LinearNoBias, Transition
+from .recycling import RecyclingTrunk
 from .transformer import AttentionPairBias
 from .triangular import (OpenfoldLinear, TriangleAttention, TriangleAttentionEndingNode,
                          TriangleAttentionStartingNode, TriangleMultiplicationIncoming,
@@ -14,6 +15,6 @@ __all__ = [
     "FusedLayerNorm", "LayerNorm", "PairformerBlock", "PairformerStack", "Linear", "LinearNoBias", "Transition",
     "AttentionPairBias", "OpenfoldLinear", "TriangleAttention", "TriangleAttentionEndingNode",
     "TriangleAttentionStartingNode", "TriangleMultiplicationIncoming", "TriangleMultiplicationOutgoing",
-    "TriangleMultiplicativeUpdate", "dropout_add_rowwise",
+    "TriangleMultiplicativeUpdate", "dropout_add_rowwise", "RecyclingTrunk",
 ]
 __version__ = "0.1.0"

@@ -39,6 +39,7 @@ SIGNATURES = {
     "px_triangle_attention": (I32, [P, P, I32, P, P, P, P, P, P, P, P, P, P, I64, I64, I32, I32, F, F, P]),
     "px_transition": (I32, [P, P, I32, P, P, P, P, P, I64, I32, F, P]),
     "px_pair_bias_proj": (I32, [P, I32, P, P, P, P, I64, I32, F, P]),
+    "px_recycle_update": (I32, [P, P, P, I32, P, P, P, I64, F, P]),
     "px_peer_alloc": (I32, [I64, P, P]),
     "px_peer_open": (I32, [P, P]),
     "px_peer_close": (I32, [P]),

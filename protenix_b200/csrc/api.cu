@@ -10,6 +10,7 @@ unsigned int triatt_in_error_flags();
 unsigned int triatt_out_error_flags();
 unsigned int trimul_out_error_flags();
 unsigned int pair_bias_error_flags();
+unsigned int recycle_error_flags();
 }  // namespace px
 
 // Synchronises the device and returns (and clears) the flags recorded by bounded waits that ran out.
@@ -19,7 +20,8 @@ extern "C" int32_t px_device_error_flags(uint32_t* flags) {
   if (!flags) return PX_ERR_BAD_ARG;
   if (cudaDeviceSynchronize() != cudaSuccess) return PX_ERR_LAUNCH;
   *flags = px::contract_error_flags() | (px::flash_error_flags() << 8) | (px::transition_error_flags() << 16) |
-           ((px::trimul_in_error_flags() | px::triatt_in_error_flags() | px::triatt_out_error_flags() | px::trimul_out_error_flags() | px::pair_bias_error_flags()) << 24);
+           ((px::trimul_in_error_flags() | px::triatt_in_error_flags() | px::triatt_out_error_flags() | px::trimul_out_error_flags() | px::pair_bias_error_flags() |
+            px::recycle_error_flags()) << 24);
   return PX_OK;
 }
 

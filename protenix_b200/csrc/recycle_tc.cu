@@ -1,0 +1,252 @@
+// Recycling update of the pair representation on the 5th-generation tensor cores:
+//   out[row] = z_init[row] + W LN(z[row]),   W [128][128], one row per pair element
+// (protenix/model/protenix.py:246: z = z_init + linear_no_bias_z_cycle(layernorm_z_cycle(z))).
+//
+// Persistent kernel, one CTA per SM, 128 rows per tile, on the row-tile pipeline of px_rowpipe.cuh (TMA-fed raw rows,
+// LayerNorm folded into the resident weight plus one correction K step, row statistics from a tensor-core Gram
+// product).  HBM-bound: per row 128*sizeof(Tz) bytes of z and of z_init are read and as many written.
+//   warps 0..7   output rows: a thread owns one row and 64 of its channels, adds rstd * accumulator to the z_init
+//                tile in shared memory (brought in by TMA, in place) and one thread stores the tile by TMA;
+//                fp32 rows read z_init from global memory and use plain stores;
+//   warps 8..11  one thread per row: statistics, correction row, the row's rstd;
+//   warp 12      TMA producer (z tiles and z_init tiles); warp 13 MMA issuer of the projection (M=128, N=128),
+//   warp 14      MMA issuer of the statistics product.
+// `out` may be the same buffer as `z` or as `z_init`: a tile is written only after all of its reads.
+// Every mbarrier wait is bounded.
+#include <cstring>
+
+#include "px_rowpipe.cuh"
+
+namespace px {
+
+constexpr int kRcWarps = 15;
+constexpr int kRcThreads = 32 * kRcWarps;
+constexpr uint32_t kRcColGram = 128;           // tensor memory: projection (128 columns) | statistics (144)
+
+struct RcBars {
+  TileBars tile;
+  uint64_t acc_full, acc_free, res_full[kTileStages], res_empty[kTileStages];
+  uint32_t tmem_base;
+};
+struct RcLayout {
+  static constexpr int w = 0;                                   // [128][128 k] as two k panels
+  static constexpr int wx = w + kOperandBytes;                  // correction panel [128][16 k]
+  static constexpr int a = wx + 128 * 32;                       // row-tile ring
+  static constexpr int ax = a + kTileStages * kTileBytes;
+  static constexpr int res = ax + kTileStages * kTileExtra;     // z_init tiles, then the output tiles, in place
+  static constexpr int scale = res + kTileStages * kOperandBytes;  // rstd per row and slot
+  static constexpr int bars = scale + kTileSlots * 128 * 4;
+  static constexpr int total = bars + (int)sizeof(RcBars);
+};
+static_assert(RcLayout::a % 1024 == 0 && RcLayout::res % 1024 == 0, "tiles must keep the swizzle alignment");
+
+static __device__ float g_rc_zero_beta[128];   // stands in for a LayerNorm without bias
+
+template <typename Tz>
+__global__ void __launch_bounds__(kRcThreads, 1)
+recycle_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_init,
+                  const __grid_constant__ CUtensorMap map_out, const Tz* __restrict__ z, const Tz* z_init, Tz* out,
+                  const float* __restrict__ ln_w, const float* __restrict__ ln_b, const bf16* __restrict__ w,
+                  long long rows, float eps, int n_tiles) {
+  constexpr bool kTma = sizeof(Tz) == 2;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  RcBars& bars = *reinterpret_cast<RcBars*>(sm + RcLayout::bars);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  TileCtx ctx;
+  ctx.tiles = sm + RcLayout::a;
+  ctx.extras = sm + RcLayout::ax;
+  ctx.bars = &bars.tile;
+  ctx.first_tile = blockIdx.x;
+  ctx.tile_step = gridDim.x;
+  ctx.n_tiles = n_tiles;
+  ctx.tiles_t = n_tiles;                                 // the rows are one long line of tiles: u = 0, t = row
+  ctx.n_u = 1;
+  ctx.n_t = (int)rows;
+  ctx.swap = 0;
+
+  if (threadIdx.x == 0) {
+    tile_bars_init(bars.tile, kTma, 2);
+    mbar_init(&bars.acc_full, 1);
+    mbar_init(&bars.acc_free, 8);
+    for (int s = 0; s < kTileStages; ++s) {
+      mbar_init(&bars.res_full[s], 1);
+      mbar_init(&bars.res_empty[s], 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 12) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&bars.tmem_base)),
+                 "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  fold_weight_rows(sm + RcLayout::w, sm + RcLayout::wx, 0, kPanelBytes, w, 0, 128, ln_w, ln_b ? ln_b : g_rc_zero_beta, 1.0f,
+                   warp, kRcWarps, lane);
+  tile_write_ones(ctx.tiles, threadIdx.x, kRcThreads);
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars.tmem_base;
+
+  if (warp >= 12) {
+    if (lane == 0) {
+      if (warp == 12) {
+        if (kTma) {
+          // z tile into the operand ring, z_init tile into the output ring
+          int k = 0;
+          for (int tile = ctx.first_tile; tile < n_tiles; tile += ctx.tile_step, ++k) {
+            const int s = k % kTileStages, n = k / kTileStages;
+            if (!mbar_wait(&bars.tile.a_empty[s], (n & 1) ^ 1, 1u)) break;
+            mbar_expect_tx(&bars.tile.raw_full[s], kOperandBytes);
+            const uint32_t dst = smem_u32(ctx.tiles + s * kTileBytes);
+            for (int p = 0; p < 2; ++p) tma_load_3d(dst + p * kTilePanel, &map_z, &bars.tile.raw_full[s], 64 * p, tile * 128, 0);
+            if (!mbar_wait(&bars.res_empty[s], (n & 1) ^ 1, 1u)) break;
+            mbar_expect_tx(&bars.res_full[s], kOperandBytes);
+            const uint32_t rdst = smem_u32(sm + RcLayout::res + s * kOperandBytes);
+            for (int p = 0; p < 2; ++p) tma_load_3d(rdst + p * kPanelBytes, &map_init, &bars.res_full[s], 64 * p, tile * 128, 0);
+          }
+        }
+      } else if (warp == 13) {
+        tile_product_loop(ctx, tmem_base, smem_u32(sm + RcLayout::w), kPanelBytes, smem_u32(sm + RcLayout::wx),
+                          umma_idesc_bf16(128, 128), &bars.acc_full, &bars.acc_free);
+      } else if (warp == 14) {
+        tile_gram_loop(ctx, tmem_base + kRcColGram);
+      }
+    }
+  } else if (warp >= 8) {
+    float* scale = reinterpret_cast<float*>(sm + RcLayout::scale);
+    tile_stats_loop<Tz>(ctx, z, eps, tmem_base + kRcColGram, warp - 8, lane,
+                        [&](int k, int u, int t, int r, float rstd) { scale[(k % kTileSlots) * 128 + r] = rstd; });
+  } else {
+    // ------------------------------------------------------------------ output rows
+    const int half = (warp >> 2) & 1, qw = warp & 3;
+    const int row = 32 * qw + lane;
+    const uint32_t t_acc = tmem_base + ((uint32_t)(32 * qw) << 16) + 64 * half;
+    const bool leader = threadIdx.x == 0;
+    int k = 0;
+    bool ok = true;
+    for (int tile = ctx.first_tile; tile < n_tiles && ok; tile += ctx.tile_step, ++k) {
+      const int s = k % kTileStages, n = k / kTileStages;
+      const long long t = (long long)tile * 128 + row;
+      ok = mbar_wait(&bars.acc_full, k & 1, 32u);
+      if (kTma) ok = ok && mbar_wait(&bars.res_full[s], n & 1, 33u);
+      ok = named_barrier_all(1, 256, ok);                  // all eight warps go on, or none
+      if (!ok) break;
+      tc_fence_after();
+      const float rstd = reinterpret_cast<const float*>(sm + RcLayout::scale)[(k % kTileSlots) * 128 + row];
+      unsigned char* rtile = sm + RcLayout::res + s * kOperandBytes;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t acc[32];
+        tmem_ld32(t_acc + 32 * hh, acc);
+        tmem_wait_ld();
+        if (hh == 1) {                                     // this warp has read its part of the accumulator
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars.acc_free);
+        }
+        if (kTma) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            unsigned char* piece = rtile + operand_piece_offset(row, 8 * half + 4 * hh + j);
+            const uint4 iv = *reinterpret_cast<const uint4*>(piece);
+            const uint32_t iw[4] = {iv.x, iv.y, iv.z, iv.w};
+            uint32_t ow[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 r2 = unpack_bf16x2(iw[e]);
+              ow[e] = pack_bf16x2_int(fmaf(rstd, __uint_as_float(acc[8 * j + 2 * e]), r2.x),
+                                      fmaf(rstd, __uint_as_float(acc[8 * j + 2 * e + 1]), r2.y));
+            }
+            *reinterpret_cast<uint4*>(piece) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+          }
+        } else if (t < rows) {
+          const size_t off = (size_t)t * kC + 64 * half + 32 * hh;
+          const float* init = reinterpret_cast<const float*>(z_init);
+          float* dst = reinterpret_cast<float*>(out);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 r4 = load4(init + off + 4 * j);
+            store2(dst + off + 4 * j, fmaf(rstd, __uint_as_float(acc[4 * j]), r4.x),
+                   fmaf(rstd, __uint_as_float(acc[4 * j + 1]), r4.y));
+            store2(dst + off + 4 * j + 2, fmaf(rstd, __uint_as_float(acc[4 * j + 2]), r4.z),
+                   fmaf(rstd, __uint_as_float(acc[4 * j + 3]), r4.w));
+          }
+        }
+      }
+      if (kTma) {
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        named_barrier(1, 256);
+        if (leader) {
+          for (int p = 0; p < 2; ++p) tma_store_3d(&map_out, smem_u32(rtile + p * kPanelBytes), 64 * p, tile * 128, 0);
+          tma_store_commit();
+          tma_store_wait_read<0>();                        // the store has read the tile: hand it back
+          mbar_arrive(&bars.res_empty[s]);
+        }
+      }
+    }
+    if (kTma && leader) tma_store_wait<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (g_tc_error != 0) {  // a wait ran out: let copies that may still be in flight land before leaving
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) {
+    }
+    __syncthreads();
+  }
+  if (warp == 12) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+unsigned int recycle_error_flags() {
+  unsigned int v = 0;
+  return read_clear_tc_error(&v) == 0 ? v : 0x80u;
+}
+
+template <typename Tz>
+static int32_t launch_recycle(const void* z, const void* z_init, void* out, const float* ln_w, const float* ln_b,
+                              const px_bf16* w, int64_t rows, float eps, cudaStream_t st) {
+  CUtensorMap mz, mi, mo;
+  if (sizeof(Tz) == 2) {
+    const void* base[3] = {z, z_init, out};
+    CUtensorMap* maps[3] = {&mz, &mi, &mo};
+    for (int i = 0; i < 3; ++i)
+      if (!make_map_3d(maps[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base[i], 128, (uint64_t)rows, 1, 256, (uint64_t)rows * 256,
+                       64, 128, CU_TENSOR_MAP_SWIZZLE_128B, 1))
+        return PX_ERR_LAUNCH;
+  } else {
+    memset(&mz, 0, sizeof(mz));
+    memset(&mi, 0, sizeof(mi));
+    memset(&mo, 0, sizeof(mo));
+  }
+  const size_t smem = RcLayout::total + 1024;
+  if (cudaFuncSetAttribute(recycle_tc_kernel<Tz>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return PX_ERR_LAUNCH;
+  const int64_t n_tiles = (rows + 127) / 128;
+  const int grid = (int)(n_tiles < sm_count() ? n_tiles : sm_count());
+  recycle_tc_kernel<Tz><<<grid, kRcThreads, smem, st>>>(mz, mi, mo, (const Tz*)z, (const Tz*)z_init, (Tz*)out, ln_w, ln_b,
+                                                        (const bf16*)w, (long long)rows, eps, (int)n_tiles);
+  return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
+}
+
+}  // namespace px
+
+using namespace px;
+
+extern "C" int32_t px_recycle_update(const void* z, const void* z_init, void* out, int32_t z_dtype, const float* ln_w,
+                                     const float* ln_b, const px_bf16* w, int64_t rows, float eps, void* stream) {
+  if (!z || !z_init || !out || !ln_w || !w || rows < 0) return PX_ERR_BAD_ARG;
+  if (((uintptr_t)z | (uintptr_t)z_init | (uintptr_t)out | (uintptr_t)w | (uintptr_t)ln_w | (uintptr_t)ln_b) & 15)
+    return PX_ERR_BAD_ARG;
+  if (rows == 0) return PX_OK;
+  if (rows > 0x3fffff80) return PX_ERR_UNSUPPORTED;
+  if (z_dtype == PX_F32) return launch_recycle<float>(z, z_init, out, ln_w, ln_b, w, rows, eps, (cudaStream_t)stream);
+  if (z_dtype == PX_BF16) return launch_recycle<bf16>(z, z_init, out, ln_w, ln_b, w, rows, eps, (cudaStream_t)stream);
+  return PX_ERR_UNSUPPORTED;
+}

@@ -253,6 +253,31 @@ def pair_bias_proj(z: torch.Tensor, ln_w, ln_b: Optional[torch.Tensor], w: torch
     return out
 
 
+def recycle_update(z: torch.Tensor, z_init: torch.Tensor, ln_w, ln_b: Optional[torch.Tensor], w: torch.Tensor,
+                   eps: float = 1e-5, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = z_init + W LN(z) over rows of 128 channels (any leading shape; `out` may be z or z_init)."""
+    _need_cuda(z, "z")
+    _need_cuda(z_init, "z_init")
+    if z.shape != z_init.shape or z.dtype != z_init.dtype or z.shape[-1] != C_Z:
+        raise RuntimeError("z and z_init must have the same shape [..., 128] and dtype")
+    if not (z.is_contiguous() and z_init.is_contiguous()):
+        raise RuntimeError("z and z_init must be contiguous")
+    _check_v(ln_w, C_Z, "ln_w")
+    if ln_b is not None:
+        _check_v(ln_b, C_Z, "ln_b")
+    _check_w(w, (C_Z, C_Z), "w")
+    if out is None:
+        out = torch.empty_like(z)
+    elif out.shape != z.shape or out.dtype != z.dtype or not out.is_contiguous():
+        raise RuntimeError("out must match z")
+    rows = z.numel() // C_Z
+    if rows == 0:
+        return out
+    _launch("px_recycle_update", _lib.load().px_recycle_update, _ptr(z), _ptr(z_init), _ptr(out), _pair_dtype(z),
+            _ptr(ln_w), _ptr(ln_b), _ptr(w), rows, float(eps), _stream(z))
+    return out
+
+
 # ---------------------------------------------------------------------------------------------
 # Stage-level calls on rectangular slabs (row-sharded pair tensor).  Outputs are allocated here.
 def _slab(z: torch.Tensor, name: str = "z") -> Tuple[int, int]:

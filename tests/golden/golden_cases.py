@@ -37,6 +37,8 @@ CASES = {
     "ln_384_both": dict(kind="layer_norm", rows=64, c=384, scale=True, offset=True, seed=42, wseed=11),
     "ln_833_scale": dict(kind="layer_norm", rows=33, c=833, scale=True, offset=False, seed=43, wseed=12),
     "ln_64_none": dict(kind="layer_norm", rows=77, c=64, scale=False, offset=False, seed=44, wseed=13),
+    # recycling loop around a 2-block stack: z, s are z_init, s_init
+    "recycle_n16": dict(kind="recycle", n=16, c_s=384, n_blocks=2, n_cycle=3, seed=51, wseed=14, pad=2),
 }
 
 

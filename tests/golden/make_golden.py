@@ -105,6 +105,27 @@ def main() -> None:
             mod = ref_layers.LayerNorm(case["c"], create_scale=case["scale"], create_offset=case["offset"]).eval()
             randomize_parameters_(mod, case["wseed"])
             out[name + ".y"] = mod(inp["x"]).numpy()
+        elif kind == "recycle":
+            # the recycling loop of Protenix.get_pairformer_output (protenix/model/protenix.py:230-296) with the
+            # reference's own layers, template embedder and MSA module left out
+            class Trunk(torch.nn.Module):
+                def __init__(self):
+                    super().__init__()
+                    self.linear_no_bias_z_cycle = ref_prim.LinearNoBias(in_features=128, out_features=128)
+                    self.linear_no_bias_s = ref_prim.LinearNoBias(in_features=case["c_s"], out_features=case["c_s"])
+                    self.layernorm_z_cycle = ref_layers.LayerNorm(128)
+                    self.layernorm_s = ref_layers.LayerNorm(case["c_s"])
+                    self.pairformer_stack = ref_pf.PairformerStack(n_blocks=case["n_blocks"], c_s=case["c_s"])
+
+            mod = Trunk().eval()
+            randomize_parameters_(mod, case["wseed"])
+            z, s = torch.zeros_like(inp["z"]), torch.zeros_like(inp["s"])
+            for _ in range(case["n_cycle"]):
+                z = inp["z"] + mod.linear_no_bias_z_cycle(mod.layernorm_z_cycle(z))
+                s = inp["s"] + mod.linear_no_bias_s(mod.layernorm_s(s))
+                s, z = mod.pairformer_stack(s, z, pair_mask=inp["mask"])
+            out[name + ".z"] = z.numpy()
+            out[name + ".s"] = s.numpy()
         else:
             raise ValueError(kind)
         print(name, {k: v.shape for k, v in out.items() if k.startswith(name + ".")})

@@ -34,6 +34,8 @@ def build_module(kind: str, case: dict) -> torch.nn.Module:
         m = px.Transition(c_in=case["c"], n=case["n"])
     elif kind == "layer_norm":
         m = px.LayerNorm(case["c"], create_scale=case["scale"], create_offset=case["offset"])
+    elif kind == "recycle":
+        m = px.RecyclingTrunk(n_blocks=case["n_blocks"], c_s=case["c_s"], N_cycle=case["n_cycle"])
     else:
         raise ValueError(kind)
     randomize_parameters_(m, case["wseed"])

@@ -36,6 +36,11 @@ def test_oracle_matches_reference_vectors(name):
         assert relf(O.transition(inp["x"], p), g[name + ".y"]) < TOL
     elif kind == "layer_norm":
         assert relf(O.layer_norm(inp["x"], p.get("weight"), p.get("bias")), g[name + ".y"]) < TOL
+    elif kind == "recycle":
+        s, z = O.recycling_trunk(inp["s"], inp["z"], inp["mask"], p, n_blocks=case["n_blocks"], n_cycle=case["n_cycle"])
+        assert relf(z, g[name + ".z"]) < TOL and relf(s, g[name + ".s"]) < TOL
+    else:
+        raise AssertionError(kind)
 
 
 def test_oracle_fp64_agrees_with_fp32():
