@@ -70,5 +70,10 @@ def test_argument_errors_are_status_codes_not_crashes(lib):
     assert lib.px_layer_norm_fwd(p, None, None, p, None, None, 1, 8, 1e-5, 7, None) == -2
     # too many heads for the pair-bias projection
     assert lib.px_pair_bias_proj(p, 0, p, None, p, p, 4, 17, 1e-5, None) == -2
+    # recycling update: null tensors, unknown dtype, misaligned pointer, empty input
+    assert lib.px_recycle_update(None, p, p, 0, p, p, p, 4, 1e-5, None) == -1
+    assert lib.px_recycle_update(p, p, p, 9, p, p, p, 4, 1e-5, None) == -2
+    assert lib.px_recycle_update(p + 2, p, p, 0, p, p, p, 4, 1e-5, None) == -1
+    assert lib.px_recycle_update(p, p, p, 0, p, None, p, 0, 1e-5, None) == 0
     # workspace too small
     assert lib.px_triangle_multiplication(p, p, 0, None, p, p, p, p, p, p, p, p, p, p, p, 64, 32, 0, 1, 1e-5, None) == -4
