@@ -92,6 +92,11 @@ class CudaStages:
     def single_layer_norm(self, ln, x):
         return ln(x)
 
+    def recycle_update(self, ln, lin, z, z_init, out):
+        b = ln.bias
+        return ops.recycle_update(z, z_init, self._f(ln.weight), None if b is None else self._f(b), bf16_of(lin.weight),
+                                  ln.eps, out=out)
+
 
 # ----------------------------------------------------------------------------------------------
 class PeerExchange:
@@ -394,4 +399,38 @@ class ShardedPairformer:
             main.wait_stream(side)
             if s is not None:
                 s.record_stream(main)
+        return s, z_loc
+
+
+class ShardedRecyclingTrunk:
+    """The recycling loop of a ``RecyclingTrunk`` on a row-sharded pair representation.
+
+    Both recycling updates are row-local (protenix/model/protenix.py:246, :287): every rank updates its own rows of z
+    from its rows of z_init, s is replicated, and the stack runs through ``ShardedPairformer``.
+    """
+
+    def __init__(self, trunk, group: Optional[dist.ProcessGroup] = None, stages=None) -> None:
+        self.trunk = trunk
+        self.stack = ShardedPairformer(trunk.pairformer_stack, group=group, stages=stages)
+        self.stages = self.stack.stages
+
+    def shard_rows(self, z: torch.Tensor) -> torch.Tensor:
+        return self.stack.shard_rows(z)
+
+    def gather_rows(self, z_loc: torch.Tensor) -> torch.Tensor:
+        return self.stack.gather_rows(z_loc)
+
+    @torch.no_grad()
+    def forward(self, s_init: torch.Tensor, z_init_loc: torch.Tensor, pair_mask: Optional[torch.Tensor] = None,
+                N_cycle: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """z_init_loc [N/P, N, 128] is left untouched; returns (s [N, c_s], the rank's rows of z)."""
+        t = self.trunk
+        n_cycle = t.N_cycle if N_cycle is None else N_cycle
+        z_loc = torch.zeros_like(z_init_loc)
+        s = torch.zeros_like(s_init)
+        for _ in range(n_cycle):
+            z_loc = self.stages.recycle_update(t.layernorm_z_cycle, t.linear_no_bias_z_cycle, z_loc, z_init_loc, z_loc)
+            x = self.stages.single_layer_norm(t.layernorm_s, s.float().contiguous())
+            s = (s_init.float() + F.linear(x, t.linear_no_bias_s.weight)).to(s_init.dtype)
+            s, z_loc = self.stack.forward(s, z_loc, pair_mask)
         return s, z_loc

@@ -81,3 +81,7 @@ class TorchStages:
 
     def single_layer_norm(self, ln, x):
         return _ln(x, ln)
+
+    def recycle_update(self, ln, lin, z, z_init, out):
+        out.copy_(z_init + _ln(z, ln) @ lin.weight.T)
+        return out

@@ -130,6 +130,16 @@ def test_sharded_path_with_one_rank_equals_module():
         assert relf(z_out, z_ref) < 1e-6 and relf(s_out, s_ref) < 1e-5
         s0, z0 = O.pairformer_stack(s.cpu(), z.cpu(), mask.cpu(), params_of(stack), n_blocks=2)
         assert relf(z_out, z0) < 2e-2 and relf(s_out, s0) < 2e-2
+        # the recycling loop over the same group: row-local updates around the sharded stack
+        from protenix_b200.sharded import ShardedRecyclingTrunk
+
+        trunk = build_module("recycle", dict(n_blocks=1, c_s=384, n_cycle=2, wseed=8)).to(DEV)
+        s_ref, z_ref = trunk(s, z, mask)
+        st = ShardedRecyclingTrunk(trunk)
+        z_init_loc = st.shard_rows(z)
+        s_out, z_out = st.forward(s, z_init_loc, mask)
+        assert torch.equal(z_init_loc, z)
+        assert relf(z_out, z_ref) < 1e-6 and relf(s_out, s_ref) < 1e-5
     finally:
         dist.destroy_process_group()
 

@@ -93,3 +93,53 @@ def test_sharding_rejects_indivisible_sizes():
             sp.shard_rows(torch.zeros(10, 10, 128))
     finally:
         dist.destroy_process_group()
+
+
+def _recycle_worker(rank, world, port, n, n_cycle, q):
+    for p in (os.path.dirname(HERE), HERE, os.path.join(HERE, "golden")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import protenix_b200 as px
+        from golden_cases import padding_mask
+        from helpers import params_of, relf
+        from oracle import pairformer_oracle as O
+        from protenix_b200.init_utils import randomize_parameters_
+        from protenix_b200.sharded import ShardedRecyclingTrunk
+        from ref_stages import TorchStages
+
+        g = torch.Generator().manual_seed(9)
+        z_init = torch.randn(n, n, 128, generator=g)
+        s_init = torch.randn(n, 384, generator=g)
+        mask = padding_mask(n, 2)
+        trunk = randomize_parameters_(px.RecyclingTrunk(n_blocks=1, N_cycle=n_cycle), 6).eval()
+        sp = ShardedRecyclingTrunk(trunk, stages=TorchStages())
+        z_init_loc = sp.shard_rows(z_init)
+        keep = z_init_loc.clone()
+        s_out, z_loc = sp.forward(s_init, z_init_loc, mask)
+        assert torch.equal(z_init_loc, keep)                      # the initial pair representation is only read
+        z_full = sp.gather_rows(z_loc)
+        if rank == 0:
+            s_ref, z_ref = O.recycling_trunk(s_init, z_init, mask, params_of(trunk), n_blocks=1, n_cycle=n_cycle)
+            q.put((relf(z_full, z_ref), relf(s_out, s_ref)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,n,n_cycle", [(2, 12, 2), (4, 16, 3)])
+def test_sharded_recycling_loop_equals_oracle(world, n, n_cycle):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_recycle_worker, args=(r, world, port, n, n_cycle, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    ez, es = q.get(timeout=10)
+    assert ez < 2e-5 and es < 2e-5, (ez, es)
