@@ -22,7 +22,8 @@
 //
 // Softmax is online in base 2 with a lazy reference maximum: the reference only moves (and O_u is rescaled
 // through TMEM) when the tile maximum exceeds it by more than 8, so probabilities stay below 2^8.
-// Exponentials are fp32 ex2; P is their truncation to bf16.  Every mbarrier wait is bounded.
+// Exponentials are fp32 ex2; P is their rounding to bf16, the denominators sum the fp32 values.  Every mbarrier
+// wait is bounded.
 #include <math_constants.h>
 
 #include "px_tcgen05.cuh"
@@ -296,12 +297,12 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const float nm = -m_ref[r];
 #pragma unroll
           for (int e = 0; e < kFKT / 2; ++e) {
-            // fp32 exponentials; P keeps the upper halves (truncation to bf16).  The denominator sums the same
-            // truncated values, so the bias of the truncation cancels in the normalisation.
+            // fp32 exponentials; P is their rounding to nearest bf16 (one conversion per pair), which is unbiased,
+            // so the denominator can sum the fp32 values themselves.
             const float p0 = fast_exp2(s[2 * e] + nm), p1 = fast_exp2(s[2 * e + 1] + nm);
-            w[e] = __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
-            l0 += __uint_as_float(w[e] << 16);
-            l1 += __uint_as_float(w[e] & 0xffff0000u);
+            w[e] = pack_bf16x2(p0, p1);
+            l0 += p0;
+            l1 += p1;
           }
         }
         l_sum[r] = l_sum[r] * alpha + (l0 + l1);
