@@ -22,8 +22,8 @@
 //
 // Softmax is online in base 2 with a lazy reference maximum: the reference only moves (and O_u is rescaled
 // through TMEM) when the tile maximum exceeds it by more than 8, so probabilities stay below 2^8.
-// Exponentials are fp32 ex2; P is their rounding to bf16, the denominators sum the fp32 values.  Every mbarrier
-// wait is bounded.
+// Exponentials are fp32 (three pairs in four by ex2, the fourth by a cubic on the FMA pipe); P is their rounding to
+// bf16, the denominators sum the fp32 values.  Every mbarrier wait is bounded.
 #include <math_constants.h>
 
 #include "px_tcgen05.cuh"
@@ -84,6 +84,39 @@ __device__ __forceinline__ void add2(float& a0, float& a1, float b0, float b1) {
   asm("{\n .reg .b64 x, y;\n mov.b64 x, {%0, %1};\n mov.b64 y, {%2, %3};\n add.f32x2 x, x, y;\n mov.b64 {%0, %1}, x;\n}\n"
       : "+f"(a0), "+f"(a1)
       : "f"(b0), "f"(b1));
+}
+
+// (d0, d1) = (a0, a1) * (b0, b1) + (c0, c1) as one packed instruction.
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+  asm("{\n .reg .b64 a, b, c, d;\n mov.b64 a, {%2, %3};\n mov.b64 b, {%4, %5};\n mov.b64 c, {%6, %7};\n"
+      " fma.rn.f32x2 d, a, b, c;\n mov.b64 {%0, %1}, d;\n}\n"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+
+// 2^x for two arguments on the FMA pipe (the special-function unit delivers 16 ex2 per clock and SM and is the
+// busiest unit of this kernel): x = n + f with n = round(x) taken from the mantissa after adding 1.5 * 2^23,
+// 2^f by a cubic on [-0.5, 0.5] (relative error 7.5e-5, far below the bf16 rounding of P), 2^n added into the exponent
+// field.  Arguments below -126 (masked or padded keys) give 2^-126.
+#ifndef PX_FLASH_POLY
+#define PX_FLASH_POLY 4   // every PX_FLASH_POLY-th pair of exponentials takes this path (0: none)
+#endif
+__device__ __forceinline__ void exp2_poly2(float x0, float x1, float& p0, float& p1) {
+  constexpr float kMagic = 12582912.f;
+  constexpr float c0 = 0.9999280571937561f, c1 = 0.6932610273361206f, c2 = 0.2426111102104187f, c3 = 0.05517144873738289f;
+  x0 = fmaxf(x0, -126.f);
+  x1 = fmaxf(x1, -126.f);
+  float t0 = x0, t1 = x1;
+  add2(t0, t1, kMagic, kMagic);
+  float n0 = t0, n1 = t1;
+  add2(n0, n1, -kMagic, -kMagic);
+  float f0, f1, q0, q1;
+  fma2(f0, f1, n0, n1, -1.f, -1.f, x0, x1);
+  fma2(q0, q1, f0, f1, c3, c3, c2, c2);
+  fma2(q0, q1, q0, q1, f0, f1, c1, c1);
+  fma2(q0, q1, q0, q1, f0, f1, c0, c0);
+  p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+  p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
 }
 
 __global__ void __launch_bounds__(kFThreads, 1)
@@ -303,7 +336,13 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // fp32 exponentials; P is their rounding to nearest bf16 (one conversion per pair), which is unbiased,
             // so the denominator can sum the fp32 values themselves.
             add2(s[2 * e], s[2 * e + 1], nm, nm);
-            const float p0 = fast_exp2(s[2 * e]), p1 = fast_exp2(s[2 * e + 1]);
+            float p0, p1;
+            if (PX_FLASH_POLY > 0 && e % (PX_FLASH_POLY > 0 ? PX_FLASH_POLY : 1) == PX_FLASH_POLY - 1) {
+              exp2_poly2(s[2 * e], s[2 * e + 1], p0, p1);
+            } else {
+              p0 = fast_exp2(s[2 * e]);
+              p1 = fast_exp2(s[2 * e + 1]);
+            }
             w[e] = pack_bf16x2(p0, p1);
             add2(l0, l1, p0, p1);
           }
