@@ -196,7 +196,7 @@ def kernel_algo(n: int, zbytes: int) -> dict:
 # captures at N = 768 summarised under profiles/ (<kernel>_N768.md).  For these kernels traffic grows with
 # N^2 (operands of the N^3 kernels are re-read from L2, not DRAM), so a launch at another N is scaled by N^2.
 NCU_TRAFFIC_PER_PAIR = {
-    "px_triatt_flash": 599.6e6 / 768 ** 2,
+    "px_triatt_flash": 597.9e6 / 768 ** 2,
     "px_transition": 248.2e6 / 768 ** 2,
     "px_trimul_contract": 417.1e6 / 768 ** 2,
     "px_trimul_in_proj": 399.2e6 / 768 ** 2,
