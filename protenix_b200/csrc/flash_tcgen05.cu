@@ -79,21 +79,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
-// (a0, a1) += (b0, b1) as one packed instruction: half the issue slots of two scalar additions.
-__device__ __forceinline__ void add2(float& a0, float& a1, float b0, float b1) {
-  asm("{\n .reg .b64 x, y;\n mov.b64 x, {%0, %1};\n mov.b64 y, {%2, %3};\n add.f32x2 x, x, y;\n mov.b64 {%0, %1}, x;\n}\n"
-      : "+f"(a0), "+f"(a1)
-      : "f"(b0), "f"(b1));
-}
-
-// (d0, d1) = (a0, a1) * (b0, b1) + (c0, c1) as one packed instruction.
-__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
-  asm("{\n .reg .b64 a, b, c, d;\n mov.b64 a, {%2, %3};\n mov.b64 b, {%4, %5};\n mov.b64 c, {%6, %7};\n"
-      " fma.rn.f32x2 d, a, b, c;\n mov.b64 {%0, %1}, d;\n}\n"
-      : "=f"(d0), "=f"(d1)
-      : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
-}
-
 // 2^x for two arguments on the FMA pipe (the special-function unit delivers 16 ex2 per clock and SM and is the
 // busiest unit of this kernel): x = n + f with n = round(x) taken from the mantissa after adding 1.5 * 2^23,
 // 2^f by a cubic on [-0.5, 0.5] (relative error 7.5e-5, far below the bf16 rounding of P), 2^n added into the exponent

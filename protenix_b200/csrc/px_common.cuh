@@ -26,6 +26,23 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
   return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
 }
 
+// Packed fp32 arithmetic (sm_100): two elements per issue slot.  Pays where the issue slots are the scarce resource
+// (flash attention: -7 %); the SwiGLU of the transition kernel got 22 % slower with it and stays scalar.
+// (a0, a1) += (b0, b1) as one packed instruction: half the issue slots of two scalar additions.
+__device__ __forceinline__ void add2(float& a0, float& a1, float b0, float b1) {
+  asm("{\n .reg .b64 x, y;\n mov.b64 x, {%0, %1};\n mov.b64 y, {%2, %3};\n add.f32x2 x, x, y;\n mov.b64 {%0, %1}, x;\n}\n"
+      : "+f"(a0), "+f"(a1)
+      : "f"(b0), "f"(b1));
+}
+
+// (d0, d1) = (a0, a1) * (b0, b1) + (c0, c1) as one packed instruction.
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+  asm("{\n .reg .b64 a, b, c, d;\n mov.b64 a, {%2, %3};\n mov.b64 b, {%4, %5};\n mov.b64 c, {%6, %7};\n"
+      " fma.rn.f32x2 d, a, b, c;\n mov.b64 {%0, %1}, d;\n}\n"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
