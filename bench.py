@@ -142,6 +142,34 @@ def cpu_baseline(n: int, pad: int, rows: int, threads: int, target_s: float = 10
                       f"({dt:.2f} s), scaled by {n}/{rows}"}
 
 
+def cpu_whole_block_check(threads: int, n: int = 768, pad: int = 77) -> dict:
+    """Times the oracle's pair path of one WHOLE block at N=768 beside the row-slab estimate for the same N, so that
+    the rows/N extrapolation used at the benchmark size is checked in the same run."""
+    import torch
+
+    import protenix_b200 as px
+    from oracle import pairformer_oracle as O
+    from protenix_b200.init_utils import randomize_parameters_
+
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    z = torch.randn(n, n, 128, generator=g)
+    t = torch.ones(n)
+    t[n - pad:] = 0
+    mask = t[:, None] * t[None, :]
+    blk = randomize_parameters_(px.PairformerBlock(c_s=0), 1).eval()
+    p = {k: v.detach() for k, v in blk.state_dict().items()}
+    with torch.no_grad():
+        t0 = time.perf_counter()
+        O.pairformer_block(None, z, mask, p, row_chunk=64)
+        whole = time.perf_counter() - t0
+    rows = max(8, min(n, int(round(n * 4.0 / max(whole, 1e-3)))))      # a slab of about 4 s
+    slab = cpu_baseline(n, pad, rows, threads)
+    return {"n_token": n, "whole_block_s": whole, "slab_estimate_s": slab["sec_per_block_est"], "slab_rows": rows,
+            "estimate_over_measured": slab["sec_per_block_est"] / whole,
+            "token_pairs_per_s_whole_block": n * n / whole, "cores": threads}
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -257,6 +285,114 @@ def run_micro(args) -> None:
                       "steps": args.steps, "warmup": args.warmup, "kernels": out}), flush=True)
 
 
+def output_check(stack, sharded, z_timed, s_timed, dev, world: int, rank: int, zdt) -> dict:
+    """Outside the timed region: is the timed output finite, did any bounded device-side wait give up, and does one
+    block at N=256 through the same objects (the sharded path on N GPUs) agree with the oracle (fp32 on this GPU,
+    TF32 off, as the checker)?"""
+    import torch
+    import torch.distributed as dist
+
+    from oracle import pairformer_oracle as O
+    from protenix_b200 import ops
+
+    finite = bool(torch.isfinite(z_timed.float()).all()) and bool(torch.isfinite(s_timed.float()).all())
+    flags = ops.device_error_flags(dev, raise_on_error=False)
+    n = 256
+    g = torch.Generator().manual_seed(11)
+    z = torch.randn(n, n, 128, generator=g).to(zdt).to(dev)
+    s = torch.randn(n, 384, generator=g).to(dev)
+    t = torch.ones(n)
+    t[n - 19:] = 0
+    mask = (t[:, None] * t[None, :]).to(dev)
+    blk = stack.blocks[0]
+    if sharded is None:
+        s1, z1 = blk(s, z, mask)
+    else:
+        from protenix_b200.sharded import ShardedPairformer
+
+        one = ShardedPairformer(blk)
+        s1, z_loc = one.forward(s, one.shard_rows(z), mask)
+        z1 = one.gather_rows(z_loc)
+        one.close()
+    flags |= ops.device_error_flags(dev, raise_on_error=False)
+    if world > 1:
+        tt = torch.tensor([float(finite), float(flags)], device=dev, dtype=torch.float64)
+        lo, hi = tt.clone(), tt.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        finite, flags = bool(lo[0].item()), int(hi[1].item())
+    out = {"finite": finite, "device_flags": flags, "block_n": n}
+    if rank == 0:
+        tf32 = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+        p = {k: v.detach().float() for k, v in blk.state_dict().items()}
+        s_ref, z_ref = O.pairformer_block(s.float(), z.float(), mask, p, row_chunk=64)
+        torch.backends.cuda.matmul.allow_tf32 = tf32
+        out["relF_block"] = O.rel_frobenius(z1.float(), z_ref)
+        out["relF_block_s"] = O.rel_frobenius(s1.float(), s_ref)
+        out["ok"] = bool(finite and flags == 0 and out["relF_block"] <= 1e-2 and out["relF_block_s"] <= 1e-2)
+    return out
+
+
+def side_size_record(stack, sharded, dev, world: int, rank: int, zdt, args) -> dict:
+    """ms per block and token-pairs/s at N=768 (the other size the metric is quoted at): four blocks of the same
+    stack, device-resident, CUDA events, max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    n, nb = 768, 4
+    if n % world:
+        return {"skipped": f"N={n} not divisible by {world} ranks"}
+    g = torch.Generator().manual_seed(5)
+    nl = n // world
+    z0 = torch.randn(n, n, 128, generator=g)[rank * nl:(rank + 1) * nl].to(zdt).to(dev)
+    s0 = torch.randn(n, 384, generator=g).to(dev)
+    t = torch.ones(n)
+    t[n - n // 10:] = 0
+    mask = (t[:, None] * t[None, :]).to(dev)
+    z = torch.empty_like(z0)
+    if sharded is None:
+        blocks = list(stack.blocks[:nb])
+
+        def step():
+            z.copy_(z0)
+            s = s0
+            for b in blocks:
+                s, _ = b(s, z, mask, inplace_safe=True)
+    else:
+        from protenix_b200.sharded import ShardedPairformer
+
+        sub = ShardedPairformer(stack, group=None)
+        sub.blocks = sub.blocks[:nb]
+
+        def step():
+            z.copy_(z0)
+            sub.forward(s0, z, mask)
+    for _ in range(max(3, args.warmup)):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    e0.record()
+    for _ in range(reps):
+        step()
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    if world > 1:
+        tt = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+        sub.close()
+    return {"n_token": n, "blocks": nb, "ms_per_block": ms / nb, "token_pairs_per_s": n * n * nb / (ms * 1e-3),
+            "note": "z is 75 MB at this size (< L2): every step starts with a copy of z over the working tensor, and a "
+                    "block's intermediates (1.1 GB) exceed L2"}
+
+
 def main() -> None:
     args = parse_args()
     if args.impl == "reference":
@@ -349,7 +485,7 @@ def main() -> None:
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        step_device()
+        s_last, z_last = step_device()
     e1.record()
     barrier()
     sampler.stop_flag = True
@@ -369,6 +505,10 @@ def main() -> None:
     e1.record()
     barrier()
     ms_e2e = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+
+    # ---- the timed output is looked at: finite, no bounded wait gave up, and one block against the oracle ----
+    check = output_check(stack, sharded, z_last, s_last, dev, world, rank, zdt)
+    n768 = side_size_record(stack, sharded, dev, world, rank, zdt, args) if n != 768 else None
 
     if rank != 0:
         if world > 1:
@@ -409,9 +549,14 @@ def main() -> None:
                 "d2h_bytes_per_step": world * (z_out_host.numel() * z_out_host.element_size() + s_out_host.numel() * 4)},
         "gpu_launches": launches,
         "roofline": roof,
+        "check": check,
     }
+    if n768 is not None:
+        line["n768"] = n768
     if not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(n, args.pad, args.cpu_rows, os.cpu_count() or 1)
+        cores = os.cpu_count() or 1
+        line["cpu_baseline"] = cpu_baseline(n, args.pad, args.cpu_rows, cores)
+        line["cpu_baseline"]["whole_block_check"] = cpu_whole_block_check(cores)
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

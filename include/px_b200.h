@@ -92,10 +92,33 @@ PX_API int32_t px_trimul_in_proj(const void* z, int32_t z_dtype, const float* ma
  * 16-byte aligned.  Replaces _combine_projections, protenix/model/triangular/triangular.py:123-150. */
 PX_API int32_t px_trimul_contract(const px_bf16* a, const px_bf16* b, px_bf16* x, int64_t channels, int64_t n, int64_t ld,
                            void* stream);
-/* Synchronises the device, then returns and clears the flags set by device-side bounded waits
- * that ran out (0 = none).  A non-zero value means a kernel gave up waiting and its output is
- * not valid.  No counterpart in the reference. */
+/* Device-side waits are bounded: a kernel whose wait runs out records a flag, stops issuing work, frees what it
+ * holds and returns; kernels launched while a flag is set return without working.  The call synchronises the
+ * device, then returns and clears the record: bit f of *flags (PX_FAMILY_*) is set when a wait of kernel family f
+ * gave up -- the outputs written since the last call are then not valid.  px_device_error_detail also fills
+ * detail[PX_N_FAMILIES] with the wait codes of each family (which pipeline role gave up).  No counterpart in the
+ * reference (torch reports asynchronous failures through the CUDA error state). */
+#define PX_FAMILY_CONTRACT 0
+#define PX_FAMILY_FLASH 1
+#define PX_FAMILY_TRANSITION 2
+#define PX_FAMILY_TRIMUL_IN 3
+#define PX_FAMILY_TRIMUL_OUT 4
+#define PX_FAMILY_TRIATT_IN 5
+#define PX_FAMILY_TRIATT_OUT 6
+#define PX_FAMILY_PAIR_BIAS 7
+#define PX_FAMILY_RECYCLE 8
+#define PX_FAMILY_SELFTEST 9
+#define PX_N_FAMILIES 10
 PX_API int32_t px_device_error_flags(uint32_t* flags);
+PX_API int32_t px_device_error_detail(uint32_t* flags, uint32_t* detail);
+/* Limit of every bounded wait on the current device, in SM clock cycles (default 2^28, about 0.14 s); cycles <= 0
+ * restores the default.  No counterpart in the reference. */
+PX_API int32_t px_set_wait_limit_cycles(int64_t cycles);
+/* Launches a one-CTA kernel whose wait can never complete (an mbarrier nobody arrives on).  It gives up after the
+ * wait limit, sets bit PX_FAMILY_SELFTEST and writes 1 to *out_word (device memory); launched while that flag is
+ * still set it writes 2 and returns at once.  Exercises the give-up path without faulting the GPU.  No counterpart in
+ * the reference. */
+PX_API int32_t px_selftest_wait_timeout(uint32_t* out_word, void* stream);
 /* Stage 3: z_out = [z_in +] W_z LN_out(x) * sigmoid(W_g LN_in(z_in)).  z_out may alias z_in.
  * Replaces protenix/model/triangular/triangular.py:559-565. */
 PX_API int32_t px_trimul_out(const px_bf16* x, const void* z_in, void* z_out, int32_t z_dtype, const float* ln_in_w,

@@ -230,7 +230,8 @@ def rel_frobenius(a: torch.Tensor, b: torch.Tensor) -> float:
 
 
 def pair_path_row_slab(z: torch.Tensor, pair_mask: Optional[torch.Tensor], p: Params, r0: int, r1: int,
-                       shared: Optional[dict] = None) -> Tuple[Dict[str, torch.Tensor], dict]:
+                       shared: Optional[dict] = None, only: Optional[Tuple[str, ...]] = None
+                       ) -> Tuple[Dict[str, torch.Tensor], dict]:
     """Timing sample of one block's pair path: the five pair updates for output rows [r0, r1) only.
 
     Every update is computed from the same input z (the sequential dependence between the five
@@ -244,8 +245,10 @@ def pair_path_row_slab(z: torch.Tensor, pair_mask: Optional[torch.Tensor], p: Pa
     None (so that the slabs equal the full updates; the tests use this), or supplied by a caller
     that only wants the timing and passes stand-in tensors of the right shapes.  Returns the five
     update slabs by sub-module name; the ending-node slab is indexed by column (rows [r0, r1) of
-    the transposed update).  Used only by the CPU-baseline leg of the benchmark.
+    the transposed update).  ``only`` restricts the work to the named sub-modules (parity tests at sizes where the
+    full update does not fit).  Used by the CPU-baseline leg of the benchmark and by tests.
     """
+    want = lambda name: only is None or name in only
     n = z.shape[0]
     mask = pair_mask if pair_mask is not None else z.new_ones(n, n)
 
@@ -255,11 +258,15 @@ def pair_path_row_slab(z: torch.Tensor, pair_mask: Optional[torch.Tensor], p: Pa
     if shared is None:
         shared = {}
         for name in ("tri_mul_out", "tri_mul_in"):
+            if not want(name):
+                continue
             q = _sub(p, name)
             zn = layer_norm(z, q["layer_norm_in.weight"], q["layer_norm_in.bias"])
             shared[name + ".a"] = gated(zn, q, "a", mask)
             shared[name + ".b"] = gated(zn, q, "b", mask)
         for name, tr in (("tri_att_start", False), ("tri_att_end", True)):
+            if not want(name):
+                continue
             q = _sub(p, name)
             x = z.transpose(0, 1) if tr else z
             xn = layer_norm(x, q["layer_norm.weight"], q["layer_norm.bias"])
@@ -267,6 +274,8 @@ def pair_path_row_slab(z: torch.Tensor, pair_mask: Optional[torch.Tensor], p: Pa
     rows = slice(r0, r1)
     out: Dict[str, torch.Tensor] = {}
     for name in ("tri_mul_out", "tri_mul_in"):
+        if not want(name):
+            continue
         q = _sub(p, name)
         zn = layer_norm(z[rows], q["layer_norm_in.weight"], q["layer_norm_in.bias"])
         a_slab = gated(zn, q, "a", mask[rows])
@@ -279,6 +288,8 @@ def pair_path_row_slab(z: torch.Tensor, pair_mask: Optional[torch.Tensor], p: Pa
         x = layer_norm(x, q["layer_norm_out.weight"], q["layer_norm_out.bias"]) @ q["linear_z.weight"].T
         out[name] = x * torch.sigmoid(zn @ q["linear_g.weight"].T)
     for name, tr in (("tri_att_start", False), ("tri_att_end", True)):
+        if not want(name):
+            continue
         q = _sub(p, name)
         x = (z.transpose(0, 1) if tr else z)[rows]
         m = (mask.transpose(0, 1) if tr else mask)[rows]
@@ -293,5 +304,6 @@ def pair_path_row_slab(z: torch.Tensor, pair_mask: Optional[torch.Tensor], p: Pa
         o = _attend(qq, kk, vv, (1e9 * (m - 1))[:, None, None, :] + shared[name + ".bias"][None])
         g = torch.sigmoid(xn @ q["mha.linear_g.weight"].T).view(-1, n, h, d)
         out[name] = (o * g).reshape(-1, n, h * d) @ q["mha.linear_o.weight"].T
-    out["pair_transition"] = transition(z[rows], _sub(p, "pair_transition"))
+    if want("pair_transition"):
+        out["pair_transition"] = transition(z[rows], _sub(p, "pair_transition"))
     return out, shared

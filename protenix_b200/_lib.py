@@ -26,6 +26,9 @@ SIGNATURES = {
     "px_trimul_in_proj": (I32, [P, I32, P, P, P, P, P, P, P, P, P, I64, I64, I64, I32, F, P]),
     "px_trimul_contract": (I32, [P, P, P, I64, I64, I64, P]),
     "px_device_error_flags": (I32, [P]),
+    "px_device_error_detail": (I32, [P, P]),
+    "px_set_wait_limit_cycles": (I32, [I64]),
+    "px_selftest_wait_timeout": (I32, [P, P]),
     "px_trimul_out": (I32, [P, P, P, I32, P, P, P, P, P, P, I64, I64, I64, I32, F, P]),
     "px_trimul_workspace_bytes": (I64, [I64]),
     "px_triangle_multiplication": (I32, [P, P, I32, P, P, P, P, P, P, P, P, P, P, P, P, I64, I64, I32, I32, F, P]),

@@ -40,6 +40,7 @@ trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nk = (ld + kTcBK - 1) / kTcBK;
 
+  if (cta_skip_after_error()) return;   // an earlier bounded wait gave up: do not start new work
   if (threadIdx.x == 0) {
     for (int s = 0; s < kTcStages; ++s) {
       mbar_init(&bars.full[s], 1);
@@ -158,13 +159,7 @@ trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 
   // teardown: everybody meets, then the allocating warp frees the tensor memory
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-  __syncthreads();
-  if (g_tc_error != 0) {  // a wait ran out somewhere: give copies that may still be in flight time to land
-    const long long t0 = clock64();
-    while (clock64() - t0 < 200000) {
-    }
-    __syncthreads();
-  }
+  cta_teardown_sync();
   if (warp == 0) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTcCols) : "memory");
@@ -178,10 +173,7 @@ static bool make_operand_map(CUtensorMap* map, const void* base, int64_t channel
                      (uint64_t)ld * 2, (uint64_t)n * ld * 2, kTcBK, box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-unsigned int contract_error_flags() {
-  unsigned int v = 0;
-  return read_clear_tc_error(&v) == 0 ? v : 0x80000000u;
-}
+PX_DEFINE_FAMILY_HOOKS(contract)
 
 }  // namespace px
 

@@ -64,15 +64,6 @@ struct FlashLayout {
 };
 static_assert(FlashLayout::kv % 1024 == 0 && FlashLayout::bias % 1024 == 0 && kFStageBytes % 1024 == 0, "swizzle alignment");
 
-#ifdef PX_FLASH_TRACE
-// Timeline probe (debug builds only): CTA (0,0,0) records clock64 stamps of its pipeline phases.
-__device__ long long g_flash_trace[4096];
-#define PX_TRACE(slot, idx) \
-  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (idx) < 64) g_flash_trace[(slot) * 64 + (idx)] = clock64();
-#else
-#define PX_TRACE(slot, idx)
-#endif
-
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -83,9 +74,7 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 // busiest unit of this kernel): x = n + f with n = round(x) taken from the mantissa after adding 1.5 * 2^23,
 // 2^f by a cubic on [-0.5, 0.5] (relative error 7.5e-5, far below the bf16 rounding of P), 2^n added into the exponent
 // field.  Arguments below -126 (masked or padded keys) give 2^-126.
-#ifndef PX_FLASH_POLY
-#define PX_FLASH_POLY 4   // every PX_FLASH_POLY-th pair of exponentials takes this path (0: none)
-#endif
+constexpr int kFPolyEvery = 4;   // every fourth pair of exponentials takes this path
 __device__ __forceinline__ void exp2_poly2(float x0, float x1, float& p0, float& p1) {
   constexpr float kMagic = 12582912.f;
   constexpr float c0 = 0.9999280571937561f, c1 = 0.6932610273361206f, c2 = 0.2426111102104187f, c3 = 0.05517144873738289f;
@@ -115,6 +104,7 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q0 = blockIdx.x * 128, h = blockIdx.y, u0 = blockIdx.z * kFRows;
 
+  if (cta_skip_after_error()) return;   // an earlier bounded wait gave up: do not start new work
   if (threadIdx.x == 0) {
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars.bias_full[b], 1);
@@ -190,12 +180,10 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       ok = ok && issue_s(0);
       for (int i = 0; i < n_items && ok; ++i) {
         const int kt = i / kFRpg, r = i % kFRpg;
-        PX_TRACE(8 + g, i);
         if (i + 1 < n_items) {                      // next S as soon as the group holds the current one in registers
           ok = mbar_wait(&bars.s_free[g], i & 1, 2u) && issue_s(i + 1);
           if (!ok) break;
         }
-        PX_TRACE(12 + g, i);
         if (i + kFStages - 1 < n_items) {           // refill: that stage was last read by P.V of item i-1
           if (i >= 1) ok = mbar_wait(&bars.pv_done[g], (i - 1) & 1, 32u);
           if (!ok) break;
@@ -246,11 +234,9 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
       for (int r = 0; r < kFRpg; ++r) {
         const int i = kt * kFRpg + r;               // this group's work item
-        if (qw == 0) { PX_TRACE(16 * g + 0, i); }
         ok = mbar_wait(&bars.s_full[g], i & 1, 128u);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (qw == 0) { PX_TRACE(16 * g + 1, i); }
         tc_fence_after();
         float s[kFKT];
         {
@@ -263,7 +249,6 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars.s_free[g]);  // S is in registers: the next S may be computed
-        if (qw == 0) { PX_TRACE(16 * g + 2, i); }
         // + pair bias: box c of the tile holds columns 32c..32c+31 of all 128 rows, 128-byte rows, 16-byte pieces
         // swizzled by row
 #pragma unroll
@@ -290,7 +275,6 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             add2(s[4 * c4 + 2], s[4 * c4 + 3], m4.z, m4.w);
           }
         }
-        if (qw == 0) { PX_TRACE(16 * g + 3, i); }
         // tile maximum: four independent chains, so the reduction costs about 8 dependent steps
         float mq[4];
 #pragma unroll
@@ -322,7 +306,7 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // so the denominator can sum the fp32 values themselves.
             add2(s[2 * e], s[2 * e + 1], nm, nm);
             float p0, p1;
-            if (PX_FLASH_POLY > 0 && e % (PX_FLASH_POLY > 0 ? PX_FLASH_POLY : 1) == PX_FLASH_POLY - 1) {
+            if (e % kFPolyEvery == kFPolyEvery - 1) {
               exp2_poly2(s[2 * e], s[2 * e + 1], p0, p1);
             } else {
               p0 = fast_exp2(s[2 * e]);
@@ -355,12 +339,10 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           uint32_t(&w0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&w[0]);
           tmem_st32(t_p, w0);
         }
-        if (qw == 0) { PX_TRACE(16 * g + 4, i); }
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars.p_ready[g]);
-        if (qw == 0) { PX_TRACE(16 * g + 5, i); }
       }
     }
     // ---- epilogue: o = O / denominator for this group's rows
@@ -392,13 +374,7 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   }
 
   tc_fence_before();
-  __syncthreads();
-  if (g_tc_error != 0) {  // a wait ran out: let copies that may still be in flight land before leaving
-    const long long t0 = clock64();
-    while (clock64() - t0 < 200000) {
-    }
-    __syncthreads();
-  }
+  cta_teardown_sync();
   if (warp == 4 * kFGroups) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kFCols) : "memory");
@@ -424,18 +400,7 @@ __global__ void flash_tile_flags_kernel(const float* __restrict__ mb, unsigned l
   if (threadIdx.x == 0) flags[(size_t)u * gridDim.y + w] = word;
 }
 
-#ifdef PX_FLASH_TRACE
-}  // namespace px
-extern "C" __attribute__((visibility("default"))) int px_debug_flash_trace(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, px::g_flash_trace, sizeof(long long) * 4096);
-}
-namespace px {
-#endif
-
-unsigned int flash_error_flags() {
-  unsigned int v = 0;
-  return read_clear_tc_error(&v) == 0 ? v : 0x800000u;
-}
+PX_DEFINE_FAMILY_HOOKS(flash)
 
 }  // namespace px
 

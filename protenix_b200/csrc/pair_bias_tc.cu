@@ -60,6 +60,7 @@ pair_bias_tc_kernel(const __grid_constant__ CUtensorMap map_z, const Tz* __restr
   ctx.n_t = (int)rows;
   ctx.swap = 0;
 
+  if (cta_skip_after_error()) return;   // an earlier bounded wait gave up: do not start new work
   if (threadIdx.x == 0) {
     tile_bars_init(bars.tile, kTma, 2);
     mbar_init(&bars.acc_full, 1);
@@ -132,23 +133,14 @@ pair_bias_tc_kernel(const __grid_constant__ CUtensorMap map_z, const Tz* __restr
   }
 
   tc_fence_before();
-  __syncthreads();
-  if (g_tc_error != 0) {  // a wait ran out: let copies that may still be in flight land before leaving
-    const long long t0 = clock64();
-    while (clock64() - t0 < 200000) {
-    }
-    __syncthreads();
-  }
+  cta_teardown_sync();
   if (warp == 8) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(256u) : "memory");
   }
 }
 
-unsigned int pair_bias_error_flags() {
-  unsigned int v = 0;
-  return read_clear_tc_error(&v) == 0 ? v : 0x80u;
-}
+PX_DEFINE_FAMILY_HOOKS(pair_bias)
 
 template <typename Tz>
 static int32_t launch_pair_bias(const void* z, const float* ln_w, const float* ln_b, const px_bf16* w, float* out,

@@ -15,15 +15,6 @@ namespace px {
 constexpr int kPanelBytes = 128 * 128;        // [128 rows][64 k] bf16, 128-byte swizzle
 constexpr int kOperandBytes = 2 * kPanelBytes;  // [128 rows][128 k] as two k panels
 
-// Optional timeline of CTA 0 (debug builds only): slot = event kind, idx = tile counter.
-#ifdef PX_ROW_TRACE
-__device__ long long g_row_trace[32 * 32];
-#define ROW_TRACE(slot, idx) \
-  if (blockIdx.x == 0 && lane == 0 && (idx) < 32) g_row_trace[(slot) * 32 + (idx)] = clock64();
-#else
-#define ROW_TRACE(slot, idx)
-#endif
-
 __device__ __forceinline__ float tanh_fast(float x) {
   float y;
   asm("tanh.approx.f32 %0, %1;\n" : "=f"(y) : "f"(x));

@@ -6,10 +6,28 @@
 
 namespace px {
 
-constexpr long long kWaitCycles = 1ll << 31;  // about one second at 2 GHz
-
-// Flags recorded by bounded waits that ran out (one word per translation unit).
+// Flags recorded by bounded waits that ran out, and the limit of a wait in clock cycles (2^28: about 0.14 s at
+// 1.9 GHz; tests shorten it).  One copy of each per translation unit.
 static __device__ unsigned int g_tc_error = 0;
+static __device__ long long g_wait_limit = 1ll << 28;
+
+// True once any bounded wait of this translation unit's kernels has given up (until the host reads the word).
+__device__ __forceinline__ bool tc_error_seen() { return *reinterpret_cast<volatile unsigned int*>(&g_tc_error) != 0; }
+
+// Called by every thread at the top of a kernel: after a wait has run out, CTAs that start later skip their work
+// (the decision is uniform over the CTA), so a failure holds the GPU for one wait limit, not one per CTA.
+__device__ __forceinline__ bool cta_skip_after_error() { return __syncthreads_or(tc_error_seen()) != 0; }
+
+// Called by every thread at the end of a kernel, in place of the closing __syncthreads(): when a wait ran out, copies
+// may still be in flight towards this CTA's shared memory, so the CTA lingers before it frees anything.
+__device__ __forceinline__ void cta_teardown_sync() {
+  if (__syncthreads_or(tc_error_seen())) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) {
+    }
+    __syncthreads();
+  }
+}
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
@@ -44,7 +62,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
         : "r"(addr), "r"(parity), "r"(1000000u)
         : "memory");
     if (done) return true;
-    if (clock64() - t0 > kWaitCycles) {
+    if (tc_error_seen()) return false;   // another wait gave up: this one would only repeat its limit
+    if (clock64() - t0 > *reinterpret_cast<volatile long long*>(&g_wait_limit)) {
       atomicOr(&g_tc_error, code);
       return false;
     }
@@ -192,5 +211,16 @@ static inline int read_clear_tc_error(unsigned int* out) {
   *out = v;
   return 0;
 }
+
+// Host hooks of one translation unit: <family>_error_flags() returns (and clears) the wait codes its kernels
+// recorded (0x80000000 when the word could not be read), <family>_set_wait_limit() replaces the limit of its waits.
+#define PX_DEFINE_FAMILY_HOOKS(family)                                                              \
+  unsigned int family##_error_flags() {                                                             \
+    unsigned int v = 0;                                                                             \
+    return read_clear_tc_error(&v) == 0 ? v : 0x80000000u;                                          \
+  }                                                                                                 \
+  int family##_set_wait_limit(long long cycles) {                                                   \
+    return cudaMemcpyToSymbol(g_wait_limit, &cycles, sizeof(cycles)) == cudaSuccess ? 0 : -1;       \
+  }
 
 }  // namespace px

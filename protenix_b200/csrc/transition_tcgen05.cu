@@ -43,14 +43,6 @@ struct TransLayout {
   static constexpr int total = bars + (int)sizeof(TransBars);
 };
 
-#ifdef PX_TRANS_TRACE
-__device__ long long g_trans_trace[16 * 64];
-#define TR_TRACE(slot, idx) \
-  if (blockIdx.x == 0 && lane == 0 && (idx) < 64) g_trans_trace[(slot) * 64 + (idx)] = clock64();
-#else
-#define TR_TRACE(slot, idx)
-#endif
-
 // Four consecutive channels as they are stored (8 or 16 bytes), so that loads can be kept in flight cheaply.
 template <typename Tz>
 struct Raw4;
@@ -84,6 +76,7 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int first_tile = blockIdx.x, tile_step = gridDim.x;
 
+  if (cta_skip_after_error()) return;   // an earlier bounded wait gave up: do not start new work
   if (threadIdx.x == 0) {
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars.a_full[b], 4);
@@ -145,7 +138,6 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
           const int s = j % kTrStages, hb = j & 1;
           ok = mbar_wait(&bars.w_full[s], (j / kTrStages) & 1, 4u) && mbar_wait(&bars.h_free[hb], ((j >> 1) & 1) ^ 1, 4u);
           if (!ok) break;
-          TR_TRACE(0, j);
           tc_fence_after();
           const uint32_t wbase = smem_u32(sm + TransLayout::w + s * kTrStageBytes);
 #pragma unroll
@@ -154,7 +146,6 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
                       umma_desc_sw128(wbase + (ks >> 2) * 16384) + 2 * (ks & 3), idesc, ks ? 1u : 0u);
           umma_commit(&bars.h_full[hb]);
           umma_commit(&bars.w_empty[s]);                // this thread's share of the reads of the stage
-          TR_TRACE(1, j);
         }
         if (ok) umma_commit(&bars.a_free[ab]);          // the tile has been read for the last time
       }
@@ -170,7 +161,6 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
           const int s = j % kTrStages, hb = j & 1;
           ok = mbar_wait(&bars.w_full[s], (j / kTrStages) & 1, 4u) && mbar_wait(&bars.p_ready[hb], (j >> 1) & 1, 8u);
           if (!ok) break;
-          TR_TRACE(2, j);
           tc_fence_after();
           const uint64_t dwo = umma_desc_sw128(smem_u32(sm + TransLayout::w + s * kTrStageBytes) + kTrW1Bytes);
 #pragma unroll
@@ -178,7 +168,6 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
             umma_bf16_ts(tmem_base + 256 + 128 * ob, tmem_base + 128 * hb + 8 * ks, dwo + 2 * ks, idesc, (c | ks) ? 1u : 0u);
           umma_commit(&bars.h_free[hb]);
           umma_commit(&bars.w_empty[s]);
-          TR_TRACE(3, j);
         }
         if (ok) umma_commit(&bars.out_full[ob]);
       }
@@ -214,7 +203,6 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
       bool ok = mbar_wait(&bars.out_full[ob], (k >> 1) & 1, 32u);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      if (qw == 0) { TR_TRACE(10, k); }
       tc_fence_after();
 #pragma unroll 1
       for (int q = 0; q < 4; ++q) {
@@ -248,7 +236,6 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
         }
         __syncwarp();
       }
-      if (qw == 0) { TR_TRACE(11, k); }
     }
   } else if (warp >= 8) {
     // ------------------------------------------------------------------ LayerNorm -> swizzled A operand
@@ -264,7 +251,6 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       unsigned char* sa = sm + TransLayout::a + ab * kTrABytes;
-      if (qw == 0) { TR_TRACE(8, k); }
       // eight rows per batch; the next batch is requested (as stored) before this one is reduced
       Raw4<Tz> raw[8];
       auto request = [&](int rb) {
@@ -321,7 +307,6 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars.a_full[ab]);
-      if (qw == 0) { TR_TRACE(9, k); }
     }
   } else {
     // ------------------------------------------------------------------ SwiGLU in registers
@@ -338,7 +323,6 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
         ok = mbar_wait(&bars.h_full[hb], (j >> 1) & 1, 64u);
         ok = named_barrier_all(2, 256, ok);                // all eight warps go on, or none
         if (!ok) break;
-        if (warp == 0) { TR_TRACE(4 + 2 * hb, j >> 1); }
         tc_fence_after();
         uint32_t w[16];
 #pragma unroll
@@ -363,37 +347,19 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars.p_ready[hb]);
-        if (warp == 0) { TR_TRACE(5 + 2 * hb, j >> 1); }
       }
     }
   }
 
   tc_fence_before();
-  __syncthreads();
-  if (g_tc_error != 0) {  // a wait ran out: let copies that may still be in flight land before leaving
-    const long long t0 = clock64();
-    while (clock64() - t0 < 200000) {
-    }
-    __syncthreads();
-  }
+  cta_teardown_sync();
   if (warp == 16) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
   }
 }
 
-#ifdef PX_TRANS_TRACE
-}  // namespace px
-extern "C" __attribute__((visibility("default"))) int px_debug_trans_trace(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, px::g_trans_trace, sizeof(long long) * 1024);
-}
-namespace px {
-#endif
-
-unsigned int transition_error_flags() {
-  unsigned int v = 0;
-  return read_clear_tc_error(&v) == 0 ? v : 0x80u;
-}
+PX_DEFINE_FAMILY_HOOKS(transition)
 
 template <typename Tz>
 static int32_t launch_transition(const void* x_in, void* x_out, const float* ln_w, const float* ln_b, const px_bf16* w_a,

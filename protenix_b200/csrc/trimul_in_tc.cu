@@ -76,6 +76,7 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   ctx.n_t = n_t;
   ctx.swap = swap;
 
+  if (cta_skip_after_error()) return;   // an earlier bounded wait gave up: do not start new work
   if (threadIdx.x == 0) {
     tile_bars_init(bars.tile, kTma, 3);
     for (int b = 0; b < 2; ++b) {
@@ -177,23 +178,14 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   }
 
   tc_fence_before();
-  __syncthreads();
-  if (g_tc_error != 0) {  // a wait ran out: let copies that may still be in flight land before leaving
-    const long long t0 = clock64();
-    while (clock64() - t0 < 200000) {
-    }
-    __syncthreads();
-  }
+  cta_teardown_sync();
   if (warp == 20) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
   }
 }
 
-unsigned int trimul_in_error_flags() {
-  unsigned int v = 0;
-  return read_clear_tc_error(&v) == 0 ? v : 0x80u;
-}
+PX_DEFINE_FAMILY_HOOKS(trimul_in)
 
 template <typename Tz>
 static int32_t launch_trimul_in(const void* z, const float* mask, const float* ln_w, const float* ln_b,

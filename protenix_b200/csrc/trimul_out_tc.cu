@@ -67,6 +67,7 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
   ToBars& bars = *reinterpret_cast<ToBars*>(sm + ToLayout::bars);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  if (cta_skip_after_error()) return;   // an earlier bounded wait gave up: do not start new work
   if (threadIdx.x == 0) {
     for (int s = 0; s < kToStages; ++s) {
       mbar_init(&bars.raw_full[s], kTma ? 1 : 5);          // fp32 rows: four converting warps beside the x tile
@@ -321,23 +322,14 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
   }
 
   tc_fence_before();
-  __syncthreads();
-  if (g_tc_error != 0) {  // a wait ran out: let copies that may still be in flight land before leaving
-    const long long t0 = clock64();
-    while (clock64() - t0 < 200000) {
-    }
-    __syncthreads();
-  }
+  cta_teardown_sync();
   if (warp == 20) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
   }
 }
 
-unsigned int trimul_out_error_flags() {
-  unsigned int v = 0;
-  return read_clear_tc_error(&v) == 0 ? v : 0x80u;
-}
+PX_DEFINE_FAMILY_HOOKS(trimul_out)
 
 template <typename Tz>
 static int32_t launch_trimul_out(const px_bf16* x, const void* z_in, void* z_out, const float* ln_in_w, const float* ln_in_b,

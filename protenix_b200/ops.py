@@ -100,7 +100,8 @@ def reset_launch_count() -> int:
 
 
 def _launch(name: str, fn, *args) -> None:
-    """Call one C-ABI launcher (exactly one kernel), optionally bracketed by CUDA events."""
+    """Call one C-ABI launcher, optionally bracketed by CUDA events (one kernel per launcher, except
+    ``px_triatt_flash``, which runs its small tile-flag kernel first: its stage time covers both)."""
     global launch_count
     if _timer is not None:
         a = torch.cuda.Event(enable_timing=True)
@@ -113,6 +114,30 @@ def _launch(name: str, fn, *args) -> None:
         st = fn(*args)
     launch_count += 1
     _lib.check(st, name)
+
+
+KERNEL_FAMILIES = ("trimul_contract", "triatt_flash", "transition", "trimul_in_proj", "trimul_out", "triatt_in_proj",
+                   "triatt_out", "pair_bias_proj", "recycle_update", "selftest")   # bit order of px_device_error_flags
+
+
+def device_error_flags(device=None, raise_on_error: bool = True) -> int:
+    """Synchronise the device and read (and clear) the record of device-side waits that ran out.
+
+    Every wait inside the kernels is bounded; one that gives up makes its kernel return early and leaves a flag.
+    Returns the flag word (bit f = ``KERNEL_FAMILIES[f]``); raises ``RuntimeError`` on a non-zero word unless
+    ``raise_on_error`` is false.  It synchronises, so call it after a forward pass, not between kernels.
+    """
+    import ctypes
+
+    flags = ctypes.c_uint32(0)
+    detail = (ctypes.c_uint32 * len(KERNEL_FAMILIES))()
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        _lib.check(_lib.load().px_device_error_detail(ctypes.byref(flags), detail), "px_device_error_detail")
+    if flags.value and raise_on_error:
+        what = ", ".join(f"{KERNEL_FAMILIES[f]} (wait codes 0x{detail[f]:x})" for f in range(len(KERNEL_FAMILIES))
+                         if flags.value >> f & 1)
+        raise RuntimeError(f"a bounded device-side wait ran out in: {what}; the outputs of those kernels are not valid")
+    return int(flags.value)
 
 
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}

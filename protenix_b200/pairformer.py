@@ -12,11 +12,13 @@ Inference only: dropout is the identity (eval mode), gradients are not produced.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Tuple
 
 import torch
 import torch.nn as nn
 
+from . import ops
 from .primitives import Transition
 from .transformer import AttentionPairBias
 from .triangular import (TriangleAttention, TriangleMultiplicationIncoming, TriangleMultiplicationOutgoing,
@@ -112,6 +114,8 @@ class PairformerStack(nn.Module):
         main.wait_stream(side)
         if s is not None:
             s.record_stream(main)
+        if os.environ.get("PX_CHECK_DEVICE_ERRORS", "0") == "1":    # synchronises: off unless asked for
+            ops.device_error_flags(zc.device)
         return s, (zc[None] if batch else zc)
 
 

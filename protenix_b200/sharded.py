@@ -135,6 +135,20 @@ class PeerExchange:
         """Stream-ordered: completes on a rank only after every rank's earlier copies have completed."""
         dist.all_reduce(self.flag, group=self.group)
 
+    def close(self) -> None:
+        """Unmaps the other ranks' buffers and frees this rank's (after a barrier: nobody may still be writing)."""
+        if not self.local:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        for k, ptrs in self.remote.items():
+            for r, ptr in enumerate(ptrs):
+                if r != self.rank:
+                    ops.peer_close(ptr)
+        for b in self.local.values():
+            b.free()
+        self.local, self.remote = {}, {}
+
     def order(self):
         """Destination ranks, starting with the next one so that the ranks do not all write to rank 0 first."""
         return [(self.rank + 1 + i) % self.world for i in range(self.world)]
@@ -151,6 +165,12 @@ class ShardedPairformer:
         self.rank = dist.get_rank(group)
         self.stages = stages if stages is not None else CudaStages()
         self._peer: Dict[tuple, PeerExchange] = {}
+
+    def close(self) -> None:
+        """Releases the peer buffers (collective: every rank of the group must call it)."""
+        for px in self._peer.values():
+            px.close()
+        self._peer = {}
 
     # ---- helpers ------------------------------------------------------------------------------
     def shard_rows(self, z: torch.Tensor) -> torch.Tensor:

@@ -1,0 +1,106 @@
+"""Parity at the sizes the benchmark configurations name, against the oracle run on the same GPU.
+
+The oracle is plain torch, so at these sizes it runs on the device in fp64 (stack) or fp32 with TF32 off (single ops);
+it stays the checker, never the thing measured.
+
+  * 48-block stack, N=384, all-ones mask, z and s ~ N(0,1): relative Frobenius error of z and s after every block is
+    printed (run pytest with -s to see it) and the final error must be <= 3e-2, for both storage types of z.
+  * the four triangle ops at N=768 with the last 10 % of the tokens masked: <= 1e-2 each, and perturbing the padded
+    part of z leaves every bit of the valid [:691, :691] region unchanged.
+  * one triangle-attention and one triangle-multiplication at N=1536 with a ragged padding (24 key tiles per row,
+    hundreds of tiles per persistent CTA): checked on a band of rows against the oracle's row-slab form.
+"""
+import pytest
+import torch
+
+from golden_cases import padding_mask
+from helpers import build_module, relf
+from oracle import pairformer_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+TOL_OP = 1e-2
+TOL_STACK = 3e-2
+
+
+def _params(module, dtype):
+    return {k: v.detach().to(DEV, dtype) for k, v in module.state_dict().items()}
+
+
+@pytest.mark.parametrize("zdtype", [torch.bfloat16, torch.float32])
+def test_stack_48_blocks_n384(zdtype):
+    from protenix_b200 import ops
+
+    n, nb = 384, 48
+    g = torch.Generator().manual_seed(0)
+    z0 = torch.randn(n, n, 128, generator=g)
+    s0 = torch.randn(n, 384, generator=g)
+    mask = torch.ones(n, n)
+    stack = build_module("stack", dict(n_blocks=nb, c_s=384, wseed=1)).to(DEV)
+    p = _params(stack, torch.float64)
+    zr, sr, mr = z0.to(DEV, torch.float64), s0.to(DEV, torch.float64), mask.to(DEV, torch.float64)
+    z, s, m = z0.to(DEV).to(zdtype), s0.to(DEV), mask.to(DEV)
+    traj = []
+    for b, blk in enumerate(stack.blocks):
+        sr, zr = O.pairformer_block(sr, zr, mr, O._sub(p, f"blocks.{b}"), row_chunk=64)
+        s, z = blk(s, z, m, inplace_safe=True)
+        traj.append((relf(z, zr), relf(s, sr), float(zr.abs().max())))
+    ops.device_error_flags()
+    print(f"\n48-block trajectory, N={n}, z storage {zdtype}: block relF(z) relF(s) max|z_ref|")
+    for b, (ez, es, mx) in enumerate(traj):
+        print(f"  {b + 1:2d}  {ez:.3e}  {es:.3e}  {mx:.1f}")
+    assert torch.isfinite(z.float()).all() and torch.isfinite(s).all()
+    ez, es, _ = traj[-1]
+    assert ez <= TOL_STACK and es <= TOL_STACK, (ez, es)
+    # the whole stack through PairformerStack.forward (side-stream single branch) gives the same tensors
+    s2, z2 = stack(s0.to(DEV), z0.to(DEV).to(zdtype), m)
+    assert torch.equal(z2, z) and torch.equal(s2, s)
+
+
+@pytest.mark.parametrize("kind", ["tri_mul_out", "tri_mul_in", "tri_att_start", "tri_att_end"])
+def test_triangle_ops_n768_last_tenth_masked(kind):
+    from protenix_b200 import ops
+
+    n, pad = 768, 77
+    valid = n - pad
+    g = torch.Generator().manual_seed(768)
+    z = torch.randn(n, n, 128, generator=g).to(torch.bfloat16).to(DEV)
+    mask = padding_mask(n, pad).to(DEV)
+    m = build_module(kind, dict(wseed=3)).to(DEV)
+    y = m(z, mask=mask)
+    ops.device_error_flags()
+    p = _params(m, torch.float32)
+    if kind.startswith("tri_mul"):
+        ref = O.triangle_multiplication(z.float(), mask, p, outgoing=(kind == "tri_mul_out"))
+    else:
+        ref = O.triangle_attention(z.float(), mask, p, starting=(kind == "tri_att_start"), row_chunk=32)
+    assert torch.isfinite(y.float()).all()
+    assert relf(y, ref) <= TOL_OP, (kind, relf(y, ref))
+    assert relf(y[:valid, :valid], ref[:valid, :valid]) <= TOL_OP
+    del ref
+    z2 = z.clone()
+    z2[valid:] += torch.randn(pad, n, 128, generator=g).to(torch.bfloat16).to(DEV)
+    z2[:, valid:] += torch.randn(n, pad, 128, generator=g).to(torch.bfloat16).to(DEV)
+    y2 = m(z2, mask=mask)
+    assert torch.equal(y[:valid, :valid], y2[:valid, :valid])
+
+
+@pytest.mark.parametrize("kind", ["tri_att_start", "tri_att_end", "tri_mul_out", "tri_mul_in"])
+def test_triangle_ops_n1536_row_band(kind):
+    """N=1536, 37 trailing tokens masked.  The fp32 oracle of a whole op would need the [4, N, N, N] logits; its
+    row-slab form gives the same update for a band of output rows, which is what is compared."""
+    from protenix_b200 import ops
+
+    n, pad, r0, r1 = 1536, 37, 700, 732
+    g = torch.Generator().manual_seed(1536)
+    z = torch.randn(n, n, 128, generator=g).to(torch.bfloat16).to(DEV)
+    mask = padding_mask(n, pad).to(DEV)
+    blk = build_module("block", dict(c_s=0, wseed=4)).to(DEV)
+    m = getattr(blk, kind)
+    y = m(z, mask=mask)
+    ops.device_error_flags()
+    assert torch.isfinite(y.float()).all()
+    p = {k: v for k, v in _params(blk, torch.float32).items() if k.startswith(kind + ".")}
+    slabs, _ = O.pair_path_row_slab(z.float(), mask, p, r0, r1, only=(kind,))
+    got = y[:, r0:r1].transpose(0, 1) if kind == "tri_att_end" else y[r0:r1]
+    assert relf(got, slabs[kind]) <= TOL_OP, (kind, relf(got, slabs[kind]))

@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import protenix_b200 as px
-from golden_cases import random_mask
+from golden_cases import padding_mask, random_mask
 from helpers import build_module, params_of, relf
 from oracle import pairformer_oracle as O
 from protenix_b200 import ops
@@ -144,7 +144,7 @@ def test_sharded_path_with_one_rank_equals_module():
         dist.destroy_process_group()
 
 
-def _nccl_worker(rank, world, port, n, q):
+def _nccl_worker(rank, world, port, n, q, n_blocks=2, pad=None):
     import sys
 
     here = os.path.dirname(os.path.abspath(__file__))
@@ -164,16 +164,45 @@ def _nccl_worker(rank, world, port, n, q):
         g = torch.Generator().manual_seed(4)
         z = torch.randn(n, n, 128, generator=g).to(torch.bfloat16).to(dev)
         s = torch.randn(n, 384, generator=g).to(dev)
-        mask = random_mask(n, 9).to(dev)
-        stack = build_module("stack", dict(n_blocks=2, c_s=384, wseed=5)).to(dev)
+        mask = (random_mask(n, 9) if pad is None else padding_mask(n, pad)).to(dev)
+        stack = build_module("stack", dict(n_blocks=n_blocks, c_s=384, wseed=5)).to(dev)
         sp = ShardedPairformer(stack)
-        s_out, z_loc = sp.forward(s, sp.shard_rows(z), mask)
-        z_out = sp.gather_rows(z_loc)
-        if rank == 0:
-            s_ref, z_ref = stack(s, z, mask)            # the single-GPU path on the same device
-            q.put((relf(z_out, z_ref), relf(s_out, s_ref), bool(torch.equal(z_out, z_ref))))
+        try:
+            s_out, z_loc = sp.forward(s, sp.shard_rows(z), mask)
+            z_out = sp.gather_rows(z_loc)
+            flags = ops.device_error_flags(dev, raise_on_error=False)
+            if rank == 0:
+                s_ref, z_ref = stack(s, z, mask)            # the single-GPU path on the same device
+                finite = bool(torch.isfinite(z_out.float()).all() and torch.isfinite(s_out).all())
+                q.put((relf(z_out, z_ref), relf(s_out, s_ref), bool(torch.equal(z_out, z_ref)), flags, finite))
+        finally:
+            sp.close()
     finally:
         dist.destroy_process_group()
+
+
+def _run_ranks(world, n, **kw):
+    """Spawns one process per GPU, returns rank 0's result; ranks still alive after the limit are killed, so a hung
+    exchange cannot keep GPUs and IPC mappings after the test has failed."""
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_nccl_worker, args=(r, world, port, n, q), kwargs=kw) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+    hung = [p for p in procs if p.is_alive()]
+    for p in hung:
+        p.kill()
+        p.join(timeout=10)
+    assert not hung, f"{len(hung)} rank(s) did not finish"
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    return q.get(timeout=10)
 
 
 @pytest.mark.parametrize("world,n", [(2, 136), (2, 144), (4, 192), (8, 256)])
@@ -182,19 +211,18 @@ def test_sharded_over_nccl_equals_single_gpu(world, n):
     all_to_all transport (the peer copies need N/P to be a multiple of 8), the other cases through the peer copies."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    import torch.multiprocessing as mp
-
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        port = s.getsockname()[1]
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    procs = [ctx.Process(target=_nccl_worker, args=(r, world, port, n, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(timeout=300)
-    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
-    ez, es, same = q.get(timeout=10)
+    ez, es, same, flags, finite = _run_ranks(world, n)
     # same kernels, same per-element arithmetic: only the reduction-free re-layouts differ
+    assert flags == 0 and finite
+    assert ez < 1e-3 and es < 1e-3, (ez, es, same)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_block_n1536_equals_single_gpu(world):
+    """One block at N=1536 (bf16 z, 37 trailing tokens masked) row-sharded over `world` GPUs against the same block
+    on one GPU: the size the multi-GPU benchmark runs."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    ez, es, same, flags, finite = _run_ranks(world, 1536, n_blocks=1, pad=37)
+    assert flags == 0 and finite
     assert ez < 1e-3 and es < 1e-3, (ez, es, same)

@@ -34,6 +34,18 @@ def _args(n, seed, zdtype):
     return z, mask, ln, ws
 
 
+def _oracle_update(n, seed, zdtype, incoming):
+    """The same update from the CPU oracle (fp32), fed with the tensors _args draws."""
+    from oracle import pairformer_oracle as O
+
+    z, mask, ln, ws = _args(n, seed, zdtype)
+    keys = ("linear_a_p", "linear_a_g", "linear_b_p", "linear_b_g", "linear_z", "linear_g")
+    p = {f"{k}.weight": w.float().cpu() for k, w in zip(keys, ws)}
+    p.update({"layer_norm_in.weight": ln[0].cpu(), "layer_norm_in.bias": ln[1].cpu(),
+              "layer_norm_out.weight": ln[2].cpu(), "layer_norm_out.bias": ln[3].cpu()})
+    return O.triangle_multiplication(z.float().cpu(), mask.cpu(), p, outgoing=not incoming)
+
+
 def _run(lib, static, n, seed, zdtype, incoming):
     from protenix_b200 import _lib
 
@@ -69,6 +81,8 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
         assert _relf(got, want) <= TOL, (n, _relf(got, want))
         assert torch.equal(got, want), "same kernels on the same inputs must give the same bits"
         assert _relf(got.float() - z.float(), want.float() - z.float()) <= TOL   # the update itself, not z + update
+        upd = _oracle_update(n, seed, zdtype, incoming)
+        assert _relf(got.float().cpu() - z.float().cpu(), upd) <= TOL, "against the CPU oracle, not only its sibling"
 
 
 def test_static_scratch_rejects_sizes_beyond_its_capacity():
