@@ -128,13 +128,17 @@ def cpu_baseline(n: int, pad: int, rows: int, threads: int, target_s: float = 10
         O.pair_path_row_slab(z, mask, p, 0, r, shared)
         return time.perf_counter() - t0
 
+    auto = rows <= 0
     with torch.no_grad():
-        if rows <= 0:
+        if auto:
             probe = min(2, n)
             sample(probe)                      # warm the thread pool and the allocator
             t_probe = sample(probe)
-            rows = int(max(probe, min(n, 128, probe * target_s / max(t_probe, 1e-3))))
+            rows = int(max(probe, min(n, 256, probe * target_s / max(t_probe, 1e-3))))
         dt = sample(rows)
+        if auto and dt < target_s / 2 and rows < min(n, 256):   # the two-row probe overestimates the cost per row
+            rows = int(min(n, 256, max(rows + 1, rows * 0.8 * target_s / max(dt, 1e-3))))
+            dt = sample(rows)
     sec_per_block = dt * n / rows
     return {"value": n * n / sec_per_block, "unit": UNIT, "cores": threads, "kind": "port",
             "sec_per_block_est": sec_per_block,
