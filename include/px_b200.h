@@ -11,10 +11,16 @@
  *
  * Conventions
  *   - N            number of tokens; the pair tensor z is [N][N][128], row-major, channel last.
- *   - z_dtype      storage type of the residual stream: PX_F32 or PX_BF16.  All matrix
- *                  products take bf16 operands and accumulate in fp32.
- *   - weights      bf16, row-major [out_features][in_features] exactly as the reference's
- *                  nn.Linear.weight (cast to bf16 by the caller); LayerNorm scale/offset fp32.
+ *   - z_dtype      storage type of the residual stream: PX_F32 or PX_BF16.  All matrix products
+ *                  take 16-bit operands and accumulate in fp32.  Rows of a bf16 z are multiplied as
+ *                  they are stored (bf16 x bf16); rows of an fp32 z are standardised and rounded to
+ *                  fp16 (fp16 x fp16: a standardised row cannot leave the fp16 range, and fp16 keeps
+ *                  three more mantissa bits).  Every intermediate 16-bit tensor (a, b, x, q, k, v, o)
+ *                  is fp16 in both cases.
+ *   - weights      16-bit, row-major [out_features][in_features] exactly as the reference's
+ *                  nn.Linear.weight, cast by the caller: px_w16 parameters take the format of the z
+ *                  they multiply (bf16 for PX_BF16, fp16 for PX_F32); px_f16 weight parameters
+ *                  (they multiply an fp16 intermediate) take fp16 always.  LayerNorm scale/offset fp32.
  *   - mask         fp32 [N][N] (1 = keep, 0 = masked) or NULL for all ones.
  *   - ld           px_ld(N): N rounded up to a multiple of 8; row stride (in elements) of the
  *                  intermediate tensors so that every row starts on a 16-byte boundary.
@@ -50,6 +56,12 @@ extern "C" {
 #define PX_F16 2
 
 typedef uint16_t px_bf16; /* storage of one bfloat16 */
+typedef uint16_t px_f16;  /* storage of one IEEE half */
+typedef uint16_t px_w16;  /* a weight element: bfloat16 when z_dtype is PX_BF16, half when it is PX_F32 */
+
+/* The contraction stores x = PX_TRIMUL_X_SCALE * sum_k a b, so that sums over thousands of k stay inside the fp16
+ * range; the output stage normalises x with eps * PX_TRIMUL_X_SCALE^2, which is LayerNorm of the unscaled x. */
+#define PX_TRIMUL_X_SCALE 0.015625f
 
 #if defined(__GNUC__)
 #define PX_API __attribute__((visibility("default")))
@@ -83,14 +95,14 @@ PX_API int32_t px_layer_norm_fwd(const void* x, const void* gamma, const void* b
  * (a[c][i][k] holds the reference's a[k][i][c]) so that stage 2 is the same product for both.
  * Replaces protenix/model/triangular/triangular.py:535-543. */
 PX_API int32_t px_trimul_in_proj(const void* z, int32_t z_dtype, const float* mask, const float* ln_w, const float* ln_b,
-                          const px_bf16* w_ap, const px_bf16* w_ag, const px_bf16* w_bp, const px_bf16* w_bg,
-                          px_bf16* a, px_bf16* b, int64_t n_u, int64_t n_t, int64_t ld, int32_t incoming, float eps,
+                          const px_w16* w_ap, const px_w16* w_ag, const px_w16* w_bp, const px_w16* w_bg,
+                          px_f16* a, px_f16* b, int64_t n_u, int64_t n_t, int64_t ld, int32_t incoming, float eps,
                           void* stream);
-/* Stage 2: x[c][i][j] = sum_k a[c][i][k] * b[c][j][k] for the 128 channels (bf16 in, fp32
- * accumulate, bf16 out, row stride ld) on the tcgen05 tensor cores: persistent kernel, TMA-fed
+/* Stage 2: x[c][i][j] = PX_TRIMUL_X_SCALE * sum_k a[c][i][k] * b[c][j][k] for the 128 channels (fp16 in, fp32
+ * accumulate, fp16 out, row stride ld) on the tcgen05 tensor cores: persistent kernel, TMA-fed
  * 128x256x64 tiles, fp32 accumulators in tensor memory, double-buffered epilogue.  a, b, x must be
  * 16-byte aligned.  Replaces _combine_projections, protenix/model/triangular/triangular.py:123-150. */
-PX_API int32_t px_trimul_contract(const px_bf16* a, const px_bf16* b, px_bf16* x, int64_t channels, int64_t n, int64_t ld,
+PX_API int32_t px_trimul_contract(const px_f16* a, const px_f16* b, px_f16* x, int64_t channels, int64_t n, int64_t ld,
                            void* stream);
 /* Device-side waits are bounded: a kernel whose wait runs out records a flag, stops issuing work, frees what it
  * holds and returns; kernels launched while a flag is set return without working.  The call synchronises the
@@ -121,9 +133,9 @@ PX_API int32_t px_set_wait_limit_cycles(int64_t cycles);
 PX_API int32_t px_selftest_wait_timeout(uint32_t* out_word, void* stream);
 /* Stage 3: z_out = [z_in +] W_z LN_out(x) * sigmoid(W_g LN_in(z_in)).  z_out may alias z_in.
  * Replaces protenix/model/triangular/triangular.py:559-565. */
-PX_API int32_t px_trimul_out(const px_bf16* x, const void* z_in, void* z_out, int32_t z_dtype, const float* ln_in_w,
-                      const float* ln_in_b, const float* ln_out_w, const float* ln_out_b, const px_bf16* w_z,
-                      const px_bf16* w_g, int64_t n_i, int64_t n_j, int64_t ld, int32_t add_residual, float eps,
+PX_API int32_t px_trimul_out(const px_f16* x, const void* z_in, void* z_out, int32_t z_dtype, const float* ln_in_w,
+                      const float* ln_in_b, const float* ln_out_w, const float* ln_out_b, const px_f16* w_z,
+                      const px_w16* w_g, int64_t n_i, int64_t n_j, int64_t ld, int32_t add_residual, float eps,
                       void* stream);
 /* Bytes of workspace px_triangle_multiplication needs for N tokens (a, b and x). */
 PX_API int64_t px_trimul_workspace_bytes(int64_t n);
@@ -132,8 +144,8 @@ PX_API int64_t px_trimul_workspace_bytes(int64_t n);
  * :28-90 the reference can dispatch to). */
 PX_API int32_t px_triangle_multiplication(const void* z_in, void* z_out, int32_t z_dtype, const float* mask,
                                    const float* ln_in_w, const float* ln_in_b, const float* ln_out_w,
-                                   const float* ln_out_b, const px_bf16* w_ap, const px_bf16* w_ag,
-                                   const px_bf16* w_bp, const px_bf16* w_bg, const px_bf16* w_z, const px_bf16* w_g,
+                                   const float* ln_out_b, const px_w16* w_ap, const px_w16* w_ag,
+                                   const px_w16* w_bp, const px_w16* w_bg, const px_f16* w_z, const px_w16* w_g,
                                    void* workspace, int64_t workspace_bytes, int64_t n, int32_t incoming,
                                    int32_t add_residual, float eps, void* stream);
 
@@ -152,15 +164,15 @@ PX_API int32_t px_triangle_multiplication(const void* z_in, void* z_out, int32_t
  * This entry point has no counterpart in the reference. */
 PX_API int32_t px_triangle_multiplication_static(const void* z_in, void* z_out, int32_t z_dtype, const float* mask,
                                           const float* ln_in_w, const float* ln_in_b, const float* ln_out_w,
-                                          const float* ln_out_b, const px_bf16* w_ap, const px_bf16* w_ag,
-                                          const px_bf16* w_bp, const px_bf16* w_bg, const px_bf16* w_z,
-                                          const px_bf16* w_g, int64_t n, int32_t incoming, int32_t add_residual,
+                                          const float* ln_out_b, const px_w16* w_ap, const px_w16* w_ag,
+                                          const px_w16* w_bp, const px_w16* w_bg, const px_f16* w_z,
+                                          const px_w16* w_g, int64_t n, int32_t incoming, int32_t add_residual,
                                           float eps, void* stream);
 /* PX_STATIC_MAX_N as seen by the loaded library. */
 PX_API int64_t px_static_max_n(void);
 
 /* ---- Triangle attention (starting / ending node), 4 heads x 32 -------------------------
- * Stage 1: xn = LN(z); q,k,v = W xn written per attended row u as [u][h][t][32] bf16 (v transposed: [u][h][32][ld(n_t)]) with q
+ * Stage 1: xn = LN(z); q,k,v = W xn written per attended row u as [u][h][t][32] fp16 (v transposed: [u][h][32][ld(n_t)]) with q
  * pre-scaled by log2(e)/sqrt(32); bias[h][u][t] = log2(e) * (W_b xn)[u][t][h] (fp32, row
  * stride ldm = px_ld_mask(N), zero in the pad columns); mask_bias[u][t] = log2(e) * inf *
  * (mask - 1) (fp32, row stride ldm, -infinity in the pad columns).  For the
@@ -168,8 +180,8 @@ PX_API int64_t px_static_max_n(void);
  * reference obtains by transposing z (protenix/model/modules/pairformer.py:160-168).
  * Replaces protenix/model/triangular/triangular.py:683-692 and layers.py:361-382. */
 PX_API int32_t px_triatt_in_proj(const void* z, int32_t z_dtype, const float* mask, const float* ln_w, const float* ln_b,
-                          const px_bf16* w_q, const px_bf16* w_k, const px_bf16* w_v, const px_bf16* w_bias,
-                          px_bf16* q, px_bf16* k, px_bf16* v, float* bias, float* mask_bias, int64_t n_u, int64_t n_t,
+                          const px_w16* w_q, const px_w16* w_k, const px_w16* w_v, const px_w16* w_bias,
+                          px_f16* q, px_f16* k, px_f16* v, float* bias, float* mask_bias, int64_t n_u, int64_t n_t,
                           int64_t ldm, int32_t ending, float eps, float inf, void* stream);
 /* Stage 2: o[u][t][h*32+d] = softmax_k(q.k + bias[h][t][k] + mask_bias[u][k]) v on the tcgen05
  * tensor cores: TMA-fed, logits and probabilities live in tensor memory only, online softmax in
@@ -178,46 +190,47 @@ PX_API int32_t px_triatt_in_proj(const void* z, int32_t z_dtype, const float* ma
  * Replaces the back-ends selected in protenix/model/triangular/layers.py:441-469 (_attention
  * :276-296, the Triton kernel protenix/model/tri_attention/forward.py:22-188, DS4Sci and
  * cuEquivariance calls). */
-PX_API int32_t px_triatt_flash(const px_bf16* q, const px_bf16* k, const px_bf16* v, const float* bias,
-                        const float* mask_bias, px_bf16* o, void* scratch, int64_t n_u, int64_t n, int64_t ldm,
+PX_API int32_t px_triatt_flash(const px_f16* q, const px_f16* k, const px_f16* v, const float* bias,
+                        const float* mask_bias, px_f16* o, void* scratch, int64_t n_u, int64_t n, int64_t ldm,
                         void* stream);
 PX_API int64_t px_triatt_flash_scratch_bytes(int64_t n_u, int64_t n);
 /* Stage 3: z_out(u,t) = [z_in(u,t) +] W_o (o[u][t] * sigmoid(W_g LN(z_in(u,t)))), where (u,t)
  * addresses z[u][t] (starting) or z[t][u] (ending).  z_out may alias z_in.
  * Replaces Attention._wrap_up, protenix/model/triangular/layers.py:384-398. */
-PX_API int32_t px_triatt_out(const px_bf16* o, const void* z_in, void* z_out, int32_t z_dtype, const float* ln_w,
-                      const float* ln_b, const px_bf16* w_g, const px_bf16* w_o, int64_t n_u, int64_t n_t, int32_t ending,
+PX_API int32_t px_triatt_out(const px_f16* o, const void* z_in, void* z_out, int32_t z_dtype, const float* ln_w,
+                      const float* ln_b, const px_w16* w_g, const px_f16* w_o, int64_t n_u, int64_t n_t, int32_t ending,
                       int32_t add_residual, float eps, void* stream);
 PX_API int64_t px_triatt_workspace_bytes(int64_t n);
 /* The three stages in sequence.  Stands in for TriangleAttention.forward,
  * protenix/model/triangular/triangular.py:657-715. */
 PX_API int32_t px_triangle_attention(const void* z_in, void* z_out, int32_t z_dtype, const float* mask, const float* ln_w,
-                              const float* ln_b, const px_bf16* w_bias, const px_bf16* w_q, const px_bf16* w_k,
-                              const px_bf16* w_v, const px_bf16* w_g, const px_bf16* w_o, void* workspace,
+                              const float* ln_b, const px_w16* w_bias, const px_w16* w_q, const px_w16* w_k,
+                              const px_w16* w_v, const px_w16* w_g, const px_f16* w_o, void* workspace,
                               int64_t workspace_bytes, int64_t n, int32_t ending, int32_t add_residual, float eps,
                               float inf, void* stream);
 
 /* ---- Transition (SwiGLU), c = 128, expansion 4 -------------------------------------------
  * x_out = [x_in +] W_o( silu(W_a LN(x_in)) * (W_b LN(x_in)) ) over rows of 128 channels; the
- * [rows][512] intermediates stay on chip.  x_out may alias x_in.
+ * [rows][512] intermediates stay on chip.  x_out may alias x_in.  The rows pass through registers for the LayerNorm
+ * whatever their storage type, so both products take fp16 operands and the three weights are fp16 always.
  * Replaces Transition.forward, protenix/model/modules/primitives.py:190-230. */
 PX_API int32_t px_transition(const void* x_in, void* x_out, int32_t dtype, const float* ln_w, const float* ln_b,
-                      const px_bf16* w_a, const px_bf16* w_b, const px_bf16* w_o, int64_t rows, int32_t add_residual,
+                      const px_f16* w_a, const px_f16* w_b, const px_f16* w_o, int64_t rows, int32_t add_residual,
                       float eps, void* stream);
 
 /* ---- Pair bias for the single-representation attention ----------------------------------
  * out[h][row] = (W LN(z[row]))[h] for h < n_heads (<= 16), fp32; ln_b may be NULL.
  * Replaces protenix/model/modules/transformer.py:185-188. */
-PX_API int32_t px_pair_bias_proj(const void* z, int32_t z_dtype, const float* ln_w, const float* ln_b, const px_bf16* w,
+PX_API int32_t px_pair_bias_proj(const void* z, int32_t z_dtype, const float* ln_w, const float* ln_b, const px_w16* w,
                           float* out, int64_t rows, int32_t n_heads, float eps, void* stream);
 
 /* ---- Recycling update of the pair representation ------------------------------------------
- * out[row] = z_init[row] + W LN(z[row]) for `rows` rows of 128 channels (W [128][128] bf16,
+ * out[row] = z_init[row] + W LN(z[row]) for `rows` rows of 128 channels (W [128][128] in the format of z,
  * z, z_init and out of one dtype, PX_BF16 or PX_F32); ln_b may be NULL; out may be z or z_init.
  * Replaces protenix/model/protenix.py:246
  * (z = z_init + linear_no_bias_z_cycle(layernorm_z_cycle(z))). */
 PX_API int32_t px_recycle_update(const void* z, const void* z_init, void* out, int32_t z_dtype, const float* ln_w,
-                          const float* ln_b, const px_bf16* w, int64_t rows, float eps, void* stream);
+                          const float* ln_b, const px_w16* w, int64_t rows, float eps, void* stream);
 
 /* ---- Exchange between the GPUs of one box (row-sharded path) ------------------------------
  * No counterpart in the reference (which runs the Pairformer on one GPU).  A peer buffer is a

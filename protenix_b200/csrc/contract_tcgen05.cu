@@ -1,5 +1,7 @@
 // Triangle-multiplication contraction on the 5th-generation tensor cores:
-//   x[c][i][j] = sum_k a[c][i][k] * b[c][j][k]      (128 channels, bf16 in, fp32 accumulate, bf16 out)
+//   x[c][i][j] = 2^-6 sum_k a[c][i][k] * b[c][j][k]      (fp16 in, fp32 accumulate, fp16 out)
+// The LayerNorm that consumes x does not see a common factor (its epsilon is scaled to match), and the factor 2^-6
+// keeps sums over thousands of k inside the fp16 range.
 //
 // Persistent kernel, one CTA per SM, 192 threads:
 //   warp 0      TMA producer: A tile [128 i][64 k] and B tile [256 j][64 k] per k-block, 128-byte swizzle,
@@ -8,7 +10,7 @@
 //               tcgen05.commit releases the shared-memory stage and, after the last k-block, publishes
 //               the accumulator
 //   warps 2..5  epilogue: tcgen05.ld of the fp32 accumulator (each warp its own 32 TMEM lanes = 32 rows),
-//               convert to bf16, 16-byte stores
+//               scale, convert to fp16, 16-byte stores
 // The accumulator is double-buffered in TMEM (2 x 256 columns) so the epilogue of tile t overlaps the
 // main loop of tile t+1.  Ragged edges need no predicates on the load side: the TMA zero-fills rows
 // >= N and k >= ld.  Tiles are ordered channel-major so that a channel's operands (2 * N * ld * 2
@@ -110,7 +112,7 @@ trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
           const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sa + kTcABytes);
 #pragma unroll
           for (int k = 0; k < kTcBK / 16; ++k)  // 16 bf16 = 32 bytes = 2 units of the start-address field
-            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, umma_idesc_bf16(kTcBM, kTcBN), (kt | k) ? 1u : 0u);
+            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, umma_idesc_f16(kTcBM, kTcBN), (kt | k) ? 1u : 0u);
           umma_commit(&bars.empty[s]);
         }
         if (!ok) break;
@@ -142,10 +144,11 @@ trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             const int j = j0 + cc * 32 + v * 8;
             if (j < ld) {
               uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-              o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-              o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-              o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+              constexpr float sc = PX_TRIMUL_X_SCALE;
+              o.x = pack_f16x2(sc * __uint_as_float(r[8 * v + 0]), sc * __uint_as_float(r[8 * v + 1]));
+              o.y = pack_f16x2(sc * __uint_as_float(r[8 * v + 2]), sc * __uint_as_float(r[8 * v + 3]));
+              o.z = pack_f16x2(sc * __uint_as_float(r[8 * v + 4]), sc * __uint_as_float(r[8 * v + 5]));
+              o.w = pack_f16x2(sc * __uint_as_float(r[8 * v + 6]), sc * __uint_as_float(r[8 * v + 7]));
               *reinterpret_cast<uint4*>(xrow + j) = o;
             }
           }
@@ -169,7 +172,7 @@ trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 // [channels][n rows][ld k] bf16 tensor, box = [1][box_rows][64], 128-byte swizzle, zero fill outside.
 static bool make_operand_map(CUtensorMap* map, const void* base, int64_t channels, int64_t n, int64_t ld,
                              uint32_t box_rows) {
-  return make_map_3d(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, (uint64_t)ld, (uint64_t)n, (uint64_t)channels,
+  return make_map_3d(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, base, (uint64_t)ld, (uint64_t)n, (uint64_t)channels,
                      (uint64_t)ld * 2, (uint64_t)n * ld * 2, kTcBK, box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 

@@ -2,6 +2,9 @@
 //
 //   o[u][q][h*32+d] = softmax_k( q[u,h,q,:] . k[u,h,k,:] + bias[h][q][k] + mask_bias[u][k] ) v[u,h,k,d]
 //
+// q, k, v and o are fp16 (projections of standardised rows and convex combinations of them: far inside its range;
+// fp16 keeps three more bits than bf16), the pair bias, the logits, the softmax and the accumulators fp32.
+//
 // One CTA = (head h, 128 queries, 6 attended rows u), 16 warps:
 //   warps 0..11   three softmax groups of four warps; group g owns rows u0+2g, u0+2g+1, each thread one query row.
 //                 The kernel is bound by the latency of a group's chain (wait S, load, add, reduce, exponentials,
@@ -12,18 +15,21 @@
 //                 one issuing thread for all groups would be the bottleneck).  It loads the group's Q tiles once
 //                 and, per work item, a K tile [64 keys][32] (64-byte swizzle) and a transposed V tile
 //                 [32 d][64 keys] (128-byte swizzle) into the group's 4-stage ring; issues S = Q K^T (M=128, N=64,
-//                 K=32) into the group's S buffer in tensor memory; and, once the group has written P (bf16) into
+//                 K=32) into the group's S buffer in tensor memory; and, once the group has written P (fp16) into
 //                 its P buffer, issues O_u += P V with P as the TMEM-resident A operand (M=128, N=32, K=64).  S of
 //                 the next item is issued as soon as the group has pulled the current S into registers, so it is
-//                 ready when the group comes back.  The control thread of group 0 also loads the pair-bias tile
-//                 [128 q][64 k] fp32 (two 128-byte-swizzled boxes, 2-deep ring).
-//   warp 15       idle (completes the control warpgroup)
-// Tensor memory: S (3 x 64) | P (3 x 32, two bf16 per column) | O (6 x 32).
+//                 ready when the group comes back.
+//   warp 15       one thread loads the pair-bias tiles [128 q][64 k] fp32 (two 128-byte-swizzled boxes, 2-deep ring).
+// Tensor memory: S (3 x 64) | P (3 x 32, two fp16 per column) | O (6 x 32).
+//
+// Letting the tensor core add the bias (S += I B with an identity operand and the bias tile as an MN-major fp16
+// operand: eight more MMAs per item) was measured and lost: 7.8 ms against 6.3 ms at N=1536.  The 48 instructions
+// it takes off every softmax thread weigh less than the ten MMA issues it puts on the group's control thread.
 //
 // Softmax is online in base 2 with a lazy reference maximum: the reference only moves (and O_u is rescaled
 // through TMEM) when the tile maximum exceeds it by more than 8, so probabilities stay below 2^8.
 // Exponentials are fp32 (three pairs in four by ex2, the fourth by a cubic on the FMA pipe); P is their rounding to
-// bf16, the denominators sum the fp32 values.  Every mbarrier wait is bounded.
+// fp16, the denominators sum the fp32 values.  Every mbarrier wait is bounded.
 #include <math_constants.h>
 
 #include "px_tcgen05.cuh"
@@ -36,10 +42,10 @@ constexpr int kFRpg = 2;                  // attended rows per group
 constexpr int kFRows = kFGroups * kFRpg;  // attended rows per CTA
 constexpr int kFKT = 64;                  // keys per work item
 constexpr int kFStages = 4;               // K/V ring of each group (work items = (key tile, row))
-constexpr int kFQBytes = 128 * 64;        // [128][32] bf16
-constexpr int kFKBytes = kFKT * 64;       // [64][32] bf16
+constexpr int kFQBytes = 128 * 64;        // [128][32] fp16
+constexpr int kFKBytes = kFKT * 64;       // [64][32] fp16
 constexpr int kFVBox = 32 * 128;          // the TMA box of the value tile: 32 rows x 64 keys
-constexpr int kFVBytes = 32 * 128;        // [32 d][64 keys] bf16
+constexpr int kFVBytes = 32 * 128;        // [32 d][64 keys] fp16
 constexpr int kFStageBytes = kFKBytes + kFVBytes;
 constexpr int kFBiasBytes = 128 * kFKT * 4;
 constexpr int kFON = 32;                  // columns of an O accumulator
@@ -135,8 +141,18 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // ------------------------------------------------------------------ control thread of group g
     asm volatile("setmaxnreg.dec.sync.aligned.u32 24;\n");   // registers go to the softmax warpgroups
     const int g = warp - 4 * kFGroups;
-    if (g < kFGroups && lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc_bf16(128, kFKT), idesc_o = umma_idesc_bf16(128, kFON);
+    if (g == kFGroups && lane == 0) {
+      // ---------------------------------------------------------------- pair-bias loader (all six rows share a tile)
+      for (int kt = 0; kt < nkt; ++kt) {
+        const int b = kt & 1;
+        if (!mbar_wait(&bars.bias_empty[b], ((kt >> 1) & 1) ^ 1, 1u)) break;
+        mbar_expect_tx(&bars.bias_full[b], kFBiasBytes);
+        for (int c = 0; c < kFKT / 32; ++c)
+          tma_load_3d(smem_u32(sm + FlashLayout::bias + b * kFBiasBytes + c * (128 * 128)), &map_b, &bars.bias_full[b],
+                      kt * kFKT + c * 32, q0, h);
+      }
+    } else if (g < kFGroups && lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_f16(128, kFKT), idesc_o = umma_idesc_f16(128, kFON);
       const int n_items = nkt * kFRpg;              // work item i = (key tile i / 3, row i % 3 of the group)
       const uint32_t q_addr = smem_u32(sm + FlashLayout::q + g * kFRpg * kFQBytes);
       const uint32_t ring = smem_u32(sm + FlashLayout::kv + g * kFStages * kFStageBytes);
@@ -150,15 +166,6 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tma_load_3d(ring + s * kFStageBytes, &map_k, &bars.kv_full[g][s], 0, kt * kFKT, uh);
         tma_load_3d(ring + s * kFStageBytes + kFKBytes, &map_v, &bars.kv_full[g][s], kt * kFKT, 0, uh);
       };
-      auto load_bias = [&](int kt) {                // group 0 only: the bias tile all rows share
-        const int b = kt & 1;
-        if (!mbar_wait(&bars.bias_empty[b], ((kt >> 1) & 1) ^ 1, 1u)) return false;
-        mbar_expect_tx(&bars.bias_full[b], kFBiasBytes);
-        for (int c = 0; c < kFKT / 32; ++c)
-          tma_load_3d(smem_u32(sm + FlashLayout::bias + b * kFBiasBytes + c * (128 * 128)), &map_b, &bars.bias_full[b],
-                      kt * kFKT + c * 32, q0, h);
-        return true;
-      };
       auto issue_s = [&](int i) {                   // S(i) = Q_r K^T
         const int s = i % kFStages;
         if (!mbar_wait(&bars.kv_full[g][s], (i / kFStages) & 1, 8u)) return false;
@@ -171,10 +178,6 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       };
       mbar_expect_tx(&bars.q_full[g], kFRpg * kFQBytes);
       for (int r = 0; r < kFRpg; ++r) tma_load_3d(q_addr + r * kFQBytes, &map_q, &bars.q_full[g], 0, q0, uh0 + r * kFH);
-      if (g == 0) {
-        ok = load_bias(0);
-        if (ok && nkt > 1) ok = load_bias(1);
-      }
       for (int i = 0; i < kFStages - 1 && i < n_items; ++i) load_kv(i);   // first use of these stages
       ok = ok && mbar_wait(&bars.q_full[g], 0, 4u);
       ok = ok && issue_s(0);
@@ -189,8 +192,6 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (!ok) break;
           load_kv(i + kFStages - 1);
         }
-        if (g == 0 && r == 0 && kt >= 1 && kt + 1 < nkt) ok = load_bias(kt + 1);
-        if (!ok) break;
         ok = mbar_wait(&bars.p_ready[g], i & 1, 16u);
         if (!ok) break;
         tc_fence_after();
@@ -302,7 +303,7 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const float nm = -m_ref[r];
 #pragma unroll
           for (int e = 0; e < kFKT / 2; ++e) {
-            // fp32 exponentials; P is their rounding to nearest bf16 (one conversion per pair), which is unbiased,
+            // fp32 exponentials; P is their rounding to nearest fp16 (one conversion per pair), which is unbiased,
             // so the denominator can sum the fp32 values themselves.
             add2(s[2 * e], s[2 * e + 1], nm, nm);
             float p0, p1;
@@ -312,7 +313,7 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               p0 = fast_exp2(s[2 * e]);
               p1 = fast_exp2(s[2 * e + 1]);
             }
-            w[e] = pack_bf16x2(p0, p1);
+            w[e] = pack_f16x2(p0, p1);
             add2(l0, l1, p0, p1);
           }
         }
@@ -362,10 +363,10 @@ triatt_flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             uint4 pk;
-            pk.x = pack_bf16x2(__uint_as_float(a[8 * v + 0]) * inv, __uint_as_float(a[8 * v + 1]) * inv);
-            pk.y = pack_bf16x2(__uint_as_float(a[8 * v + 2]) * inv, __uint_as_float(a[8 * v + 3]) * inv);
-            pk.z = pack_bf16x2(__uint_as_float(a[8 * v + 4]) * inv, __uint_as_float(a[8 * v + 5]) * inv);
-            pk.w = pack_bf16x2(__uint_as_float(a[8 * v + 6]) * inv, __uint_as_float(a[8 * v + 7]) * inv);
+            pk.x = pack_f16x2(__uint_as_float(a[8 * v + 0]) * inv, __uint_as_float(a[8 * v + 1]) * inv);
+            pk.y = pack_f16x2(__uint_as_float(a[8 * v + 2]) * inv, __uint_as_float(a[8 * v + 3]) * inv);
+            pk.z = pack_f16x2(__uint_as_float(a[8 * v + 4]) * inv, __uint_as_float(a[8 * v + 5]) * inv);
+            pk.w = pack_f16x2(__uint_as_float(a[8 * v + 6]) * inv, __uint_as_float(a[8 * v + 7]) * inv);
             *reinterpret_cast<uint4*>(dst + 8 * v) = pk;
           }
         }
@@ -413,8 +414,8 @@ extern "C" int64_t px_triatt_flash_scratch_bytes(int64_t n_u, int64_t n) {
   return (n_u * ((((n + kFKT - 1) / kFKT) + 63) / 64) * 8 + 255) / 256 * 256;
 }
 
-extern "C" int32_t px_triatt_flash(const px_bf16* q, const px_bf16* k, const px_bf16* v, const float* bias,
-                                   const float* mask_bias, px_bf16* o, void* scratch, int64_t n_u, int64_t n,
+extern "C" int32_t px_triatt_flash(const px_f16* q, const px_f16* k, const px_f16* v, const float* bias,
+                                   const float* mask_bias, px_f16* o, void* scratch, int64_t n_u, int64_t n,
                                    int64_t ldm, void* stream) {
   if (!q || !k || !v || !bias || !mask_bias || !o || !scratch || n_u <= 0 || n <= 0 || n_u > 32768 || n > 32768 ||
       ldm != px_ld_mask(n))
@@ -425,13 +426,13 @@ extern "C" int32_t px_triatt_flash(const px_bf16* q, const px_bf16* k, const px_
   const int nkt = (int)((n + kFKT - 1) / kFKT);
   CUtensorMap mq, mk, mv, mbias;
   const uint64_t uh = (uint64_t)n_u * kFH;
-  // q, k: [n_u*4][n][32] bf16, box [1][128][32], 64-byte swizzle
-  if (!make_map_3d(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, q, kFD, (uint64_t)n, uh, kFD * 2, (uint64_t)n * kFD * 2, kFD,
+  // q, k: [n_u*4][n][32] fp16, box [1][128][32], 64-byte swizzle
+  if (!make_map_3d(&mq, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, q, kFD, (uint64_t)n, uh, kFD * 2, (uint64_t)n * kFD * 2, kFD,
                    128, CU_TENSOR_MAP_SWIZZLE_64B) ||
-      !make_map_3d(&mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, k, kFD, (uint64_t)n, uh, kFD * 2, (uint64_t)n * kFD * 2, kFD,
+      !make_map_3d(&mk, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, k, kFD, (uint64_t)n, uh, kFD * 2, (uint64_t)n * kFD * 2, kFD,
                    kFKT, CU_TENSOR_MAP_SWIZZLE_64B) ||
-      // v (transposed): [n_u*4][32][n keys, row stride ldt] bf16, box [1][32][64], 128-byte swizzle
-      !make_map_3d(&mv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, v, (uint64_t)n, kFD, uh, (uint64_t)ldt * 2,
+      // v (transposed): [n_u*4][32][n keys, row stride ldt] fp16, box [1][32][64], 128-byte swizzle
+      !make_map_3d(&mv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, v, (uint64_t)n, kFD, uh, (uint64_t)ldt * 2,
                    (uint64_t)kFD * ldt * 2, 64, kFD, CU_TENSOR_MAP_SWIZZLE_128B) ||
       // pair bias: [4][n q][n k, row stride ldm] fp32, box [1][128][32], 128-byte swizzle
       !make_map_3d(&mbias, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, bias, (uint64_t)n, (uint64_t)n, kFH, (uint64_t)ldm * 4,

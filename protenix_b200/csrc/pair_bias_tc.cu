@@ -44,6 +44,7 @@ pair_bias_tc_kernel(const __grid_constant__ CUtensorMap map_z, const Tz* __restr
                     const float* __restrict__ ln_b, const bf16* __restrict__ w, float* __restrict__ out, long long rows,
                     int n_heads, float eps, int n_tiles) {
   constexpr bool kTma = sizeof(Tz) == 2;
+  constexpr bool kF16 = !kTma;                           // fp32 rows are multiplied as fp16 against fp16 weights
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   PbBars& bars = *reinterpret_cast<PbBars*>(sm + PbLayout::bars);
@@ -74,7 +75,7 @@ pair_bias_tc_kernel(const __grid_constant__ CUtensorMap map_z, const Tz* __restr
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   {
-    fold_weight_rows(sm + PbLayout::w, sm + PbLayout::wx, 0, kPbWPanel, w, 0, n_heads, ln_w, ln_b ? ln_b : g_zero_beta, 1.0f,
+    fold_weight_rows<kF16, kF16>(sm + PbLayout::w, sm + PbLayout::wx, 0, kPbWPanel, w, 0, n_heads, ln_w, ln_b ? ln_b : g_zero_beta, 1.0f,
                      warp, kPbWarps, lane);
     // operand and correction rows of the heads that do not exist
     for (int i = threadIdx.x; i < (16 - n_heads) * 18; i += kPbThreads) {
@@ -83,7 +84,7 @@ pair_bias_tc_kernel(const __grid_constant__ CUtensorMap map_z, const Tz* __restr
                                       : sm + PbLayout::wx + r * 32 + (piece - 16) * 16;
       *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
     }
-    tile_write_ones(ctx.tiles, threadIdx.x, kPbThreads);
+    tile_write_ones<kF16>(ctx.tiles, threadIdx.x, kPbThreads);
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
   tc_fence_before();
@@ -97,9 +98,9 @@ pair_bias_tc_kernel(const __grid_constant__ CUtensorMap map_z, const Tz* __restr
         if (kTma) tile_producer_loop(ctx, &map_z);
       } else if (warp == 9) {
         tile_product_loop(ctx, tmem_base, smem_u32(sm + PbLayout::w), kPbWPanel, smem_u32(sm + PbLayout::wx),
-                          umma_idesc_bf16(128, 16), &bars.acc_full, &bars.acc_free);
+                          umma_idesc_16(128, 16, kF16, kF16), &bars.acc_full, &bars.acc_free);
       } else if (warp == 10) {
-        tile_gram_loop(ctx, tmem_base + kPbColGram);
+        tile_gram_loop<kF16>(ctx, tmem_base + kPbColGram);
       }
     }
   } else if (warp >= 4) {

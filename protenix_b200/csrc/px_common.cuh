@@ -1,6 +1,7 @@
 // Shared device helpers for the sm_100a Pairformer kernels.
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -21,10 +22,41 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// Two fp32 -> one f16x2 word (round to nearest; values beyond the fp16 range saturate to +-65504 instead of inf).
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;\n" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ float2 unpack_f16x2(uint32_t u) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&u));
+}
+// The two 16-bit operand formats of the tensor-core kernels: bf16 (kF16 = false) and fp16 (kF16 = true).
+template <bool kF16>
+__device__ __forceinline__ uint32_t pack16x2(float lo, float hi) {
+  return kF16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
+}
+template <bool kF16>
+__device__ __forceinline__ float2 unpack16x2(uint32_t u);
+template <>
+__device__ __forceinline__ float2 unpack16x2<true>(uint32_t u) {
+  return unpack_f16x2(u);
+}
 // bf16 -> fp32 is a 16-bit shift: spelled out so that it runs on the integer pipe, not the conversion unit
 __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
   return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
 }
+
+template <>
+__device__ __forceinline__ float2 unpack16x2<false>(uint32_t u) {
+  return unpack_bf16x2(u);
+}
+template <bool kF16>
+__device__ __forceinline__ uint16_t round16(float v) {
+  return kF16 ? __half_as_ushort(__float2half_rn(v)) : __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+// (1, 1) as a pair of bf16 or of fp16
+__host__ __device__ constexpr uint32_t ones16x2(bool f16) { return f16 ? 0x3C003C00u : 0x3F803F80u; }
 
 // Packed fp32 arithmetic (sm_100): two elements per issue slot.  Pays where the issue slots are the scarce resource
 // (flash attention: -7 %); the SwiGLU of the transition kernel got 22 % slower with it and stays scalar.

@@ -1,12 +1,17 @@
 // Pieces shared by the persistent, TMA-fed row kernels (LayerNorm'd 128-channel rows times resident weights).
 //
+// Operand formats.  Rows stored as bf16 are multiplied as they are, against bf16 weights.  Rows stored as fp32 are
+// standardised and rounded to fp16 (a standardised row lies within +-sqrt(128), so fp16's range is safe and its three
+// extra mantissa bits cut the operand rounding error eightfold), against fp16 weights.  `kF16` names the format of a
+// product's operands; the correction step below is a separate MMA and always takes bf16 head/tail pairs.
+//
 // LayerNorm is not applied to the operand.  With W' = W diag(gamma), s = W' 1, t = W beta and std = 1/rstd,
 //     W LN(x) = rstd * ( W' x - mean * s + std * t ),
 // so the tensor core multiplies the rows exactly as they are stored (bf16 rows go from global memory to the swizzled
 // operand by TMA without passing through registers).  The two correction terms ride along as one extra K step of 16:
 // the row side holds (-mean, std) and the weight side (s, t), each split into a bf16 head and tail so that the
 // products carry about 17 bits.  What is left for the epilogue is one multiplication by the row's rstd.
-// Rows stored as fp32 are standardised ((x - mean) * rstd) while they are converted, and then carry mean 0, std 1.
+// Rows stored as fp32 are standardised ((x - mean) * rstd) while they are converted to fp16, and then carry mean 0, std 1.
 #pragma once
 #include "px_tcgen05.cuh"
 
@@ -62,27 +67,39 @@ __device__ __forceinline__ void write_correction_row(unsigned char* panel, int r
 // Rounds to bf16 and stores two bytes.
 __device__ __forceinline__ void store_bf16_int(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-// Folds gamma (and `scale`) into rows [row_begin, row_begin + count) of a [*][128] bf16 weight and writes them as rows
-// dst_row0.. of a K-major swizzled operand with `panel_bytes` per 64-wide k panel; the matching rows of the
-// correction panel `extra` receive (s, t): s = sum_c W'[row][c] over the rounded values,
-// t = scale * sum_c W[row][c] * beta[c].  Warp-per-row; called by `nwarps` warps with consecutive `warp` numbers.
+// 16-bit weight values -> fp32 (`kF16`: the weights are fp16, otherwise bf16).
+template <bool kF16>
+__device__ __forceinline__ float4 load4_w16(const uint16_t* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const float2 a = unpack16x2<kF16>(u.x), b = unpack16x2<kF16>(u.y);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
+// Folds gamma (and `scale`) into rows [row_begin, row_begin + count) of a [*][128] 16-bit weight (format kInF16) and
+// writes them in the operand format kOutF16 as rows dst_row0.. of a K-major swizzled operand with `panel_bytes` per
+// 64-wide k panel; the matching rows of the correction panel `extra` receive (s, t): s = sum_c W'[row][c] over the
+// rounded values, t = scale * sum_c W[row][c] * beta[c].  Warp-per-row; called by `nwarps` warps with consecutive
+// `warp` numbers.  gamma == nullptr: no LayerNorm to fold (plain copy with `scale`, no correction row).
+template <bool kInF16, bool kOutF16>
 __device__ __forceinline__ void fold_weight_rows(unsigned char* dst, unsigned char* extra, int dst_row0, int panel_bytes,
                                                  const bf16* __restrict__ W, int row_begin, int count,
                                                  const float* __restrict__ gamma, const float* __restrict__ beta,
                                                  float scale, int warp, int nwarps, int lane, int khalf = 0) {
-  const float4 g4 = *reinterpret_cast<const float4*>(gamma + 4 * lane);
-  const float4 b4 = *reinterpret_cast<const float4*>(beta + 4 * lane);
+  const float4 g4 = gamma ? *reinterpret_cast<const float4*>(gamma + 4 * lane) : make_float4(1.f, 1.f, 1.f, 1.f);
+  const float4 b4 = gamma ? *reinterpret_cast<const float4*>(beta + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 2
   for (int i = warp; i < count; i += nwarps) {
-    const float4 w = load4(W + (size_t)(row_begin + i) * kC + 4 * lane);
-    const uint32_t lo = pack_bf16x2(w.x * g4.x * scale, w.y * g4.y * scale);
-    const uint32_t hi = pack_bf16x2(w.z * g4.z * scale, w.w * g4.w * scale);
-    const float2 f0 = unpack_bf16x2(lo), f1 = unpack_bf16x2(hi);
-    const float s = warp_sum(f0.x + f0.y + f1.x + f1.y);
-    const float t = warp_sum(w.x * b4.x + w.y * b4.y + w.z * b4.z + w.w * b4.w) * scale;
+    const float4 w = load4_w16<kInF16>(reinterpret_cast<const uint16_t*>(W) + (size_t)(row_begin + i) * kC + 4 * lane);
+    const uint32_t lo = pack16x2<kOutF16>(w.x * g4.x * scale, w.y * g4.y * scale);
+    const uint32_t hi = pack16x2<kOutF16>(w.z * g4.z * scale, w.w * g4.w * scale);
     const int r = i + dst_row0;
     *reinterpret_cast<uint2*>(dst + operand_piece_offset(r, lane >> 1, panel_bytes) + (lane & 1) * 8) = make_uint2(lo, hi);
-    if (lane == 0) write_correction_row(extra, r, s, t, true, khalf);
+    if (gamma) {
+      const float2 f0 = unpack16x2<kOutF16>(lo), f1 = unpack16x2<kOutF16>(hi);
+      const float s = warp_sum(f0.x + f0.y + f1.x + f1.y);
+      const float t = warp_sum(w.x * b4.x + w.y * b4.y + w.z * b4.z + w.w * b4.w) * scale;
+      if (lane == 0) write_correction_row(extra, r, s, t, true, khalf);
+    }
   }
 }
 
@@ -156,41 +173,46 @@ __device__ __forceinline__ void row_stats_from_operand(const unsigned char* op, 
   rstd = rsqrtf(fmaxf(q * (1.0f / kC) - m * m, 0.f) + eps);
 }
 
-// One fp32 row from global memory (nullptr = a row of zeros) -> standardised bf16 row r of the operand at `op`;
-// one thread per row.  The row is read twice (the second pass hits L1/L2).
-__device__ __forceinline__ void standardise_row_to_operand(unsigned char* op, int r, const float* __restrict__ src,
-                                                           float eps, int panel_bytes = kPanelBytes) {
-  float mean = 0.f, rstd = 0.f;
-  if (src) {
-    float s = 0.f;
-#pragma unroll 8
-    for (int p = 0; p < 32; ++p) {
-      const float4 v = load4(src + 4 * p);
-      s += (v.x + v.y) + (v.z + v.w);
-    }
-    mean = s * (1.0f / kC);
-    float q = 0.f;
-#pragma unroll 8
-    for (int p = 0; p < 32; ++p) {
-      const float4 v = load4(src + 4 * p);
-      q = fmaf(v.x - mean, v.x - mean, q);
-      q = fmaf(v.y - mean, v.y - mean, q);
-      q = fmaf(v.z - mean, v.z - mean, q);
-      q = fmaf(v.w - mean, v.w - mean, q);
-    }
-    rstd = rsqrtf(q * (1.0f / kC) + eps);
+// Asks the L2 cache for 32 fp32 rows (512 bytes each) ahead of their use: one 128-byte line per lane and request,
+// four requests per warp.  The converting warps keep only four rows in flight in registers, which covers an L2 hit
+// but not a trip to HBM; with the next tile requested a whole tile period ahead the loads find their lines in L2.
+template <typename RowPtr>
+__device__ __forceinline__ void prefetch_rows_l2(int lane, RowPtr row_ptr) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int line = 32 * j + lane;
+    const float* src = row_ptr(line >> 2);
+    if (src) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(src + 32 * (line & 3)));
   }
-#pragma unroll 4
-  for (int p = 0; p < 16; ++p) {
-    uint4 o = make_uint4(0u, 0u, 0u, 0u);
-    if (src) {
-      const float4 v0 = load4(src + 8 * p), v1 = load4(src + 8 * p + 4);
-      o.x = pack_bf16x2((v0.x - mean) * rstd, (v0.y - mean) * rstd);
-      o.y = pack_bf16x2((v0.z - mean) * rstd, (v0.w - mean) * rstd);
-      o.z = pack_bf16x2((v1.x - mean) * rstd, (v1.y - mean) * rstd);
-      o.w = pack_bf16x2((v1.z - mean) * rstd, (v1.w - mean) * rstd);
+}
+
+// 32 fp32 rows from global memory -> standardised fp16 rows r0..r0+31 of the operand at `op`, by one warp: a row is
+// 512 contiguous bytes, so the warp reads it with one coalesced 16-byte load per lane, reduces mean and variance with
+// shuffles (two passes over the registers) and writes eight bytes per lane.  row_ptr(i) gives the address of row
+// r0 + i or nullptr for a row of zeros.  Four rows are in flight at a time to cover the load latency.
+template <typename RowPtr>
+__device__ __forceinline__ void standardise_rows_to_operand(unsigned char* op, int r0, int lane, float eps, int panel_bytes,
+                                                            RowPtr row_ptr) {
+#pragma unroll 1
+  for (int i0 = 0; i0 < 32; i0 += 4) {
+    float4 v[4];
+    bool have[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float* src = row_ptr(i0 + j);
+      have[j] = src != nullptr;
+      v[j] = have[j] ? __ldg(reinterpret_cast<const float4*>(src) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    *reinterpret_cast<uint4*>(op + operand_piece_offset(r, p, panel_bytes)) = o;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float mean = warp_sum((v[j].x + v[j].y) + (v[j].z + v[j].w)) * (1.0f / kC);
+      const float dx = v[j].x - mean, dy = v[j].y - mean, dz = v[j].z - mean, dw = v[j].w - mean;
+      const float var = warp_sum(fmaf(dx, dx, dy * dy) + fmaf(dz, dz, dw * dw)) * (1.0f / kC);
+      const float rstd = have[j] ? rsqrtf(var + eps) : 0.f;
+      const int r = r0 + i0 + j;
+      *reinterpret_cast<uint2*>(op + operand_piece_offset(r, lane >> 1, panel_bytes) + (lane & 1) * 8) =
+          make_uint2(pack_f16x2(dx * rstd, dy * rstd), pack_f16x2(dz * rstd, dw * rstd));
+    }
   }
 }
 
@@ -199,7 +221,8 @@ __device__ __forceinline__ void standardise_row_to_operand(unsigned char* op, in
 // A tile is 128 pair elements (one u, 128 consecutive t); element (u, t) is row u*n_t + t of z, or row t*n_u + u when
 // the two indices are exchanged (`swap`).  A stage of the ring holds the tile as two k panels of 144 rows (the
 // last 16 rows are ones, see below) and the tile's correction panel.
-//   * producer thread: TMA loads of bf16 rows (fp32 rows are converted by the statistics threads instead);
+//   * producer thread: TMA loads of bf16 rows (fp32 rows are standardised and converted to fp16 by the statistics
+//     warps instead, a warp per row);
 //   * statistics issuer thread: Z Z^T | Z 1 (M=128, N=144) into tensor memory: the diagonal holds each row's sum
 //     of squares and columns 128..143 its plain sum;
 //   * statistics threads (one per row): variance = E[x^2] - mean^2 in fp32 (accurate while |mean| is not orders of
@@ -236,11 +259,12 @@ __device__ __forceinline__ void tile_bars_init(TileBars& b, bool tma, int issuer
 }
 
 // The 16 rows of ones behind every tile panel (never overwritten: a tile load covers 128 rows).
+template <bool kF16>
 __device__ __forceinline__ void tile_write_ones(unsigned char* tiles, int tid, int nthreads) {
+  constexpr uint32_t one = ones16x2(kF16);
   for (int i = tid; i < kTileStages * 2 * 16 * 8; i += nthreads) {
     const int panel = i >> 7, piece = i & 127;
-    *reinterpret_cast<uint4*>(tiles + panel * kTilePanel + 128 * 128 + piece * 16) =
-        make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
+    *reinterpret_cast<uint4*>(tiles + panel * kTilePanel + 128 * 128 + piece * 16) = make_uint4(one, one, one, one);
   }
 }
 
@@ -259,8 +283,9 @@ __device__ __forceinline__ void tile_producer_loop(const TileCtx& c, const CUten
 }
 
 // One thread: the statistics product of every tile into tensor-memory columns [gram_col, gram_col + 144).
+template <bool kF16>
 __device__ __forceinline__ void tile_gram_loop(const TileCtx& c, uint32_t tmem_gram) {
-  constexpr uint32_t idesc_gram = umma_idesc_bf16(128, kGramCols);
+  constexpr uint32_t idesc_gram = umma_idesc_16(128, kGramCols, kF16, kF16);
   int k = 0;
   for (int tile = c.first_tile; tile < c.n_tiles; tile += c.tile_step, ++k) {
     const int s = k % kTileStages, n = k / kTileStages;
@@ -295,9 +320,17 @@ __device__ __forceinline__ void tile_stats_loop(const TileCtx& c, const Tz* __re
       ok = mbar_wait(&c.bars->a_empty[s], (n & 1) ^ 1, 16u);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      const size_t pair = c.swap ? ((size_t)t * c.n_u + u) : ((size_t)u * c.n_t + t);
-      standardise_row_to_operand(c.tiles + s * kTileBytes, r,
-                                 t < c.n_t ? reinterpret_cast<const float*>(z) + pair * kC : nullptr, eps, kTilePanel);
+      auto rows_of = [&](int tl) {                         // this warp's 32 rows of tile tl
+        const int uu = tl / c.tiles_t, t_first = (tl % c.tiles_t) * 128 + 32 * qw;
+        return [=](int i) -> const float* {
+          const int tt = t_first + i;
+          if (tt >= c.n_t) return nullptr;
+          const size_t pair = c.swap ? ((size_t)tt * c.n_u + uu) : ((size_t)uu * c.n_t + tt);
+          return reinterpret_cast<const float*>(z) + pair * kC;
+        };
+      };
+      if (tile + c.tile_step < c.n_tiles) prefetch_rows_l2(lane, rows_of(tile + c.tile_step));
+      standardise_rows_to_operand(c.tiles + s * kTileBytes, 32 * qw, lane, eps, kTilePanel, rows_of(tile));
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&c.bars->raw_full[s]);
@@ -332,6 +365,8 @@ __device__ __forceinline__ void tile_product_loop(const TileCtx& c, uint32_t d_t
                                                   uint32_t wx_addr, uint32_t idesc, uint64_t* acc_full,
                                                   uint64_t* acc_free) {
   const uint64_t wx_desc = umma_desc_sw32(wx_addr);
+  // the correction step multiplies bf16 head/tail pairs whatever the format of the main operands; M and N as `idesc`
+  const uint32_t idesc_corr = idesc | (1u << 7) | (1u << 10);
   int k = 0;
   for (int tile = c.first_tile; tile < c.n_tiles; tile += c.tile_step, ++k) {
     const int s = k % kTileStages, n = k / kTileStages;
@@ -344,7 +379,7 @@ __device__ __forceinline__ void tile_product_loop(const TileCtx& c, uint32_t d_t
                 umma_desc_sw128(w_addr + (ks >> 2) * w_panel) + 2 * (ks & 3), idesc, ks ? 1u : 0u);
     if (!mbar_wait(&c.bars->a_ready[s], n & 1, 4u)) break;   // the correction step needs the statistics
     tc_fence_after();
-    umma_bf16(d_tmem, umma_desc_sw32(smem_u32(c.extras + s * kTileExtra)), wx_desc, idesc, 1u);
+    umma_bf16(d_tmem, umma_desc_sw32(smem_u32(c.extras + s * kTileExtra)), wx_desc, idesc_corr, 1u);
     umma_commit(acc_full);
     umma_commit(&c.bars->a_empty[s]);                        // this thread's share of the reads of the stage
   }

@@ -103,7 +103,16 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, bool a_mn_m
   return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
-// D[tmem] (+)= A[smem] * B[smem]
+// The same for any pair of 16-bit operand formats (fp16 or bf16 per operand) and fp32 D.
+__host__ __device__ constexpr uint32_t umma_idesc_16(int m, int n, bool a_f16, bool b_f16, bool a_mn_major = false,
+                                                     bool b_mn_major = false) {
+  return (1u << 4) | ((a_f16 ? 0u : 1u) << 7) | ((b_f16 ? 0u : 1u) << 10) | ((a_mn_major ? 1u : 0u) << 15) |
+         ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n, bool a_mn_major = false, bool b_mn_major = false) {
+  return umma_idesc_16(m, n, true, true, a_mn_major, b_mn_major);
+}
+// D[tmem] (+)= A[smem] * B[smem]   (kind::f16 covers fp16 and bf16 operands; the instruction descriptor says which)
 __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                           uint32_t accumulate) {
   asm volatile(

@@ -49,6 +49,7 @@ recycle_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_consta
                   const float* __restrict__ ln_w, const float* __restrict__ ln_b, const bf16* __restrict__ w,
                   long long rows, float eps, int n_tiles) {
   constexpr bool kTma = sizeof(Tz) == 2;
+  constexpr bool kF16 = !kTma;                           // fp32 rows are multiplied as fp16 against fp16 weights
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   RcBars& bars = *reinterpret_cast<RcBars*>(sm + RcLayout::bars);
@@ -82,9 +83,9 @@ recycle_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_consta
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
-  fold_weight_rows(sm + RcLayout::w, sm + RcLayout::wx, 0, kPanelBytes, w, 0, 128, ln_w, ln_b ? ln_b : g_rc_zero_beta, 1.0f,
+  fold_weight_rows<kF16, kF16>(sm + RcLayout::w, sm + RcLayout::wx, 0, kPanelBytes, w, 0, 128, ln_w, ln_b ? ln_b : g_rc_zero_beta, 1.0f,
                    warp, kRcWarps, lane);
-  tile_write_ones(ctx.tiles, threadIdx.x, kRcThreads);
+  tile_write_ones<kF16>(ctx.tiles, threadIdx.x, kRcThreads);
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   tc_fence_before();
   __syncthreads();
@@ -111,9 +112,9 @@ recycle_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_consta
         }
       } else if (warp == 13) {
         tile_product_loop(ctx, tmem_base, smem_u32(sm + RcLayout::w), kPanelBytes, smem_u32(sm + RcLayout::wx),
-                          umma_idesc_bf16(128, 128), &bars.acc_full, &bars.acc_free);
+                          umma_idesc_16(128, 128, kF16, kF16), &bars.acc_full, &bars.acc_free);
       } else if (warp == 14) {
-        tile_gram_loop(ctx, tmem_base + kRcColGram);
+        tile_gram_loop<kF16>(ctx, tmem_base + kRcColGram);
       }
     }
   } else if (warp >= 8) {

@@ -1,12 +1,14 @@
 // SwiGLU transition for 128-channel rows on the 5th-generation tensor cores:
 //   x_out = [x +] W_o( silu(W_a LN(x)) * (W_b LN(x)) ),  hidden width 512, the [rows][512] intermediates never
-//   leave the SM (tensor memory -> registers -> tensor memory).
+//   leave the SM (tensor memory -> registers -> tensor memory).  Both products take fp16 operands, whatever the
+//   storage type of x: the rows pass through registers for the LayerNorm anyway, a normalised row and the weights
+//   lie far inside the fp16 range, and fp16 keeps three more bits than bf16 (h saturates at +-65504).
 //
 // Persistent kernel, one CTA per SM, 128 rows per tile, three tiles in flight: while the tensor core works through
 // the eight 64-wide hidden chunks of one tile, the next tile is being normalised and the previous one written out.
 //
 //   warps 0..7    SwiGLU: a thread owns one row and half of the current hidden chunk: it pulls a|b out of tensor
-//                 memory, forms h = silu(a) * b, and writes h (bf16) back over the first 32 columns of the same
+//                 memory, forms h = silu(a) * b, and writes h (fp16) back over the first 32 columns of the same
 //                 H buffer as the A operand of the second product.  The two H buffers alternate.
 //   warps 8..11   LayerNorm: lanes across channels (coalesced), eight rows in flight per warp; the normalised rows
 //                 are written as the K-major, 128-byte-swizzled A operand of the first product (two buffers).
@@ -22,7 +24,7 @@
 namespace px {
 
 constexpr int kTrStages = 3;
-constexpr int kTrABytes = 2 * 128 * 128;            // one tile: two k panels of [128 rows][64 k] bf16
+constexpr int kTrABytes = 2 * 128 * 128;            // one tile: two k panels of [128 rows][64 k] fp16
 constexpr int kTrW1Bytes = 2 * 128 * 128;           // [W_a chunk; W_b chunk]: two k panels of [128 rows][64 k]
 constexpr int kTrW2Bytes = 128 * 128;               // W_o chunk: [128 out rows][64 hidden]
 constexpr int kTrStageBytes = kTrW1Bytes + kTrW2Bytes;
@@ -127,7 +129,7 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
       }
     } else if (warp == 17) {
       // ---------------------------------------------------------------- first product: H = A [W_a;W_b]_c^T
-      constexpr uint32_t idesc = umma_idesc_bf16(128, 128);
+      constexpr uint32_t idesc = umma_idesc_f16(128, 128);
       int j = 0, k = 0;
       bool ok = true;
       for (int tile = first_tile; tile < n_tiles && ok; tile += tile_step, ++k) {
@@ -151,7 +153,7 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
       }
     } else if (warp == 18) {
       // ---------------------------------------------------------------- second product: OUT += h W_o,c^T
-      constexpr uint32_t idesc = umma_idesc_bf16(128, 128);
+      constexpr uint32_t idesc = umma_idesc_f16(128, 128);
       int j = 0, k = 0;
       bool ok = true;
       for (int tile = first_tile; tile < n_tiles && ok; tile += tile_step, ++k) {
@@ -298,8 +300,8 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
           const float rstd = rsqrtf(sum[j] * (1.0f / kC) + eps);
           uint2 o = make_uint2(0u, 0u);
           if (grow < rows) {
-            o.x = pack_bf16x2(x[j].x * rstd * g4.x + b4.x, x[j].y * rstd * g4.y + b4.y);
-            o.y = pack_bf16x2(x[j].z * rstd * g4.z + b4.z, x[j].w * rstd * g4.w + b4.w);
+            o.x = pack_f16x2(x[j].x * rstd * g4.x + b4.x, x[j].y * rstd * g4.y + b4.y);
+            o.y = pack_f16x2(x[j].z * rstd * g4.z + b4.z, x[j].w * rstd * g4.w + b4.w);
           }
           *reinterpret_cast<uint2*>(sa + panel_off + r * 128 + ((chunk ^ (r & 7)) << 4)) = o;
         }
@@ -336,7 +338,7 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
             // silu(a) * b = 0.5 * a * b * (1 + tanh(a / 2)): one special-function op per element
             const float a0 = __uint_as_float(a[2 * e]), a1 = __uint_as_float(a[2 * e + 1]);
             const float h0 = 0.5f * a0 * __uint_as_float(b[2 * e]), h1 = 0.5f * a1 * __uint_as_float(b[2 * e + 1]);
-            w[8 * hh + e] = pack_bf16x2(fmaf(h0, tanh_fast(0.5f * a0), h0), fmaf(h1, tanh_fast(0.5f * a1), h1));
+            w[8 * hh + e] = pack_f16x2(fmaf(h0, tanh_fast(0.5f * a0), h0), fmaf(h1, tanh_fast(0.5f * a1), h1));
           }
         }
         // h overwrites the first 32 columns of H; all warps must have read their a before any of them writes:
@@ -366,12 +368,12 @@ static int32_t launch_transition(const void* x_in, void* x_out, const float* ln_
                                  const px_bf16* w_b, const px_bf16* w_o, int64_t rows, int32_t add_residual, float eps,
                                  cudaStream_t st) {
   CUtensorMap ma, mb, mo;
-  // W_a, W_b: [512 rows][128 k] bf16, box [64 rows][64 k]; W_o: [128 rows][512 k], box [128 rows][64 k]
-  if (!make_map_3d(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, w_a, 128, 512, 1, 256, 512 * 256, 64, 64,
+  // W_a, W_b: [512 rows][128 k] fp16, box [64 rows][64 k]; W_o: [128 rows][512 k], box [128 rows][64 k]
+  if (!make_map_3d(&ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, w_a, 128, 512, 1, 256, 512 * 256, 64, 64,
                    CU_TENSOR_MAP_SWIZZLE_128B) ||
-      !make_map_3d(&mb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, w_b, 128, 512, 1, 256, 512 * 256, 64, 64,
+      !make_map_3d(&mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, w_b, 128, 512, 1, 256, 512 * 256, 64, 64,
                    CU_TENSOR_MAP_SWIZZLE_128B) ||
-      !make_map_3d(&mo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, w_o, 512, 128, 1, 1024, 128 * 1024, 64, 128,
+      !make_map_3d(&mo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, w_o, 512, 128, 1, 1024, 128 * 1024, 64, 128,
                    CU_TENSOR_MAP_SWIZZLE_128B))
     return PX_ERR_LAUNCH;
   const size_t smem = TransLayout::total + 1024;

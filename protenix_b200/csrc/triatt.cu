@@ -20,7 +20,7 @@ static size_t align256(size_t b) { return (b + 255) / 256 * 256; }
 
 using namespace px;
 
-// workspace layout: q | k | v | o (bf16) | bias (fp32 [4][n][ldm]) | mask_bias (fp32 [n][ldm]) | tile flags
+// workspace layout: q | k | v | o (fp16) | bias (fp32 [4][n][ldm]) | mask_bias (fp32 [n][ldm]) | tile flags
 extern "C" int64_t px_triatt_workspace_bytes(int64_t n) {
   if (n <= 0) return 0;
   const int64_t ld = px_ld_mask(n);
@@ -30,22 +30,22 @@ extern "C" int64_t px_triatt_workspace_bytes(int64_t n) {
 }
 
 extern "C" int32_t px_triangle_attention(const void* z_in, void* z_out, int32_t z_dtype, const float* mask,
-                                         const float* ln_w, const float* ln_b, const px_bf16* w_bias,
-                                         const px_bf16* w_q, const px_bf16* w_k, const px_bf16* w_v,
-                                         const px_bf16* w_g, const px_bf16* w_o, void* workspace,
+                                         const float* ln_w, const float* ln_b, const px_w16* w_bias,
+                                         const px_w16* w_q, const px_w16* w_k, const px_w16* w_v,
+                                         const px_w16* w_g, const px_f16* w_o, void* workspace,
                                          int64_t workspace_bytes, int64_t n, int32_t ending, int32_t add_residual,
                                          float eps, float inf, void* stream) {
   if (!workspace || n <= 0 || ((uintptr_t)workspace & 255)) return PX_ERR_BAD_ARG;
   if (workspace_bytes < px_triatt_workspace_bytes(n)) return PX_ERR_WORKSPACE;
   const int64_t ld = px_ld_mask(n);
   unsigned char* p = (unsigned char*)workspace;
-  px_bf16* q = (px_bf16*)p;
+  px_f16* q = (px_f16*)p;
   p += align256(att_qkv_elems(n) * 2);
-  px_bf16* k = (px_bf16*)p;
+  px_f16* k = (px_f16*)p;
   p += align256(att_qkv_elems(n) * 2);
-  px_bf16* v = (px_bf16*)p;
+  px_f16* v = (px_f16*)p;
   p += align256(att_qkv_elems(n) * 2);
-  px_bf16* o = (px_bf16*)p;
+  px_f16* o = (px_f16*)p;
   p += align256((size_t)n * n * kC * 2);
   float* bias = (float*)p;
   p += align256((size_t)kH * n * ld * 4);

@@ -1,7 +1,8 @@
 // Triangle attention, stage 1 on the 5th-generation tensor cores:
 //   LN(z) -> q, k [u][h][t][32] (q pre-scaled by log2(e)/sqrt(32)), v transposed [u][h][32][ld] (zero pad columns),
-//   bias[h][u][t] = log2(e) * (W_bias LN(z))_h (zero pad columns) and mask_bias[u][t] = log2(e) * inf * (mask - 1)
-//   (-inf in the pad columns), for the pair element (u, t) = z[u][t] (starting node) or z[t][u] (ending node).
+//   in fp16 (projections of standardised rows: far inside its range), bias[h][u][t] = log2(e) * (W_bias LN(z))_h (zero
+//   pad columns) and mask_bias[u][t] = log2(e) * inf * (mask - 1) (-inf in the pad columns) in fp32, for the pair
+//   element (u, t) = z[u][t] (starting node) or z[t][u] (ending node).
 //
 // Persistent kernel, one CTA per SM, on the row-tile pipeline of px_rowpipe.cuh (TMA-fed raw rows, LayerNorm folded
 // into the resident weights plus one correction K step, row statistics from a tensor-core Gram product).  The CTAs
@@ -25,7 +26,7 @@ namespace px {
 
 constexpr int kAiH = 4, kAiD = 32;
 constexpr int kAiW1Panel = 80 * 128;           // [v 64 | bias 16][64 k]
-constexpr int kAiStageOut = 64 * 256;          // [64 d][128 t] bf16
+constexpr int kAiStageOut = 64 * 256;          // [64 d][128 t] fp16
 constexpr int kAiWarps = 24;
 constexpr int kAiThreads = 32 * kAiWarps;
 constexpr uint32_t kAiColGram = 256;           // tensor memory: q|k (128) | v|bias (80) | - | statistics (144)
@@ -58,6 +59,7 @@ triatt_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
                     bf16* __restrict__ k_out, float* __restrict__ bias_out, float* __restrict__ mb_out, int n_u, int n,
                     int ldm, int swap, float eps, float inf, int tiles_t, int n_tiles) {
   constexpr bool kTma = sizeof(Tz) == 2;
+  constexpr bool kF16 = !kTma;                           // fp32 rows are multiplied as fp16 against fp16 weights
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   AiBars& bars = *reinterpret_cast<AiBars*>(sm + AiLayout::bars);
@@ -93,13 +95,13 @@ triatt_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   {
     // weights -> resident operands (q carries the softmax scale, the bias rows log2(e))
     const float qscale = kLog2e * rsqrtf((float)kAiD);
-    fold_weight_rows(sm + AiLayout::w0, sm + AiLayout::wx0, 0, kPanelBytes, w_q, 64 * hpair, 64, ln_w, ln_b, qscale, warp,
+    fold_weight_rows<kF16, kF16>(sm + AiLayout::w0, sm + AiLayout::wx0, 0, kPanelBytes, w_q, 64 * hpair, 64, ln_w, ln_b, qscale, warp,
                      kAiWarps, lane);
-    fold_weight_rows(sm + AiLayout::w0, sm + AiLayout::wx0, 64, kPanelBytes, w_k, 64 * hpair, 64, ln_w, ln_b, 1.0f, warp,
+    fold_weight_rows<kF16, kF16>(sm + AiLayout::w0, sm + AiLayout::wx0, 64, kPanelBytes, w_k, 64 * hpair, 64, ln_w, ln_b, 1.0f, warp,
                      kAiWarps, lane);
-    fold_weight_rows(sm + AiLayout::w1, sm + AiLayout::wx1, 0, kAiW1Panel, w_v, 64 * hpair, 64, ln_w, ln_b, 1.0f, warp,
+    fold_weight_rows<kF16, kF16>(sm + AiLayout::w1, sm + AiLayout::wx1, 0, kAiW1Panel, w_v, 64 * hpair, 64, ln_w, ln_b, 1.0f, warp,
                      kAiWarps, lane);
-    fold_weight_rows(sm + AiLayout::w1, sm + AiLayout::wx1, 64, kAiW1Panel, w_bias, 2 * hpair, 2, ln_w, ln_b, kLog2e, warp,
+    fold_weight_rows<kF16, kF16>(sm + AiLayout::w1, sm + AiLayout::wx1, 64, kAiW1Panel, w_bias, 2 * hpair, 2, ln_w, ln_b, kLog2e, warp,
                      kAiWarps, lane);
     // rows 66..79 of the second operand (and of its correction panel) are padding
     for (int i = threadIdx.x; i < 14 * 18; i += kAiThreads) {
@@ -108,7 +110,7 @@ triatt_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
                                       : sm + AiLayout::wx1 + r * 32 + (piece - 16) * 16;
       *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
     }
-    tile_write_ones(ctx.tiles, threadIdx.x, kAiThreads);
+    tile_write_ones<kF16>(ctx.tiles, threadIdx.x, kAiThreads);
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
   tc_fence_before();
@@ -121,13 +123,13 @@ triatt_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
       if (warp == 20) {
         if (kTma) tile_producer_loop(ctx, &map_z);
       } else if (warp == 23) {
-        tile_gram_loop(ctx, tmem_base + kAiColGram);
+        tile_gram_loop<kF16>(ctx, tmem_base + kAiColGram);
       } else if (warp == 21) {
         tile_product_loop(ctx, tmem_base, smem_u32(sm + AiLayout::w0), kPanelBytes, smem_u32(sm + AiLayout::wx0),
-                          umma_idesc_bf16(128, 128), &bars.acc_full[0], &bars.acc_free[0]);
+                          umma_idesc_16(128, 128, kF16, kF16), &bars.acc_full[0], &bars.acc_free[0]);
       } else {
         tile_product_loop(ctx, tmem_base + 128, smem_u32(sm + AiLayout::w1), kAiW1Panel, smem_u32(sm + AiLayout::wx1),
-                          umma_idesc_bf16(128, 80), &bars.acc_full[1], &bars.acc_free[1]);
+                          umma_idesc_16(128, 80, kF16, kF16), &bars.acc_full[1], &bars.acc_free[1]);
       }
     }
   } else if (warp >= 16) {
@@ -169,10 +171,10 @@ triatt_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint4 o;
-            o.x = pack_bf16x2_int(rstd * __uint_as_float(v[8 * j + 0]), rstd * __uint_as_float(v[8 * j + 1]));
-            o.y = pack_bf16x2_int(rstd * __uint_as_float(v[8 * j + 2]), rstd * __uint_as_float(v[8 * j + 3]));
-            o.z = pack_bf16x2_int(rstd * __uint_as_float(v[8 * j + 4]), rstd * __uint_as_float(v[8 * j + 5]));
-            o.w = pack_bf16x2_int(rstd * __uint_as_float(v[8 * j + 6]), rstd * __uint_as_float(v[8 * j + 7]));
+            o.x = pack_f16x2(rstd * __uint_as_float(v[8 * j + 0]), rstd * __uint_as_float(v[8 * j + 1]));
+            o.y = pack_f16x2(rstd * __uint_as_float(v[8 * j + 2]), rstd * __uint_as_float(v[8 * j + 3]));
+            o.z = pack_f16x2(rstd * __uint_as_float(v[8 * j + 4]), rstd * __uint_as_float(v[8 * j + 5]));
+            o.w = pack_f16x2(rstd * __uint_as_float(v[8 * j + 6]), rstd * __uint_as_float(v[8 * j + 7]));
             dst[j] = o;
           }
         };
@@ -207,7 +209,7 @@ triatt_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
       if (lane == 0) mbar_arrive(&bars.acc_free[1]);     // this warp has read its part of the accumulator
 #pragma unroll
       for (int e = 0; e < 32; ++e)
-        *reinterpret_cast<bf16*>(stage + e * 256) = __float2bfloat16_rn(sc.y * __uint_as_float(v[e]));
+        *reinterpret_cast<__half*>(stage + e * 256) = __float2half_rn(sc.y * __uint_as_float(v[e]));
       if (half == 0 && t < ldm) {                        // zero in the pad columns [n, ldm)
 #pragma unroll
         for (int e = 0; e < 2; ++e)
@@ -236,7 +238,7 @@ PX_DEFINE_FAMILY_HOOKS(triatt_in)
 template <typename Tz>
 static int32_t launch_triatt_in(const void* z, const float* mask, const float* ln_w, const float* ln_b,
                                 const px_bf16* w_q, const px_bf16* w_k, const px_bf16* w_v, const px_bf16* w_bias,
-                                px_bf16* q, px_bf16* k, px_bf16* v, float* bias, float* mask_bias, int64_t n_u,
+                                px_f16* q, px_f16* k, px_f16* v, float* bias, float* mask_bias, int64_t n_u,
                                 int64_t n, int64_t ldm, int32_t ending, float eps, float inf, cudaStream_t st) {
   CUtensorMap mz, mv;
   if (sizeof(Tz) == 2) {
@@ -251,7 +253,7 @@ static int32_t launch_triatt_in(const void* z, const float* mask, const float* l
   }
   // v is [n_u * 128 rows (u, head, d)][ldt]: a store writes [64 rows][128 t]
   const uint64_t ldt = (uint64_t)px_ld(n);
-  if (!make_map_3d(&mv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, v, ldt, (uint64_t)n_u * 128, 1, ldt * 2, ldt * 2 * n_u * 128, 128,
+  if (!make_map_3d(&mv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, v, ldt, (uint64_t)n_u * 128, 1, ldt * 2, ldt * 2 * n_u * 128, 128,
                    64, CU_TENSOR_MAP_SWIZZLE_NONE, 1))
     return PX_ERR_LAUNCH;
   const size_t smem = AiLayout::total + 1024;
@@ -273,7 +275,7 @@ using namespace px;
 
 extern "C" int32_t px_triatt_in_proj(const void* z, int32_t z_dtype, const float* mask, const float* ln_w,
                                      const float* ln_b, const px_bf16* w_q, const px_bf16* w_k, const px_bf16* w_v,
-                                     const px_bf16* w_bias, px_bf16* q, px_bf16* k, px_bf16* v, float* bias,
+                                     const px_bf16* w_bias, px_f16* q, px_f16* k, px_f16* v, float* bias,
                                      float* mask_bias, int64_t n_u, int64_t n_t, int64_t ldm, int32_t ending,
                                      float eps, float inf, void* stream) {
   if (!z || !ln_w || !ln_b || !w_q || !w_k || !w_v || !w_bias || !q || !k || !v || !bias || !mask_bias)

@@ -9,14 +9,14 @@
 // never touch shared memory.
 //
 //   warps 0..7    gate: a thread owns one pair element and 64 channels: g from the accumulator, o from the
-//                 swizzled tile, o * sigmoid(g) packed to bf16 into tensor memory.
+//                 swizzled tile (fp16), o * sigmoid(g) packed to fp16 into tensor memory.
 //   warps 8..15   output: accumulator + residual (the raw z tile still in shared memory), packed to bf16 over the
 //                 o tile in place, which then leaves through a TMA store; the store addresses z[u][t] or z[t][u],
 //                 so the ending node costs nothing extra.  fp32 rows are written with plain stores instead.
 //   warps 16..19  one thread per row: statistics, correction row, the row's rstd.
 //   warp 20       TMA producer (z and o tiles); warp 21 MMA issuer of the gate product, warp 22 of the output
 //                 product (A operand in tensor memory), warp 23 of the statistics product.
-// Tensor memory: gate accumulator (128) | gated rows, two bf16 per column (64) | output accumulator (128) |
+// Tensor memory: gate accumulator (128) | gated rows, two fp16 per column (64) | output accumulator (128) |
 // statistics (144).  Algorithmic HBM traffic per pair element: 256 + 128*sizeof(Tz) read, 128*sizeof(Tz) written.
 // Every mbarrier wait is bounded.
 #include <cstring>
@@ -47,15 +47,6 @@ struct AoLayout {
 };
 static_assert(AoLayout::a % 1024 == 0 && AoLayout::o % 1024 == 0, "tiles must keep the swizzle alignment");
 
-// Plain copy of a [128][128] bf16 weight into a K-major swizzled operand.
-__device__ __forceinline__ void copy_weight_operand(unsigned char* dst, const bf16* __restrict__ W, int tid, int nthreads) {
-  for (int i = tid; i < 128 * 16; i += nthreads) {
-    const int r = i >> 4, piece = i & 15;
-    *reinterpret_cast<uint4*>(dst + operand_piece_offset(r, piece)) =
-        *reinterpret_cast<const uint4*>(W + (size_t)r * kC + 8 * piece);
-  }
-}
-
 template <typename Tz>
 __global__ void __launch_bounds__(kAoThreads, 1)
 triatt_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_o,
@@ -64,6 +55,7 @@ triatt_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
                      const bf16* __restrict__ w_o, int n_u, int n, int swap, int add_residual, float eps, int tiles_t,
                      int n_tiles) {
   constexpr bool kTma = sizeof(Tz) == 2;
+  constexpr bool kF16 = !kTma;                           // operand format of the z side; o and W_o are always fp16
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   AoBars& bars = *reinterpret_cast<AoBars*>(sm + AoLayout::bars);
@@ -102,9 +94,12 @@ triatt_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
   }
   {
     // the gate rows carry the 1/2 of sigmoid(x) = 1/2 + 1/2 tanh(x/2)
-    fold_weight_rows(sm + AoLayout::wg, sm + AoLayout::wx, 0, kPanelBytes, w_g, 0, 128, ln_w, ln_b, 0.5f, warp, kAoWarps, lane);
-    copy_weight_operand(sm + AoLayout::wo, w_o, threadIdx.x, kAoThreads);
-    tile_write_ones(ctx.tiles, threadIdx.x, kAoThreads);
+    fold_weight_rows<kF16, kF16>(sm + AoLayout::wg, sm + AoLayout::wx, 0, kPanelBytes, w_g, 0, 128, ln_w, ln_b, 0.5f, warp,
+                                 kAoWarps, lane);
+    // the output weights multiply the fp16 rows o * sigmoid(g) and arrive as fp16
+    fold_weight_rows<true, true>(sm + AoLayout::wo, nullptr, 0, kPanelBytes, w_o, 0, 128, nullptr, nullptr, 1.0f, warp,
+                                 kAoWarps, lane);
+    tile_write_ones<kF16>(ctx.tiles, threadIdx.x, kAoThreads);
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
   tc_fence_before();
@@ -129,13 +124,13 @@ triatt_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
           }
         }
       } else if (warp == 23) {
-        tile_gram_loop(ctx, tmem_base + kAoColGram);
+        tile_gram_loop<kF16>(ctx, tmem_base + kAoColGram);
       } else if (warp == 21) {
         tile_product_loop(ctx, tmem_base + kAoColG, smem_u32(sm + AoLayout::wg), kPanelBytes, smem_u32(sm + AoLayout::wx),
-                          umma_idesc_bf16(128, 128), &bars.g_full, &bars.g_free);
+                          umma_idesc_16(128, 128, kF16, kF16), &bars.g_full, &bars.g_free);
       } else {
         // ---------------------------------------------------------------- output product, A operand in tensor memory
-        constexpr uint32_t idesc = umma_idesc_bf16(128, 128);
+        constexpr uint32_t idesc = umma_idesc_f16(128, 128);
         const uint32_t wo_addr = smem_u32(sm + AoLayout::wo);
         int k = 0;
         for (int tile = ctx.first_tile; tile < n_tiles; tile += ctx.tile_step, ++k) {
@@ -186,10 +181,10 @@ triatt_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
           const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float2 o2 = unpack_bf16x2(ow[e]);
+            const float2 o2 = unpack_f16x2(ow[e]);
             const float s0 = fmaf(0.5f, tanh_fast(rstd * __uint_as_float(g[8 * j + 2 * e])), 0.5f);
             const float s1 = fmaf(0.5f, tanh_fast(rstd * __uint_as_float(g[8 * j + 2 * e + 1])), 0.5f);
-            packed[16 * hh + 4 * j + e] = pack_bf16x2_int(o2.x * s0, o2.y * s1);
+            packed[16 * hh + 4 * j + e] = pack_f16x2(o2.x * s0, o2.y * s1);
           }
         }
       }
@@ -311,7 +306,7 @@ static int32_t launch_triatt_out(const px_bf16* o, const void* z_in, void* z_out
     memset(&mz, 0, sizeof(mz));
     memset(&mout, 0, sizeof(mout));
   }
-  if (!make_map_3d(&mo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, o, 128, (uint64_t)n, (uint64_t)n_u, 256, (uint64_t)n * 256, 64,
+  if (!make_map_3d(&mo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, o, 128, (uint64_t)n, (uint64_t)n_u, 256, (uint64_t)n * 256, 64,
                    128, CU_TENSOR_MAP_SWIZZLE_128B, 1))
     return PX_ERR_LAUNCH;
   const size_t smem = AoLayout::total + 1024;

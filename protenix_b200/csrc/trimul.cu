@@ -18,22 +18,22 @@ extern "C" int64_t px_ld(int64_t n) { return (n + 7) / 8 * 8; }
 
 extern "C" int64_t px_trimul_workspace_bytes(int64_t n) {
   if (n <= 0) return 0;
-  return (int64_t)(3 * trimul_elems(n) * sizeof(bf16));
+  return (int64_t)(3 * trimul_elems(n) * 2);   // a, b, x in fp16
 }
 
 extern "C" int32_t px_triangle_multiplication(const void* z_in, void* z_out, int32_t z_dtype, const float* mask,
                                               const float* ln_in_w, const float* ln_in_b, const float* ln_out_w,
-                                              const float* ln_out_b, const px_bf16* w_ap, const px_bf16* w_ag,
-                                              const px_bf16* w_bp, const px_bf16* w_bg, const px_bf16* w_z,
-                                              const px_bf16* w_g, void* workspace, int64_t workspace_bytes, int64_t n,
+                                              const float* ln_out_b, const px_w16* w_ap, const px_w16* w_ag,
+                                              const px_w16* w_bp, const px_w16* w_bg, const px_f16* w_z,
+                                              const px_w16* w_g, void* workspace, int64_t workspace_bytes, int64_t n,
                                               int32_t incoming, int32_t add_residual, float eps, void* stream) {
   if (!workspace || n <= 0) return PX_ERR_BAD_ARG;
   if (workspace_bytes < px_trimul_workspace_bytes(n)) return PX_ERR_WORKSPACE;
   if ((uintptr_t)workspace & 15) return PX_ERR_BAD_ARG;
   const int64_t ld = px_ld(n);
-  px_bf16* a = (px_bf16*)workspace;
-  px_bf16* b = a + trimul_elems(n);
-  px_bf16* x = b + trimul_elems(n);
+  px_f16* a = (px_f16*)workspace;
+  px_f16* b = a + trimul_elems(n);
+  px_f16* x = b + trimul_elems(n);
   int32_t s = px_trimul_in_proj(z_in, z_dtype, mask, ln_in_w, ln_in_b, w_ap, w_ag, w_bp, w_bg, a, b, n, n, ld,
                                 incoming, eps, stream);
   if (s != PX_OK) return s;
@@ -81,8 +81,8 @@ extern "C" int64_t px_static_max_n(void) { return kStaticMaxN; }
 extern "C" int32_t px_triangle_multiplication_static(const void* z_in, void* z_out, int32_t z_dtype,
                                                      const float* mask, const float* ln_in_w, const float* ln_in_b,
                                                      const float* ln_out_w, const float* ln_out_b,
-                                                     const px_bf16* w_ap, const px_bf16* w_ag, const px_bf16* w_bp,
-                                                     const px_bf16* w_bg, const px_bf16* w_z, const px_bf16* w_g,
+                                                     const px_w16* w_ap, const px_w16* w_ag, const px_w16* w_bp,
+                                                     const px_w16* w_bg, const px_f16* w_z, const px_w16* w_g,
                                                      int64_t n, int32_t incoming, int32_t add_residual, float eps,
                                                      void* stream) {
   if (n <= 0) return PX_ERR_BAD_ARG;
@@ -90,7 +90,7 @@ extern "C" int32_t px_triangle_multiplication_static(const void* z_in, void* z_o
   void* scratch = nullptr;
   int32_t s = static_scratch(&scratch);
   if (s != PX_OK) return s;
-  // Layout for this N: a | b | x, each [128][N][ld] bf16.  Every element a stage reads was written
+  // Layout for this N: a | b | x, each [128][N][ld] fp16.  Every element a stage reads was written
   // earlier in the same call (the projection also writes the zero pad columns), so nothing left by
   // a previous call, possibly with another N, has to be cleared.
   return px_triangle_multiplication(z_in, z_out, z_dtype, mask, ln_in_w, ln_in_b, ln_out_w, ln_out_b, w_ap, w_ag, w_bp,

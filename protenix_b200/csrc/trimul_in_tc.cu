@@ -1,6 +1,7 @@
 // Triangle multiplication, stage 1 on the 5th-generation tensor cores:
 //   a[c][u][t] = mask * (W_ap LN(z))_c * sigmoid((W_ag LN(z))_c),  b likewise, for the pair element (u, t),
-//   stored channel-major with the contraction index t contiguous.
+//   stored channel-major in fp16 with the contraction index t contiguous.  (a and b are products of a bounded gate
+//   and a projection of a standardised row: far inside the fp16 range, and fp16 keeps three more bits than bf16.)
 //
 // Persistent kernel, one CTA per SM.  A tile is 128 pair elements (one u, 128 consecutive t); the CTAs work in
 // pairs on the same sequence of tiles, each CTA producing 64 of the 128 channels of a and of b (the second read of
@@ -30,7 +31,7 @@
 namespace px {
 
 constexpr int kTiWExtra = 128 * 32;            // [128 rows][16 k] weight-side correction panel
-constexpr int kTiStageOut = 64 * 256;          // [64 channels][128 t] bf16
+constexpr int kTiStageOut = 64 * 256;          // [64 channels][128 t] fp16
 constexpr int kTiWarps = 24;
 constexpr int kTiThreads = 32 * kTiWarps;
 constexpr uint32_t kTiColGram = 256;           // tensor memory: out a | out b | statistics (144 columns)
@@ -59,6 +60,7 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
                     const bf16* __restrict__ w_ag, const bf16* __restrict__ w_bp, const bf16* __restrict__ w_bg,
                     int n_u, int n_t, int swap, float eps, int tiles_t, int n_tiles) {
   constexpr bool kTma = sizeof(Tz) == 2;
+  constexpr bool kF16 = !kTma;                           // fp32 rows are multiplied as fp16 against fp16 weights
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   TiBars& bars = *reinterpret_cast<TiBars*>(sm + TiLayout::bars);
@@ -95,11 +97,11 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     // weights -> resident operands; the gate rows carry the 1/2 of sigmoid(x) = 1/2 + 1/2 tanh(x/2)
     unsigned char* w0 = sm + TiLayout::w;
     unsigned char* x0 = sm + TiLayout::wx;
-    fold_weight_rows(w0, x0, 0, kPanelBytes, w_ap, chan0, 64, ln_w, ln_b, 1.0f, warp, kTiWarps, lane);
-    fold_weight_rows(w0, x0, 64, kPanelBytes, w_ag, chan0, 64, ln_w, ln_b, 0.5f, warp, kTiWarps, lane);
-    fold_weight_rows(w0 + kOperandBytes, x0 + kTiWExtra, 0, kPanelBytes, w_bp, chan0, 64, ln_w, ln_b, 1.0f, warp, kTiWarps, lane);
-    fold_weight_rows(w0 + kOperandBytes, x0 + kTiWExtra, 64, kPanelBytes, w_bg, chan0, 64, ln_w, ln_b, 0.5f, warp, kTiWarps, lane);
-    tile_write_ones(ctx.tiles, threadIdx.x, kTiThreads);
+    fold_weight_rows<kF16, kF16>(w0, x0, 0, kPanelBytes, w_ap, chan0, 64, ln_w, ln_b, 1.0f, warp, kTiWarps, lane);
+    fold_weight_rows<kF16, kF16>(w0, x0, 64, kPanelBytes, w_ag, chan0, 64, ln_w, ln_b, 0.5f, warp, kTiWarps, lane);
+    fold_weight_rows<kF16, kF16>(w0 + kOperandBytes, x0 + kTiWExtra, 0, kPanelBytes, w_bp, chan0, 64, ln_w, ln_b, 1.0f, warp, kTiWarps, lane);
+    fold_weight_rows<kF16, kF16>(w0 + kOperandBytes, x0 + kTiWExtra, 64, kPanelBytes, w_bg, chan0, 64, ln_w, ln_b, 0.5f, warp, kTiWarps, lane);
+    tile_write_ones<kF16>(ctx.tiles, threadIdx.x, kTiThreads);
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
   tc_fence_before();
@@ -112,11 +114,11 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
       if (warp == 20) {
         if (kTma) tile_producer_loop(ctx, &map_z);
       } else if (warp == 23) {
-        tile_gram_loop(ctx, tmem_base + kTiColGram);
+        tile_gram_loop<kF16>(ctx, tmem_base + kTiColGram);
       } else {
         const int ph = warp - 21;                          // MMA issuer of output ph
         tile_product_loop(ctx, tmem_base + 128 * ph, smem_u32(sm + TiLayout::w) + ph * kOperandBytes, kPanelBytes,
-                          smem_u32(sm + TiLayout::wx) + ph * kTiWExtra, umma_idesc_bf16(128, 128), &bars.acc_full[ph],
+                          smem_u32(sm + TiLayout::wx) + ph * kTiWExtra, umma_idesc_16(128, 128, kF16, kF16), &bars.acc_full[ph],
                           &bars.acc_free[ph]);
       }
     }
@@ -153,7 +155,7 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
         for (int e = 0; e < 16; ++e) {
           const float h = sc.y * __uint_as_float(p[e]);
           const float v = fmaf(h, tanh_fast(sc.x * __uint_as_float(g[e])), h);
-          *reinterpret_cast<bf16*>(stage + (16 * hh + e) * 256) = __float2bfloat16_rn(v);
+          *reinterpret_cast<__half*>(stage + (16 * hh + e) * 256) = __float2half_rn(v);
         }
       };
       uint32_t p0[16], g0[16], p1[16], g1[16];
@@ -204,9 +206,9 @@ static int32_t launch_trimul_in(const void* z, const float* mask, const float* l
     memset(&mz, 0, sizeof(mz));
   }
   // outputs [128 channels][n_u][ld]: a store writes [64 channels][one u][128 t]
-  if (!make_map_3d(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a, (uint64_t)ld, (uint64_t)n_u, 128, (uint64_t)ld * 2,
+  if (!make_map_3d(&ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, (uint64_t)ld, (uint64_t)n_u, 128, (uint64_t)ld * 2,
                    (uint64_t)n_u * ld * 2, 128, 1, CU_TENSOR_MAP_SWIZZLE_NONE, 64) ||
-      !make_map_3d(&mb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, b, (uint64_t)ld, (uint64_t)n_u, 128, (uint64_t)ld * 2,
+      !make_map_3d(&mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, b, (uint64_t)ld, (uint64_t)n_u, 128, (uint64_t)ld * 2,
                    (uint64_t)n_u * ld * 2, 128, 1, CU_TENSOR_MAP_SWIZZLE_NONE, 64))
     return PX_ERR_LAUNCH;
   const size_t smem = TiLayout::total + 1024;

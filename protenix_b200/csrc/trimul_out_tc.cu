@@ -1,6 +1,7 @@
 // Triangle multiplication, stage 3 on the 5th-generation tensor cores:
 //   z_out[i][j] = [z_in[i][j] +] (W_z LN_out(x[:, i, j])) * sigmoid(W_g LN_in(z_in[i][j])),
-//   x [128 channels][n_i][ld] channel-major as the contraction leaves it.
+//   x [128 channels][n_i][ld] fp16, channel-major and scaled by PX_TRIMUL_X_SCALE as the contraction leaves it
+//   (LN_out runs with eps * scale^2, which gives exactly LN_out of the unscaled x).
 //
 // Persistent kernel, one CTA per SM, 128 pair elements (one i, 128 consecutive j) per tile.  Both LayerNorms are
 // folded into the resident weights plus one shared correction K step (px_rowpipe.cuh); nothing is normalised or
@@ -62,6 +63,7 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
                      const float* __restrict__ ln_out_w, const float* __restrict__ ln_out_b, const bf16* __restrict__ w_z,
                      const bf16* __restrict__ w_g, int n_i, int n, int add_residual, float eps, int tiles_j, int n_tiles) {
   constexpr bool kTma = sizeof(Tz) == 2;
+  constexpr bool kF16 = !kTma;                           // operand format of the z side; the x side is always fp16
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   ToBars& bars = *reinterpret_cast<ToBars*>(sm + ToLayout::bars);
@@ -90,14 +92,14 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
   {
     // weights -> resident operands; the gate rows carry the 1/2 of sigmoid(x) = 1/2 + 1/2 tanh(x/2).  The z
     // statistics use k 0..7 of the correction step, the x statistics k 8..15.
-    fold_weight_rows(sm + ToLayout::wg, sm + ToLayout::wxg, 0, kToWPanel, w_g, 0, 128, ln_in_w, ln_in_b, 0.5f, warp, kToWarps,
+    fold_weight_rows<kF16, kF16>(sm + ToLayout::wg, sm + ToLayout::wxg, 0, kToWPanel, w_g, 0, 128, ln_in_w, ln_in_b, 0.5f, warp, kToWarps,
                      lane, 0);
-    fold_weight_rows(sm + ToLayout::wz, sm + ToLayout::wxz, 0, kToWPanel, w_z, 0, 128, ln_out_w, ln_out_b, 1.0f, warp, kToWarps,
+    fold_weight_rows<true, true>(sm + ToLayout::wz, sm + ToLayout::wxz, 0, kToWPanel, w_z, 0, 128, ln_out_w, ln_out_b, 1.0f, warp, kToWarps,
                      lane, 1);
     for (int i = threadIdx.x; i < 2 * 2 * 16 * 8; i += kToThreads) {   // rows of ones behind both weights
       const int panel = i >> 7, piece = i & 127;
-      *reinterpret_cast<uint4*>(sm + ToLayout::wg + panel * kToWPanel + 128 * 128 + piece * 16) =
-          make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
+      const uint32_t one = ones16x2(panel >= 2 || kF16);     // panels 0, 1: gate weights, 2, 3: projection
+      *reinterpret_cast<uint4*>(sm + ToLayout::wg + panel * kToWPanel + 128 * 128 + piece * 16) = make_uint4(one, one, one, one);
     }
     for (int i = threadIdx.x; i < 2 * 16 * 2; i += kToThreads)         // ... which take no correction
       *reinterpret_cast<uint4*>(sm + ToLayout::wxg + (i >> 5) * kToWExtra + 128 * 32 + (i & 31) * 16) = make_uint4(0u, 0u, 0u, 0u);
@@ -129,7 +131,7 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
         }
       } else if (warp == 23) {
         // ---------------------------------------------------------------- statistics products: Z Z^T, then X^T X
-        constexpr uint32_t idesc_z = umma_idesc_bf16(128, 128), idesc_x = umma_idesc_bf16(128, 128, true, true);
+        constexpr uint32_t idesc_z = umma_idesc_16(128, 128, kF16, kF16), idesc_x = umma_idesc_f16(128, 128, true, true);
         int k = 0;
         for (int tile = first_tile; tile < n_tiles; tile += tile_step, ++k) {
           const int s = k % kToStages, m = k / kToStages;
@@ -155,7 +157,7 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
       } else {
         // ---------------------------------------------------------------- gate (warp 21) / projection (warp 22) product
         const bool proj = warp == 22;
-        const uint32_t idesc = umma_idesc_bf16(128, 144, proj, false);
+        const uint32_t idesc = proj ? umma_idesc_f16(128, 144, true, false) : umma_idesc_16(128, 144, kF16, kF16);
         const uint32_t d_tmem = tmem_base + (proj ? kToColP : kToColG);
         const uint32_t w_addr = smem_u32(sm + (proj ? ToLayout::wz : ToLayout::wg));
         const uint64_t wx_desc = umma_desc_sw32(smem_u32(sm + (proj ? ToLayout::wxz : ToLayout::wxg)));
@@ -196,8 +198,15 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
         ok = mbar_wait(&bars.a_empty[s], (m & 1) ^ 1, 16u);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        standardise_row_to_operand(sm + ToLayout::zt + s * kOperandBytes, r,
-                                   j < n ? reinterpret_cast<const float*>(z_in) + ((size_t)i * n + j) * kC : nullptr, eps);
+        auto rows_of = [&](int tl) {                       // this warp's 32 rows of tile tl
+          const int ii = tl / tiles_j, j_first = (tl % tiles_j) * 128 + 32 * qw;
+          return [=](int rr) -> const float* {
+            const int jj = j_first + rr;
+            return jj < n ? reinterpret_cast<const float*>(z_in) + ((size_t)ii * n + jj) * kC : nullptr;
+          };
+        };
+        if (tile + tile_step < n_tiles) prefetch_rows_l2(lane, rows_of(tile + tile_step));
+        standardise_rows_to_operand(sm + ToLayout::zt + s * kOperandBytes, 32 * qw, lane, eps, kPanelBytes, rows_of(tile));
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars.raw_full[s]);
@@ -232,9 +241,10 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
       for (int which = 0; which < 2; ++which) {
         const float mean = __uint_as_float(which ? sx[0] : sz[0]) * (1.0f / kC);
         const float var = fmaxf(sumsq[which] * (1.0f / kC) - mean * mean, 0.f);
-        rstd[which] = rsqrtf(var + eps);
+        const float e = which ? eps * (PX_TRIMUL_X_SCALE * PX_TRIMUL_X_SCALE) : eps;   // x arrives scaled
+        rstd[which] = rsqrtf(var + e);
         // rstd * (W'x - mean * s + std * t): the row side of the correction step holds (-mean, std)
-        write_correction_row(sm + ToLayout::ax + s * 128 * 32, r, -mean, sqrtf(var + eps), false, which, false);
+        write_correction_row(sm + ToLayout::ax + s * 128 * 32, r, -mean, sqrtf(var + e), false, which, false);
       }
       scale[(k % kToSlots) * 128 + r] = make_float2(rstd[0], rstd[1]);
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -347,7 +357,7 @@ static int32_t launch_trimul_out(const px_bf16* x, const void* z_in, void* z_out
     memset(&mout, 0, sizeof(mout));
   }
   // x [128 channels][n_i][ld]: a load brings [128 channels][one i][64 j]
-  if (!make_map_3d(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, (uint64_t)ld, (uint64_t)n_i, 128, (uint64_t)ld * 2,
+  if (!make_map_3d(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x, (uint64_t)ld, (uint64_t)n_i, 128, (uint64_t)ld * 2,
                    (uint64_t)n_i * ld * 2, 64, 1, CU_TENSOR_MAP_SWIZZLE_128B, 128))
     return PX_ERR_LAUNCH;
   const size_t smem = ToLayout::total + 1024;

@@ -12,9 +12,11 @@ import torch
 
 from . import _lib
 from ._lib import PX_BF16, PX_F16, PX_F32
+from .weights import w16_of
 
 _DTYPE = {torch.float32: PX_F32, torch.bfloat16: PX_BF16, torch.float16: PX_F16}
 C_Z = 128
+X_SCALE = 1.0 / 64      # PX_TRIMUL_X_SCALE: the contraction stores x scaled so that it stays inside the fp16 range
 N_HEAD_PAIR = 4
 D_HEAD_PAIR = 32
 
@@ -47,10 +49,22 @@ def _check_pair(z: torch.Tensor, name: str = "z") -> int:
     return z.shape[0]
 
 
-def _check_w(w: torch.Tensor, shape: Tuple[int, ...], name: str) -> None:
-    _need_cuda(w, name)
-    if w.dtype != torch.bfloat16 or tuple(w.shape) != shape:
-        raise RuntimeError(f"{name} must be bfloat16 {shape}, got {w.dtype} {tuple(w.shape)}")
+F16 = torch.float16
+
+
+def _zfmt(z: torch.Tensor) -> torch.dtype:
+    """Format of the weights that multiply rows of z: bf16 rows are multiplied as stored, fp32 rows as fp16."""
+    return torch.float16 if z.dtype == torch.float32 else torch.bfloat16
+
+
+def _w(w: torch.Tensor, fmt: torch.dtype, shape: Tuple[int, ...], name: str) -> torch.Tensor:
+    """A weight matrix (an fp32 parameter or an already converted tensor) in the 16-bit format the kernel wants;
+    the conversion is cached per parameter version."""
+    if not isinstance(w, torch.Tensor) or not w.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: this package has no CPU path")
+    if tuple(w.shape) != shape or not w.is_floating_point():
+        raise RuntimeError(f"{name} must be a floating-point tensor of shape {shape}, got {w.dtype} {tuple(w.shape)}")
+    return w16_of(w, fmt)
 
 
 def _check_v(v: torch.Tensor, n: int, name: str) -> None:
@@ -198,12 +212,14 @@ def triangle_multiplication(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optio
     mask = _check_mask(mask, n)
     for v, nm in ((ln_in_w, "ln_in_w"), (ln_in_b, "ln_in_b"), (ln_out_w, "ln_out_w"), (ln_out_b, "ln_out_b")):
         _check_v(v, C_Z, nm)
-    for w, nm in ((w_ap, "w_ap"), (w_ag, "w_ag"), (w_bp, "w_bp"), (w_bg, "w_bg"), (w_z, "w_z"), (w_g, "w_g")):
-        _check_w(w, (C_Z, C_Z), nm)
+    zf = _zfmt(z_in)
+    w_ap, w_ag, w_bp, w_bg, w_g = (_w(w, zf, (C_Z, C_Z), nm) for w, nm in
+                                   ((w_ap, "w_ap"), (w_ag, "w_ag"), (w_bp, "w_bp"), (w_bg, "w_bg"), (w_g, "w_g")))
+    w_z = _w(w_z, F16, (C_Z, C_Z), "w_z")
     lib = _lib.load()
     ws = workspace(z_in.device, lib.px_trimul_workspace_bytes(n))
     ldn = lib.px_ld(n)
-    per = C_Z * n * ldn * 2                      # bytes of one channel-major [128][N][ld] bf16 tensor
+    per = C_Z * n * ldn * 2                      # bytes of one channel-major [128][N][ld] fp16 tensor
     a, b, x = ws.data_ptr(), ws.data_ptr() + per, ws.data_ptr() + 2 * per
     dt, st, eps = _pair_dtype(z_in), _stream(z_in), float(eps)
     _launch("px_trimul_in_proj", lib.px_trimul_in_proj, _ptr(z_in), dt, _ptr(mask), _ptr(ln_in_w), _ptr(ln_in_b),
@@ -223,9 +239,10 @@ def triangle_attention(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optional[t
     mask = _check_mask(mask, n)
     _check_v(ln_w, C_Z, "ln_w")
     _check_v(ln_b, C_Z, "ln_b")
-    _check_w(w_bias, (N_HEAD_PAIR, C_Z), "w_bias")
-    for w, nm in ((w_q, "w_q"), (w_k, "w_k"), (w_v, "w_v"), (w_g, "w_g"), (w_o, "w_o")):
-        _check_w(w, (C_Z, C_Z), nm)
+    zf = _zfmt(z_in)
+    w_bias = _w(w_bias, zf, (N_HEAD_PAIR, C_Z), "w_bias")
+    w_q, w_k, w_v, w_g = (_w(w, zf, (C_Z, C_Z), nm) for w, nm in ((w_q, "w_q"), (w_k, "w_k"), (w_v, "w_v"), (w_g, "w_g")))
+    w_o = _w(w_o, F16, (C_Z, C_Z), "w_o")
     lib = _lib.load()
     ws = workspace(z_in.device, lib.px_triatt_workspace_bytes(n))
     ldn = lib.px_ld_mask(n)
@@ -254,9 +271,9 @@ def transition(x_in: torch.Tensor, x_out: torch.Tensor, ln_w, ln_b, w_a, w_b, w_
         raise RuntimeError(f"transition kernel handles [..., {C_Z}] rows with matching output")
     _check_v(ln_w, C_Z, "ln_w")
     _check_v(ln_b, C_Z, "ln_b")
-    _check_w(w_a, (4 * C_Z, C_Z), "w_a")
-    _check_w(w_b, (4 * C_Z, C_Z), "w_b")
-    _check_w(w_o, (C_Z, 4 * C_Z), "w_o")
+    w_a = _w(w_a, F16, (4 * C_Z, C_Z), "w_a")
+    w_b = _w(w_b, F16, (4 * C_Z, C_Z), "w_b")
+    w_o = _w(w_o, F16, (C_Z, 4 * C_Z), "w_o")
     rows = x_in.numel() // C_Z
     _launch("px_transition", _lib.load().px_transition, _ptr(x_in), _ptr(x_out), _pair_dtype(x_in), _ptr(ln_w),
             _ptr(ln_b), _ptr(w_a), _ptr(w_b), _ptr(w_o), rows, int(add_residual), float(eps), _stream(x_in))
@@ -271,7 +288,7 @@ def pair_bias_proj(z: torch.Tensor, ln_w, ln_b: Optional[torch.Tensor], w: torch
     if ln_b is not None:
         _check_v(ln_b, C_Z, "ln_b")
     heads = w.shape[0]
-    _check_w(w, (heads, C_Z), "w")
+    w = _w(w, _zfmt(z), (heads, C_Z), "w")
     out = torch.empty(heads, n, n, dtype=torch.float32, device=z.device)
     _launch("px_pair_bias_proj", _lib.load().px_pair_bias_proj, _ptr(z), _pair_dtype(z), _ptr(ln_w), _ptr(ln_b),
             _ptr(w), _ptr(out), n * n, heads, float(eps), _stream(z))
@@ -290,7 +307,7 @@ def recycle_update(z: torch.Tensor, z_init: torch.Tensor, ln_w, ln_b: Optional[t
     _check_v(ln_w, C_Z, "ln_w")
     if ln_b is not None:
         _check_v(ln_b, C_Z, "ln_b")
-    _check_w(w, (C_Z, C_Z), "w")
+    w = _w(w, _zfmt(z), (C_Z, C_Z), "w")
     if out is None:
         out = torch.empty_like(z)
     elif out.shape != z.shape or out.dtype != z.dtype or not out.is_contiguous():
@@ -314,12 +331,14 @@ def _slab(z: torch.Tensor, name: str = "z") -> Tuple[int, int]:
 
 def trimul_in_proj(z: torch.Tensor, mask: Optional[torch.Tensor], ln_w, ln_b, w_ap, w_ag, w_bp, w_bg,
                    incoming: bool, eps: float = 1e-5) -> Tuple[torch.Tensor, torch.Tensor]:
-    """a, b as [128][n_u][ld(n_t)] bf16.  z is [n_u][n_t][128]; with ``incoming`` it is [n_t][n_u][128]."""
+    """a, b as [128][n_u][ld(n_t)] fp16.  z is [n_u][n_t][128]; with ``incoming`` it is [n_t][n_u][128]."""
     r, c = _slab(z)
     n_u, n_t = (c, r) if incoming else (r, c)
     lib = _lib.load()
     ldt = lib.px_ld(n_t)
-    a = torch.empty(C_Z, n_u, ldt, dtype=torch.bfloat16, device=z.device)
+    zf = _zfmt(z)
+    w_ap, w_ag, w_bp, w_bg = (_w(w, zf, (C_Z, C_Z), "w") for w in (w_ap, w_ag, w_bp, w_bg))
+    a = torch.empty(C_Z, n_u, ldt, dtype=torch.float16, device=z.device)
     b = torch.empty_like(a)
     _launch("px_trimul_in_proj", lib.px_trimul_in_proj, _ptr(z), _pair_dtype(z), _ptr(mask), _ptr(ln_w), _ptr(ln_b),
             _ptr(w_ap), _ptr(w_ag), _ptr(w_bp), _ptr(w_bg), _ptr(a), _ptr(b), n_u, n_t, ldt, int(incoming), float(eps),
@@ -328,12 +347,12 @@ def trimul_in_proj(z: torch.Tensor, mask: Optional[torch.Tensor], ln_w, ln_b, w_
 
 
 def trimul_contract(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """x[c][i][j] = sum_k a[c][i][k] b[c][j][k] for [C][n][ld] bf16 operands (pad columns zero)."""
+    """x[c][i][j] = X_SCALE * sum_k a[c][i][k] b[c][j][k] for [C][n][ld] fp16 operands (pad columns zero)."""
     _need_cuda(a, "a")
     _need_cuda(b, "b")
     ch, n, ldn = a.shape
-    if a.dtype != torch.bfloat16 or b.shape != a.shape or b.dtype != a.dtype or ldn != ld(n):
-        raise RuntimeError("contraction operands must be bfloat16 [C][n][ld(n)] of equal shape")
+    if a.dtype != torch.float16 or b.shape != a.shape or b.dtype != a.dtype or ldn != ld(n):
+        raise RuntimeError("contraction operands must be float16 [C][n][ld(n)] of equal shape")
     x = torch.empty_like(a)
     _launch("px_trimul_contract", _lib.load().px_trimul_contract, _ptr(a), _ptr(b), _ptr(x), ch, n, ldn, _stream(a))
     return x
@@ -343,6 +362,10 @@ def trimul_out(x: torch.Tensor, z: torch.Tensor, ln_in_w, ln_in_b, ln_out_w, ln_
                eps: float = 1e-5) -> torch.Tensor:
     """z[n_i][n_j] += W_z LN(x) * sigmoid(W_g LN(z)) in place; x is [128][n_i][ld(n_j)]."""
     n_i, n_j = _slab(z)
+    _need_cuda(x, "x")
+    if x.dtype != torch.float16 or x.dim() != 3 or x.shape[0] != C_Z or x.shape[1] != n_i or x.shape[2] != ld(n_j):
+        raise RuntimeError("x must be float16 [128][n_i][ld(n_j)]")
+    w_z, w_g = _w(w_z, F16, (C_Z, C_Z), "w_z"), _w(w_g, _zfmt(z), (C_Z, C_Z), "w_g")
     _launch("px_trimul_out", _lib.load().px_trimul_out, _ptr(x), _ptr(z), _ptr(z), _pair_dtype(z), _ptr(ln_in_w),
             _ptr(ln_in_b), _ptr(ln_out_w), _ptr(ln_out_b), _ptr(w_z), _ptr(w_g), n_i, n_j, x.shape[2], 1, float(eps),
             _stream(z))
@@ -351,17 +374,20 @@ def trimul_out(x: torch.Tensor, z: torch.Tensor, ln_in_w, ln_in_b, ln_out_w, ln_
 
 def triatt_in_proj(z: torch.Tensor, mask: Optional[torch.Tensor], ln_w, ln_b, w_bias, w_q, w_k, w_v,
                    eps: float = 1e-5, inf: float = 1e9, ending: bool = False):
-    """q, k [n_u][4][n_t][32] and v (transposed) [n_u][4][32][ld(n_t)] bf16, bias [4][n_u][ldm] fp32,
-    mask_bias [n_u][ldm] fp32 for a slab.  z (and the mask) is [n_u][n_t][128]; with ``ending`` it is the
+    """q, k [n_u][4][n_t][32] and v (transposed) [n_u][4][32][ld(n_t)] in fp16, bias [4][n_u][ldm] and
+    mask_bias [n_u][ldm] in fp32 for a slab.  z (and the mask) is [n_u][n_t][128]; with ``ending`` it is the
     column slab [n_t][n_u][128] and the attended rows u are its columns."""
     n_u, n_t = _slab(z)
     if ending:
         n_u, n_t = n_t, n_u
     lib = _lib.load()
     ldm = lib.px_ld_mask(n_t)
-    q = torch.empty(n_u, N_HEAD_PAIR, n_t, D_HEAD_PAIR, dtype=torch.bfloat16, device=z.device)
+    zf = _zfmt(z)
+    w_bias = _w(w_bias, zf, (N_HEAD_PAIR, C_Z), "w_bias")
+    w_q, w_k, w_v = (_w(w, zf, (C_Z, C_Z), "w") for w in (w_q, w_k, w_v))
+    q = torch.empty(n_u, N_HEAD_PAIR, n_t, D_HEAD_PAIR, dtype=torch.float16, device=z.device)
     k = torch.empty_like(q)
-    v = torch.empty(n_u, N_HEAD_PAIR, D_HEAD_PAIR, lib.px_ld(n_t), dtype=torch.bfloat16, device=z.device)
+    v = torch.empty(n_u, N_HEAD_PAIR, D_HEAD_PAIR, lib.px_ld(n_t), dtype=torch.float16, device=z.device)
     bias = torch.empty(N_HEAD_PAIR, n_u, ldm, dtype=torch.float32, device=z.device)
     mb = torch.empty(n_u, ldm, dtype=torch.float32, device=z.device)
     _launch("px_triatt_in_proj", lib.px_triatt_in_proj, _ptr(z), _pair_dtype(z), _ptr(mask), _ptr(ln_w), _ptr(ln_b),
@@ -371,14 +397,17 @@ def triatt_in_proj(z: torch.Tensor, mask: Optional[torch.Tensor], ln_w, ln_b, w_
 
 
 def triatt_flash(q, k, v, bias_full: torch.Tensor, mb) -> torch.Tensor:
-    """o [n_u][n][128] bf16 from q,k,v [n_u][4][n][32], the full pair bias [4][n][ldm] and mask_bias [n_u][ldm]."""
+    """o [n_u][n][128] fp16 from q,k,v [n_u][4][n][32] (fp16), the full pair bias [4][n][ldm] and mask_bias
+    [n_u][ldm] (fp32)."""
     n_u, _, n, _ = q.shape
     for t, nm in ((q, "q"), (k, "k"), (v, "v"), (bias_full, "bias"), (mb, "mask_bias")):
         _need_cuda(t, nm)
     ldm = bias_full.shape[2]
     if tuple(bias_full.shape) != (N_HEAD_PAIR, n, ldm) or tuple(mb.shape) != (n_u, ldm):
         raise RuntimeError("pair bias must be [4][n][ldm] and mask_bias [n_u][ldm]")
-    o = torch.empty(n_u, n, C_Z, dtype=torch.bfloat16, device=q.device)
+    if any(t.dtype != torch.float16 for t in (q, k, v)) or bias_full.dtype != torch.float32 or mb.dtype != torch.float32:
+        raise RuntimeError("q, k, v must be float16, the pair bias and mask_bias float32")
+    o = torch.empty(n_u, n, C_Z, dtype=torch.float16, device=q.device)
     lib = _lib.load()
     scratch = torch.empty(int(lib.px_triatt_flash_scratch_bytes(n_u, n)), dtype=torch.uint8, device=q.device)
     _launch("px_triatt_flash", lib.px_triatt_flash, _ptr(q), _ptr(k), _ptr(v), _ptr(bias_full), _ptr(mb), _ptr(o),
@@ -393,6 +422,10 @@ def triatt_out(o: torch.Tensor, z: torch.Tensor, ln_w, ln_b, w_g, w_o, eps: floa
     n_u, n_t = _slab(z)
     if ending:
         n_u, n_t = n_t, n_u
+    _need_cuda(o, "o")
+    if o.dtype != torch.float16 or tuple(o.shape) != (n_u, n_t, C_Z):
+        raise RuntimeError("o must be float16 [n_u][n_t][128]")
+    w_g, w_o = _w(w_g, _zfmt(z), (C_Z, C_Z), "w_g"), _w(w_o, F16, (C_Z, C_Z), "w_o")
     _launch("px_triatt_out", _lib.load().px_triatt_out, _ptr(o), _ptr(z), _ptr(z), _pair_dtype(z), _ptr(ln_w),
             _ptr(ln_b), _ptr(w_g), _ptr(w_o), n_u, n_t, int(ending), 1, float(eps), _stream(z))
     return z
@@ -403,6 +436,7 @@ def pair_bias_rows(z: torch.Tensor, ln_w, ln_b: Optional[torch.Tensor], w: torch
     """bias[h, u, t] for a row slab z [n_u][n_t][128]."""
     n_u, n_t = _slab(z)
     heads = w.shape[0]
+    w = _w(w, _zfmt(z), (heads, C_Z), "w")
     out = torch.empty(heads, n_u, n_t, dtype=torch.float32, device=z.device)
     _launch("px_pair_bias_proj", _lib.load().px_pair_bias_proj, _ptr(z), _pair_dtype(z), _ptr(ln_w), _ptr(ln_b),
             _ptr(w), _ptr(out), n_u * n_t, heads, float(eps), _stream(z))
@@ -412,6 +446,8 @@ def pair_bias_rows(z: torch.Tensor, ln_w, ln_b: Optional[torch.Tensor], w: torch
 def transition_rows(x: torch.Tensor, ln_w, ln_b, w_a, w_b, w_o, eps: float = 1e-5) -> torch.Tensor:
     """x += Transition(x) in place for any [..., 128] slab."""
     _need_cuda(x, "x")
+    w_a, w_b = _w(w_a, F16, (4 * C_Z, C_Z), "w_a"), _w(w_b, F16, (4 * C_Z, C_Z), "w_b")
+    w_o = _w(w_o, F16, (C_Z, 4 * C_Z), "w_o")
     _launch("px_transition", _lib.load().px_transition, _ptr(x), _ptr(x), _pair_dtype(x), _ptr(ln_w), _ptr(ln_b),
             _ptr(w_a), _ptr(w_b), _ptr(w_o), x.numel() // C_Z, 1, float(eps), _stream(x))
     return x
@@ -439,7 +475,7 @@ class PeerBuffer:
         item = torch.empty(0, dtype=dtype).element_size()
         if offset_bytes + numel * item > self.nbytes:
             raise RuntimeError("peer buffer too small for the requested view")
-        typestr = {torch.bfloat16: "<u2", torch.float32: "<f4", torch.uint8: "|u1"}[dtype]
+        typestr = {torch.bfloat16: "<u2", torch.float16: "<f2", torch.float32: "<f4", torch.uint8: "|u1"}[dtype]
 
         class _View:
             pass

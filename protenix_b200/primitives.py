@@ -18,7 +18,6 @@ import torch.nn.functional as F
 
 from . import ops
 from .layer_norm import LayerNorm
-from .weights import bf16_of
 
 _TRUNC_STD = 0.87962566103423978  # std of a unit normal truncated to [-2, 2]
 
@@ -80,8 +79,8 @@ class Transition(nn.Module):
 
     def _weights(self):
         return (self.layernorm1.weight.detach().float(), self.layernorm1.bias.detach().float(),
-                bf16_of(self.linear_no_bias_a.weight), bf16_of(self.linear_no_bias_b.weight),
-                bf16_of(self.linear_no_bias.weight))
+                self.linear_no_bias_a.weight, self.linear_no_bias_b.weight,
+                self.linear_no_bias.weight)
 
     def forward_residual_(self, x: torch.Tensor) -> torch.Tensor:
         """x += Transition(x) in place (pair path of the Pairformer block)."""

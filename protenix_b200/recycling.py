@@ -27,7 +27,6 @@ from .layer_norm import LayerNorm
 from .pairformer import PairformerStack
 from .primitives import LinearNoBias
 from .triangular import _pair_input
-from .weights import bf16_of
 
 
 class RecyclingTrunk(nn.Module):
@@ -54,7 +53,7 @@ class RecyclingTrunk(nn.Module):
             z = torch.zeros_like(z_init)
         return ops.recycle_update(z, z_init, ln.weight.detach().float(),
                                   ln.bias.detach().float() if ln.bias is not None else None,
-                                  bf16_of(self.linear_no_bias_z_cycle.weight), eps=ln.eps, out=out)
+                                  self.linear_no_bias_z_cycle.weight, eps=ln.eps, out=out)
 
     def update_single(self, s: torch.Tensor, s_init: torch.Tensor) -> torch.Tensor:
         x = self.layernorm_s(s.float().contiguous())

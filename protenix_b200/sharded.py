@@ -37,7 +37,6 @@ import torch.distributed as dist
 import torch.nn.functional as F
 
 from . import ops
-from .weights import bf16_of
 
 
 # ----------------------------------------------------------------------------------------------
@@ -51,8 +50,8 @@ class CudaStages:
     def trimul_in_proj(self, mod, z, mask, incoming):
         f = self._f
         return ops.trimul_in_proj(z, mask, f(mod.layer_norm_in.weight), f(mod.layer_norm_in.bias),
-                                  bf16_of(mod.linear_a_p.weight), bf16_of(mod.linear_a_g.weight),
-                                  bf16_of(mod.linear_b_p.weight), bf16_of(mod.linear_b_g.weight), incoming,
+                                  mod.linear_a_p.weight, mod.linear_a_g.weight,
+                                  mod.linear_b_p.weight, mod.linear_b_g.weight, incoming,
                                   mod.layer_norm_in.eps)
 
     def trimul_contract(self, a, b):
@@ -61,13 +60,13 @@ class CudaStages:
     def trimul_out(self, mod, x, z):
         f = self._f
         return ops.trimul_out(x, z, f(mod.layer_norm_in.weight), f(mod.layer_norm_in.bias),
-                              f(mod.layer_norm_out.weight), f(mod.layer_norm_out.bias), bf16_of(mod.linear_z.weight),
-                              bf16_of(mod.linear_g.weight), mod.layer_norm_in.eps)
+                              f(mod.layer_norm_out.weight), f(mod.layer_norm_out.bias), mod.linear_z.weight,
+                              mod.linear_g.weight, mod.layer_norm_in.eps)
 
     def triatt_in_proj(self, mod, z, mask, ending=False):
         f, m = self._f, mod.mha
-        return ops.triatt_in_proj(z, mask, f(mod.layer_norm.weight), f(mod.layer_norm.bias), bf16_of(mod.linear.weight),
-                                  bf16_of(m.linear_q.weight), bf16_of(m.linear_k.weight), bf16_of(m.linear_v.weight),
+        return ops.triatt_in_proj(z, mask, f(mod.layer_norm.weight), f(mod.layer_norm.bias), mod.linear.weight,
+                                  m.linear_q.weight, m.linear_k.weight, m.linear_v.weight,
                                   mod.layer_norm.eps, mod.inf, ending)
 
     def triatt_flash(self, q, k, v, bias_full, mb):
@@ -75,26 +74,26 @@ class CudaStages:
 
     def triatt_out(self, mod, o, z, ending=False):
         f, m = self._f, mod.mha
-        return ops.triatt_out(o, z, f(mod.layer_norm.weight), f(mod.layer_norm.bias), bf16_of(m.linear_g.weight),
-                              bf16_of(m.linear_o.weight), mod.layer_norm.eps, ending)
+        return ops.triatt_out(o, z, f(mod.layer_norm.weight), f(mod.layer_norm.bias), m.linear_g.weight,
+                              m.linear_o.weight, mod.layer_norm.eps, ending)
 
     def transition(self, mod, z):
         f = self._f
         return ops.transition_rows(z, f(mod.layernorm1.weight), f(mod.layernorm1.bias),
-                                   bf16_of(mod.linear_no_bias_a.weight), bf16_of(mod.linear_no_bias_b.weight),
-                                   bf16_of(mod.linear_no_bias.weight), mod.layernorm1.eps)
+                                   mod.linear_no_bias_a.weight, mod.linear_no_bias_b.weight,
+                                   mod.linear_no_bias.weight, mod.layernorm1.eps)
 
     def pair_bias(self, mod, z):
         b = mod.layernorm_z.bias
         return ops.pair_bias_rows(z, self._f(mod.layernorm_z.weight), None if b is None else self._f(b),
-                                  bf16_of(mod.linear_nobias_z.weight), mod.layernorm_z.eps)
+                                  mod.linear_nobias_z.weight, mod.layernorm_z.eps)
 
     def single_layer_norm(self, ln, x):
         return ln(x)
 
     def recycle_update(self, ln, lin, z, z_init, out):
         b = ln.bias
-        return ops.recycle_update(z, z_init, self._f(ln.weight), None if b is None else self._f(b), bf16_of(lin.weight),
+        return ops.recycle_update(z, z_init, self._f(ln.weight), None if b is None else self._f(b), lin.weight,
                                   ln.eps, out=out)
 
 
@@ -282,7 +281,7 @@ class ShardedPairformer:
         """Pair bias [4][N/P u][ldm] of my rows -> rows me*nl.. of buffer ``bias`` [4][N][ldm] of every rank."""
         p, me = self.world, self.rank
         h, nl, ldm = bias_loc.shape
-        run = nl * ldm * 4
+        run = nl * ldm * bias_loc.element_size()
         px.put_all("bias", me * run, p * run, bias_loc, lambda d: 0, run, run, h)
 
     def _tri_att_start_peer(self, px: PeerExchange, mod, z_loc, mask_loc) -> None:
@@ -303,12 +302,12 @@ class ShardedPairformer:
         self._peer_rows_to_channels(px, b, "b", incoming)
         px.fence()
         del a, b
-        x = st.trimul_contract(px.local["a"].tensor((cp, n, ldn), torch.bfloat16),
-                               px.local["b"].tensor((cp, n, ldn), torch.bfloat16))
+        x = st.trimul_contract(px.local["a"].tensor((cp, n, ldn), torch.float16),
+                               px.local["b"].tensor((cp, n, ldn), torch.float16))
         self._peer_channels_to_rows(px, x)
         px.fence()
         del x
-        st.trimul_out(mod, px.local["x"].tensor((128, nl, ldn), torch.bfloat16), z_loc)
+        st.trimul_out(mod, px.local["x"].tensor((128, nl, ldn), torch.float16), z_loc)
 
     def _tri_att_end_peer(self, px: PeerExchange, mod, z_loc, mask_cols) -> None:
         """Ending node on the column slab zc [N i][N/P j][c] (the kernels address it as element (u=j, t=i))."""

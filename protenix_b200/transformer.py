@@ -18,7 +18,6 @@ import torch.nn.functional as F
 from . import ops
 from .layer_norm import LayerNorm
 from .primitives import Linear, LinearNoBias
-from .weights import bf16_of
 
 
 class _SingleAttention(nn.Module):
@@ -59,7 +58,7 @@ class AttentionPairBias(nn.Module):
         ln_b = self.layernorm_z.bias
         return ops.pair_bias_proj(z.contiguous(), self.layernorm_z.weight.detach().float(),
                                   ln_b.detach().float() if ln_b is not None else None,
-                                  bf16_of(self.linear_nobias_z.weight), eps=self.layernorm_z.eps)
+                                  self.linear_nobias_z.weight, eps=self.layernorm_z.eps)
 
     def forward(self, a: torch.Tensor, s: Optional[torch.Tensor], z: Optional[torch.Tensor],
                 bias: Optional[torch.Tensor] = None, **_unused) -> torch.Tensor:

@@ -19,7 +19,6 @@ import torch.nn as nn
 from . import ops
 from .layer_norm import LayerNorm
 from .primitives import trunc_normal_init_
-from .weights import bf16_of
 
 
 class OpenfoldLinear(nn.Linear):
@@ -100,9 +99,9 @@ class TriangleMultiplicativeUpdate(BaseTriangleMultiplicativeUpdate):
                 f"got c_z={self.c_z}, c_hidden={self.c_hidden} (no fallback path)")
         f = lambda p: p.detach().float()
         return (f(self.layer_norm_in.weight), f(self.layer_norm_in.bias), f(self.layer_norm_out.weight),
-                f(self.layer_norm_out.bias), bf16_of(self.linear_a_p.weight), bf16_of(self.linear_a_g.weight),
-                bf16_of(self.linear_b_p.weight), bf16_of(self.linear_b_g.weight), bf16_of(self.linear_z.weight),
-                bf16_of(self.linear_g.weight))
+                f(self.layer_norm_out.bias), self.linear_a_p.weight, self.linear_a_g.weight,
+                self.linear_b_p.weight, self.linear_b_g.weight, self.linear_z.weight,
+                self.linear_g.weight)
 
     def apply_(self, z: torch.Tensor, mask: Optional[torch.Tensor]) -> torch.Tensor:
         """z += update, in place, on a contiguous [N,N,128] tensor (used by the block)."""
@@ -168,8 +167,8 @@ class TriangleAttention(nn.Module):
                 f"{ops.D_HEAD_PAIR}; got c_in={self.c_in}, {self.no_heads} heads x {self.c_hidden} (no fallback path)")
         m = self.mha
         return (self.layer_norm.weight.detach().float(), self.layer_norm.bias.detach().float(),
-                bf16_of(self.linear.weight), bf16_of(m.linear_q.weight), bf16_of(m.linear_k.weight),
-                bf16_of(m.linear_v.weight), bf16_of(m.linear_g.weight), bf16_of(m.linear_o.weight))
+                self.linear.weight, m.linear_q.weight, m.linear_k.weight,
+                m.linear_v.weight, m.linear_g.weight, m.linear_o.weight)
 
     def apply_(self, z: torch.Tensor, mask: Optional[torch.Tensor], ending: bool) -> torch.Tensor:
         """z += update in place; ``ending`` selects attention along columns of the *untransposed* z,

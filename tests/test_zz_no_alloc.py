@@ -30,7 +30,10 @@ def _args(n, seed, zdtype):
     mask = (torch.rand(n, n, generator=g) > 0.15).float().cuda()
     vec = lambda s: (s * torch.randn(128, generator=g)).cuda()
     ln = [1 + vec(0.1), vec(0.1), 1 + vec(0.1), vec(0.1)]
-    ws = [(torch.randn(128, 128, generator=g) / 128 ** 0.5).to(torch.bfloat16).cuda() for _ in range(6)]
+    # 16-bit weights as the C ABI wants them: in the format of the rows they multiply (bf16 rows as stored, fp32 rows
+    # as fp16), except w_z (index 4), which multiplies the fp16 intermediate x
+    zfmt = torch.bfloat16 if zdtype == torch.bfloat16 else torch.float16
+    ws = [(torch.randn(128, 128, generator=g) / 128 ** 0.5).to(torch.float16 if i == 4 else zfmt).cuda() for i in range(6)]
     return z, mask, ln, ws
 
 
