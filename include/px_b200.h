@@ -13,9 +13,13 @@
  *   - N            number of tokens; the pair tensor z is [N][N][128], row-major, channel last.
  *   - z_dtype      storage type of the residual stream: PX_F32 or PX_BF16.  All matrix products
  *                  take 16-bit operands and accumulate in fp32.  Rows of a bf16 z are multiplied as
- *                  they are stored (bf16 x bf16); rows of an fp32 z are standardised and rounded to
- *                  fp16 (fp16 x fp16: a standardised row cannot leave the fp16 range, and fp16 keeps
- *                  three more mantissa bits).  Every intermediate 16-bit tensor (a, b, x, q, k, v, o)
+ *                  they are stored (bf16 x bf16).  For an fp32 z the kernels multiply a standardised
+ *                  fp16 copy of the rows, zn = (z - mean) * rstd, written by px_standardise_rows
+ *                  (fp16 x fp16: a standardised row cannot leave the fp16 range, and fp16 keeps three
+ *                  more mantissa bits).  The composite entry points make that copy in their
+ *                  workspace; the stage entry points take it as an argument: stages that only
+ *                  read LayerNorm'd rows accept PX_BF16 (the rows of z) or PX_F16 (the copy),
+ *                  stages that also add the residual take z (PX_BF16 or PX_F32) and, for PX_F32, zn.  Every intermediate 16-bit tensor (a, b, x, q, k, v, o)
  *                  is fp16 in both cases.
  *   - weights      16-bit, row-major [out_features][in_features] exactly as the reference's
  *                  nn.Linear.weight, cast by the caller: px_w16 parameters take the format of the z
@@ -88,6 +92,13 @@ PX_API int64_t px_ld_mask(int64_t n);
 PX_API int32_t px_layer_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* invvar,
                           int64_t rows, int64_t cols, float eps, int32_t dtype, void* stream);
 
+/* ---- Standardised copy of fp32 rows --------------------------------------------------------
+ * zn[row] = fp16((z[row] - mean) * rsqrt(var + eps)) over `rows` rows of 128 channels: LayerNorm without scale and
+ * offset (the consumers fold those into their weights).  One copy serves every stage that normalises the same z with
+ * the same eps.  HBM-bound, 768 bytes per row.  No counterpart in the reference (its LayerNorm kernel writes the
+ * normalised tensor in the input's type, protenix/model/layer_norm/kernel/layer_norm_cuda_kernel.cu:145-388). */
+PX_API int32_t px_standardise_rows(const float* z, px_f16* zn, int64_t rows, float eps, void* stream);
+
 /* ---- Triangle multiplication (outgoing / incoming) ---------------------------------------
  * Stage 1: zn = LN(z); a = mask * sigmoid(W_ag zn) * (W_ap zn); b likewise.  a and b are
  * written channel-major, contraction index contiguous: a[c][i][k] (row stride ld), zero in
@@ -131,9 +142,10 @@ PX_API int32_t px_set_wait_limit_cycles(int64_t cycles);
  * still set it writes 2 and returns at once.  Exercises the give-up path without faulting the GPU.  No counterpart in
  * the reference. */
 PX_API int32_t px_selftest_wait_timeout(uint32_t* out_word, void* stream);
-/* Stage 3: z_out = [z_in +] W_z LN_out(x) * sigmoid(W_g LN_in(z_in)).  z_out may alias z_in.
+/* Stage 3: z_out = [z_in +] W_z LN_out(x) * sigmoid(W_g LN_in(z_in)).  z_out may alias z_in.  zn: the standardised
+ * copy of z_in when z_dtype is PX_F32 (NULL otherwise).
  * Replaces protenix/model/triangular/triangular.py:559-565. */
-PX_API int32_t px_trimul_out(const px_f16* x, const void* z_in, void* z_out, int32_t z_dtype, const float* ln_in_w,
+PX_API int32_t px_trimul_out(const px_f16* x, const void* z_in, const px_f16* zn, void* z_out, int32_t z_dtype, const float* ln_in_w,
                       const float* ln_in_b, const float* ln_out_w, const float* ln_out_b, const px_f16* w_z,
                       const px_w16* w_g, int64_t n_i, int64_t n_j, int64_t ld, int32_t add_residual, float eps,
                       void* stream);
@@ -152,8 +164,8 @@ PX_API int32_t px_triangle_multiplication(const void* z_in, void* z_out, int32_t
 /* Triangle multiplication without any workspace argument, for callers that must not or cannot
  * allocate device memory: a plug-in running inside a host application that has handed all device
  * memory to its own pool (cudaMalloc then fails), or a latency-critical thread that must avoid
- * cudaMalloc/cudaFree because they synchronise the device.  The scratch for a, b and x is a
- * 12 MiB array inside the library image (held by every GPU that loads the library until the
+ * cudaMalloc/cudaFree because they synchronise the device.  The scratch for a, b, x and the
+ * standardised copy of an fp32 z is a 16 MiB array inside the library image (held by every GPU that loads the library until the
  * process exits), so N is limited to PX_STATIC_MAX_N = 128; a larger N returns PX_ERR_TOO_LARGE.
  * The call itself allocates nothing.  Its first call on a device looks up the array's device
  * address (cudaGetSymbolAddress, with that device current); make that first call before any stream
@@ -195,9 +207,10 @@ PX_API int32_t px_triatt_flash(const px_f16* q, const px_f16* k, const px_f16* v
                         void* stream);
 PX_API int64_t px_triatt_flash_scratch_bytes(int64_t n_u, int64_t n);
 /* Stage 3: z_out(u,t) = [z_in(u,t) +] W_o (o[u][t] * sigmoid(W_g LN(z_in(u,t)))), where (u,t)
- * addresses z[u][t] (starting) or z[t][u] (ending).  z_out may alias z_in.
+ * addresses z[u][t] (starting) or z[t][u] (ending).  z_out may alias z_in.  zn: the standardised copy of z_in
+ * (same layout) when z_dtype is PX_F32 (NULL otherwise).
  * Replaces Attention._wrap_up, protenix/model/triangular/layers.py:384-398. */
-PX_API int32_t px_triatt_out(const px_f16* o, const void* z_in, void* z_out, int32_t z_dtype, const float* ln_w,
+PX_API int32_t px_triatt_out(const px_f16* o, const void* z_in, const px_f16* zn, void* z_out, int32_t z_dtype, const float* ln_w,
                       const float* ln_b, const px_w16* w_g, const px_f16* w_o, int64_t n_u, int64_t n_t, int32_t ending,
                       int32_t add_residual, float eps, void* stream);
 PX_API int64_t px_triatt_workspace_bytes(int64_t n);
@@ -219,14 +232,16 @@ PX_API int32_t px_transition(const void* x_in, void* x_out, int32_t dtype, const
                       float eps, void* stream);
 
 /* ---- Pair bias for the single-representation attention ----------------------------------
- * out[h][row] = (W LN(z[row]))[h] for h < n_heads (<= 16), fp32; ln_b may be NULL.
+ * out[h][row] = (W LN(z[row]))[h] for h < n_heads (<= 16), fp32; ln_b may be NULL.  z_dtype PX_BF16 (rows of z) or
+ * PX_F16 (standardised copy of an fp32 z).
  * Replaces protenix/model/modules/transformer.py:185-188. */
 PX_API int32_t px_pair_bias_proj(const void* z, int32_t z_dtype, const float* ln_w, const float* ln_b, const px_w16* w,
                           float* out, int64_t rows, int32_t n_heads, float eps, void* stream);
 
 /* ---- Recycling update of the pair representation ------------------------------------------
  * out[row] = z_init[row] + W LN(z[row]) for `rows` rows of 128 channels (W [128][128] in the format of z,
- * z, z_init and out of one dtype, PX_BF16 or PX_F32); ln_b may be NULL; out may be z or z_init.
+ * z_init and out of one dtype, PX_BF16 or PX_F32; z the bf16 rows, or for PX_F32 their standardised fp16 copy);
+ * ln_b may be NULL; out may be z or z_init.
  * Replaces protenix/model/protenix.py:246
  * (z = z_init + linear_no_bias_z_cycle(layernorm_z_cycle(z))). */
 PX_API int32_t px_recycle_update(const void* z, const void* z_init, void* out, int32_t z_dtype, const float* ln_w,

@@ -10,7 +10,8 @@ import os
 from ctypes import c_char_p, c_float, c_int32, c_int64, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libpx_b200.so")
+# PX_B200_LIB names another build of the same library (e.g. one compiled with different options)
+LIB_PATH = os.environ.get("PX_B200_LIB") or os.path.join(HERE, "libpx_b200.so")
 
 PX_F32, PX_BF16, PX_F16 = 0, 1, 2
 
@@ -29,7 +30,8 @@ SIGNATURES = {
     "px_device_error_detail": (I32, [P, P]),
     "px_set_wait_limit_cycles": (I32, [I64]),
     "px_selftest_wait_timeout": (I32, [P, P]),
-    "px_trimul_out": (I32, [P, P, P, I32, P, P, P, P, P, P, I64, I64, I64, I32, F, P]),
+    "px_standardise_rows": (I32, [P, P, I64, F, P]),
+    "px_trimul_out": (I32, [P, P, P, P, I32, P, P, P, P, P, P, I64, I64, I64, I32, F, P]),
     "px_trimul_workspace_bytes": (I64, [I64]),
     "px_triangle_multiplication": (I32, [P, P, I32, P, P, P, P, P, P, P, P, P, P, P, P, I64, I64, I32, I32, F, P]),
     "px_triangle_multiplication_static": (I32, [P, P, I32, P, P, P, P, P, P, P, P, P, P, P, I64, I32, I32, F, P]),
@@ -37,7 +39,7 @@ SIGNATURES = {
     "px_triatt_in_proj": (I32, [P, I32, P, P, P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I32, F, F, P]),
     "px_triatt_flash": (I32, [P, P, P, P, P, P, P, I64, I64, I64, P]),
     "px_triatt_flash_scratch_bytes": (I64, [I64, I64]),
-    "px_triatt_out": (I32, [P, P, P, I32, P, P, P, P, I64, I64, I32, I32, F, P]),
+    "px_triatt_out": (I32, [P, P, P, P, I32, P, P, P, P, I64, I64, I32, I32, F, P]),
     "px_triatt_workspace_bytes": (I64, [I64]),
     "px_triangle_attention": (I32, [P, P, I32, P, P, P, P, P, P, P, P, P, P, I64, I64, I32, I32, F, F, P]),
     "px_transition": (I32, [P, P, I32, P, P, P, P, P, I64, I32, F, P]),

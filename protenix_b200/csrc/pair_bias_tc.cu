@@ -9,8 +9,6 @@
 //   warps 4..7  one thread per row: statistics, correction row, the row's rstd;
 //   warp 8      TMA producer; warp 9 MMA issuer of the projection (M=128, N=16), warp 10 of the statistics product.
 // Every mbarrier wait is bounded.
-#include <cstring>
-
 #include "px_rowpipe.cuh"
 
 namespace px {
@@ -38,13 +36,12 @@ static_assert(PbLayout::a % 1024 == 0, "tile ring must keep the swizzle alignmen
 
 static __device__ float g_zero_beta[128];      // stands in for a LayerNorm without bias
 
-template <typename Tz>
+// kF16: the rows are the standardised fp16 copy of an fp32 pair tensor (fp16 weights); otherwise bf16 rows of z.
+template <bool kF16>
 __global__ void __launch_bounds__(kPbThreads, 1)
-pair_bias_tc_kernel(const __grid_constant__ CUtensorMap map_z, const Tz* __restrict__ z, const float* __restrict__ ln_w,
+pair_bias_tc_kernel(const __grid_constant__ CUtensorMap map_z, const float* __restrict__ ln_w,
                     const float* __restrict__ ln_b, const bf16* __restrict__ w, float* __restrict__ out, long long rows,
                     int n_heads, float eps, int n_tiles) {
-  constexpr bool kTma = sizeof(Tz) == 2;
-  constexpr bool kF16 = !kTma;                           // fp32 rows are multiplied as fp16 against fp16 weights
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   PbBars& bars = *reinterpret_cast<PbBars*>(sm + PbLayout::bars);
@@ -63,7 +60,7 @@ pair_bias_tc_kernel(const __grid_constant__ CUtensorMap map_z, const Tz* __restr
 
   if (cta_skip_after_error()) return;   // an earlier bounded wait gave up: do not start new work
   if (threadIdx.x == 0) {
-    tile_bars_init(bars.tile, kTma, 2);
+    tile_bars_init(bars.tile, 2);
     mbar_init(&bars.acc_full, 1);
     mbar_init(&bars.acc_free, 4);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -95,7 +92,7 @@ pair_bias_tc_kernel(const __grid_constant__ CUtensorMap map_z, const Tz* __restr
   if (warp >= 8) {
     if (lane == 0) {
       if (warp == 8) {
-        if (kTma) tile_producer_loop(ctx, &map_z);
+        tile_producer_loop(ctx, &map_z);
       } else if (warp == 9) {
         tile_product_loop(ctx, tmem_base, smem_u32(sm + PbLayout::w), kPbWPanel, smem_u32(sm + PbLayout::wx),
                           umma_idesc_16(128, 16, kF16, kF16), &bars.acc_full, &bars.acc_free);
@@ -105,7 +102,7 @@ pair_bias_tc_kernel(const __grid_constant__ CUtensorMap map_z, const Tz* __restr
     }
   } else if (warp >= 4) {
     float* scale = reinterpret_cast<float*>(sm + PbLayout::scale);
-    tile_stats_loop<Tz>(ctx, z, eps, tmem_base + kPbColGram, warp - 4, lane,
+    tile_stats_loop<kF16>(ctx, eps, tmem_base + kPbColGram, warp - 4, lane,
                         [&](int k, int u, int t, int r, float rstd) { scale[(k % kTileSlots) * 128 + r] = rstd; });
   } else {
     // ------------------------------------------------------------------ epilogue
@@ -143,23 +140,19 @@ pair_bias_tc_kernel(const __grid_constant__ CUtensorMap map_z, const Tz* __restr
 
 PX_DEFINE_FAMILY_HOOKS(pair_bias)
 
-template <typename Tz>
+template <bool kF16>
 static int32_t launch_pair_bias(const void* z, const float* ln_w, const float* ln_b, const px_bf16* w, float* out,
                                 int64_t rows, int32_t n_heads, float eps, cudaStream_t st) {
   CUtensorMap mz;
-  if (sizeof(Tz) == 2) {
-    if (!make_map_3d(&mz, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, z, 128, (uint64_t)rows, 1, 256, (uint64_t)rows * 256, 64, 128,
-                     CU_TENSOR_MAP_SWIZZLE_128B, 1))
-      return PX_ERR_LAUNCH;
-  } else {
-    memset(&mz, 0, sizeof(mz));
-  }
+  if (!make_map_3d(&mz, kF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, z, 128, (uint64_t)rows, 1,
+                   256, (uint64_t)rows * 256, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B, 1))
+    return PX_ERR_LAUNCH;
   const size_t smem = PbLayout::total + 1024;
-  if (cudaFuncSetAttribute(pair_bias_tc_kernel<Tz>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+  if (cudaFuncSetAttribute(pair_bias_tc_kernel<kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return PX_ERR_LAUNCH;
   const int64_t n_tiles = (rows + 127) / 128;
   const int grid = (int)(n_tiles < sm_count() ? n_tiles : sm_count());
-  pair_bias_tc_kernel<Tz><<<grid, kPbThreads, smem, st>>>(mz, (const Tz*)z, ln_w, ln_b, (const bf16*)w, out, (long long)rows,
+  pair_bias_tc_kernel<kF16><<<grid, kPbThreads, smem, st>>>(mz, ln_w, ln_b, (const bf16*)w, out, (long long)rows,
                                                           n_heads, eps, (int)n_tiles);
   return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
 }
@@ -176,7 +169,7 @@ extern "C" int32_t px_pair_bias_proj(const void* z, int32_t z_dtype, const float
   if (((uintptr_t)z | (uintptr_t)w | (uintptr_t)ln_w | (uintptr_t)ln_b) & 15) return PX_ERR_BAD_ARG;
   if (rows == 0) return PX_OK;
   if (rows > 0x3fffffff) return PX_ERR_UNSUPPORTED;
-  if (z_dtype == PX_F32) return launch_pair_bias<float>(z, ln_w, ln_b, w, out, rows, n_heads, eps, (cudaStream_t)stream);
-  if (z_dtype == PX_BF16) return launch_pair_bias<bf16>(z, ln_w, ln_b, w, out, rows, n_heads, eps, (cudaStream_t)stream);
+  if (z_dtype == PX_F16) return launch_pair_bias<true>(z, ln_w, ln_b, w, out, rows, n_heads, eps, (cudaStream_t)stream);
+  if (z_dtype == PX_BF16) return launch_pair_bias<false>(z, ln_w, ln_b, w, out, rows, n_heads, eps, (cudaStream_t)stream);
   return PX_ERR_UNSUPPORTED;
 }

@@ -1,9 +1,11 @@
 // Pieces shared by the persistent, TMA-fed row kernels (LayerNorm'd 128-channel rows times resident weights).
 //
-// Operand formats.  Rows stored as bf16 are multiplied as they are, against bf16 weights.  Rows stored as fp32 are
-// standardised and rounded to fp16 (a standardised row lies within +-sqrt(128), so fp16's range is safe and its three
-// extra mantissa bits cut the operand rounding error eightfold), against fp16 weights.  `kF16` names the format of a
-// product's operands; the correction step below is a separate MMA and always takes bf16 head/tail pairs.
+// Operand formats.  Rows of a bf16 pair tensor are multiplied as they are stored, against bf16 weights.  For an fp32
+// pair tensor the kernels read a standardised fp16 copy of the rows, (x - mean) * rstd, that px_standardise_rows
+// writes (a standardised row lies within +-sqrt(128), so fp16's range is safe and its three extra mantissa bits cut
+// the operand rounding error eightfold), against fp16 weights; such rows carry mean 0 and deviation 1, so their
+// correction step only adds the beta term.  `kF16` names the format of a product's operands; the correction step
+// is a separate MMA and always takes bf16 head/tail pairs.
 //
 // LayerNorm is not applied to the operand.  With W' = W diag(gamma), s = W' 1, t = W beta and std = 1/rstd,
 //     W LN(x) = rstd * ( W' x - mean * s + std * t ),
@@ -11,7 +13,6 @@
 // operand by TMA without passing through registers).  The two correction terms ride along as one extra K step of 16:
 // the row side holds (-mean, std) and the weight side (s, t), each split into a bf16 head and tail so that the
 // products carry about 17 bits.  What is left for the epilogue is one multiplication by the row's rstd.
-// Rows stored as fp32 are standardised ((x - mean) * rstd) while they are converted to fp16, and then carry mean 0, std 1.
 #pragma once
 #include "px_tcgen05.cuh"
 
@@ -173,60 +174,17 @@ __device__ __forceinline__ void row_stats_from_operand(const unsigned char* op, 
   rstd = rsqrtf(fmaxf(q * (1.0f / kC) - m * m, 0.f) + eps);
 }
 
-// Asks the L2 cache for 32 fp32 rows (512 bytes each) ahead of their use: one 128-byte line per lane and request,
-// four requests per warp.  The converting warps keep only four rows in flight in registers, which covers an L2 hit
-// but not a trip to HBM; with the next tile requested a whole tile period ahead the loads find their lines in L2.
-template <typename RowPtr>
-__device__ __forceinline__ void prefetch_rows_l2(int lane, RowPtr row_ptr) {
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int line = 32 * j + lane;
-    const float* src = row_ptr(line >> 2);
-    if (src) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(src + 32 * (line & 3)));
-  }
-}
-
-// 32 fp32 rows from global memory -> standardised fp16 rows r0..r0+31 of the operand at `op`, by one warp: a row is
-// 512 contiguous bytes, so the warp reads it with one coalesced 16-byte load per lane, reduces mean and variance with
-// shuffles (two passes over the registers) and writes eight bytes per lane.  row_ptr(i) gives the address of row
-// r0 + i or nullptr for a row of zeros.  Four rows are in flight at a time to cover the load latency.
-template <typename RowPtr>
-__device__ __forceinline__ void standardise_rows_to_operand(unsigned char* op, int r0, int lane, float eps, int panel_bytes,
-                                                            RowPtr row_ptr) {
-#pragma unroll 1
-  for (int i0 = 0; i0 < 32; i0 += 4) {
-    float4 v[4];
-    bool have[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float* src = row_ptr(i0 + j);
-      have[j] = src != nullptr;
-      v[j] = have[j] ? __ldg(reinterpret_cast<const float4*>(src) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float mean = warp_sum((v[j].x + v[j].y) + (v[j].z + v[j].w)) * (1.0f / kC);
-      const float dx = v[j].x - mean, dy = v[j].y - mean, dz = v[j].z - mean, dw = v[j].w - mean;
-      const float var = warp_sum(fmaf(dx, dx, dy * dy) + fmaf(dz, dz, dw * dw)) * (1.0f / kC);
-      const float rstd = have[j] ? rsqrtf(var + eps) : 0.f;
-      const int r = r0 + i0 + j;
-      *reinterpret_cast<uint2*>(op + operand_piece_offset(r, lane >> 1, panel_bytes) + (lane & 1) * 8) =
-          make_uint2(pack_f16x2(dx * rstd, dy * rstd), pack_f16x2(dz * rstd, dw * rstd));
-    }
-  }
-}
-
 // ---------------------------------------------------------------------------------------------------------------
 // Row tiles: the part of the pipeline that is the same for every kernel that consumes LayerNorm'd pair rows.
 // A tile is 128 pair elements (one u, 128 consecutive t); element (u, t) is row u*n_t + t of z, or row t*n_u + u when
 // the two indices are exchanged (`swap`).  A stage of the ring holds the tile as two k panels of 144 rows (the
 // last 16 rows are ones, see below) and the tile's correction panel.
-//   * producer thread: TMA loads of bf16 rows (fp32 rows are standardised and converted to fp16 by the statistics
-//     warps instead, a warp per row);
+//   * producer thread: TMA loads of the rows (bf16 rows of z, or the standardised fp16 copy of an fp32 z);
 //   * statistics issuer thread: Z Z^T | Z 1 (M=128, N=144) into tensor memory: the diagonal holds each row's sum
 //     of squares and columns 128..143 its plain sum;
 //   * statistics threads (one per row): variance = E[x^2] - mean^2 in fp32 (accurate while |mean| is not orders of
-//     magnitude above the deviation), correction row (-mean, std), and whatever the kernel wants per row.
+//     magnitude above the deviation), correction row (-mean, std), and whatever the kernel wants per row.  For
+//     standardised rows the statistics are known: (0, 1).
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kTileStages = 2;
 constexpr int kTileSlots = kTileStages + 1;    // per-row scale slots: read by the epilogue after the stage is freed
@@ -248,9 +206,9 @@ struct TileCtx {
   int first_tile, tile_step, n_tiles, tiles_t, n_u, n_t, swap;
 };
 
-__device__ __forceinline__ void tile_bars_init(TileBars& b, bool tma, int issuers) {
+__device__ __forceinline__ void tile_bars_init(TileBars& b, int issuers) {
   for (int s = 0; s < kTileStages; ++s) {
-    mbar_init(&b.raw_full[s], tma ? 1 : 4);
+    mbar_init(&b.raw_full[s], 1);
     mbar_init(&b.a_ready[s], 4);
     mbar_init(&b.a_empty[s], issuers);
   }
@@ -303,38 +261,18 @@ __device__ __forceinline__ void tile_gram_loop(const TileCtx& c, uint32_t tmem_g
 }
 
 // Four warps, one thread per row (`qw` = warp's lane quarter, 0..3).  per_row(k, u, t, r, rstd) is called once per
-// tile and row with the row's 1/std, before a_ready is signalled.
-template <typename Tz, typename PerRow>
-__device__ __forceinline__ void tile_stats_loop(const TileCtx& c, const Tz* __restrict__ z, float eps, uint32_t tmem_gram,
-                                                int qw, int lane, PerRow per_row) {
-  constexpr bool kTma = sizeof(Tz) == 2;
+// tile and row with the row's 1/std, before a_ready is signalled.  `kStandardised`: the rows are a standardised copy
+// (mean 0, deviation 1 by construction), so the correction row is (0, 1) and the factor is 1.
+template <bool kStandardised, typename PerRow>
+__device__ __forceinline__ void tile_stats_loop(const TileCtx& c, float eps, uint32_t tmem_gram, int qw, int lane,
+                                                PerRow per_row) {
   const int r = 32 * qw + lane;
   const uint32_t t_gram = tmem_gram + ((uint32_t)(32 * qw) << 16);
   int k = 0;
   bool ok = true;
   for (int tile = c.first_tile; tile < c.n_tiles; tile += c.tile_step, ++k) {
-    const int s = k % kTileStages, n = k / kTileStages;
+    const int s = k % kTileStages;
     const int u = tile / c.tiles_t, t = (tile % c.tiles_t) * 128 + r;
-    if (!kTma) {
-      // fp32 rows: standardised while they are converted into the operand
-      ok = mbar_wait(&c.bars->a_empty[s], (n & 1) ^ 1, 16u);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      auto rows_of = [&](int tl) {                         // this warp's 32 rows of tile tl
-        const int uu = tl / c.tiles_t, t_first = (tl % c.tiles_t) * 128 + 32 * qw;
-        return [=](int i) -> const float* {
-          const int tt = t_first + i;
-          if (tt >= c.n_t) return nullptr;
-          const size_t pair = c.swap ? ((size_t)tt * c.n_u + uu) : ((size_t)uu * c.n_t + tt);
-          return reinterpret_cast<const float*>(z) + pair * kC;
-        };
-      };
-      if (tile + c.tile_step < c.n_tiles) prefetch_rows_l2(lane, rows_of(tile + c.tile_step));
-      standardise_rows_to_operand(c.tiles + s * kTileBytes, 32 * qw, lane, eps, kTilePanel, rows_of(tile));
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&c.bars->raw_full[s]);
-    }
     ok = mbar_wait(&c.bars->gram_full, k & 1, 16u);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) break;
@@ -346,11 +284,15 @@ __device__ __forceinline__ void tile_stats_loop(const TileCtx& c, const Tz* __re
     tc_fence_before();
     __syncwarp();
     if (lane == 0) mbar_arrive(&c.bars->gram_free);
-    const float mean = __uint_as_float(sums[0]) * (1.0f / kC);
-    const float var = fmaxf(select_own(diag, lane) * (1.0f / kC) - mean * mean, 0.f);
-    const float rstd = rsqrtf(var + eps);
+    float mean = 0.f, std = 1.f, rstd = 1.f;
+    if (!kStandardised) {
+      mean = __uint_as_float(sums[0]) * (1.0f / kC);
+      const float var = fmaxf(select_own(diag, lane) * (1.0f / kC) - mean * mean, 0.f);
+      rstd = rsqrtf(var + eps);
+      std = sqrtf(var + eps);
+    }
     // rstd * (W'x - mean * s + std * t): the row side of the correction step holds (-mean, std)
-    write_correction_row(c.extras + s * kTileExtra, r, -mean, sqrtf(var + eps), false);
+    write_correction_row(c.extras + s * kTileExtra, r, -mean, std, false);
     per_row(k, u, t, r, rstd);
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     __syncwarp();

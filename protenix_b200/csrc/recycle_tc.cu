@@ -45,11 +45,11 @@ static __device__ float g_rc_zero_beta[128];   // stands in for a LayerNorm with
 template <typename Tz>
 __global__ void __launch_bounds__(kRcThreads, 1)
 recycle_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_init,
-                  const __grid_constant__ CUtensorMap map_out, const Tz* __restrict__ z, const Tz* z_init, Tz* out,
+                  const __grid_constant__ CUtensorMap map_out, const Tz* z_init, Tz* out,
                   const float* __restrict__ ln_w, const float* __restrict__ ln_b, const bf16* __restrict__ w,
                   long long rows, float eps, int n_tiles) {
-  constexpr bool kTma = sizeof(Tz) == 2;
-  constexpr bool kF16 = !kTma;                           // fp32 rows are multiplied as fp16 against fp16 weights
+  constexpr bool kTma = sizeof(Tz) == 2;               // bf16: z_init and out go through shared memory and TMA
+  constexpr bool kF16 = !kTma;                           // fp32: the rows of z arrive as a standardised fp16 copy
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   RcBars& bars = *reinterpret_cast<RcBars*>(sm + RcLayout::bars);
@@ -68,7 +68,7 @@ recycle_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_consta
 
   if (cta_skip_after_error()) return;   // an earlier bounded wait gave up: do not start new work
   if (threadIdx.x == 0) {
-    tile_bars_init(bars.tile, kTma, 2);
+    tile_bars_init(bars.tile, 2);
     mbar_init(&bars.acc_full, 1);
     mbar_init(&bars.acc_free, 8);
     for (int s = 0; s < kTileStages; ++s) {
@@ -95,15 +95,15 @@ recycle_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_consta
   if (warp >= 12) {
     if (lane == 0) {
       if (warp == 12) {
-        if (kTma) {
-          // z tile into the operand ring, z_init tile into the output ring
-          int k = 0;
-          for (int tile = ctx.first_tile; tile < n_tiles; tile += ctx.tile_step, ++k) {
-            const int s = k % kTileStages, n = k / kTileStages;
-            if (!mbar_wait(&bars.tile.a_empty[s], (n & 1) ^ 1, 1u)) break;
-            mbar_expect_tx(&bars.tile.raw_full[s], kOperandBytes);
-            const uint32_t dst = smem_u32(ctx.tiles + s * kTileBytes);
-            for (int p = 0; p < 2; ++p) tma_load_3d(dst + p * kTilePanel, &map_z, &bars.tile.raw_full[s], 64 * p, tile * 128, 0);
+        // z tile into the operand ring and (bf16) the z_init tile into the output ring
+        int k = 0;
+        for (int tile = ctx.first_tile; tile < n_tiles; tile += ctx.tile_step, ++k) {
+          const int s = k % kTileStages, n = k / kTileStages;
+          if (!mbar_wait(&bars.tile.a_empty[s], (n & 1) ^ 1, 1u)) break;
+          mbar_expect_tx(&bars.tile.raw_full[s], kOperandBytes);
+          const uint32_t dst = smem_u32(ctx.tiles + s * kTileBytes);
+          for (int p = 0; p < 2; ++p) tma_load_3d(dst + p * kTilePanel, &map_z, &bars.tile.raw_full[s], 64 * p, tile * 128, 0);
+          if (kTma) {
             if (!mbar_wait(&bars.res_empty[s], (n & 1) ^ 1, 1u)) break;
             mbar_expect_tx(&bars.res_full[s], kOperandBytes);
             const uint32_t rdst = smem_u32(sm + RcLayout::res + s * kOperandBytes);
@@ -119,7 +119,7 @@ recycle_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_consta
     }
   } else if (warp >= 8) {
     float* scale = reinterpret_cast<float*>(sm + RcLayout::scale);
-    tile_stats_loop<Tz>(ctx, z, eps, tmem_base + kRcColGram, warp - 8, lane,
+    tile_stats_loop<kF16>(ctx, eps, tmem_base + kRcColGram, warp - 8, lane,
                         [&](int k, int u, int t, int r, float rstd) { scale[(k % kTileSlots) * 128 + r] = rstd; });
   } else {
     // ------------------------------------------------------------------ output rows
@@ -206,15 +206,18 @@ template <typename Tz>
 static int32_t launch_recycle(const void* z, const void* z_init, void* out, const float* ln_w, const float* ln_b,
                               const px_bf16* w, int64_t rows, float eps, cudaStream_t st) {
   CUtensorMap mz, mi, mo;
+  // the rows of z: bf16 as stored, or the standardised fp16 copy
+  if (!make_map_3d(&mz, sizeof(Tz) == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, z, 128,
+                   (uint64_t)rows, 1, 256, (uint64_t)rows * 256, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B, 1))
+    return PX_ERR_LAUNCH;
   if (sizeof(Tz) == 2) {
-    const void* base[3] = {z, z_init, out};
-    CUtensorMap* maps[3] = {&mz, &mi, &mo};
-    for (int i = 0; i < 3; ++i)
+    const void* base[2] = {z_init, out};
+    CUtensorMap* maps[2] = {&mi, &mo};
+    for (int i = 0; i < 2; ++i)
       if (!make_map_3d(maps[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base[i], 128, (uint64_t)rows, 1, 256, (uint64_t)rows * 256,
                        64, 128, CU_TENSOR_MAP_SWIZZLE_128B, 1))
         return PX_ERR_LAUNCH;
   } else {
-    memset(&mz, 0, sizeof(mz));
     memset(&mi, 0, sizeof(mi));
     memset(&mo, 0, sizeof(mo));
   }
@@ -223,7 +226,7 @@ static int32_t launch_recycle(const void* z, const void* z_init, void* out, cons
     return PX_ERR_LAUNCH;
   const int64_t n_tiles = (rows + 127) / 128;
   const int grid = (int)(n_tiles < sm_count() ? n_tiles : sm_count());
-  recycle_tc_kernel<Tz><<<grid, kRcThreads, smem, st>>>(mz, mi, mo, (const Tz*)z, (const Tz*)z_init, (Tz*)out, ln_w, ln_b,
+  recycle_tc_kernel<Tz><<<grid, kRcThreads, smem, st>>>(mz, mi, mo, (const Tz*)z_init, (Tz*)out, ln_w, ln_b,
                                                         (const bf16*)w, (long long)rows, eps, (int)n_tiles);
   return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
 }

@@ -15,10 +15,8 @@
 //   warps 16..19  one thread per row: statistics, correction row, scale pair, mask bias.
 //   warp 20       TMA producer; warps 21, 22 MMA issuers of the two products (N = 128 and N = 80), warp 23 of the
 //                 statistics product.
-// Algorithmic HBM traffic per pair element: 128*sizeof(Tz) + 4 read, 3*256 + 16 + 4 written.  Every wait is bounded.
+// Algorithmic HBM traffic per pair element: 256 + 4 read, 3*256 + 16 + 4 written.  Every wait is bounded.
 #include <math_constants.h>
-
-#include <cstring>
 
 #include "px_rowpipe.cuh"
 
@@ -50,16 +48,15 @@ struct AiLayout {
 };
 static_assert(AiLayout::a % 1024 == 0, "tile ring must keep the swizzle alignment");
 
-template <typename Tz>
+// kF16: the rows are the standardised fp16 copy of an fp32 pair tensor (fp16 weights); otherwise bf16 rows of z.
+template <bool kF16>
 __global__ void __launch_bounds__(kAiThreads, 1)
 triatt_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_v,
-                    const Tz* __restrict__ z, const float* __restrict__ mask, const float* __restrict__ ln_w,
+                    const float* __restrict__ mask, const float* __restrict__ ln_w,
                     const float* __restrict__ ln_b, const bf16* __restrict__ w_q, const bf16* __restrict__ w_k,
                     const bf16* __restrict__ w_v, const bf16* __restrict__ w_bias, bf16* __restrict__ q_out,
                     bf16* __restrict__ k_out, float* __restrict__ bias_out, float* __restrict__ mb_out, int n_u, int n,
                     int ldm, int swap, float eps, float inf, int tiles_t, int n_tiles) {
-  constexpr bool kTma = sizeof(Tz) == 2;
-  constexpr bool kF16 = !kTma;                           // fp32 rows are multiplied as fp16 against fp16 weights
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   AiBars& bars = *reinterpret_cast<AiBars*>(sm + AiLayout::bars);
@@ -79,7 +76,7 @@ triatt_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
 
   if (cta_skip_after_error()) return;   // an earlier bounded wait gave up: do not start new work
   if (threadIdx.x == 0) {
-    tile_bars_init(bars.tile, kTma, 3);
+    tile_bars_init(bars.tile, 3);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars.acc_full[b], 1);
       mbar_init(&bars.acc_free[b], 8);
@@ -121,7 +118,7 @@ triatt_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   if (warp >= 20) {
     if (lane == 0) {
       if (warp == 20) {
-        if (kTma) tile_producer_loop(ctx, &map_z);
+        tile_producer_loop(ctx, &map_z);
       } else if (warp == 23) {
         tile_gram_loop<kF16>(ctx, tmem_base + kAiColGram);
       } else if (warp == 21) {
@@ -135,7 +132,7 @@ triatt_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   } else if (warp >= 16) {
     // ------------------------------------------------------------------ row statistics, one thread per row
     float2* scale = reinterpret_cast<float2*>(sm + AiLayout::scale);
-    tile_stats_loop<Tz>(ctx, z, eps, tmem_base + kAiColGram, warp - 16, lane, [&](int k, int u, int t, int r, float rstd) {
+    tile_stats_loop<kF16>(ctx, eps, tmem_base + kAiColGram, warp - 16, lane, [&](int k, int u, int t, int r, float rstd) {
       scale[(k % kTileSlots) * 128 + r] = make_float2(rstd, t < n ? rstd : 0.f);
       if (hpair == 0 && t < ldm) {                       // mask bias, -inf in the pad columns [n, ldm)
         float mv = -CUDART_INF_F;
@@ -235,34 +232,31 @@ triatt_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
 
 PX_DEFINE_FAMILY_HOOKS(triatt_in)
 
-template <typename Tz>
+template <bool kF16>
 static int32_t launch_triatt_in(const void* z, const float* mask, const float* ln_w, const float* ln_b,
                                 const px_bf16* w_q, const px_bf16* w_k, const px_bf16* w_v, const px_bf16* w_bias,
                                 px_f16* q, px_f16* k, px_f16* v, float* bias, float* mask_bias, int64_t n_u,
                                 int64_t n, int64_t ldm, int32_t ending, float eps, float inf, cudaStream_t st) {
   CUtensorMap mz, mv;
-  if (sizeof(Tz) == 2) {
-    // pair element (u, t) is row u*n + t of z, or row t*n_u + u when the two indices are exchanged
-    const bool ok = ending ? make_map_3d(&mz, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, z, 128, (uint64_t)n_u, (uint64_t)n, 256,
-                                         (uint64_t)n_u * 256, 64, 1, CU_TENSOR_MAP_SWIZZLE_128B, 128)
-                           : make_map_3d(&mz, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, z, 128, (uint64_t)n, (uint64_t)n_u, 256,
-                                         (uint64_t)n * 256, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B, 1);
-    if (!ok) return PX_ERR_LAUNCH;
-  } else {
-    memset(&mz, 0, sizeof(mz));
-  }
+  const CUtensorMapDataType zt = kF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  // pair element (u, t) is row u*n + t of z, or row t*n_u + u when the two indices are exchanged
+  const bool ok = ending ? make_map_3d(&mz, zt, z, 128, (uint64_t)n_u, (uint64_t)n, 256, (uint64_t)n_u * 256, 64, 1,
+                                       CU_TENSOR_MAP_SWIZZLE_128B, 128)
+                         : make_map_3d(&mz, zt, z, 128, (uint64_t)n, (uint64_t)n_u, 256, (uint64_t)n * 256, 64, 128,
+                                       CU_TENSOR_MAP_SWIZZLE_128B, 1);
+  if (!ok) return PX_ERR_LAUNCH;
   // v is [n_u * 128 rows (u, head, d)][ldt]: a store writes [64 rows][128 t]
   const uint64_t ldt = (uint64_t)px_ld(n);
   if (!make_map_3d(&mv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, v, ldt, (uint64_t)n_u * 128, 1, ldt * 2, ldt * 2 * n_u * 128, 128,
                    64, CU_TENSOR_MAP_SWIZZLE_NONE, 1))
     return PX_ERR_LAUNCH;
   const size_t smem = AiLayout::total + 1024;
-  if (cudaFuncSetAttribute(triatt_in_tc_kernel<Tz>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+  if (cudaFuncSetAttribute(triatt_in_tc_kernel<kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return PX_ERR_LAUNCH;
   const int64_t tiles_t = (n + 127) / 128, n_tiles = tiles_t * n_u;   // 128-wide tiles cover the pad columns up to ldm
   if (n_tiles > 0x7fffffff) return PX_ERR_UNSUPPORTED;
   const int pairs = (int)(n_tiles < sm_count() / 2 ? n_tiles : sm_count() / 2);
-  triatt_in_tc_kernel<Tz><<<2 * pairs, kAiThreads, smem, st>>>(mz, mv, (const Tz*)z, mask, ln_w, ln_b, (const bf16*)w_q,
+  triatt_in_tc_kernel<kF16><<<2 * pairs, kAiThreads, smem, st>>>(mz, mv, mask, ln_w, ln_b, (const bf16*)w_q,
                                                                (const bf16*)w_k, (const bf16*)w_v, (const bf16*)w_bias,
                                                                (bf16*)q, (bf16*)k, bias, mask_bias, (int)n_u, (int)n,
                                                                (int)ldm, ending, eps, inf, (int)tiles_t, (int)n_tiles);
@@ -284,11 +278,11 @@ extern "C" int32_t px_triatt_in_proj(const void* z, int32_t z_dtype, const float
   if (((uintptr_t)z | (uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)w_q | (uintptr_t)w_k | (uintptr_t)w_v |
        (uintptr_t)w_bias | (uintptr_t)ln_w | (uintptr_t)ln_b) & 15)
     return PX_ERR_BAD_ARG;
-  if (z_dtype == PX_F32)
-    return launch_triatt_in<float>(z, mask, ln_w, ln_b, w_q, w_k, w_v, w_bias, q, k, v, bias, mask_bias, n_u, n_t, ldm,
+  if (z_dtype == PX_F16)   // standardised rows of an fp32 pair tensor (px_standardise_rows)
+    return launch_triatt_in<true>(z, mask, ln_w, ln_b, w_q, w_k, w_v, w_bias, q, k, v, bias, mask_bias, n_u, n_t, ldm,
                                    ending, eps, inf, (cudaStream_t)stream);
   if (z_dtype == PX_BF16)
-    return launch_triatt_in<bf16>(z, mask, ln_w, ln_b, w_q, w_k, w_v, w_bias, q, k, v, bias, mask_bias, n_u, n_t, ldm,
+    return launch_triatt_in<false>(z, mask, ln_w, ln_b, w_q, w_k, w_v, w_bias, q, k, v, bias, mask_bias, n_u, n_t, ldm,
                                   ending, eps, inf, (cudaStream_t)stream);
   return PX_ERR_UNSUPPORTED;
 }

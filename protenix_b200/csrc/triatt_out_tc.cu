@@ -54,8 +54,8 @@ triatt_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
                      const float* __restrict__ ln_w, const float* __restrict__ ln_b, const bf16* __restrict__ w_g,
                      const bf16* __restrict__ w_o, int n_u, int n, int swap, int add_residual, float eps, int tiles_t,
                      int n_tiles) {
-  constexpr bool kTma = sizeof(Tz) == 2;
-  constexpr bool kF16 = !kTma;                           // operand format of the z side; o and W_o are always fp16
+  constexpr bool kTma = sizeof(Tz) == 2;               // bf16: residual from the z tile, output through TMA
+  constexpr bool kF16 = !kTma;                           // fp32 z: the z tile is its standardised fp16 copy; o, W_o fp16
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   AoBars& bars = *reinterpret_cast<AoBars*>(sm + AoLayout::bars);
@@ -75,9 +75,7 @@ triatt_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
   if (cta_skip_after_error()) return;   // an earlier bounded wait gave up: do not start new work
   if (threadIdx.x == 0) {
     // a stage is read by the statistics product, the gate product and the output warps
-    tile_bars_init(bars.tile, kTma, 3);
-    if (!kTma)  // the o tile always arrives by TMA: one more arrival beside the four converting warps
-      for (int s = 0; s < kTileStages; ++s) mbar_init(&bars.tile.raw_full[s], 5);
+    tile_bars_init(bars.tile, 3);
     mbar_init(&bars.g_full, 1);
     mbar_init(&bars.g_free, 8);
     mbar_init(&bars.a2_ready, 8);
@@ -116,10 +114,10 @@ triatt_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
           const int s = k % kTileStages, m = k / kTileStages;
           if (!mbar_wait(&bars.tile.a_empty[s], (m & 1) ^ 1, 1u)) break;
           const int u = tile / tiles_t, t0 = (tile % tiles_t) * 128;
-          mbar_expect_tx(&bars.tile.raw_full[s], (kTma ? 2 : 1) * kOperandBytes);
+          mbar_expect_tx(&bars.tile.raw_full[s], 2 * kOperandBytes);
           const uint32_t zdst = smem_u32(ctx.tiles + s * kTileBytes), odst = smem_u32(sm + AoLayout::o + s * kOperandBytes);
           for (int p = 0; p < 2; ++p) {
-            if (kTma) tma_load_3d(zdst + p * kTilePanel, &map_z, &bars.tile.raw_full[s], 64 * p, swap ? u : t0, swap ? t0 : u);
+            tma_load_3d(zdst + p * kTilePanel, &map_z, &bars.tile.raw_full[s], 64 * p, swap ? u : t0, swap ? t0 : u);
             tma_load_3d(odst + p * kPanelBytes, &map_o, &bars.tile.raw_full[s], 64 * p, t0, u);
           }
         }
@@ -148,7 +146,7 @@ triatt_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
   } else if (warp >= 16) {
     // ------------------------------------------------------------------ row statistics, one thread per row
     float* scale = reinterpret_cast<float*>(sm + AoLayout::scale);
-    tile_stats_loop<Tz>(ctx, z_in, eps, tmem_base + kAoColGram, warp - 16, lane,
+    tile_stats_loop<kF16>(ctx, eps, tmem_base + kAoColGram, warp - 16, lane,
                         [&](int k, int u, int t, int r, float rstd) { scale[(k % kTileSlots) * 128 + r] = rstd; });
   } else if (warp < 8) {
     // ------------------------------------------------------------------ gate: o * sigmoid(g) -> tensor memory
@@ -286,24 +284,26 @@ triatt_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
 PX_DEFINE_FAMILY_HOOKS(triatt_out)
 
 template <typename Tz>
-static int32_t launch_triatt_out(const px_bf16* o, const void* z_in, void* z_out, const float* ln_w, const float* ln_b,
+static int32_t launch_triatt_out(const px_f16* o, const void* z_in, const px_f16* zn, void* z_out, const float* ln_w, const float* ln_b,
                                  const px_bf16* w_g, const px_bf16* w_o, int64_t n_u, int64_t n, int32_t ending,
                                  int32_t add_residual, float eps, cudaStream_t st) {
   CUtensorMap mz, mo, mout;
+  // operand rows: bf16 z itself, or the standardised fp16 copy of an fp32 z; pair element (u, t) is row u*n + t, or
+  // row t*n_u + u when the two indices are exchanged
+  const CUtensorMapDataType zt = sizeof(Tz) == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const void* zrows = sizeof(Tz) == 2 ? z_in : (const void*)zn;
+  if (!(ending ? make_map_3d(&mz, zt, zrows, 128, (uint64_t)n_u, (uint64_t)n, 256, (uint64_t)n_u * 256, 64, 1,
+                             CU_TENSOR_MAP_SWIZZLE_128B, 128)
+               : make_map_3d(&mz, zt, zrows, 128, (uint64_t)n, (uint64_t)n_u, 256, (uint64_t)n * 256, 64, 128,
+                             CU_TENSOR_MAP_SWIZZLE_128B, 1)))
+    return PX_ERR_LAUNCH;
   if (sizeof(Tz) == 2) {
-    // pair element (u, t) is row u*n + t of z, or row t*n_u + u when the two indices are exchanged
-    const bool ok =
-        ending ? make_map_3d(&mz, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, z_in, 128, (uint64_t)n_u, (uint64_t)n, 256,
-                             (uint64_t)n_u * 256, 64, 1, CU_TENSOR_MAP_SWIZZLE_128B, 128) &&
-                     make_map_3d(&mout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, z_out, 128, (uint64_t)n_u, (uint64_t)n, 256,
-                                 (uint64_t)n_u * 256, 64, 1, CU_TENSOR_MAP_SWIZZLE_128B, 128)
-               : make_map_3d(&mz, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, z_in, 128, (uint64_t)n, (uint64_t)n_u, 256,
-                             (uint64_t)n * 256, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B, 1) &&
-                     make_map_3d(&mout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, z_out, 128, (uint64_t)n, (uint64_t)n_u, 256,
-                                 (uint64_t)n * 256, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B, 1);
-    if (!ok) return PX_ERR_LAUNCH;
+    if (!(ending ? make_map_3d(&mout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, z_out, 128, (uint64_t)n_u, (uint64_t)n, 256,
+                               (uint64_t)n_u * 256, 64, 1, CU_TENSOR_MAP_SWIZZLE_128B, 128)
+                 : make_map_3d(&mout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, z_out, 128, (uint64_t)n, (uint64_t)n_u, 256,
+                               (uint64_t)n * 256, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B, 1)))
+      return PX_ERR_LAUNCH;
   } else {
-    memset(&mz, 0, sizeof(mz));
     memset(&mout, 0, sizeof(mout));
   }
   if (!make_map_3d(&mo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, o, 128, (uint64_t)n, (uint64_t)n_u, 256, (uint64_t)n * 256, 64,
@@ -325,19 +325,20 @@ static int32_t launch_triatt_out(const px_bf16* o, const void* z_in, void* z_out
 
 using namespace px;
 
-extern "C" int32_t px_triatt_out(const px_bf16* o, const void* z_in, void* z_out, int32_t z_dtype, const float* ln_w,
-                                 const float* ln_b, const px_bf16* w_g, const px_bf16* w_o, int64_t n_u, int64_t n_t,
-                                 int32_t ending, int32_t add_residual, float eps, void* stream) {
+extern "C" int32_t px_triatt_out(const px_f16* o, const void* z_in, const px_f16* zn, void* z_out, int32_t z_dtype,
+                                 const float* ln_w, const float* ln_b, const px_w16* w_g, const px_f16* w_o, int64_t n_u,
+                                 int64_t n_t, int32_t ending, int32_t add_residual, float eps, void* stream) {
   if (!o || !z_in || !z_out || !ln_w || !ln_b || !w_g || !w_o || n_u <= 0 || n_t <= 0 || n_u > 32768 || n_t > 32768)
     return PX_ERR_BAD_ARG;
+  if (z_dtype == PX_F32 && (!zn || ((uintptr_t)zn & 15))) return PX_ERR_BAD_ARG;
   if (((uintptr_t)o | (uintptr_t)z_in | (uintptr_t)z_out | (uintptr_t)w_g | (uintptr_t)w_o | (uintptr_t)ln_w |
        (uintptr_t)ln_b) & 15)
     return PX_ERR_BAD_ARG;
   if (z_dtype == PX_F32)
-    return launch_triatt_out<float>(o, z_in, z_out, ln_w, ln_b, w_g, w_o, n_u, n_t, ending, add_residual, eps,
+    return launch_triatt_out<float>(o, z_in, zn, z_out, ln_w, ln_b, w_g, w_o, n_u, n_t, ending, add_residual, eps,
                                     (cudaStream_t)stream);
   if (z_dtype == PX_BF16)
-    return launch_triatt_out<bf16>(o, z_in, z_out, ln_w, ln_b, w_g, w_o, n_u, n_t, ending, add_residual, eps,
+    return launch_triatt_out<bf16>(o, z_in, nullptr, z_out, ln_w, ln_b, w_g, w_o, n_u, n_t, ending, add_residual, eps,
                                    (cudaStream_t)stream);
   return PX_ERR_UNSUPPORTED;
 }

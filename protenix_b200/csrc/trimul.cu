@@ -16,9 +16,10 @@ using namespace px;
 
 extern "C" int64_t px_ld(int64_t n) { return (n + 7) / 8 * 8; }
 
+// a, b, x in fp16, then room for the standardised fp16 copy of an fp32 z
 extern "C" int64_t px_trimul_workspace_bytes(int64_t n) {
   if (n <= 0) return 0;
-  return (int64_t)(3 * trimul_elems(n) * 2);   // a, b, x in fp16
+  return (int64_t)(3 * trimul_elems(n) * 2 + (size_t)n * n * kC * 2);
 }
 
 extern "C" int32_t px_triangle_multiplication(const void* z_in, void* z_out, int32_t z_dtype, const float* mask,
@@ -34,12 +35,21 @@ extern "C" int32_t px_triangle_multiplication(const void* z_in, void* z_out, int
   px_f16* a = (px_f16*)workspace;
   px_f16* b = a + trimul_elems(n);
   px_f16* x = b + trimul_elems(n);
-  int32_t s = px_trimul_in_proj(z_in, z_dtype, mask, ln_in_w, ln_in_b, w_ap, w_ag, w_bp, w_bg, a, b, n, n, ld,
-                                incoming, eps, stream);
+  px_f16* zn = x + trimul_elems(n);
+  const void* rows = z_in;                 // the rows the tensor core multiplies: bf16 z itself, or ...
+  int32_t rows_dtype = z_dtype, s;
+  if (z_dtype == PX_F32) {                 // ... the standardised fp16 copy of an fp32 z (shared by stages 1 and 3)
+    s = px_standardise_rows((const float*)z_in, zn, n * n, eps, stream);
+    if (s != PX_OK) return s;
+    rows = zn;
+    rows_dtype = PX_F16;
+  }
+  s = px_trimul_in_proj(rows, rows_dtype, mask, ln_in_w, ln_in_b, w_ap, w_ag, w_bp, w_bg, a, b, n, n, ld, incoming, eps,
+                        stream);
   if (s != PX_OK) return s;
   s = px_trimul_contract(a, b, x, kC, n, ld, stream);
   if (s != PX_OK) return s;
-  return px_trimul_out(x, z_in, z_out, z_dtype, ln_in_w, ln_in_b, ln_out_w, ln_out_b, w_z, w_g, n, n, ld,
+  return px_trimul_out(x, z_in, zn, z_out, z_dtype, ln_in_w, ln_in_b, ln_out_w, ln_out_b, w_z, w_g, n, n, ld,
                        add_residual, eps, stream);
 }
 
@@ -48,11 +58,11 @@ extern "C" int32_t px_triangle_multiplication(const void* z_in, void* z_out, int
 //
 // The three stages need scratch for a, b and x.  Here that scratch is a fixed array that is part
 // of the loaded library image, so the call needs no workspace from the caller and makes no
-// cudaMalloc / cudaFree.  The array is 12 MiB (N <= 128) and every GPU that loads the library
+// cudaMalloc / cudaFree.  The array is 16 MiB (N <= 128) and every GPU that loads the library
 // holds it until the process exits.
 // =========================================================================================
 constexpr int64_t kStaticMaxN = PX_STATIC_MAX_N;
-constexpr size_t kStaticScratchBytes = 3 * (size_t)px::kC * kStaticMaxN * kStaticMaxN * sizeof(px::bf16);
+constexpr size_t kStaticScratchBytes = 4 * (size_t)px::kC * kStaticMaxN * kStaticMaxN * 2;   // a, b, x, zn in fp16
 static __device__ __align__(256) unsigned char g_trimul_static_scratch[kStaticScratchBytes];
 
 namespace {
@@ -90,9 +100,9 @@ extern "C" int32_t px_triangle_multiplication_static(const void* z_in, void* z_o
   void* scratch = nullptr;
   int32_t s = static_scratch(&scratch);
   if (s != PX_OK) return s;
-  // Layout for this N: a | b | x, each [128][N][ld] fp16.  Every element a stage reads was written
-  // earlier in the same call (the projection also writes the zero pad columns), so nothing left by
-  // a previous call, possibly with another N, has to be cleared.
+  // Layout for this N: a | b | x, each [128][N][ld] fp16, then the standardised copy of an fp32 z.  Every
+  // element a stage reads was written earlier in the same call (the projection also writes the zero pad
+  // columns), so nothing left by a previous call, possibly with another N, has to be cleared.
   return px_triangle_multiplication(z_in, z_out, z_dtype, mask, ln_in_w, ln_in_b, ln_out_w, ln_out_b, w_ap, w_ag, w_bp,
                                     w_bg, w_z, w_g, scratch, (int64_t)kStaticScratchBytes, n, incoming, add_residual,
                                     eps, stream);

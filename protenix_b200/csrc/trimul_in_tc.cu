@@ -17,15 +17,13 @@
 //
 //   warps 0..7    epilogue of output a: a thread owns one pair element (accumulator lane) and 32 of the CTA's 64
 //                 channels; warps 8..15 do the same for output b, concurrently.
-//   warps 16..19  one thread per row: reads the two statistics out of tensor memory, writes the correction row,
-//                 the row's scale pair and (fp32 rows only) first converts the row into the operand.
-//   warp 20       TMA producer of the bf16 row tiles, two-stage ring.
+//   warps 16..19  one thread per row: reads the two statistics out of tensor memory, writes the correction row and
+//                 the row's scale pair.
+//   warp 20       TMA producer of the row tiles (bf16 rows of z, or standardised fp16 rows), two-stage ring.
 //   warps 21..23  MMA issuers (a tcgen05.mma costs its issuing thread 100 cycles and more, so the work is split):
 //                 warp 21 output a, warp 22 output b, each 8 MMAs M=128 (t) N=128 (projection | gate) K=16 plus the
 //                 correction step; warp 23 the statistics product (8 MMAs, N=144).
-// Algorithmic HBM traffic per pair element: 128*sizeof(Tz) + 4 read, 512 written.  Every mbarrier wait is bounded.
-#include <cstring>
-
+// Algorithmic HBM traffic per pair element: 256 + 4 read, 512 written.  Every mbarrier wait is bounded.
 #include "px_rowpipe.cuh"
 
 namespace px {
@@ -52,15 +50,14 @@ struct TiLayout {
   static constexpr int total = bars + (int)sizeof(TiBars);
 };
 
-template <typename Tz>
+// kF16: the rows are the standardised fp16 copy of an fp32 pair tensor (fp16 weights); otherwise bf16 rows of z.
+template <bool kF16>
 __global__ void __launch_bounds__(kTiThreads, 1)
 trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_a,
-                    const __grid_constant__ CUtensorMap map_b, const Tz* __restrict__ z, const float* __restrict__ mask,
+                    const __grid_constant__ CUtensorMap map_b, const float* __restrict__ mask,
                     const float* __restrict__ ln_w, const float* __restrict__ ln_b, const bf16* __restrict__ w_ap,
                     const bf16* __restrict__ w_ag, const bf16* __restrict__ w_bp, const bf16* __restrict__ w_bg,
                     int n_u, int n_t, int swap, float eps, int tiles_t, int n_tiles) {
-  constexpr bool kTma = sizeof(Tz) == 2;
-  constexpr bool kF16 = !kTma;                           // fp32 rows are multiplied as fp16 against fp16 weights
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   TiBars& bars = *reinterpret_cast<TiBars*>(sm + TiLayout::bars);
@@ -80,7 +77,7 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
 
   if (cta_skip_after_error()) return;   // an earlier bounded wait gave up: do not start new work
   if (threadIdx.x == 0) {
-    tile_bars_init(bars.tile, kTma, 3);
+    tile_bars_init(bars.tile, 3);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars.acc_full[b], 1);
       mbar_init(&bars.acc_free[b], 8);
@@ -112,7 +109,7 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   if (warp >= 20) {
     if (lane == 0) {
       if (warp == 20) {
-        if (kTma) tile_producer_loop(ctx, &map_z);
+        tile_producer_loop(ctx, &map_z);
       } else if (warp == 23) {
         tile_gram_loop<kF16>(ctx, tmem_base + kTiColGram);
       } else {
@@ -125,7 +122,7 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
   } else if (warp >= 16) {
     // ------------------------------------------------------------------ row statistics, one thread per row
     float2* scale = reinterpret_cast<float2*>(sm + TiLayout::scale);
-    tile_stats_loop<Tz>(ctx, z, eps, tmem_base + kTiColGram, warp - 16, lane, [&](int k, int u, int t, int r, float rstd) {
+    tile_stats_loop<kF16>(ctx, eps, tmem_base + kTiColGram, warp - 16, lane, [&](int k, int u, int t, int r, float rstd) {
       float mk = 0.f;
       if (t < n_t) mk = mask ? __ldg(mask + (swap ? ((size_t)t * n_u + u) : ((size_t)u * n_t + t))) : 1.f;
       scale[(k % kTileSlots) * 128 + r] = make_float2(rstd, 0.5f * rstd * mk);
@@ -189,22 +186,19 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
 
 PX_DEFINE_FAMILY_HOOKS(trimul_in)
 
-template <typename Tz>
+template <bool kF16>
 static int32_t launch_trimul_in(const void* z, const float* mask, const float* ln_w, const float* ln_b,
-                                const px_bf16* w_ap, const px_bf16* w_ag, const px_bf16* w_bp, const px_bf16* w_bg,
-                                px_bf16* a, px_bf16* b, int64_t n_u, int64_t n_t, int64_t ld, int32_t incoming, float eps,
+                                const px_w16* w_ap, const px_w16* w_ag, const px_w16* w_bp, const px_w16* w_bg,
+                                px_f16* a, px_f16* b, int64_t n_u, int64_t n_t, int64_t ld, int32_t incoming, float eps,
                                 cudaStream_t st) {
   CUtensorMap mz, ma, mb;
-  if (sizeof(Tz) == 2) {
-    // pair element (u, t) is row u*n_t + t of z, or row t*n_u + u when the two indices are exchanged
-    const bool ok = incoming ? make_map_3d(&mz, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, z, 128, (uint64_t)n_u, (uint64_t)n_t,
-                                           256, (uint64_t)n_u * 256, 64, 1, CU_TENSOR_MAP_SWIZZLE_128B, 128)
-                             : make_map_3d(&mz, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, z, 128, (uint64_t)n_t, (uint64_t)n_u,
-                                           256, (uint64_t)n_t * 256, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B, 1);
-    if (!ok) return PX_ERR_LAUNCH;
-  } else {
-    memset(&mz, 0, sizeof(mz));
-  }
+  const CUtensorMapDataType zt = kF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  // pair element (u, t) is row u*n_t + t of z, or row t*n_u + u when the two indices are exchanged
+  const bool ok = incoming ? make_map_3d(&mz, zt, z, 128, (uint64_t)n_u, (uint64_t)n_t, 256, (uint64_t)n_u * 256, 64, 1,
+                                         CU_TENSOR_MAP_SWIZZLE_128B, 128)
+                           : make_map_3d(&mz, zt, z, 128, (uint64_t)n_t, (uint64_t)n_u, 256, (uint64_t)n_t * 256, 64, 128,
+                                         CU_TENSOR_MAP_SWIZZLE_128B, 1);
+  if (!ok) return PX_ERR_LAUNCH;
   // outputs [128 channels][n_u][ld]: a store writes [64 channels][one u][128 t]
   if (!make_map_3d(&ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, (uint64_t)ld, (uint64_t)n_u, 128, (uint64_t)ld * 2,
                    (uint64_t)n_u * ld * 2, 128, 1, CU_TENSOR_MAP_SWIZZLE_NONE, 64) ||
@@ -212,15 +206,15 @@ static int32_t launch_trimul_in(const void* z, const float* mask, const float* l
                    (uint64_t)n_u * ld * 2, 128, 1, CU_TENSOR_MAP_SWIZZLE_NONE, 64))
     return PX_ERR_LAUNCH;
   const size_t smem = TiLayout::total + 1024;
-  if (cudaFuncSetAttribute(trimul_in_tc_kernel<Tz>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+  if (cudaFuncSetAttribute(trimul_in_tc_kernel<kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return PX_ERR_LAUNCH;
   const int64_t tiles_t = (ld + 127) / 128, n_tiles = tiles_t * n_u;
   if (n_tiles > 0x7fffffff) return PX_ERR_UNSUPPORTED;
   const int pairs = (int)(n_tiles < sm_count() / 2 ? n_tiles : sm_count() / 2);
-  trimul_in_tc_kernel<Tz><<<2 * pairs, kTiThreads, smem, st>>>(mz, ma, mb, (const Tz*)z, mask, ln_w, ln_b, (const bf16*)w_ap,
-                                                               (const bf16*)w_ag, (const bf16*)w_bp, (const bf16*)w_bg,
-                                                               (int)n_u, (int)n_t, incoming, eps, (int)tiles_t,
-                                                               (int)n_tiles);
+  trimul_in_tc_kernel<kF16><<<2 * pairs, kTiThreads, smem, st>>>(mz, ma, mb, mask, ln_w, ln_b, (const bf16*)w_ap,
+                                                                 (const bf16*)w_ag, (const bf16*)w_bp, (const bf16*)w_bg,
+                                                                 (int)n_u, (int)n_t, incoming, eps, (int)tiles_t,
+                                                                 (int)n_tiles);
   return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
 }
 
@@ -229,19 +223,19 @@ static int32_t launch_trimul_in(const void* z, const float* mask, const float* l
 using namespace px;
 
 extern "C" int32_t px_trimul_in_proj(const void* z, int32_t z_dtype, const float* mask, const float* ln_w,
-                                     const float* ln_b, const px_bf16* w_ap, const px_bf16* w_ag,
-                                     const px_bf16* w_bp, const px_bf16* w_bg, px_bf16* a, px_bf16* b, int64_t n_u,
+                                     const float* ln_b, const px_w16* w_ap, const px_w16* w_ag,
+                                     const px_w16* w_bp, const px_w16* w_bg, px_f16* a, px_f16* b, int64_t n_u,
                                      int64_t n_t, int64_t ld, int32_t incoming, float eps, void* stream) {
   if (!z || !ln_w || !ln_b || !w_ap || !w_ag || !w_bp || !w_bg || !a || !b) return PX_ERR_BAD_ARG;
   if (n_u <= 0 || n_t <= 0 || n_u > 32768 || n_t > 32768 || ld != px_ld(n_t)) return PX_ERR_BAD_ARG;
   if (((uintptr_t)z | (uintptr_t)a | (uintptr_t)b | (uintptr_t)w_ap | (uintptr_t)w_ag | (uintptr_t)w_bp |
        (uintptr_t)w_bg | (uintptr_t)ln_w | (uintptr_t)ln_b) & 15)
     return PX_ERR_BAD_ARG;
-  if (z_dtype == PX_F32)
-    return launch_trimul_in<float>(z, mask, ln_w, ln_b, w_ap, w_ag, w_bp, w_bg, a, b, n_u, n_t, ld, incoming, eps,
-                                   (cudaStream_t)stream);
-  if (z_dtype == PX_BF16)
-    return launch_trimul_in<bf16>(z, mask, ln_w, ln_b, w_ap, w_ag, w_bp, w_bg, a, b, n_u, n_t, ld, incoming, eps,
+  if (z_dtype == PX_F16)   // standardised rows of an fp32 pair tensor (px_standardise_rows)
+    return launch_trimul_in<true>(z, mask, ln_w, ln_b, w_ap, w_ag, w_bp, w_bg, a, b, n_u, n_t, ld, incoming, eps,
                                   (cudaStream_t)stream);
+  if (z_dtype == PX_BF16)
+    return launch_trimul_in<false>(z, mask, ln_w, ln_b, w_ap, w_ag, w_bp, w_bg, a, b, n_u, n_t, ld, incoming, eps,
+                                   (cudaStream_t)stream);
   return PX_ERR_UNSUPPORTED;
 }

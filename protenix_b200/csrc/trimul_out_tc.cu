@@ -6,7 +6,8 @@
 // Persistent kernel, one CTA per SM, 128 pair elements (one i, 128 consecutive j) per tile.  Both LayerNorms are
 // folded into the resident weights plus one shared correction K step (px_rowpipe.cuh); nothing is normalised or
 // transposed on the way in:
-//   * the z tile arrives by TMA as a K-major operand (rows of 128 channels);
+//   * the z tile arrives by TMA as a K-major operand (rows of 128 channels): the bf16 rows of z themselves, or, for an
+//     fp32 z, its standardised fp16 copy `zn` (px_standardise_rows), whose statistics are known;
 //   * the x tile arrives by TMA exactly as it lies in memory, [128 channels][128 j], and is used as an MN-major
 //     operand: the tensor core reads it transposed;
 //   * the statistics of both come from Gram products (diagonal = sums of squares) and from 16 rows of ones kept
@@ -62,7 +63,7 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
                      const float* __restrict__ ln_in_w, const float* __restrict__ ln_in_b,
                      const float* __restrict__ ln_out_w, const float* __restrict__ ln_out_b, const bf16* __restrict__ w_z,
                      const bf16* __restrict__ w_g, int n_i, int n, int add_residual, float eps, int tiles_j, int n_tiles) {
-  constexpr bool kTma = sizeof(Tz) == 2;
+  constexpr bool kTma = sizeof(Tz) == 2;               // bf16: residual from the z tile, output through TMA
   constexpr bool kF16 = !kTma;                           // operand format of the z side; the x side is always fp16
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -72,7 +73,7 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
   if (cta_skip_after_error()) return;   // an earlier bounded wait gave up: do not start new work
   if (threadIdx.x == 0) {
     for (int s = 0; s < kToStages; ++s) {
-      mbar_init(&bars.raw_full[s], kTma ? 1 : 5);          // fp32 rows: four converting warps beside the x tile
+      mbar_init(&bars.raw_full[s], 1);
       mbar_init(&bars.a_ready[s], 4);
       mbar_init(&bars.a_empty[s], 4);                      // three issuing threads and the store of the output rows
     }
@@ -122,10 +123,10 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
           const int s = k % kToStages, m = k / kToStages;
           if (!mbar_wait(&bars.a_empty[s], (m & 1) ^ 1, 1u)) break;
           const int i = tile / tiles_j, j0 = (tile % tiles_j) * 128;
-          mbar_expect_tx(&bars.raw_full[s], (kTma ? 2 : 1) * kOperandBytes);
+          mbar_expect_tx(&bars.raw_full[s], 2 * kOperandBytes);
           const uint32_t zdst = smem_u32(sm + ToLayout::zt + s * kOperandBytes), xdst = smem_u32(sm + ToLayout::xt + s * kOperandBytes);
           for (int p = 0; p < 2; ++p) {
-            if (kTma) tma_load_3d(zdst + p * kPanelBytes, &map_z, &bars.raw_full[s], 64 * p, j0, i);
+            tma_load_3d(zdst + p * kPanelBytes, &map_z, &bars.raw_full[s], 64 * p, j0, i);
             tma_load_3d(xdst + p * kPanelBytes, &map_x, &bars.raw_full[s], j0 + 64 * p, i, 0);
           }
         }
@@ -192,25 +193,6 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
     bool ok = true;
     for (int tile = first_tile; tile < n_tiles; tile += tile_step, ++k) {
       const int s = k % kToStages, m = k / kToStages;
-      if (!kTma) {
-        // fp32 rows: standardised while they are converted into the operand
-        const int i = tile / tiles_j, j = (tile % tiles_j) * 128 + r;
-        ok = mbar_wait(&bars.a_empty[s], (m & 1) ^ 1, 16u);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        auto rows_of = [&](int tl) {                       // this warp's 32 rows of tile tl
-          const int ii = tl / tiles_j, j_first = (tl % tiles_j) * 128 + 32 * qw;
-          return [=](int rr) -> const float* {
-            const int jj = j_first + rr;
-            return jj < n ? reinterpret_cast<const float*>(z_in) + ((size_t)ii * n + jj) * kC : nullptr;
-          };
-        };
-        if (tile + tile_step < n_tiles) prefetch_rows_l2(lane, rows_of(tile + tile_step));
-        standardise_rows_to_operand(sm + ToLayout::zt + s * kOperandBytes, 32 * qw, lane, eps, kPanelBytes, rows_of(tile));
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars.raw_full[s]);
-      }
       float sumsq[2];
 #pragma unroll
       for (int which = 0; which < 2; ++which) {              // 0: z, 1: x
@@ -239,12 +221,14 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
       float rstd[2];
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
-        const float mean = __uint_as_float(which ? sx[0] : sz[0]) * (1.0f / kC);
+        float mean = __uint_as_float(which ? sx[0] : sz[0]) * (1.0f / kC);
         const float var = fmaxf(sumsq[which] * (1.0f / kC) - mean * mean, 0.f);
         const float e = which ? eps * (PX_TRIMUL_X_SCALE * PX_TRIMUL_X_SCALE) : eps;   // x arrives scaled
+        float std = sqrtf(var + e);
         rstd[which] = rsqrtf(var + e);
+        if (kF16 && which == 0) mean = 0.f, std = 1.f, rstd[0] = 1.f;   // standardised rows: known statistics
         // rstd * (W'x - mean * s + std * t): the row side of the correction step holds (-mean, std)
-        write_correction_row(sm + ToLayout::ax + s * 128 * 32, r, -mean, sqrtf(var + e), false, which, false);
+        write_correction_row(sm + ToLayout::ax + s * 128 * 32, r, -mean, std, false, which, false);
       }
       scale[(k % kToSlots) * 128 + r] = make_float2(rstd[0], rstd[1]);
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -342,18 +326,20 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
 PX_DEFINE_FAMILY_HOOKS(trimul_out)
 
 template <typename Tz>
-static int32_t launch_trimul_out(const px_bf16* x, const void* z_in, void* z_out, const float* ln_in_w, const float* ln_in_b,
+static int32_t launch_trimul_out(const px_f16* x, const void* z_in, const px_f16* zn, void* z_out, const float* ln_in_w, const float* ln_in_b,
                                  const float* ln_out_w, const float* ln_out_b, const px_bf16* w_z, const px_bf16* w_g,
                                  int64_t n_i, int64_t n, int64_t ld, int32_t add_residual, float eps, cudaStream_t st) {
   CUtensorMap mz, mx, mout;
+  // operand rows: bf16 z itself, or the standardised fp16 copy of an fp32 z
+  if (!make_map_3d(&mz, sizeof(Tz) == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                   sizeof(Tz) == 2 ? z_in : (const void*)zn, 128, (uint64_t)n, (uint64_t)n_i, 256, (uint64_t)n * 256, 64, 128,
+                   CU_TENSOR_MAP_SWIZZLE_128B, 1))
+    return PX_ERR_LAUNCH;
   if (sizeof(Tz) == 2) {
-    if (!make_map_3d(&mz, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, z_in, 128, (uint64_t)n, (uint64_t)n_i, 256, (uint64_t)n * 256, 64,
-                     128, CU_TENSOR_MAP_SWIZZLE_128B, 1) ||
-        !make_map_3d(&mout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, z_out, 128, (uint64_t)n, (uint64_t)n_i, 256, (uint64_t)n * 256,
+    if (!make_map_3d(&mout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, z_out, 128, (uint64_t)n, (uint64_t)n_i, 256, (uint64_t)n * 256,
                      64, 128, CU_TENSOR_MAP_SWIZZLE_128B, 1))
       return PX_ERR_LAUNCH;
   } else {
-    memset(&mz, 0, sizeof(mz));
     memset(&mout, 0, sizeof(mout));
   }
   // x [128 channels][n_i][ld]: a load brings [128 channels][one i][64 j]
@@ -376,20 +362,21 @@ static int32_t launch_trimul_out(const px_bf16* x, const void* z_in, void* z_out
 
 using namespace px;
 
-extern "C" int32_t px_trimul_out(const px_bf16* x, const void* z_in, void* z_out, int32_t z_dtype,
+extern "C" int32_t px_trimul_out(const px_f16* x, const void* z_in, const px_f16* zn, void* z_out, int32_t z_dtype,
                                  const float* ln_in_w, const float* ln_in_b, const float* ln_out_w,
-                                 const float* ln_out_b, const px_bf16* w_z, const px_bf16* w_g, int64_t n_i,
+                                 const float* ln_out_b, const px_f16* w_z, const px_w16* w_g, int64_t n_i,
                                  int64_t n_j, int64_t ld, int32_t add_residual, float eps, void* stream) {
   if (!x || !z_in || !z_out || !ln_in_w || !ln_in_b || !ln_out_w || !ln_out_b || !w_z || !w_g) return PX_ERR_BAD_ARG;
+  if (z_dtype == PX_F32 && (!zn || ((uintptr_t)zn & 15))) return PX_ERR_BAD_ARG;
   if (n_i <= 0 || n_j <= 0 || n_i > 32768 || n_j > 32768 || ld != px_ld(n_j)) return PX_ERR_BAD_ARG;
   if (((uintptr_t)x | (uintptr_t)z_in | (uintptr_t)z_out | (uintptr_t)w_z | (uintptr_t)w_g | (uintptr_t)ln_in_w |
        (uintptr_t)ln_in_b | (uintptr_t)ln_out_w | (uintptr_t)ln_out_b) & 15)
     return PX_ERR_BAD_ARG;
   if (z_dtype == PX_F32)
-    return launch_trimul_out<float>(x, z_in, z_out, ln_in_w, ln_in_b, ln_out_w, ln_out_b, w_z, w_g, n_i, n_j, ld,
+    return launch_trimul_out<float>(x, z_in, zn, z_out, ln_in_w, ln_in_b, ln_out_w, ln_out_b, w_z, w_g, n_i, n_j, ld,
                                     add_residual, eps, (cudaStream_t)stream);
   if (z_dtype == PX_BF16)
-    return launch_trimul_out<bf16>(x, z_in, z_out, ln_in_w, ln_in_b, ln_out_w, ln_out_b, w_z, w_g, n_i, n_j, ld,
+    return launch_trimul_out<bf16>(x, z_in, nullptr, z_out, ln_in_w, ln_in_b, ln_out_w, ln_out_b, w_z, w_g, n_i, n_j, ld,
                                    add_residual, eps, (cudaStream_t)stream);
   return PX_ERR_UNSUPPORTED;
 }

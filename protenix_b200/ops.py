@@ -203,6 +203,33 @@ def layer_norm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[t
     return (y, mean, invvar) if return_stats else y
 
 
+def standardise_rows(z: torch.Tensor, eps: float = 1e-5, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """zn = fp16((z - mean) * rstd) over rows of 128 channels of an fp32 tensor: the rows the tensor core multiplies
+    when the pair tensor is stored as fp32.  One copy serves every stage that normalises the same z."""
+    _need_cuda(z, "z")
+    if z.dtype != torch.float32 or z.shape[-1] != C_Z:
+        raise RuntimeError("standardise_rows takes a float32 tensor [..., 128]")
+    if out is None:
+        out = torch.empty(z.shape, dtype=torch.float16, device=z.device)
+    rows = z.numel() // C_Z
+    _launch("px_standardise_rows", _lib.load().px_standardise_rows, _ptr(z), _ptr(out), rows, float(eps), _stream(z))
+    return out
+
+
+def _rows_of(z: torch.Tensor, zn: Optional[torch.Tensor], eps: float) -> Tuple[torch.Tensor, int]:
+    """The rows a stage multiplies and their dtype code: bf16 z itself, or the standardised fp16 copy of an fp32 z
+    (made here unless the caller already holds one)."""
+    if z.dtype == torch.bfloat16:
+        return z, PX_BF16
+    if z.dtype != torch.float32:
+        raise RuntimeError(f"pair tensor must be float32 or bfloat16, got {z.dtype}")
+    if zn is None:
+        zn = standardise_rows(z, eps)
+    elif zn.dtype != torch.float16 or zn.shape != z.shape or not zn.is_cuda or not zn.is_contiguous():
+        raise RuntimeError("zn must be the contiguous float16 standardised copy of z")
+    return zn, PX_F16
+
+
 def triangle_multiplication(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optional[torch.Tensor],
                             ln_in_w, ln_in_b, ln_out_w, ln_out_b, w_ap, w_ag, w_bp, w_bg, w_z, w_g,
                             incoming: bool, add_residual: bool, eps: float = 1e-5) -> torch.Tensor:
@@ -220,12 +247,17 @@ def triangle_multiplication(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optio
     ws = workspace(z_in.device, lib.px_trimul_workspace_bytes(n))
     ldn = lib.px_ld(n)
     per = C_Z * n * ldn * 2                      # bytes of one channel-major [128][N][ld] fp16 tensor
-    a, b, x = ws.data_ptr(), ws.data_ptr() + per, ws.data_ptr() + 2 * per
+    a, b, x, zn = ws.data_ptr(), ws.data_ptr() + per, ws.data_ptr() + 2 * per, None
     dt, st, eps = _pair_dtype(z_in), _stream(z_in), float(eps)
-    _launch("px_trimul_in_proj", lib.px_trimul_in_proj, _ptr(z_in), dt, _ptr(mask), _ptr(ln_in_w), _ptr(ln_in_b),
+    rows, rows_dt = _ptr(z_in), dt
+    if dt == PX_F32:            # the projection and the output stage normalise the same z: one standardised copy
+        zn = rows = ws.data_ptr() + 3 * per
+        rows_dt = PX_F16
+        _launch("px_standardise_rows", lib.px_standardise_rows, _ptr(z_in), zn, n * n, eps, st)
+    _launch("px_trimul_in_proj", lib.px_trimul_in_proj, rows, rows_dt, _ptr(mask), _ptr(ln_in_w), _ptr(ln_in_b),
             _ptr(w_ap), _ptr(w_ag), _ptr(w_bp), _ptr(w_bg), a, b, n, n, ldn, int(incoming), eps, st)
     _launch("px_trimul_contract", lib.px_trimul_contract, a, b, x, C_Z, n, ldn, st)
-    _launch("px_trimul_out", lib.px_trimul_out, x, _ptr(z_in), _ptr(z_out), dt, _ptr(ln_in_w), _ptr(ln_in_b),
+    _launch("px_trimul_out", lib.px_trimul_out, x, _ptr(z_in), zn, _ptr(z_out), dt, _ptr(ln_in_w), _ptr(ln_in_b),
             _ptr(ln_out_w), _ptr(ln_out_b), _ptr(w_z), _ptr(w_g), n, n, ldn, int(add_residual), eps, st)
     return z_out
 
@@ -254,11 +286,16 @@ def triangle_attention(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optional[t
     mbias = bias + al(N_HEAD_PAIR * n * ldn * 4)
     flags = mbias + al(n * ldn * 4)
     dt, st, eps = _pair_dtype(z_in), _stream(z_in), float(eps)
-    _launch("px_triatt_in_proj", lib.px_triatt_in_proj, _ptr(z_in), dt, _ptr(mask), _ptr(ln_w), _ptr(ln_b),
+    rows, rows_dt, zn = _ptr(z_in), dt, None
+    if dt == PX_F32:            # the projection and the output stage normalise the same z: one standardised copy
+        zn = rows = flags + al(lib.px_triatt_flash_scratch_bytes(n, n))
+        rows_dt = PX_F16
+        _launch("px_standardise_rows", lib.px_standardise_rows, _ptr(z_in), zn, n * n, eps, st)
+    _launch("px_triatt_in_proj", lib.px_triatt_in_proj, rows, rows_dt, _ptr(mask), _ptr(ln_w), _ptr(ln_b),
             _ptr(w_q), _ptr(w_k), _ptr(w_v), _ptr(w_bias), q, k, v, bias, mbias, n, n, ldn, int(ending), eps,
             float(inf), st)
     _launch("px_triatt_flash", lib.px_triatt_flash, q, k, v, bias, mbias, o, flags, n, n, ldn, st)
-    _launch("px_triatt_out", lib.px_triatt_out, o, _ptr(z_in), _ptr(z_out), dt, _ptr(ln_w), _ptr(ln_b), _ptr(w_g),
+    _launch("px_triatt_out", lib.px_triatt_out, o, _ptr(z_in), zn, _ptr(z_out), dt, _ptr(ln_w), _ptr(ln_b), _ptr(w_g),
             _ptr(w_o), n, n, int(ending), int(add_residual), eps, st)
     return z_out
 
@@ -290,7 +327,8 @@ def pair_bias_proj(z: torch.Tensor, ln_w, ln_b: Optional[torch.Tensor], w: torch
     heads = w.shape[0]
     w = _w(w, _zfmt(z), (heads, C_Z), "w")
     out = torch.empty(heads, n, n, dtype=torch.float32, device=z.device)
-    _launch("px_pair_bias_proj", _lib.load().px_pair_bias_proj, _ptr(z), _pair_dtype(z), _ptr(ln_w), _ptr(ln_b),
+    rows, rows_dt = _rows_of(z, None, eps)
+    _launch("px_pair_bias_proj", _lib.load().px_pair_bias_proj, _ptr(rows), rows_dt, _ptr(ln_w), _ptr(ln_b),
             _ptr(w), _ptr(out), n * n, heads, float(eps), _stream(z))
     return out
 
@@ -315,7 +353,9 @@ def recycle_update(z: torch.Tensor, z_init: torch.Tensor, ln_w, ln_b: Optional[t
     rows = z.numel() // C_Z
     if rows == 0:
         return out
-    _launch("px_recycle_update", _lib.load().px_recycle_update, _ptr(z), _ptr(z_init), _ptr(out), _pair_dtype(z),
+    zdt = _pair_dtype(z)
+    z, _ = _rows_of(z, None, eps)          # an fp32 z enters as its standardised fp16 copy
+    _launch("px_recycle_update", _lib.load().px_recycle_update, _ptr(z), _ptr(z_init), _ptr(out), zdt,
             _ptr(ln_w), _ptr(ln_b), _ptr(w), rows, float(eps), _stream(z))
     return out
 
@@ -330,7 +370,8 @@ def _slab(z: torch.Tensor, name: str = "z") -> Tuple[int, int]:
 
 
 def trimul_in_proj(z: torch.Tensor, mask: Optional[torch.Tensor], ln_w, ln_b, w_ap, w_ag, w_bp, w_bg,
-                   incoming: bool, eps: float = 1e-5) -> Tuple[torch.Tensor, torch.Tensor]:
+                   incoming: bool, eps: float = 1e-5, zn: Optional[torch.Tensor] = None
+                   ) -> Tuple[torch.Tensor, torch.Tensor]:
     """a, b as [128][n_u][ld(n_t)] fp16.  z is [n_u][n_t][128]; with ``incoming`` it is [n_t][n_u][128]."""
     r, c = _slab(z)
     n_u, n_t = (c, r) if incoming else (r, c)
@@ -340,7 +381,8 @@ def trimul_in_proj(z: torch.Tensor, mask: Optional[torch.Tensor], ln_w, ln_b, w_
     w_ap, w_ag, w_bp, w_bg = (_w(w, zf, (C_Z, C_Z), "w") for w in (w_ap, w_ag, w_bp, w_bg))
     a = torch.empty(C_Z, n_u, ldt, dtype=torch.float16, device=z.device)
     b = torch.empty_like(a)
-    _launch("px_trimul_in_proj", lib.px_trimul_in_proj, _ptr(z), _pair_dtype(z), _ptr(mask), _ptr(ln_w), _ptr(ln_b),
+    rows, rows_dt = _rows_of(z, zn, eps)
+    _launch("px_trimul_in_proj", lib.px_trimul_in_proj, _ptr(rows), rows_dt, _ptr(mask), _ptr(ln_w), _ptr(ln_b),
             _ptr(w_ap), _ptr(w_ag), _ptr(w_bp), _ptr(w_bg), _ptr(a), _ptr(b), n_u, n_t, ldt, int(incoming), float(eps),
             _stream(z))
     return a, b
@@ -359,21 +401,22 @@ def trimul_contract(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 
 def trimul_out(x: torch.Tensor, z: torch.Tensor, ln_in_w, ln_in_b, ln_out_w, ln_out_b, w_z, w_g,
-               eps: float = 1e-5) -> torch.Tensor:
+               eps: float = 1e-5, zn: Optional[torch.Tensor] = None) -> torch.Tensor:
     """z[n_i][n_j] += W_z LN(x) * sigmoid(W_g LN(z)) in place; x is [128][n_i][ld(n_j)]."""
     n_i, n_j = _slab(z)
     _need_cuda(x, "x")
     if x.dtype != torch.float16 or x.dim() != 3 or x.shape[0] != C_Z or x.shape[1] != n_i or x.shape[2] != ld(n_j):
         raise RuntimeError("x must be float16 [128][n_i][ld(n_j)]")
     w_z, w_g = _w(w_z, F16, (C_Z, C_Z), "w_z"), _w(w_g, _zfmt(z), (C_Z, C_Z), "w_g")
-    _launch("px_trimul_out", _lib.load().px_trimul_out, _ptr(x), _ptr(z), _ptr(z), _pair_dtype(z), _ptr(ln_in_w),
+    zn = _rows_of(z, zn, eps)[0] if z.dtype == torch.float32 else None
+    _launch("px_trimul_out", _lib.load().px_trimul_out, _ptr(x), _ptr(z), _ptr(zn), _ptr(z), _pair_dtype(z), _ptr(ln_in_w),
             _ptr(ln_in_b), _ptr(ln_out_w), _ptr(ln_out_b), _ptr(w_z), _ptr(w_g), n_i, n_j, x.shape[2], 1, float(eps),
             _stream(z))
     return z
 
 
 def triatt_in_proj(z: torch.Tensor, mask: Optional[torch.Tensor], ln_w, ln_b, w_bias, w_q, w_k, w_v,
-                   eps: float = 1e-5, inf: float = 1e9, ending: bool = False):
+                   eps: float = 1e-5, inf: float = 1e9, ending: bool = False, zn: Optional[torch.Tensor] = None):
     """q, k [n_u][4][n_t][32] and v (transposed) [n_u][4][32][ld(n_t)] in fp16, bias [4][n_u][ldm] and
     mask_bias [n_u][ldm] in fp32 for a slab.  z (and the mask) is [n_u][n_t][128]; with ``ending`` it is the
     column slab [n_t][n_u][128] and the attended rows u are its columns."""
@@ -390,7 +433,8 @@ def triatt_in_proj(z: torch.Tensor, mask: Optional[torch.Tensor], ln_w, ln_b, w_
     v = torch.empty(n_u, N_HEAD_PAIR, D_HEAD_PAIR, lib.px_ld(n_t), dtype=torch.float16, device=z.device)
     bias = torch.empty(N_HEAD_PAIR, n_u, ldm, dtype=torch.float32, device=z.device)
     mb = torch.empty(n_u, ldm, dtype=torch.float32, device=z.device)
-    _launch("px_triatt_in_proj", lib.px_triatt_in_proj, _ptr(z), _pair_dtype(z), _ptr(mask), _ptr(ln_w), _ptr(ln_b),
+    rows, rows_dt = _rows_of(z, zn, eps)
+    _launch("px_triatt_in_proj", lib.px_triatt_in_proj, _ptr(rows), rows_dt, _ptr(mask), _ptr(ln_w), _ptr(ln_b),
             _ptr(w_q), _ptr(w_k), _ptr(w_v), _ptr(w_bias), _ptr(q), _ptr(k), _ptr(v), _ptr(bias), _ptr(mb), n_u, n_t,
             ldm, int(ending), float(eps), float(inf), _stream(z))
     return q, k, v, bias, mb
@@ -415,8 +459,8 @@ def triatt_flash(q, k, v, bias_full: torch.Tensor, mb) -> torch.Tensor:
     return o
 
 
-def triatt_out(o: torch.Tensor, z: torch.Tensor, ln_w, ln_b, w_g, w_o, eps: float = 1e-5, ending: bool = False
-               ) -> torch.Tensor:
+def triatt_out(o: torch.Tensor, z: torch.Tensor, ln_w, ln_b, w_g, w_o, eps: float = 1e-5, ending: bool = False,
+               zn: Optional[torch.Tensor] = None) -> torch.Tensor:
     """z(u,t) += W_o(o[u][t] * sigmoid(W_g LN(z(u,t)))) in place; z is [n_u][n_t][128], or the column slab
     [n_t][n_u][128] with ``ending``."""
     n_u, n_t = _slab(z)
@@ -426,7 +470,8 @@ def triatt_out(o: torch.Tensor, z: torch.Tensor, ln_w, ln_b, w_g, w_o, eps: floa
     if o.dtype != torch.float16 or tuple(o.shape) != (n_u, n_t, C_Z):
         raise RuntimeError("o must be float16 [n_u][n_t][128]")
     w_g, w_o = _w(w_g, _zfmt(z), (C_Z, C_Z), "w_g"), _w(w_o, F16, (C_Z, C_Z), "w_o")
-    _launch("px_triatt_out", _lib.load().px_triatt_out, _ptr(o), _ptr(z), _ptr(z), _pair_dtype(z), _ptr(ln_w),
+    zn = _rows_of(z, zn, eps)[0] if z.dtype == torch.float32 else None
+    _launch("px_triatt_out", _lib.load().px_triatt_out, _ptr(o), _ptr(z), _ptr(zn), _ptr(z), _pair_dtype(z), _ptr(ln_w),
             _ptr(ln_b), _ptr(w_g), _ptr(w_o), n_u, n_t, int(ending), 1, float(eps), _stream(z))
     return z
 
@@ -438,7 +483,8 @@ def pair_bias_rows(z: torch.Tensor, ln_w, ln_b: Optional[torch.Tensor], w: torch
     heads = w.shape[0]
     w = _w(w, _zfmt(z), (heads, C_Z), "w")
     out = torch.empty(heads, n_u, n_t, dtype=torch.float32, device=z.device)
-    _launch("px_pair_bias_proj", _lib.load().px_pair_bias_proj, _ptr(z), _pair_dtype(z), _ptr(ln_w), _ptr(ln_b),
+    rows, rows_dt = _rows_of(z, None, eps)
+    _launch("px_pair_bias_proj", _lib.load().px_pair_bias_proj, _ptr(rows), rows_dt, _ptr(ln_w), _ptr(ln_b),
             _ptr(w), _ptr(out), n_u * n_t, heads, float(eps), _stream(z))
     return out
 

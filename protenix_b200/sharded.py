@@ -47,35 +47,40 @@ class CudaStages:
     def _f(p):
         return p.detach().float()
 
-    def trimul_in_proj(self, mod, z, mask, incoming):
+    def standardised(self, z, eps):
+        """The standardised fp16 copy of an fp32 slab (the rows the tensor core multiplies), made once per
+        sub-module and handed to its projection and its output stage; None for bf16 slabs, which are used as stored."""
+        return ops.standardise_rows(z, eps) if z.dtype == torch.float32 else None
+
+    def trimul_in_proj(self, mod, z, mask, incoming, zn=None):
         f = self._f
         return ops.trimul_in_proj(z, mask, f(mod.layer_norm_in.weight), f(mod.layer_norm_in.bias),
                                   mod.linear_a_p.weight, mod.linear_a_g.weight,
                                   mod.linear_b_p.weight, mod.linear_b_g.weight, incoming,
-                                  mod.layer_norm_in.eps)
+                                  mod.layer_norm_in.eps, zn=zn)
 
     def trimul_contract(self, a, b):
         return ops.trimul_contract(a, b)
 
-    def trimul_out(self, mod, x, z):
+    def trimul_out(self, mod, x, z, zn=None):
         f = self._f
         return ops.trimul_out(x, z, f(mod.layer_norm_in.weight), f(mod.layer_norm_in.bias),
                               f(mod.layer_norm_out.weight), f(mod.layer_norm_out.bias), mod.linear_z.weight,
-                              mod.linear_g.weight, mod.layer_norm_in.eps)
+                              mod.linear_g.weight, mod.layer_norm_in.eps, zn=zn)
 
-    def triatt_in_proj(self, mod, z, mask, ending=False):
+    def triatt_in_proj(self, mod, z, mask, ending=False, zn=None):
         f, m = self._f, mod.mha
         return ops.triatt_in_proj(z, mask, f(mod.layer_norm.weight), f(mod.layer_norm.bias), mod.linear.weight,
                                   m.linear_q.weight, m.linear_k.weight, m.linear_v.weight,
-                                  mod.layer_norm.eps, mod.inf, ending)
+                                  mod.layer_norm.eps, mod.inf, ending, zn=zn)
 
     def triatt_flash(self, q, k, v, bias_full, mb):
         return ops.triatt_flash(q, k, v, bias_full, mb)
 
-    def triatt_out(self, mod, o, z, ending=False):
+    def triatt_out(self, mod, o, z, ending=False, zn=None):
         f, m = self._f, mod.mha
         return ops.triatt_out(o, z, f(mod.layer_norm.weight), f(mod.layer_norm.bias), m.linear_g.weight,
-                              m.linear_o.weight, mod.layer_norm.eps, ending)
+                              m.linear_o.weight, mod.layer_norm.eps, ending, zn=zn)
 
     def transition(self, mod, z):
         f = self._f
@@ -286,18 +291,20 @@ class ShardedPairformer:
 
     def _tri_att_start_peer(self, px: PeerExchange, mod, z_loc, mask_loc) -> None:
         st = self.stages
-        q, k, v, bias_loc, mb = st.triatt_in_proj(mod, z_loc, mask_loc)
+        zn = st.standardised(z_loc, mod.layer_norm.eps)
+        q, k, v, bias_loc, mb = st.triatt_in_proj(mod, z_loc, mask_loc, zn=zn)
         h, nl, ldm = bias_loc.shape
         self._peer_gather_bias(px, bias_loc)
         px.fence()
         bias_full = px.local["bias"].tensor((h, self.world * nl, ldm), torch.float32)
-        st.triatt_out(mod, st.triatt_flash(q, k, v, bias_full, mb), z_loc)
+        st.triatt_out(mod, st.triatt_flash(q, k, v, bias_full, mb), z_loc, zn=zn)
 
     def _tri_mul_peer(self, px: PeerExchange, mod, z_loc, mask_loc, incoming: bool) -> None:
         st, p, me = self.stages, self.world, self.rank
         nl, n, _ = z_loc.shape
         cp, ldn = 128 // p, (n + 7) // 8 * 8
-        a, b = st.trimul_in_proj(mod, z_loc, mask_loc, incoming)
+        zn = st.standardised(z_loc, mod.layer_norm_in.eps)
+        a, b = st.trimul_in_proj(mod, z_loc, mask_loc, incoming, zn=zn)
         self._peer_rows_to_channels(px, a, "a", incoming)
         self._peer_rows_to_channels(px, b, "b", incoming)
         px.fence()
@@ -307,7 +314,7 @@ class ShardedPairformer:
         self._peer_channels_to_rows(px, x)
         px.fence()
         del x
-        st.trimul_out(mod, px.local["x"].tensor((128, nl, ldn), torch.float16), z_loc)
+        st.trimul_out(mod, px.local["x"].tensor((128, nl, ldn), torch.float16), z_loc, zn=zn)
 
     def _tri_att_end_peer(self, px: PeerExchange, mod, z_loc, mask_cols) -> None:
         """Ending node on the column slab zc [N i][N/P j][c] (the kernels address it as element (u=j, t=i))."""
@@ -316,12 +323,13 @@ class ShardedPairformer:
         self._peer_to_columns(px, z_loc)
         px.fence()
         zc = px.local["zc"].tensor((n, nl, c), z_loc.dtype)
-        q, k, v, bias_loc, mb = st.triatt_in_proj(mod, zc, mask_cols, True)
+        zn = st.standardised(zc, mod.layer_norm.eps)
+        q, k, v, bias_loc, mb = st.triatt_in_proj(mod, zc, mask_cols, True, zn=zn)
         h, _, ldm = bias_loc.shape
         self._peer_gather_bias(px, bias_loc)
         px.fence()
         bias_full = px.local["bias"].tensor((h, p * nl, ldm), torch.float32)
-        st.triatt_out(mod, st.triatt_flash(q, k, v, bias_full, mb), zc, True)
+        st.triatt_out(mod, st.triatt_flash(q, k, v, bias_full, mb), zc, True, zn=zn)
         self._peer_from_columns(px, zc)
         px.fence()
         z_loc.copy_(px.local["zr"].tensor((nl, n, c), z_loc.dtype))
@@ -329,19 +337,21 @@ class ShardedPairformer:
     # ---- sub-modules ----------------------------------------------------------------------------
     def _tri_mul(self, mod, z_loc, mask_loc, incoming: bool) -> None:
         st = self.stages
-        a, b = st.trimul_in_proj(mod, z_loc, mask_loc, incoming)
+        zn = st.standardised(z_loc, mod.layer_norm_in.eps)
+        a, b = st.trimul_in_proj(mod, z_loc, mask_loc, incoming, zn=zn)
         a = self._rows_to_channels(a, k_sharded=incoming)
         b = self._rows_to_channels(b, k_sharded=incoming)
         x = st.trimul_contract(a, b)
         del a, b
-        st.trimul_out(mod, self._channels_to_rows(x), z_loc)
+        st.trimul_out(mod, self._channels_to_rows(x), z_loc, zn=zn)
 
     def _tri_att_rows(self, mod, z_loc, mask_loc) -> None:
         st = self.stages
-        q, k, v, bias_loc, mb = st.triatt_in_proj(mod, z_loc, mask_loc)
+        zn = st.standardised(z_loc, mod.layer_norm.eps)
+        q, k, v, bias_loc, mb = st.triatt_in_proj(mod, z_loc, mask_loc, zn=zn)
         h, nl, ldm = bias_loc.shape
         bias_full = self._all_gather(bias_loc).permute(1, 0, 2, 3).reshape(h, self.world * nl, ldm)
-        st.triatt_out(mod, st.triatt_flash(q, k, v, bias_full, mb), z_loc)
+        st.triatt_out(mod, st.triatt_flash(q, k, v, bias_full, mb), z_loc, zn=zn)
 
     def _single_branch(self, blk, s, bias):
         """s + AttentionPairBias(s, z) + Transition(.), query rows sharded like z; ``bias`` [H, N/P, N] is the pair

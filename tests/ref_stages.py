@@ -25,7 +25,10 @@ def _ld(n, m=8):
 
 
 class TorchStages:
-    def trimul_in_proj(self, mod, z, mask, incoming):
+    def standardised(self, z, eps):
+        return None                                        # the fp32 stand-in normalises inside every stage
+
+    def trimul_in_proj(self, mod, z, mask, incoming, zn=None):
         zn = _ln(z, mod.layer_norm_in)
         m = (mask if mask is not None else z.new_ones(z.shape[:2]))[..., None]
         a = m * torch.sigmoid(zn @ mod.linear_a_g.weight.T) * (zn @ mod.linear_a_p.weight.T)
@@ -39,14 +42,14 @@ class TorchStages:
         x = torch.einsum("cik,cjk->cij", a, b)
         return _pad_last(x, _ld(n))
 
-    def trimul_out(self, mod, x, z):
+    def trimul_out(self, mod, x, z, zn=None):
         n_j = z.shape[1]
         xin = x[:, :, :n_j].permute(1, 2, 0)
         zn = _ln(z, mod.layer_norm_in)
         z += (_ln(xin, mod.layer_norm_out) @ mod.linear_z.weight.T) * torch.sigmoid(zn @ mod.linear_g.weight.T)
         return z
 
-    def triatt_in_proj(self, mod, z, mask):
+    def triatt_in_proj(self, mod, z, mask, ending=False, zn=None):
         n_u, n_t, _ = z.shape
         xn = _ln(z, mod.layer_norm)
         h, d = mod.no_heads, mod.c_hidden
@@ -66,7 +69,7 @@ class TorchStages:
         w = torch.softmax(logits * math.log(2.0), dim=-1)
         return torch.einsum("uhqk,uhdk->uqhd", w, v[..., :n]).reshape(n_u, n, h * d)
 
-    def triatt_out(self, mod, o, z):
+    def triatt_out(self, mod, o, z, ending=False, zn=None):
         xn = _ln(z, mod.layer_norm)
         z += (o * torch.sigmoid(xn @ mod.mha.linear_g.weight.T)) @ mod.mha.linear_o.weight.T
         return z

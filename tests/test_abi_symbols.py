@@ -51,7 +51,7 @@ def test_binding_table_matches_header(lib):
 def test_host_side_queries(lib):
     assert lib.px_version() >= 100
     assert lib.px_ld(1) == 8 and lib.px_ld(128) == 128 and lib.px_ld(129) == 136
-    assert lib.px_trimul_workspace_bytes(128) == 3 * 128 * 128 * 128 * 2
+    assert lib.px_trimul_workspace_bytes(128) == 4 * 128 * 128 * 128 * 2   # a, b, x and the standardised rows, fp16
     assert lib.px_triatt_workspace_bytes(64) > 4 * 64 * 64 * 128 * 2
     assert lib.px_status_string(0) == b"ok"
     assert b"workspace" in lib.px_status_string(-4)

@@ -3,7 +3,7 @@
 Some hosts of this library have no way to give it a workspace: a plug-in inside an application
 that has already handed every byte of device memory to its own pool (cudaMalloc fails there), or a
 latency-critical thread that may not call cudaMalloc/cudaFree because those synchronise the whole
-device.  For them the library carries a fixed 12 MiB scratch array in its own image (N <= 128).
+device.  For them the library carries a fixed 16 MiB scratch array in its own image (N <= 128).
 This test drives that entry point through the C ABI and compares it with the workspace-taking
 entry point on the same inputs, twice in a row with different sizes, because the second call finds
 the first call's leftovers in the shared array.
