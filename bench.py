@@ -215,12 +215,15 @@ def kernel_algo(n: int, zbytes: int) -> dict:
         "px_triatt_flash": ("tensor", 512.0 * n ** 3),
         "px_trimul_contract": ("tensor", 256.0 * n ** 3),
         "px_transition": ("tensor", 393216.0 * n2),
-        "px_trimul_in_proj": ("hbm", (128 * zbytes + 4 + 512) * n2),
-        "px_trimul_out": ("hbm", (256 + 2 * 128 * zbytes) * n2),
-        "px_triatt_in_proj": ("hbm", (128 * zbytes + 4 + 768 + 20) * n2),
-        "px_triatt_out": ("hbm", (256 + 2 * 128 * zbytes) * n2),
-        "px_pair_bias_proj": ("hbm", (128 * zbytes + 64) * n2),
+        # the projections read 16-bit rows (bf16 z, or the standardised fp16 copy of an fp32 z); the output stages
+        # read those rows and x / o, and read and write the residual stream in its storage type
+        "px_trimul_in_proj": ("hbm", (256 + 4 + 512) * n2),
+        "px_trimul_out": ("hbm", (256 + (256 if zbytes == 4 else 0) + 2 * 128 * zbytes) * n2),
+        "px_triatt_in_proj": ("hbm", (256 + 4 + 768 + 20) * n2),
+        "px_triatt_out": ("hbm", (256 + (256 if zbytes == 4 else 0) + 2 * 128 * zbytes) * n2),
+        "px_pair_bias_proj": ("hbm", (256 + 64) * n2),
         "px_recycle_update": ("hbm", 3 * 128 * zbytes * n2),
+        "px_standardise_rows": ("hbm", 768.0 * n2),
     }
 
 

@@ -131,7 +131,8 @@ PX_API int32_t px_trimul_contract(const px_f16* a, const px_f16* b, px_f16* x, i
 #define PX_FAMILY_PAIR_BIAS 7
 #define PX_FAMILY_RECYCLE 8
 #define PX_FAMILY_SELFTEST 9
-#define PX_N_FAMILIES 10
+#define PX_FAMILY_PEER 10 /* px_peer_barrier: a rank did not arrive; detail bit r names the rank (mod 16) */
+#define PX_N_FAMILIES 11
 PX_API int32_t px_device_error_flags(uint32_t* flags);
 PX_API int32_t px_device_error_detail(uint32_t* flags, uint32_t* detail);
 /* Limit of every bounded wait on the current device, in SM clock cycles (default 2^28, about 0.14 s); cycles <= 0
@@ -252,8 +253,8 @@ PX_API int32_t px_recycle_update(const void* z, const void* z_init, void* out, i
  * cudaMalloc allocation whose 64-byte handle other processes on the same machine can open;
  * px_copy_2d copies `height` rows of `width_bytes` (pointers, pitches and width multiples of 16
  * bytes) with a hand-written kernel: 16-byte loads and stores, dst may be an opened peer buffer
- * (plain stores over NVLink; no TMA, no multicast).  Ordering across GPUs is the caller's job
- * (a stream-ordered collective after the copies, before the receiver's kernels). */
+ * (plain stores over NVLink; no TMA, no multicast).  Ordering across GPUs is the caller's job:
+ * px_peer_barrier after the copies, before the receiver's kernels. */
 #define PX_PEER_HANDLE_BYTES 64
 PX_API int32_t px_peer_alloc(int64_t bytes, void** ptr, unsigned char* handle);
 PX_API int32_t px_peer_open(const unsigned char* handle, void** ptr);
@@ -261,6 +262,18 @@ PX_API int32_t px_peer_close(void* ptr);
 PX_API int32_t px_peer_free(void* ptr);
 PX_API int32_t px_copy_2d(void* dst, int64_t dpitch, const void* src, int64_t spitch, int64_t width_bytes,
                           int64_t height, void* stream);
+/* The copy of px_copy_2d issued to the copy engines (cudaMemcpy2DAsync): uses no SM, overlaps any kernel; for wide
+ * rows.  No alignment requirement. */
+PX_API int32_t px_copy_2d_dma(void* dst, int64_t dpitch, const void* src, int64_t spitch, int64_t width_bytes,
+                              int64_t height, void* stream);
+/* Barrier between the `world` (<= PX_COPY_BATCH_MAX) ranks of a box, stream-ordered on every rank: completes on a
+ * rank once every rank has reached its call with the same `epoch`, i.e. once everybody's earlier copies are in place.
+ * flag_arrays[r] is rank r's flag array (at least `world` 32-bit words in a peer buffer, zero at the start) as mapped
+ * into this process; `epoch` is 1 for the first barrier on these arrays and grows by one per barrier, on all ranks
+ * alike.  One warp: system-scope release stores into the peers' arrays, bounded acquire polling of the own one.  A
+ * rank that does not arrive within the wait limit sets PX_FAMILY_PEER in px_device_error_flags on the waiting ranks.
+ * Every rank must run on its own GPU.  No counterpart in the reference. */
+PX_API int32_t px_peer_barrier(void* const* flag_arrays, int32_t rank, int32_t world, uint32_t epoch, void* stream);
 /* The same copy geometry for `count` (<= PX_COPY_BATCH_MAX) source/destination pairs in one launch. */
 #define PX_COPY_BATCH_MAX 16
 PX_API int32_t px_copy_2d_batch(void* const* dst, const void* const* src, int32_t count, int64_t dpitch, int64_t spitch,

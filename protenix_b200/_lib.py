@@ -49,7 +49,9 @@ SIGNATURES = {
     "px_peer_open": (I32, [P, P]),
     "px_peer_close": (I32, [P]),
     "px_peer_free": (I32, [P]),
+    "px_peer_barrier": (I32, [P, I32, I32, ctypes.c_uint32, P]),
     "px_copy_2d": (I32, [P, I64, P, I64, I64, I64, P]),
+    "px_copy_2d_dma": (I32, [P, I64, P, I64, I64, I64, P]),
     "px_copy_2d_batch": (I32, [P, P, I32, I64, I64, I64, I64, P]),
 }
 

@@ -327,6 +327,49 @@ __device__ __forceinline__ void tile_product_loop(const TileCtx& c, uint32_t d_t
   }
 }
 
+// fp32 output rows, coalesced.  A thread of the epilogue owns one row (its accumulator lane) and 32 consecutive
+// channels of it; written as they are, a warp's store would touch 32 rows 512 bytes apart.  Instead the warp passes
+// its [32 rows][32 channels] block through a private 4 KB staging area (rows of 128 bytes, 16-byte pieces swizzled
+// by row) and reads it back with 8 lanes per row, so that every global access of the warp covers four rows x 128
+// contiguous bytes.  `res` holds the residual values of the same block in the read-back arrangement, loaded by
+// rows_out_request before the accumulator is waited for (zeros without a residual).
+struct RowsOutReq {
+  float4 v[8];
+};
+// first_row: index (inside the tensor, in rows of 128 channels) of the warp's row 0; row_stride: distance in rows
+// between consecutive rows of the warp (1, or n_u for a column slab); rows_valid: how many of the 32 rows exist.
+__device__ __forceinline__ void rows_out_request(RowsOutReq& rq, const float* __restrict__ z, long long first_row,
+                                                 long long row_stride, int rows_valid, int chan0, int lane, bool want) {
+  const int rsub = lane >> 3, piece = lane & 7;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int rl = 4 * it + rsub;
+    rq.v[it] = (want && rl < rows_valid)
+                   ? __ldg(reinterpret_cast<const float4*>(z + (size_t)(first_row + rl * row_stride) * kC + chan0) + piece)
+                   : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+__device__ __forceinline__ void rows_out_store(unsigned char* stg, const float (&v)[32], const RowsOutReq& rq,
+                                               float* __restrict__ out, long long first_row, long long row_stride,
+                                               int rows_valid, int chan0, int lane) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c)
+    *reinterpret_cast<float4*>(stg + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+        make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+  __syncwarp();
+  const int rsub = lane >> 3, piece = lane & 7;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int rl = 4 * it + rsub;
+    float4 o = *reinterpret_cast<const float4*>(stg + rl * 128 + ((piece ^ (rl & 7)) << 4));
+    if (rl < rows_valid) {
+      o.x += rq.v[it].x, o.y += rq.v[it].y, o.z += rq.v[it].z, o.w += rq.v[it].w;
+      *(reinterpret_cast<float4*>(out + (size_t)(first_row + rl * row_stride) * kC + chan0) + piece) = o;
+    }
+  }
+  __syncwarp();
+}
+
 // Number of SMs of the current device (cached per device ordinal).
 static inline int sm_count() {
   static int cached[64] = {};

@@ -202,7 +202,20 @@ triatt_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
     bool ok = true;
     for (int tile = ctx.first_tile; tile < n_tiles && ok; tile += ctx.tile_step, ++k) {
       const int s = k % kTileStages;
-      const int u = tile / tiles_t, t0 = (tile % tiles_t) * 128, t = t0 + row;
+      const int u = tile / tiles_t, t0 = (tile % tiles_t) * 128;
+      // fp32 rows: this warp's 32 rows (u, t0 + 32 qw + i) in units of 128-channel rows of z, and their residual
+      // values for the first 32 channels, requested before the wait (the second block's lines are asked of L2)
+      const long long first_row = swap ? (long long)(t0 + 32 * qw) * n_u + u : (long long)u * n + t0 + 32 * qw;
+      const long long row_stride = swap ? n_u : 1;
+      const int valid = n - (t0 + 32 * qw) < 32 ? (n - (t0 + 32 * qw) > 0 ? n - (t0 + 32 * qw) : 0) : 32;
+      RowsOutReq rq;
+      if (!kTma) {
+        rows_out_request(rq, reinterpret_cast<const float*>(z_in), first_row, row_stride, valid, 64 * half, lane,
+                         add_residual != 0);
+        if (add_residual && lane < valid)
+          asm volatile("prefetch.global.L2 [%0];\n" ::"l"(reinterpret_cast<const float*>(z_in) +
+                                                            (size_t)(first_row + lane * row_stride) * kC + 64 * half + 32));
+      }
       ok = mbar_wait(&bars.out_full, k & 1, 64u);
       ok = named_barrier_all(1, 256, ok);                  // all eight warps go on, or none
       if (!ok) break;
@@ -239,20 +252,17 @@ triatt_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
             }
             *reinterpret_cast<uint4*>(otile + operand_piece_offset(row, piece)) = make_uint4(w[0], w[1], w[2], w[3]);
           }
-        } else if (t < n) {
-          // fp32 rows: residual from global memory, plain stores
-          const size_t off = (swap ? ((size_t)t * n_u + u) : ((size_t)u * n + t)) * kC + 64 * half + 32 * hh;
+        } else {
+          // fp32 rows: coalesced through a warp-private staging area inside the o tile, which the gate warps and
+          // the tensor core have finished reading (8 warps x 4 KB)
+          float v[32];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float4 v = make_float4(__uint_as_float(acc[4 * j]), __uint_as_float(acc[4 * j + 1]),
-                                   __uint_as_float(acc[4 * j + 2]), __uint_as_float(acc[4 * j + 3]));
-            if (add_residual) {
-              const float4 r4 = load4(z_in + off + 4 * j);
-              v.x += r4.x, v.y += r4.y, v.z += r4.z, v.w += r4.w;
-            }
-            store2(z_out + off + 4 * j, v.x, v.y);
-            store2(z_out + off + 4 * j + 2, v.z, v.w);
-          }
+          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(acc[e]);
+          rows_out_store(otile + (warp & 7) * 4096, v, rq, reinterpret_cast<float*>(z_out), first_row, row_stride, valid,
+                         64 * half + 32 * hh, lane);
+          if (hh == 0)
+            rows_out_request(rq, reinterpret_cast<const float*>(z_in), first_row, row_stride, valid, 64 * half + 32, lane,
+                             add_residual != 0);
         }
       }
       if (kTma) {

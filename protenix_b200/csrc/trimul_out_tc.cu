@@ -192,7 +192,7 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
     int k = 0;
     bool ok = true;
     for (int tile = first_tile; tile < n_tiles; tile += tile_step, ++k) {
-      const int s = k % kToStages, m = k / kToStages;
+      const int s = k % kToStages;
       float sumsq[2];
 #pragma unroll
       for (int which = 0; which < 2; ++which) {              // 0: z, 1: x
@@ -245,7 +245,13 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
     bool ok = true;
     for (int tile = first_tile; tile < n_tiles && ok; tile += tile_step, ++k) {
       const int s = k % kToStages;
-      const int i = tile / tiles_j, j0 = (tile % tiles_j) * 128, j = j0 + row;
+      const int i = tile / tiles_j, j0 = (tile % tiles_j) * 128;
+      RowsOutReq rq;
+      if (!kTma) {                                         // the residual values are requested before the wait
+        const int valid = n - (j0 + 32 * qw) < 32 ? (n - (j0 + 32 * qw) > 0 ? n - (j0 + 32 * qw) : 0) : 32;
+        rows_out_request(rq, reinterpret_cast<const float*>(z_in), (long long)i * n + j0 + 32 * qw, 1, valid, 32 * part, lane,
+                         add_residual != 0);
+      }
       ok = mbar_wait(&bars.acc_full, k & 1, 32u);
       ok = named_barrier_all(1, 512, ok);                  // all sixteen warps go on, or none
       if (!ok) break;
@@ -294,20 +300,11 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
           mbar_arrive(&bars.a_empty[s]);
         }
       } else {
-        if (j < n) {
-          // fp32 rows: residual from global memory, plain stores
-          const size_t off = ((size_t)i * n + j) * kC + 32 * part;
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            if (add_residual) {
-              const float4 r4 = load4(z_in + off + 4 * q);
-              o.x += r4.x, o.y += r4.y, o.z += r4.z, o.w += r4.w;
-            }
-            store2(z_out + off + 4 * q, o.x, o.y);
-            store2(z_out + off + 4 * q + 2, o.z, o.w);
-          }
-        }
+        // fp32 rows: coalesced through a warp-private staging area inside the stage's tiles, which the tensor core
+        // has finished reading (16 warps x 4 KB = the z tile and the x tile)
+        unsigned char* stg = sm + (warp < 8 ? ToLayout::zt : ToLayout::xt) + s * kOperandBytes + (warp & 7) * 4096;
+        const int valid = n - (j0 + 32 * qw) < 32 ? (n - (j0 + 32 * qw) > 0 ? n - (j0 + 32 * qw) : 0) : 32;
+        rows_out_store(stg, v, rq, reinterpret_cast<float*>(z_out), (long long)i * n + j0 + 32 * qw, 1, valid, 32 * part, lane);
         named_barrier(1, 512);
         if (leader) mbar_arrive(&bars.a_empty[s]);
       }

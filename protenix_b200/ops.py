@@ -6,6 +6,7 @@ status.  torch is used for memory and streams only.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -131,7 +132,7 @@ def _launch(name: str, fn, *args) -> None:
 
 
 KERNEL_FAMILIES = ("trimul_contract", "triatt_flash", "transition", "trimul_in_proj", "trimul_out", "triatt_in_proj",
-                   "triatt_out", "pair_bias_proj", "recycle_update", "selftest")   # bit order of px_device_error_flags
+                   "triatt_out", "pair_bias_proj", "recycle_update", "selftest", "peer_barrier")   # bit order of px_device_error_flags
 
 
 def device_error_flags(device=None, raise_on_error: bool = True) -> int:
@@ -489,14 +490,21 @@ def pair_bias_rows(z: torch.Tensor, ln_w, ln_b: Optional[torch.Tensor], w: torch
     return out
 
 
-def transition_rows(x: torch.Tensor, ln_w, ln_b, w_a, w_b, w_o, eps: float = 1e-5) -> torch.Tensor:
-    """x += Transition(x) in place for any [..., 128] slab."""
+def transition_rows(x: torch.Tensor, ln_w, ln_b, w_a, w_b, w_o, eps: float = 1e-5,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = x + Transition(x) for any [..., 128] slab; in place when ``out`` is None."""
     _need_cuda(x, "x")
+    if out is None:
+        out = x
+    else:
+        _need_cuda(out, "out")
+        if out.shape != x.shape or out.dtype != x.dtype:
+            raise RuntimeError("out must match x")
     w_a, w_b = _w(w_a, F16, (4 * C_Z, C_Z), "w_a"), _w(w_b, F16, (4 * C_Z, C_Z), "w_b")
     w_o = _w(w_o, F16, (C_Z, 4 * C_Z), "w_o")
-    _launch("px_transition", _lib.load().px_transition, _ptr(x), _ptr(x), _pair_dtype(x), _ptr(ln_w), _ptr(ln_b),
+    _launch("px_transition", _lib.load().px_transition, _ptr(x), _ptr(out), _pair_dtype(x), _ptr(ln_w), _ptr(ln_b),
             _ptr(w_a), _ptr(w_b), _ptr(w_o), x.numel() // C_Z, 1, float(eps), _stream(x))
-    return x
+    return out
 
 
 # ---------------------------------------------------------------------------------------------
@@ -554,6 +562,15 @@ def peer_close(ptr: int) -> None:
     _lib.load().px_peer_close(ptr)
 
 
+def peer_barrier(flag_ptrs, rank: int, world: int, epoch: int, device: torch.device) -> None:
+    """Stream-ordered barrier between the ranks of a box through flags in peer memory (one small kernel per rank)."""
+    import ctypes
+
+    arr = (ctypes.c_void_p * world)(*[int(p) for p in flag_ptrs])
+    _launch("px_peer_barrier", _lib.load().px_peer_barrier, arr, int(rank), int(world), int(epoch) & 0xFFFFFFFF,
+            torch.cuda.current_stream(device).cuda_stream)
+
+
 def copy_2d(dst_ptr: int, dpitch: int, src: torch.Tensor, src_offset_bytes: int, spitch: int, width_bytes: int,
             height: int) -> None:
     """height rows of width_bytes from src (+offset) to the raw address dst_ptr, on src's current stream."""
@@ -561,11 +578,22 @@ def copy_2d(dst_ptr: int, dpitch: int, src: torch.Tensor, src_offset_bytes: int,
             int(spitch), int(width_bytes), int(height), _stream(src))
 
 
+DMA_MIN_WIDTH = 16384     # rows at least this wide go to the copy engines, narrower ones to the copy kernel
+
+
 def copy_2d_batch(dst_ptrs, src: torch.Tensor, src_offsets, dpitch: int, spitch: int, width_bytes: int, height: int) -> None:
-    """One launch: for every i, height rows of width_bytes from src (+src_offsets[i]) to the raw address dst_ptrs[i]."""
+    """For every i, height rows of width_bytes from src (+src_offsets[i]) to the raw address dst_ptrs[i], on src's
+    current stream: one pitched copy-engine transfer per destination when the rows are wide (no SM involved, so the
+    transfers overlap the compute kernels), one launch of the copy kernel otherwise."""
     import ctypes
 
     n = len(dst_ptrs)
+    if width_bytes >= DMA_MIN_WIDTH and os.environ.get("PX_PEER_DMA", "1") != "0":
+        lib, st = _lib.load(), _stream(src)
+        for d, o in zip(dst_ptrs, src_offsets):
+            _launch("px_copy_2d_dma", lib.px_copy_2d_dma, int(d), int(dpitch), src.data_ptr() + int(o), int(spitch),
+                    int(width_bytes), int(height), st)
+        return
     d = (ctypes.c_void_p * n)(*[int(p) for p in dst_ptrs])
     s_ = (ctypes.c_void_p * n)(*[src.data_ptr() + int(o) for o in src_offsets])
     _launch("px_copy_2d_batch", _lib.load().px_copy_2d_batch, d, s_, n, int(dpitch), int(spitch), int(width_bytes),

@@ -82,11 +82,11 @@ class CudaStages:
         return ops.triatt_out(o, z, f(mod.layer_norm.weight), f(mod.layer_norm.bias), m.linear_g.weight,
                               m.linear_o.weight, mod.layer_norm.eps, ending, zn=zn)
 
-    def transition(self, mod, z):
+    def transition(self, mod, z, out=None):
         f = self._f
         return ops.transition_rows(z, f(mod.layernorm1.weight), f(mod.layernorm1.bias),
                                    mod.linear_no_bias_a.weight, mod.linear_no_bias_b.weight,
-                                   mod.linear_no_bias.weight, mod.layernorm1.eps)
+                                   mod.linear_no_bias.weight, mod.layernorm1.eps, out=out)
 
     def pair_bias(self, mod, z):
         b = mod.layernorm_z.bias
@@ -113,10 +113,14 @@ class PeerExchange:
         nl, cp, ldn = n // world, 128 // world, (n + 7) // 8 * 8
         ldm = (n + 127) // 128 * 128
         sizes = {"a": cp * n * ldn * 2, "b": cp * n * ldn * 2, "x": 128 * nl * ldn * 2,
-                 "zc": n * nl * 128 * z_itemsize, "zr": nl * n * 128 * z_itemsize, "bias": 4 * n * ldm * 4}
+                 "zc": n * nl * 128 * z_itemsize, "zr": nl * n * 128 * z_itemsize, "bias": 4 * n * ldm * 4,
+                 "flags": 256}
         self.local: Dict[str, ops.PeerBuffer] = {k: ops.PeerBuffer(v, device) for k, v in sizes.items()}
-        for k in ("a", "b"):       # pad columns [n, ld) are never written by an exchange and must read as zero
+        for k in ("a", "b", "flags"):   # pad columns [n, ld) are never written by an exchange and must read as zero
             self.local[k].tensor((sizes[k],), torch.uint8).zero_()
+        self.epoch = 0                  # number of the last barrier; the same sequence on every rank
+        self.comm = torch.cuda.Stream(device=device)      # copies and barriers run here, beside the compute stream
+        self.use_flags = os.environ.get("PX_PEER_FENCE", "flags") != "nccl"
         torch.cuda.synchronize(device)
         handles = [None] * world
         dist.all_gather_object(handles, {k: b.handle for k, b in self.local.items()}, group=group)
@@ -136,8 +140,32 @@ class PeerExchange:
                           dpitch, spitch, width, height)
 
     def fence(self) -> None:
-        """Stream-ordered: completes on a rank only after every rank's earlier copies have completed."""
-        dist.all_reduce(self.flag, group=self.group)
+        """Stream-ordered (current stream): completes on a rank only after every rank's earlier copies have completed.
+        A barrier of flags in peer memory (``px_peer_barrier``); ``PX_PEER_FENCE=nccl`` selects a 4-byte all_reduce."""
+        self.epoch += 1
+        if self.use_flags:
+            ops.peer_barrier(self.remote["flags"], self.rank, self.world, self.epoch, self.device)
+        else:
+            dist.all_reduce(self.flag, group=self.group)
+
+    def send(self, fn, *keep: torch.Tensor) -> None:
+        """Runs ``fn`` (copies into peer buffers) on the communication stream, after everything the compute stream has
+        been given so far; the compute stream goes on.  ``keep``: tensors the copies read (their memory must not be
+        reused before the copies are through)."""
+        main = torch.cuda.current_stream(self.device)
+        self.comm.wait_stream(main)
+        for t in keep:
+            t.record_stream(self.comm)
+        with torch.cuda.stream(self.comm):
+            fn()
+
+    def join(self) -> None:
+        """Barrier after the copies sent so far, on the communication stream; the compute stream waits for it."""
+        main = torch.cuda.current_stream(self.device)
+        self.comm.wait_stream(main)
+        with torch.cuda.stream(self.comm):
+            self.fence()
+        main.wait_stream(self.comm)
 
     def close(self) -> None:
         """Unmaps the other ranks' buffers and frees this rank's (after a barrier: nobody may still be writing)."""
@@ -250,30 +278,36 @@ class ShardedPairformer:
             self._peer[key] = PeerExchange(self.group, self.world, self.rank, z_loc.device, n, z_loc.element_size())
         return self._peer[key]
 
-    def _peer_rows_to_channels(self, px: PeerExchange, t: torch.Tensor, key: str, k_sharded: bool) -> None:
-        """The copies of ``_rows_to_channels`` (no fence): t [128][rows][ld] -> buffer ``key`` [128/P][N][ld(N)]."""
+    def _peer_rows_to_channels(self, px: PeerExchange, t: torch.Tensor, key: str, k_sharded: bool, nl: int,
+                               r0: int = 0) -> None:
+        """The copies of ``_rows_to_channels`` (no fence) for local rows [r0, r0 + rc) of this rank's nl rows:
+        t [128][rc][ld] (or, ``k_sharded``, [128][N][ld(rc)]) -> buffer ``key`` [128/P][N][ld(N)]."""
         p, me = self.world, self.rank
         c, r, ldl = t.shape
         cp = c // p
-        if not k_sharded:          # my rows become rows me*r.. of every channel: one run of r*ld per channel
-            px.put_all(key, me * r * ldl * 2, p * r * ldl * 2, t, lambda d: d * cp * r * ldl * 2, r * ldl * 2, r * ldl * 2, cp)
-        else:                      # my rows are the contraction index: a run of N/P per (channel, i)
-            nl, ldn = r // p, (r + 7) // 8 * 8
-            px.put_all(key, me * nl * 2, ldn * 2, t, lambda d: d * cp * r * ldl * 2, ldl * 2, nl * 2, cp * r)
+        if not k_sharded:          # my rows become rows me*nl + r0.. of every channel: one run of rc*ld per channel
+            px.put_all(key, (me * nl + r0) * ldl * 2, p * nl * ldl * 2, t, lambda d: d * cp * r * ldl * 2, r * ldl * 2,
+                       r * ldl * 2, cp)
+        else:                      # my rows are the contraction index: a run of rc per (channel, i)
+            ldn = (r + 7) // 8 * 8
+            px.put_all(key, (me * nl + r0) * 2, ldn * 2, t, lambda d: d * cp * r * ldl * 2, ldl * 2, ldl * 2, cp * r)
 
-    def _peer_channels_to_rows(self, px, x: torch.Tensor) -> None:
-        """x [128/P][N][ld] (my channels) -> buffer ``x`` [128][N/P][ld] of every rank: rows d*nl.. go to rank d."""
+    def _peer_channels_to_rows(self, px, x: torch.Tensor, c0: int = 0) -> None:
+        """x [cc][N][ld] (channels c0.. of my 128/P) -> buffer ``x`` [128][N/P][ld] of every rank: rows d*nl.. go to
+        rank d."""
         p, me = self.world, self.rank
-        cp, n, ldn = x.shape
-        nl = n // p
-        px.put_all("x", me * cp * nl * ldn * 2, nl * ldn * 2, x, lambda d: d * nl * ldn * 2, n * ldn * 2, nl * ldn * 2, cp)
+        cc, n, ldn = x.shape
+        nl, cp = n // p, 128 // p
+        px.put_all("x", (me * cp + c0) * nl * ldn * 2, nl * ldn * 2, x, lambda d: d * nl * ldn * 2, n * ldn * 2,
+                   nl * ldn * 2, cc)
 
-    def _peer_to_columns(self, px, z_loc: torch.Tensor) -> None:
-        """Row slab [N/P i][N j][c] -> buffer ``zc`` [N i][N/P j][c] of every rank: columns d*nl.. go to rank d."""
+    def _peer_to_columns(self, px, z_rows: torch.Tensor, nl: int, r0: int = 0) -> None:
+        """Rows [r0, r0 + rc) of the row slab [N/P i][N j][c] -> buffer ``zc`` [N i][N/P j][c] of every rank: columns
+        d*nl.. go to rank d."""
         p, me = self.world, self.rank
-        nl, n, c = z_loc.shape
-        run = nl * c * z_loc.element_size()
-        px.put_all("zc", me * nl * run, run, z_loc, lambda d: d * run, p * run, run, nl)
+        rc, n, c = z_rows.shape
+        run = nl * c * z_rows.element_size()
+        px.put_all("zc", (me * nl + r0) * run, run, z_rows, lambda d: d * run, p * run, run, rc)
 
     def _peer_from_columns(self, px, zc: torch.Tensor) -> None:
         """Column slab [N i][N/P j][c] -> buffer ``zr`` [N/P i][N j][c] of every rank: rows e*nl.. go to rank e."""
@@ -289,50 +323,70 @@ class ShardedPairformer:
         run = nl * ldm * bias_loc.element_size()
         px.put_all("bias", me * run, p * run, bias_loc, lambda d: 0, run, run, h)
 
-    def _tri_att_start_peer(self, px: PeerExchange, mod, z_loc, mask_loc) -> None:
-        st = self.stages
-        zn = st.standardised(z_loc, mod.layer_norm.eps)
-        q, k, v, bias_loc, mb = st.triatt_in_proj(mod, z_loc, mask_loc, zn=zn)
-        h, nl, ldm = bias_loc.shape
-        self._peer_gather_bias(px, bias_loc)
-        px.fence()
-        bias_full = px.local["bias"].tensor((h, self.world * nl, ldm), torch.float32)
-        st.triatt_out(mod, st.triatt_flash(q, k, v, bias_full, mb), z_loc, zn=zn)
+    # The exchanges are pipelined against the kernels that produce their data: the producer runs in row (or channel)
+    # chunks on the compute stream, and the copies of a chunk run on the communication stream while the next chunk
+    # is being computed; one barrier of flags closes each exchange.  A rank arrives at a barrier only after all the
+    # compute-stream work it was given before the exchange, so a receive buffer is never overwritten while its owner
+    # still reads what the previous exchange left there.
+    def _row_chunks(self, nl: int):
+        """Splits the nl local rows into pieces of multiples of 8 rows (copied runs are multiples of 16 bytes)."""
+        want = max(1, int(os.environ.get("PX_PEER_CHUNKS", "2")))
+        units = nl // 8
+        k = max(1, min(want, units))
+        cuts = [8 * (units * i // k) for i in range(k + 1)]
+        return [(cuts[i], cuts[i + 1]) for i in range(k) if cuts[i + 1] > cuts[i]]
 
     def _tri_mul_peer(self, px: PeerExchange, mod, z_loc, mask_loc, incoming: bool) -> None:
         st, p, me = self.stages, self.world, self.rank
         nl, n, _ = z_loc.shape
         cp, ldn = 128 // p, (n + 7) // 8 * 8
         zn = st.standardised(z_loc, mod.layer_norm_in.eps)
-        a, b = st.trimul_in_proj(mod, z_loc, mask_loc, incoming, zn=zn)
-        self._peer_rows_to_channels(px, a, "a", incoming)
-        self._peer_rows_to_channels(px, b, "b", incoming)
-        px.fence()
-        del a, b
-        x = st.trimul_contract(px.local["a"].tensor((cp, n, ldn), torch.float16),
-                               px.local["b"].tensor((cp, n, ldn), torch.float16))
-        self._peer_channels_to_rows(px, x)
-        px.fence()
-        del x
+        for r0, r1 in self._row_chunks(nl):
+            a, b = st.trimul_in_proj(mod, z_loc[r0:r1], None if mask_loc is None else mask_loc[r0:r1], incoming,
+                                     zn=None if zn is None else zn[r0:r1])
+            px.send(lambda a=a, b=b, r0=r0: (self._peer_rows_to_channels(px, a, "a", incoming, nl, r0),
+                                              self._peer_rows_to_channels(px, b, "b", incoming, nl, r0)), a, b)
+            del a, b
+        px.join()
+        a_full = px.local["a"].tensor((cp, n, ldn), torch.float16)
+        b_full = px.local["b"].tensor((cp, n, ldn), torch.float16)
+        halves = [(0, cp)] if cp < 2 else [(0, cp // 2), (cp // 2, cp)]
+        for c0, c1 in halves:                       # the contraction in two channel groups: x of the first travels
+            x = st.trimul_contract(a_full[c0:c1], b_full[c0:c1])      # while the second is contracted
+            px.send(lambda x=x, c0=c0: self._peer_channels_to_rows(px, x, c0), x)
+            del x
+        px.join()
         st.trimul_out(mod, px.local["x"].tensor((128, nl, ldn), torch.float16), z_loc, zn=zn)
 
-    def _tri_att_end_peer(self, px: PeerExchange, mod, z_loc, mask_cols) -> None:
-        """Ending node on the column slab zc [N i][N/P j][c] (the kernels address it as element (u=j, t=i))."""
+    def _tri_att_pair_peer(self, px: PeerExchange, start, end, z_loc, mask_loc, mask_cols) -> torch.Tensor:
+        """Starting-node then ending-node attention.  The output stage of the first runs in row chunks whose rows leave
+        for the column slabs of the other ranks as soon as they are final; the second works on the received column slab
+        zc [N i][N/P j][c] (the kernels address it as element (u=j, t=i)) and sends the rows back.  Returns the
+        updated row slab: a view of this rank's receive buffer (the caller's z_loc is NOT written)."""
         st, p, me = self.stages, self.world, self.rank
         nl, n, c = z_loc.shape
-        self._peer_to_columns(px, z_loc)
-        px.fence()
-        zc = px.local["zc"].tensor((n, nl, c), z_loc.dtype)
-        zn = st.standardised(zc, mod.layer_norm.eps)
-        q, k, v, bias_loc, mb = st.triatt_in_proj(mod, zc, mask_cols, True, zn=zn)
+        zn = st.standardised(z_loc, start.layer_norm.eps)
+        q, k, v, bias_loc, mb = st.triatt_in_proj(start, z_loc, mask_loc, zn=zn)
         h, _, ldm = bias_loc.shape
-        self._peer_gather_bias(px, bias_loc)
-        px.fence()
+        px.send(lambda: self._peer_gather_bias(px, bias_loc), bias_loc)
+        px.join()
         bias_full = px.local["bias"].tensor((h, p * nl, ldm), torch.float32)
-        st.triatt_out(mod, st.triatt_flash(q, k, v, bias_full, mb), zc, True, zn=zn)
-        self._peer_from_columns(px, zc)
-        px.fence()
-        z_loc.copy_(px.local["zr"].tensor((nl, n, c), z_loc.dtype))
+        o = st.triatt_flash(q, k, v, bias_full, mb)
+        del q, k, v
+        for r0, r1 in self._row_chunks(nl):
+            st.triatt_out(start, o[r0:r1], z_loc[r0:r1], zn=None if zn is None else zn[r0:r1])
+            px.send(lambda r0=r0, r1=r1: self._peer_to_columns(px, z_loc[r0:r1], nl, r0), z_loc)
+        px.join()
+        del o, zn
+        zc = px.local["zc"].tensor((n, nl, c), z_loc.dtype)
+        zn = st.standardised(zc, end.layer_norm.eps)
+        q, k, v, bias_loc, mb = st.triatt_in_proj(end, zc, mask_cols, True, zn=zn)
+        px.send(lambda: self._peer_gather_bias(px, bias_loc), bias_loc)
+        px.join()
+        st.triatt_out(end, st.triatt_flash(q, k, v, bias_full, mb), zc, True, zn=zn)
+        px.send(lambda: self._peer_from_columns(px, zc))
+        px.join()
+        return px.local["zr"].tensor((nl, n, c), z_loc.dtype)
 
     # ---- sub-modules ----------------------------------------------------------------------------
     def _tri_mul(self, mod, z_loc, mask_loc, incoming: bool) -> None:
@@ -404,8 +458,8 @@ class ShardedPairformer:
             if px is not None:
                 self._tri_mul_peer(px, blk.tri_mul_out, z_loc, mask_loc, incoming=False)
                 self._tri_mul_peer(px, blk.tri_mul_in, z_loc, mask_loc, incoming=True)
-                self._tri_att_start_peer(px, blk.tri_att_start, z_loc, mask_loc)
-                self._tri_att_end_peer(px, blk.tri_att_end, z_loc, mask_cols)
+                zr = self._tri_att_pair_peer(px, blk.tri_att_start, blk.tri_att_end, z_loc, mask_loc, mask_cols)
+                self.stages.transition(blk.pair_transition, zr, out=z_loc)    # reads the received rows, writes z_loc
             else:
                 self._tri_mul(blk.tri_mul_out, z_loc, mask_loc, incoming=False)
                 self._tri_mul(blk.tri_mul_in, z_loc, mask_loc, incoming=True)
@@ -414,7 +468,7 @@ class ShardedPairformer:
                 self._tri_att_rows(blk.tri_att_end, zt, mask_t_loc)
                 z_loc.copy_(self._transpose_shard(zt))
                 del zt
-            self.stages.transition(blk.pair_transition, z_loc)
+                self.stages.transition(blk.pair_transition, z_loc)
             if blk.c_s > 0 and s is not None:
                 bias = self.stages.pair_bias(blk.attention_pair_bias, z_loc)        # reads the block's final z
                 if side is None:

@@ -74,10 +74,14 @@ class TorchStages:
         z += (o * torch.sigmoid(xn @ mod.mha.linear_g.weight.T)) @ mod.mha.linear_o.weight.T
         return z
 
-    def transition(self, mod, z):
+    def transition(self, mod, z, out=None):
         y = _ln(z, mod.layernorm1)
-        z += (F.silu(y @ mod.linear_no_bias_a.weight.T) * (y @ mod.linear_no_bias_b.weight.T)) @ mod.linear_no_bias.weight.T
-        return z
+        upd = (F.silu(y @ mod.linear_no_bias_a.weight.T) * (y @ mod.linear_no_bias_b.weight.T)) @ mod.linear_no_bias.weight.T
+        if out is None:
+            z += upd
+            return z
+        out.copy_(z + upd)
+        return out
 
     def pair_bias(self, mod, z):
         return (_ln(z, mod.layernorm_z) @ mod.linear_nobias_z.weight.T).permute(2, 0, 1).contiguous()
