@@ -50,8 +50,22 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(BarrierPeers peers, in
 __global__ void __launch_bounds__(128)
 copy_2d_kernel(uint4* __restrict__ dst, long long dpitch16, const uint4* __restrict__ src, long long spitch16,
                long long units, long long height) {
-  const long long total = units * height;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+  const long long total = units * height, step = (long long)gridDim.x * blockDim.x;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  // four pieces in flight per thread: the loads from local memory overlap, the stores to peer memory are posted
+  for (; i + 3 * step < total; i += 4 * step) {
+    uint4 v[4];
+    long long at[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const long long j = i + k * step, r = j / units, c = j - r * units;
+      v[k] = __ldcs(src + r * spitch16 + c);
+      at[k] = r * dpitch16 + c;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) dst[at[k]] = v[k];
+  }
+  for (; i < total; i += step) {
     const long long r = i / units, c = i - r * units;
     dst[r * dpitch16 + c] = src[r * spitch16 + c];
   }
@@ -67,8 +81,22 @@ __global__ void __launch_bounds__(128)
 copy_2d_batch_kernel(CopyBatch b, long long dpitch16, long long spitch16, long long units, long long height) {
   uint4* __restrict__ dst = b.dst[blockIdx.y];
   const uint4* __restrict__ src = b.src[blockIdx.y];
-  const long long total = units * height;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+  const long long total = units * height, step = (long long)gridDim.x * blockDim.x;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  // four pieces in flight per thread: the loads from local memory overlap, the stores to peer memory are posted
+  for (; i + 3 * step < total; i += 4 * step) {
+    uint4 v[4];
+    long long at[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const long long j = i + k * step, r = j / units, c = j - r * units;
+      v[k] = __ldcs(src + r * spitch16 + c);
+      at[k] = r * dpitch16 + c;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) dst[at[k]] = v[k];
+  }
+  for (; i < total; i += step) {
     const long long r = i / units, c = i - r * units;
     dst[r * dpitch16 + c] = src[r * spitch16 + c];
   }

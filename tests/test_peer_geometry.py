@@ -1,5 +1,6 @@
 """The pitched copies of the peer transport, replayed on CPU: every rank's ``put_all`` calls are executed byte by byte
-into plain host buffers and the assembled buffers are compared with what the all_to_all path would deliver."""
+into plain host buffers and the assembled buffers are compared with what the all_to_all path would deliver.  Every
+exchange that the sharded path pipelines is replayed in the row (or channel) chunks it uses there."""
 import pytest
 import torch
 
@@ -49,19 +50,21 @@ def test_peer_copies_assemble_the_same_tensors_as_all_to_all(world, n):
     bf = torch.bfloat16
     # (1) rows -> channels, rows sharded: full_a [128][N][ld]
     full = torch.randn(128, n, ldn, generator=g).to(bf)
+    chunks = _rank(world, 0)._row_chunks(nl)
+    assert sum(b - a for a, b in chunks) == nl and all(a % 8 == 0 for a, _ in chunks)
     for r in range(world):
         fx.rank = r
-        _rank(world, r)._peer_rows_to_channels(fx, full[:, r * nl:(r + 1) * nl].contiguous(), "a", False)
+        for r0, r1 in chunks:
+            _rank(world, r)._peer_rows_to_channels(fx, full[:, r * nl + r0:r * nl + r1].contiguous(), "a", False, nl, r0)
     for d in range(world):
         assert torch.equal(fx.bufs["a"][d].view(bf).view(cp, n, ldn), full[d * cp:(d + 1) * cp])
     # (2) rows -> channels, contraction index sharded: local [128][N][ld(nl)], valid columns nl
     full_k = torch.randn(128, n, n, generator=g).to(bf)
-    ldl = _ld(nl)
     for r in range(world):
         fx.rank = r
-        loc = torch.zeros(128, n, ldl, dtype=bf)
-        loc[:, :, :nl] = full_k[:, :, r * nl:(r + 1) * nl]
-        _rank(world, r)._peer_rows_to_channels(fx, loc, "b", True)
+        for r0, r1 in chunks:
+            loc = full_k[:, :, r * nl + r0:r * nl + r1].contiguous()        # [128][N][rc], rc a multiple of 8
+            _rank(world, r)._peer_rows_to_channels(fx, loc, "b", True, nl, r0)
     for d in range(world):
         got = fx.bufs["b"][d].view(bf).view(cp, n, ldn)
         assert torch.equal(got[:, :, :n], full_k[d * cp:(d + 1) * cp]) and float(got[:, :, n:].float().abs().sum()) == 0.0
@@ -69,14 +72,16 @@ def test_peer_copies_assemble_the_same_tensors_as_all_to_all(world, n):
     xf = torch.randn(128, n, ldn, generator=g).to(bf)
     for r in range(world):
         fx.rank = r
-        _rank(world, r)._peer_channels_to_rows(fx, xf[r * cp:(r + 1) * cp].contiguous())
+        for c0, c1 in ((0, cp // 2), (cp // 2, cp)):
+            _rank(world, r)._peer_channels_to_rows(fx, xf[r * cp + c0:r * cp + c1].contiguous(), c0)
     for d in range(world):
         assert torch.equal(fx.bufs["x"][d].view(bf).view(128, nl, ldn), xf[:, d * nl:(d + 1) * nl])
     # (4) row slab -> column slab and back
     z = torch.randn(n, n, 128, generator=g).to(bf)
     for r in range(world):
         fx.rank = r
-        _rank(world, r)._peer_to_columns(fx, z[r * nl:(r + 1) * nl].contiguous())
+        for r0, r1 in chunks:
+            _rank(world, r)._peer_to_columns(fx, z[r * nl + r0:r * nl + r1].contiguous(), nl, r0)
     for d in range(world):
         assert torch.equal(fx.bufs["zc"][d].view(bf).view(n, nl, 128), z[:, d * nl:(d + 1) * nl])
     for r in range(world):
