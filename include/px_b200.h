@@ -98,6 +98,9 @@ PX_API int32_t px_layer_norm_fwd(const void* x, const void* gamma, const void* b
  * the same eps.  HBM-bound, 768 bytes per row.  No counterpart in the reference (its LayerNorm kernel writes the
  * normalised tensor in the input's type, protenix/model/layer_norm/kernel/layer_norm_cuda_kernel.cu:145-388). */
 PX_API int32_t px_standardise_rows(const float* z, px_f16* zn, int64_t rows, float eps, void* stream);
+/* z[row] += upd[row] over `rows` rows of 128 channels, z fp32, upd fp16: adds an update that was computed elsewhere
+ * (px_triatt_out with z_dtype PX_F16) to the residual stream.  No counterpart in the reference. */
+PX_API int32_t px_add_update_rows(float* z, const px_f16* upd, int64_t rows, void* stream);
 
 /* ---- Triangle multiplication (outgoing / incoming) ---------------------------------------
  * Stage 1: zn = LN(z); a = mask * sigmoid(W_ag zn) * (W_ap zn); b likewise.  a and b are
@@ -209,7 +212,8 @@ PX_API int32_t px_triatt_flash(const px_f16* q, const px_f16* k, const px_f16* v
 PX_API int64_t px_triatt_flash_scratch_bytes(int64_t n_u, int64_t n);
 /* Stage 3: z_out(u,t) = [z_in(u,t) +] W_o (o[u][t] * sigmoid(W_g LN(z_in(u,t)))), where (u,t)
  * addresses z[u][t] (starting) or z[t][u] (ending).  z_out may alias z_in.  zn: the standardised copy of z_in
- * (same layout) when z_dtype is PX_F32 (NULL otherwise).
+ * (same layout) when z_dtype is PX_F32 (NULL otherwise).  z_dtype PX_F16: z_in is itself the standardised fp16 copy
+ * and z_out receives the update alone, in fp16 (add_residual must be 0): for callers that add the update elsewhere.
  * Replaces Attention._wrap_up, protenix/model/triangular/layers.py:384-398. */
 PX_API int32_t px_triatt_out(const px_f16* o, const void* z_in, const px_f16* zn, void* z_out, int32_t z_dtype, const float* ln_w,
                       const float* ln_b, const px_w16* w_g, const px_f16* w_o, int64_t n_u, int64_t n_t, int32_t ending,

@@ -31,6 +31,7 @@ SIGNATURES = {
     "px_set_wait_limit_cycles": (I32, [I64]),
     "px_selftest_wait_timeout": (I32, [P, P]),
     "px_standardise_rows": (I32, [P, P, I64, F, P]),
+    "px_add_update_rows": (I32, [P, P, I64, P]),
     "px_trimul_out": (I32, [P, P, P, P, I32, P, P, P, P, P, P, I64, I64, I64, I32, F, P]),
     "px_trimul_workspace_bytes": (I64, [I64]),
     "px_triangle_multiplication": (I32, [P, P, I32, P, P, P, P, P, P, P, P, P, P, P, P, I64, I64, I32, I32, F, P]),

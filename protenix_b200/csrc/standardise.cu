@@ -56,7 +56,33 @@ __global__ void __launch_bounds__(256) standardise_rows_kernel(const float* __re
   }
 }
 
+// z[i] += upd[i] for an fp32 tensor and an fp16 update (the row-sharded path adds the ending-node update, computed
+// where the columns live and returned in fp16, to the rows it owns).  HBM-bound; eight elements per thread and step.
+__global__ void __launch_bounds__(256) add_update_kernel(float* __restrict__ z, const __half* __restrict__ upd, long long n8) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    const uint4 u = __ldcs(reinterpret_cast<const uint4*>(upd) + i);
+    float4 a = reinterpret_cast<const float4*>(z)[2 * i], b = reinterpret_cast<const float4*>(z)[2 * i + 1];
+    const float2 u0 = unpack_f16x2(u.x), u1 = unpack_f16x2(u.y), u2 = unpack_f16x2(u.z), u3 = unpack_f16x2(u.w);
+    a.x += u0.x, a.y += u0.y, a.z += u1.x, a.w += u1.y;
+    b.x += u2.x, b.y += u2.y, b.z += u3.x, b.w += u3.y;
+    reinterpret_cast<float4*>(z)[2 * i] = a;
+    reinterpret_cast<float4*>(z)[2 * i + 1] = b;
+  }
+}
+
 }  // namespace px
+
+extern "C" int32_t px_add_update_rows(float* z, const px_f16* upd, int64_t rows, void* stream) {
+  if (!z || !upd || rows < 0 || (((uintptr_t)z | (uintptr_t)upd) & 15)) return PX_ERR_BAD_ARG;
+  if (rows == 0) return PX_OK;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long n8 = (long long)rows * (px::kC / 8);
+  long long grid = (n8 + 255) / 256;
+  if (grid > 8ll * sms) grid = 8ll * sms;
+  px::add_update_kernel<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(z, (const __half*)upd, n8);
+  return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
+}
 
 extern "C" int32_t px_standardise_rows(const float* z, px_f16* zn, int64_t rows, float eps, void* stream) {
   if (!z || !zn || rows < 0 || (((uintptr_t)z | (uintptr_t)zn) & 15)) return PX_ERR_BAD_ARG;

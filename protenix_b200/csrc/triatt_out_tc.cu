@@ -1,6 +1,11 @@
 // Triangle attention, stage 3 on the 5th-generation tensor cores:
 //   z_out(u,t) = [z_in(u,t) +] W_o ( o[u][t] * sigmoid(W_g LN(z_in(u,t))) ),
 //   (u,t) = z[u][t] (starting node) or z[t][u] (ending node); z_out may alias z_in.
+// Three forms (kMode): 0 = z stored as bf16 (rows multiplied as stored, output through shared memory and TMA);
+// 1 = z stored as fp32 (the rows arrive as their standardised fp16 copy, residual and output fp32, coalesced through
+// a staging area); 2 = only the standardised fp16 rows are at hand and the update itself is wanted, in fp16, without
+// residual (the row-sharded path computes the ending-node update where the columns live and adds it where the rows
+// live, so that 16-bit tensors cross NVLink in both directions).
 //
 // Persistent kernel, one CTA per SM, on the row-tile pipeline of px_rowpipe.cuh (TMA-fed raw rows, LayerNorm folded
 // into the resident gate weights plus one correction K step, row statistics from a tensor-core Gram product).  A
@@ -47,15 +52,15 @@ struct AoLayout {
 };
 static_assert(AoLayout::a % 1024 == 0 && AoLayout::o % 1024 == 0, "tiles must keep the swizzle alignment");
 
-template <typename Tz>
+template <int kMode>
 __global__ void __launch_bounds__(kAoThreads, 1)
 triatt_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_o,
-                     const __grid_constant__ CUtensorMap map_out, const Tz* __restrict__ z_in, Tz* __restrict__ z_out,
+                     const __grid_constant__ CUtensorMap map_out, const void* __restrict__ z_in, void* __restrict__ z_out,
                      const float* __restrict__ ln_w, const float* __restrict__ ln_b, const bf16* __restrict__ w_g,
                      const bf16* __restrict__ w_o, int n_u, int n, int swap, int add_residual, float eps, int tiles_t,
                      int n_tiles) {
-  constexpr bool kTma = sizeof(Tz) == 2;               // bf16: residual from the z tile, output through TMA
-  constexpr bool kF16 = !kTma;                           // fp32 z: the z tile is its standardised fp16 copy; o, W_o fp16
+  constexpr bool kTma = kMode != 1;                      // 16-bit output: packed over the o tile, leaves through TMA
+  constexpr bool kF16 = kMode != 0;                      // the z tile is a standardised fp16 copy; o, W_o always fp16
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   AoBars& bars = *reinterpret_cast<AoBars*>(sm + AoLayout::bars);
@@ -242,13 +247,13 @@ triatt_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
               const uint32_t zw[4] = {zv.x, zv.y, zv.z, zv.w};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                const float2 r2 = unpack_bf16x2(zw[e]);
-                w[e] = pack_bf16x2_int(__uint_as_float(acc[8 * j + 2 * e]) + r2.x, __uint_as_float(acc[8 * j + 2 * e + 1]) + r2.y);
+                const float2 r2 = unpack16x2<kF16>(zw[e]);
+                w[e] = pack16x2<kF16>(__uint_as_float(acc[8 * j + 2 * e]) + r2.x, __uint_as_float(acc[8 * j + 2 * e + 1]) + r2.y);
               }
             } else {
 #pragma unroll
               for (int e = 0; e < 4; ++e)
-                w[e] = pack_bf16x2_int(__uint_as_float(acc[8 * j + 2 * e]), __uint_as_float(acc[8 * j + 2 * e + 1]));
+                w[e] = pack16x2<kF16>(__uint_as_float(acc[8 * j + 2 * e]), __uint_as_float(acc[8 * j + 2 * e + 1]));
             }
             *reinterpret_cast<uint4*>(otile + operand_piece_offset(row, piece)) = make_uint4(w[0], w[1], w[2], w[3]);
           }
@@ -293,25 +298,25 @@ triatt_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
 
 PX_DEFINE_FAMILY_HOOKS(triatt_out)
 
-template <typename Tz>
+template <int kMode>
 static int32_t launch_triatt_out(const px_f16* o, const void* z_in, const px_f16* zn, void* z_out, const float* ln_w, const float* ln_b,
                                  const px_bf16* w_g, const px_bf16* w_o, int64_t n_u, int64_t n, int32_t ending,
                                  int32_t add_residual, float eps, cudaStream_t st) {
   CUtensorMap mz, mo, mout;
   // operand rows: bf16 z itself, or the standardised fp16 copy of an fp32 z; pair element (u, t) is row u*n + t, or
   // row t*n_u + u when the two indices are exchanged
-  const CUtensorMapDataType zt = sizeof(Tz) == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  const void* zrows = sizeof(Tz) == 2 ? z_in : (const void*)zn;
+  const CUtensorMapDataType zt = kMode == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const void* zrows = kMode == 1 ? (const void*)zn : z_in;
   if (!(ending ? make_map_3d(&mz, zt, zrows, 128, (uint64_t)n_u, (uint64_t)n, 256, (uint64_t)n_u * 256, 64, 1,
                              CU_TENSOR_MAP_SWIZZLE_128B, 128)
                : make_map_3d(&mz, zt, zrows, 128, (uint64_t)n, (uint64_t)n_u, 256, (uint64_t)n * 256, 64, 128,
                              CU_TENSOR_MAP_SWIZZLE_128B, 1)))
     return PX_ERR_LAUNCH;
-  if (sizeof(Tz) == 2) {
-    if (!(ending ? make_map_3d(&mout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, z_out, 128, (uint64_t)n_u, (uint64_t)n, 256,
-                               (uint64_t)n_u * 256, 64, 1, CU_TENSOR_MAP_SWIZZLE_128B, 128)
-                 : make_map_3d(&mout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, z_out, 128, (uint64_t)n, (uint64_t)n_u, 256,
-                               (uint64_t)n * 256, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B, 1)))
+  if (kMode != 1) {
+    if (!(ending ? make_map_3d(&mout, zt, z_out, 128, (uint64_t)n_u, (uint64_t)n, 256, (uint64_t)n_u * 256, 64, 1,
+                               CU_TENSOR_MAP_SWIZZLE_128B, 128)
+                 : make_map_3d(&mout, zt, z_out, 128, (uint64_t)n, (uint64_t)n_u, 256, (uint64_t)n * 256, 64, 128,
+                               CU_TENSOR_MAP_SWIZZLE_128B, 1)))
       return PX_ERR_LAUNCH;
   } else {
     memset(&mout, 0, sizeof(mout));
@@ -320,12 +325,12 @@ static int32_t launch_triatt_out(const px_f16* o, const void* z_in, const px_f16
                    128, CU_TENSOR_MAP_SWIZZLE_128B, 1))
     return PX_ERR_LAUNCH;
   const size_t smem = AoLayout::total + 1024;
-  if (cudaFuncSetAttribute(triatt_out_tc_kernel<Tz>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+  if (cudaFuncSetAttribute(triatt_out_tc_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return PX_ERR_LAUNCH;
   const int64_t tiles_t = (n + 127) / 128, n_tiles = tiles_t * n_u;
   if (n_tiles > 0x7fffffff) return PX_ERR_UNSUPPORTED;
   const int grid = (int)(n_tiles < sm_count() ? n_tiles : sm_count());
-  triatt_out_tc_kernel<Tz><<<grid, kAoThreads, smem, st>>>(mz, mo, mout, (const Tz*)z_in, (Tz*)z_out, ln_w, ln_b,
+  triatt_out_tc_kernel<kMode><<<grid, kAoThreads, smem, st>>>(mz, mo, mout, z_in, z_out, ln_w, ln_b,
                                                            (const bf16*)w_g, (const bf16*)w_o, (int)n_u, (int)n, ending,
                                                            add_residual, eps, (int)tiles_t, (int)n_tiles);
   return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
@@ -344,11 +349,15 @@ extern "C" int32_t px_triatt_out(const px_f16* o, const void* z_in, const px_f16
   if (((uintptr_t)o | (uintptr_t)z_in | (uintptr_t)z_out | (uintptr_t)w_g | (uintptr_t)w_o | (uintptr_t)ln_w |
        (uintptr_t)ln_b) & 15)
     return PX_ERR_BAD_ARG;
+  if (z_dtype == PX_F16)   // z_in: standardised fp16 rows; z_out: the update in fp16 (no residual to add)
+    return add_residual ? PX_ERR_BAD_ARG
+                        : launch_triatt_out<2>(o, z_in, nullptr, z_out, ln_w, ln_b, w_g, w_o, n_u, n_t, ending, 0, eps,
+                                               (cudaStream_t)stream);
   if (z_dtype == PX_F32)
-    return launch_triatt_out<float>(o, z_in, zn, z_out, ln_w, ln_b, w_g, w_o, n_u, n_t, ending, add_residual, eps,
+    return launch_triatt_out<1>(o, z_in, zn, z_out, ln_w, ln_b, w_g, w_o, n_u, n_t, ending, add_residual, eps,
                                     (cudaStream_t)stream);
   if (z_dtype == PX_BF16)
-    return launch_triatt_out<bf16>(o, z_in, nullptr, z_out, ln_w, ln_b, w_g, w_o, n_u, n_t, ending, add_residual, eps,
+    return launch_triatt_out<0>(o, z_in, nullptr, z_out, ln_w, ln_b, w_g, w_o, n_u, n_t, ending, add_residual, eps,
                                    (cudaStream_t)stream);
   return PX_ERR_UNSUPPORTED;
 }

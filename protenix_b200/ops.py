@@ -55,7 +55,7 @@ F16 = torch.float16
 
 def _zfmt(z: torch.Tensor) -> torch.dtype:
     """Format of the weights that multiply rows of z: bf16 rows are multiplied as stored, fp32 rows as fp16."""
-    return torch.float16 if z.dtype == torch.float32 else torch.bfloat16
+    return torch.bfloat16 if z.dtype == torch.bfloat16 else torch.float16
 
 
 def _w(w: torch.Tensor, fmt: torch.dtype, shape: Tuple[int, ...], name: str) -> torch.Tensor:
@@ -217,11 +217,23 @@ def standardise_rows(z: torch.Tensor, eps: float = 1e-5, out: Optional[torch.Ten
     return out
 
 
+def add_update_rows(z: torch.Tensor, upd: torch.Tensor) -> torch.Tensor:
+    """z += upd in place for an fp32 tensor [..., 128] and an fp16 update of the same shape."""
+    _need_cuda(z, "z")
+    _need_cuda(upd, "upd")
+    if z.dtype != torch.float32 or upd.dtype != torch.float16 or z.shape != upd.shape or z.shape[-1] != C_Z:
+        raise RuntimeError("add_update_rows takes a float32 tensor [..., 128] and a float16 update of the same shape")
+    _launch("px_add_update_rows", _lib.load().px_add_update_rows, _ptr(z), _ptr(upd), z.numel() // C_Z, _stream(z))
+    return z
+
+
 def _rows_of(z: torch.Tensor, zn: Optional[torch.Tensor], eps: float) -> Tuple[torch.Tensor, int]:
     """The rows a stage multiplies and their dtype code: bf16 z itself, or the standardised fp16 copy of an fp32 z
-    (made here unless the caller already holds one)."""
+    (made here unless the caller already holds one; a float16 ``z`` is taken to be that copy)."""
     if z.dtype == torch.bfloat16:
         return z, PX_BF16
+    if z.dtype == torch.float16:
+        return z, PX_F16
     if z.dtype != torch.float32:
         raise RuntimeError(f"pair tensor must be float32 or bfloat16, got {z.dtype}")
     if zn is None:
@@ -461,15 +473,25 @@ def triatt_flash(q, k, v, bias_full: torch.Tensor, mb) -> torch.Tensor:
 
 
 def triatt_out(o: torch.Tensor, z: torch.Tensor, ln_w, ln_b, w_g, w_o, eps: float = 1e-5, ending: bool = False,
-               zn: Optional[torch.Tensor] = None) -> torch.Tensor:
+               zn: Optional[torch.Tensor] = None, update_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """z(u,t) += W_o(o[u][t] * sigmoid(W_g LN(z(u,t)))) in place; z is [n_u][n_t][128], or the column slab
-    [n_t][n_u][128] with ``ending``."""
+    [n_t][n_u][128] with ``ending``.  With a float16 ``z`` (the standardised copy of rows that live elsewhere) the
+    update alone is written, in fp16, to ``update_out`` (same layout as z), which is returned."""
     n_u, n_t = _slab(z)
     if ending:
         n_u, n_t = n_t, n_u
     _need_cuda(o, "o")
     if o.dtype != torch.float16 or tuple(o.shape) != (n_u, n_t, C_Z):
         raise RuntimeError("o must be float16 [n_u][n_t][128]")
+    if z.dtype == torch.float16:            # update only, from standardised rows
+        w_g, w_o = _w(w_g, F16, (C_Z, C_Z), "w_g"), _w(w_o, F16, (C_Z, C_Z), "w_o")
+        if update_out is None:
+            update_out = torch.empty_like(z)
+        elif update_out.dtype != torch.float16 or update_out.shape != z.shape or not update_out.is_contiguous():
+            raise RuntimeError("update_out must be a contiguous float16 tensor of z's shape")
+        _launch("px_triatt_out", _lib.load().px_triatt_out, _ptr(o), _ptr(z), None, _ptr(update_out), PX_F16, _ptr(ln_w),
+                _ptr(ln_b), _ptr(w_g), _ptr(w_o), n_u, n_t, int(ending), 0, float(eps), _stream(z))
+        return update_out
     w_g, w_o = _w(w_g, _zfmt(z), (C_Z, C_Z), "w_g"), _w(w_o, F16, (C_Z, C_Z), "w_o")
     zn = _rows_of(z, zn, eps)[0] if z.dtype == torch.float32 else None
     _launch("px_triatt_out", _lib.load().px_triatt_out, _ptr(o), _ptr(z), _ptr(zn), _ptr(z), _pair_dtype(z), _ptr(ln_w),

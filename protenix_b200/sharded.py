@@ -82,6 +82,9 @@ class CudaStages:
         return ops.triatt_out(o, z, f(mod.layer_norm.weight), f(mod.layer_norm.bias), m.linear_g.weight,
                               m.linear_o.weight, mod.layer_norm.eps, ending, zn=zn)
 
+    def add_update(self, z, upd):
+        return ops.add_update_rows(z, upd)
+
     def transition(self, mod, z, out=None):
         f = self._f
         return ops.transition_rows(z, f(mod.layernorm1.weight), f(mod.layernorm1.bias),
@@ -113,7 +116,7 @@ class PeerExchange:
         nl, cp, ldn = n // world, 128 // world, (n + 7) // 8 * 8
         ldm = (n + 127) // 128 * 128
         sizes = {"a": cp * n * ldn * 2, "b": cp * n * ldn * 2, "x": 128 * nl * ldn * 2,
-                 "zc": n * nl * 128 * z_itemsize, "zr": nl * n * 128 * z_itemsize, "bias": 4 * n * ldm * 4,
+                 "zc": n * nl * 128 * 2, "zr": nl * n * 128 * 2, "bias": 4 * n * ldm * 4,
                  "flags": 256}
         self.local: Dict[str, ops.PeerBuffer] = {k: ops.PeerBuffer(v, device) for k, v in sizes.items()}
         for k in ("a", "b", "flags"):   # pad columns [n, ld) are never written by an exchange and must read as zero
@@ -364,7 +367,8 @@ class ShardedPairformer:
         """Starting-node then ending-node attention.  The output stage of the first runs in row chunks whose rows leave
         for the column slabs of the other ranks as soon as they are final; the second works on the received column slab
         zc [N i][N/P j][c] (the kernels address it as element (u=j, t=i)) and sends the rows back.  Returns the
-        updated row slab: a view of this rank's receive buffer (the caller's z_loc is NOT written)."""
+        updated row slab: a view of this rank's receive buffer (bf16 z: the caller's z_loc is NOT written), or z_loc
+        itself with the returned update added (fp32 z)."""
         st, p, me = self.stages, self.world, self.rank
         nl, n, c = z_loc.shape
         zn = st.standardised(z_loc, start.layer_norm.eps)
@@ -375,20 +379,28 @@ class ShardedPairformer:
         bias_full = px.local["bias"].tensor((h, p * nl, ldm), torch.float32)
         o = st.triatt_flash(q, k, v, bias_full, mb)
         del q, k, v
+        # 16-bit tensors cross NVLink in both directions: the bf16 rows themselves, or, for an fp32 z, the standardised
+        # fp16 copy on the way out and the update alone on the way back (the rows' owner adds it to its fp32 rows)
+        fp32 = z_loc.dtype == torch.float32
         for r0, r1 in self._row_chunks(nl):
             st.triatt_out(start, o[r0:r1], z_loc[r0:r1], zn=None if zn is None else zn[r0:r1])
-            px.send(lambda r0=r0, r1=r1: self._peer_to_columns(px, z_loc[r0:r1], nl, r0), z_loc)
+            rows = st.standardised(z_loc[r0:r1], end.layer_norm.eps) if fp32 else z_loc[r0:r1]
+            px.send(lambda rows=rows, r0=r0: self._peer_to_columns(px, rows, nl, r0), rows, z_loc)
+            del rows
         px.join()
         del o, zn
-        zc = px.local["zc"].tensor((n, nl, c), z_loc.dtype)
-        zn = st.standardised(zc, end.layer_norm.eps)
+        zc = px.local["zc"].tensor((n, nl, c), torch.float16 if fp32 else z_loc.dtype)
+        zn = None if fp32 else st.standardised(zc, end.layer_norm.eps)      # (fp32: zc already is the standardised copy)
         q, k, v, bias_loc, mb = st.triatt_in_proj(end, zc, mask_cols, True, zn=zn)
         px.send(lambda: self._peer_gather_bias(px, bias_loc), bias_loc)
         px.join()
-        st.triatt_out(end, st.triatt_flash(q, k, v, bias_full, mb), zc, True, zn=zn)
-        px.send(lambda: self._peer_from_columns(px, zc))
+        back = st.triatt_out(end, st.triatt_flash(q, k, v, bias_full, mb), zc, True, zn=zn)   # fp32: the update, fp16
+        px.send(lambda: self._peer_from_columns(px, back), back)
         px.join()
-        return px.local["zr"].tensor((nl, n, c), z_loc.dtype)
+        zr = px.local["zr"].tensor((nl, n, c), torch.float16 if fp32 else z_loc.dtype)
+        if fp32:
+            return st.add_update(z_loc, zr)
+        return zr
 
     # ---- sub-modules ----------------------------------------------------------------------------
     def _tri_mul(self, mod, z_loc, mask_loc, incoming: bool) -> None:
@@ -461,7 +473,7 @@ class ShardedPairformer:
                 self._tri_mul_peer(px, blk.tri_mul_out, z_loc, mask_loc, incoming=False)
                 self._tri_mul_peer(px, blk.tri_mul_in, z_loc, mask_loc, incoming=True)
                 zr = self._tri_att_pair_peer(px, blk.tri_att_start, blk.tri_att_end, z_loc, mask_loc, mask_cols)
-                self.stages.transition(blk.pair_transition, zr, out=z_loc)    # reads the received rows, writes z_loc
+                self.stages.transition(blk.pair_transition, zr, out=z_loc)    # reads the received rows (or z_loc itself)
             else:
                 self._tri_mul(blk.tri_mul_out, z_loc, mask_loc, incoming=False)
                 self._tri_mul(blk.tri_mul_in, z_loc, mask_loc, incoming=True)

@@ -144,7 +144,7 @@ def test_sharded_path_with_one_rank_equals_module():
         dist.destroy_process_group()
 
 
-def _nccl_worker(rank, world, port, n, q, n_blocks=2, pad=None):
+def _nccl_worker(rank, world, port, n, q, n_blocks=2, pad=None, zdtype="bf16"):
     import sys
 
     here = os.path.dirname(os.path.abspath(__file__))
@@ -162,7 +162,7 @@ def _nccl_worker(rank, world, port, n, q, n_blocks=2, pad=None):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
         g = torch.Generator().manual_seed(4)
-        z = torch.randn(n, n, 128, generator=g).to(torch.bfloat16).to(dev)
+        z = torch.randn(n, n, 128, generator=g).to(torch.bfloat16 if zdtype == "bf16" else torch.float32).to(dev)
         s = torch.randn(n, 384, generator=g).to(dev)
         mask = (random_mask(n, 9) if pad is None else padding_mask(n, pad)).to(dev)
         stack = build_module("stack", dict(n_blocks=n_blocks, c_s=384, wseed=5)).to(dev)
@@ -205,24 +205,26 @@ def _run_ranks(world, n, **kw):
     return q.get(timeout=10)
 
 
-@pytest.mark.parametrize("world,n", [(2, 136), (2, 144), (4, 192), (8, 256)])
-def test_sharded_over_nccl_equals_single_gpu(world, n):
-    """Gathered output of the row-sharded stack on `world` GPUs against the one-GPU stack.  N/P = 68 goes through the
-    all_to_all transport (the peer copies need N/P to be a multiple of 8), the other cases through the peer copies."""
+@pytest.mark.parametrize("world,n,zdtype", [(2, 136, "bf16"), (2, 144, "bf16"), (2, 144, "fp32"), (2, 136, "fp32"),
+                                            (4, 192, "bf16"), (4, 192, "fp32"), (8, 256, "bf16"), (8, 256, "fp32")])
+def test_sharded_over_nccl_equals_single_gpu(world, n, zdtype):
+    """Gathered output of the row-sharded stack on `world` GPUs against the one-GPU stack, for both storage types of z.
+    N/P = 68 goes through the all_to_all transport (the peer copies need N/P to be a multiple of 8), the other cases
+    through the peer copies."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    ez, es, same, flags, finite = _run_ranks(world, n)
+    ez, es, same, flags, finite = _run_ranks(world, n, zdtype=zdtype)
     # same kernels, same per-element arithmetic: only the reduction-free re-layouts differ
     assert flags == 0 and finite
     assert ez < 1e-3 and es < 1e-3, (ez, es, same)
 
 
-@pytest.mark.parametrize("world", [2, 4, 8])
-def test_sharded_block_n1536_equals_single_gpu(world):
-    """One block at N=1536 (bf16 z, 37 trailing tokens masked) row-sharded over `world` GPUs against the same block
-    on one GPU: the size the multi-GPU benchmark runs."""
+@pytest.mark.parametrize("world,zdtype", [(2, "fp32"), (2, "bf16"), (4, "fp32"), (8, "fp32")])
+def test_sharded_block_n1536_equals_single_gpu(world, zdtype):
+    """One block at N=1536 (37 trailing tokens masked) row-sharded over `world` GPUs against the same block on one GPU:
+    the size the multi-GPU benchmark runs."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    ez, es, same, flags, finite = _run_ranks(world, 1536, n_blocks=1, pad=37)
+    ez, es, same, flags, finite = _run_ranks(world, 1536, n_blocks=1, pad=37, zdtype=zdtype)
     assert flags == 0 and finite
     assert ez < 1e-3 and es < 1e-3, (ez, es, same)
