@@ -231,16 +231,17 @@ def kernel_algo(n: int, zbytes: int) -> dict:
 
 
 # DRAM bytes per pair element (dram__bytes_read.sum + dram__bytes_write.sum of one launch / N^2) from the ncu
-# captures at N = 768 summarised under profiles/ (<kernel>_N768.md).  For these kernels traffic grows with
-# N^2 (operands of the N^3 kernels are re-read from L2, not DRAM), so a launch at another N is scaled by N^2.
+# captures at N = 768 with an fp32 z summarised under profiles/ (<kernel>_N768.md).  For these kernels traffic grows
+# with N^2 (operands of the N^3 kernels are re-read from L2, not DRAM), so a launch at another N is scaled by N^2.
 NCU_TRAFFIC_PER_PAIR = {
     "px_triatt_flash": 597.9e6 / 768 ** 2,
-    "px_transition": 248.2e6 / 768 ** 2,
-    "px_trimul_contract": 417.1e6 / 768 ** 2,
-    "px_trimul_in_proj": 399.2e6 / 768 ** 2,
-    "px_trimul_out": 410.9e6 / 768 ** 2,
-    "px_triatt_in_proj": 561.6e6 / 768 ** 2,
-    "px_triatt_out": 411.2e6 / 768 ** 2,
+    "px_transition": 551.5e6 / 768 ** 2,
+    "px_trimul_contract": 418.4e6 / 768 ** 2,
+    "px_trimul_in_proj": 399.4e6 / 768 ** 2,
+    "px_trimul_out": 892.1e6 / 768 ** 2,
+    "px_triatt_in_proj": 561.7e6 / 768 ** 2,
+    "px_triatt_out": 864.6e6 / 768 ** 2,
+    "px_standardise_rows": 399.0e6 / 768 ** 2,
 }
 
 
@@ -291,7 +292,48 @@ def run_micro(args) -> None:
             peak = pk["tflops"] if bound == "tensor" else pk["hbm_gbs"]
             out[f"{name}/{k}"] = {"ms": round(ms, 4), "bound": bound, "achieved": round(ach, 1),
                                   "unit": "TFLOP/s" if bound == "tensor" else "GB/s", "frac": round(ach / peak, 4)}
+    # The LayerNorm op on a z-sized tensor [N^2, 128], beside the reference's own extension (fast_layer_norm_cuda_v2,
+    # built for sm_100 from the reference's sources by oracle/build_ref_layer_norm.py; timed when that build is
+    # present) and beside torch.nn.functional.layer_norm on the same tensor.
+    import torch.nn.functional as F
+
+    ref_ln = None
+    try:
+        from oracle.build_ref_layer_norm import load_if_built
+
+        ref_ln = load_if_built()
+    except Exception as e:  # the build is optional: say why it is absent
+        ref_ln = None
+        print(f"reference LayerNorm extension not loaded: {type(e).__name__}: {e}", file=sys.stderr)
+    ln = {"reference_extension": "oracle/_ref/fast_layer_norm_cuda_v2.so" if ref_ln is not None else "absent"}
+    for dt in (torch.bfloat16, torch.float32):
+        x = torch.randn(n * n, 128, device="cuda").to(dt)
+        w = (1 + 0.1 * torch.randn(128, device="cuda")).to(dt)
+        b = (0.1 * torch.randn(128, device="cuda")).to(dt)
+        res = {}
+        cases = [("px_layer_norm_fwd", lambda: ops.layer_norm(x, w, b, 1e-5)),
+                 ("torch_layer_norm", lambda: F.layer_norm(x, (128,), w, b, 1e-5))]
+        if ref_ln is not None:
+            cases.append(("reference_fast_layer_norm_cuda_v2", lambda: ref_ln.forward_with_both_affine(x, (128,), w, b, 1e-5)))
+            y_ref = ref_ln.forward_with_both_affine(x, (128,), w, b, 1e-5)[0]
+            y_px = ops.layer_norm(x, w, b, 1e-5)
+            res["max_abs_diff_vs_reference"] = float((y_px.float() - y_ref.float()).abs().max())
+        for nm, fn in cases:
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            gbs = 2.0 * x.numel() * x.element_size() / (ms * 1e-3) / 1e9
+            res[nm] = {"ms": round(ms, 4), "GB/s": round(gbs, 1), "frac": round(gbs / pk["hbm_gbs"], 4)}
+        ln[str(dt).replace("torch.", "")] = res
     print(json.dumps({"micro": True, "n_token": n, "z_storage": args.z_dtype, "peak_source": pk["source"],
+                      "layer_norm_op_rows128": ln,
                       "steps": args.steps, "warmup": args.warmup, "kernels": out}), flush=True)
 
 

@@ -3,6 +3,9 @@
 // HBM-bound: 2 * cols * sizeof(T) algorithmic bytes per row.  One warp owns a row; the row is
 // held in registers between the statistics and the write-back (cols <= 32*VEC*kMaxIt), so x is
 // read from HBM exactly once.  VEC is the widest vector (up to 16 bytes) that divides cols.
+// Rows that fit 4..32 lanes x 16 bytes (the pair representation's 128 channels in any of the three types, the
+// template embedder's 64) take ln_fwd_rows16: every lane moves 16 bytes, a warp works on 32/LANES rows at once and
+// keeps 4 KB of such groups in flight.
 #include <cuda_fp16.h>
 
 #include "px_common.cuh"
@@ -103,6 +106,89 @@ __global__ void __launch_bounds__(256) ln_fwd_cached(const T* __restrict__ x, co
   }
 }
 
+// Rows of exactly LANES x 16 bytes, LANES a power of two <= 32: a group of LANES lanes owns a row.
+template <typename T, int LANES>
+__global__ void __launch_bounds__(256) ln_fwd_rows16(const T* __restrict__ x, const T* __restrict__ gamma,
+                                                     const T* __restrict__ beta, T* __restrict__ y,
+                                                     float* __restrict__ mean_out, float* __restrict__ invvar_out,
+                                                     int64_t rows, float eps) {
+  constexpr int VEC = 16 / (int)sizeof(T), kCols = VEC * LANES, kR = 32 / LANES;
+  constexpr int kB = LANES >= 32 ? 4 : 8;               // row groups in flight: 4 KB of loads per warp either way
+  const int lane = threadIdx.x & 31, sub = lane / LANES, li = lane % LANES;
+  const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  float g[VEC], b[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) {
+    g[e] = gamma ? Cvt<T>::to_f(gamma[li * VEC + e]) : 1.f;
+    b[e] = beta ? Cvt<T>::to_f(beta[li * VEC + e]) : 0.f;
+  }
+  for (int64_t r0 = warp0 * (kB * kR); r0 < rows; r0 += nwarps * (kB * kR)) {
+    float v[kB][VEC], acc[kB];
+#pragma unroll
+    for (int j = 0; j < kB; ++j) {
+      const int64_t row = r0 + j * kR + sub;
+      Vec<T, VEC> t;
+      if (row < rows) {                                  // one 16-byte streaming load per lane
+        const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(x + row * kCols) + li);
+        t = *reinterpret_cast<const Vec<T, VEC>*>(&raw);
+      }
+      acc[j] = 0.f;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        v[j][e] = row < rows ? Cvt<T>::to_f(t.v[e]) : 0.f;
+        acc[j] += v[j][e];
+      }
+    }
+#pragma unroll
+    for (int o = LANES / 2; o > 0; o >>= 1)
+#pragma unroll
+      for (int j = 0; j < kB; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+    float mean[kB];
+#pragma unroll
+    for (int j = 0; j < kB; ++j) {
+      mean[j] = acc[j] * (1.0f / kCols);
+      acc[j] = 0.f;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        v[j][e] -= mean[j];
+        acc[j] = fmaf(v[j][e], v[j][e], acc[j]);
+      }
+    }
+#pragma unroll
+    for (int o = LANES / 2; o > 0; o >>= 1)
+#pragma unroll
+      for (int j = 0; j < kB; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+#pragma unroll
+    for (int j = 0; j < kB; ++j) {
+      const int64_t row = r0 + j * kR + sub;
+      if (row < rows) {
+        const float rstd = rsqrtf(acc[j] * (1.0f / kCols) + eps);
+        if (li == 0) {
+          if (mean_out) mean_out[row] = mean[j];
+          if (invvar_out) invvar_out[row] = rstd;
+        }
+        Vec<T, VEC> o;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o.v[e] = Cvt<T>::from_f(fmaf(v[j][e] * rstd, g[e], b[e]));
+        reinterpret_cast<Vec<T, VEC>*>(y + row * kCols)[li] = o;
+      }
+    }
+  }
+}
+
+template <typename T, int LANES>
+static cudaError_t launch_rows16(const void* x, const void* g, const void* b, void* y, float* mean, float* invvar,
+                                 int64_t rows, float eps, cudaStream_t st) {
+  const int64_t rows_per_cta = 8 * (LANES >= 32 ? 4 : 8) * (32 / LANES);
+  int64_t ctas = (rows + rows_per_cta - 1) / rows_per_cta;
+  const int64_t cap = 148 * 8;                           // eight CTAs of 256 threads resident per SM
+  if (ctas > cap) ctas = cap;
+  ln_fwd_rows16<T, LANES><<<(unsigned)ctas, 256, 0, st>>>((const T*)x, (const T*)g, (const T*)b, (T*)y, mean, invvar, rows,
+                                                          eps);
+  return cudaGetLastError();
+}
+
 // Wide rows: three passes over the row (the second and third hit L1/L2).
 template <typename T>
 __global__ void __launch_bounds__(256) ln_fwd_wide(const T* __restrict__ x, const T* __restrict__ gamma,
@@ -159,6 +245,15 @@ static cudaError_t dispatch(const void* x, const void* g, const void* b, void* y
     return cols % vec == 0 && cols <= 32 * vec * kMaxIt && !((uintptr_t)x & m) && !((uintptr_t)y & m) &&
            !((uintptr_t)g & m) && !((uintptr_t)b & m);
   };
+  if (cols % kMaxVec == 0 && aligned(kMaxVec)) {       // rows of 4..32 lanes x 16 bytes
+    switch (cols / kMaxVec) {
+      case 32: return launch_rows16<T, 32>(x, g, b, y, mean, invvar, rows, eps, st);
+      case 16: return launch_rows16<T, 16>(x, g, b, y, mean, invvar, rows, eps, st);
+      case 8: return launch_rows16<T, 8>(x, g, b, y, mean, invvar, rows, eps, st);
+      case 4: return launch_rows16<T, 4>(x, g, b, y, mean, invvar, rows, eps, st);
+      default: break;
+    }
+  }
   if (kMaxVec >= 8 && aligned(8) && cols >= 32 * 8)
     return launch_cached<T, (kMaxVec >= 8 ? 8 : 1)>(x, g, b, y, mean, invvar, rows, cols, eps, st);
   if (aligned(4)) return launch_cached<T, 4>(x, g, b, y, mean, invvar, rows, cols, eps, st);
