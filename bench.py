@@ -184,8 +184,10 @@ def run_reference(args) -> None:
     threads = os.cpu_count() or 1
     times = []
     cb = None
+    # every step is a bounded row-slab sample; the samples are sized so that the whole run stays near two minutes
+    per_step = max(1.0, min(10.0, 100.0 / max(1, args.warmup + args.steps)))
     for i in range(args.warmup + args.steps):
-        cb = cpu_baseline(args.n_token, args.pad, args.cpu_rows, threads)
+        cb = cpu_baseline(args.n_token, args.pad, args.cpu_rows, threads, target_s=per_step)
         if i >= args.warmup:
             times.append(cb["sec_per_block_est"])
     sec_block = sum(times) / len(times)

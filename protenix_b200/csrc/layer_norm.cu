@@ -113,8 +113,7 @@ __global__ void __launch_bounds__(256) ln_fwd_rows16(const T* __restrict__ x, co
                                                      float* __restrict__ mean_out, float* __restrict__ invvar_out,
                                                      int64_t rows, float eps) {
   constexpr int VEC = 16 / (int)sizeof(T), kCols = VEC * LANES, kR = 32 / LANES;
-  constexpr int kB = sizeof(T) == 2 ? 2 : 4;             // row groups in flight per warp (registers: 8 values per lane
-                                                         // and group for the 16-bit types, 4 for fp32)
+  constexpr int kB = 4;                                  // row groups in flight per warp (2 and 8 measured slower)
   const int lane = threadIdx.x & 31, sub = lane / LANES, li = lane % LANES;
   const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
@@ -181,7 +180,7 @@ __global__ void __launch_bounds__(256) ln_fwd_rows16(const T* __restrict__ x, co
 template <typename T, int LANES>
 static cudaError_t launch_rows16(const void* x, const void* g, const void* b, void* y, float* mean, float* invvar,
                                  int64_t rows, float eps, cudaStream_t st) {
-  const int64_t rows_per_cta = 8 * (sizeof(T) == 2 ? 2 : 4) * (32 / LANES);
+  const int64_t rows_per_cta = 8 * 4 * (32 / LANES);
   int64_t ctas = (rows + rows_per_cta - 1) / rows_per_cta;
   const int64_t cap = 148 * 8;                           // eight CTAs of 256 threads resident per SM
   if (ctas > cap) ctas = cap;
