@@ -28,10 +28,11 @@ struct PbLayout {
   static constexpr int wx = w + 2 * kPbWPanel;                  // correction panel [16][16 k]
   static constexpr int a = wx + 1024;                           // row-tile ring
   static constexpr int ax = a + kTileStages * kTileBytes;
-  static constexpr int scale = ax + kTileStages * kTileExtra;   // rstd per row and slot
+  static constexpr int scale = ax + kTileSlots * kTileExtra;    // rstd per row and slot
   static constexpr int bars = scale + kTileSlots * 128 * 4;
   static constexpr int total = bars + (int)sizeof(PbBars);
 };
+static_assert(PbLayout::total + 1024 <= 232448, "shared memory budget");
 static_assert(PbLayout::a % 1024 == 0, "tile ring must keep the swizzle alignment");
 
 static __device__ float g_zero_beta[128];      // stands in for a LayerNorm without bias

@@ -191,7 +191,6 @@ constexpr int kTileSlots = kTileStages + 1;    // per-row scale slots: read by t
 constexpr int kTilePanel = 144 * 128;          // [128 rows + 16 rows of ones][64 k] bf16
 constexpr int kTileBytes = 2 * kTilePanel;
 constexpr int kTileExtra = 128 * 32;           // [128 rows][16 k] correction panel
-constexpr int kTileRing = kTileStages * (kTileBytes + kTileExtra);
 constexpr uint32_t kGramCols = 144;
 
 struct TileBars {
@@ -201,7 +200,7 @@ struct TileBars {
 };
 struct TileCtx {
   unsigned char* tiles;     // kTileStages x kTileBytes
-  unsigned char* extras;    // kTileStages x kTileExtra
+  unsigned char* extras;    // kTileSlots x kTileExtra (the correction step of a tile runs after its stage is freed)
   TileBars* bars;
   int first_tile, tile_step, n_tiles, tiles_t, n_u, n_t, swap;
 };
@@ -292,7 +291,7 @@ __device__ __forceinline__ void tile_stats_loop(const TileCtx& c, float eps, uin
       std = sqrtf(var + eps);
     }
     // rstd * (W'x - mean * s + std * t): the row side of the correction step holds (-mean, std)
-    write_correction_row(c.extras + s * kTileExtra, r, -mean, std, false);
+    write_correction_row(c.extras + (k % kTileSlots) * kTileExtra, r, -mean, std, false);
     per_row(k, u, t, r, rstd);
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     __syncwarp();
@@ -319,11 +318,15 @@ __device__ __forceinline__ void tile_product_loop(const TileCtx& c, uint32_t d_t
     for (int ks = 0; ks < 8; ++ks)
       umma_bf16(d_tmem, umma_desc_sw128(a_addr + (ks >> 2) * kTilePanel) + 2 * (ks & 3),
                 umma_desc_sw128(w_addr + (ks >> 2) * w_panel) + 2 * (ks & 3), idesc, ks ? 1u : 0u);
+    // This thread's reads of the stage end here: the producer may refill it while the statistics of the tile are
+    // still on their way.  The correction step reads the tile's slot of the correction ring instead, which has one
+    // slot more than the tile ring: slot k % 3 is rewritten for tile k + 3, whose stage is handed out only after
+    // this thread's products of tile k + 1, issued after the correction step below, are complete.
+    umma_commit(&c.bars->a_empty[s]);
     if (!mbar_wait(&c.bars->a_ready[s], n & 1, 4u)) break;   // the correction step needs the statistics
     tc_fence_after();
-    umma_bf16(d_tmem, umma_desc_sw32(smem_u32(c.extras + s * kTileExtra)), wx_desc, idesc_corr, 1u);
+    umma_bf16(d_tmem, umma_desc_sw32(smem_u32(c.extras + (k % kTileSlots) * kTileExtra)), wx_desc, idesc_corr, 1u);
     umma_commit(acc_full);
-    umma_commit(&c.bars->a_empty[s]);                        // this thread's share of the reads of the stage
   }
 }
 

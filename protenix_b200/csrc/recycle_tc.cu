@@ -33,11 +33,12 @@ struct RcLayout {
   static constexpr int wx = w + kOperandBytes;                  // correction panel [128][16 k]
   static constexpr int a = wx + 128 * 32;                       // row-tile ring
   static constexpr int ax = a + kTileStages * kTileBytes;
-  static constexpr int res = ax + kTileStages * kTileExtra;     // z_init tiles, then the output tiles, in place
+  static constexpr int res = ax + kTileSlots * kTileExtra;      // z_init tiles, then the output tiles, in place
   static constexpr int scale = res + kTileStages * kOperandBytes;  // rstd per row and slot
   static constexpr int bars = scale + kTileSlots * 128 * 4;
   static constexpr int total = bars + (int)sizeof(RcBars);
 };
+static_assert(RcLayout::total + 1024 <= 232448, "shared memory budget");
 static_assert(RcLayout::a % 1024 == 0 && RcLayout::res % 1024 == 0, "tiles must keep the swizzle alignment");
 
 static __device__ float g_rc_zero_beta[128];   // stands in for a LayerNorm without bias
@@ -131,7 +132,11 @@ recycle_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_consta
     bool ok = true;
     for (int tile = ctx.first_tile; tile < n_tiles && ok; tile += ctx.tile_step, ++k) {
       const int s = k % kTileStages, n = k / kTileStages;
-      const long long t = (long long)tile * 128 + row;
+      // fp32 rows: this warp's 32 rows and their z_init values for the first 32 channels, requested before the wait
+      const long long first_row = (long long)tile * 128 + 32 * qw;
+      const int valid = rows - first_row < 32 ? (rows - first_row > 0 ? (int)(rows - first_row) : 0) : 32;
+      RowsOutReq rq;
+      if (!kTma) rows_out_request(rq, reinterpret_cast<const float*>(z_init), first_row, 1, valid, 64 * half, lane, true);
       ok = mbar_wait(&bars.acc_full, k & 1, 32u);
       if (kTma) ok = ok && mbar_wait(&bars.res_full[s], n & 1, 33u);
       ok = named_barrier_all(1, 256, ok);                  // all eight warps go on, or none
@@ -164,18 +169,16 @@ recycle_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_consta
             }
             *reinterpret_cast<uint4*>(piece) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
           }
-        } else if (t < rows) {
-          const size_t off = (size_t)t * kC + 64 * half + 32 * hh;
-          const float* init = reinterpret_cast<const float*>(z_init);
-          float* dst = reinterpret_cast<float*>(out);
+        } else {
+          // fp32 rows: coalesced through a warp-private 4 KB staging area in the z_init ring, which this mode does
+          // not otherwise use (z_init is read straight from global memory, in the arrangement of the stores)
+          float v[32];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float4 r4 = load4(init + off + 4 * j);
-            store2(dst + off + 4 * j, fmaf(rstd, __uint_as_float(acc[4 * j]), r4.x),
-                   fmaf(rstd, __uint_as_float(acc[4 * j + 1]), r4.y));
-            store2(dst + off + 4 * j + 2, fmaf(rstd, __uint_as_float(acc[4 * j + 2]), r4.z),
-                   fmaf(rstd, __uint_as_float(acc[4 * j + 3]), r4.w));
-          }
+          for (int e = 0; e < 32; ++e) v[e] = rstd * __uint_as_float(acc[e]);
+          rows_out_store(sm + RcLayout::res + warp * 4096, v, rq, reinterpret_cast<float*>(out), first_row, 1, valid,
+                         64 * half + 32 * hh, lane);
+          if (hh == 0)
+            rows_out_request(rq, reinterpret_cast<const float*>(z_init), first_row, 1, valid, 64 * half + 32, lane, true);
         }
       }
       if (kTma) {

@@ -41,11 +41,12 @@ struct AiLayout {
   static constexpr int wx1 = wx0 + 128 * 32;
   static constexpr int a = wx1 + 128 * 32;                      // row-tile ring
   static constexpr int ax = a + kTileStages * kTileBytes;
-  static constexpr int out = ax + kTileStages * kTileExtra;     // v staging
+  static constexpr int out = ax + kTileSlots * kTileExtra;      // v staging
   static constexpr int scale = out + kAiStageOut;               // float2 (rstd, rstd or 0 beyond n) per row and slot
   static constexpr int bars = scale + kTileSlots * 128 * 8;
   static constexpr int total = bars + (int)sizeof(AiBars);
 };
+static_assert(AiLayout::total + 1024 <= 232448, "shared memory budget");
 static_assert(AiLayout::a % 1024 == 0, "tile ring must keep the swizzle alignment");
 
 // kF16: the rows are the standardised fp16 copy of an fp32 pair tensor (fp16 weights); otherwise bf16 rows of z.

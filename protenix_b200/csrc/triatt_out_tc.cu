@@ -45,11 +45,12 @@ struct AoLayout {
   static constexpr int wx = wo + kOperandBytes;                 // gate correction panel
   static constexpr int a = wx + 128 * 32;                       // z tiles
   static constexpr int ax = a + kTileStages * kTileBytes;       // z correction panels
-  static constexpr int o = ax + kTileStages * kTileExtra;       // o tiles (later the output rows)
+  static constexpr int o = ax + kTileSlots * kTileExtra;        // o tiles (later the output rows)
   static constexpr int scale = o + kTileStages * kOperandBytes; // rstd per row and slot
   static constexpr int bars = scale + kTileSlots * 128 * 4;
   static constexpr int total = bars + (int)sizeof(AoBars);
 };
+static_assert(AoLayout::total + 1024 <= 232448, "shared memory budget");
 static_assert(AoLayout::a % 1024 == 0 && AoLayout::o % 1024 == 0, "tiles must keep the swizzle alignment");
 
 template <int kMode>

@@ -44,11 +44,12 @@ struct TiLayout {
   static constexpr int wx = w + 2 * kOperandBytes;              // per output: correction panel
   static constexpr int a = wx + 2 * kTiWExtra;                  // row-tile ring
   static constexpr int ax = a + kTileStages * kTileBytes;       // row-tile correction panels
-  static constexpr int out = ax + kTileStages * kTileExtra;     // output staging, one buffer per output
+  static constexpr int out = ax + kTileSlots * kTileExtra;      // output staging, one buffer per output
   static constexpr int scale = out + 2 * kTiStageOut;           // float2 (rstd, rstd*mask/2) per row and slot
   static constexpr int bars = scale + kTileSlots * 128 * 8;
   static constexpr int total = bars + (int)sizeof(TiBars);
 };
+static_assert(TiLayout::total + 1024 <= 232448, "shared memory budget");
 
 // kF16: the rows are the standardised fp16 copy of an fp32 pair tensor (fp16 weights); otherwise bf16 rows of z.
 template <bool kF16>

@@ -227,6 +227,17 @@ def add_update_rows(z: torch.Tensor, upd: torch.Tensor) -> torch.Tensor:
     return z
 
 
+def _zn_arg(z: torch.Tensor, zn: Optional[torch.Tensor]) -> Optional[int]:
+    """Raw pointer of an optional standardised copy of z that the caller hands in."""
+    if zn is None:
+        return None
+    if z.dtype != torch.float32:
+        raise RuntimeError("zn goes with a float32 pair tensor")
+    if zn.dtype != torch.float16 or zn.shape != z.shape or zn.device != z.device or not zn.is_contiguous():
+        raise RuntimeError("zn must be a contiguous float16 tensor of the shape of z")
+    return zn.data_ptr()
+
+
 def _rows_of(z: torch.Tensor, zn: Optional[torch.Tensor], eps: float) -> Tuple[torch.Tensor, int]:
     """The rows a stage multiplies and their dtype code: bf16 z itself, or the standardised fp16 copy of an fp32 z
     (made here unless the caller already holds one; a float16 ``z`` is taken to be that copy)."""
@@ -245,7 +256,9 @@ def _rows_of(z: torch.Tensor, zn: Optional[torch.Tensor], eps: float) -> Tuple[t
 
 def triangle_multiplication(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optional[torch.Tensor],
                             ln_in_w, ln_in_b, ln_out_w, ln_out_b, w_ap, w_ag, w_bp, w_bg, w_z, w_g,
-                            incoming: bool, add_residual: bool, eps: float = 1e-5) -> torch.Tensor:
+                            incoming: bool, add_residual: bool, eps: float = 1e-5,
+                            zn: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """zn: the standardised fp16 copy of an fp32 z_in when the caller already has it (same eps)."""
     n = _check_pair(z_in, "z_in")
     if _check_pair(z_out, "z_out") != n or z_out.dtype != z_in.dtype:
         raise RuntimeError("z_out must match z_in in shape and dtype")
@@ -260,13 +273,15 @@ def triangle_multiplication(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optio
     ws = workspace(z_in.device, lib.px_trimul_workspace_bytes(n))
     ldn = lib.px_ld(n)
     per = C_Z * n * ldn * 2                      # bytes of one channel-major [128][N][ld] fp16 tensor
-    a, b, x, zn = ws.data_ptr(), ws.data_ptr() + per, ws.data_ptr() + 2 * per, None
+    a, b, x = ws.data_ptr(), ws.data_ptr() + per, ws.data_ptr() + 2 * per
     dt, st, eps = _pair_dtype(z_in), _stream(z_in), float(eps)
     rows, rows_dt = _ptr(z_in), dt
+    zn = _zn_arg(z_in, zn)
     if dt == PX_F32:            # the projection and the output stage normalise the same z: one standardised copy
-        zn = rows = ws.data_ptr() + 3 * per
-        rows_dt = PX_F16
-        _launch("px_standardise_rows", lib.px_standardise_rows, _ptr(z_in), zn, n * n, eps, st)
+        if zn is None:
+            zn = ws.data_ptr() + 3 * per
+            _launch("px_standardise_rows", lib.px_standardise_rows, _ptr(z_in), zn, n * n, eps, st)
+        rows, rows_dt = zn, PX_F16
     _launch("px_trimul_in_proj", lib.px_trimul_in_proj, rows, rows_dt, _ptr(mask), _ptr(ln_in_w), _ptr(ln_in_b),
             _ptr(w_ap), _ptr(w_ag), _ptr(w_bp), _ptr(w_bg), a, b, n, n, ldn, int(incoming), eps, st)
     _launch("px_trimul_contract", lib.px_trimul_contract, a, b, x, C_Z, n, ldn, st)
@@ -277,7 +292,8 @@ def triangle_multiplication(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optio
 
 def triangle_attention(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optional[torch.Tensor], ln_w, ln_b, w_bias,
                        w_q, w_k, w_v, w_g, w_o, ending: bool, add_residual: bool, eps: float = 1e-5,
-                       inf: float = 1e9) -> torch.Tensor:
+                       inf: float = 1e9, zn: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """zn: as for triangle_multiplication."""
     n = _check_pair(z_in, "z_in")
     if _check_pair(z_out, "z_out") != n or z_out.dtype != z_in.dtype:
         raise RuntimeError("z_out must match z_in in shape and dtype")
@@ -299,11 +315,13 @@ def triangle_attention(z_in: torch.Tensor, z_out: torch.Tensor, mask: Optional[t
     mbias = bias + al(N_HEAD_PAIR * n * ldn * 4)
     flags = mbias + al(n * ldn * 4)
     dt, st, eps = _pair_dtype(z_in), _stream(z_in), float(eps)
-    rows, rows_dt, zn = _ptr(z_in), dt, None
+    rows, rows_dt = _ptr(z_in), dt
+    zn = _zn_arg(z_in, zn)
     if dt == PX_F32:            # the projection and the output stage normalise the same z: one standardised copy
-        zn = rows = flags + al(lib.px_triatt_flash_scratch_bytes(n, n))
-        rows_dt = PX_F16
-        _launch("px_standardise_rows", lib.px_standardise_rows, _ptr(z_in), zn, n * n, eps, st)
+        if zn is None:
+            zn = flags + al(lib.px_triatt_flash_scratch_bytes(n, n))
+            _launch("px_standardise_rows", lib.px_standardise_rows, _ptr(z_in), zn, n * n, eps, st)
+        rows, rows_dt = zn, PX_F16
     _launch("px_triatt_in_proj", lib.px_triatt_in_proj, rows, rows_dt, _ptr(mask), _ptr(ln_w), _ptr(ln_b),
             _ptr(w_q), _ptr(w_k), _ptr(w_v), _ptr(w_bias), q, k, v, bias, mbias, n, n, ldn, int(ending), eps,
             float(inf), st)
@@ -330,9 +348,10 @@ def transition(x_in: torch.Tensor, x_out: torch.Tensor, ln_w, ln_b, w_a, w_b, w_
     return x_out
 
 
-def pair_bias_proj(z: torch.Tensor, ln_w, ln_b: Optional[torch.Tensor], w: torch.Tensor, eps: float = 1e-5
-                   ) -> torch.Tensor:
-    """bias[h, i, j] = (W LN(z[i, j]))[h] in fp32, for the single-representation attention."""
+def pair_bias_proj(z: torch.Tensor, ln_w, ln_b: Optional[torch.Tensor], w: torch.Tensor, eps: float = 1e-5,
+                   zn: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bias[h, i, j] = (W LN(z[i, j]))[h] in fp32, for the single-representation attention.  zn: the standardised
+    copy of an fp32 z when the caller has it."""
     n = _check_pair(z)
     _check_v(ln_w, C_Z, "ln_w")
     if ln_b is not None:
@@ -340,7 +359,7 @@ def pair_bias_proj(z: torch.Tensor, ln_w, ln_b: Optional[torch.Tensor], w: torch
     heads = w.shape[0]
     w = _w(w, _zfmt(z), (heads, C_Z), "w")
     out = torch.empty(heads, n, n, dtype=torch.float32, device=z.device)
-    rows, rows_dt = _rows_of(z, None, eps)
+    rows, rows_dt = _rows_of(z, zn, eps)
     _launch("px_pair_bias_proj", _lib.load().px_pair_bias_proj, _ptr(rows), rows_dt, _ptr(ln_w), _ptr(ln_b),
             _ptr(w), _ptr(out), n * n, heads, float(eps), _stream(z))
     return out

@@ -46,9 +46,10 @@ class PairformerBlock(nn.Module):
                                                          c_a=c_s, c_z=c_z)
             self.single_transition = Transition(c_in=c_s, n=4)
 
-    def pair_path_(self, zc: torch.Tensor, mask: Optional[torch.Tensor]) -> None:
-        """The five pair updates of the block, in place."""
-        self.tri_mul_out.apply_(zc, mask)
+    def pair_path_(self, zc: torch.Tensor, mask: Optional[torch.Tensor], zn: Optional[torch.Tensor] = None) -> None:
+        """The five pair updates of the block, in place.  ``zn``: the standardised fp16 copy of an fp32 zc as passed
+        in, when the caller has it (the first triangle update then skips its standardising pass)."""
+        self.tri_mul_out.apply_(zc, mask, zn=zn)
         self.tri_mul_in.apply_(zc, mask)
         self.tri_att_start.apply_(zc, mask, ending=False)
         self.tri_att_end.apply_(zc, mask, ending=True)
@@ -101,12 +102,20 @@ class PairformerStack(nn.Module):
         main = torch.cuda.current_stream(zc.device)
         side = _side_stream(zc.device)
         side.wait_stream(main)
+        # fp32 z: the standardised copy made for a block's pair bias (its final z) also serves the first triangle
+        # update of the next block, which normalises the same rows with the same eps
+        zn_buf = torch.empty_like(zc, dtype=torch.float16) if zc.dtype == torch.float32 and s is not None else None
+        zn, zn_eps = None, None
         for block in self.blocks:
             if block.training and block.p_drop > 0:
                 raise RuntimeError("PairformerBlock: training-mode dropout is not implemented; call .eval()")
-            block.pair_path_(zc, mask)
+            block.pair_path_(zc, mask, zn if zn is not None and zn_eps == block.tri_mul_out.layer_norm_in.eps else None)
+            zn = None
             if block.c_s > 0 and s is not None:
-                bias = block.attention_pair_bias.pair_bias(zc)       # reads the block's final z, on the main stream
+                if zn_buf is not None:
+                    zn = ops.standardise_rows(zc, block.attention_pair_bias.layernorm_z.eps, out=zn_buf)
+                    zn_eps = block.attention_pair_bias.layernorm_z.eps
+                bias = block.attention_pair_bias.pair_bias(zc, zn)   # reads the block's final z, on the main stream
                 bias.record_stream(side)
                 side.wait_stream(main)
                 with torch.cuda.stream(side):

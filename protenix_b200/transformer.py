@@ -51,14 +51,15 @@ class AttentionPairBias(nn.Module):
         self.layernorm_z = LayerNorm(c_z, create_offset=create_offset_ln_z)
         self.linear_nobias_z = LinearNoBias(in_features=c_z, out_features=n_heads)
 
-    def pair_bias(self, z: torch.Tensor) -> torch.Tensor:
-        """[H, N, N] fp32 = Linear(LayerNorm(z)): the only thing this module takes from the pair representation."""
+    def pair_bias(self, z: torch.Tensor, zn: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """[H, N, N] fp32 = Linear(LayerNorm(z)): the only thing this module takes from the pair representation.
+        ``zn``: the standardised fp16 copy of a contiguous fp32 z, when the caller has it."""
         if z.dim() == 4:
             z = z[0]
         ln_b = self.layernorm_z.bias
         return ops.pair_bias_proj(z.contiguous(), self.layernorm_z.weight.detach().float(),
                                   ln_b.detach().float() if ln_b is not None else None,
-                                  self.linear_nobias_z.weight, eps=self.layernorm_z.eps)
+                                  self.linear_nobias_z.weight, eps=self.layernorm_z.eps, zn=zn)
 
     def forward(self, a: torch.Tensor, s: Optional[torch.Tensor], z: Optional[torch.Tensor],
                 bias: Optional[torch.Tensor] = None, **_unused) -> torch.Tensor:

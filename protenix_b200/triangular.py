@@ -103,10 +103,11 @@ class TriangleMultiplicativeUpdate(BaseTriangleMultiplicativeUpdate):
                 self.linear_b_p.weight, self.linear_b_g.weight, self.linear_z.weight,
                 self.linear_g.weight)
 
-    def apply_(self, z: torch.Tensor, mask: Optional[torch.Tensor]) -> torch.Tensor:
-        """z += update, in place, on a contiguous [N,N,128] tensor (used by the block)."""
+    def apply_(self, z: torch.Tensor, mask: Optional[torch.Tensor], zn: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """z += update, in place, on a contiguous [N,N,128] tensor (used by the block).  ``zn``: the standardised
+        fp16 copy of an fp32 z, if the caller has it."""
         ops.triangle_multiplication(z, z, mask, *self._kernel_args(), incoming=not self._outgoing,
-                                    add_residual=True, eps=self.layer_norm_in.eps)
+                                    add_residual=True, eps=self.layer_norm_in.eps, zn=zn)
         return z
 
     def forward(self, z: torch.Tensor, mask: Optional[torch.Tensor] = None, inplace_safe: bool = False,
@@ -170,12 +171,13 @@ class TriangleAttention(nn.Module):
                 self.linear.weight, m.linear_q.weight, m.linear_k.weight,
                 m.linear_v.weight, m.linear_g.weight, m.linear_o.weight)
 
-    def apply_(self, z: torch.Tensor, mask: Optional[torch.Tensor], ending: bool) -> torch.Tensor:
+    def apply_(self, z: torch.Tensor, mask: Optional[torch.Tensor], ending: bool,
+               zn: Optional[torch.Tensor] = None) -> torch.Tensor:
         """z += update in place; ``ending`` selects attention along columns of the *untransposed* z,
         which equals the reference's transpose / starting-node / transpose sequence
         (protenix/model/modules/pairformer.py:160-168)."""
         ops.triangle_attention(z, z, mask, *self._kernel_args(), ending=ending, add_residual=True,
-                               eps=self.layer_norm.eps, inf=self.inf)
+                               eps=self.layer_norm.eps, inf=self.inf, zn=zn)
         return z
 
     def forward(self, x: torch.Tensor, mask: Optional[torch.Tensor] = None, chunk_size: Optional[int] = None,
