@@ -61,7 +61,7 @@ pair_bias_tc_kernel(const __grid_constant__ CUtensorMap map_z, const float* __re
 
   if (cta_skip_after_error()) return;   // an earlier bounded wait gave up: do not start new work
   if (threadIdx.x == 0) {
-    tile_bars_init(bars.tile, 2);
+    tile_bars_init(bars.tile, 1, kF16);
     mbar_init(&bars.acc_full, 1);
     mbar_init(&bars.acc_free, 4);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -98,7 +98,7 @@ pair_bias_tc_kernel(const __grid_constant__ CUtensorMap map_z, const float* __re
         tile_product_loop(ctx, tmem_base, smem_u32(sm + PbLayout::w), kPbWPanel, smem_u32(sm + PbLayout::wx),
                           umma_idesc_16(128, 16, kF16, kF16), &bars.acc_full, &bars.acc_free);
       } else if (warp == 10) {
-        tile_gram_loop<kF16>(ctx, tmem_base + kPbColGram);
+        if (!kF16) tile_gram_loop<kF16>(ctx, tmem_base + kPbColGram);   // standardised rows: nothing to measure
       }
     }
   } else if (warp >= 4) {

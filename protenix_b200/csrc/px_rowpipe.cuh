@@ -187,7 +187,9 @@ __device__ __forceinline__ void row_stats_from_operand(const unsigned char* op, 
 //     standardised rows the statistics are known: (0, 1).
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kTileStages = 2;
-constexpr int kTileSlots = kTileStages + 1;    // per-row scale slots: read by the epilogue after the stage is freed
+constexpr int kTileSlots = 4;    // slots of everything written per tile by the statistics warps (scales, correction
+                                 // rows, the a_ready barrier): read after the stage is freed, by an epilogue that may
+                                 // run two tiles behind the products when the accumulators are double-buffered
 constexpr int kTilePanel = 144 * 128;          // [128 rows + 16 rows of ones][64 k] bf16
 constexpr int kTileBytes = 2 * kTilePanel;
 constexpr int kTileExtra = 128 * 32;           // [128 rows][16 k] correction panel
@@ -196,7 +198,7 @@ constexpr uint32_t kGramCols = 144;
 struct TileBars {
   // raw_full: tile in shared memory; a_ready: statistics, correction rows and scales written;
   // a_empty: every MMA that reads the stage is complete (one commit per issuing thread)
-  uint64_t raw_full[kTileStages], a_ready[kTileStages], a_empty[kTileStages], gram_full, gram_free;
+  uint64_t raw_full[kTileStages], a_ready[kTileSlots], a_empty[kTileStages], gram_full, gram_free;
 };
 struct TileCtx {
   unsigned char* tiles;     // kTileStages x kTileBytes
@@ -205,12 +207,14 @@ struct TileCtx {
   int first_tile, tile_step, n_tiles, tiles_t, n_u, n_t, swap;
 };
 
-__device__ __forceinline__ void tile_bars_init(TileBars& b, int issuers) {
+// readers: how many arrivals free a stage besides the statistics side, which adds one (the thread that issues the
+// statistics product) or, for standardised rows, four (the statistics warps, which only watch the tile arrive).
+__device__ __forceinline__ void tile_bars_init(TileBars& b, int readers, bool standardised) {
   for (int s = 0; s < kTileStages; ++s) {
     mbar_init(&b.raw_full[s], 1);
-    mbar_init(&b.a_ready[s], 4);
-    mbar_init(&b.a_empty[s], issuers);
+    mbar_init(&b.a_empty[s], readers + (standardised ? 4 : 1));
   }
+  for (int s = 0; s < kTileSlots; ++s) mbar_init(&b.a_ready[s], 4);
   mbar_init(&b.gram_full, 1);
   mbar_init(&b.gram_free, 4);
 }
@@ -272,19 +276,27 @@ __device__ __forceinline__ void tile_stats_loop(const TileCtx& c, float eps, uin
   for (int tile = c.first_tile; tile < c.n_tiles; tile += c.tile_step, ++k) {
     const int s = k % kTileStages;
     const int u = tile / c.tiles_t, t = (tile % c.tiles_t) * 128 + r;
-    ok = mbar_wait(&c.bars->gram_full, k & 1, 16u);
-    ok = __all_sync(0xffffffffu, ok);
-    if (!ok) break;
-    tc_fence_after();
-    uint32_t diag[32], sums[16];
-    tmem_ld32(t_gram + 32 * qw, diag);
-    tmem_ld16(t_gram + 128, sums);
-    tmem_wait_ld();
-    tc_fence_before();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&c.bars->gram_free);
     float mean = 0.f, std = 1.f, rstd = 1.f;
-    if (!kStandardised) {
+    if (kStandardised) {
+      // nothing to measure (no statistics product runs in this mode): the arrival of the tile only paces this loop,
+      // so that the slots it writes are those of tiles in flight
+      ok = mbar_wait(&c.bars->raw_full[s], (k / kTileStages) & 1, 16u);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&c.bars->a_empty[s]);   // seen: the stage may move on (no phase can be missed)
+    } else {
+      ok = mbar_wait(&c.bars->gram_full, k & 1, 16u);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t diag[32], sums[16];
+      tmem_ld32(t_gram + 32 * qw, diag);
+      tmem_ld16(t_gram + 128, sums);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&c.bars->gram_free);
       mean = __uint_as_float(sums[0]) * (1.0f / kC);
       const float var = fmaxf(select_own(diag, lane) * (1.0f / kC) - mean * mean, 0.f);
       rstd = rsqrtf(var + eps);
@@ -295,38 +307,42 @@ __device__ __forceinline__ void tile_stats_loop(const TileCtx& c, float eps, uin
     per_row(k, u, t, r, rstd);
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     __syncwarp();
-    if (lane == 0) mbar_arrive(&c.bars->a_ready[s]);
+    if (lane == 0) mbar_arrive(&c.bars->a_ready[k % kTileSlots]);
   }
 }
 
 // One thread: for every tile, 8 MMAs M=128 (rows) x N (weight rows of `w_addr`, two k panels of w_panel bytes) into
-// tensor-memory column d_col, then the correction step against the weight-side panel at wx_addr; acc_free/acc_full
-// hand the accumulator back and forth with the epilogue warps (`free_parity_flip`: 1 for a single buffer).
+// tensor-memory column d_tmem, then the correction step against the weight-side panel at wx_addr.  acc_full/acc_free
+// hand the accumulator back and forth with the epilogue warps: arrays of n_acc barriers, tile k uses accumulator
+// k % n_acc at d_tmem + (k % n_acc) * acc_cols (n_acc = 1 or 2).
 __device__ __forceinline__ void tile_product_loop(const TileCtx& c, uint32_t d_tmem, uint32_t w_addr, int w_panel,
                                                   uint32_t wx_addr, uint32_t idesc, uint64_t* acc_full,
-                                                  uint64_t* acc_free) {
+                                                  uint64_t* acc_free, int n_acc = 1, uint32_t acc_cols = 0) {
   const uint64_t wx_desc = umma_desc_sw32(wx_addr);
   // the correction step multiplies bf16 head/tail pairs whatever the format of the main operands; M and N as `idesc`
   const uint32_t idesc_corr = idesc | (1u << 7) | (1u << 10);
   int k = 0;
   for (int tile = c.first_tile; tile < c.n_tiles; tile += c.tile_step, ++k) {
     const int s = k % kTileStages, n = k / kTileStages;
-    if (!mbar_wait(&c.bars->raw_full[s], n & 1, 4u) || !mbar_wait(acc_free, (k & 1) ^ 1, 8u)) break;
+    const int ab = n_acc == 2 ? (k & 1) : 0, an = n_acc == 2 ? (k >> 1) : k;
+    const uint32_t d = d_tmem + ab * acc_cols;
+    if (!mbar_wait(&c.bars->raw_full[s], n & 1, 4u) || !mbar_wait(&acc_free[ab], (an & 1) ^ 1, 8u)) break;
     tc_fence_after();
     const uint32_t a_addr = smem_u32(c.tiles + s * kTileBytes);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks)
-      umma_bf16(d_tmem, umma_desc_sw128(a_addr + (ks >> 2) * kTilePanel) + 2 * (ks & 3),
+      umma_bf16(d, umma_desc_sw128(a_addr + (ks >> 2) * kTilePanel) + 2 * (ks & 3),
                 umma_desc_sw128(w_addr + (ks >> 2) * w_panel) + 2 * (ks & 3), idesc, ks ? 1u : 0u);
     // This thread's reads of the stage end here: the producer may refill it while the statistics of the tile are
-    // still on their way.  The correction step reads the tile's slot of the correction ring instead, which has one
-    // slot more than the tile ring: slot k % 3 is rewritten for tile k + 3, whose stage is handed out only after
-    // this thread's products of tile k + 1, issued after the correction step below, are complete.
+    // still on their way.  The correction step reads the tile's slot of the correction ring; slot k % 4 (rows, scales
+    // and the a_ready barrier alike) is rewritten for tile k + 4, whose stage is handed out only after the products
+    // of tile k + 2, which this thread issues after the correction step below and which wait for the epilogue of
+    // tile k (at the latest) to have read its scales and its accumulator.
     umma_commit(&c.bars->a_empty[s]);
-    if (!mbar_wait(&c.bars->a_ready[s], n & 1, 4u)) break;   // the correction step needs the statistics
+    if (!mbar_wait(&c.bars->a_ready[k % kTileSlots], (k / kTileSlots) & 1, 4u)) break;   // needs the statistics
     tc_fence_after();
-    umma_bf16(d_tmem, umma_desc_sw32(smem_u32(c.extras + (k % kTileSlots) * kTileExtra)), wx_desc, idesc_corr, 1u);
-    umma_commit(acc_full);
+    umma_bf16(d, umma_desc_sw32(smem_u32(c.extras + (k % kTileSlots) * kTileExtra)), wx_desc, idesc_corr, 1u);
+    umma_commit(&acc_full[ab]);
   }
 }
 

@@ -69,7 +69,7 @@ recycle_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_consta
 
   if (cta_skip_after_error()) return;   // an earlier bounded wait gave up: do not start new work
   if (threadIdx.x == 0) {
-    tile_bars_init(bars.tile, 2);
+    tile_bars_init(bars.tile, 1, kF16);
     mbar_init(&bars.acc_full, 1);
     mbar_init(&bars.acc_free, 8);
     for (int s = 0; s < kTileStages; ++s) {
@@ -115,7 +115,7 @@ recycle_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_consta
         tile_product_loop(ctx, tmem_base, smem_u32(sm + RcLayout::w), kPanelBytes, smem_u32(sm + RcLayout::wx),
                           umma_idesc_16(128, 128, kF16, kF16), &bars.acc_full, &bars.acc_free);
       } else if (warp == 14) {
-        tile_gram_loop<kF16>(ctx, tmem_base + kRcColGram);
+        if (!kF16) tile_gram_loop<kF16>(ctx, tmem_base + kRcColGram);   // standardised rows: nothing to measure
       }
     }
   } else if (warp >= 8) {

@@ -27,11 +27,12 @@ constexpr int kAiW1Panel = 80 * 128;           // [v 64 | bias 16][64 k]
 constexpr int kAiStageOut = 64 * 256;          // [64 d][128 t] fp16
 constexpr int kAiWarps = 24;
 constexpr int kAiThreads = 32 * kAiWarps;
-constexpr uint32_t kAiColGram = 256;           // tensor memory: q|k (128) | v|bias (80) | - | statistics (144)
+constexpr uint32_t kAiColGram = 256;           // tensor memory: q|k (128) | v|bias (80) | - | statistics (144);
+                                               // standardised rows: a second set of accumulators at 256 instead
 
 struct AiBars {
   TileBars tile;
-  uint64_t acc_full[2], acc_free[2];
+  uint64_t acc_full[2][2], acc_free[2][2];   // [product][accumulator]
   uint32_t tmem_base;
 };
 struct AiLayout {
@@ -58,6 +59,7 @@ triatt_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
                     const bf16* __restrict__ w_v, const bf16* __restrict__ w_bias, bf16* __restrict__ q_out,
                     bf16* __restrict__ k_out, float* __restrict__ bias_out, float* __restrict__ mb_out, int n_u, int n,
                     int ldm, int swap, float eps, float inf, int tiles_t, int n_tiles) {
+  constexpr int kAiAcc = kF16 ? 2 : 1;   // accumulators per product: the products of tile k+1 run beside the epilogue of k
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   AiBars& bars = *reinterpret_cast<AiBars*>(sm + AiLayout::bars);
@@ -77,10 +79,10 @@ triatt_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
 
   if (cta_skip_after_error()) return;   // an earlier bounded wait gave up: do not start new work
   if (threadIdx.x == 0) {
-    tile_bars_init(bars.tile, 3);
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(&bars.acc_full[b], 1);
-      mbar_init(&bars.acc_free[b], 8);
+    tile_bars_init(bars.tile, 2, kF16);
+    for (int b = 0; b < 4; ++b) {
+      mbar_init(&bars.acc_full[b >> 1][b & 1], 1);
+      mbar_init(&bars.acc_free[b >> 1][b & 1], 8);
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -121,13 +123,13 @@ triatt_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
       if (warp == 20) {
         tile_producer_loop(ctx, &map_z);
       } else if (warp == 23) {
-        tile_gram_loop<kF16>(ctx, tmem_base + kAiColGram);
+        if (!kF16) tile_gram_loop<kF16>(ctx, tmem_base + kAiColGram);   // standardised rows: nothing to measure
       } else if (warp == 21) {
         tile_product_loop(ctx, tmem_base, smem_u32(sm + AiLayout::w0), kPanelBytes, smem_u32(sm + AiLayout::wx0),
-                          umma_idesc_16(128, 128, kF16, kF16), &bars.acc_full[0], &bars.acc_free[0]);
+                          umma_idesc_16(128, 128, kF16, kF16), bars.acc_full[0], bars.acc_free[0], kAiAcc, 256);
       } else {
         tile_product_loop(ctx, tmem_base + 128, smem_u32(sm + AiLayout::w1), kAiW1Panel, smem_u32(sm + AiLayout::wx1),
-                          umma_idesc_16(128, 80, kF16, kF16), &bars.acc_full[1], &bars.acc_free[1]);
+                          umma_idesc_16(128, 80, kF16, kF16), bars.acc_full[1], bars.acc_free[1], kAiAcc, 256);
       }
     }
   } else if (warp >= 16) {
@@ -151,18 +153,19 @@ triatt_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     int k = 0;
     for (int tile = ctx.first_tile; tile < n_tiles; tile += ctx.tile_step, ++k) {
       const int u = tile / tiles_t, t = (tile % tiles_t) * 128 + row;
-      bool ok = mbar_wait(&bars.acc_full[0], k & 1, 32u);
+      const int ab = kAiAcc == 2 ? (k & 1) : 0, an = kAiAcc == 2 ? (k >> 1) : k;
+      bool ok = mbar_wait(&bars.acc_full[0][ab], an & 1, 32u);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       const float rstd = reinterpret_cast<const float2*>(sm + AiLayout::scale)[(k % kTileSlots) * 128 + row].x;
       uint32_t h0[32], h1[32];
-      tmem_ld32(t_acc, h0);
-      tmem_ld32(t_acc + 32, h1);
+      tmem_ld32(t_acc + 256 * ab, h0);
+      tmem_ld32(t_acc + 256 * ab + 32, h1);
       tmem_wait_ld();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars.acc_free[0]);     // this warp has read its part of the accumulator
+      if (lane == 0) mbar_arrive(&bars.acc_free[0][ab]);  // this warp has read its part of the accumulator
       if (t < n) {
         auto emit = [&](const uint32_t(&v)[32], int head) {
           uint4* dst = reinterpret_cast<uint4*>(out + (((size_t)u * kAiH + head) * n + t) * kAiD);
@@ -191,7 +194,8 @@ triatt_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     bool ok = true;
     for (int tile = ctx.first_tile; tile < n_tiles && ok; tile += ctx.tile_step, ++k) {
       const int u = tile / tiles_t, t0 = (tile % tiles_t) * 128, t = t0 + row;
-      ok = mbar_wait(&bars.acc_full[1], k & 1, 64u);
+      const int ab = kAiAcc == 2 ? (k & 1) : 0, an = kAiAcc == 2 ? (k >> 1) : k;
+      ok = mbar_wait(&bars.acc_full[1][ab], an & 1, 64u);
       // the store that last read the staging buffer (one tile ago) must be through with it
       if (leader) tma_store_wait_read<0>();
       ok = named_barrier_all(1, 256, ok);                  // all eight warps go on, or none
@@ -199,12 +203,12 @@ triatt_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
       tc_fence_after();
       const float2 sc = reinterpret_cast<const float2*>(sm + AiLayout::scale)[(k % kTileSlots) * 128 + row];
       uint32_t v[32], b[16];
-      tmem_ld32(t_acc, v);
-      if (half == 0) tmem_ld16(tmem_base + ((uint32_t)(32 * qw) << 16) + 128 + 64, b);
+      tmem_ld32(t_acc + 256 * ab, v);
+      if (half == 0) tmem_ld16(tmem_base + ((uint32_t)(32 * qw) << 16) + 256 * ab + 128 + 64, b);
       tmem_wait_ld();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars.acc_free[1]);     // this warp has read its part of the accumulator
+      if (lane == 0) mbar_arrive(&bars.acc_free[1][ab]);  // this warp has read its part of the accumulator
 #pragma unroll
       for (int e = 0; e < 32; ++e)
         *reinterpret_cast<__half*>(stage + e * 256) = __float2half_rn(sc.y * __uint_as_float(v[e]));

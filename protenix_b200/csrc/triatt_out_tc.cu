@@ -81,7 +81,7 @@ triatt_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
   if (cta_skip_after_error()) return;   // an earlier bounded wait gave up: do not start new work
   if (threadIdx.x == 0) {
     // a stage is read by the statistics product, the gate product and the output warps
-    tile_bars_init(bars.tile, 3);
+    tile_bars_init(bars.tile, 2, kF16);
     mbar_init(&bars.g_full, 1);
     mbar_init(&bars.g_free, 8);
     mbar_init(&bars.a2_ready, 8);
@@ -128,7 +128,7 @@ triatt_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
           }
         }
       } else if (warp == 23) {
-        tile_gram_loop<kF16>(ctx, tmem_base + kAoColGram);
+        if (!kF16) tile_gram_loop<kF16>(ctx, tmem_base + kAoColGram);   // standardised rows: nothing to measure
       } else if (warp == 21) {
         tile_product_loop(ctx, tmem_base + kAoColG, smem_u32(sm + AoLayout::wg), kPanelBytes, smem_u32(sm + AoLayout::wx),
                           umma_idesc_16(128, 128, kF16, kF16), &bars.g_full, &bars.g_free);

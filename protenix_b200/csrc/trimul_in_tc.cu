@@ -32,11 +32,12 @@ constexpr int kTiWExtra = 128 * 32;            // [128 rows][16 k] weight-side c
 constexpr int kTiStageOut = 64 * 256;          // [64 channels][128 t] fp16
 constexpr int kTiWarps = 24;
 constexpr int kTiThreads = 32 * kTiWarps;
-constexpr uint32_t kTiColGram = 256;           // tensor memory: out a | out b | statistics (144 columns)
+constexpr uint32_t kTiColGram = 256;           // tensor memory: out a | out b | statistics (144 columns); standardised
+                                               // rows need no statistics product: a second pair of accumulators there
 
 struct TiBars {
   TileBars tile;
-  uint64_t acc_full[2], acc_free[2];
+  uint64_t acc_full[2][2], acc_free[2][2];   // [output][accumulator]
   uint32_t tmem_base;
 };
 struct TiLayout {
@@ -59,6 +60,7 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
                     const float* __restrict__ ln_w, const float* __restrict__ ln_b, const bf16* __restrict__ w_ap,
                     const bf16* __restrict__ w_ag, const bf16* __restrict__ w_bp, const bf16* __restrict__ w_bg,
                     int n_u, int n_t, int swap, float eps, int tiles_t, int n_tiles) {
+  constexpr int kTiAcc = kF16 ? 2 : 1;   // accumulators per output: the products of tile k+1 run beside the epilogue of k
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   TiBars& bars = *reinterpret_cast<TiBars*>(sm + TiLayout::bars);
@@ -78,10 +80,10 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
 
   if (cta_skip_after_error()) return;   // an earlier bounded wait gave up: do not start new work
   if (threadIdx.x == 0) {
-    tile_bars_init(bars.tile, 3);
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(&bars.acc_full[b], 1);
-      mbar_init(&bars.acc_free[b], 8);
+    tile_bars_init(bars.tile, 2, kF16);
+    for (int b = 0; b < 4; ++b) {
+      mbar_init(&bars.acc_full[b >> 1][b & 1], 1);
+      mbar_init(&bars.acc_free[b >> 1][b & 1], 8);
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -112,12 +114,12 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
       if (warp == 20) {
         tile_producer_loop(ctx, &map_z);
       } else if (warp == 23) {
-        tile_gram_loop<kF16>(ctx, tmem_base + kTiColGram);
+        if (!kF16) tile_gram_loop<kF16>(ctx, tmem_base + kTiColGram);   // standardised rows: nothing to measure
       } else {
         const int ph = warp - 21;                          // MMA issuer of output ph
         tile_product_loop(ctx, tmem_base + 128 * ph, smem_u32(sm + TiLayout::w) + ph * kOperandBytes, kPanelBytes,
-                          smem_u32(sm + TiLayout::wx) + ph * kTiWExtra, umma_idesc_16(128, 128, kF16, kF16), &bars.acc_full[ph],
-                          &bars.acc_free[ph]);
+                          smem_u32(sm + TiLayout::wx) + ph * kTiWExtra, umma_idesc_16(128, 128, kF16, kF16), bars.acc_full[ph],
+                          bars.acc_free[ph], kTiAcc, 256);
       }
     }
   } else if (warp >= 16) {
@@ -140,7 +142,9 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
     bool ok = true;
     for (int tile = ctx.first_tile; tile < n_tiles && ok; tile += ctx.tile_step, ++k) {
       const int u = tile / tiles_t, t0 = (tile % tiles_t) * 128;
-      ok = mbar_wait(&bars.acc_full[ph], k & 1, 32u);
+      const int ab = kTiAcc == 2 ? (k & 1) : 0, an = kTiAcc == 2 ? (k >> 1) : k;
+      const uint32_t t_buf = t_acc + 256 * ab;
+      ok = mbar_wait(&bars.acc_full[ph][ab], an & 1, 32u);
       // the store that last read the staging buffer (one tile ago) must be through with it
       if (leader) tma_store_wait_read<0>();
       ok = named_barrier_all(1 + ph, 256, ok);             // all eight warps go on, or none
@@ -157,14 +161,14 @@ trimul_in_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_cons
         }
       };
       uint32_t p0[16], g0[16], p1[16], g1[16];
-      tmem_ld16(t_acc, p0);
-      tmem_ld16(t_acc + 64, g0);
-      tmem_ld16(t_acc + 16, p1);
-      tmem_ld16(t_acc + 64 + 16, g1);
+      tmem_ld16(t_buf, p0);
+      tmem_ld16(t_buf + 64, g0);
+      tmem_ld16(t_buf + 16, p1);
+      tmem_ld16(t_buf + 64 + 16, g1);
       tmem_wait_ld();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars.acc_free[ph]);      // this warp has read its part of the accumulator
+      if (lane == 0) mbar_arrive(&bars.acc_free[ph][ab]);  // this warp has read its part of the accumulator
       emit(p0, g0, 0);
       emit(p1, g1, 1);
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
