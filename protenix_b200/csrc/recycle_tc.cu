@@ -136,7 +136,16 @@ recycle_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_consta
       const long long first_row = (long long)tile * 128 + 32 * qw;
       const int valid = rows - first_row < 32 ? (rows - first_row > 0 ? (int)(rows - first_row) : 0) : 32;
       RowsOutReq rq;
-      if (!kTma) rows_out_request(rq, reinterpret_cast<const float*>(z_init), first_row, 1, valid, 64 * half, lane, true);
+      if (!kTma) {
+        rows_out_request(rq, reinterpret_cast<const float*>(z_init), first_row, 1, valid, 64 * half, lane, true);
+        // z_init of the next tile is asked of L2 now (both 32-channel blocks of this warp's rows)
+        const long long r2 = (long long)(tile + ctx.tile_step) * 128 + 32 * qw + lane;
+        if (r2 < rows) {
+          const float* p2 = reinterpret_cast<const float*>(z_init) + (size_t)r2 * kC + 64 * half;
+          asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p2));
+          asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p2 + 32));
+        }
+      }
       ok = mbar_wait(&bars.acc_full, k & 1, 32u);
       if (kTma) ok = ok && mbar_wait(&bars.res_full[s], n & 1, 33u);
       ok = named_barrier_all(1, 256, ok);                  // all eight warps go on, or none

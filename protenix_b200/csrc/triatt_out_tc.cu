@@ -221,6 +221,16 @@ triatt_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
         if (add_residual && lane < valid)
           asm volatile("prefetch.global.L2 [%0];\n" ::"l"(reinterpret_cast<const float*>(z_in) +
                                                             (size_t)(first_row + lane * row_stride) * kC + 64 * half + 32));
+        // and both blocks of the next tile, so that its requests hit L2
+        const int nt = tile + ctx.tile_step;
+        if (add_residual && nt < n_tiles) {
+          const int u2 = nt / tiles_t, t2 = (nt % tiles_t) * 128 + 32 * qw + lane;
+          if (t2 < n) {
+            const float* p2 = reinterpret_cast<const float*>(z_in) + (size_t)(swap ? (long long)t2 * n_u + u2 : (long long)u2 * n + t2) * kC + 64 * half;
+            asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p2));
+            asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p2 + 32));
+          }
+        }
       }
       ok = mbar_wait(&bars.out_full, k & 1, 64u);
       ok = named_barrier_all(1, 256, ok);                  // all eight warps go on, or none

@@ -251,6 +251,13 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
         const int valid = n - (j0 + 32 * qw) < 32 ? (n - (j0 + 32 * qw) > 0 ? n - (j0 + 32 * qw) : 0) : 32;
         rows_out_request(rq, reinterpret_cast<const float*>(z_in), (long long)i * n + j0 + 32 * qw, 1, valid, 32 * part, lane,
                          add_residual != 0);
+        // the residual lines of the next tile are asked of L2 now: a tile later they are a hit, not a trip to HBM
+        const int nt = tile + tile_step;
+        if (add_residual && nt < n_tiles) {
+          const int i2 = nt / tiles_j, j2 = (nt % tiles_j) * 128 + 32 * qw + lane;
+          if (j2 < n)
+            asm volatile("prefetch.global.L2 [%0];\n" ::"l"(reinterpret_cast<const float*>(z_in) + ((size_t)i2 * n + j2) * kC + 32 * part));
+        }
       }
       ok = mbar_wait(&bars.acc_full, k & 1, 32u);
       ok = named_barrier_all(1, 512, ok);                  // all sixteen warps go on, or none
