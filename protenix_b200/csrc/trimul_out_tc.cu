@@ -136,17 +136,21 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
         int k = 0;
         for (int tile = first_tile; tile < n_tiles; tile += tile_step, ++k) {
           const int s = k % kToStages, m = k / kToStages;
-          if (!mbar_wait(&bars.raw_full[s], m & 1, 2u) || !mbar_wait(&bars.gram_free, 1u, 2u)) break;
+          // bf16 rows: two phases of the statistics accumulator per tile (z, then x); standardised rows have known
+          // statistics, so only x is measured and the phases alternate from tile to tile
+          if (!mbar_wait(&bars.raw_full[s], m & 1, 2u) || !mbar_wait(&bars.gram_free, kF16 ? ((k & 1) ^ 1) : 1u, 2u)) break;
           tc_fence_after();
           const uint32_t z_addr = smem_u32(sm + ToLayout::zt + s * kOperandBytes), x_addr = smem_u32(sm + ToLayout::xt + s * kOperandBytes);
+          if (!kF16) {
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const uint64_t d = umma_desc_sw128(z_addr + (ks >> 2) * kPanelBytes) + 2 * (ks & 3);
-            umma_bf16(tmem_base + kToColGram, d, d, idesc_z, ks ? 1u : 0u);
+            for (int ks = 0; ks < 8; ++ks) {
+              const uint64_t d = umma_desc_sw128(z_addr + (ks >> 2) * kPanelBytes) + 2 * (ks & 3);
+              umma_bf16(tmem_base + kToColGram, d, d, idesc_z, ks ? 1u : 0u);
+            }
+            umma_commit(&bars.gram_full);
+            if (!mbar_wait(&bars.gram_free, 0u, 2u)) break;
+            tc_fence_after();
           }
-          umma_commit(&bars.gram_full);
-          if (!mbar_wait(&bars.gram_free, 0u, 2u)) break;
-          tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint64_t d = umma_desc_mn_sw128(x_addr + ks * 2048, kPanelBytes, 1024);
@@ -193,10 +197,10 @@ trimul_out_tc_kernel(const __grid_constant__ CUtensorMap map_z, const __grid_con
     bool ok = true;
     for (int tile = first_tile; tile < n_tiles; tile += tile_step, ++k) {
       const int s = k % kToStages;
-      float sumsq[2];
+      float sumsq[2] = {0.f, 0.f};
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {              // 0: z, 1: x
-        ok = mbar_wait(&bars.gram_full, which, 16u);
+      for (int which = kF16 ? 1 : 0; which < 2; ++which) {   // 0: z (bf16 rows only), 1: x
+        ok = mbar_wait(&bars.gram_full, kF16 ? (k & 1) : which, 16u);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();

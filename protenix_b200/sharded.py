@@ -170,6 +170,18 @@ class PeerExchange:
             self.fence()
         main.wait_stream(self.comm)
 
+    def mark(self) -> "torch.cuda.Event":
+        """Barrier after the copies sent so far, on the communication stream only; returns the event that follows it,
+        for the compute stream to wait on when it gets to the data (``wait``)."""
+        with torch.cuda.stream(self.comm):
+            self.fence()
+            ev = torch.cuda.Event()
+            ev.record(self.comm)
+        return ev
+
+    def wait(self, ev: "torch.cuda.Event") -> None:
+        torch.cuda.current_stream(self.device).wait_event(ev)
+
     def close(self) -> None:
         """Unmaps the other ranks' buffers and frees this rank's (after a barrier: nobody may still be writing)."""
         if not self.local:
@@ -282,18 +294,21 @@ class ShardedPairformer:
         return self._peer[key]
 
     def _peer_rows_to_channels(self, px: PeerExchange, t: torch.Tensor, key: str, k_sharded: bool, nl: int,
-                               r0: int = 0) -> None:
+                               r0: int = 0, csel: Optional[Tuple[int, int]] = None) -> None:
         """The copies of ``_rows_to_channels`` (no fence) for local rows [r0, r0 + rc) of this rank's nl rows:
-        t [128][rc][ld] (or, ``k_sharded``, [128][N][ld(rc)]) -> buffer ``key`` [128/P][N][ld(N)]."""
+        t [128][rc][ld] (or, ``k_sharded``, [128][N][ld(rc)]) -> buffer ``key`` [128/P][N][ld(N)].  ``csel``: only
+        channels [c0, c1) of every destination's 128/P."""
         p, me = self.world, self.rank
         c, r, ldl = t.shape
         cp = c // p
+        c0, c1 = csel if csel is not None else (0, cp)
         if not k_sharded:          # my rows become rows me*nl + r0.. of every channel: one run of rc*ld per channel
-            px.put_all(key, (me * nl + r0) * ldl * 2, p * nl * ldl * 2, t, lambda d: d * cp * r * ldl * 2, r * ldl * 2,
-                       r * ldl * 2, cp)
+            px.put_all(key, ((me * nl + r0) + c0 * p * nl) * ldl * 2, p * nl * ldl * 2, t,
+                       lambda d: (d * cp + c0) * r * ldl * 2, r * ldl * 2, r * ldl * 2, c1 - c0)
         else:                      # my rows are the contraction index: a run of rc per (channel, i)
             ldn = (r + 7) // 8 * 8
-            px.put_all(key, (me * nl + r0) * 2, ldn * 2, t, lambda d: d * cp * r * ldl * 2, ldl * 2, ldl * 2, cp * r)
+            px.put_all(key, (me * nl + r0) * 2 + c0 * r * ldn * 2, ldn * 2, t, lambda d: (d * cp + c0) * r * ldl * 2,
+                       ldl * 2, ldl * 2, (c1 - c0) * r)
 
     def _peer_channels_to_rows(self, px, x: torch.Tensor, c0: int = 0) -> None:
         """x [cc][N][ld] (channels c0.. of my 128/P) -> buffer ``x`` [128][N/P][ld] of every rank: rows d*nl.. go to
@@ -346,18 +361,32 @@ class ShardedPairformer:
         nl, n, _ = z_loc.shape
         cp, ldn = 128 // p, (n + 7) // 8 * 8
         zn = st.standardised(z_loc, mod.layer_norm_in.eps)
-        for r0, r1 in self._row_chunks(nl):
-            a, b = st.trimul_in_proj(mod, z_loc[r0:r1], None if mask_loc is None else mask_loc[r0:r1], incoming,
-                                     zn=None if zn is None else zn[r0:r1])
-            px.send(lambda a=a, b=b, r0=r0: (self._peer_rows_to_channels(px, a, "a", incoming, nl, r0),
-                                              self._peer_rows_to_channels(px, b, "b", incoming, nl, r0)), a, b)
-            del a, b
-        px.join()
+        halves = [(0, cp)] if cp < 2 else [(0, cp // 2), (cp // 2, cp)]
         a_full = px.local["a"].tensor((cp, n, ldn), torch.float16)
         b_full = px.local["b"].tensor((cp, n, ldn), torch.float16)
-        halves = [(0, cp)] if cp < 2 else [(0, cp // 2), (cp // 2, cp)]
-        for c0, c1 in halves:                       # the contraction in two channel groups: x of the first travels
-            x = st.trimul_contract(a_full[c0:c1], b_full[c0:c1])      # while the second is contracted
+        if len(halves) == 2 and os.environ.get("PX_PEER_AB_HALVES", "0") == "1":
+            # a and b leave in two channel groups, each closed by its own barrier on the communication stream: the
+            # first group is contracted while the second is still travelling
+            a, b = st.trimul_in_proj(mod, z_loc, mask_loc, incoming, zn=zn)
+            ready = []
+            for cs in halves:
+                px.send(lambda cs=cs: (self._peer_rows_to_channels(px, a, "a", incoming, nl, 0, cs),
+                                       self._peer_rows_to_channels(px, b, "b", incoming, nl, 0, cs)), a, b)
+                ready.append(px.mark())
+            del a, b
+        else:
+            for r0, r1 in self._row_chunks(nl):
+                a, b = st.trimul_in_proj(mod, z_loc[r0:r1], None if mask_loc is None else mask_loc[r0:r1], incoming,
+                                         zn=None if zn is None else zn[r0:r1])
+                px.send(lambda a=a, b=b, r0=r0: (self._peer_rows_to_channels(px, a, "a", incoming, nl, r0),
+                                                  self._peer_rows_to_channels(px, b, "b", incoming, nl, r0)), a, b)
+                del a, b
+            px.join()
+            ready = [None] * len(halves)
+        for (c0, c1), ev in zip(halves, ready):     # the contraction in two channel groups: x of the first travels
+            if ev is not None:                      # while the second is contracted
+                px.wait(ev)
+            x = st.trimul_contract(a_full[c0:c1], b_full[c0:c1])
             px.send(lambda x=x, c0=c0: self._peer_channels_to_rows(px, x, c0), x)
             del x
         px.join()

@@ -68,6 +68,20 @@ def test_peer_copies_assemble_the_same_tensors_as_all_to_all(world, n):
     for d in range(world):
         got = fx.bufs["b"][d].view(bf).view(cp, n, ldn)
         assert torch.equal(got[:, :, :n], full_k[d * cp:(d + 1) * cp]) and float(got[:, :, n:].float().abs().sum()) == 0.0
+    # (1b), (2b) the same two exchanges sent as two channel groups per destination
+    if cp >= 2:
+        for k in ("a", "b"):
+            for d in range(world):
+                fx.bufs[k][d].zero_()
+        for r in range(world):
+            fx.rank = r
+            for cs in ((0, cp // 2), (cp // 2, cp)):
+                _rank(world, r)._peer_rows_to_channels(fx, full[:, r * nl:(r + 1) * nl].contiguous(), "a", False, nl, 0, cs)
+                _rank(world, r)._peer_rows_to_channels(fx, full_k[:, :, r * nl:(r + 1) * nl].contiguous(), "b", True, nl, 0, cs)
+        for d in range(world):
+            assert torch.equal(fx.bufs["a"][d].view(bf).view(cp, n, ldn), full[d * cp:(d + 1) * cp])
+            got = fx.bufs["b"][d].view(bf).view(cp, n, ldn)
+            assert torch.equal(got[:, :, :n], full_k[d * cp:(d + 1) * cp]) and float(got[:, :, n:].float().abs().sum()) == 0.0
     # (3) channels -> rows: x [128][N][ld], rank r holds channels r*cp..
     xf = torch.randn(128, n, ldn, generator=g).to(bf)
     for r in range(world):
