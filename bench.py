@@ -227,7 +227,7 @@ def kernel_algo(n: int, zbytes: int) -> dict:
         "px_triatt_in_proj": ("hbm", (256 + 4 + 768 + 20) * n2),
         "px_triatt_out": ("hbm", (256 + (256 if zbytes == 4 else 0) + 2 * 128 * zbytes) * n2),
         "px_pair_bias_proj": ("hbm", (256 + 64) * n2),
-        "px_recycle_update": ("hbm", 3 * 128 * zbytes * n2),
+        "px_recycle_update": ("hbm", ((256 if zbytes == 4 else 128 * zbytes) + 2 * 128 * zbytes) * n2),
         "px_standardise_rows": ("hbm", 768.0 * n2),
     }
 
@@ -236,14 +236,15 @@ def kernel_algo(n: int, zbytes: int) -> dict:
 # captures at N = 768 with an fp32 z summarised under profiles/ (<kernel>_N768.md).  For these kernels traffic grows
 # with N^2 (operands of the N^3 kernels are re-read from L2, not DRAM), so a launch at another N is scaled by N^2.
 NCU_TRAFFIC_PER_PAIR = {
-    "px_triatt_flash": 597.9e6 / 768 ** 2,
-    "px_transition": 551.5e6 / 768 ** 2,
-    "px_trimul_contract": 418.4e6 / 768 ** 2,
-    "px_trimul_in_proj": 399.4e6 / 768 ** 2,
-    "px_trimul_out": 892.1e6 / 768 ** 2,
-    "px_triatt_in_proj": 561.7e6 / 768 ** 2,
-    "px_triatt_out": 864.6e6 / 768 ** 2,
-    "px_standardise_rows": 399.0e6 / 768 ** 2,
+    "px_triatt_flash": 596.6e6 / 768 ** 2,
+    "px_transition": 551.6e6 / 768 ** 2,
+    "px_trimul_contract": 420.1e6 / 768 ** 2,
+    "px_trimul_in_proj": 399.0e6 / 768 ** 2,
+    "px_trimul_out": 877.6e6 / 768 ** 2,
+    "px_triatt_in_proj": 563.4e6 / 768 ** 2,
+    "px_triatt_out": 863.3e6 / 768 ** 2,
+    "px_standardise_rows": 399.8e6 / 768 ** 2,
+    "px_recycle_update": 728.3e6 / 768 ** 2,
 }
 
 
