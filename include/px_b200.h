@@ -135,7 +135,8 @@ PX_API int32_t px_trimul_contract(const px_f16* a, const px_f16* b, px_f16* x, i
 #define PX_FAMILY_RECYCLE 8
 #define PX_FAMILY_SELFTEST 9
 #define PX_FAMILY_PEER 10 /* px_peer_barrier: a rank did not arrive; detail bit r names the rank (mod 16) */
-#define PX_N_FAMILIES 11
+#define PX_FAMILY_OPM 11
+#define PX_N_FAMILIES 12
 PX_API int32_t px_device_error_flags(uint32_t* flags);
 PX_API int32_t px_device_error_detail(uint32_t* flags, uint32_t* detail);
 /* Limit of every bounded wait on the current device, in SM clock cycles (default 2^28, about 0.14 s); cycles <= 0
@@ -251,6 +252,20 @@ PX_API int32_t px_pair_bias_proj(const void* z, int32_t z_dtype, const float* ln
  * (z = z_init + linear_no_bias_z_cycle(layernorm_z_cycle(z))). */
 PX_API int32_t px_recycle_update(const void* z, const void* z_init, void* out, int32_t z_dtype, const float* ln_w,
                           const float* ln_b, const px_w16* w, int64_t rows, float eps, void* stream);
+
+/* ---- Outer product mean of the MSA module (c_hidden = 32, c_z = 128) ------------------------
+ * Stage 1: x[32 i + c][32 j + e] = PX_TRIMUL_X_SCALE * sum_s a_t[32 i + c][s] * b_t[32 j + e][s], fp16, where a_t and
+ * b_t are the masked projections of the normalised MSA embedding laid out [rows = 32 N][ld_k] with the MSA row s
+ * contiguous (ld_k a multiple of 8, pad columns zero) and x is [rows][rows].  The tensor-core contraction of the
+ * triangle multiplication on one "channel".  rows <= 32768 (N <= 1024).
+ * Stage 2: z_out[i][j][:] = [z_in[i][j][:] +] (W_out (x[i, j block] / PX_TRIMUL_X_SCALE) + bias) * inv_norm[i][j], with
+ * W_out fp16 [128][1024] (input index 32 c + e, as the reference flattens), bias fp32 [128], inv_norm fp32 [N][N] =
+ * 1 / (sum_s mask[s][i] mask[s][j] + eps); z PX_F32 or PX_BF16 [N][N][128]; z_out may alias z_in.
+ * Replace OuterProductMean._opm and the normalisation, protenix/model/triangular/layers.py:685-695 and :770-777
+ * (the einsum, the reshape, linear_out, the division). */
+PX_API int32_t px_opm_outer(const px_f16* a_t, const px_f16* b_t, px_f16* x, int64_t rows, int64_t ld_k, void* stream);
+PX_API int32_t px_opm_out(const px_f16* x, const px_f16* w_out, const float* bias, const float* inv_norm, const void* z_in,
+                   void* z_out, int32_t z_dtype, int64_t n, int32_t add_residual, void* stream);
 
 /* ---- Exchange between the GPUs of one box (row-sharded path) ------------------------------
  * No counterpart in the reference (which runs the Pairformer on one GPU).  A peer buffer is a

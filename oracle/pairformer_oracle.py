@@ -222,6 +222,28 @@ def recycling_trunk(s_init: torch.Tensor, z_init: torch.Tensor, pair_mask: Optio
     return s, z
 
 
+def outer_product_mean(m: torch.Tensor, msa_mask: Optional[torch.Tensor], p: Params, eps: float = 1e-3) -> torch.Tensor:
+    """The pair update of the MSA module's OuterProductMean: [N, N, c_z] from an MSA embedding m [S, N, c_m] and an
+    MSA mask [S, N] (None: all ones).
+
+    Follows protenix/model/triangular/layers.py:657-780: ln = LayerNorm(m) (:749); a = linear_1(ln) * mask,
+    b = linear_2(ln) * mask (:752-757); outer[i, j, c, e] = sum_s a[s, i, c] * b[s, j, e] (einsum at :687, after the
+    transposes at :761-762), flattened with c slow and e fast (:690); linear_out with its bias (:693); divided by
+    norm[i, j] + eps with norm = sum_s mask[s, i] * mask[s, j] (:770-771, :775-777).  The caller adds the result to z
+    (protenix/model/modules/pairformer.py, MSABlock.forward).
+    """
+    if msa_mask is None:
+        msa_mask = m.new_ones(m.shape[:-1])
+    ln = layer_norm(m, p["layer_norm.weight"], p.get("layer_norm.bias"))
+    a = (ln @ p["linear_1.weight"].t()) * msa_mask[..., None]            # [S, N, C]
+    b = (ln @ p["linear_2.weight"].t()) * msa_mask[..., None]
+    n, c = a.shape[1], a.shape[2]
+    outer = torch.einsum("sic,sje->ijce", a, b).reshape(n, n, c * c)
+    out = outer @ p["linear_out.weight"].t() + p["linear_out.bias"]
+    norm = torch.einsum("si,sj->ij", msa_mask, msa_mask)[..., None] + eps
+    return out / norm
+
+
 def rel_frobenius(a: torch.Tensor, b: torch.Tensor) -> float:
     """||a - b||_F / ||b||_F in fp64."""
     a = a.detach().double().cpu()

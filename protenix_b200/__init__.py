@@ -2,6 +2,7 @@
 bytedance/Protenix.  One code path: hand-written CUDA kernels reached through a C ABI
 (``include/px_b200.h``); nothing falls back to the CPU or to another back-end."""
 from .layer_norm import FusedLayerNorm, LayerNorm
+from .msa import OuterProductMean
 from .pairformer import PairformerBlock, PairformerStack
 from .primitives import Linear, LinearNoBias, Transition
 from .recycling import RecyclingTrunk
@@ -15,6 +16,6 @@ __all__ = [
     "FusedLayerNorm", "LayerNorm", "PairformerBlock", "PairformerStack", "Linear", "LinearNoBias", "Transition",
     "AttentionPairBias", "OpenfoldLinear", "TriangleAttention", "TriangleAttentionEndingNode",
     "TriangleAttentionStartingNode", "TriangleMultiplicationIncoming", "TriangleMultiplicationOutgoing",
-    "TriangleMultiplicativeUpdate", "dropout_add_rowwise", "RecyclingTrunk",
+    "TriangleMultiplicativeUpdate", "dropout_add_rowwise", "RecyclingTrunk", "OuterProductMean",
 ]
 __version__ = "0.1.0"

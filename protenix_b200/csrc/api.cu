@@ -4,7 +4,7 @@
 namespace px {
 #define PX_FAMILY(name) unsigned int name##_error_flags(); int name##_set_wait_limit(long long);
 PX_FAMILY(contract) PX_FAMILY(flash) PX_FAMILY(transition) PX_FAMILY(trimul_in) PX_FAMILY(trimul_out)
-PX_FAMILY(triatt_in) PX_FAMILY(triatt_out) PX_FAMILY(pair_bias) PX_FAMILY(recycle) PX_FAMILY(selftest) PX_FAMILY(peer)
+PX_FAMILY(triatt_in) PX_FAMILY(triatt_out) PX_FAMILY(pair_bias) PX_FAMILY(recycle) PX_FAMILY(selftest) PX_FAMILY(peer) PX_FAMILY(opm)
 #undef PX_FAMILY
 }  // namespace px
 
@@ -15,11 +15,11 @@ typedef int (*LimitFn)(long long);
 const FlagsFn kFlagFns[PX_N_FAMILIES] = {px::contract_error_flags, px::flash_error_flags, px::transition_error_flags,
                                          px::trimul_in_error_flags, px::trimul_out_error_flags, px::triatt_in_error_flags,
                                          px::triatt_out_error_flags, px::pair_bias_error_flags, px::recycle_error_flags,
-                                         px::selftest_error_flags, px::peer_error_flags};
+                                         px::selftest_error_flags, px::peer_error_flags, px::opm_error_flags};
 const LimitFn kLimitFns[PX_N_FAMILIES] = {px::contract_set_wait_limit, px::flash_set_wait_limit, px::transition_set_wait_limit,
                                           px::trimul_in_set_wait_limit, px::trimul_out_set_wait_limit, px::triatt_in_set_wait_limit,
                                           px::triatt_out_set_wait_limit, px::pair_bias_set_wait_limit, px::recycle_set_wait_limit,
-                                          px::selftest_set_wait_limit, px::peer_set_wait_limit};
+                                          px::selftest_set_wait_limit, px::peer_set_wait_limit, px::opm_set_wait_limit};
 }  // namespace
 
 // Synchronises the device and returns (and clears) what the bounded waits recorded: bit f of *flags is set when a wait

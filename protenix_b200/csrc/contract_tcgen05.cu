@@ -34,13 +34,13 @@ struct TcBarriers {
 
 __global__ void __launch_bounds__(192, 1)
 trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                          bf16* __restrict__ x, int n, int ld, int tiles_i, int tiles_j, int total_tiles) {
+                          bf16* __restrict__ x, int n, int ld_k, int ld, int tiles_i, int tiles_j, int total_tiles) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // operand ring first (1024-byte aligned for the 128-byte swizzle), barriers after it
   unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   TcBarriers& bars = *reinterpret_cast<TcBarriers*>(ring + kTcStages * kTcStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nk = (ld + kTcBK - 1) / kTcBK;
+  const int nk = (ld_k + kTcBK - 1) / kTcBK;      // ld_k: extent of the contraction index; ld: row stride of x
 
   if (cta_skip_after_error()) return;   // an earlier bounded wait gave up: do not start new work
   if (threadIdx.x == 0) {
@@ -182,6 +182,12 @@ PX_DEFINE_FAMILY_HOOKS(contract)
 
 using namespace px;
 
+static int sm_count_contract() {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms;
+}
+
 extern "C" int32_t px_trimul_contract(const px_bf16* a, const px_bf16* b, px_bf16* x, int64_t channels, int64_t n,
                                       int64_t ld, void* stream) {
   if (!a || !b || !x || channels <= 0 || channels > 65535 || n <= 0 || n > 32768 || ld != px_ld(n))
@@ -199,8 +205,30 @@ extern "C" int32_t px_trimul_contract(const px_bf16* a, const px_bf16* b, px_bf1
   if (cudaFuncSetAttribute(trimul_contract_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
     return PX_ERR_LAUNCH;
-  trimul_contract_tc_kernel<<<grid, 192, smem, (cudaStream_t)stream>>>(ma, mb, (bf16*)x, (int)n, (int)ld, tiles_i,
-                                                                       tiles_j, total);
+  trimul_contract_tc_kernel<<<grid, 192, smem, (cudaStream_t)stream>>>(ma, mb, (bf16*)x, (int)n, (int)ld, (int)ld,
+                                                                       tiles_i, tiles_j, total);
+  return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
+}
+
+// The same kernel for the outer product of the MSA module: one "channel", rows = 32 N, contraction over the ld_k
+// (padded) MSA rows; x is [rows][rows].
+extern "C" int32_t px_opm_outer(const px_f16* a_t, const px_f16* b_t, px_f16* x, int64_t rows, int64_t ld_k, void* stream) {
+  if (!a_t || !b_t || !x || rows <= 0 || rows > 32768 || rows % 8 || ld_k <= 0 || ld_k % 8 || ld_k > (1 << 20))
+    return PX_ERR_BAD_ARG;
+  if (((uintptr_t)a_t | (uintptr_t)b_t | (uintptr_t)x) & 15) return PX_ERR_BAD_ARG;
+  CUtensorMap ma, mb;
+  if (!make_operand_map(&ma, a_t, 1, rows, ld_k, kTcBM) || !make_operand_map(&mb, b_t, 1, rows, ld_k, kTcBN))
+    return PX_ERR_LAUNCH;
+  const int tiles_i = (int)((rows + kTcBM - 1) / kTcBM), tiles_j = (int)((rows + kTcBN - 1) / kTcBN);
+  const int total = tiles_i * tiles_j;
+  const int sms = sm_count_contract();
+  const int grid = total < sms ? total : sms;
+  const size_t smem = (size_t)kTcStages * kTcStageBytes + sizeof(TcBarriers) + 1024;
+  if (cudaFuncSetAttribute(trimul_contract_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess)
+    return PX_ERR_LAUNCH;
+  trimul_contract_tc_kernel<<<grid, 192, smem, (cudaStream_t)stream>>>(ma, mb, (bf16*)x, (int)rows, (int)ld_k, (int)rows,
+                                                                       tiles_i, tiles_j, total);
   return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
 }
 

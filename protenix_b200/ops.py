@@ -132,7 +132,8 @@ def _launch(name: str, fn, *args) -> None:
 
 
 KERNEL_FAMILIES = ("trimul_contract", "triatt_flash", "transition", "trimul_in_proj", "trimul_out", "triatt_in_proj",
-                   "triatt_out", "pair_bias_proj", "recycle_update", "selftest", "peer_barrier")   # bit order of px_device_error_flags
+                   "triatt_out", "pair_bias_proj", "recycle_update", "selftest", "peer_barrier",
+                   "outer_product_mean")   # bit order of px_device_error_flags
 
 
 def device_error_flags(device=None, raise_on_error: bool = True) -> int:
@@ -390,6 +391,52 @@ def recycle_update(z: torch.Tensor, z_init: torch.Tensor, ln_w, ln_b: Optional[t
     _launch("px_recycle_update", _lib.load().px_recycle_update, _ptr(z), _ptr(z_init), _ptr(out), zdt,
             _ptr(ln_w), _ptr(ln_b), _ptr(w), rows, float(eps), _stream(z))
     return out
+
+
+def outer_product_mean(z_in: Optional[torch.Tensor], z_out: torch.Tensor, m: torch.Tensor,
+                       msa_mask: Optional[torch.Tensor], ln_w, ln_b, w_1, w_2, w_out, b_out, eps: float = 1e-3,
+                       ln_eps: float = 1e-5) -> torch.Tensor:
+    """z_out = [z_in +] OuterProductMean(m): m [S, N, c_m] (fp32 or bf16), msa_mask [S, N] or None, w_1 / w_2
+    [32, c_m], w_out [128, 1024], b_out [128]; z [N, N, 128] fp32 or bf16.  The S*N-sized preparation (LayerNorm
+    kernel, the two small projections on the library GEMM, mask, transposition to [(i, c)][s] in fp16) happens here;
+    the outer product and the output projection are the tcgen05 kernels."""
+    _need_cuda(m, "m")
+    if m.dim() != 3 or not m.is_contiguous():
+        raise RuntimeError("m must be a contiguous [N_seq, N_res, c_m] tensor")
+    s_rows, n, c_m = m.shape
+    if tuple(w_1.shape) != (32, c_m) or tuple(w_2.shape) != (32, c_m) or tuple(w_out.shape) != (C_Z, 1024) or \
+            tuple(b_out.shape) != (C_Z,):
+        raise RuntimeError("outer_product_mean kernels are built for c_hidden = 32 and c_z = 128")
+    if n > 1024 or n < 1 or s_rows < 1:
+        raise RuntimeError("outer_product_mean supports 1 <= N <= 1024 tokens")
+    if _check_pair(z_out, "z_out") != n or (z_in is not None and (z_in.shape != z_out.shape or z_in.dtype != z_out.dtype)):
+        raise RuntimeError("z must be [N, N, 128] with N = m.shape[1]")
+    if not z_out.is_contiguous() or (z_in is not None and not z_in.is_contiguous()):
+        raise RuntimeError("z must be contiguous")
+    dev = m.device
+    if msa_mask is None:
+        mask = torch.ones(s_rows, n, dtype=torch.float32, device=dev)
+    else:
+        _need_cuda(msa_mask, "msa_mask")
+        if tuple(msa_mask.shape) != (s_rows, n):
+            raise RuntimeError("msa_mask must be [N_seq, N_res]")
+        mask = msa_mask.to(torch.float32)
+    ln = layer_norm(m, ln_w.detach().to(m.dtype), None if ln_b is None else ln_b.detach().to(m.dtype), ln_eps)
+    w12 = torch.cat([w_1.detach(), w_2.detach()], 0).float()
+    ab = (ln.float().view(s_rows * n, c_m) @ w12.t()).view(s_rows, n, 64) * mask[..., None]
+    ld_k = (s_rows + 7) // 8 * 8
+    a_t = torch.zeros(n * 32, ld_k, dtype=torch.float16, device=dev)
+    b_t = torch.zeros(n * 32, ld_k, dtype=torch.float16, device=dev)
+    a_t[:, :s_rows] = ab[..., :32].permute(1, 2, 0).reshape(n * 32, s_rows)
+    b_t[:, :s_rows] = ab[..., 32:].permute(1, 2, 0).reshape(n * 32, s_rows)
+    inv_norm = torch.reciprocal(mask.t() @ mask + eps).contiguous()
+    x = torch.empty(n * 32, n * 32, dtype=torch.float16, device=dev)
+    lib, st = _lib.load(), _stream(m)
+    _launch("px_opm_outer", lib.px_opm_outer, _ptr(a_t), _ptr(b_t), _ptr(x), n * 32, ld_k, st)
+    b32 = b_out.detach().float().contiguous()
+    _launch("px_opm_out", lib.px_opm_out, _ptr(x), _ptr(_w(w_out, F16, (C_Z, 1024), "w_out")), _ptr(b32), _ptr(inv_norm),
+            _ptr(z_in), _ptr(z_out), _pair_dtype(z_out), n, int(z_in is not None), st)
+    return z_out
 
 
 # ---------------------------------------------------------------------------------------------

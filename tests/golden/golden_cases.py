@@ -39,6 +39,9 @@ CASES = {
     "ln_64_none": dict(kind="layer_norm", rows=77, c=64, scale=False, offset=False, seed=44, wseed=13),
     # recycling loop around a 2-block stack: z, s are z_init, s_init
     "recycle_n16": dict(kind="recycle", n=16, c_s=384, n_blocks=2, n_cycle=3, seed=51, wseed=14, pad=2),
+    # the MSA module's OuterProductMean: MSA embedding [n_msa, n, 64] -> pair update [n, n, 128]; random MSA mask
+    "opm_n24": dict(kind="opm", n=24, n_msa=20, c_m=64, c_hidden=32, seed=61, wseed=15, p_drop=0.25),
+    "opm_n40_nomask": dict(kind="opm", n=40, n_msa=9, c_m=64, c_hidden=32, seed=62, wseed=16, p_drop=0.0),
 }
 
 
@@ -47,6 +50,13 @@ def make_inputs(case: dict) -> dict:
     kind = case["kind"]
     if kind in ("transition", "layer_norm"):
         return {"x": torch.randn(case["rows"], case["c"], generator=g)}
+    if kind == "opm":
+        m = torch.randn(case["n_msa"], case["n"], case["c_m"], generator=g)
+        mask = None
+        if case["p_drop"] > 0:
+            mask = (torch.rand(case["n_msa"], case["n"], generator=g) > case["p_drop"]).float()
+            mask[0] = 1                                  # the query sequence is never masked
+        return {"m": m, "msa_mask": mask}
     n = case["n"]
     z = torch.randn(n, n, 128, generator=g)
     s = torch.randn(n, case["c_s"], generator=g) if case.get("c_s", 0) > 0 else None

@@ -126,6 +126,10 @@ def main() -> None:
                 s, z = mod.pairformer_stack(s, z, pair_mask=inp["mask"])
             out[name + ".z"] = z.numpy()
             out[name + ".s"] = s.numpy()
+        elif kind == "opm":
+            mod = ref_layers.OuterProductMean(c_m=case["c_m"], c_z=128, c_hidden=case["c_hidden"]).eval()
+            randomize_parameters_(mod, case["wseed"])
+            out[name + ".y"] = mod(inp["m"], mask=inp["msa_mask"]).numpy()
         else:
             raise ValueError(kind)
         print(name, {k: v.shape for k, v in out.items() if k.startswith(name + ".")})

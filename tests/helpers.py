@@ -34,6 +34,8 @@ def build_module(kind: str, case: dict) -> torch.nn.Module:
         m = px.Transition(c_in=case["c"], n=case["n"])
     elif kind == "layer_norm":
         m = px.LayerNorm(case["c"], create_scale=case["scale"], create_offset=case["offset"])
+    elif kind == "opm":
+        m = px.OuterProductMean(c_m=case.get("c_m", 64), c_z=128, c_hidden=case.get("c_hidden", 32))
     elif kind == "recycle":
         m = px.RecyclingTrunk(n_blocks=case["n_blocks"], c_s=case["c_s"], N_cycle=case["n_cycle"])
     else:

@@ -1,0 +1,89 @@
+"""OuterProductMean (the MSA module's update of the pair representation) on the GPU against the reference's own
+vectors and against the CPU oracle.  Tolerance: relative Frobenius error <= 1e-2 against fp32 ground truth (fp16
+operands, fp32 accumulation: measured values are around 1e-3)."""
+import pytest
+import torch
+
+import protenix_b200 as px
+from golden_cases import CASES, make_inputs
+from helpers import build_module, golden, params_of, relf
+from oracle import pairformer_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+TOL = 1e-2
+
+
+@pytest.mark.parametrize("name", ["opm_n24", "opm_n40_nomask"])
+def test_outer_product_mean_against_reference_vectors(name):
+    case = CASES[name]
+    inp = make_inputs(case)
+    mod = build_module("opm", case).to(DEV)
+    mask = None if inp["msa_mask"] is None else inp["msa_mask"].to(DEV)
+    y = mod(inp["m"].to(DEV), mask=mask)
+    assert y.dtype == torch.float32 and torch.isfinite(y).all()
+    assert relf(y, golden()[name + ".y"]) < TOL
+    y1 = mod(inp["m"].to(DEV)[None], mask=None if mask is None else mask[None])      # a batch of one, as the reference allows
+    assert y1.shape == (1,) + tuple(y.shape) and torch.equal(y1[0], y)
+    px.ops.device_error_flags()
+
+
+@pytest.mark.parametrize("n,s_rows,p_drop,zdtype", [(1, 1, 0.0, torch.float32), (37, 5, 0.3, torch.float32),
+                                                    (100, 37, 0.2, torch.bfloat16), (128, 64, 0.0, torch.float32),
+                                                    (130, 200, 0.5, torch.float32), (256, 128, 0.1, torch.bfloat16),
+                                                    (384, 256, 0.2, torch.float32)])
+def test_outer_product_mean_added_to_z_vs_oracle(n, s_rows, p_drop, zdtype):
+    """z += OuterProductMean(m), as MSABlock applies it: ragged N and N_seq, random MSA masks (columns that no MSA
+    row covers divide by eps alone), both storage types of z."""
+    g = torch.Generator().manual_seed(1000 * n + s_rows)
+    m = torch.randn(s_rows, n, 64, generator=g)
+    mask = (torch.rand(s_rows, n, generator=g) > p_drop).float() if p_drop > 0 else None
+    z = torch.randn(n, n, 128, generator=g).to(zdtype)
+    mod = build_module("opm", dict(wseed=n + 7)).to(DEV)
+    ref_upd = O.outer_product_mean(m, mask, params_of(mod))
+    zc = z.to(DEV).clone()
+    mod.apply_(zc, m.to(DEV), None if mask is None else mask.to(DEV))
+    want = z.float() + ref_upd
+    assert torch.isfinite(zc.float()).all()
+    tol = TOL if zdtype == torch.float32 else 1.2e-2          # bf16 storage rounds the sum once more
+    assert relf(zc, want) < tol, (n, s_rows, relf(zc, want))
+    upd = mod(m.to(DEV), mask=None if mask is None else mask.to(DEV))
+    assert relf(upd, ref_upd) < TOL, (n, s_rows, relf(upd, ref_upd))
+    px.ops.device_error_flags()
+
+
+def test_outer_product_mean_is_bilinear_in_the_two_projections():
+    """A size-independent property at a size the CPU oracle would not finish quickly: doubling linear_1 doubles the
+    update minus the bias term; swapping linear_1 and linear_2 transposes (i, j) and (c, e)."""
+    n, s_rows = 512, 384
+    g = torch.Generator().manual_seed(3)
+    m = torch.randn(s_rows, n, 64, generator=g).to(DEV)
+    mod = build_module("opm", dict(wseed=5)).to(DEV)
+    with torch.no_grad():
+        mod.linear_out.bias.zero_()
+    y = mod(m)
+    with torch.no_grad():
+        mod.linear_1.weight.mul_(2.0)
+    y2 = mod(m)
+    assert relf(y2, 2.0 * y) < 2e-3
+    with torch.no_grad():
+        mod.linear_1.weight.mul_(0.5)
+        w1, w2 = mod.linear_1.weight.clone(), mod.linear_2.weight.clone()
+        mod.linear_1.weight.copy_(w2)
+        mod.linear_2.weight.copy_(w1)
+        wo = mod.linear_out.weight.view(128, 32, 32).transpose(1, 2).reshape(128, 1024).clone()
+        mod.linear_out.weight.copy_(wo)
+    y3 = mod(m)
+    assert relf(y3, y.transpose(0, 1)) < 2e-3
+    px.ops.device_error_flags()
+
+
+def test_outer_product_mean_rejects_what_it_was_not_built_for():
+    mod = build_module("opm", dict(wseed=1)).to(DEV)
+    with pytest.raises(RuntimeError):
+        mod(torch.randn(4, 8, 64))                                   # CPU tensor
+    with pytest.raises(RuntimeError):
+        mod(torch.randn(4, 1025, 64, device=DEV))                    # N beyond the supported range
+    other = px.OuterProductMean(c_m=64, c_z=128, c_hidden=16).to(DEV)
+    with pytest.raises(RuntimeError):
+        other(torch.randn(4, 8, 64, device=DEV))                     # c_hidden other than 32

@@ -39,6 +39,8 @@ def test_oracle_matches_reference_vectors(name):
     elif kind == "recycle":
         s, z = O.recycling_trunk(inp["s"], inp["z"], inp["mask"], p, n_blocks=case["n_blocks"], n_cycle=case["n_cycle"])
         assert relf(z, g[name + ".z"]) < TOL and relf(s, g[name + ".s"]) < TOL
+    elif kind == "opm":
+        assert relf(O.outer_product_mean(inp["m"], inp["msa_mask"], p), g[name + ".y"]) < TOL
     else:
         raise AssertionError(kind)
 
