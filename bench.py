@@ -44,6 +44,7 @@ def parse_args():
                          "per-block tolerance only)")
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU row-slab sample (0 = auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--n-msa", type=int, default=1024, help="MSA rows of the outer-product-mean entry of --micro")
     ap.add_argument("--micro", action="store_true",
                     help="per-kernel micro-benchmark of one block (tri-att start/end, tri-mul out/in, transition) and of "
                          "the recycling update")
@@ -213,7 +214,7 @@ def workload_config(args, world: int) -> dict:
             "parallelism": "single GPU" if world == 1 else f"z row-sharded over {world} GPUs (all_to_all / all_gather over NVLink)"}
 
 
-def kernel_algo(n: int, zbytes: int) -> dict:
+def kernel_algo(n: int, zbytes: int, n_msa: int = 1024) -> dict:
     """Algorithmic FLOPs (tensor-bound kernels) or bytes (HBM-bound kernels) of one launch."""
     n2 = float(n) * n
     return {
@@ -229,6 +230,10 @@ def kernel_algo(n: int, zbytes: int) -> dict:
         "px_pair_bias_proj": ("hbm", (256 + 64) * n2),
         "px_recycle_update": ("hbm", ((256 if zbytes == 4 else 128 * zbytes) + 2 * 128 * zbytes) * n2),
         "px_standardise_rows": ("hbm", 768.0 * n2),
+        # outer product mean with n_msa MSA rows (--n-msa): 32 x 32 products per pair and MSA row; the output stage
+        # reads the 1024 fp16 products of a pair and reads and writes z
+        "px_opm_outer": ("tensor", 2048.0 * n2 * n_msa),
+        "px_opm_out": ("hbm", (2048 + 2 * 128 * zbytes) * n2),
     }
 
 
@@ -273,8 +278,12 @@ def run_micro(args) -> None:
                 ("tri_att_end", lambda: blk.tri_att_end.apply_(work, mask, ending=True)),
                 ("pair_transition", lambda: blk.pair_transition.forward_residual_(work)),
                 ("recycle_update", lambda: trunk.update_pair(work, z_init, out=work))]
+    if n <= 1024:   # the MSA module's outer product mean (N <= 1024), with --n-msa MSA rows of 64 channels
+        opm = randomize_parameters_(px.OuterProductMean(c_m=64, c_z=128, c_hidden=32), 3).eval().cuda()
+        msa = torch.randn(args.n_msa, n, 64, generator=torch.Generator().manual_seed(2)).cuda()
+        variants.append(("outer_product_mean", lambda: opm.apply_(work, msa)))
     pk = peaks()
-    algo = kernel_algo(n, z.element_size())
+    algo = kernel_algo(n, z.element_size(), args.n_msa)
     out = {}
     for name, fn in variants:
         for _ in range(args.warmup):
@@ -290,6 +299,8 @@ def run_micro(args) -> None:
         ops.set_stage_timer(None)
         for k, (cnt, tot) in timer.summary().items():
             ms = tot / cnt
+            if k not in algo:          # small preparation launches (the LayerNorm of the MSA embedding)
+                continue
             bound, work_units = algo[k]
             ach = work_units / (ms * 1e-3) / (1e12 if bound == "tensor" else 1e9)
             peak = pk["tflops"] if bound == "tensor" else pk["hbm_gbs"]

@@ -244,6 +244,43 @@ def outer_product_mean(m: torch.Tensor, msa_mask: Optional[torch.Tensor], p: Par
     return out / norm
 
 
+def msa_pair_weighted_averaging(m: torch.Tensor, z: torch.Tensor, p: Params, n_heads: int = 8) -> torch.Tensor:
+    """The update of the MSA embedding m [S, N, c_m] weighted by the pair representation (not added).
+
+    Follows protenix/model/modules/pairformer.py:385-422: v = linear_no_bias_mv(LN(m)) split into heads (:398-402),
+    b = linear_no_bias_z(LN(z)) (:403-405), g = sigmoid(linear_no_bias_mg(LN(m))) (:406-411), w = softmax of b over
+    the second token index (dim -2 of [i, j, h], :412), wv[s, i, h, :] = sum_j w[i, j, h] v[s, j, h, :] (:413-415),
+    linear_no_bias_out(g * wv) (:416-420).
+    """
+    mn = layer_norm(m, p["layernorm_m.weight"], p.get("layernorm_m.bias"))
+    s_rows, n, _ = m.shape
+    v = (mn @ p["linear_no_bias_mv.weight"].t()).view(s_rows, n, n_heads, -1)
+    g = torch.sigmoid(mn @ p["linear_no_bias_mg.weight"].t()).view(s_rows, n, n_heads, -1)
+    b = layer_norm(z, p["layernorm_z.weight"], p.get("layernorm_z.bias")) @ p["linear_no_bias_z.weight"].t()
+    w = torch.softmax(b, dim=-2)
+    wv = torch.einsum("ijh,sjhc->sihc", w, v)
+    return (g * wv).reshape(s_rows, n, -1) @ p["linear_no_bias_out.weight"].t()
+
+
+def msa_stack(m: torch.Tensor, z: torch.Tensor, p: Params) -> torch.Tensor:
+    """m + pair-weighted averaging, then + transition (protenix/model/modules/pairformer.py:551-572, the eval path;
+    its chunking over MSA rows changes nothing in the result)."""
+    m = m + msa_pair_weighted_averaging(m, z, _sub(p, "msa_pair_weighted_averaging"))
+    return m + transition(m, _sub(p, "transition_m"))
+
+
+def msa_block(m: torch.Tensor, z: torch.Tensor, pair_mask: Optional[torch.Tensor], p: Params,
+              is_last_block: bool = False) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
+    """One block of the MSA module (protenix/model/modules/pairformer.py:658-678): z += OuterProductMean(m) without an
+    MSA mask (:659-661), m = MSAStack(m, z) unless this is the last block (:662-664), then the pair-only Pairformer
+    block (:666-674); the last block returns no m (:675-678)."""
+    z = z + outer_product_mean(m, None, _sub(p, "outer_product_mean_msa"))
+    if not is_last_block:
+        m = msa_stack(m, z, _sub(p, "msa_stack"))
+    _, z = pairformer_block(None, z, pair_mask, _sub(p, "pair_stack"))
+    return (None if is_last_block else m), z
+
+
 def rel_frobenius(a: torch.Tensor, b: torch.Tensor) -> float:
     """||a - b||_F / ||b||_F in fp64."""
     a = a.detach().double().cpu()

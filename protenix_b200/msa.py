@@ -67,3 +67,109 @@ class OuterProductMean(nn.Module):
         """z += OuterProductMean(m) in place on a contiguous [N, N, c_z] pair tensor (how MSABlock uses the module)."""
         m, mask, _ = self._msa_input(m, mask)
         return self._run(m, mask, z, z)
+
+
+class MSAPairWeightedAveraging(nn.Module):
+    """Mirror of protenix/model/modules/pairformer.py:343-422.  The pair bias Linear(LayerNorm(z)) (n_heads values per
+    pair element, the only N^2-sized step) runs in ``px_pair_bias_proj``; the rest is S*N-sized work on the LayerNorm
+    kernel and library GEMMs."""
+
+    def __init__(self, c_m: int = 64, c: int = 32, c_z: int = 128, n_heads: int = 8) -> None:
+        super().__init__()
+        from .primitives import LinearNoBias
+
+        self.c_m, self.c, self.n_heads, self.c_z = c_m, c, n_heads, c_z
+        self.layernorm_m = LayerNorm(c_m)
+        self.linear_no_bias_mv = LinearNoBias(in_features=c_m, out_features=c * n_heads)
+        self.layernorm_z = LayerNorm(c_z)
+        self.linear_no_bias_z = LinearNoBias(in_features=c_z, out_features=n_heads)
+        self.linear_no_bias_mg = LinearNoBias(in_features=c_m, out_features=c * n_heads, initializer="zeros")
+        self.linear_no_bias_out = LinearNoBias(in_features=c * n_heads, out_features=c_m, initializer="zeros")
+
+    def pair_weights(self, z: torch.Tensor) -> torch.Tensor:
+        """w [n_heads, N, N] = softmax over the second token index of Linear(LayerNorm(z)), fp32."""
+        ln_b = self.layernorm_z.bias
+        b = ops.pair_bias_proj(z.contiguous(), self.layernorm_z.weight.detach().float(),
+                               None if ln_b is None else ln_b.detach().float(), self.linear_no_bias_z.weight,
+                               eps=self.layernorm_z.eps)
+        return torch.softmax(b, dim=-1)
+
+    @torch.no_grad()
+    def forward(self, m: torch.Tensor, z: torch.Tensor, w: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The update of m [S, N, c_m] (not added).  ``w``: pair weights computed earlier with ``pair_weights(z)``."""
+        if w is None:
+            w = self.pair_weights(z)
+        s_rows, n, _ = m.shape
+        mn = self.layernorm_m(m)
+        v = self.linear_no_bias_mv(mn).view(s_rows, n, self.n_heads, self.c)
+        g = torch.sigmoid(self.linear_no_bias_mg(mn)).view(s_rows, n, self.n_heads, self.c)
+        # wv[s, i, h, :] = sum_j w[h, i, j] v[s, j, h, :]: one [N x N] . [N x S c] product per head
+        vh = v.permute(2, 1, 0, 3).reshape(self.n_heads, n, s_rows * self.c)
+        wv = torch.bmm(w.to(vh.dtype), vh).view(self.n_heads, n, s_rows, self.c).permute(2, 1, 0, 3)
+        o = (g * wv).reshape(s_rows, n, self.n_heads * self.c)
+        return self.linear_no_bias_out(o)
+
+
+class MSAStack(nn.Module):
+    """Mirror of protenix/model/modules/pairformer.py:425-572 (eval path: ``inference_forward``)."""
+
+    def __init__(self, c_m: int = 64, c_z: int = 128, c: int = 8, dropout: float = 0.15,
+                 msa_chunk_size: Optional[int] = 2048, msa_max_size: Optional[int] = 16384) -> None:
+        super().__init__()
+        from .primitives import Transition
+
+        self.c = c
+        self.msa_pair_weighted_averaging = MSAPairWeightedAveraging(c_m=c_m, c=c, c_z=c_z)
+        self.p_drop = dropout
+        self.transition_m = Transition(c_in=c_m, n=4)
+        self.msa_chunk_size, self.msa_max_size = msa_chunk_size, msa_max_size
+
+    @torch.no_grad()
+    def forward(self, m: torch.Tensor, z: torch.Tensor) -> torch.Tensor:
+        """m += PairWeightedAveraging(m, z); m += Transition(m), in place over chunks of MSA rows."""
+        if self.training and self.p_drop > 0:
+            raise RuntimeError("MSAStack: training-mode dropout is not implemented; call .eval()")
+        w = self.msa_pair_weighted_averaging.pair_weights(z)      # the same for every chunk
+        chunk = self.msa_chunk_size or m.shape[0]
+        for start in range(0, m.shape[0], chunk):
+            part = m[start:start + chunk]
+            part += self.msa_pair_weighted_averaging(part, z, w)
+            part += self.transition_m(part)
+        return m
+
+
+class MSABlock(nn.Module):
+    """Mirror of protenix/model/modules/pairformer.py:575-678: outer product mean into z, the MSA stack (unless this
+    is the last block), then a pair-only Pairformer block."""
+
+    def __init__(self, c_m: int = 64, c_z: int = 128, c_hidden: int = 32, is_last_block: bool = False,
+                 msa_dropout: float = 0.15, pair_dropout: float = 0.25, msa_chunk_size: Optional[int] = 2048,
+                 msa_max_size: Optional[int] = 16384, hidden_scale_up: bool = False) -> None:
+        super().__init__()
+        from .pairformer import PairformerBlock
+
+        self.c_m, self.c_z, self.c_hidden, self.is_last_block = c_m, c_z, c_hidden, is_last_block
+        self.outer_product_mean_msa = OuterProductMean(c_m=c_m, c_z=c_z, c_hidden=c_hidden)
+        if not is_last_block:
+            self.msa_stack = MSAStack(c_m=c_m, c_z=c_z, dropout=msa_dropout, msa_chunk_size=msa_chunk_size,
+                                      msa_max_size=msa_max_size)
+        self.pair_stack = PairformerBlock(c_z=c_z, c_s=0, dropout=pair_dropout, hidden_scale_up=hidden_scale_up)
+
+    @torch.no_grad()
+    def forward(self, m: torch.Tensor, z: torch.Tensor, pair_mask, triangle_multiplicative: str = "torch",
+                triangle_attention: str = "torch", inplace_safe: bool = False, chunk_size: Optional[int] = None):
+        """(m, z) -> (m or None, z).  m [S, N, c_m], z [N, N, c_z] (a leading batch of 1 is accepted for z).  m is
+        updated in place, as the reference's eval path does; z is copied first unless ``inplace_safe``."""
+        batch = z.dim() == 4
+        zc = z[0] if batch else z
+        if not zc.is_cuda or not m.is_cuda:
+            raise RuntimeError("MSABlock: CUDA tensors only (no CPU path)")
+        zc = zc.contiguous()
+        if not inplace_safe and zc.data_ptr() == z.data_ptr():
+            zc = zc.clone()
+        mm = m[0] if m.dim() == 4 else m
+        self.outer_product_mean_msa.apply_(zc, mm)
+        if not self.is_last_block:
+            mm = self.msa_stack(mm, zc)
+        _, zc = self.pair_stack(None, zc, pair_mask, inplace_safe=True)
+        return (None if self.is_last_block else m), (zc[None] if batch else zc)

@@ -42,6 +42,9 @@ CASES = {
     # the MSA module's OuterProductMean: MSA embedding [n_msa, n, 64] -> pair update [n, n, 128]; random MSA mask
     "opm_n24": dict(kind="opm", n=24, n_msa=20, c_m=64, c_hidden=32, seed=61, wseed=15, p_drop=0.25),
     "opm_n40_nomask": dict(kind="opm", n=40, n_msa=9, c_m=64, c_hidden=32, seed=62, wseed=16, p_drop=0.0),
+    # one block of the MSA module (outer product mean, MSA stack, pair-only Pairformer block), padding mask
+    "msa_block_n20": dict(kind="msa_block", n=20, n_msa=12, c_m=64, seed=71, wseed=17, pad=3, last=False),
+    "msa_block_last_n16": dict(kind="msa_block", n=16, n_msa=7, c_m=64, seed=72, wseed=18, pad=0, last=True),
 }
 
 
@@ -57,6 +60,10 @@ def make_inputs(case: dict) -> dict:
             mask = (torch.rand(case["n_msa"], case["n"], generator=g) > case["p_drop"]).float()
             mask[0] = 1                                  # the query sequence is never masked
         return {"m": m, "msa_mask": mask}
+    if kind == "msa_block":
+        n = case["n"]
+        return {"m": torch.randn(case["n_msa"], n, case["c_m"], generator=g), "z": torch.randn(n, n, 128, generator=g),
+                "mask": padding_mask(n, case.get("pad", 0))}
     n = case["n"]
     z = torch.randn(n, n, 128, generator=g)
     s = torch.randn(n, case["c_s"], generator=g) if case.get("c_s", 0) > 0 else None

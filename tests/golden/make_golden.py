@@ -130,6 +130,13 @@ def main() -> None:
             mod = ref_layers.OuterProductMean(c_m=case["c_m"], c_z=128, c_hidden=case["c_hidden"]).eval()
             randomize_parameters_(mod, case["wseed"])
             out[name + ".y"] = mod(inp["m"], mask=inp["msa_mask"]).numpy()
+        elif kind == "msa_block":
+            mod = ref_pf.MSABlock(c_m=case["c_m"], c_z=128, c_hidden=32, is_last_block=case["last"]).eval()
+            randomize_parameters_(mod, case["wseed"])
+            m, z = mod(inp["m"].clone(), inp["z"].clone(), inp["mask"])
+            out[name + ".z"] = z.numpy()
+            if m is not None:
+                out[name + ".m"] = m.numpy()
         else:
             raise ValueError(kind)
         print(name, {k: v.shape for k, v in out.items() if k.startswith(name + ".")})
@@ -142,6 +149,11 @@ def main() -> None:
     keys = {k: list(v.shape) for k, v in blk.state_dict().items()}
     with open(os.path.join(HERE, "block_state_dict_keys.json"), "w") as f:
         json.dump(keys, f, indent=0, sort_keys=True)
+    torch.manual_seed(0)
+    np.random.seed(0)
+    msa = ref_pf.MSABlock().eval()
+    with open(os.path.join(HERE, "msa_block_state_dict_keys.json"), "w") as f:
+        json.dump({k: list(v.shape) for k, v in msa.state_dict().items()}, f, indent=0, sort_keys=True)
     path = os.path.join(HERE, "pairformer_golden.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")

@@ -36,6 +36,9 @@ def build_module(kind: str, case: dict) -> torch.nn.Module:
         m = px.LayerNorm(case["c"], create_scale=case["scale"], create_offset=case["offset"])
     elif kind == "opm":
         m = px.OuterProductMean(c_m=case.get("c_m", 64), c_z=128, c_hidden=case.get("c_hidden", 32))
+    elif kind == "msa_block":
+        from protenix_b200.msa import MSABlock
+        m = MSABlock(c_m=case.get("c_m", 64), c_z=128, c_hidden=32, is_last_block=case.get("last", False))
     elif kind == "recycle":
         m = px.RecyclingTrunk(n_blocks=case["n_blocks"], c_s=case["c_s"], N_cycle=case["n_cycle"])
     else:

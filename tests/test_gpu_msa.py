@@ -87,3 +87,44 @@ def test_outer_product_mean_rejects_what_it_was_not_built_for():
     other = px.OuterProductMean(c_m=64, c_z=128, c_hidden=16).to(DEV)
     with pytest.raises(RuntimeError):
         other(torch.randn(4, 8, 64, device=DEV))                     # c_hidden other than 32
+
+
+@pytest.mark.parametrize("name", ["msa_block_n20", "msa_block_last_n16"])
+@pytest.mark.parametrize("zdtype", [torch.float32, torch.bfloat16])
+def test_msa_block_against_reference_vectors(name, zdtype):
+    """One block of the MSA module against what the reference itself returned: z through the outer product mean and
+    the pair-only Pairformer block, m through pair-weighted averaging and its transition."""
+    case = CASES[name]
+    inp = make_inputs(case)
+    mod = build_module("msa_block", case).to(DEV)
+    m_in = inp["m"].to(DEV)
+    m, z = mod(m_in.clone(), inp["z"].to(zdtype).to(DEV), inp["mask"].to(DEV))
+    g = golden()
+    assert relf(z, g[name + ".z"]) < (TOL if zdtype == torch.float32 else 1.5e-2)
+    if case["last"]:
+        assert m is None
+    else:
+        assert relf(m, g[name + ".m"]) < TOL
+    px.ops.device_error_flags()
+
+
+def test_msa_block_vs_oracle_ragged_sizes_and_chunked_msa_rows():
+    n, s_rows = 100, 33
+    g = torch.Generator().manual_seed(9)
+    m = torch.randn(s_rows, n, 64, generator=g)
+    z = torch.randn(n, n, 128, generator=g)
+    t = torch.ones(n)
+    t[n - 7:] = 0
+    mask = t[:, None] * t[None, :]
+    from protenix_b200.msa import MSABlock
+    from protenix_b200.init_utils import randomize_parameters_
+
+    mod = randomize_parameters_(MSABlock(msa_chunk_size=10), 21).eval().to(DEV)      # four chunks of MSA rows
+    m_ref, z_ref = O.msa_block(m, z, mask, params_of(mod))
+    m_out, z_out = mod(m.to(DEV).clone(), z.to(DEV), mask.to(DEV))
+    assert relf(z_out, z_ref) < TOL and relf(m_out, m_ref) < TOL
+    # the input z is left alone unless the caller allows in-place work; m is updated in place like the reference's
+    zin = z.to(DEV)
+    mod(m.to(DEV).clone(), zin, mask.to(DEV))
+    assert torch.equal(zin.cpu(), z)
+    px.ops.device_error_flags()

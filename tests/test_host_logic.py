@@ -19,6 +19,15 @@ def test_block_state_dict_matches_reference_layout():
     assert sum(p.numel() for p in px.PairformerBlock().parameters()) == 3070848
 
 
+def test_msa_block_state_dict_matches_reference_layout():
+    from protenix_b200.msa import MSABlock
+
+    ref = json.load(open(os.path.join(ROOT, "tests", "golden", "msa_block_state_dict_keys.json")))
+    assert {k: list(v.shape) for k, v in MSABlock().state_dict().items()} == ref
+    last = MSABlock(is_last_block=True).state_dict()
+    assert not any(k.startswith("msa_stack") for k in last) and "outer_product_mean_msa.linear_out.bias" in last
+
+
 def test_stack_keys_and_pair_only_block():
     st = px.PairformerStack(n_blocks=2)
     keys = list(st.state_dict())

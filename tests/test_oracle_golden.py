@@ -41,6 +41,12 @@ def test_oracle_matches_reference_vectors(name):
         assert relf(z, g[name + ".z"]) < TOL and relf(s, g[name + ".s"]) < TOL
     elif kind == "opm":
         assert relf(O.outer_product_mean(inp["m"], inp["msa_mask"], p), g[name + ".y"]) < TOL
+    elif kind == "msa_block":
+        m, z = O.msa_block(inp["m"], inp["z"], inp["mask"], p, is_last_block=case["last"])
+        assert relf(z, g[name + ".z"]) < TOL
+        assert (m is None) == case["last"]
+        if m is not None:
+            assert relf(m, g[name + ".m"]) < TOL
     else:
         raise AssertionError(kind)
 
