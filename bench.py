@@ -278,10 +278,10 @@ def run_micro(args) -> None:
                 ("tri_att_end", lambda: blk.tri_att_end.apply_(work, mask, ending=True)),
                 ("pair_transition", lambda: blk.pair_transition.forward_residual_(work)),
                 ("recycle_update", lambda: trunk.update_pair(work, z_init, out=work))]
-    if n <= 1024:   # the MSA module's outer product mean (N <= 1024), with --n-msa MSA rows of 64 channels
-        opm = randomize_parameters_(px.OuterProductMean(c_m=64, c_z=128, c_hidden=32), 3).eval().cuda()
-        msa = torch.randn(args.n_msa, n, 64, generator=torch.Generator().manual_seed(2)).cuda()
-        variants.append(("outer_product_mean", lambda: opm.apply_(work, msa)))
+    # the MSA module's outer product mean with --n-msa MSA rows of 64 channels
+    opm = randomize_parameters_(px.OuterProductMean(c_m=64, c_z=128, c_hidden=32), 3).eval().cuda()
+    msa = torch.randn(args.n_msa, n, 64, generator=torch.Generator().manual_seed(2)).cuda()
+    variants.append(("outer_product_mean", lambda: opm.apply_(work, msa)))
     pk = peaks()
     algo = kernel_algo(n, z.element_size(), args.n_msa)
     out = {}
@@ -299,6 +299,8 @@ def run_micro(args) -> None:
         ops.set_stage_timer(None)
         for k, (cnt, tot) in timer.summary().items():
             ms = tot / cnt
+            if k.startswith("px_opm"):   # launched once per block of token rows: the work figure is for all of them
+                ms = tot / args.steps
             if k not in algo:          # small preparation launches (the LayerNorm of the MSA embedding)
                 continue
             bound, work_units = algo[k]

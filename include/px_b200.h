@@ -256,16 +256,19 @@ PX_API int32_t px_recycle_update(const void* z, const void* z_init, void* out, i
 /* ---- Outer product mean of the MSA module (c_hidden = 32, c_z = 128) ------------------------
  * Stage 1: x[32 i + c][32 j + e] = PX_TRIMUL_X_SCALE * sum_s a_t[32 i + c][s] * b_t[32 j + e][s], fp16, where a_t and
  * b_t are the masked projections of the normalised MSA embedding laid out [rows = 32 N][ld_k] with the MSA row s
- * contiguous (ld_k a multiple of 8, pad columns zero) and x is [rows][rows].  The tensor-core contraction of the
- * triangle multiplication on one "channel".  rows <= 32768 (N <= 1024).
+ * contiguous (ld_k a multiple of 8, pad columns zero): a_t has rows_a = 32 n_i rows (a block of n_i tokens i), b_t
+ * rows_b = 32 N, and x is [rows_a][rows_b].  The tensor-core contraction of the triangle multiplication on one
+ * "channel".
  * Stage 2: z_out[i][j][:] = [z_in[i][j][:] +] (W_out (x[i, j block] / PX_TRIMUL_X_SCALE) + bias) * inv_norm[i][j], with
  * W_out fp16 [128][1024] (input index 32 c + e, as the reference flattens), bias fp32 [128], inv_norm fp32 [N][N] =
- * 1 / (sum_s mask[s][i] mask[s][j] + eps); z PX_F32 or PX_BF16 [N][N][128]; z_out may alias z_in.
+ * 1 / (sum_s mask[s][i] mask[s][j] + eps); z PX_F32 or PX_BF16 [N][N][128]; z_out may alias z_in.  The call covers
+ * n_i rows i: x, inv_norm, z_in and z_out point at the first of them (x is then the [32 n_i][32 N] block of stage 1).
  * Replace OuterProductMean._opm and the normalisation, protenix/model/triangular/layers.py:685-695 and :770-777
  * (the einsum, the reshape, linear_out, the division). */
-PX_API int32_t px_opm_outer(const px_f16* a_t, const px_f16* b_t, px_f16* x, int64_t rows, int64_t ld_k, void* stream);
+PX_API int32_t px_opm_outer(const px_f16* a_t, const px_f16* b_t, px_f16* x, int64_t rows_a, int64_t rows_b, int64_t ld_k,
+                     void* stream);
 PX_API int32_t px_opm_out(const px_f16* x, const px_f16* w_out, const float* bias, const float* inv_norm, const void* z_in,
-                   void* z_out, int32_t z_dtype, int64_t n, int32_t add_residual, void* stream);
+                   void* z_out, int32_t z_dtype, int64_t n_i, int64_t n, int32_t add_residual, void* stream);
 
 /* ---- Exchange between the GPUs of one box (row-sharded path) ------------------------------
  * No counterpart in the reference (which runs the Pairformer on one GPU).  A peer buffer is a

@@ -210,16 +210,20 @@ extern "C" int32_t px_trimul_contract(const px_bf16* a, const px_bf16* b, px_bf1
   return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
 }
 
-// The same kernel for the outer product of the MSA module: one "channel", rows = 32 N, contraction over the ld_k
-// (padded) MSA rows; x is [rows][rows].
-extern "C" int32_t px_opm_outer(const px_f16* a_t, const px_f16* b_t, px_f16* x, int64_t rows, int64_t ld_k, void* stream) {
-  if (!a_t || !b_t || !x || rows <= 0 || rows > 32768 || rows % 8 || ld_k <= 0 || ld_k % 8 || ld_k > (1 << 20))
+// The same kernel for the outer product of the MSA module: one "channel", a_t [rows_a][ld_k] against
+// b_t [rows_b][ld_k] (rows = 32 x tokens), contraction over the ld_k (padded) MSA rows; x is [rows_a][rows_b].
+extern "C" int32_t px_opm_outer(const px_f16* a_t, const px_f16* b_t, px_f16* x, int64_t rows_a, int64_t rows_b,
+                                int64_t ld_k, void* stream) {
+  if (!a_t || !b_t || !x || rows_a <= 0 || rows_a > (1 << 20) || rows_b <= 0 || rows_b > (1 << 20) || rows_b % 8 ||
+      ld_k <= 0 || ld_k % 8 || ld_k > (1 << 20))
     return PX_ERR_BAD_ARG;
   if (((uintptr_t)a_t | (uintptr_t)b_t | (uintptr_t)x) & 15) return PX_ERR_BAD_ARG;
   CUtensorMap ma, mb;
-  if (!make_operand_map(&ma, a_t, 1, rows, ld_k, kTcBM) || !make_operand_map(&mb, b_t, 1, rows, ld_k, kTcBN))
+  if (!make_operand_map(&ma, a_t, 1, rows_a, ld_k, kTcBM) || !make_operand_map(&mb, b_t, 1, rows_b, ld_k, kTcBN))
     return PX_ERR_LAUNCH;
-  const int tiles_i = (int)((rows + kTcBM - 1) / kTcBM), tiles_j = (int)((rows + kTcBN - 1) / kTcBN);
+  const int64_t ti = (rows_a + kTcBM - 1) / kTcBM, tj = (rows_b + kTcBN - 1) / kTcBN;
+  if (ti * tj > 0x7fffffff) return PX_ERR_UNSUPPORTED;
+  const int tiles_i = (int)ti, tiles_j = (int)tj;
   const int total = tiles_i * tiles_j;
   const int sms = sm_count_contract();
   const int grid = total < sms ? total : sms;
@@ -227,8 +231,8 @@ extern "C" int32_t px_opm_outer(const px_f16* a_t, const px_f16* b_t, px_f16* x,
   if (cudaFuncSetAttribute(trimul_contract_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
     return PX_ERR_LAUNCH;
-  trimul_contract_tc_kernel<<<grid, 192, smem, (cudaStream_t)stream>>>(ma, mb, (bf16*)x, (int)rows, (int)ld_k, (int)rows,
-                                                                       tiles_i, tiles_j, total);
+  trimul_contract_tc_kernel<<<grid, 192, smem, (cudaStream_t)stream>>>(ma, mb, (bf16*)x, (int)rows_a, (int)ld_k,
+                                                                       (int)rows_b, tiles_i, tiles_j, total);
   return cudaGetLastError() == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
 }
 

@@ -18,6 +18,8 @@
 //   warps 2..5  epilogue: (acc * 2^6 + bias) * inv_norm + residual; fp32 rows go out coalesced through a 4 KB
 //               staging area per warp, bf16 rows as 64-byte runs
 // HBM-bound: 2048 bytes of x per pair element against 2 * 128 * 1024 FLOP.  Every mbarrier wait is bounded.
+// The entry point takes a block of n_i rows i (pointers of x, inv_norm and z at the block's first row), so that a
+// caller can bound the size of x: (32 n_i) x (32 N) fp16.
 #include "px_rowpipe.cuh"
 
 namespace px {
@@ -197,10 +199,11 @@ PX_DEFINE_FAMILY_HOOKS(opm)
 
 template <typename Tz>
 static int32_t launch_opm_out(const px_f16* x, const px_f16* w_out, const float* bias, const float* inv_norm,
-                              const void* z_in, void* z_out, int64_t n, int32_t add_residual, cudaStream_t st) {
+                              const void* z_in, void* z_out, int64_t n_i, int64_t n, int32_t add_residual,
+                              cudaStream_t st) {
   CUtensorMap mx, mw;
-  // x [32 n rows (i, c)][32 n columns (j, e)] seen as (e, j, row): box [4 rows][128 j][32 e], 64-byte swizzle
-  if (!make_map_3d(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x, 32, (uint64_t)n, (uint64_t)n * 32, 64, (uint64_t)n * 64, 32, 128,
+  // x [32 n_i rows (i, c)][32 n columns (j, e)] seen as (e, j, row): box [4 rows][128 j][32 e], 64-byte swizzle
+  if (!make_map_3d(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x, 32, (uint64_t)n, (uint64_t)n_i * 32, 64, (uint64_t)n * 64, 32, 128,
                    CU_TENSOR_MAP_SWIZZLE_64B, kOpCc) ||
       // W_out [128 o][32 c][32 e] seen as (e, o, c): box [4 c][128 o][32 e]
       !make_map_3d(&mw, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, w_out, 32, 128, 32, 2048, 64, 32, 128, CU_TENSOR_MAP_SWIZZLE_64B,
@@ -209,7 +212,7 @@ static int32_t launch_opm_out(const px_f16* x, const px_f16* w_out, const float*
   const size_t smem = OpLayout::total + 1024;
   if (cudaFuncSetAttribute(opm_out_tc_kernel<Tz>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return PX_ERR_LAUNCH;
-  const int64_t tiles_j = (n + 127) / 128, total = tiles_j * n;
+  const int64_t tiles_j = (n + 127) / 128, total = tiles_j * n_i;
   if (total > 0x7fffffff) return PX_ERR_UNSUPPORTED;
   const int grid = (int)(total < sm_count() ? total : sm_count());
   opm_out_tc_kernel<Tz><<<grid, 192, smem, st>>>(mx, mw, bias, inv_norm, (const Tz*)z_in, (Tz*)z_out, (int)n, add_residual,
@@ -222,14 +225,16 @@ static int32_t launch_opm_out(const px_f16* x, const px_f16* w_out, const float*
 using namespace px;
 
 extern "C" int32_t px_opm_out(const px_f16* x, const px_f16* w_out, const float* bias, const float* inv_norm,
-                              const void* z_in, void* z_out, int32_t z_dtype, int64_t n, int32_t add_residual,
-                              void* stream) {
-  if (!x || !w_out || !bias || !inv_norm || !z_out || (add_residual && !z_in) || n <= 0 || n > 1024) return PX_ERR_BAD_ARG;
+                              const void* z_in, void* z_out, int32_t z_dtype, int64_t n_i, int64_t n,
+                              int32_t add_residual, void* stream) {
+  if (!x || !w_out || !bias || !inv_norm || !z_out || (add_residual && !z_in) || n <= 0 || n > 32768 || n_i <= 0 ||
+      n_i > n)
+    return PX_ERR_BAD_ARG;
   if (((uintptr_t)x | (uintptr_t)w_out | (uintptr_t)bias | (uintptr_t)inv_norm | (uintptr_t)z_in | (uintptr_t)z_out) & 15)
     return PX_ERR_BAD_ARG;
   if (z_dtype == PX_F32)
-    return launch_opm_out<float>(x, w_out, bias, inv_norm, z_in, z_out, n, add_residual, (cudaStream_t)stream);
+    return launch_opm_out<float>(x, w_out, bias, inv_norm, z_in, z_out, n_i, n, add_residual, (cudaStream_t)stream);
   if (z_dtype == PX_BF16)
-    return launch_opm_out<bf16>(x, w_out, bias, inv_norm, z_in, z_out, n, add_residual, (cudaStream_t)stream);
+    return launch_opm_out<bf16>(x, w_out, bias, inv_norm, z_in, z_out, n_i, n, add_residual, (cudaStream_t)stream);
   return PX_ERR_UNSUPPORTED;
 }

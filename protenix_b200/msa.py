@@ -6,7 +6,7 @@ signature, ``state_dict`` keys).  The work that scales with N^2 -- the outer pro
 residual -- runs in the tcgen05 kernels behind ``px_opm_outer`` / ``px_opm_out``.  What scales with S * N (the
 LayerNorm of the MSA embedding, the two c_m -> 32 projections, the mask and the normalisation counts: a thousandth of
 the FLOPs) is prepared here with the LayerNorm kernel and library GEMMs.  CUDA only; c_hidden = 32 and c_z = 128 are
-the compiled shapes, N <= 1024.
+the compiled shapes; the outer products are formed for blocks of token rows so that their buffer stays within 2 GiB.
 """
 from __future__ import annotations
 

@@ -393,6 +393,9 @@ def recycle_update(z: torch.Tensor, z_init: torch.Tensor, ln_w, ln_b: Optional[t
     return out
 
 
+OPM_X_BYTES = 2 << 30      # bound of the outer-product buffer of outer_product_mean
+
+
 def outer_product_mean(z_in: Optional[torch.Tensor], z_out: torch.Tensor, m: torch.Tensor,
                        msa_mask: Optional[torch.Tensor], ln_w, ln_b, w_1, w_2, w_out, b_out, eps: float = 1e-3,
                        ln_eps: float = 1e-5) -> torch.Tensor:
@@ -407,8 +410,8 @@ def outer_product_mean(z_in: Optional[torch.Tensor], z_out: torch.Tensor, m: tor
     if tuple(w_1.shape) != (32, c_m) or tuple(w_2.shape) != (32, c_m) or tuple(w_out.shape) != (C_Z, 1024) or \
             tuple(b_out.shape) != (C_Z,):
         raise RuntimeError("outer_product_mean kernels are built for c_hidden = 32 and c_z = 128")
-    if n > 1024 or n < 1 or s_rows < 1:
-        raise RuntimeError("outer_product_mean supports 1 <= N <= 1024 tokens")
+    if n > 32768 or n < 1 or s_rows < 1:
+        raise RuntimeError("outer_product_mean supports 1 <= N <= 32768 tokens")
     if _check_pair(z_out, "z_out") != n or (z_in is not None and (z_in.shape != z_out.shape or z_in.dtype != z_out.dtype)):
         raise RuntimeError("z must be [N, N, 128] with N = m.shape[1]")
     if not z_out.is_contiguous() or (z_in is not None and not z_in.is_contiguous()):
@@ -430,12 +433,20 @@ def outer_product_mean(z_in: Optional[torch.Tensor], z_out: torch.Tensor, m: tor
     a_t[:, :s_rows] = ab[..., :32].permute(1, 2, 0).reshape(n * 32, s_rows)
     b_t[:, :s_rows] = ab[..., 32:].permute(1, 2, 0).reshape(n * 32, s_rows)
     inv_norm = torch.reciprocal(mask.t() @ mask + eps).contiguous()
-    x = torch.empty(n * 32, n * 32, dtype=torch.float16, device=dev)
+    # blocks of rows i bound the size of x = [32 n_i][32 N] fp16 (OPM_X_BYTES, 2 GiB by default)
+    n_blk = max(1, min(n, OPM_X_BYTES // (2048 * n)))
+    x = torch.empty(min(n, n_blk) * 32, n * 32, dtype=torch.float16, device=dev)
     lib, st = _lib.load(), _stream(m)
-    _launch("px_opm_outer", lib.px_opm_outer, _ptr(a_t), _ptr(b_t), _ptr(x), n * 32, ld_k, st)
     b32 = b_out.detach().float().contiguous()
-    _launch("px_opm_out", lib.px_opm_out, _ptr(x), _ptr(_w(w_out, F16, (C_Z, 1024), "w_out")), _ptr(b32), _ptr(inv_norm),
-            _ptr(z_in), _ptr(z_out), _pair_dtype(z_out), n, int(z_in is not None), st)
+    w16 = _w(w_out, F16, (C_Z, 1024), "w_out")
+    zb = z_out.element_size() * n * C_Z                # bytes of one row i of z
+    for i0 in range(0, n, n_blk):
+        ni = min(n_blk, n - i0)
+        _launch("px_opm_outer", lib.px_opm_outer, a_t.data_ptr() + i0 * 32 * ld_k * 2, _ptr(b_t), _ptr(x), ni * 32, n * 32,
+                ld_k, st)
+        _launch("px_opm_out", lib.px_opm_out, _ptr(x), _ptr(w16), _ptr(b32), inv_norm.data_ptr() + i0 * n * 4,
+                None if z_in is None else z_in.data_ptr() + i0 * zb, z_out.data_ptr() + i0 * zb, _pair_dtype(z_out), ni, n,
+                int(z_in is not None), st)
     return z_out
 
 

@@ -82,8 +82,6 @@ def test_outer_product_mean_rejects_what_it_was_not_built_for():
     mod = build_module("opm", dict(wseed=1)).to(DEV)
     with pytest.raises(RuntimeError):
         mod(torch.randn(4, 8, 64))                                   # CPU tensor
-    with pytest.raises(RuntimeError):
-        mod(torch.randn(4, 1025, 64, device=DEV))                    # N beyond the supported range
     other = px.OuterProductMean(c_m=64, c_z=128, c_hidden=16).to(DEV)
     with pytest.raises(RuntimeError):
         other(torch.randn(4, 8, 64, device=DEV))                     # c_hidden other than 32
@@ -127,4 +125,21 @@ def test_msa_block_vs_oracle_ragged_sizes_and_chunked_msa_rows():
     zin = z.to(DEV)
     mod(m.to(DEV).clone(), zin, mask.to(DEV))
     assert torch.equal(zin.cpu(), z)
+    px.ops.device_error_flags()
+
+
+def test_outer_product_mean_in_blocks_of_rows_is_the_same_to_the_bit(monkeypatch):
+    """The outer products are formed for blocks of token rows to bound their buffer; the block size changes no bit."""
+    n, s_rows = 150, 40
+    g = torch.Generator().manual_seed(17)
+    m = torch.randn(s_rows, n, 64, generator=g).to(DEV)
+    mask = (torch.rand(s_rows, n, generator=g) > 0.2).float().to(DEV)
+    z = torch.randn(n, n, 128, generator=g).to(DEV)
+    mod = build_module("opm", dict(wseed=2)).to(DEV)
+    whole = mod.apply_(z.clone(), m, mask)
+    monkeypatch.setattr(px.ops, "OPM_X_BYTES", 2048 * n * 37)       # blocks of 37 rows: 37, 37, 37, 37, 2
+    parts = mod.apply_(z.clone(), m, mask)
+    assert torch.equal(whole, parts)
+    ref = z.cpu() + O.outer_product_mean(m.cpu(), mask.cpu(), params_of(mod))
+    assert relf(parts, ref) < TOL
     px.ops.device_error_flags()
