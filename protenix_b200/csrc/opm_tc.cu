@@ -230,8 +230,8 @@ extern "C" int32_t px_opm_out(const px_f16* x, const px_f16* w_out, const float*
   if (!x || !w_out || !bias || !inv_norm || !z_out || (add_residual && !z_in) || n <= 0 || n > 32768 || n_i <= 0 ||
       n_i > n)
     return PX_ERR_BAD_ARG;
-  if (((uintptr_t)x | (uintptr_t)w_out | (uintptr_t)bias | (uintptr_t)inv_norm | (uintptr_t)z_in | (uintptr_t)z_out) & 15)
-    return PX_ERR_BAD_ARG;
+  if ((((uintptr_t)x | (uintptr_t)w_out | (uintptr_t)bias | (uintptr_t)z_in | (uintptr_t)z_out) & 15) || ((uintptr_t)inv_norm & 3))
+    return PX_ERR_BAD_ARG;          // inv_norm is read one value at a time: a block of rows may start anywhere
   if (z_dtype == PX_F32)
     return launch_opm_out<float>(x, w_out, bias, inv_norm, z_in, z_out, n_i, n, add_residual, (cudaStream_t)stream);
   if (z_dtype == PX_BF16)
