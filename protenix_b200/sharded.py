@@ -122,7 +122,9 @@ class PeerExchange:
         for k in ("a", "b", "flags"):   # pad columns [n, ld) are never written by an exchange and must read as zero
             self.local[k].tensor((sizes[k],), torch.uint8).zero_()
         self.epoch = 0                  # number of the last barrier; the same sequence on every rank
-        self.comm = torch.cuda.Stream(device=device)      # copies and barriers run here, beside the compute stream
+        # copies and barriers run on a stream of their own, beside the compute stream; PX_PEER_STREAM=main keeps them
+        # on the compute stream (no cross-stream events, no overlap of the x return with the contraction)
+        self.comm = None if os.environ.get("PX_PEER_STREAM", "comm") == "main" else torch.cuda.Stream(device=device)
         self.use_flags = os.environ.get("PX_PEER_FENCE", "flags") != "nccl"
         torch.cuda.synchronize(device)
         handles = [None] * world
@@ -155,6 +157,9 @@ class PeerExchange:
         """Runs ``fn`` (copies into peer buffers) on the communication stream, after everything the compute stream has
         been given so far; the compute stream goes on.  ``keep``: tensors the copies read (their memory must not be
         reused before the copies are through)."""
+        if self.comm is None:
+            fn()
+            return
         main = torch.cuda.current_stream(self.device)
         self.comm.wait_stream(main)
         for t in keep:
@@ -164,6 +169,9 @@ class PeerExchange:
 
     def join(self) -> None:
         """Barrier after the copies sent so far, on the communication stream; the compute stream waits for it."""
+        if self.comm is None:
+            self.fence()
+            return
         main = torch.cuda.current_stream(self.device)
         self.comm.wait_stream(main)
         with torch.cuda.stream(self.comm):
@@ -173,10 +181,11 @@ class PeerExchange:
     def mark(self) -> "torch.cuda.Event":
         """Barrier after the copies sent so far, on the communication stream only; returns the event that follows it,
         for the compute stream to wait on when it gets to the data (``wait``)."""
-        with torch.cuda.stream(self.comm):
+        stream = self.comm if self.comm is not None else torch.cuda.current_stream(self.device)
+        with torch.cuda.stream(stream):
             self.fence()
             ev = torch.cuda.Event()
-            ev.record(self.comm)
+            ev.record(stream)
         return ev
 
     def wait(self, ev: "torch.cuda.Event") -> None:
