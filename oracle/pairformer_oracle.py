@@ -281,6 +281,20 @@ def msa_block(m: torch.Tensor, z: torch.Tensor, pair_mask: Optional[torch.Tensor
     return (None if is_last_block else m), z
 
 
+def msa_module(msa: torch.Tensor, has_deletion: torch.Tensor, deletion_value: torch.Tensor, z: torch.Tensor,
+               s_inputs: torch.Tensor, pair_mask: Optional[torch.Tensor], p: Params, n_blocks: int) -> torch.Tensor:
+    """The MSA module on MSA rows that are already sampled (protenix/model/modules/pairformer.py:872-911): the
+    features one_hot(msa, 32) | has_deletion | deletion_value (:872-889) through linear_no_bias_m (:895), plus
+    linear_no_bias_s(s_inputs) broadcast over the rows (:898), then the blocks (:899-910); the last block returns no m
+    (:675-678)."""
+    feat = torch.cat([F.one_hot(msa, 32).to(z.dtype), has_deletion[..., None].to(z.dtype),
+                      deletion_value[..., None].to(z.dtype)], dim=-1)
+    m = feat @ p["linear_no_bias_m.weight"].t() + s_inputs @ p["linear_no_bias_s.weight"].t()
+    for i in range(n_blocks):
+        m, z = msa_block(m, z, pair_mask, _sub(p, f"blocks.{i}"), is_last_block=(i + 1 == n_blocks))
+    return z
+
+
 def rel_frobenius(a: torch.Tensor, b: torch.Tensor) -> float:
     """||a - b||_F / ||b||_F in fp64."""
     a = a.detach().double().cpu()

@@ -173,3 +173,73 @@ class MSABlock(nn.Module):
             mm = self.msa_stack(mm, zc)
         _, zc = self.pair_stack(None, zc, pair_mask, inplace_safe=True)
         return (None if self.is_last_block else m), (zc[None] if batch else zc)
+
+
+def sample_msa_indices(n: int, device, lower_bound: int = 1, strategy: str = "random") -> torch.Tensor:
+    """How many and which MSA rows a forward pass uses (protenix/model/utils.py:290-311): a size drawn uniformly from
+    [min(lower_bound, n), n], then a random subset or the first rows."""
+    if strategy not in ("random", "topk"):
+        raise ValueError("strategy must be 'random' or 'topk'")
+    size = int(torch.randint(low=min(lower_bound, n), high=n + 1, size=(1,)).item())
+    return torch.randperm(n, device=device)[:size] if strategy == "random" else torch.arange(size, device=device)
+
+
+class MSAModule(nn.Module):
+    """Mirror of protenix/model/modules/pairformer.py:682-911 (Algorithm 8): MSA features -> m, then ``n_blocks``
+    MSABlocks that write into the pair representation.  Eval only."""
+
+    def __init__(self, n_blocks: int = 4, c_m: int = 64, c_z: int = 128, c_s_inputs: int = 449,
+                 msa_dropout: float = 0.15, pair_dropout: float = 0.25, blocks_per_ckpt: Optional[int] = 1,
+                 msa_chunk_size: Optional[int] = 2048, msa_max_size: Optional[int] = 16384,
+                 msa_configs: Optional[dict] = None, hidden_scale_up: bool = False) -> None:
+        super().__init__()
+        from .primitives import LinearNoBias
+
+        msa_configs = msa_configs or {}
+        self.n_blocks, self.c_m, self.c_s_inputs, self.blocks_per_ckpt = n_blocks, c_m, c_s_inputs, blocks_per_ckpt
+        self.msa_chunk_size, self.msa_max_size = msa_chunk_size, msa_max_size
+        self.input_feature = {"msa": 32, "has_deletion": 1, "deletion_value": 1}
+        self.msa_configs = {"enable": msa_configs.get("enable", False), "strategy": msa_configs.get("strategy", "random"),
+                            "train_cutoff": 512, "test_cutoff": 16384, "train_lowerb": 1, "test_lowerb": 1}
+        if "sample_cutoff" in msa_configs:
+            self.msa_configs["train_cutoff"] = msa_configs["sample_cutoff"].get("train", 512)
+            self.msa_configs["test_cutoff"] = msa_configs["sample_cutoff"].get("test", 16384)
+            self.msa_max_size = self.msa_configs["train_cutoff"]
+        if "min_size" in msa_configs:
+            self.msa_configs["train_lowerb"] = msa_configs["min_size"].get("train", 1)
+            self.msa_configs["test_lowerb"] = msa_configs["min_size"].get("test", 1)
+        self.linear_no_bias_m = LinearNoBias(in_features=32 + 1 + 1, out_features=c_m)
+        self.linear_no_bias_s = LinearNoBias(in_features=c_s_inputs, out_features=c_m)
+        self.blocks = nn.ModuleList(
+            MSABlock(c_m=c_m, c_z=c_z, is_last_block=(i + 1 == n_blocks), msa_dropout=msa_dropout,
+                     pair_dropout=pair_dropout, msa_chunk_size=self.msa_chunk_size, msa_max_size=self.msa_max_size,
+                     hidden_scale_up=hidden_scale_up) for i in range(n_blocks))
+
+    @torch.no_grad()
+    def forward(self, input_feature_dict: dict, z: torch.Tensor, s_inputs: torch.Tensor, pair_mask: torch.Tensor,
+                triangle_multiplicative: str = "torch", triangle_attention: str = "torch",
+                inplace_safe: bool = False, chunk_size: Optional[int] = None) -> torch.Tensor:
+        """z [N, N, c_z] (or [1, N, N, c_z]) -> updated z.  ``input_feature_dict``: "msa" [N_msa, N] int64 classes,
+        "has_deletion" and "deletion_value" [N_msa, N]."""
+        if self.n_blocks < 1 or "msa" not in input_feature_dict or input_feature_dict["msa"].dim() < 2:
+            return z
+        if self.training:
+            raise RuntimeError("MSAModule: eval mode only")
+        msa = input_feature_dict["msa"]
+        idx = sample_msa_indices(msa.shape[-2], msa.device, self.msa_configs["test_lowerb"], self.msa_configs["strategy"])
+        if self.msa_configs["test_cutoff"] > 0:
+            idx = idx[:self.msa_configs["test_cutoff"]]
+        feat = {k: torch.index_select(input_feature_dict[k], -2, idx) for k in self.input_feature}
+        onehot = torch.zeros(*feat["msa"].shape, 32, dtype=torch.float32, device=msa.device)
+        onehot.scatter_(feat["msa"].dim(), feat["msa"].unsqueeze(-1), 1)
+        sample = torch.cat([onehot, feat["has_deletion"].reshape(*onehot.shape[:-1], 1).float(),
+                            feat["deletion_value"].reshape(*onehot.shape[:-1], 1).float()], dim=-1)
+        m = self.linear_no_bias_m(sample) + self.linear_no_bias_s(s_inputs.float())
+        if m.dim() == 4:
+            m = m[0]
+        m = m.contiguous()
+        first = True
+        for block in self.blocks:
+            m, z = block(m, z, pair_mask, inplace_safe=inplace_safe or not first, chunk_size=chunk_size)
+            first = False               # every later block works on the copy the first one made
+        return z

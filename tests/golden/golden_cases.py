@@ -45,7 +45,13 @@ CASES = {
     # one block of the MSA module (outer product mean, MSA stack, pair-only Pairformer block), padding mask
     "msa_block_n20": dict(kind="msa_block", n=20, n_msa=12, c_m=64, seed=71, wseed=17, pad=3, last=False),
     "msa_block_last_n16": dict(kind="msa_block", n=16, n_msa=7, c_m=64, seed=72, wseed=18, pad=0, last=True),
+    # the whole MSA module: feature embedding, 3 blocks (the last without an MSA stack); all MSA rows are used, in order
+    "msa_module_n18": dict(kind="msa_module", n=18, n_msa=11, n_blocks=3, c_s_inputs=449, seed=81, wseed=19, pad=2),
 }
+
+# sampling made deterministic: the lower bound exceeds the number of rows, so all of them are taken, first to last
+MSA_CONFIGS = {"enable": True, "strategy": "topk", "sample_cutoff": {"train": 512, "test": 16384},
+               "min_size": {"train": 1, "test": 1 << 30}}
 
 
 def make_inputs(case: dict) -> dict:
@@ -60,6 +66,11 @@ def make_inputs(case: dict) -> dict:
             mask = (torch.rand(case["n_msa"], case["n"], generator=g) > case["p_drop"]).float()
             mask[0] = 1                                  # the query sequence is never masked
         return {"m": m, "msa_mask": mask}
+    if kind == "msa_module":
+        n, sr = case["n"], case["n_msa"]
+        return {"msa": torch.randint(0, 32, (sr, n), generator=g), "has_deletion": (torch.rand(sr, n, generator=g) > 0.8).float(),
+                "deletion_value": torch.rand(sr, n, generator=g), "z": torch.randn(n, n, 128, generator=g),
+                "s_inputs": torch.randn(n, case["c_s_inputs"], generator=g), "mask": padding_mask(n, case.get("pad", 0))}
     if kind == "msa_block":
         n = case["n"]
         return {"m": torch.randn(case["n_msa"], n, case["c_m"], generator=g), "z": torch.randn(n, n, 128, generator=g),

@@ -137,6 +137,13 @@ def main() -> None:
             out[name + ".z"] = z.numpy()
             if m is not None:
                 out[name + ".m"] = m.numpy()
+        elif kind == "msa_module":
+            from golden_cases import MSA_CONFIGS
+
+            mod = ref_pf.MSAModule(n_blocks=case["n_blocks"], c_s_inputs=case["c_s_inputs"], msa_configs=MSA_CONFIGS).eval()
+            randomize_parameters_(mod, case["wseed"])
+            feat = {k: inp[k] for k in ("msa", "has_deletion", "deletion_value")}
+            out[name + ".z"] = mod(feat, inp["z"].clone(), inp["s_inputs"], inp["mask"]).numpy()
         else:
             raise ValueError(kind)
         print(name, {k: v.shape for k, v in out.items() if k.startswith(name + ".")})
@@ -154,6 +161,11 @@ def main() -> None:
     msa = ref_pf.MSABlock().eval()
     with open(os.path.join(HERE, "msa_block_state_dict_keys.json"), "w") as f:
         json.dump({k: list(v.shape) for k, v in msa.state_dict().items()}, f, indent=0, sort_keys=True)
+    from golden_cases import MSA_CONFIGS
+
+    mm = ref_pf.MSAModule(n_blocks=2, msa_configs=MSA_CONFIGS).eval()
+    with open(os.path.join(HERE, "msa_module_state_dict_keys.json"), "w") as f:
+        json.dump({k: list(v.shape) for k, v in mm.state_dict().items()}, f, indent=0, sort_keys=True)
     path = os.path.join(HERE, "pairformer_golden.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")

@@ -39,6 +39,10 @@ def build_module(kind: str, case: dict) -> torch.nn.Module:
     elif kind == "msa_block":
         from protenix_b200.msa import MSABlock
         m = MSABlock(c_m=case.get("c_m", 64), c_z=128, c_hidden=32, is_last_block=case.get("last", False))
+    elif kind == "msa_module":
+        from golden_cases import MSA_CONFIGS
+        from protenix_b200.msa import MSAModule
+        m = MSAModule(n_blocks=case["n_blocks"], c_s_inputs=case["c_s_inputs"], msa_configs=MSA_CONFIGS)
     elif kind == "recycle":
         m = px.RecyclingTrunk(n_blocks=case["n_blocks"], c_s=case["c_s"], N_cycle=case["n_cycle"])
     else:

@@ -143,3 +143,27 @@ def test_outer_product_mean_in_blocks_of_rows_is_the_same_to_the_bit(monkeypatch
     ref = z.cpu() + O.outer_product_mean(m.cpu(), mask.cpu(), params_of(mod))
     assert relf(parts, ref) < TOL
     px.ops.device_error_flags()
+
+
+@pytest.mark.parametrize("zdtype", [torch.float32, torch.bfloat16])
+def test_msa_module_against_reference_vector(zdtype):
+    """The whole MSA module (feature embedding, three blocks) against the reference's own output; and with the
+    reference's default random sampling of MSA rows the module still runs and returns a finite z of the same shape."""
+    name = "msa_module_n18"
+    case = CASES[name]
+    inp = make_inputs(case)
+    mod = build_module("msa_module", case).to(DEV)
+    feat = {k: inp[k].to(DEV) for k in ("msa", "has_deletion", "deletion_value")}
+    z_in = inp["z"].to(zdtype).to(DEV)
+    z = mod(feat, z_in, inp["s_inputs"].to(DEV), inp["mask"].to(DEV))
+    assert relf(z, golden()[name + ".z"]) < (1.5e-2 if zdtype == torch.float32 else 2.5e-2)   # three blocks deep
+    assert torch.equal(z_in.cpu(), inp["z"].to(zdtype))                  # the caller's z is not written
+    from protenix_b200.msa import MSAModule
+    from protenix_b200.init_utils import randomize_parameters_
+
+    torch.manual_seed(0)
+    rnd = randomize_parameters_(MSAModule(n_blocks=2, msa_configs={"enable": True, "strategy": "random"}), 4).eval().to(DEV)
+    z2 = rnd(feat, z_in, inp["s_inputs"].to(DEV), inp["mask"].to(DEV))
+    assert z2.shape == z_in.shape and torch.isfinite(z2.float()).all()
+    assert rnd({}, z_in, inp["s_inputs"].to(DEV), inp["mask"].to(DEV)) is z_in      # no MSA features: z comes back as it is
+    px.ops.device_error_flags()

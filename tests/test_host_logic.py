@@ -28,6 +28,21 @@ def test_msa_block_state_dict_matches_reference_layout():
     assert not any(k.startswith("msa_stack") for k in last) and "outer_product_mean_msa.linear_out.bias" in last
 
 
+def test_msa_module_state_dict_matches_reference_layout():
+    import sys
+    sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+    from golden_cases import MSA_CONFIGS
+    from protenix_b200.msa import MSAModule
+
+    ref = json.load(open(os.path.join(ROOT, "tests", "golden", "msa_module_state_dict_keys.json")))
+    mod = MSAModule(n_blocks=2, msa_configs=MSA_CONFIGS)
+    assert {k: list(v.shape) for k, v in mod.state_dict().items()} == ref
+    assert mod.msa_configs["test_lowerb"] == 1 << 30 and mod.msa_max_size == 512
+    with pytest.raises(RuntimeError):          # no CPU path
+        mod.eval()({"msa": torch.zeros(3, 4, dtype=torch.long), "has_deletion": torch.zeros(3, 4),
+                    "deletion_value": torch.zeros(3, 4)}, torch.zeros(4, 4, 128), torch.zeros(4, 449), torch.ones(4, 4))
+
+
 def test_stack_keys_and_pair_only_block():
     st = px.PairformerStack(n_blocks=2)
     keys = list(st.state_dict())

@@ -47,6 +47,10 @@ def test_oracle_matches_reference_vectors(name):
         assert (m is None) == case["last"]
         if m is not None:
             assert relf(m, g[name + ".m"]) < TOL
+    elif kind == "msa_module":
+        z = O.msa_module(inp["msa"], inp["has_deletion"], inp["deletion_value"], inp["z"], inp["s_inputs"], inp["mask"], p,
+                         n_blocks=case["n_blocks"])
+        assert relf(z, g[name + ".z"]) < TOL
     else:
         raise AssertionError(kind)
 
