@@ -206,7 +206,8 @@ def recycle_update(x: torch.Tensor, x_init: torch.Tensor, p: Params, ln: str, li
 
 
 def recycling_trunk(s_init: torch.Tensor, z_init: torch.Tensor, pair_mask: Optional[torch.Tensor], p: Params,
-                    n_blocks: int, n_cycle: int, n_heads: int = 16) -> Tuple[torch.Tensor, torch.Tensor]:
+                    n_blocks: int, n_cycle: int, n_heads: int = 16, msa: Optional[dict] = None,
+                    msa_n_blocks: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
     """The recycling loop around the Pairformer stack, without template embedder and MSA module.
 
     Follows protenix/model/protenix.py:230-296: z and s start at zero (:230-231); every cycle
@@ -217,6 +218,9 @@ def recycling_trunk(s_init: torch.Tensor, z_init: torch.Tensor, pair_mask: Optio
     s = torch.zeros_like(s_init)
     for _ in range(n_cycle):
         z = recycle_update(z, z_init, p, "layernorm_z_cycle", "linear_no_bias_z_cycle")
+        if msa is not None and msa_n_blocks > 0:        # protenix/model/protenix.py:258-267, between the two updates
+            z = msa_module(msa["msa"], msa["has_deletion"], msa["deletion_value"], z, msa["s_inputs"], pair_mask,
+                           _sub(p, "msa_module"), msa_n_blocks)
         s = recycle_update(s, s_init, p, "layernorm_s", "linear_no_bias_s")
         s, z = pairformer_stack(s, z, pair_mask, _sub(p, "pairformer_stack"), n_blocks, n_heads)
     return s, z

@@ -47,6 +47,9 @@ CASES = {
     "msa_block_last_n16": dict(kind="msa_block", n=16, n_msa=7, c_m=64, seed=72, wseed=18, pad=0, last=True),
     # the whole MSA module: feature embedding, 3 blocks (the last without an MSA stack); all MSA rows are used, in order
     "msa_module_n18": dict(kind="msa_module", n=18, n_msa=11, n_blocks=3, c_s_inputs=449, seed=81, wseed=19, pad=2),
+    # the trunk's recycling loop with the MSA module inside: 2 cycles x (2 MSA blocks + 2 Pairformer blocks)
+    "trunk_msa_n16": dict(kind="trunk_msa", n=16, n_msa=6, c_s=384, n_blocks=2, msa_n_blocks=2, n_cycle=2, c_s_inputs=449,
+                          seed=91, wseed=20, pad=2),
 }
 
 # sampling made deterministic: the lower bound exceeds the number of rows, so all of them are taken, first to last
@@ -66,9 +69,10 @@ def make_inputs(case: dict) -> dict:
             mask = (torch.rand(case["n_msa"], case["n"], generator=g) > case["p_drop"]).float()
             mask[0] = 1                                  # the query sequence is never masked
         return {"m": m, "msa_mask": mask}
-    if kind == "msa_module":
+    if kind in ("msa_module", "trunk_msa"):
         n, sr = case["n"], case["n_msa"]
-        return {"msa": torch.randint(0, 32, (sr, n), generator=g), "has_deletion": (torch.rand(sr, n, generator=g) > 0.8).float(),
+        extra = {"s": torch.randn(n, case["c_s"], generator=g)} if kind == "trunk_msa" else {}
+        return {**extra, "msa": torch.randint(0, 32, (sr, n), generator=g), "has_deletion": (torch.rand(sr, n, generator=g) > 0.8).float(),
                 "deletion_value": torch.rand(sr, n, generator=g), "z": torch.randn(n, n, 128, generator=g),
                 "s_inputs": torch.randn(n, case["c_s_inputs"], generator=g), "mask": padding_mask(n, case.get("pad", 0))}
     if kind == "msa_block":

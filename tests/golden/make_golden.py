@@ -144,6 +144,31 @@ def main() -> None:
             randomize_parameters_(mod, case["wseed"])
             feat = {k: inp[k] for k in ("msa", "has_deletion", "deletion_value")}
             out[name + ".z"] = mod(feat, inp["z"].clone(), inp["s_inputs"], inp["mask"]).numpy()
+        elif kind == "trunk_msa":
+            from golden_cases import MSA_CONFIGS
+
+            class TrunkMsa(torch.nn.Module):        # protenix/model/protenix.py:230-296 without the template embedder
+                def __init__(self):
+                    super().__init__()
+                    self.linear_no_bias_z_cycle = ref_prim.LinearNoBias(in_features=128, out_features=128)
+                    self.linear_no_bias_s = ref_prim.LinearNoBias(in_features=case["c_s"], out_features=case["c_s"])
+                    self.layernorm_z_cycle = ref_layers.LayerNorm(128)
+                    self.layernorm_s = ref_layers.LayerNorm(case["c_s"])
+                    self.pairformer_stack = ref_pf.PairformerStack(n_blocks=case["n_blocks"], c_s=case["c_s"])
+                    self.msa_module = ref_pf.MSAModule(n_blocks=case["msa_n_blocks"], c_s_inputs=case["c_s_inputs"],
+                                                       msa_configs=MSA_CONFIGS)
+
+            mod = TrunkMsa().eval()
+            randomize_parameters_(mod, case["wseed"])
+            feat = {k: inp[k] for k in ("msa", "has_deletion", "deletion_value")}
+            z, s = torch.zeros_like(inp["z"]), torch.zeros_like(inp["s"])
+            for _ in range(case["n_cycle"]):
+                z = inp["z"] + mod.linear_no_bias_z_cycle(mod.layernorm_z_cycle(z))
+                z = mod.msa_module(feat, z, inp["s_inputs"], pair_mask=inp["mask"])
+                s = inp["s"] + mod.linear_no_bias_s(mod.layernorm_s(s))
+                s, z = mod.pairformer_stack(s, z, pair_mask=inp["mask"])
+            out[name + ".z"] = z.numpy()
+            out[name + ".s"] = s.numpy()
         else:
             raise ValueError(kind)
         print(name, {k: v.shape for k, v in out.items() if k.startswith(name + ".")})

@@ -43,6 +43,10 @@ def build_module(kind: str, case: dict) -> torch.nn.Module:
         from golden_cases import MSA_CONFIGS
         from protenix_b200.msa import MSAModule
         m = MSAModule(n_blocks=case["n_blocks"], c_s_inputs=case["c_s_inputs"], msa_configs=MSA_CONFIGS)
+    elif kind == "trunk_msa":
+        from golden_cases import MSA_CONFIGS
+        m = px.RecyclingTrunk(n_blocks=case["n_blocks"], c_s=case["c_s"], N_cycle=case["n_cycle"],
+                              msa_n_blocks=case["msa_n_blocks"], c_s_inputs=case["c_s_inputs"], msa_configs=MSA_CONFIGS)
     elif kind == "recycle":
         m = px.RecyclingTrunk(n_blocks=case["n_blocks"], c_s=case["c_s"], N_cycle=case["n_cycle"])
     else:

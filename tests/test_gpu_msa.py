@@ -167,3 +167,18 @@ def test_msa_module_against_reference_vector(zdtype):
     assert z2.shape == z_in.shape and torch.isfinite(z2.float()).all()
     assert rnd({}, z_in, inp["s_inputs"].to(DEV), inp["mask"].to(DEV)) is z_in      # no MSA features: z comes back as it is
     px.ops.device_error_flags()
+
+
+def test_recycling_trunk_with_msa_module_against_reference_vector():
+    """Two recycling cycles of (pair update, MSA module, single update, Pairformer stack) against the reference's own
+    loop (protenix/model/protenix.py:230-296 without the template embedder)."""
+    name = "trunk_msa_n16"
+    case = CASES[name]
+    inp = make_inputs(case)
+    mod = build_module("trunk_msa", case).to(DEV)
+    feat = {k: inp[k].to(DEV) for k in ("msa", "has_deletion", "deletion_value")}
+    s, z = mod(inp["s"].to(DEV), inp["z"].to(DEV), inp["mask"].to(DEV), input_feature_dict=feat,
+               s_inputs=inp["s_inputs"].to(DEV))
+    g = golden()
+    assert relf(z, g[name + ".z"]) < 2e-2 and relf(s, g[name + ".s"]) < 2e-2        # eight blocks deep
+    px.ops.device_error_flags()

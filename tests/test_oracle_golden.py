@@ -51,6 +51,11 @@ def test_oracle_matches_reference_vectors(name):
         z = O.msa_module(inp["msa"], inp["has_deletion"], inp["deletion_value"], inp["z"], inp["s_inputs"], inp["mask"], p,
                          n_blocks=case["n_blocks"])
         assert relf(z, g[name + ".z"]) < TOL
+    elif kind == "trunk_msa":
+        msa = {k: inp[k] for k in ("msa", "has_deletion", "deletion_value", "s_inputs")}
+        s, z = O.recycling_trunk(inp["s"], inp["z"], inp["mask"], p, n_blocks=case["n_blocks"], n_cycle=case["n_cycle"],
+                                 msa=msa, msa_n_blocks=case["msa_n_blocks"])
+        assert relf(z, g[name + ".z"]) < TOL and relf(s, g[name + ".s"]) < TOL
     else:
         raise AssertionError(kind)
 
