@@ -576,14 +576,14 @@ def triatt_out(o: torch.Tensor, z: torch.Tensor, ln_w, ln_b, w_g, w_o, eps: floa
     return z
 
 
-def pair_bias_rows(z: torch.Tensor, ln_w, ln_b: Optional[torch.Tensor], w: torch.Tensor, eps: float = 1e-5
-                   ) -> torch.Tensor:
-    """bias[h, u, t] for a row slab z [n_u][n_t][128]."""
+def pair_bias_rows(z: torch.Tensor, ln_w, ln_b: Optional[torch.Tensor], w: torch.Tensor, eps: float = 1e-5,
+                   zn: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bias[h, u, t] for a row slab z [n_u][n_t][128].  zn: the standardised copy of an fp32 slab, if at hand."""
     n_u, n_t = _slab(z)
     heads = w.shape[0]
     w = _w(w, _zfmt(z), (heads, C_Z), "w")
     out = torch.empty(heads, n_u, n_t, dtype=torch.float32, device=z.device)
-    rows, rows_dt = _rows_of(z, None, eps)
+    rows, rows_dt = _rows_of(z, zn, eps)
     _launch("px_pair_bias_proj", _lib.load().px_pair_bias_proj, _ptr(rows), rows_dt, _ptr(ln_w), _ptr(ln_b),
             _ptr(w), _ptr(out), n_u * n_t, heads, float(eps), _stream(z))
     return out

@@ -91,10 +91,10 @@ class CudaStages:
                                    mod.linear_no_bias_a.weight, mod.linear_no_bias_b.weight,
                                    mod.linear_no_bias.weight, mod.layernorm1.eps, out=out)
 
-    def pair_bias(self, mod, z):
+    def pair_bias(self, mod, z, zn=None):
         b = mod.layernorm_z.bias
         return ops.pair_bias_rows(z, self._f(mod.layernorm_z.weight), None if b is None else self._f(b),
-                                  mod.linear_nobias_z.weight, mod.layernorm_z.eps)
+                                  mod.linear_nobias_z.weight, mod.layernorm_z.eps, zn=zn)
 
     def single_layer_norm(self, ln, x):
         return ln(x)
@@ -365,11 +365,13 @@ class ShardedPairformer:
         cuts = [8 * (units * i // k) for i in range(k + 1)]
         return [(cuts[i], cuts[i + 1]) for i in range(k) if cuts[i + 1] > cuts[i]]
 
-    def _tri_mul_peer(self, px: PeerExchange, mod, z_loc, mask_loc, incoming: bool) -> None:
+    def _tri_mul_peer(self, px: PeerExchange, mod, z_loc, mask_loc, incoming: bool, zn=None) -> None:
+        """``zn``: the standardised copy of an fp32 z_loc, when the caller has it already."""
         st, p, me = self.stages, self.world, self.rank
         nl, n, _ = z_loc.shape
         cp, ldn = 128 // p, (n + 7) // 8 * 8
-        zn = st.standardised(z_loc, mod.layer_norm_in.eps)
+        if zn is None:
+            zn = st.standardised(z_loc, mod.layer_norm_in.eps)
         halves = [(0, cp)] if cp < 2 else [(0, cp // 2), (cp // 2, cp)]
         a_full = px.local["a"].tensor((cp, n, ldn), torch.float16)
         b_full = px.local["b"].tensor((cp, n, ldn), torch.float16)
@@ -508,9 +510,13 @@ class ShardedPairformer:
                 mask_t_loc = pair_mask.t()[rows].contiguous()
             else:
                 mask_cols = pair_mask[:, rows].contiguous()
+        zn_final = None      # fp32 z: the standardised copy made for a block's pair bias serves the next block's first update
         for blk in self.blocks:
             if px is not None:
-                self._tri_mul_peer(px, blk.tri_mul_out, z_loc, mask_loc, incoming=False)
+                zn_first = zn_final if zn_final is not None and zn_eps == blk.tri_mul_out.layer_norm_in.eps else None
+                zn_final = None
+                self._tri_mul_peer(px, blk.tri_mul_out, z_loc, mask_loc, incoming=False, zn=zn_first)
+                del zn_first
                 self._tri_mul_peer(px, blk.tri_mul_in, z_loc, mask_loc, incoming=True)
                 zr = self._tri_att_pair_peer(px, blk.tri_att_start, blk.tri_att_end, z_loc, mask_loc, mask_cols)
                 self.stages.transition(blk.pair_transition, zr, out=z_loc)    # reads the received rows (or z_loc itself)
@@ -524,7 +530,10 @@ class ShardedPairformer:
                 del zt
                 self.stages.transition(blk.pair_transition, z_loc)
             if blk.c_s > 0 and s is not None:
-                bias = self.stages.pair_bias(blk.attention_pair_bias, z_loc)        # reads the block's final z
+                if px is not None:
+                    zn_eps = blk.attention_pair_bias.layernorm_z.eps
+                    zn_final = self.stages.standardised(z_loc, zn_eps)              # None for bf16 rows
+                bias = self.stages.pair_bias(blk.attention_pair_bias, z_loc, zn=zn_final)   # reads the block's final z
                 if side is None:
                     s = self._single_branch(blk, s, bias)
                 else:               # the pair path never reads s: the rest runs beside the next block's pair path

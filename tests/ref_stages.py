@@ -83,7 +83,7 @@ class TorchStages:
         out.copy_(z + upd)
         return out
 
-    def pair_bias(self, mod, z):
+    def pair_bias(self, mod, z, zn=None):
         return (_ln(z, mod.layernorm_z) @ mod.linear_nobias_z.weight.T).permute(2, 0, 1).contiguous()
 
     def single_layer_norm(self, ln, x):
