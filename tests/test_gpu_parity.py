@@ -234,6 +234,27 @@ def test_stack_error_growth_stays_in_budget():
         assert relf(z1, z0) < TOL_STACK and relf(s1, s0) < TOL_STACK
 
 
+def test_confidence_head_stack_in_the_fp32_residual_path():
+    """The confidence head runs a 4-block PairformerStack on an fp32 pair tensor outside autocast
+    (protenix/model/modules/confidence.py:99-106, 307-315).  The fp32-residual path (fp16 operands of standardised
+    rows, fp32 accumulation, statistics and residuals) keeps that stack within 2e-3 of the fp64 oracle -- the level of
+    TF32 arithmetic, five times tighter than the per-block bound of the 16-bit path."""
+    n, nb = 96, 4
+    g = torch.Generator().manual_seed(77)
+    z, s = torch.randn(n, n, 128, generator=g), torch.randn(n, 384, generator=g)
+    mask = padding_mask(n, 9)
+    m = build_module("stack", dict(n_blocks=nb, c_s=384, wseed=41)).to(DEV)
+    # the fp32 oracle: in fully masked rows the reference's fp32 sum -1e9 + logit drops the logit (a uniform average),
+    # which is the behaviour to match; an fp64 oracle keeps it and differs there by construction
+    s0, z0 = O.pairformer_stack(s, z, mask, params_of(m), n_blocks=nb)
+    s1, z1 = m(cuda(s), cuda(z), cuda(mask))
+    assert z1.dtype == torch.float32
+    assert relf(z1, z0) < 2e-3 and relf(s1, s0) < 2e-3, (relf(z1, z0), relf(s1, s0))
+    v = n - 9                                        # and against fp64 where the mask leaves something to attend to
+    _, z64 = O.pairformer_stack(s.double(), z.double(), mask.double(), params_of(m, torch.float64), n_blocks=nb)
+    assert relf(z1[:v, :v], z64[:v, :v]) < 2e-3
+
+
 def test_block_api_contract():
     n = 33
     g = torch.Generator().manual_seed(2)
