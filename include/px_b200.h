@@ -91,6 +91,14 @@ PX_API int64_t px_ld_mask(int64_t n);
  * layer_norm_cuda_kernel.cu:145-388).  Unlike the reference it launches on `stream`. */
 PX_API int32_t px_layer_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* invvar,
                           int64_t rows, int64_t cols, float eps, int32_t dtype, void* stream);
+/* Backward of the same op: dx (type of x), and, when wanted (non-NULL), dgamma and dbeta (type of x, [cols]).
+ * mean and invvar are the fp32 statistics the forward returned; gamma NULL = no scale.  scratch: 2 * cols floats of
+ * device memory when dgamma or dbeta is wanted (zeroed here).  cols <= 16384.
+ * Replaces backward_{none,with_bias,with_weight,with_both}_affine of
+ * protenix/model/layer_norm/kernel/layer_norm_cuda.cpp:162-179 (kernels layer_norm_cuda_kernel.cu:412-977). */
+PX_API int32_t px_layer_norm_bwd(const void* dy, const void* x, const float* mean, const float* invvar, const void* gamma,
+                          void* dx, void* dgamma, void* dbeta, float* scratch, int64_t rows, int64_t cols,
+                          int32_t dtype, void* stream);
 
 /* ---- Standardised copy of fp32 rows --------------------------------------------------------
  * zn[row] = fp16((z[row] - mean) * rsqrt(var + eps)) over `rows` rows of 128 channels: LayerNorm without scale and

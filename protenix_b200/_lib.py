@@ -24,6 +24,7 @@ SIGNATURES = {
     "px_ld": (I64, [I64]),
     "px_ld_mask": (I64, [I64]),
     "px_layer_norm_fwd": (I32, [P, P, P, P, P, P, I64, I64, F, I32, P]),
+    "px_layer_norm_bwd": (I32, [P, P, P, P, P, P, P, P, P, I64, I64, I32, P]),
     "px_trimul_in_proj": (I32, [P, I32, P, P, P, P, P, P, P, P, P, I64, I64, I64, I32, F, P]),
     "px_trimul_contract": (I32, [P, P, P, I64, I64, I64, P]),
     "px_device_error_flags": (I32, [P]),

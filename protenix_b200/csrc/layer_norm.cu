@@ -267,7 +267,105 @@ static cudaError_t dispatch(const void* x, const void* g, const void* b, void* y
   return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Backward.  With xhat = (x - mean) * invvar and g = dy * gamma (g = dy without a scale):
+//   dx = invvar * (g - mean_c(g) - xhat * mean_c(g * xhat)),   dgamma = sum_rows dy * xhat,   dbeta = sum_rows dy.
+// One warp per row, two passes over the row (the second is served by L1/L2); the column sums of a CTA's rows are
+// collected in shared memory and added to an fp32 scratch of 2 * cols values with one atomic per column and CTA,
+// which a second kernel converts to the parameter type.
+template <typename T>
+__global__ void __launch_bounds__(256) ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                                     const float* __restrict__ mean, const float* __restrict__ invvar,
+                                                     const T* __restrict__ gamma, T* __restrict__ dx,
+                                                     float* __restrict__ scratch, long long rows, int cols) {
+  extern __shared__ float ln_bwd_sums[];                 // [2][cols]: dgamma, dbeta partial sums of this CTA
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  if (scratch) {
+    for (int c = threadIdx.x; c < 2 * cols; c += blockDim.x) ln_bwd_sums[c] = 0.f;
+    __syncthreads();
+  }
+  const float inv_cols = 1.0f / (float)cols;
+  for (long long row = (long long)blockIdx.x * warps + warp; row < rows; row += (long long)gridDim.x * warps) {
+    const T* xr = x + (size_t)row * cols;
+    const T* dyr = dy + (size_t)row * cols;
+    const float mu = mean[row], rs = invvar[row];
+    float s1 = 0.f, s2 = 0.f;
+    for (int c = lane; c < cols; c += 32) {
+      const float g = Cvt<T>::to_f(dyr[c]) * (gamma ? Cvt<T>::to_f(gamma[c]) : 1.0f);
+      s1 += g;
+      s2 += g * ((Cvt<T>::to_f(xr[c]) - mu) * rs);
+    }
+    s1 = warp_sum(s1) * inv_cols;
+    s2 = warp_sum(s2) * inv_cols;
+    T* dxr = dx + (size_t)row * cols;
+    for (int c = lane; c < cols; c += 32) {
+      const float d = Cvt<T>::to_f(dyr[c]), xh = (Cvt<T>::to_f(xr[c]) - mu) * rs;
+      const float g = d * (gamma ? Cvt<T>::to_f(gamma[c]) : 1.0f);
+      dxr[c] = Cvt<T>::from_f(rs * (g - s1 - xh * s2));
+      if (scratch) {
+        atomicAdd(&ln_bwd_sums[c], d * xh);
+        atomicAdd(&ln_bwd_sums[cols + c], d);
+      }
+    }
+  }
+  if (scratch) {
+    __syncthreads();
+    for (int c = threadIdx.x; c < 2 * cols; c += blockDim.x) atomicAdd(&scratch[c], ln_bwd_sums[c]);
+  }
+}
+
+template <typename T>
+__global__ void ln_bwd_finish_kernel(const float* __restrict__ scratch, T* __restrict__ dgamma, T* __restrict__ dbeta,
+                                     int cols) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  if (dgamma) dgamma[c] = Cvt<T>::from_f(scratch[c]);
+  if (dbeta) dbeta[c] = Cvt<T>::from_f(scratch[cols + c]);
+}
+
+template <typename T>
+static cudaError_t dispatch_bwd(const void* dy, const void* x, const float* mean, const float* invvar, const void* gamma,
+                                void* dx, void* dgamma, void* dbeta, float* scratch, long long rows, int cols,
+                                cudaStream_t st) {
+  const bool sums = dgamma || dbeta;
+  const size_t smem = sums ? (size_t)2 * cols * sizeof(float) : 0;
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(ln_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return cudaErrorInvalidValue;
+  if (sums) {
+    const cudaError_t e = cudaMemsetAsync(scratch, 0, (size_t)2 * cols * sizeof(float), st);
+    if (e != cudaSuccess) return e;
+  }
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long want = (rows + 7) / 8;
+  const int grid = (int)(want < 4ll * sms ? want : 4ll * sms);
+  if (rows > 0)
+    ln_bwd_kernel<T><<<grid, 256, smem, st>>>((const T*)dy, (const T*)x, mean, invvar, (const T*)gamma, (T*)dx,
+                                              sums ? scratch : nullptr, rows, cols);
+  if (sums)
+    ln_bwd_finish_kernel<T><<<(cols + 255) / 256, 256, 0, st>>>(scratch, (T*)dgamma, (T*)dbeta, cols);
+  return cudaGetLastError();
+}
+
 }  // namespace px
+
+extern "C" int32_t px_layer_norm_bwd(const void* dy, const void* x, const float* mean, const float* invvar,
+                                     const void* gamma, void* dx, void* dgamma, void* dbeta, float* scratch,
+                                     int64_t rows, int64_t cols, int32_t dtype, void* stream) {
+  if (cols <= 0 || cols > 16384 || rows < 0) return PX_ERR_BAD_ARG;
+  if ((dgamma || dbeta) && !scratch) return PX_ERR_BAD_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (rows > 0 && (!dy || !x || !mean || !invvar || !dx)) return PX_ERR_BAD_ARG;
+  cudaError_t e;
+  switch (dtype) {   // rows == 0 still runs the (empty) reduction so that the parameter gradients come out as zeros
+    case PX_F32: e = px::dispatch_bwd<float>(dy, x, mean, invvar, gamma, dx, dgamma, dbeta, scratch, rows, (int)cols, st); break;
+    case PX_BF16: e = px::dispatch_bwd<px::bf16>(dy, x, mean, invvar, gamma, dx, dgamma, dbeta, scratch, rows, (int)cols, st); break;
+    case PX_F16: e = px::dispatch_bwd<__half>(dy, x, mean, invvar, gamma, dx, dgamma, dbeta, scratch, rows, (int)cols, st); break;
+    default: return PX_ERR_UNSUPPORTED;
+  }
+  return e == cudaSuccess ? PX_OK : PX_ERR_LAUNCH;
+}
 
 extern "C" int32_t px_layer_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean,
                                      float* invvar, int64_t rows, int64_t cols, float eps, int32_t dtype,

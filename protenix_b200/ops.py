@@ -205,6 +205,30 @@ def layer_norm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[t
     return (y, mean, invvar) if return_stats else y
 
 
+def layer_norm_bwd(dy: torch.Tensor, x: torch.Tensor, mean: torch.Tensor, invvar: torch.Tensor,
+                   weight: Optional[torch.Tensor], want_weight: bool, want_bias: bool):
+    """Gradients of layer_norm: (dx, dweight or None, dbias or None) from the upstream gradient dy, the input x and the
+    fp32 statistics the forward returned."""
+    _need_cuda(dy, "dy")
+    _need_cuda(x, "x")
+    if dy.shape != x.shape or dy.dtype != x.dtype or x.dtype not in _DTYPE:
+        raise RuntimeError("dy must match x (float32 / bfloat16 / float16)")
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    if mean.numel() != rows or invvar.numel() != rows or mean.dtype != torch.float32 or invvar.dtype != torch.float32:
+        raise RuntimeError("mean and invvar must be the float32 [rows] statistics of the forward")
+    if weight is not None and (weight.dtype != x.dtype or weight.numel() != cols):
+        raise RuntimeError(f"weight must be {x.dtype} with {cols} elements")
+    dy, x = dy.contiguous(), x.contiguous()
+    dx = torch.empty_like(x)
+    dw = torch.empty(cols, dtype=x.dtype, device=x.device) if want_weight else None
+    db = torch.empty(cols, dtype=x.dtype, device=x.device) if want_bias else None
+    scratch = torch.empty(2 * cols, dtype=torch.float32, device=x.device) if (want_weight or want_bias) else None
+    _launch("px_layer_norm_bwd", _lib.load().px_layer_norm_bwd, _ptr(dy), _ptr(x), _ptr(mean), _ptr(invvar), _ptr(weight),
+            _ptr(dx), _ptr(dw), _ptr(db), _ptr(scratch), rows, cols, _DTYPE[x.dtype], _stream(x))
+    return dx, dw, db
+
+
 def standardise_rows(z: torch.Tensor, eps: float = 1e-5, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """zn = fp16((z - mean) * rstd) over rows of 128 channels of an fp32 tensor: the rows the tensor core multiplies
     when the pair tensor is stored as fp32.  One copy serves every stage that normalises the same z."""

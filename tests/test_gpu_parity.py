@@ -55,6 +55,39 @@ def test_layer_norm_widths_dtypes_and_stats(dtype, cols):
         assert relf(mean, mu) < 1e-5 and relf(invvar, iv) < 1e-5
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,cols,scale,offset", [(200, 128, True, True), (64, 384, True, True), (33, 833, True, False),
+                                                    (77, 64, False, False), (1000, 128, True, True), (5, 9000, True, True),
+                                                    (1, 16, False, True)])
+def test_layer_norm_backward_against_autograd_of_the_oracle(rows, cols, scale, offset, dtype):
+    """dx, dweight, dbias of the LayerNorm op (the reference's extension has the matching backward_* functions,
+    layer_norm_cuda.cpp:162-179) against torch autograd through the fp64 oracle on the same (rounded) inputs."""
+    g = torch.Generator().manual_seed(rows * 7 + cols)
+    x = (torch.randn(rows, cols, generator=g) * 2 + 3).to(dtype)
+    dy = torch.randn(rows, cols, generator=g).to(dtype)
+    mod = px.LayerNorm(cols, create_scale=scale, create_offset=offset).to(DEV)
+    with torch.no_grad():
+        if scale:
+            mod.weight.copy_(1 + 0.2 * torch.randn(cols, generator=g))
+        if offset:
+            mod.bias.copy_(0.2 * torch.randn(cols, generator=g))
+    xg = x.to(DEV).requires_grad_(True)
+    y = mod(xg)
+    y.backward(dy.to(DEV))
+    x64 = x.double().requires_grad_(True)
+    w64 = mod.weight.detach().cpu().to(dtype).double().requires_grad_(True) if scale else None
+    b64 = mod.bias.detach().cpu().to(dtype).double().requires_grad_(True) if offset else None
+    O.layer_norm(x64, w64, b64).backward(dy.double())
+    tol = 2e-5 if dtype == torch.float32 else (6e-3 if dtype == torch.bfloat16 else 1e-3)
+    assert relf(xg.grad, x64.grad) < tol
+    if scale:
+        assert mod.weight.grad.dtype == mod.weight.dtype and relf(mod.weight.grad, w64.grad) < tol
+    if offset:
+        assert relf(mod.bias.grad, b64.grad) < tol
+    with torch.no_grad():                                   # the inference path is the plain kernel, same values
+        assert torch.equal(mod(x.to(DEV)), y.detach())
+
+
 def test_layer_norm_leading_dims_and_empty():
     m = px.LayerNorm(128).to(DEV)
     x = torch.randn(3, 5, 7, 128, device=DEV)
