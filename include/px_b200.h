@@ -278,6 +278,15 @@ PX_API int32_t px_opm_outer(const px_f16* a_t, const px_f16* b_t, px_f16* x, int
 PX_API int32_t px_opm_out(const px_f16* x, const px_f16* w_out, const float* bias, const float* inv_norm, const void* z_in,
                    void* z_out, int32_t z_dtype, int64_t n_i, int64_t n, int32_t add_residual, void* stream);
 
+/* ---- Row-shared dropout + residual add (training path) ---------------------------------------
+ * out[b][r][k] = residual[b][r][k] + x[b][r][k] * mask[b][k] for tensors [batches][rows][cd] and a mask [batches][cd]
+ * of zeros and 1 / (1 - p) in the same type (PX_F32, PX_BF16, PX_F16), one value per (b, k) shared by all rows;
+ * residual NULL: the product alone (the gradient with respect to x).  The product is rounded to the storage type before
+ * the add.  Replaces the Triton kernels behind dropout_add_rowwise, protenix/model/modules/fused_ops.py:40-187 (forward
+ * and backward), whose mask comes from a counter-based generator inside the kernel; here the caller draws it. */
+PX_API int32_t px_scale_add_rowwise(const void* residual, const void* x, const void* mask, void* out, int64_t batches,
+                             int64_t rows, int64_t cd, int32_t dtype, void* stream);
+
 /* ---- Exchange between the GPUs of one box (row-sharded path) ------------------------------
  * No counterpart in the reference (which runs the Pairformer on one GPU).  A peer buffer is a
  * cudaMalloc allocation whose 64-byte handle other processes on the same machine can open;

@@ -47,6 +47,7 @@ SIGNATURES = {
     "px_transition": (I32, [P, P, I32, P, P, P, P, P, I64, I32, F, P]),
     "px_pair_bias_proj": (I32, [P, I32, P, P, P, P, I64, I32, F, P]),
     "px_recycle_update": (I32, [P, P, P, I32, P, P, P, I64, F, P]),
+    "px_scale_add_rowwise": (I32, [P, P, P, P, I64, I64, I64, I32, P]),
     "px_opm_outer": (I32, [P, P, P, I64, I64, I64, P]),
     "px_opm_out": (I32, [P, P, P, P, P, P, I32, I64, I64, I32, P]),
     "px_peer_alloc": (I32, [I64, P, P]),

@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libpx_b200.so")
-SOURCES = ["api.cu", "layer_norm.cu", "trimul.cu", "trimul_in_tc.cu", "trimul_out_tc.cu", "contract_tcgen05.cu", "flash_tcgen05.cu", "triatt.cu", "triatt_in_tc.cu", "triatt_out_tc.cu", "pair_bias_tc.cu", "recycle_tc.cu", "transition_tcgen05.cu", "peer.cu", "selftest.cu", "standardise.cu", "opm_tc.cu"]
+SOURCES = ["api.cu", "layer_norm.cu", "trimul.cu", "trimul_in_tc.cu", "trimul_out_tc.cu", "contract_tcgen05.cu", "flash_tcgen05.cu", "triatt.cu", "triatt_in_tc.cu", "triatt_out_tc.cu", "pair_bias_tc.cu", "recycle_tc.cu", "transition_tcgen05.cu", "peer.cu", "selftest.cu", "standardise.cu", "opm_tc.cu", "dropout_add.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

@@ -229,6 +229,29 @@ def layer_norm_bwd(dy: torch.Tensor, x: torch.Tensor, mean: torch.Tensor, invvar
     return dx, dw, db
 
 
+def scale_add_rowwise(residual: Optional[torch.Tensor], x: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+    """residual + x * mask with mask [..., 1, C, D] shared over axis -3 of x [..., R, C, D] (residual None: x * mask)."""
+    _need_cuda(x, "x")
+    _need_cuda(mask, "mask")
+    if x.dim() < 3 or x.dtype not in _DTYPE or mask.dtype != x.dtype:
+        raise RuntimeError("x must be [..., R, C, D] in float32 / bfloat16 / float16 and the mask of the same type")
+    want = list(x.shape)
+    want[-3] = 1
+    if list(mask.shape) != want:
+        raise RuntimeError(f"mask must have shape {want}")
+    if residual is not None and (residual.shape != x.shape or residual.dtype != x.dtype or not residual.is_cuda):
+        raise RuntimeError("residual must match x")
+    x = x.contiguous()
+    residual = None if residual is None else residual.contiguous()
+    mask = mask.contiguous()
+    out = torch.empty_like(x)
+    rows, cd = x.shape[-3], x.shape[-2] * x.shape[-1]
+    batches = x.numel() // (rows * cd) if rows * cd else 0
+    _launch("px_scale_add_rowwise", _lib.load().px_scale_add_rowwise, _ptr(residual), _ptr(x), _ptr(mask), _ptr(out),
+            batches, rows, cd, _DTYPE[x.dtype], _stream(x))
+    return out
+
+
 def standardise_rows(z: torch.Tensor, eps: float = 1e-5, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """zn = fp16((z - mean) * rstd) over rows of 128 channels of an fp32 tensor: the rows the tensor core multiplies
     when the pair tensor is stored as fp32.  One copy serves every stage that normalises the same z."""

@@ -108,5 +108,6 @@ def test_unsupported_shapes_raise_clear_errors():
 def test_dropout_add_rowwise_eval_is_plain_add():
     r, x = torch.randn(3, 4, 5), torch.randn(3, 4, 5)
     assert torch.equal(px.dropout_add_rowwise(r, x, 0.25, False), r + x)
+    assert torch.equal(px.dropout_add_rowwise(r, x, 0.0, True), r + x)
     with pytest.raises(RuntimeError):
         px.dropout_add_rowwise(r, x, 0.25, True)
