@@ -93,8 +93,9 @@ class Transition(nn.Module):
         if self._fused_ok(x):
             xc = x.contiguous()
             return ops.transition(xc, torch.empty_like(xc), *self._weights(), add_residual=False)
-        # small widths (single representation, c_in = 384): LayerNorm kernel + library GEMMs
-        y = self.layernorm1(x)
-        a = F.silu(self.linear_no_bias_a(y))
-        b = self.linear_no_bias_b(y)
-        return self.linear_no_bias(a * b)
+        # small widths (single representation, c_in = 384): LayerNorm kernel + library GEMMs, fp32 arithmetic whatever
+        # the storage type of x and of the parameters
+        y = self.layernorm1(x.float().contiguous())
+        a = F.silu(F.linear(y, self.linear_no_bias_a.weight.float()))
+        b = F.linear(y, self.linear_no_bias_b.weight.float())
+        return F.linear(a * b, self.linear_no_bias.weight.float()).to(x.dtype)

@@ -71,10 +71,12 @@ class AttentionPairBias(nn.Module):
         x = self.layernorm_a(a.float().contiguous())
         lead = x.shape[:-2]
         n, h, d = x.shape[-2], self.n_heads, att.c_hidden
-        q = F.linear(x, att.linear_q.weight, att.linear_q.bias).view(*lead, n, h, d).transpose(-2, -3)
-        k = F.linear(x, att.linear_k.weight).view(*lead, n, h, d).transpose(-2, -3)
-        v = F.linear(x, att.linear_v.weight).view(*lead, n, h, d).transpose(-2, -3)
+        # fp32 arithmetic whatever the storage type of a and of the parameters (a module cast with .bfloat16() included)
+        f = lambda p: p.float()
+        q = F.linear(x, f(att.linear_q.weight), f(att.linear_q.bias)).view(*lead, n, h, d).transpose(-2, -3)
+        k = F.linear(x, f(att.linear_k.weight)).view(*lead, n, h, d).transpose(-2, -3)
+        v = F.linear(x, f(att.linear_v.weight)).view(*lead, n, h, d).transpose(-2, -3)
         o = F.scaled_dot_product_attention(q / math.sqrt(d), k, v, attn_mask=bias, scale=1.0)
         o = o.transpose(-2, -3).reshape(*lead, n, h * d)
-        o = o * torch.sigmoid(F.linear(x, att.linear_g.weight))
-        return F.linear(o, att.linear_o.weight).to(dt)
+        o = o * torch.sigmoid(F.linear(x, f(att.linear_g.weight)))
+        return F.linear(o, f(att.linear_o.weight)).to(dt)

@@ -311,6 +311,30 @@ def test_block_api_contract():
         m(s, z[:, :, :64].contiguous(), mask)
 
 
+def test_stacked_blocks_with_half_precision_modules_like_the_reference_regression_test():
+    """After the reference's TestPairformerCueqContiguity (tests/test_fused_dropout_add.py:140-221): three blocks
+    whose parameters were cast to bf16, bf16 inputs with a leading batch of one (z, s and the mask), the
+    cuEquivariance back-end names in the kwargs, in place; z must come back contiguous and finite, and equal to what
+    fp32 parameters of the same values give."""
+    n = 128
+    g = torch.Generator().manual_seed(5)
+    blocks = [build_module("block", dict(c_s=384, wseed=50 + i)).to(DEV).bfloat16() for i in range(3)]
+    z = torch.randn(1, n, n, 128, generator=g).to(torch.bfloat16).to(DEV)
+    s = torch.randn(1, n, 384, generator=g).to(torch.bfloat16).to(DEV)
+    mask = torch.ones(1, n, n, dtype=torch.bfloat16, device=DEV)
+    z_run, s_run = z.clone(), s.clone()
+    for blk in blocks:
+        s_run, z_run = blk(s_run, z_run, mask, triangle_multiplicative="cuequivariance",
+                           triangle_attention="cuequivariance", inplace_safe=True)
+        assert z_run.is_contiguous() and z_run.shape == z.shape and z_run.dtype == torch.bfloat16
+        assert s_run.shape == s.shape
+    assert torch.isfinite(z_run.float()).all() and torch.isfinite(s_run.float()).all()
+    z_ref, s_ref = z.clone(), s.clone()
+    for blk in blocks:
+        s_ref, z_ref = blk.float()(s_ref, z_ref, mask.float(), inplace_safe=True)
+    assert relf(z_run, z_ref) < 2e-2
+
+
 def test_tri_mul_add_with_inplace_returns_sum():
     n = 40
     z = cuda(torch.randn(n, n, 128, generator=torch.Generator().manual_seed(8)))
