@@ -111,3 +111,26 @@ def test_dropout_add_rowwise_eval_is_plain_add():
     assert torch.equal(px.dropout_add_rowwise(r, x, 0.0, True), r + x)
     with pytest.raises(RuntimeError):
         px.dropout_add_rowwise(r, x, 0.25, True)
+
+
+def test_msa_row_sampling_follows_the_reference_rules():
+    """protenix/model/utils.py:290-311: a size drawn from [min(lower_bound, n), n], then the first rows ('topk') or a
+    random subset without replacement ('random')."""
+    from protenix_b200.msa import sample_msa_indices
+
+    torch.manual_seed(0)
+    idx = sample_msa_indices(10, "cpu", lower_bound=1 << 30, strategy="topk")
+    assert idx.tolist() == list(range(10))                       # lower bound beyond n: every row, in order
+    torch.manual_seed(0)
+    sizes = {len(sample_msa_indices(10, "cpu", lower_bound=4, strategy="random")) for _ in range(200)}
+    assert min(sizes) >= 4 and max(sizes) == 10
+    torch.manual_seed(1)
+    idx = sample_msa_indices(50, "cpu", lower_bound=50, strategy="random")
+    assert sorted(idx.tolist()) == list(range(50)) and idx.tolist() != list(range(50))
+    torch.manual_seed(5)
+    a = sample_msa_indices(20, "cpu", 1, "random")
+    torch.manual_seed(5)                                          # the same generator calls as the reference's function
+    size = int(torch.randint(low=1, high=21, size=(1,)).item())
+    assert torch.equal(a, torch.randperm(20)[:size])
+    with pytest.raises(ValueError):
+        sample_msa_indices(5, "cpu", 1, "sequential")
