@@ -232,8 +232,8 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
           if (grow < rows) {
             const size_t off = (size_t)grow * kC + 32 * q + 4 * piece;
             const float4 rs = res[it].get();
-            store2(x_out + off, v.x + rs.x, v.y + rs.y);
-            store2(x_out + off + 2, v.z + rs.z, v.w + rs.w);
+            store2(x_out + off, fmaf(2.0f, v.x, rs.x), fmaf(2.0f, v.y, rs.y));      // the second product is of h / 2
+            store2(x_out + off + 2, fmaf(2.0f, v.z, rs.z), fmaf(2.0f, v.w, rs.w));
           }
         }
         __syncwarp();
@@ -242,8 +242,13 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
   } else if (warp >= 8) {
     // ------------------------------------------------------------------ LayerNorm -> swizzled A operand
     const int qw = warp - 8;
-    const float4 g4 = *reinterpret_cast<const float4*>(ln_w + 4 * lane);
-    const float4 b4 = *reinterpret_cast<const float4*>(ln_b + 4 * lane);
+    // The normalised rows enter the first product halved: a' = a / 2 is the argument of the gate's tanh, b' = b / 2,
+    // and h' = a' b' (1 + tanh a') = silu(a) b / 2 is what the SwiGLU warps write; the output warps double the second
+    // product.  Powers of two: nothing changes but two multiplications per hidden element that are no longer needed.
+    float4 g4 = *reinterpret_cast<const float4*>(ln_w + 4 * lane);
+    float4 b4 = *reinterpret_cast<const float4*>(ln_b + 4 * lane);
+    g4.x *= 0.5f, g4.y *= 0.5f, g4.z *= 0.5f, g4.w *= 0.5f;
+    b4.x *= 0.5f, b4.y *= 0.5f, b4.z *= 0.5f, b4.w *= 0.5f;
     const int panel_off = (lane >> 4) * 16384 + (lane & 1) * 8, chunk = (lane & 15) >> 1;
     int k = 0;
     for (int tile = first_tile; tile < n_tiles; tile += tile_step, ++k) {
@@ -335,10 +340,11 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_wa, const __grid_co
           tmem_wait_ld();
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            // silu(a) * b = 0.5 * a * b * (1 + tanh(a / 2)): one special-function op per element
+            // silu(a) * b / 2 = a' b' (1 + tanh a') with a' = a / 2, b' = b / 2 as the accumulators hold them:
+            // one special-function op, one multiplication and one fused multiply-add per element
             const float a0 = __uint_as_float(a[2 * e]), a1 = __uint_as_float(a[2 * e + 1]);
-            const float h0 = 0.5f * a0 * __uint_as_float(b[2 * e]), h1 = 0.5f * a1 * __uint_as_float(b[2 * e + 1]);
-            w[8 * hh + e] = pack_f16x2(fmaf(h0, tanh_fast(0.5f * a0), h0), fmaf(h1, tanh_fast(0.5f * a1), h1));
+            const float h0 = a0 * __uint_as_float(b[2 * e]), h1 = a1 * __uint_as_float(b[2 * e + 1]);
+            w[8 * hh + e] = pack_f16x2(fmaf(h0, tanh_fast(a0), h0), fmaf(h1, tanh_fast(a1), h1));
           }
         }
         // h overwrites the first 32 columns of H; all warps must have read their a before any of them writes:
